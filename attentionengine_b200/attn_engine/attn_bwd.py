@@ -1,0 +1,92 @@
+"""Backward launches of AttentionEngine: delta pre-pass, dQ pass, dK/dV pass.
+
+Stands in for the generated ``_attention.backward`` of the reference
+(attention_engine/core/template/tl_template/attn/attn_tl.py:582-601): ``mod_prep`` (only when
+``OnlineFunc.backward`` reads doosum), ``mod_bwd`` and ``mod_post``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from .. import runtime as rt
+
+
+@dataclass
+class BwdKernels:
+    prep: rt.Module
+    dq: rt.Module
+    dkv: rt.Module
+    bn: int
+    nbuf: int
+    stages: int
+
+
+def bwd_tile_config(D: int, DV: int):
+    """(streamed tile rows, TMEM buffers, ring depth).  Two S/dP buffers of 64 columns fit next to
+    the accumulators in the 512 TMEM columns and let the tensor pipe run ahead of the row threads."""
+    return 64, 2, 4 if max(D, DV) <= 64 else 3
+
+
+def compile_bwd(k) -> BwdKernels:
+    D, DV, low = k.D, k.DV, k.low
+    bn, nbuf, stages = bwd_tile_config(D, DV)
+    defs = f"#define AE_BWD_BN {bn}\n#define AE_BWD_NBUF {nbuf}\n#define AE_BWD_STAGES {stages}\n"
+    prelude = low.prelude_bwd + defs
+    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_PREP, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=256,
+                          smem_bytes=0, stages=0, mask_mode=k.mask_mode)
+    prep = rt.compile_module(rt.kernel_source("attn_bwd_prep.cuh", prelude=prelude), "ae_attn_bwd_prep", cfg)
+    smem_dq = 128 * (D + DV) * 2 + stages * bn * (D + DV) * 2 + 512 + 1024
+    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DQ, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=192,
+                          smem_bytes=smem_dq, stages=stages, mask_mode=k.mask_mode)
+    cfg.reserved[0] = bn
+    dq = rt.compile_module(rt.kernel_source("attn_bwd_dq.cuh", prelude=prelude), "ae_attn_bwd_dq", cfg)
+    ncs = len(low.final_names) + 1
+    smem_kv = 128 * (D + DV) * 2 + stages * bn * (D + DV) * 2 + 2 * bn * ncs * 4 + 16 + 512 + 1024
+    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DKV, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=192,
+                          smem_bytes=smem_kv, stages=stages, mask_mode=k.mask_mode)
+    cfg.reserved[0] = bn
+    dkv = rt.compile_module(rt.kernel_source("attn_bwd_dkv.cuh", prelude=prelude), "ae_attn_bwd_dkv", cfg)
+    return BwdKernels(prep, dq, dkv, bn, nbuf, stages)
+
+
+def _s3(t):
+    return (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def launch_bwd(eng, q, k, v, o, d_o, finals, custom):
+    kern = eng.kernels.bwd
+    B, Sq, Hq, Skv, Hkv = eng._check_qkv(q, k, v)
+    dev = q.device
+    if d_o.stride(3) != 1 or d_o.stride(2) % 8 or d_o.stride(1) % 8 or d_o.data_ptr() % 16:
+        d_o = d_o.contiguous()
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    p = rt.AttnBwdParams()
+    p.q, p.k, p.v, p.o, p.d_o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr()
+    p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    p.q_stride, p.k_stride, p.v_stride, p.o_stride, p.do_stride = _s3(q), _s3(k), _s3(v), _s3(o), _s3(d_o)
+    p.dq_stride, p.dk_stride, p.dv_stride = _s3(dq), _s3(dk), _s3(dv)
+    for i, f in enumerate(finals):
+        p.final_rowscales[i] = f.data_ptr()
+    delta = None
+    if eng.lowered.uses_doosum:
+        delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=dev)
+        p.delta = delta.data_ptr()
+    p.custom, p.custom_stride, keep = eng._custom_args(custom, Sq, Skv)
+    lists = eng._ensure_lists(dev, eng.block_mask if eng.extern_block_mask else None, B, Hq, Sq, Skv)
+    if lists is not None:
+        p.block_count, p.block_index = lists[0].data_ptr(), lists[1].data_ptr()
+        p.block_count_t, p.block_index_t = lists[2].data_ptr(), lists[3].data_ptr()
+    p.B, p.Hq, p.Hkv, p.Sq, p.Skv = B, Hq, Hkv, Sq, Skv
+    p.status = eng._get_status(dev).data_ptr()
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    L = rt.lib()
+    if delta is not None:
+        rt.check(L.ae_launch_attn_bwd_prep(kern.prep.handle, C.byref(p), stream), "ae_launch_attn_bwd_prep")
+    rt.check(L.ae_launch_attn_bwd_dq(kern.dq.handle, C.byref(p), stream), "ae_launch_attn_bwd_dq")
+    rt.check(L.ae_launch_attn_bwd_dkv(kern.dkv.handle, C.byref(p), stream), "ae_launch_attn_bwd_dkv")
+    return dq, dk, dv

@@ -1,0 +1,311 @@
+"""AttentionEngine / OnlineFunc: the operator API, re-pointed at the sm_100a back end.
+
+Same constructor and call signature as the reference (attention_engine/attn_engine/attn_engine.py:
+``OnlineFunc`` :16-105, ``AttentionEngine.__init__`` :109-115, shape-class dispatch
+``_select_lower_template`` :218-332, ``__call__`` :388-395).  Instead of rendering a TileLang module
+the constructor traces the user callables, lowers them to CUDA functor fragments
+(``lower.cuda_lower``), splices them into the kernel templates under ``csrc/kernels`` and compiles
+them with NVRTC through the C ABI; the call launches those kernels on the current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from .. import runtime as rt
+from ..core.transform.core import (CustomIO, SymbolicArray, SymbolScalar, Var, block_mask_counts)
+from ..lower.cuda_lower import LoweredAttention, lower_attention
+
+
+class OnlineFunc:
+    """User-defined online (streaming) row normalisation, as in the reference
+    (attn_engine.py:16-105):
+
+    * ``online_fwd(scores, online_rowscales, b, h, q_idx) -> (scores, new_rowscales, o_scale)``
+    * ``online_fwd_epilogue(o, online_rowscales, b, h, q_idx) -> (o, final_rowscales)``
+    * ``forward(scores, final_rowscales, b, h, q_idx, kv_idx) -> p`` (recompute for backward)
+    * ``backward(dp, scores, final_rowscales, doosum_rowscales, b, h, q_idx, kv_idx) -> dscores``
+    * ``combine(final_rowscales) -> o_scale`` (split-KV merge)
+    """
+
+    def __init__(self, online_rowscales: dict, final_rowscales: dict, external_fwd_tensors: CustomIO):
+        self.online_rowscales = online_rowscales
+        self.final_rowscales = final_rowscales
+        self.vars = {"scores": SymbolicArray(), "o_scale": None}
+        self.external_fwd_tensors = external_fwd_tensors
+        self.doosum_rowscales = SymbolicArray("doosum", Var("doosum"), shape_idx=["block_M"])
+
+    @staticmethod
+    def online_fwd(scores, online_rowscales, b, h, q_idx):
+        return scores, online_rowscales, SymbolScalar("o_scale", Var("1"))
+
+    @staticmethod
+    def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+        return o, online_rowscales
+
+    @staticmethod
+    def forward(scores, final_rowscales, b, h, q_idx, kv_idx):
+        return scores
+
+    @staticmethod
+    def backward(dp, scores, final_rowscales, doosum_rowscales, b, h, q_idx, kv_idx):
+        return dp
+
+    @staticmethod
+    def combine(final_rowscales):
+        return SymbolScalar("o_scale", Var("1"))
+
+
+class H100:
+    """Placeholder accepted for the reference's ``device=`` argument (autotuner/arch); the back end
+    always targets B200."""
+
+
+_TORCH_DTYPES = {torch.float16: rt.DTYPE_F16, torch.bfloat16: rt.DTYPE_BF16}
+
+
+def _strides3(t: torch.Tensor):
+    # [B, S, H, D] -> (batch, seq, head) element strides
+    return (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _block_lists(cnt: torch.Tensor, q_blk: int, kv_blk: int, Sq: int, Skv: int, B: int, H: int, device):
+    """Per (b, h, q tile): ascending list of kept kv tiles, entry = tile | partial << 30.
+    Returns (count [B,H,nq] int32, index [B,H,nq,nk] int32) and the transposed pair."""
+    cnt = cnt.to("cpu")
+    b_, h_, nq, nk = cnt.shape
+    rows = torch.clamp(Sq - torch.arange(nq) * q_blk, max=q_blk).view(1, 1, nq, 1)
+    cols = torch.clamp(Skv - torch.arange(nk) * kv_blk, max=kv_blk).view(1, 1, 1, nk)
+    full = cnt == rows * cols
+    keep = cnt > 0
+
+    def lists(keep_m, full_m):
+        n = keep_m.shape[-1]
+        order = torch.argsort((~keep_m).to(torch.int8), dim=-1, stable=True)
+        part = (~torch.gather(full_m, -1, order)).to(torch.int32)
+        idx = (order.to(torch.int32) | (part << 30))
+        return keep_m.sum(-1, dtype=torch.int32), idx
+
+    c, i = lists(keep, full)
+    ct, it = lists(keep.transpose(2, 3), full.transpose(2, 3))
+
+    def ex(t):
+        return t.expand(B, H, *t.shape[2:]).contiguous().to(device)
+
+    return ex(c), ex(i), ex(ct), ex(it)
+
+
+class _AttnKernels:
+    """Compiled kernels of one engine instance."""
+
+    def __init__(self, low: LoweredAttention, D: int, DV: int, dtype_tag: int, mask_mode: int, stages: int):
+        self.low = low
+        self.D, self.DV, self.dtype_tag, self.mask_mode, self.stages = D, DV, dtype_tag, mask_mode, stages
+        smem = 2 * 128 * D * 2 + stages * 128 * (D + DV) * 2 + 512 + 1024
+        cfg = rt.KernelConfig(kind=rt.KIND_ATTN_FWD, dtype=dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
+                              smem_bytes=smem, stages=stages, mask_mode=mask_mode)
+        self.fwd_src = rt.kernel_source("attn_fwd.cuh", prelude=low.prelude_fwd)
+        self.fwd = rt.compile_module(self.fwd_src, "ae_attn_fwd", cfg)
+        self._bwd = None
+
+    @property
+    def bwd(self):
+        if self._bwd is None:
+            from .attn_bwd import compile_bwd
+            self._bwd = compile_bwd(self)
+        return self._bwd
+
+
+class _AttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, eng, q, k, v, *custom):
+        o, finals = eng._launch_fwd(q, k, v, custom)
+        ctx.eng = eng
+        ctx.n_custom = len(custom)
+        ctx.save_for_backward(q, k, v, o, *finals, *custom)
+        ctx.n_final = len(finals)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        eng = ctx.eng
+        saved = ctx.saved_tensors
+        q, k, v, o = saved[:4]
+        finals = saved[4:4 + ctx.n_final]
+        custom = saved[4 + ctx.n_final:]
+        dq, dk, dv = eng._launch_bwd(q, k, v, o, d_o, finals, custom)
+        return (None, dq, dk, dv) + (None,) * ctx.n_custom
+
+
+class AttentionEngine:
+    def __init__(self, qkv_meta, custom_fwd_inputs, score_mod, mask_mod, online_func, mask_value="-inf",
+                 device=None, backend="tl", tune=False, tune_file="", tune_bwd=False, tune_file_bwd="",
+                 infer_mask=True, infer_mask_block_M=128, infer_mask_block_N=128, extern_block_mask=False,
+                 kv_shared=False):
+        if backend not in ("tl", "b200"):
+            raise NotImplementedError(f"backend={backend!r}: only the B200 back end exists here "
+                                      "(the reference's 'cute' sm_90a path is not part of it)")
+        qm, km, vm = qkv_meta
+        self.dtype = qm.dtype
+        if self.dtype not in _TORCH_DTYPES:
+            raise NotImplementedError(f"dtype {self.dtype}: fp16 and bf16 only")
+        B, Hq, Sq, D = qm.shape
+        _, Hkv, Skv, _ = km.shape
+        DV = vm.shape[3]
+        self.B, self.Hq, self.Hkv, self.Sq, self.Skv, self.D, self.DV = B, Hq, Hkv, Sq, Skv, D, DV
+        self.custom_fwd_inputs = custom_fwd_inputs if custom_fwd_inputs is not None else CustomIO()
+        self.score_mod, self.mask_mod, self.online_func = score_mod, mask_mod, online_func
+        self.mask_value = mask_value
+        self.extern_block_mask = extern_block_mask
+        self.block_mask = None
+        self._lists = None
+        self._status = None
+        dynamic = any(isinstance(x, str) for x in (B, Hq, Sq, Skv))
+
+        # shape-class dispatch, as attn_engine.py:218-332
+        if kv_shared:
+            raise NotImplementedError("kv_shared (MLA decode) kernels are not built yet")
+        if not dynamic and Sq != Skv:
+            raise NotImplementedError("decode (q_len != kv_len) kernels are not built yet")
+        if isinstance(D, str) or isinstance(DV, str) or D % 64 or DV % 64 or D > 128 or DV > 128:
+            raise NotImplementedError(f"head dims D={D}, DV={DV}: multiples of 64 up to 128 are supported")
+        if not isinstance(Hq, str) and not isinstance(Hkv, str):
+            assert Hq % Hkv == 0, "query heads must be a multiple of kv heads"
+
+        # mask classification (reference: lower.py:708-738)
+        mask_mode = 0
+        self._mask_counts = None
+        if extern_block_mask:
+            mask_mode = 2
+        elif mask_mod is not None:
+            if infer_mask and not dynamic:
+                cnt = block_mask_counts(mask_mod, B, Hq, Sq, Skv, "cpu", 128, 128)
+                causal_cnt = block_mask_counts(lambda b, h, q, kv: q >= kv, 1, 1, Sq, Skv, "cpu", 128, 128)
+                if cnt.shape[:2] == (1, 1) and torch.equal(cnt, causal_cnt):
+                    mask_mode = 1
+                else:
+                    rows = torch.clamp(Sq - torch.arange(cnt.shape[2]) * 128, max=128).view(1, 1, -1, 1)
+                    cols = torch.clamp(Skv - torch.arange(cnt.shape[3]) * 128, max=128).view(1, 1, 1, -1)
+                    mask_mode = 0 if bool((cnt == rows * cols).all()) else 2
+                    self._mask_counts = cnt
+                if infer_mask_block_M == 128 and infer_mask_block_N == 128:
+                    self.block_mask = (cnt > 0).to(torch.int8).expand(B, Hq, cnt.shape[2], cnt.shape[3])
+            else:
+                mask_mode = 3  # no block information: visit every tile, mask every element
+        self.mask_mode = mask_mode
+
+        low = lower_attention(score_mod, mask_mod, online_func, self.custom_fwd_inputs, D=D, DV=DV,
+                              bf16=self.dtype == torch.bfloat16, mask_mode=mask_mode, stages=2,
+                              mask_value=mask_value)
+        self.lowered = low
+        self.kernels = _AttnKernels(low, D, DV, _TORCH_DTYPES[self.dtype], mask_mode, 2)
+        self.tl_code = self.kernels.fwd_src  # name kept from the reference (attn_engine.py:365): generated source
+
+    # ------------------------------------------------------------------------------------------
+    def _get_status(self, device):
+        if self._status is None or self._status.device != device:
+            self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._status
+
+    def check_status(self):
+        """Raise if a kernel of this engine recorded a bounded-wait timeout."""
+        if self._status is not None:
+            code = int(self._status.item())
+            if code:
+                self._status.zero_()
+                raise rt.AeError(f"kernel reported status 0x{code:x} (a bounded wait gave up)")
+
+    def _ensure_lists(self, device, block_mask: Optional[torch.Tensor], B, Hq, Sq, Skv):
+        if self.mask_mode != 2:
+            return None
+        if block_mask is not None:
+            cnt = block_mask.to(torch.int32).cpu()
+            if self.mask_mod is None:
+                # listed blocks are complete blocks
+                nq, nk = cnt.shape[2], cnt.shape[3]
+                rows = torch.clamp(Sq - torch.arange(nq) * 128, max=128).view(1, 1, nq, 1)
+                cols = torch.clamp(Skv - torch.arange(nk) * 128, max=128).view(1, 1, 1, nk)
+                cnt = (cnt > 0).to(torch.int32) * rows * cols
+            return _block_lists(cnt, 128, 128, Sq, Skv, B, Hq, device)
+        if self._lists is None or self._lists[0].device != device:
+            if self._mask_counts is None:
+                raise ValueError("this engine needs block_mask= at call time (extern_block_mask=True)")
+            self._lists = _block_lists(self._mask_counts, 128, 128, Sq, Skv, B, Hq, device)
+        return self._lists
+
+    def _custom_args(self, custom, Sq, Skv):
+        specs = self.lowered.custom
+        if len(custom) != len(specs):
+            raise TypeError(f"expected {len(specs)} custom input(s) {[s.name for s in specs]}, got {len(custom)}")
+        ptrs = (C.c_void_p * rt.AE_MAX_CUSTOM)()
+        strides = ((C.c_int64 * 4) * rt.AE_MAX_CUSTOM)()
+        keep = []
+        for sp, t in zip(specs, custom):
+            want = self.dtype if sp.is_16bit else torch.float32
+            if t.dtype != want:
+                t = t.to(want)
+            if t.dim() != len(sp.shape):
+                raise ValueError(f"custom input {sp.name}: expected {len(sp.shape)} dims, got {tuple(t.shape)}")
+            if sp.is_16bit and (Sq % 128 or Skv % 128):
+                raise NotImplementedError("tile-shaped custom inputs need sequence lengths that are multiples of 128")
+            keep.append(t)
+            ptrs[sp.slot] = t.data_ptr()
+            for d, slot in enumerate(sp.dim_slots):
+                if slot >= 0 and t.shape[d] > 1:
+                    strides[sp.slot][slot] = t.stride(d)
+        return ptrs, strides, keep
+
+    def _check_qkv(self, q, k, v):
+        for name, t in (("q", q), ("k", k), ("v", v)):
+            if not t.is_cuda:
+                raise rt.AeError(f"{name} must be a CUDA tensor: this back end has no CPU path")
+            if t.dtype != self.dtype:
+                raise TypeError(f"{name} has dtype {t.dtype}, engine was built for {self.dtype}")
+            if t.dim() != 4 or t.stride(3) != 1:
+                raise ValueError(f"{name} must be [B, S, H, D] with a contiguous last dimension")
+        B, Sq, Hq, D = q.shape
+        _, Skv, Hkv, _ = k.shape
+        if (D, v.shape[3]) != (self.D, self.DV):
+            raise ValueError(f"head dims {(D, v.shape[3])} differ from the engine's {(self.D, self.DV)}")
+        if Hq % Hkv or v.shape[1] != Skv or v.shape[2] != Hkv or k.shape[0] != B or v.shape[0] != B:
+            raise ValueError("inconsistent q/k/v shapes")
+        return B, Sq, Hq, Skv, Hkv
+
+    def _launch_fwd(self, q, k, v, custom, block_mask=None):
+        B, Sq, Hq, Skv, Hkv = self._check_qkv(q, k, v)
+        dev = q.device
+        o = torch.empty(B, Sq, Hq, self.DV, dtype=self.dtype, device=dev)
+        finals = [torch.empty(B, Hq, Sq, dtype=torch.float32, device=dev) for _ in self.lowered.final_names]
+        p = rt.AttnParams()
+        p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+        p.q_stride, p.k_stride, p.v_stride, p.o_stride = _strides3(q), _strides3(k), _strides3(v), _strides3(o)
+        for i, f in enumerate(finals):
+            p.final_rowscales[i] = f.data_ptr()
+        p.custom, p.custom_stride, keep = self._custom_args(custom, Sq, Skv)
+        lists = self._ensure_lists(dev, block_mask if block_mask is not None else (
+            self.block_mask if self.extern_block_mask else None), B, Hq, Sq, Skv)
+        if lists is not None:
+            p.block_count, p.block_index = lists[0].data_ptr(), lists[1].data_ptr()
+        p.B, p.Hq, p.Hkv, p.Sq, p.Skv = B, Hq, Hkv, Sq, Skv
+        p.status = self._get_status(dev).data_ptr()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rt.check(rt.lib().ae_launch_attn_fwd(self.kernels.fwd.handle, C.byref(p), C.c_void_p(stream)),
+                 "ae_launch_attn_fwd")
+        self._last_lists = lists
+        return o, finals
+
+    def _launch_bwd(self, q, k, v, o, d_o, finals, custom):
+        from .attn_bwd import launch_bwd
+        return launch_bwd(self, q, k, v, o, d_o, finals, custom)
+
+    def __call__(self, *args, **kargs):
+        block_mask = kargs.get("block_mask")
+        if block_mask is not None:
+            self.block_mask = block_mask
+            self.extern_block_mask = True
+            if self.mask_mode != 2:
+                raise ValueError("block_mask= needs an engine built with extern_block_mask=True")
+        q, k, v, *custom = args
+        return _AttentionFn.apply(self, q, k, v, *custom)

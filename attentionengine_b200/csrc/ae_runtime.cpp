@@ -1,0 +1,526 @@
+// Host side of libae_b200.so: NVRTC compile, cubin modules, TMA descriptors, launches.
+// libcuda and libnvrtc are opened lazily with dlopen so that the library loads (and
+// compiles kernels) on a machine without a GPU driver.
+#include <cuda.h>
+#include <dlfcn.h>
+#include <nvrtc.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/ae_b200.h"
+#include "kernels/ae_args.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+void set_error(const std::string& s) { g_last_error = s; }
+
+// ------------------------------------------------------------------ driver symbols
+struct Driver {
+  void* lib = nullptr;
+  CUresult (*cuInit)(unsigned) = nullptr;
+  CUresult (*cuCtxGetCurrent)(CUcontext*) = nullptr;
+  CUresult (*cuCtxSetCurrent)(CUcontext) = nullptr;
+  CUresult (*cuDeviceGet)(CUdevice*, int) = nullptr;
+  CUresult (*cuDevicePrimaryCtxRetain)(CUcontext*, CUdevice) = nullptr;
+  CUresult (*cuModuleLoadData)(CUmodule*, const void*) = nullptr;
+  CUresult (*cuModuleUnload)(CUmodule) = nullptr;
+  CUresult (*cuModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+  CUresult (*cuFuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+  CUresult (*cuFuncGetAttribute)(int*, CUfunction_attribute, CUfunction) = nullptr;
+  CUresult (*cuLaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
+                             CUstream, void**, void**) = nullptr;
+  CUresult (*cuGetErrorString)(CUresult, const char**) = nullptr;
+  CUresult (*cuTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
+  bool ok = false;
+};
+
+Driver& driver() {
+  static Driver d;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    d.lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+    if (!d.lib) d.lib = dlopen("libcuda.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!d.lib) return;
+#define AE_SYM(name, sym)                                 \
+  d.name = (decltype(d.name))dlsym(d.lib, sym);           \
+  if (!d.name) return;
+    AE_SYM(cuInit, "cuInit")
+    AE_SYM(cuCtxGetCurrent, "cuCtxGetCurrent")
+    AE_SYM(cuCtxSetCurrent, "cuCtxSetCurrent")
+    AE_SYM(cuDeviceGet, "cuDeviceGet")
+    AE_SYM(cuDevicePrimaryCtxRetain, "cuDevicePrimaryCtxRetain")
+    AE_SYM(cuModuleLoadData, "cuModuleLoadData")
+    AE_SYM(cuModuleUnload, "cuModuleUnload")
+    AE_SYM(cuModuleGetFunction, "cuModuleGetFunction")
+    AE_SYM(cuFuncSetAttribute, "cuFuncSetAttribute")
+    AE_SYM(cuFuncGetAttribute, "cuFuncGetAttribute")
+    AE_SYM(cuLaunchKernel, "cuLaunchKernel")
+    AE_SYM(cuGetErrorString, "cuGetErrorString")
+    AE_SYM(cuTensorMapEncodeTiled, "cuTensorMapEncodeTiled")
+#undef AE_SYM
+    d.ok = (d.cuInit(0) == CUDA_SUCCESS);
+  });
+  return d;
+}
+
+int cu_fail(CUresult r, const char* what) {
+  const char* s = nullptr;
+  Driver& d = driver();
+  if (d.cuGetErrorString) d.cuGetErrorString(r, &s);
+  char buf[256];
+  snprintf(buf, sizeof buf, "%s failed: %s (%d)", what, s ? s : "?", (int)r);
+  set_error(buf);
+  return AE_ERR_CUDA;
+}
+#define AE_CU(call)                                   \
+  do {                                                \
+    CUresult r_ = (call);                             \
+    if (r_ != CUDA_SUCCESS) return cu_fail(r_, #call); \
+  } while (0)
+
+// ------------------------------------------------------------------ NVRTC symbols
+struct Nvrtc {
+  void* lib = nullptr;
+  nvrtcResult (*CreateProgram)(nvrtcProgram*, const char*, const char*, int, const char* const*,
+                               const char* const*) = nullptr;
+  nvrtcResult (*CompileProgram)(nvrtcProgram, int, const char* const*) = nullptr;
+  nvrtcResult (*GetCUBINSize)(nvrtcProgram, size_t*) = nullptr;
+  nvrtcResult (*GetCUBIN)(nvrtcProgram, char*) = nullptr;
+  nvrtcResult (*GetProgramLogSize)(nvrtcProgram, size_t*) = nullptr;
+  nvrtcResult (*GetProgramLog)(nvrtcProgram, char*) = nullptr;
+  nvrtcResult (*DestroyProgram)(nvrtcProgram*) = nullptr;
+  const char* (*GetErrorString)(nvrtcResult) = nullptr;
+  bool ok = false;
+};
+
+Nvrtc& nvrtc() {
+  static Nvrtc n;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* names[] = {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12"};
+    for (const char* nm : names) {
+      n.lib = dlopen(nm, RTLD_NOW | RTLD_LOCAL);
+      if (n.lib) break;
+    }
+    if (!n.lib) return;
+#define AE_SYM(name, sym)                        \
+  n.name = (decltype(n.name))dlsym(n.lib, sym);  \
+  if (!n.name) return;
+    AE_SYM(CreateProgram, "nvrtcCreateProgram")
+    AE_SYM(CompileProgram, "nvrtcCompileProgram")
+    AE_SYM(GetCUBINSize, "nvrtcGetCUBINSize")
+    AE_SYM(GetCUBIN, "nvrtcGetCUBIN")
+    AE_SYM(GetProgramLogSize, "nvrtcGetProgramLogSize")
+    AE_SYM(GetProgramLog, "nvrtcGetProgramLog")
+    AE_SYM(DestroyProgram, "nvrtcDestroyProgram")
+    AE_SYM(GetErrorString, "nvrtcGetErrorString")
+#undef AE_SYM
+    n.ok = true;
+  });
+  return n;
+}
+
+// ------------------------------------------------------------------ module
+struct Module {
+  std::vector<char> cubin;
+  std::string kernel;
+  AeKernelConfig cfg{};
+  std::mutex mu;
+  CUmodule mod = nullptr;
+  CUfunction fn = nullptr;
+};
+
+int ensure_context() {
+  Driver& d = driver();
+  if (!d.ok) {
+    set_error("libcuda.so.1 not available or cuInit failed");
+    return AE_ERR_NO_DRIVER;
+  }
+  CUcontext ctx = nullptr;
+  AE_CU(d.cuCtxGetCurrent(&ctx));
+  if (!ctx) {
+    CUdevice dev;
+    AE_CU(d.cuDeviceGet(&dev, 0));
+    AE_CU(d.cuDevicePrimaryCtxRetain(&ctx, dev));
+    AE_CU(d.cuCtxSetCurrent(ctx));
+  }
+  return AE_OK;
+}
+
+int ensure_loaded(Module* m) {
+  std::lock_guard<std::mutex> lk(m->mu);
+  if (m->fn) return AE_OK;
+  int rc = ensure_context();
+  if (rc) return rc;
+  Driver& d = driver();
+  AE_CU(d.cuModuleLoadData(&m->mod, m->cubin.data()));
+  AE_CU(d.cuModuleGetFunction(&m->fn, m->mod, m->kernel.c_str()));
+  if (m->cfg.smem_bytes > 48 * 1024)
+    AE_CU(d.cuFuncSetAttribute(m->fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, m->cfg.smem_bytes));
+  return AE_OK;
+}
+
+int launch(Module* m, unsigned gx, unsigned gy, unsigned gz, void* args, void* stream) {
+  Driver& d = driver();
+  void* params[] = {args};
+  AE_CU(d.cuLaunchKernel(m->fn, gx, gy, gz, (unsigned)m->cfg.threads, 1, 1, (unsigned)m->cfg.smem_bytes,
+                         (CUstream)stream, params, nullptr));
+  return AE_OK;
+}
+
+// Tensor map over a [B, S, H, D] tensor (element strides sb, ss, sh; d contiguous) seen as
+// (d, h, s, b) with a box of {64, 1, rows, 1} and 128-byte swizzle: one box is a `rows` x 128 B
+// tile in the K-major (for Q/K) or MN-major (for V) layout the UMMA descriptors expect.
+int make_bshd_map(AeTmaDesc* out, const void* base, int dtype, int64_t B, int64_t S, int64_t H, int64_t D,
+                  const int64_t st[3], int rows) {
+  Driver& d = driver();
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) {
+    set_error("tensor base address must be 16-byte aligned");
+    return AE_ERR_INVALID;
+  }
+  for (int i = 0; i < 3; ++i)
+    if ((st[i] * 2) % 16 != 0 && !((i == 0 && B == 1))) {
+      set_error("tensor strides must be multiples of 8 elements");
+      return AE_ERR_INVALID;
+    }
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)st[2] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)(B == 1 ? S * st[1] : st[0]) * 2};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMapDataType dt = dtype == AE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  AE_CU(d.cuTensorMapEncodeTiled(reinterpret_cast<CUtensorMap*>(out), dt, 4, const_cast<void*>(base), dims, strides,
+                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return AE_OK;
+}
+
+int make_2d_map(AeTmaDesc* out, const void* base, int dtype, int64_t rows, int64_t cols, int box_rows) {
+  Driver& d = driver();
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = dtype == AE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  AE_CU(d.cuTensorMapEncodeTiled(reinterpret_cast<CUtensorMap*>(out), dt, 2, const_cast<void*>(base), dims, strides,
+                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return AE_OK;
+}
+
+int check_attn_common(const Module* m, int kind, int B, int Hq, int Hkv, int Sq, int Skv) {
+  if (m->cfg.kind != kind) {
+    set_error("module kind does not match the entry point");
+    return AE_ERR_UNSUPPORTED;
+  }
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Skv <= 0 || Hq % Hkv != 0) {
+    set_error("bad attention shape");
+    return AE_ERR_INVALID;
+  }
+  if (m->cfg.head_dim % 64 || m->cfg.head_dim_v % 64) {
+    set_error("head dims must be multiples of 64");
+    return AE_ERR_INVALID;
+  }
+  return AE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* ae_strerror(int code) {
+  switch (code) {
+    case AE_OK: return "ok";
+    case AE_ERR_INVALID: return "invalid argument";
+    case AE_ERR_COMPILE: return "kernel compilation failed";
+    case AE_ERR_NO_NVRTC: return "libnvrtc not available";
+    case AE_ERR_NO_DRIVER: return "CUDA driver not available";
+    case AE_ERR_CUDA: return "CUDA driver call failed";
+    case AE_ERR_UNSUPPORTED: return "unsupported kernel kind for this entry point";
+    default: return "unknown error";
+  }
+}
+
+const char* ae_last_error(void) { return g_last_error.c_str(); }
+
+int ae_compile(const char* cuda_src, const char* kernel_name, const char* arch, const char** opts, int nopts,
+               const AeKernelConfig* cfg, void** out_module, char* log, size_t log_cap) {
+  if (!cuda_src || !kernel_name || !cfg || !out_module) return AE_ERR_INVALID;
+  if (log && log_cap) log[0] = 0;
+  Nvrtc& n = nvrtc();
+  if (!n.ok) {
+    set_error("libnvrtc.so.12 not found");
+    return AE_ERR_NO_NVRTC;
+  }
+  nvrtcProgram prog;
+  nvrtcResult r = n.CreateProgram(&prog, cuda_src, "ae_kernel.cu", 0, nullptr, nullptr);
+  if (r != NVRTC_SUCCESS) {
+    set_error(n.GetErrorString(r));
+    return AE_ERR_COMPILE;
+  }
+  std::vector<std::string> o;
+  o.push_back(std::string("--gpu-architecture=") + (arch ? arch : "sm_100a"));
+  o.push_back("--std=c++17");
+  o.push_back("-lineinfo");
+  for (int i = 0; i < nopts; ++i) o.push_back(opts[i]);
+  std::vector<const char*> oc;
+  for (auto& s : o) oc.push_back(s.c_str());
+  r = n.CompileProgram(prog, (int)oc.size(), oc.data());
+  size_t ls = 0;
+  n.GetProgramLogSize(prog, &ls);
+  if (ls > 1) {
+    std::vector<char> lb(ls + 1, 0);
+    n.GetProgramLog(prog, lb.data());
+    if (log && log_cap) {
+      size_t c = ls < log_cap - 1 ? ls : log_cap - 1;
+      memcpy(log, lb.data(), c);
+      log[c] = 0;
+    }
+    if (r != NVRTC_SUCCESS) set_error(std::string(lb.data(), ls < 2000 ? ls : 2000));
+  }
+  if (r != NVRTC_SUCCESS) {
+    n.DestroyProgram(&prog);
+    return AE_ERR_COMPILE;
+  }
+  size_t cs = 0;
+  n.GetCUBINSize(prog, &cs);
+  Module* m = new Module();
+  m->cubin.resize(cs);
+  n.GetCUBIN(prog, m->cubin.data());
+  n.DestroyProgram(&prog);
+  m->kernel = kernel_name;
+  m->cfg = *cfg;
+  *out_module = m;
+  return AE_OK;
+}
+
+int ae_module_from_cubin(const void* cubin, size_t size, const char* kernel_name, const AeKernelConfig* cfg,
+                         void** out_module) {
+  if (!cubin || !size || !kernel_name || !cfg || !out_module) return AE_ERR_INVALID;
+  Module* m = new Module();
+  m->cubin.assign((const char*)cubin, (const char*)cubin + size);
+  m->kernel = kernel_name;
+  m->cfg = *cfg;
+  *out_module = m;
+  return AE_OK;
+}
+
+int ae_module_cubin(void* module, const void** data, size_t* size) {
+  if (!module || !data || !size) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  *data = m->cubin.data();
+  *size = m->cubin.size();
+  return AE_OK;
+}
+
+int ae_query(void* module, AeKernelInfo* info) {
+  if (!module || !info) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  int rc = ensure_loaded(m);
+  if (rc) return rc;
+  Driver& d = driver();
+  AE_CU(d.cuFuncGetAttribute(&info->num_regs, CU_FUNC_ATTRIBUTE_NUM_REGS, m->fn));
+  AE_CU(d.cuFuncGetAttribute(&info->static_smem_bytes, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, m->fn));
+  AE_CU(d.cuFuncGetAttribute(&info->max_dynamic_smem_bytes, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, m->fn));
+  AE_CU(d.cuFuncGetAttribute(&info->local_bytes, CU_FUNC_ATTRIBUTE_LOCAL_SIZE_BYTES, m->fn));
+  AE_CU(d.cuFuncGetAttribute(&info->max_threads, CU_FUNC_ATTRIBUTE_MAX_THREADS_PER_BLOCK, m->fn));
+  return AE_OK;
+}
+
+void ae_release(void* module) {
+  if (!module) return;
+  Module* m = (Module*)module;
+  if (m->mod) driver().cuModuleUnload(m->mod);
+  delete m;
+}
+
+int ae_launch_probe(void* module, const void* a, const void* b, const void* p, float* d_out, int mode,
+                    uint32_t* status, void* stream) {
+  if (!module || !b || !d_out) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  if (m->cfg.kind != AE_KIND_PROBE) return AE_ERR_UNSUPPORTED;
+  int rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeProbeArgs args;
+  memset(&args, 0, sizeof args);
+  if (mode == 0) {
+    if (!a) return AE_ERR_INVALID;
+    rc = make_2d_map(&args.tm_a, a, m->cfg.dtype, 128, 128, 128);
+    if (rc) return rc;
+  } else if (!p) {
+    return AE_ERR_INVALID;
+  }
+  rc = make_2d_map(&args.tm_b, b, m->cfg.dtype, 128, 128, 128);
+  if (rc) return rc;
+  args.p = p;
+  args.d = d_out;
+  args.mode = mode;
+  args.status = status;
+  return launch(m, 1, 1, 1, &args, stream);
+}
+
+int ae_launch_attn_fwd(void* module, const AeAttnParams* p, void* stream) {
+  if (!module || !p || !p->q || !p->k || !p->v || !p->o) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  int rc = check_attn_common(m, AE_KIND_ATTN_FWD, p->B, p->Hq, p->Hkv, p->Sq, p->Skv);
+  if (rc) return rc;
+  if (m->cfg.mask_mode == 2 && (!p->block_count || !p->block_index)) {
+    set_error("block lists required for mask_mode 2");
+    return AE_ERR_INVALID;
+  }
+  rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeAttnFwdArgs args;
+  memset(&args, 0, sizeof args);
+  const int D = m->cfg.head_dim, DV = m->cfg.head_dim_v;
+  rc = make_bshd_map(&args.tm_q, p->q, m->cfg.dtype, p->B, p->Sq, p->Hq, D, p->q_stride, 128);
+  if (rc) return rc;
+  rc = make_bshd_map(&args.tm_k, p->k, m->cfg.dtype, p->B, p->Skv, p->Hkv, D, p->k_stride, 128);
+  if (rc) return rc;
+  rc = make_bshd_map(&args.tm_v, p->v, m->cfg.dtype, p->B, p->Skv, p->Hkv, DV, p->v_stride, 128);
+  if (rc) return rc;
+  args.o = p->o;
+  args.o_sb = p->o_stride[0];
+  args.o_ss = p->o_stride[1];
+  args.o_sh = p->o_stride[2];
+  if ((reinterpret_cast<uintptr_t>(p->o) & 15) || (args.o_ss % 8) || (args.o_sh % 8) || (args.o_sb % 8)) {
+    set_error("output must be 16-byte aligned with strides that are multiples of 8 elements");
+    return AE_ERR_INVALID;
+  }
+  for (int i = 0; i < AE_MAX_FINAL; ++i) args.final_rs[i] = p->final_rowscales[i];
+  for (int i = 0; i < AE_MAX_CUSTOM; ++i) {
+    args.custom[i] = p->custom[i];
+    for (int k = 0; k < 4; ++k) args.custom_st[i][k] = p->custom_stride[i][k];
+  }
+  args.blk_cnt = p->block_count;
+  args.blk_idx = p->block_index;
+  args.B = p->B;
+  args.Hq = p->Hq;
+  args.Hkv = p->Hkv;
+  args.Sq = p->Sq;
+  args.Skv = p->Skv;
+  args.n_qt = (p->Sq + 127) / 128;
+  args.n_kt = (p->Skv + 127) / 128;
+  args.status = p->status;
+  const unsigned gx = (unsigned)((args.n_qt + 1) / 2);
+  return launch(m, gx, (unsigned)p->Hq, (unsigned)p->B, &args, stream);
+}
+
+static int fill_bwd_args(Module* m, const AeAttnBwdParams* p, AeAttnBwdArgs* a, int q_rows, int kv_rows) {
+  memset(a, 0, sizeof *a);
+  const int D = m->cfg.head_dim, DV = m->cfg.head_dim_v;
+  int rc;
+  if ((rc = make_bshd_map(&a->tm_q, p->q, m->cfg.dtype, p->B, p->Sq, p->Hq, D, p->q_stride, q_rows))) return rc;
+  if ((rc = make_bshd_map(&a->tm_do, p->d_o, m->cfg.dtype, p->B, p->Sq, p->Hq, DV, p->do_stride, q_rows))) return rc;
+  if ((rc = make_bshd_map(&a->tm_k, p->k, m->cfg.dtype, p->B, p->Skv, p->Hkv, D, p->k_stride, kv_rows))) return rc;
+  if ((rc = make_bshd_map(&a->tm_v, p->v, m->cfg.dtype, p->B, p->Skv, p->Hkv, DV, p->v_stride, kv_rows))) return rc;
+  a->dq = p->dq;
+  a->dk = p->dk;
+  a->dv = p->dv;
+  a->dq_sb = p->dq_stride[0]; a->dq_ss = p->dq_stride[1]; a->dq_sh = p->dq_stride[2];
+  a->dk_sb = p->dk_stride[0]; a->dk_ss = p->dk_stride[1]; a->dk_sh = p->dk_stride[2];
+  a->dv_sb = p->dv_stride[0]; a->dv_ss = p->dv_stride[1]; a->dv_sh = p->dv_stride[2];
+  const void* outs[3] = {p->dq, p->dk, p->dv};
+  const int64_t* sts[3] = {p->dq_stride, p->dk_stride, p->dv_stride};
+  for (int i = 0; i < 3; ++i) {
+    if (!outs[i]) continue;
+    if ((reinterpret_cast<uintptr_t>(outs[i]) & 15) || sts[i][0] % 8 || sts[i][1] % 8 || sts[i][2] % 8) {
+      set_error("gradient outputs must be 16-byte aligned with strides that are multiples of 8 elements");
+      return AE_ERR_INVALID;
+    }
+  }
+  for (int i = 0; i < AE_MAX_FINAL; ++i) a->final_rs[i] = p->final_rowscales[i];
+  a->delta = p->delta;
+  for (int i = 0; i < AE_MAX_CUSTOM; ++i) {
+    a->custom[i] = p->custom[i];
+    for (int k = 0; k < 4; ++k) a->custom_st[i][k] = p->custom_stride[i][k];
+  }
+  a->blk_cnt = p->block_count;
+  a->blk_idx = p->block_index;
+  a->blkT_cnt = p->block_count_t;
+  a->blkT_idx = p->block_index_t;
+  a->B = p->B; a->Hq = p->Hq; a->Hkv = p->Hkv; a->Sq = p->Sq; a->Skv = p->Skv;
+  a->n_qt = (p->Sq + 127) / 128;
+  a->n_kt = (p->Skv + 127) / 128;
+  a->status = p->status;
+  return AE_OK;
+}
+
+int ae_launch_attn_bwd_prep(void* module, const AeAttnBwdParams* p, void* stream) {
+  if (!module || !p || !p->o || !p->d_o || !p->delta) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  int rc = check_attn_common(m, AE_KIND_ATTN_BWD_PREP, p->B, p->Hq, p->Hkv, p->Sq, p->Skv);
+  if (rc) return rc;
+  rc = ensure_loaded(m);
+  if (rc) return rc;
+  if ((reinterpret_cast<uintptr_t>(p->o) & 3) || (reinterpret_cast<uintptr_t>(p->d_o) & 3)) {
+    set_error("o / dO must be 4-byte aligned");
+    return AE_ERR_INVALID;
+  }
+  AeAttnBwdPrepArgs a;
+  memset(&a, 0, sizeof a);
+  a.o = p->o;
+  a.d_o = p->d_o;
+  a.delta = p->delta;
+  a.o_sb = p->o_stride[0]; a.o_ss = p->o_stride[1]; a.o_sh = p->o_stride[2];
+  a.do_sb = p->do_stride[0]; a.do_ss = p->do_stride[1]; a.do_sh = p->do_stride[2];
+  if (a.o_sb % 2 || a.o_ss % 2 || a.o_sh % 2 || a.do_sb % 2 || a.do_ss % 2 || a.do_sh % 2) {
+    set_error("o / dO strides must be even");
+    return AE_ERR_INVALID;
+  }
+  a.B = p->B; a.Hq = p->Hq; a.Sq = p->Sq; a.DV = m->cfg.head_dim_v;
+  return launch(m, (unsigned)((p->Sq + 7) / 8), (unsigned)p->Hq, (unsigned)p->B, &a, stream);
+}
+
+int ae_launch_attn_bwd_dq(void* module, const AeAttnBwdParams* p, void* stream) {
+  if (!module || !p || !p->q || !p->k || !p->v || !p->d_o || !p->dq) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  int rc = check_attn_common(m, AE_KIND_ATTN_BWD_DQ, p->B, p->Hq, p->Hkv, p->Sq, p->Skv);
+  if (rc) return rc;
+  if (m->cfg.mask_mode == 2 && (!p->block_count || !p->block_index)) {
+    set_error("block lists required for mask_mode 2");
+    return AE_ERR_INVALID;
+  }
+  const int bn = m->cfg.reserved[0];
+  if (bn != 64 && bn != 128) {
+    set_error("backward tile (reserved[0]) must be 64 or 128");
+    return AE_ERR_INVALID;
+  }
+  rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeAttnBwdArgs a;
+  rc = fill_bwd_args(m, p, &a, 128, bn);
+  if (rc) return rc;
+  return launch(m, (unsigned)a.n_qt, (unsigned)p->Hq, (unsigned)p->B, &a, stream);
+}
+
+int ae_launch_attn_bwd_dkv(void* module, const AeAttnBwdParams* p, void* stream) {
+  if (!module || !p || !p->q || !p->k || !p->v || !p->d_o || !p->dk || !p->dv) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  int rc = check_attn_common(m, AE_KIND_ATTN_BWD_DKV, p->B, p->Hq, p->Hkv, p->Sq, p->Skv);
+  if (rc) return rc;
+  if (m->cfg.mask_mode == 2 && (!p->block_count_t || !p->block_index_t)) {
+    set_error("transposed block lists required for mask_mode 2");
+    return AE_ERR_INVALID;
+  }
+  const int bn = m->cfg.reserved[0];
+  if (bn != 64 && bn != 128) {
+    set_error("backward tile (reserved[0]) must be 64 or 128");
+    return AE_ERR_INVALID;
+  }
+  rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeAttnBwdArgs a;
+  rc = fill_bwd_args(m, p, &a, bn, 128);
+  if (rc) return rc;
+  return launch(m, (unsigned)a.n_kt, (unsigned)p->Hkv, (unsigned)p->B, &a, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,93 @@
+// Kernel argument blocks shared by the host launcher (compiled with g++) and the
+// kernel sources (compiled with NVRTC / nvcc).  Plain C layout, no CUDA headers.
+#ifndef AE_ARGS_H_
+#define AE_ARGS_H_
+
+#ifndef AE_DEVICE
+typedef unsigned char u8;
+typedef unsigned short u16;
+typedef unsigned int u32;
+typedef unsigned long long u64;
+typedef long long i64;
+struct alignas(64) AeTmaDesc {
+  u64 opaque[16];
+};
+#endif
+
+#define AE_MAX_CUSTOM 4
+#define AE_MAX_FINAL 4
+
+#ifdef AE_DEVICE
+// custom inputs as seen by the generated functors
+struct AeCustom {
+  const void* p[AE_MAX_CUSTOM];
+  i64 st[AE_MAX_CUSTOM][4];
+};
+#endif
+
+// ---- fused attention forward (kernel ae_attn_fwd) --------------------------------
+struct AeAttnFwdArgs {
+  AeTmaDesc tm_q;  // dims (d, h, s, b), box {64, 1, 128, 1}, 128-byte swizzle
+  AeTmaDesc tm_k;
+  AeTmaDesc tm_v;
+  void* o;
+  i64 o_sb, o_ss, o_sh;           // element strides of O [B, S, H, DV]
+  float* final_rs[AE_MAX_FINAL];  // each [B, Hq, Sq] fp32
+  const void* custom[AE_MAX_CUSTOM];
+  i64 custom_st[AE_MAX_CUSTOM][4];  // element strides over (b, h, q, kv); 0 = broadcast
+  const int* blk_cnt;  // [B, Hq, n_qt] number of listed kv tiles            (mask mode 2)
+  const int* blk_idx;  // [B, Hq, n_qt, n_kt] kv tile index | (partial << 30)  (mask mode 2)
+  int B, Hq, Hkv, Sq, Skv;
+  int n_qt, n_kt;  // number of 128-row q tiles / 128-column kv tiles
+  u32* status;
+};
+
+// ---- attention backward ------------------------------------------------------------
+// Pre-pass: delta[b, h, s] = sum_d O * dO                     (kernel ae_attn_bwd_prep)
+struct AeAttnBwdPrepArgs {
+  const void* o;
+  const void* d_o;
+  float* delta;  // [B, Hq, Sq]
+  i64 o_sb, o_ss, o_sh;
+  i64 do_sb, do_ss, do_sh;
+  int B, Hq, Sq, DV;
+};
+
+// dQ pass (kernel ae_attn_bwd_dq): one CTA per 128-row q tile, streams K/V tiles.
+// dK/dV pass (kernel ae_attn_bwd_dkv): one CTA per 128-row kv tile, streams Q/dO tiles
+// of every q-head of the kv-head's group.
+struct AeAttnBwdArgs {
+  AeTmaDesc tm_q;
+  AeTmaDesc tm_k;
+  AeTmaDesc tm_v;
+  AeTmaDesc tm_do;
+  void* dq;
+  void* dk;
+  void* dv;
+  i64 dq_sb, dq_ss, dq_sh;
+  i64 dk_sb, dk_ss, dk_sh;
+  i64 dv_sb, dv_ss, dv_sh;
+  const float* final_rs[AE_MAX_FINAL];  // each [B, Hq, Sq]
+  const float* delta;                   // [B, Hq, Sq]
+  const void* custom[AE_MAX_CUSTOM];
+  i64 custom_st[AE_MAX_CUSTOM][4];
+  const int* blk_cnt;   // per q tile lists (dQ pass)
+  const int* blk_idx;
+  const int* blkT_cnt;  // per kv tile lists of q tiles (dK/dV pass)
+  const int* blkT_idx;
+  int B, Hq, Hkv, Sq, Skv;
+  int n_qt, n_kt;
+  u32* status;
+};
+
+// ---- UMMA / TMA probe kernels (bring-up checks, kernel ae_probe) -------------------
+struct AeProbeArgs {
+  AeTmaDesc tm_a;  // [128 rows, KD] 16-bit, box {64, 128}
+  AeTmaDesc tm_b;  // [128 rows, KD] 16-bit, box {64, 128}
+  const void* p;   // [128, 128] 16-bit row-major (mode 1: A operand staged through TMEM)
+  float* d;        // [128, 128] fp32 out
+  int mode;        // 0: D = A * B^T (both K-major, smem)  1: D = P * B (P via TMEM, B MN-major)
+  u32* status;
+};
+
+#endif  // AE_ARGS_H_

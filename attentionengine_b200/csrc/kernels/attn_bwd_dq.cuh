@@ -1,0 +1,316 @@
+// Attention backward, dQ pass, for sm_100a.  Together with attn_bwd_dkv.cuh it replaces
+// the reference's `flash_bwd` + `flash_bwd_post` kernels
+// (attention_engine/core/template/tl_template/attn/attn_tl.py:239-415, 436-455): instead of
+// one kv-stationary kernel that atomically adds fp32 dQ tiles into a staging buffer, dQ is
+// produced here by a q-stationary kernel that owns its output rows, so there are no
+// atomics, no fp32 dQ buffer and no conversion kernel; the price is that S and dP are
+// recomputed in both passes.
+//
+// One CTA owns one 128-row q tile of one (batch, q-head) and streams K/V tiles of AE_BWD_BN
+// rows.  Per kv tile:
+//   S  = Q  K^T   (SS MMA)        dP = dO V^T   (SS MMA)
+//   row threads: T = score_mod(S); P = OnlineFunc.forward(T); mask; dT = OnlineFunc.backward(dP, P);
+//                dS = score_mod'(S) dT  -> 16-bit pairs written over S in TMEM
+//   dQ += dS K    (TS MMA, K tile read MN-major)
+// TMEM columns: AE_BWD_NBUF x (S | dP) then dQ.  With two buffers the tensor pipe computes the
+// next tile's S / dP while the row threads work on the current one.
+// Roles: warps 0-3 row threads (thread = q row = TMEM lane), warp 4 TMA producer, warp 5 MMA issuer.
+
+#define AE_BM 128
+#define AE_NTHREADS_BWD 192
+#define AE_NSUB (128 / AE_BWD_BN)
+
+#define AE_DQ_Q_BYTES (AE_BM * AE_D * 2)
+#define AE_DQ_DO_BYTES (AE_BM * AE_DV * 2)
+#define AE_DQ_K_BYTES (AE_BWD_BN * AE_D * 2)
+#define AE_DQ_V_BYTES (AE_BWD_BN * AE_DV * 2)
+#define AE_DQ_SMEM_Q 0
+#define AE_DQ_SMEM_DO (AE_DQ_Q_BYTES)
+#define AE_DQ_SMEM_K (AE_DQ_SMEM_DO + AE_DQ_DO_BYTES)
+#define AE_DQ_SMEM_V (AE_DQ_SMEM_K + AE_BWD_STAGES * AE_DQ_K_BYTES)
+#define AE_DQ_SMEM_BAR (AE_DQ_SMEM_V + AE_BWD_STAGES * AE_DQ_V_BYTES)
+
+struct AeDqBars {
+  u64 qdo_full;
+  u64 k_full[AE_BWD_STAGES];
+  u64 k_empty[AE_BWD_STAGES];
+  u64 v_full[AE_BWD_STAGES];
+  u64 v_empty[AE_BWD_STAGES];
+  u64 sp_full[AE_BWD_NBUF];
+  u64 ds_full[AE_BWD_NBUF];
+  u64 dq_done;
+  AeCtaCtl ctl;
+};
+
+extern "C" __global__ void __launch_bounds__(AE_NTHREADS_BWD, 1)
+ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
+  extern __shared__ u8 smem_raw[];
+  u8* smem = smem_align1024(smem_raw);
+  AeDqBars* bars = (AeDqBars*)(smem + AE_DQ_SMEM_BAR);
+  AeCtaCtl* ctl = &bars->ctl;
+  const u32 warp = threadIdx.x >> 5;
+  const u32 lane = threadIdx.x & 31;
+
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy tiles first under a causal mask
+  const int hq = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hk = hq / (args.Hq / args.Hkv);
+  const int q0 = qt * AE_BM;
+  const int n_kt_bn = (args.Skv + AE_BWD_BN - 1) / AE_BWD_BN;
+
+  // ---- kv schedule ------------------------------------------------------------------
+  int n_steps;
+#if AE_MASK_MODE == 1
+  n_steps = (q0 + AE_BM + AE_BWD_BN - 1) / AE_BWD_BN;
+  if (n_steps > n_kt_bn) n_steps = n_kt_bn;
+#elif AE_MASK_MODE == 2
+  const int n_list = args.blk_cnt[((i64)b * args.Hq + hq) * args.n_qt + qt];
+  const int* list = args.blk_idx + (((i64)b * args.Hq + hq) * args.n_qt + qt) * (i64)args.n_kt;
+  n_steps = n_list * AE_NSUB;
+#else
+  n_steps = n_kt_bn;
+#endif
+  // step -> (first kv column, needs element mask)
+  auto step_info = [&](int s, int& kv0, bool& partial) {
+#if AE_MASK_MODE == 2
+    const int e = list[s / AE_NSUB];
+    kv0 = (e & 0x3fffffff) * 128 + (s % AE_NSUB) * AE_BWD_BN;
+    partial = ((u32)e >> 30) & 1u;
+#else
+    kv0 = s * AE_BWD_BN;
+#if AE_MASK_MODE == 1
+    partial = kv0 + AE_BWD_BN - 1 > q0;
+#elif AE_MASK_MODE == 3
+    partial = true;
+#else
+    partial = false;
+#endif
+#endif
+  };
+
+  if (threadIdx.x == 0) {
+    ctl->abort = 0;
+    mbar_init(&bars->qdo_full, 1);
+    mbar_init(&bars->dq_done, 1);
+    for (int i = 0; i < AE_BWD_STAGES; ++i) {
+      mbar_init(&bars->k_full[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+    }
+    for (int i = 0; i < AE_BWD_NBUF; ++i) {
+      mbar_init(&bars->sp_full[i], 1);
+      mbar_init(&bars->ds_full[i], 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&ctl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const u32 tmem = ctl->tmem_base;
+  const u32 TM_DQ = AE_BWD_NBUF * 2 * AE_BWD_BN;
+
+  if (warp == 4) {
+    // =============================== TMA producer ===============================
+    if (lane == 0 && n_steps > 0) {
+      tma_prefetch_desc(&args.tm_q);
+      tma_prefetch_desc(&args.tm_k);
+      tma_prefetch_desc(&args.tm_v);
+      tma_prefetch_desc(&args.tm_do);
+      mbar_arrive_expect_tx(&bars->qdo_full, AE_DQ_Q_BYTES + AE_DQ_DO_BYTES);
+      for (int dh = 0; dh < AE_D / 64; ++dh)
+        tma_load_4d(smem + AE_DQ_SMEM_Q + dh * (AE_BM * 128), &args.tm_q, &bars->qdo_full, dh * 64, hq, q0, b);
+      for (int dh = 0; dh < AE_DV / 64; ++dh)
+        tma_load_4d(smem + AE_DQ_SMEM_DO + dh * (AE_BM * 128), &args.tm_do, &bars->qdo_full, dh * 64, hq, q0, b);
+      for (int s = 0; s < n_steps; ++s) {
+        int kv0;
+        bool partial;
+        step_info(s, kv0, partial);
+        const int stage = s % AE_BWD_STAGES;
+        const u32 par = ((s / AE_BWD_STAGES) & 1) ^ 1;
+        if (!mbar_wait(&bars->k_empty[stage], par, ctl, args.status, 21)) break;
+        mbar_arrive_expect_tx(&bars->k_full[stage], AE_DQ_K_BYTES);
+        for (int dh = 0; dh < AE_D / 64; ++dh)
+          tma_load_4d(smem + AE_DQ_SMEM_K + stage * AE_DQ_K_BYTES + dh * (AE_BWD_BN * 128), &args.tm_k,
+                      &bars->k_full[stage], dh * 64, hk, kv0, b);
+        if (!mbar_wait(&bars->v_empty[stage], par, ctl, args.status, 22)) break;
+        mbar_arrive_expect_tx(&bars->v_full[stage], AE_DQ_V_BYTES);
+        for (int dh = 0; dh < AE_DV / 64; ++dh)
+          tma_load_4d(smem + AE_DQ_SMEM_V + stage * AE_DQ_V_BYTES + dh * (AE_BWD_BN * 128), &args.tm_v,
+                      &bars->v_full[stage], dh * 64, hk, kv0, b);
+      }
+    }
+  } else if (warp == 5) {
+    // =============================== MMA issuer =================================
+    if (lane == 0 && n_steps > 0) {
+      const u32 idesc_s = umma_idesc_f16(AE_BM, AE_BWD_BN, AE_BF16, 0, 0);
+      const u32 idesc_dq = umma_idesc_f16(AE_BM, AE_D, AE_BF16, 0, 1);
+      const u32 q_addr = smem_u32(smem + AE_DQ_SMEM_Q);
+      const u32 do_addr = smem_u32(smem + AE_DQ_SMEM_DO);
+      const u32 k_addr = smem_u32(smem + AE_DQ_SMEM_K);
+      const u32 v_addr = smem_u32(smem + AE_DQ_SMEM_V);
+      bool ok = mbar_wait(&bars->qdo_full, 0, ctl, args.status, 23);
+
+      auto issue_sp = [&](int s) -> bool {
+        const int stage = s % AE_BWD_STAGES;
+        const u32 par = (s / AE_BWD_STAGES) & 1;
+        const int buf = s % AE_BWD_NBUF;
+        const u32 tm_s = tmem + buf * 2 * AE_BWD_BN;
+        const u32 tm_dp = tm_s + AE_BWD_BN;
+        if (!mbar_wait(&bars->k_full[stage], par, ctl, args.status, 24)) return false;
+        tc_fence_after_sync();
+        const u32 ka = k_addr + stage * AE_DQ_K_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < AE_D / 16; ++kk) {
+          umma_ss(tm_s, umma_smem_desc_sw128(q_addr + (kk >> 2) * (AE_BM * 128) + (kk & 3) * 32, 16, 1024),
+                  umma_smem_desc_sw128(ka + (kk >> 2) * (AE_BWD_BN * 128) + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
+        }
+        if (!mbar_wait(&bars->v_full[stage], par, ctl, args.status, 25)) return false;
+        tc_fence_after_sync();
+        const u32 va = v_addr + stage * AE_DQ_V_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < AE_DV / 16; ++kk) {
+          umma_ss(tm_dp, umma_smem_desc_sw128(do_addr + (kk >> 2) * (AE_BM * 128) + (kk & 3) * 32, 16, 1024),
+                  umma_smem_desc_sw128(va + (kk >> 2) * (AE_BWD_BN * 128) + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
+        }
+        umma_commit(&bars->sp_full[buf]);
+        umma_commit(&bars->v_empty[stage]);
+        return true;
+      };
+
+      if (ok) ok = issue_sp(0);
+      for (int s = 0; s < n_steps && ok; ++s) {
+        const int stage = s % AE_BWD_STAGES;
+        const int buf = s % AE_BWD_NBUF;
+        if (AE_BWD_NBUF > 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
+        if (!ok) break;
+        ok = mbar_wait(&bars->ds_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 26);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const u32 tm_ds = tmem + buf * 2 * AE_BWD_BN;  // dS pairs over the S columns
+        const u32 ka = k_addr + stage * AE_DQ_K_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < AE_BWD_BN / 16; ++kk) {
+          umma_ts(tmem + TM_DQ, tm_ds + kk * 8, umma_smem_desc_sw128(ka + kk * 2048, AE_BWD_BN * 128, 1024), idesc_dq,
+                  (s > 0) | (kk > 0));
+        }
+        umma_commit(&bars->k_empty[stage]);
+        if (s + 1 == n_steps) umma_commit(&bars->dq_done);
+        if (AE_BWD_NBUF == 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
+      }
+    }
+  } else {
+    // =============================== row threads ================================
+    const u32 row = threadIdx.x & 127;
+    const u32 lane_base = ((warp & 3) * 32) << 16;
+    const int q_idx = q0 + (int)row;
+    const bool row_valid = q_idx < args.Sq;
+    const i64 rs_off = ((i64)b * args.Hq + hq) * args.Sq + (row_valid ? q_idx : 0);
+
+    AeCustom cu;
+#pragma unroll
+    for (int i = 0; i < AE_MAX_CUSTOM; ++i) {
+      cu.p[i] = args.custom[i];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) cu.st[i][k] = args.custom_st[i][k];
+    }
+    float fr[AE_NFINAL > 0 ? AE_NFINAL : 1];
+#pragma unroll
+    for (int i = 0; i < AE_NFINAL; ++i) fr[i] = args.final_rs[i][rs_off];
+#if AE_USES_DOOSUM
+    const float delta = args.delta[rs_off];
+#else
+    const float delta = 0.f;
+#endif
+
+    bool ok = true;
+    for (int s = 0; s < n_steps; ++s) {
+      int kv0;
+      bool partial;
+      step_info(s, kv0, partial);
+      const int buf = s % AE_BWD_NBUF;
+      const u32 tm_s = tmem + buf * 2 * AE_BWD_BN + lane_base;
+      const u32 tm_dp = tm_s + AE_BWD_BN;
+      ok = ok && mbar_wait(&bars->sp_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 27);
+      tc_fence_after_sync();
+      const bool tail = kv0 + AE_BWD_BN > args.Skv;
+#pragma unroll
+      for (int c = 0; c < AE_BWD_BN / 32; ++c) {
+        float sv[32], dp[32];
+        tmem_ld_f32x32(tm_s + c * 32, sv);
+        tmem_ld_f32x32(tm_dp + c * 32, dp);
+        u32 pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float ds2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int kv_idx = kv0 + c * 32 + i + e;
+            bool keep = true;
+            if (tail) keep = kv_idx < args.Skv;
+#if AE_MASK_MODE != 0
+            if (partial) keep = keep && ae_mask(b, hq, q_idx, kv_idx);
+#endif
+            const float sraw = sv[i + e];
+            const float t = ae_score_mod(sraw, b, hq, q_idx, kv_idx, cu);
+            float p = ae_bwd_forward(t, fr, b, hq, q_idx, kv_idx, cu);
+            float dpv = dp[i + e];
+            if (!keep) {
+              p = 0.f;
+              dpv = 0.f;
+            }
+            const float dT = ae_bwd_backward(dpv, p, fr, delta, b, hq, q_idx, kv_idx, cu);
+            float dsv = ae_score_mod_bwd(sraw, dT, b, hq, q_idx, kv_idx, cu);
+            if (!keep) dsv = 0.f;
+            ds2[e] = dsv;
+          }
+          pk[i >> 1] = pack2<AE_BF16>(ds2[0], ds2[1]);
+        }
+        tmem_st16(tm_s + c * 16, pk);
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->ds_full[buf]);
+    }
+
+    // ---- epilogue: dQ rows -------------------------------------------------------------
+    if (n_steps > 0) {
+      ok = ok && mbar_wait(&bars->dq_done, 0, ctl, args.status, 28);
+      tc_fence_after_sync();
+    }
+    if (row_valid && ok) {
+      u16* drow = (u16*)args.dq + (i64)b * args.dq_sb + (i64)q_idx * args.dq_ss + (i64)hq * args.dq_sh;
+#pragma unroll
+      for (int c = 0; c < AE_D / 32; ++c) {
+        float r[32];
+        if (n_steps > 0) {
+          tmem_ld_f32x32(tmem + TM_DQ + lane_base + c * 32, r);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0.f;
+        }
+        uint4* dst = (uint4*)(drow + c * 32);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 w;
+          w.x = pack2<AE_BF16>(r[v * 8 + 0], r[v * 8 + 1]);
+          w.y = pack2<AE_BF16>(r[v * 8 + 2], r[v * 8 + 3]);
+          w.z = pack2<AE_BF16>(r[v * 8 + 4], r[v * 8 + 5]);
+          w.w = pack2<AE_BF16>(r[v * 8 + 6], r[v * 8 + 7]);
+          dst[v] = w;
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}

@@ -1,0 +1,419 @@
+// Fused attention forward for sm_100a (replaces the reference's generated forward
+// kernel, attention_engine/core/template/tl_template/attn/attn_tl.py:76-174, GQA
+// variant attn_gqa_tl.py:38-133, block-sparse variant blockattn_tl.py:48-162).
+//
+// One CTA owns two query tiles of 128 rows of one (batch, q-head) and streams the
+// K/V tiles of the matching kv-head once for both.  Roles:
+//   warps 0-3 / 4-7 : "row" warpgroups, one per query tile.  Thread i of a group owns
+//                     row i: it reads its 128 scores from TMEM, applies mask,
+//                     score_mod and the online recurrence in registers (no shuffles),
+//                     writes P back to TMEM as 16-bit pairs, rescales O when needed
+//                     and runs the epilogue.
+//   warp 8          : TMA producer (Q once, K/V ring of AE_STAGES stages).
+//   warp 9          : tcgen05.mma issuer; owns the TMEM allocation.
+// TMEM columns: S0 | S1 | O0 | O1 (P_t aliases the first half of S_t).
+// While one group runs its recurrence the tensor pipe runs the other tile's MMAs.
+//
+// Expects the generated prelude to define:
+//   AE_D, AE_DV (multiples of 64, <= 128), AE_BF16 (0/1), AE_STAGES,
+//   AE_MASK_MODE (0 none, 1 causal bounds, 2 block list), AE_NFINAL, AE_O_SCALE_ONE,
+//   struct AeRow, ae_mask(), ae_score_mod(), ae_online_fwd(), ae_epilogue_o(),
+//   ae_final_rowscales().
+
+#define AE_BM 128
+#define AE_BN 128
+#define AE_NTHREADS 320
+
+// shared memory carve-up (dynamic, 1024-byte aligned by the launch)
+#define AE_Q_BYTES (AE_BM * AE_D * 2)
+#define AE_K_BYTES (AE_BN * AE_D * 2)
+#define AE_V_BYTES (AE_BN * AE_DV * 2)
+#define AE_SMEM_Q 0
+#define AE_SMEM_K (2 * AE_Q_BYTES)
+#define AE_SMEM_V (AE_SMEM_K + AE_STAGES * AE_K_BYTES)
+#define AE_SMEM_BAR (AE_SMEM_V + AE_STAGES * AE_V_BYTES)
+#define AE_SMEM_TOTAL (AE_SMEM_BAR + 512)
+
+struct AeFwdBars {
+  u64 q_full[2];
+  u64 k_full[AE_STAGES];
+  u64 k_empty[AE_STAGES];
+  u64 v_full[AE_STAGES];
+  u64 v_empty[AE_STAGES];
+  u64 s_full[2];
+  u64 p_full[2];
+  u64 o_done[2];
+  AeCtaCtl ctl;
+};
+
+// kv tile schedule of one q tile --------------------------------------------------
+// The CTA walks the union of its two tiles' lists; entry `j` of the walk gives the kv
+// tile index and, per q tile, whether it takes part and whether it needs the
+// element-wise mask.
+struct AeKvStep {
+  int kt;        // kv tile index
+  u32 flags;     // bit t: tile t active; bit 2+t: tile t needs element mask
+};
+
+AE_DEVICE int ae_causal_ntiles(int qt, int n_kt) {
+  // rows [qt*128, qt*128+127] see kv columns [0, qt*128+127]
+  int n = qt + 1;
+  return n < n_kt ? n : n_kt;
+}
+
+extern "C" __global__ void __launch_bounds__(AE_NTHREADS, 1)
+ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
+  extern __shared__ u8 smem_raw[];
+  u8* smem = smem_align1024(smem_raw);
+  AeFwdBars* bars = (AeFwdBars*)(smem + AE_SMEM_BAR);
+  AeCtaCtl* ctl = &bars->ctl;
+  const u32 warp = threadIdx.x >> 5;
+  const u32 lane = threadIdx.x & 31;
+
+  // heaviest (latest) q tiles first: better tail under a causal mask
+  const int qpair = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int hq = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hk = hq / (args.Hq / args.Hkv);
+  const int qt0 = qpair * 2;
+
+  // ---- kv schedule (uniform over the CTA) ---------------------------------------
+  int n_steps;
+#if AE_MASK_MODE == 1
+  int n_t0 = ae_causal_ntiles(qt0, args.n_kt);
+  int n_t1 = (qt0 + 1 < args.n_qt) ? ae_causal_ntiles(qt0 + 1, args.n_kt) : 0;
+  n_steps = n_t0 > n_t1 ? n_t0 : n_t1;
+#elif AE_MASK_MODE == 2
+  const int* cnt_base = args.blk_cnt + ((i64)b * args.Hq + hq) * args.n_qt;
+  const int* idx_base = args.blk_idx + ((i64)b * args.Hq + hq) * args.n_qt * (i64)args.n_kt;
+  const int n_t0 = cnt_base[qt0];
+  const int n_t1 = (qt0 + 1 < args.n_qt) ? cnt_base[qt0 + 1] : 0;
+  const int* list0 = idx_base + (i64)qt0 * args.n_kt;
+  const int* list1 = idx_base + (i64)(qt0 + 1) * args.n_kt;
+  n_steps = 0;  // computed by the merge walk below (same code in every role)
+#else
+  int n_t0 = args.n_kt;
+  int n_t1 = (qt0 + 1 < args.n_qt) ? args.n_kt : 0;
+  n_steps = args.n_kt;
+#endif
+
+  // step iterator: all roles call next() in lockstep order
+  struct Walk {
+    int j, i0, i1;
+  } walk = {0, 0, 0};
+  auto next_step = [&](AeKvStep& st) -> bool {
+#if AE_MASK_MODE == 2
+    int a = walk.i0 < n_t0 ? (list0[walk.i0] & 0x3fffffff) : 0x7fffffff;
+    int c = walk.i1 < n_t1 ? (list1[walk.i1] & 0x3fffffff) : 0x7fffffff;
+    int kt = a < c ? a : c;
+    if (kt == 0x7fffffff) return false;
+    st.kt = kt;
+    st.flags = 0;
+    if (a == kt) {
+      st.flags |= 1u | (((u32)list0[walk.i0] >> 30) & 1u) << 2;
+      walk.i0++;
+    }
+    if (c == kt) {
+      st.flags |= 2u | (((u32)list1[walk.i1] >> 30) & 1u) << 3;
+      walk.i1++;
+    }
+    walk.j++;
+    return true;
+#else
+    if (walk.j >= n_steps) return false;
+    st.kt = walk.j;
+    st.flags = 0;
+    if (walk.j < n_t0) st.flags |= 1u;
+    if (walk.j < n_t1) st.flags |= 2u;
+#if AE_MASK_MODE == 3
+    st.flags |= 12u;  // no block information: every tile is masked element-wise
+#endif
+#if AE_MASK_MODE == 1
+    // partial when the tile's last column exceeds the tile's first row
+    if (walk.j * AE_BN + AE_BN - 1 > qt0 * AE_BM) st.flags |= 4u;
+    if (walk.j * AE_BN + AE_BN - 1 > (qt0 + 1) * AE_BM) st.flags |= 8u;
+#endif
+    walk.j++;
+    return true;
+#endif
+  };
+
+  // ---- setup ---------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    ctl->abort = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->q_full[i], 1);
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->p_full[i], 128);
+      mbar_init(&bars->o_done[i], 1);
+    }
+    for (int i = 0; i < AE_STAGES; ++i) {
+      mbar_init(&bars->k_full[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(&ctl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const u32 tmem = ctl->tmem_base;
+  const u32 TM_S0 = 0, TM_S1 = 128, TM_O0 = 256, TM_O1 = 256 + AE_DV;
+
+  if (warp == 8) {
+    // =============================== TMA producer ===============================
+    if (lane == 0) {
+      tma_prefetch_desc(&args.tm_q);
+      tma_prefetch_desc(&args.tm_k);
+      tma_prefetch_desc(&args.tm_v);
+      for (int t = 0; t < 2; ++t) {
+        mbar_arrive_expect_tx(&bars->q_full[t], AE_Q_BYTES);
+        for (int dh = 0; dh < AE_D / 64; ++dh)
+          tma_load_4d(smem + AE_SMEM_Q + t * AE_Q_BYTES + dh * (AE_BM * 128), &args.tm_q, &bars->q_full[t], dh * 64,
+                      hq, (qt0 + t) * AE_BM, b);
+      }
+      AeKvStep st;
+      int it = 0;
+      while (next_step(st)) {
+        const int stage = it % AE_STAGES;
+        const u32 par = ((it / AE_STAGES) & 1) ^ 1;
+        if (!mbar_wait(&bars->k_empty[stage], par, ctl, args.status, 1)) break;
+        mbar_arrive_expect_tx(&bars->k_full[stage], AE_K_BYTES);
+        for (int dh = 0; dh < AE_D / 64; ++dh)
+          tma_load_4d(smem + AE_SMEM_K + stage * AE_K_BYTES + dh * (AE_BN * 128), &args.tm_k, &bars->k_full[stage],
+                      dh * 64, hk, st.kt * AE_BN, b);
+        if (!mbar_wait(&bars->v_empty[stage], par, ctl, args.status, 2)) break;
+        mbar_arrive_expect_tx(&bars->v_full[stage], AE_V_BYTES);
+        for (int dh = 0; dh < AE_DV / 64; ++dh)
+          tma_load_4d(smem + AE_SMEM_V + stage * AE_V_BYTES + dh * (AE_BN * 128), &args.tm_v, &bars->v_full[stage],
+                      dh * 64, hk, st.kt * AE_BN, b);
+        ++it;
+      }
+    }
+  } else if (warp == 9) {
+    // =============================== MMA issuer =================================
+    if (lane == 0) {
+      const u32 idesc_s = umma_idesc_f16(AE_BM, AE_BN, AE_BF16, 0, 0);
+      const u32 idesc_o = umma_idesc_f16(AE_BM, AE_DV, AE_BF16, 0, 1);
+      const u32 q_addr = smem_u32(smem + AE_SMEM_Q);
+      const u32 k_addr = smem_u32(smem + AE_SMEM_K);
+      const u32 v_addr = smem_u32(smem + AE_SMEM_V);
+      const u32 tm_s[2] = {tmem + TM_S0, tmem + TM_S1};
+      const u32 tm_o[2] = {tmem + TM_O0, tmem + TM_O1};
+
+      auto issue_s = [&](int t, int stage) {
+        const u32 qa = q_addr + t * AE_Q_BYTES;
+        const u32 ka = k_addr + stage * AE_K_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < AE_D / 16; ++kk) {
+          const u32 off = (kk >> 2) * (AE_BM * 128) + (kk & 3) * 32;
+          umma_ss(tm_s[t], umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
+                  idesc_s, kk > 0);
+        }
+      };
+      auto issue_pv = [&](int t, int stage, u32 acc) {
+        const u32 va = v_addr + stage * AE_V_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < AE_BN / 16; ++kk) {
+          umma_ts(tm_o[t], tm_s[t] + kk * 8, umma_smem_desc_sw128(va + kk * 2048, AE_BN * 128, 1024), idesc_o,
+                  acc | (kk > 0));
+        }
+      };
+
+      // The walk is consumed one step ahead for the S GEMMs.
+      AeKvStep cur, nxt;
+      bool ok = true;
+      bool have = next_step(cur);
+      int it = 0;
+      u32 np[2] = {0, 0};  // P tiles consumed per q tile
+      if (have) {
+        ok = mbar_wait(&bars->k_full[0], 0, ctl, args.status, 3);
+        tc_fence_after_sync();
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (cur.flags & (1u << t)) {
+            ok = mbar_wait(&bars->q_full[t], 0, ctl, args.status, 4);
+            tc_fence_after_sync();
+            issue_s(t, 0);
+            umma_commit(&bars->s_full[t]);
+          }
+        }
+        umma_commit(&bars->k_empty[0]);
+      }
+      while (have && ok) {
+        const int stage = it % AE_STAGES;
+        const u32 par = (it / AE_STAGES) & 1;
+        const bool have_n = next_step(nxt);
+        const int nstage = (it + 1) % AE_STAGES;
+        const u32 npar = ((it + 1) / AE_STAGES) & 1;
+        bool v_ready = false, k_ready = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (cur.flags & (1u << t)) {
+            ok = mbar_wait(&bars->p_full[t], np[t] & 1, ctl, args.status, 5);
+            if (!ok) break;
+            if (!v_ready) {
+              ok = mbar_wait(&bars->v_full[stage], par, ctl, args.status, 6);
+              if (!ok) break;
+              v_ready = true;
+            }
+            tc_fence_after_sync();
+            issue_pv(t, stage, np[t] > 0);
+            umma_commit(&bars->o_done[t]);
+            np[t]++;
+          }
+          if (have_n && (nxt.flags & (1u << t))) {
+            if (!k_ready) {
+              ok = mbar_wait(&bars->k_full[nstage], npar, ctl, args.status, 7);
+              if (!ok) break;
+              k_ready = true;
+            }
+            ok = mbar_wait(&bars->q_full[t], 0, ctl, args.status, 8);  // Q landed (phase 0 stays complete)
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_s(t, nstage);
+            umma_commit(&bars->s_full[t]);
+          }
+        }
+        umma_commit(&bars->v_empty[stage]);
+        if (have_n) umma_commit(&bars->k_empty[nstage]);
+        cur = nxt;
+        have = have_n;
+        ++it;
+      }
+    }
+  } else {
+    // =============================== row warpgroups =============================
+    const int t = warp >> 2;                 // q tile of this group
+    const u32 row = threadIdx.x & 127;       // row inside the tile == TMEM lane
+    const u32 lane_base = ((warp & 3) * 32) << 16;
+    const u32 tm_s = tmem + (t ? TM_S1 : TM_S0) + lane_base;
+    const u32 tm_o = tmem + (t ? TM_O1 : TM_O0) + lane_base;
+    const int q_idx = (qt0 + t) * AE_BM + (int)row;
+    const bool tile_valid = (qt0 + t) < args.n_qt;
+
+    AeCustom cu;
+#pragma unroll
+    for (int i = 0; i < AE_MAX_CUSTOM; ++i) {
+      cu.p[i] = args.custom[i];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) cu.st[i][k] = args.custom_st[i][k];
+    }
+
+    AeRow st;
+    st.init();
+    u32 n_done = 0;
+    bool ok = true;
+    AeKvStep step;
+    while (next_step(step)) {
+      if (!(step.flags & (1u << t))) continue;
+      ok = ok && mbar_wait(&bars->s_full[t], n_done & 1, ctl, args.status, 9);
+      tc_fence_after_sync();
+      float s[AE_BN];
+      tmem_ld_f32x128(tm_s, s);
+      const int kv0 = step.kt * AE_BN;
+      const bool tail = (kv0 + AE_BN > args.Skv);
+      const bool partial = (step.flags >> (2 + t)) & 1u;
+      if (partial || tail) {
+#pragma unroll
+        for (int c = 0; c < AE_BN; ++c) {
+          const int kv_idx = kv0 + c;
+          bool keep = kv_idx < args.Skv;
+#if AE_MASK_MODE != 0
+          if (partial) keep = keep && ae_mask(b, hq, q_idx, kv_idx);
+#endif
+#if AE_MASK_NEG_INF
+          if (!keep) s[c] = -__int_as_float(0x7f800000);
+#else
+          if (kv_idx >= args.Skv) s[c] = 0.f;  // additive mask value 0: scores stay as they are
+          (void)keep;
+#endif
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < AE_BN; ++c) s[c] = ae_score_mod(s[c], b, hq, q_idx, kv0 + c, cu);
+
+      const float o_scale = ae_online_fwd<AE_BN>(s, st, b, hq, q_idx, kv0, cu);
+
+      // P -> TMEM (16-bit pairs, column c/2 holds kv columns c, c+1)
+      {
+        u32 pk[32];
+#pragma unroll
+        for (int half = 0; half < AE_BN / 64; ++half) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pk[i] = pack2<AE_BF16>(s[half * 64 + 2 * i], s[half * 64 + 2 * i + 1]);
+          tmem_st32(tm_s + half * 32, pk);
+        }
+      }
+#if !AE_O_SCALE_ONE
+      if (n_done > 0) {
+        // O of the previous step must be complete before it is rescaled
+        ok = ok && mbar_wait(&bars->o_done[t], (n_done - 1) & 1, ctl, args.status, 10);
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, o_scale != 1.0f)) {
+#pragma unroll
+          for (int c = 0; c < AE_DV / 32; ++c) {
+            float f[32];
+            u32 r[32];
+            tmem_ld_f32x32(tm_o + c * 32, f);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(f[i] * o_scale);
+            tmem_st32(tm_o + c * 32, r);
+          }
+        }
+      }
+#endif
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->p_full[t]);
+      ++n_done;
+    }
+
+    // ---- epilogue ------------------------------------------------------------------
+    if (n_done > 0) {
+      ok = ok && mbar_wait(&bars->o_done[t], (n_done - 1) & 1, ctl, args.status, 11);
+      tc_fence_after_sync();
+    }
+    if (tile_valid && q_idx < args.Sq && ok) {
+      u16* orow = (u16*)args.o + (i64)b * args.o_sb + (i64)q_idx * args.o_ss + (i64)hq * args.o_sh;
+#pragma unroll
+      for (int c = 0; c < AE_DV / 32; ++c) {
+        float r[32];
+        if (n_done > 0) {
+          tmem_ld_f32x32(tm_o + c * 32, r);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0.f;
+        }
+        uint4* dst = (uint4*)(orow + c * 32);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 w;
+          w.x = pack2<AE_BF16>(ae_epilogue_o((r[v * 8 + 0]), st), ae_epilogue_o((r[v * 8 + 1]), st));
+          w.y = pack2<AE_BF16>(ae_epilogue_o((r[v * 8 + 2]), st), ae_epilogue_o((r[v * 8 + 3]), st));
+          w.z = pack2<AE_BF16>(ae_epilogue_o((r[v * 8 + 4]), st), ae_epilogue_o((r[v * 8 + 5]), st));
+          w.w = pack2<AE_BF16>(ae_epilogue_o((r[v * 8 + 6]), st), ae_epilogue_o((r[v * 8 + 7]), st));
+          dst[v] = w;
+        }
+      }
+#if AE_NFINAL > 0
+      float fr[AE_NFINAL];
+      ae_final_rowscales(st, fr);
+#pragma unroll
+      for (int i = 0; i < AE_NFINAL; ++i)
+        args.final_rs[i][((i64)b * args.Hq + hq) * args.Sq + q_idx] = fr[i];
+#endif
+    }
+  }
+
+  // ---- teardown --------------------------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}

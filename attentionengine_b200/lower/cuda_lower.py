@@ -1,0 +1,471 @@
+"""Lower traced IR expressions to CUDA C++ functor fragments.
+
+Replaces the reference's lowering + codegen layers for the attention path
+(attention_engine/core/lower/lower.py:318-614 ``lower_online_func`` / ``lower_score_mod`` /
+``lower_custom_inputs`` and core/codegen/tl_gen.py:7-132,306-370), which emit TileLang statements
+over tile buffers.  Here one query row is owned by one thread, so
+
+* tile values ([block_M, block_N]) become ``float x[N]`` register arrays indexed by the column,
+* row values ([block_M]) become scalars,
+* row reductions become in-thread loops (no shuffles),
+
+and the result is a *prelude*: ``#define``s plus ``__device__`` functions that the hand-written
+kernel templates in ``csrc/kernels`` call.  Evaluation order follows the DAG (SSA), so the result
+does not depend on operand order the way the reference's in-place buffer reuse does.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+from ..core.transform.core import (CustomIO, SymbolicArray, SymbolicConst, SymbolicTensor, SymbolScalar)
+from ..core.transform.graph import Var
+
+NEG_INF_SENTINEL = "-1e38f"  # finite stand-in for a "-inf" initial row scale (reference: lower.py:23-29)
+
+
+def _flit(x: float) -> str:
+    if isinstance(x, str):
+        x = x.strip()
+        if x in ("-inf", "-float('inf')"):
+            return NEG_INF_SENTINEL
+        if x in ("inf", "float('inf')"):
+            return "1e38f"
+        x = float(x)
+    if math.isinf(x):
+        return NEG_INF_SENTINEL if x < 0 else "1e38f"
+    r = repr(float(x))
+    if "e" not in r and "." not in r:
+        r += ".0"
+    return r + "f"
+
+
+def _is_number(s: str) -> bool:
+    try:
+        float(s)
+        return True
+    except ValueError:
+        return s.strip() in ("-inf", "inf")
+
+
+_RANK = {"const": 0, "uniform": 1, "row": 2, "tile": 3}
+
+
+class Emitter:
+    """Emits C++ for a set of root values.  ``env`` maps id(leaf SymbolScalar) or a leaf's Var
+    name to a (C++ expression, kind) pair; tile-kind leaf expressions contain ``{c}`` where the
+    column index goes."""
+
+    def __init__(self, env_by_id: dict, env_by_name: dict, n_cols: str = "N", tile_mode: str = "array"):
+        self.by_id = env_by_id
+        self.by_name = env_by_name
+        self.n = n_cols
+        self.tile_mode = tile_mode  # "array": tiles are float[N]; "scalar": inside a per-element function
+        self.lines: list[str] = []
+        self.names: dict[int, tuple[str, str]] = {}  # id(value) -> (expr, kind)
+        self.used_leaves: set[str] = set()
+        self.k = 0
+
+    def _tmp(self) -> str:
+        self.k += 1
+        return f"t{self.k}"
+
+    def ref(self, v: SymbolScalar, col: str = "c") -> str:
+        expr, kind = self.value(v)
+        if kind == "tile" and self.tile_mode == "array":
+            return expr.replace("{c}", col)
+        return expr
+
+    def value(self, v: SymbolScalar) -> tuple[str, str]:
+        if id(v) in self.names:
+            return self.names[id(v)]
+        res = self._lower(v)
+        self.names[id(v)] = res
+        return res
+
+    def _leaf(self, v: SymbolScalar) -> tuple[str, str]:
+        if id(v) in self.by_id:
+            e = self.by_id[id(v)]
+            self.used_leaves.add(v.varname)
+            return e
+        t = v.code.type
+        if t == "Const":
+            return _flit(v.code.value), "const"
+        if t == "Var":
+            nm = v.code.name
+            if v.varname in self.by_name:
+                self.used_leaves.add(v.varname)
+                return self.by_name[v.varname]
+            if nm in self.by_name:
+                self.used_leaves.add(nm)
+                return self.by_name[nm]
+            if _is_number(nm):
+                return _flit(nm), "const"
+        raise KeyError(f"unbound symbolic value {v.varname!r} ({v.code})")
+
+    def _lower(self, v: SymbolScalar) -> tuple[str, str]:
+        if not v.prev:
+            return self._leaf(v)
+        t = v.code.type
+        ops = [self.value(p) for p in v.prev]
+        kinds = [k for _, k in ops]
+        if t in ("ReduceSum", "ReduceMax", "ReduceAbsSum"):
+            src = self.ref(v.prev[0], "c")
+            if kinds[0] != "tile" or self.tile_mode != "array":
+                raise NotImplementedError("row reduction outside of online_fwd")
+            name = self._tmp()
+            if t == "ReduceMax":
+                self.lines.append(f"float {name} = {self.ref(v.prev[0], '0')};")
+                self.lines.append(f"#pragma unroll\nfor (int c = 1; c < {self.n}; ++c) {name} = fmaxf({name}, {src});")
+            elif t == "ReduceSum":
+                self.lines.append(f"float {name} = 0.f;")
+                self.lines.append(f"#pragma unroll\nfor (int c = 0; c < {self.n}; ++c) {name} += {src};")
+            else:
+                self.lines.append(f"float {name} = 0.f;")
+                self.lines.append(f"#pragma unroll\nfor (int c = 0; c < {self.n}; ++c) {name} += fabsf({src});")
+            return name, "row"
+        kind = max(kinds, key=lambda k: _RANK[k])
+        if kind == "const":
+            kind = "uniform"
+        a = [self.ref(p, "c") for p in v.prev]
+        expr = self._expr(t, a)
+        name = self._tmp()
+        if kind == "tile" and self.tile_mode == "array":
+            self.lines.append(f"float {name}[{self.n}];")
+            self.lines.append(f"#pragma unroll\nfor (int c = 0; c < {self.n}; ++c) {name}[c] = {expr};")
+            return name + "[{c}]", "tile"
+        self.lines.append(f"const float {name} = {expr};")
+        return name, kind
+
+    @staticmethod
+    def _expr(t: str, a: list[str]) -> str:
+        if t == "Add":
+            return f"({a[0]} + {a[1]})"
+        if t == "Sub":
+            return f"({a[0]} - {a[1]})"
+        if t == "Mul":
+            return f"({a[0]} * {a[1]})"
+        if t == "Div":
+            return f"__fdividef({a[0]}, {a[1]})"
+        if t == "Neg":
+            return f"(-{a[0]})"
+        if t == "Abs":
+            return f"fabsf({a[0]})"
+        if t == "Max":
+            return f"fmaxf({a[0]}, {a[1]})"
+        if t == "Exp":
+            return f"ae_exp({a[0]})"
+        if t == "Exp2":
+            return f"ae_exp2({a[0]})"
+        if t == "Log":
+            return f"ae_log({a[0]})"
+        if t == "Log2":
+            return f"ae_log2({a[0]})"
+        if t == "Tanh":
+            return f"ae_tanh({a[0]})"
+        if t == "MaxBwd":
+            return f"(({a[1]} > {a[2]}) ? {a[0]} : 0.f)"
+        raise NotImplementedError(f"no CUDA lowering for IR op {t}")
+
+    def body(self, indent: str = "  ") -> str:
+        return "".join(indent + l + "\n" for l in self.lines)
+
+
+# -------------------------------------------------------------------------------------------
+# custom inputs
+# -------------------------------------------------------------------------------------------
+_DIM_SLOT = {"batch": 0, "heads": 1, "seq_len": 2, "seq_len_kv": 3}
+
+
+@dataclass
+class CustomSpec:
+    name: str
+    shape: tuple
+    slot: int
+    is_16bit: bool            # tile-shaped inputs travel in the q/k/v dtype, the rest in fp32
+    dim_slots: list           # per tensor dim: index slot (0 b, 1 h, 2 q, 3 kv) or -1 for broadcast
+
+
+def custom_specs(custom: CustomIO) -> list[CustomSpec]:
+    specs = []
+    for slot, (name, t) in enumerate(custom.input_tensors.items()):
+        shape = tuple(t.shape_idx)
+        dims = [(_DIM_SLOT[s] if s in _DIM_SLOT else -1) for s in shape]
+        for s in shape:
+            if s not in _DIM_SLOT and not (s.isdigit() and int(s) == 1):
+                raise NotImplementedError(f"custom input {name}: dimension {s!r} is not one of "
+                                          f"{sorted(_DIM_SLOT)} or 1")
+        is16 = (2 in dims) and (3 in dims)
+        specs.append(CustomSpec(name, shape, slot, is16, dims))
+    if len(specs) > 4:
+        raise NotImplementedError("at most 4 custom inputs are supported")
+    return specs
+
+
+def _custom_env(specs: list[CustomSpec], custom: CustomIO, bf16: bool, tile_mode: str, transposed: bool = False):
+    env = {}
+    for sp in specs:
+        t = custom.input_tensors[sp.name]
+        kind = "tile" if 3 in sp.dim_slots else ("row" if 2 in sp.dim_slots else "uniform")
+        kv = "(kv0 + {c})" if tile_mode == "array" else "kv_idx"
+        names = {0: "b", 1: "h", 2: "q_idx", 3: kv}
+        terms = [f"(i64){names[d]} * cu.st[{sp.slot}][{d}]" for d in sorted(set(sp.dim_slots)) if d >= 0]
+        idx = " + ".join(terms) if terms else "0"
+        if sp.is_16bit:
+            expr = f"ae_ld16<{1 if bf16 else 0}>(cu.p[{sp.slot}], {idx})"
+        else:
+            expr = f"((const float*)cu.p[{sp.slot}])[{idx}]"
+        env[id(t)] = (expr, kind)
+    return env
+
+
+# -------------------------------------------------------------------------------------------
+# the lowered bundle
+# -------------------------------------------------------------------------------------------
+@dataclass
+class LoweredAttention:
+    prelude_fwd: str
+    prelude_bwd: str
+    final_names: list[str]
+    custom: list[CustomSpec]
+    o_scale_one: bool
+    uses_doosum: bool
+    has_mask: bool
+    defines: dict = field(default_factory=dict)
+
+
+def _trace_mask(mask_mod: Optional[Callable]) -> Optional[str]:
+    """C++ boolean expression over (b, h, q_idx, kv_idx) for ``mask_mod`` (reference: fx trace of
+    the mask restricted to python operators and logical_and, core/codegen/common.py:124-152).
+    Traced with a tiny operator-overloading value instead of torch.fx."""
+    if mask_mod is None:
+        return None
+
+    class E:
+        def __init__(self, s):
+            self.s = s
+
+        def _b(self, o, op):
+            return E(f"({self.s} {op} {_e(o)})")
+
+        def _rb(self, o, op):
+            return E(f"({_e(o)} {op} {self.s})")
+
+        __add__ = lambda a, o: a._b(o, "+")
+        __radd__ = lambda a, o: a._rb(o, "+")
+        __sub__ = lambda a, o: a._b(o, "-")
+        __rsub__ = lambda a, o: a._rb(o, "-")
+        __mul__ = lambda a, o: a._b(o, "*")
+        __rmul__ = lambda a, o: a._rb(o, "*")
+        __floordiv__ = lambda a, o: a._b(o, "/")
+        __mod__ = lambda a, o: a._b(o, "%")
+        __ge__ = lambda a, o: a._b(o, ">=")
+        __gt__ = lambda a, o: a._b(o, ">")
+        __le__ = lambda a, o: a._b(o, "<=")
+        __lt__ = lambda a, o: a._b(o, "<")
+        __eq__ = lambda a, o: a._b(o, "==")
+        __ne__ = lambda a, o: a._b(o, "!=")
+        __and__ = lambda a, o: a._b(o, "&&")
+        __rand__ = lambda a, o: a._rb(o, "&&")
+        __or__ = lambda a, o: a._b(o, "||")
+        __ror__ = lambda a, o: a._rb(o, "||")
+        __invert__ = lambda a: E(f"(!{a.s})")
+        __neg__ = lambda a: E(f"(-{a.s})")
+        __hash__ = None
+
+        def __bool__(self):
+            raise TypeError("mask_mod must not branch on index values; combine conditions with & and |")
+
+        @classmethod
+        def __torch_function__(cls, func, types, args=(), kwargs=None):
+            nm = getattr(func, "__name__", "")
+            if nm == "logical_and":
+                return E(f"({_e(args[0])} && {_e(args[1])})")
+            if nm == "logical_or":
+                return E(f"({_e(args[0])} || {_e(args[1])})")
+            if nm == "logical_not":
+                return E(f"(!{_e(args[0])})")
+            if nm == "abs":
+                return E(f"abs({_e(args[0])})")
+            raise NotImplementedError(f"mask_mod uses torch.{nm}, which has no CUDA lowering")
+
+    def _e(o):
+        if isinstance(o, E):
+            return o.s
+        if isinstance(o, bool):
+            return "true" if o else "false"
+        if isinstance(o, int):
+            return str(o)
+        raise TypeError(f"mask_mod mixes index values with {type(o).__name__}")
+
+    out = mask_mod(E("b"), E("h"), E("q_idx"), E("kv_idx"))
+    return _e(out)
+
+
+_LD16 = """
+template <int kBf16>
+AE_DEVICE float ae_ld16(const void* p, i64 idx) {
+  const u16 w = ((const u16*)p)[idx];
+  return unpack_lo<kBf16>((u32)w);
+}
+"""
+
+
+def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomIO, *, D: int, DV: int, bf16: bool,
+                    mask_mode: int, stages: int = 2, mask_value: str = "-inf") -> LoweredAttention:
+    """Trace the user callables and produce the kernel preludes.
+
+    Order of operations per score tile follows the reference forward kernel
+    (core/template/tl_template/attn/attn_tl.py:124-164): mask (to ``mask_value``) -> score_mod ->
+    online_fwd -> rescale O by o_scale -> O += P V; after the loop online_fwd_epilogue.  The backward
+    fragments follow attn_tl.py:348-403: score_mod, OnlineFunc.forward with the saved final
+    rowscales, OnlineFunc.backward (its ``scores`` argument is P), score_mod's derivative.
+    """
+    specs = custom_specs(custom_fwd_inputs)
+    idx_env = {"b": ("(float)b", "uniform"), "h": ("(float)h", "uniform"), "q_idx": ("(float)q_idx", "row"),
+               "kv_idx": ("(float)kv_idx", "tile")}
+
+    def sym_idx(name):
+        return SymbolScalar(name, Var(name), shape_idx=["block_N"] if name == "kv_idx" else (
+            ["block_M"] if name == "q_idx" else ["1"]), require_grad=False)
+
+    src = []
+    src.append(_LD16)
+
+    # ---- mask ---------------------------------------------------------------------------------
+    mask_expr = _trace_mask(mask_mod)
+    src.append("AE_DEVICE bool ae_mask(int b, int h, int q_idx, int kv_idx) { return %s; }\n" %
+               (mask_expr if mask_expr is not None else "true"))
+
+    # ---- score_mod (per element) -----------------------------------------------------------------
+    def trace_score_mod():
+        scores = SymbolicArray("scores", Var("scores"), shape_idx=["block_M", "block_N"])
+        out = score_mod(scores, custom_fwd_inputs, sym_idx("b"), sym_idx("h"), sym_idx("q_idx"), sym_idx("kv_idx"))
+        return scores, out
+
+    scores, out = trace_score_mod()
+    env = _custom_env(specs, custom_fwd_inputs, bf16, "scalar")
+    env[id(scores)] = ("s", "tile")
+    em = Emitter(env, idx_env, tile_mode="scalar")
+    res = em.ref(out)
+    src.append("AE_DEVICE float ae_score_mod(float s, int b, int h, int q_idx, int kv_idx, const AeCustom& cu) {\n"
+               + em.body() + f"  return {res};\n}}\n")
+
+    # derivative of score_mod: dS = f'(S) * dT
+    scores_b, out_b = trace_score_mod()
+    seed = SymbolicArray("dT", Var("dT"), shape_idx=["block_M", "block_N"])
+    seed.require_grad = False
+    out_b.backward(seed)
+    env = _custom_env(specs, custom_fwd_inputs, bf16, "scalar")
+    env[id(scores_b)] = ("s", "tile")
+    env[id(seed)] = ("dT", "tile")
+    em = Emitter(env, idx_env, tile_mode="scalar")
+    if scores_b.grad is None:
+        gres = "0.f"
+    else:
+        gres = em.ref(scores_b.grad)
+    score_mod_bwd_src = (
+        "AE_DEVICE float ae_score_mod_bwd(float s, float dT, int b, int h, int q_idx, int kv_idx, const AeCustom& cu) {\n"
+        + em.body() + f"  return {gres};\n}}\n")
+
+    # ---- online_fwd (per row, N columns) ------------------------------------------------------------
+    state_names = list(online_func.online_rowscales.keys())
+    state_init = {k: v.code.name if v.code.type == "Var" else str(v.code.value)
+                  for k, v in online_func.online_rowscales.items()}
+    row_struct = "struct AeRow {\n"
+    if state_names:
+        row_struct += "  float " + ", ".join(f"st_{k}" for k in state_names) + ";\n"
+    row_struct += "  AE_DEVICE void init() {" + " ".join(
+        f"st_{k} = {_flit(state_init[k])};" for k in state_names) + " }\n};\n"
+    src.append(row_struct)
+
+    t_scores = SymbolicArray("scores", Var("scores"), shape_idx=["block_M", "block_N"])
+    rs_in = {}
+    env = _custom_env(specs, custom_fwd_inputs, bf16, "array")
+    for k in state_names:
+        v = SymbolScalar(k, Var(k), shape_idx=["block_M"])
+        rs_in[k] = v
+        env[id(v)] = (f"st.st_{k}", "row")
+    env[id(t_scores)] = ("s[{c}]", "tile")
+    new_scores, new_rs, o_scale = online_func.online_fwd(t_scores, dict(rs_in), sym_idx("b"), sym_idx("h"),
+                                                          sym_idx("q_idx"))
+    em = Emitter(env, {"b": idx_env["b"], "h": idx_env["h"], "q_idx": idx_env["q_idx"]}, n_cols="N")
+    o_expr, o_kind = em.value(o_scale)
+    o_scale_one = (o_kind == "const" and float(o_expr.rstrip("f")) == 1.0)
+    new_exprs = {k: em.ref(v) for k, v in new_rs.items()}
+    p_expr = em.ref(new_scores, "c")
+    body = em.body()
+    body += "".join(f"  const float n_{k} = {e};\n" for k, e in new_exprs.items())
+    body += f"  const float o_scale_ = {o_expr};\n"
+    if id(new_scores) != id(t_scores):
+        body += f"  #pragma unroll\nfor (int c = 0; c < N; ++c) s[c] = {p_expr};\n"
+    body += "".join(f"  st.st_{k} = n_{k};\n" for k in new_exprs)
+    src.append("template <int N>\nAE_DEVICE float ae_online_fwd(float (&s)[N], AeRow& st, int b, int h, int q_idx, "
+               "int kv0, const AeCustom& cu) {\n" + body + "  return o_scale_;\n}\n")
+
+    # ---- epilogue --------------------------------------------------------------------------------------
+    o_sym = SymbolicArray("o", Var("o"), shape_idx=["block_M", "dimv"])
+    rs_ep = {}
+    env = {}
+    for k in state_names:
+        v = SymbolScalar(k, Var(k), shape_idx=["block_M"])
+        rs_ep[k] = v
+        env[id(v)] = (f"st.st_{k}", "row")
+    env[id(o_sym)] = ("o", "row")
+    o_new, finals = online_func.online_fwd_epilogue(o_sym, rs_ep, sym_idx("b"), sym_idx("h"), sym_idx("q_idx"))
+    em = Emitter(env, {}, tile_mode="scalar")
+    res = em.ref(o_new)
+    src.append("AE_DEVICE float ae_epilogue_o(float o, const AeRow& st) {\n" + em.body() + f"  return {res};\n}}\n")
+    final_names = list(finals.keys())
+    if len(final_names) > 4:
+        raise NotImplementedError("at most 4 final rowscales are supported")
+    em = Emitter(env, {}, tile_mode="scalar")
+    fl = [em.ref(v) for v in finals.values()]
+    src.append("AE_DEVICE void ae_final_rowscales(const AeRow& st, float* out) {\n" + em.body()
+               + "".join(f"  out[{i}] = {e};\n" for i, e in enumerate(fl)) + "}\n")
+
+    # ---- backward fragments ----------------------------------------------------------------------------------
+    bsrc = []
+    qkT = SymbolScalar("scores", Var("scores"), shape_idx=["block_M", "block_N"])
+    fr = {}
+    env = _custom_env(specs, custom_fwd_inputs, bf16, "scalar")
+    for i, k in enumerate(final_names):
+        v = SymbolScalar(k, Var(k), shape_idx=["block_M"], require_grad=False)
+        fr[k] = v
+        env[id(v)] = (f"fr[{i}]", "row")
+    env[id(qkT)] = ("t", "tile")
+    p_out = online_func.forward(qkT, fr, sym_idx("b"), sym_idx("h"), sym_idx("q_idx"), sym_idx("kv_idx"))
+    em = Emitter(env, idx_env, tile_mode="scalar")
+    res = em.ref(p_out)
+    bsrc.append("AE_DEVICE float ae_bwd_forward(float t, const float* fr, int b, int h, int q_idx, int kv_idx, "
+                "const AeCustom& cu) {\n" + em.body() + f"  return {res};\n}}\n")
+
+    dp = SymbolScalar("dp", Var("dp"), shape_idx=["block_M", "block_N"])
+    pp = SymbolScalar("p", Var("p"), shape_idx=["block_M", "block_N"])
+    doosum = SymbolScalar("doosum", Var("doosum"), shape_idx=["block_M"])
+    env2 = dict(env)
+    env2[id(dp)] = ("dp", "tile")
+    env2[id(pp)] = ("p", "tile")
+    env2[id(doosum)] = ("doosum", "row")
+    ds = online_func.backward(dp, pp, fr, doosum, sym_idx("b"), sym_idx("h"), sym_idx("q_idx"), sym_idx("kv_idx"))
+    em = Emitter(env2, idx_env, tile_mode="scalar")
+    res = em.ref(ds)
+    uses_doosum = "doosum" in em.used_leaves
+    bsrc.append("AE_DEVICE float ae_bwd_backward(float dp, float p, const float* fr, float doosum, int b, int h, "
+                "int q_idx, int kv_idx, const AeCustom& cu) {\n" + em.body() + f"  return {res};\n}}\n")
+    bsrc.append(score_mod_bwd_src)
+
+    defines = {
+        "AE_D": D, "AE_DV": DV, "AE_BF16": int(bf16), "AE_STAGES": stages, "AE_MASK_MODE": mask_mode,
+        "AE_NFINAL": len(final_names), "AE_O_SCALE_ONE": int(o_scale_one), "AE_USES_DOOSUM": int(uses_doosum),
+        "AE_MASK_NEG_INF": int(str(mask_value).strip() in ("-inf", "-float('inf')")),
+    }
+    head = "".join(f"#define {k} {v}\n" for k, v in defines.items()) + "struct AeCustom;\n"
+    fwd = head + "".join(src)
+    bwd = fwd + "".join(bsrc)
+    return LoweredAttention(prelude_fwd=fwd, prelude_bwd=bwd, final_names=final_names, custom=specs,
+                            o_scale_one=o_scale_one, uses_doosum=uses_doosum, has_mask=mask_mod is not None,
+                            defines=defines)

@@ -1,0 +1,166 @@
+/* C ABI of libae_b200.so: the B200 (sm_100a) back end behind AttentionEngine's
+ * operator API.
+ *
+ * The reference has no C interface for this path: its Python front end renders a
+ * TileLang module and lets TileLang/TVM compile and launch it
+ * (attention_engine/attn_engine/attn_engine.py:334-395), or binds the CuTe kernels
+ * with pybind11 (attention_engine/core/template/cute_template/flash_api.cpp:696-697,
+ * cute_template_kvshared/flash_api.cpp:212-216).  The entry points below are what a
+ * ctypes / cffi stub in that front end binds instead.  Each comment names the
+ * reference interface the entry point stands in for.
+ *
+ * Conventions
+ *  - plain pointers and sizes only; device pointers are raw CUDA device addresses;
+ *  - every function returns 0 on success or an AE_ERR_* code (ae_strerror() gives
+ *    text); nothing here calls exit() or traps;
+ *  - `stream` is a cudaStream_t / CUstream passed as void*;
+ *  - all tensors are owned by the caller; the library allocates no device memory;
+ *  - runtime tensors are [B, S, H, D] with the last dimension contiguous; strides
+ *    are in elements, ordered (batch, seq, head);
+ *  - `status` is an optional device word the kernels write when a bounded wait gives
+ *    up (0 = ok); the caller clears and reads it.
+ */
+#ifndef AE_B200_H_
+#define AE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  AE_OK = 0,
+  AE_ERR_INVALID = 1,     /* bad argument (null pointer, unsupported shape / dtype / stride) */
+  AE_ERR_COMPILE = 2,     /* NVRTC reported errors; see the log buffer */
+  AE_ERR_NO_NVRTC = 3,    /* libnvrtc could not be loaded */
+  AE_ERR_NO_DRIVER = 4,   /* libcuda could not be loaded / no CUDA context */
+  AE_ERR_CUDA = 5,        /* a driver call failed; ae_last_error() has the text */
+  AE_ERR_UNSUPPORTED = 6, /* kernel kind does not match the entry point */
+};
+
+enum { AE_DTYPE_F16 = 0, AE_DTYPE_BF16 = 1 };
+
+enum {
+  AE_KIND_PROBE = 0,
+  AE_KIND_ATTN_FWD = 1,
+  AE_KIND_ATTN_BWD_PREP = 2,
+  AE_KIND_ATTN_BWD_DQ = 3,
+  AE_KIND_ATTN_BWD_DKV = 4,
+  AE_KIND_MLA_DECODE = 5,
+  AE_KIND_MLA_COMBINE = 6,
+  AE_KIND_LINEAR_FWD = 7,
+  AE_KIND_LINEAR_BWD = 8,
+};
+
+#define AE_MAX_CUSTOM_INPUTS 4
+#define AE_MAX_FINAL_ROWSCALES 4
+
+/* Static facts about one compiled kernel, given by whoever generated its source. */
+typedef struct AeKernelConfig {
+  int kind;       /* AE_KIND_* */
+  int dtype;      /* AE_DTYPE_* */
+  int head_dim;   /* D  */
+  int head_dim_v; /* DV */
+  int threads;    /* block size */
+  int smem_bytes; /* dynamic shared memory */
+  int stages;     /* depth of the K/V (or Q/dO) ring */
+  int mask_mode;  /* 0 none, 1 causal loop bounds, 2 block list */
+  int reserved[8];
+} AeKernelConfig;
+
+/* Resource usage read back from the driver after loading. */
+typedef struct AeKernelInfo {
+  int num_regs;
+  int static_smem_bytes;
+  int max_dynamic_smem_bytes;
+  int local_bytes; /* spill / stack bytes per thread */
+  int max_threads;
+} AeKernelInfo;
+
+/* Compile CUDA C++ source to an sm_100a cubin with NVRTC and wrap it in a module
+ * handle.  No GPU is needed; the cubin is loaded into the current context on the
+ * first launch.  Replaces the reference's JIT step `tl.compile(...)` run when the
+ * rendered module is imported (core/template/tl_template/attn/attn_tl.py:523-561)
+ * and `torch.utils.cpp_extension.load` (cute_template/flash_attn_interface.py:136-147). */
+int ae_compile(const char* cuda_src, const char* kernel_name, const char* arch, const char** opts, int nopts,
+               const AeKernelConfig* cfg, void** out_module, char* log, size_t log_cap);
+
+/* Wrap a cubin produced earlier (content-addressed cache).  Replaces the
+ * reference's md5-keyed source cache (attn_engine/attn_engine.py:369-382). */
+int ae_module_from_cubin(const void* cubin, size_t size, const char* kernel_name, const AeKernelConfig* cfg,
+                         void** out_module);
+/* Borrow the module's cubin image (valid until ae_release). */
+int ae_module_cubin(void* module, const void** data, size_t* size);
+/* Load (if needed) and report registers / shared memory / spills.  Needs a GPU. */
+int ae_query(void* module, AeKernelInfo* info);
+void ae_release(void* module);
+const char* ae_strerror(int code);
+/* Text of the last driver / NVRTC failure on the calling thread. */
+const char* ae_last_error(void);
+
+/* ---- fused attention forward --------------------------------------------------
+ * Stands in for the generated `_attention.forward` -> `mod(q, k, v, *custom)`
+ * (core/template/tl_template/attn/attn_tl.py:567-580; GQA attn_gqa_tl.py:354-380;
+ * block-sparse blockattn_tl.py). */
+typedef struct AeAttnParams {
+  const void* q; /* [B, Sq, Hq, D]   */
+  const void* k; /* [B, Skv, Hkv, D] */
+  const void* v; /* [B, Skv, Hkv, DV]*/
+  void* o;       /* [B, Sq, Hq, DV]  */
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3]; /* (batch, seq, head) */
+  float* final_rowscales[AE_MAX_FINAL_ROWSCALES];             /* each [B, Hq, Sq] fp32 */
+  const void* custom[AE_MAX_CUSTOM_INPUTS];
+  int64_t custom_stride[AE_MAX_CUSTOM_INPUTS][4]; /* over (b, h, q, kv); 0 = broadcast */
+  const int32_t* block_count; /* [B, Hq, n_qt]        (mask_mode 2) */
+  const int32_t* block_index; /* [B, Hq, n_qt, n_kt]  (mask_mode 2) */
+  int32_t B, Hq, Hkv, Sq, Skv;
+  uint32_t* status;
+} AeAttnParams;
+
+int ae_launch_attn_fwd(void* module, const AeAttnParams* p, void* stream);
+
+/* ---- attention backward -----------------------------------------------------------
+ * Stands in for `_attention.backward` (attn_tl.py:582-601): `mod_prep(o, dO)` (K2,
+ * attn_tl.py:196-223), `mod_bwd(...)` (K3, :239-415) and `mod_post(dq)` (K4, :436-455).
+ * Here the dQ and the dK/dV parts are two launches with no atomics and no fp32 dQ
+ * staging buffer, so there is no post kernel. */
+typedef struct AeAttnBwdParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  void* dq;
+  void* dk;
+  void* dv;
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], do_stride[3];
+  int64_t dq_stride[3], dk_stride[3], dv_stride[3];
+  const float* final_rowscales[AE_MAX_FINAL_ROWSCALES];
+  float* delta; /* [B, Hq, Sq] fp32 scratch: rowsum(O * dO) */
+  const void* custom[AE_MAX_CUSTOM_INPUTS];
+  int64_t custom_stride[AE_MAX_CUSTOM_INPUTS][4];
+  const int32_t* block_count;
+  const int32_t* block_index;
+  const int32_t* block_count_t; /* transposed lists: per kv tile, the q tiles */
+  const int32_t* block_index_t;
+  int32_t B, Hq, Hkv, Sq, Skv;
+  uint32_t* status;
+} AeAttnBwdParams;
+
+int ae_launch_attn_bwd_prep(void* module, const AeAttnBwdParams* p, void* stream);
+int ae_launch_attn_bwd_dq(void* module, const AeAttnBwdParams* p, void* stream);
+int ae_launch_attn_bwd_dkv(void* module, const AeAttnBwdParams* p, void* stream);
+
+/* ---- bring-up probe (tests only): one 128x128x128 tcgen05 GEMM -------------------
+ * mode 0: d = a * b^T (a, b [128,128] 16-bit row-major);
+ * mode 1: d = p * b   (p, b [128,128] 16-bit row-major). d is [128,128] fp32.
+ * No counterpart in the reference. */
+int ae_launch_probe(void* module, const void* a, const void* b, const void* p, float* d, int mode, uint32_t* status,
+                    void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AE_B200_H_ */
