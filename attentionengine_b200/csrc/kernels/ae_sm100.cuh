@@ -83,23 +83,22 @@ struct AeCtaCtl {
 };
 
 #ifndef AE_WAIT_CYCLES
-#define AE_WAIT_CYCLES 4000000000ll  // about two seconds at B200 clocks
+#define AE_WAIT_CYCLES 2000000000ll  // about one second at B200 clocks
 #endif
 
 // Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting.
+// mbarrier.try_wait may itself block for a system-dependent time, so the clock and the abort
+// word are checked after every failed poll.
 AE_DEVICE bool mbar_wait(u64* bar, u32 parity, AeCtaCtl* ctl, u32* g_status, u32 site) {
   if (mbar_try_wait(bar, parity)) return true;
   const i64 t0 = clock64();
-  u32 spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3ffu) == 0) {
-      if (ctl->abort) return false;
-      if (clock64() - t0 > AE_WAIT_CYCLES) {
-        ctl->abort = 1;
-        if (g_status) atomicCAS(g_status, 0u, AE_ST_TIMEOUT_BASE + site);
-        return false;
-      }
+    if (ctl->abort) return false;
+    if (clock64() - t0 > AE_WAIT_CYCLES) {
+      ctl->abort = 1;
+      if (g_status) atomicCAS(g_status, 0u, AE_ST_TIMEOUT_BASE + site);
+      return false;
     }
   }
 }

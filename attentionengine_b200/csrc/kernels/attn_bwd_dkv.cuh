@@ -332,9 +332,12 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       ok = ok && mbar_wait(&bars->acc_done, 0, ctl, args.status, 37);
       tc_fence_after_sync();
     }
-    if (row_valid && ok) {
-      u16* dkrow = (u16*)args.dk + (i64)b * args.dk_sb + (i64)kv_idx * args.dk_ss + (i64)hk * args.dk_sh;
-      u16* dvrow = (u16*)args.dv + (i64)b * args.dv_sb + (i64)kv_idx * args.dv_ss + (i64)hk * args.dv_sh;
+    {
+      // tcgen05.ld is warp-collective: every lane runs it; only the stores are per-row
+      const bool store = row_valid && ok;
+      const int kv_s = store ? kv_idx : 0;
+      u16* dkrow = (u16*)args.dk + (i64)b * args.dk_sb + (i64)kv_s * args.dk_ss + (i64)hk * args.dk_sh;
+      u16* dvrow = (u16*)args.dv + (i64)b * args.dv_sb + (i64)kv_s * args.dv_ss + (i64)hk * args.dv_sh;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const int ncol = which ? AE_DV : AE_D;
@@ -348,15 +351,17 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = 0.f;
           }
-          uint4* dst = (uint4*)(drow + c * 32);
+          if (store) {
+            uint4* dst = (uint4*)(drow + c * 32);
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 w;
-            w.x = pack2<AE_BF16>(r[v * 8 + 0], r[v * 8 + 1]);
-            w.y = pack2<AE_BF16>(r[v * 8 + 2], r[v * 8 + 3]);
-            w.z = pack2<AE_BF16>(r[v * 8 + 4], r[v * 8 + 5]);
-            w.w = pack2<AE_BF16>(r[v * 8 + 6], r[v * 8 + 7]);
-            dst[v] = w;
+            for (int v = 0; v < 4; ++v) {
+              uint4 w;
+              w.x = pack2<AE_BF16>(r[v * 8 + 0], r[v * 8 + 1]);
+              w.y = pack2<AE_BF16>(r[v * 8 + 2], r[v * 8 + 3]);
+              w.z = pack2<AE_BF16>(r[v * 8 + 4], r[v * 8 + 5]);
+              w.w = pack2<AE_BF16>(r[v * 8 + 6], r[v * 8 + 7]);
+              dst[v] = w;
+            }
           }
         }
       }

@@ -282,8 +282,10 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       ok = ok && mbar_wait(&bars->dq_done, 0, ctl, args.status, 28);
       tc_fence_after_sync();
     }
-    if (row_valid && ok) {
-      u16* drow = (u16*)args.dq + (i64)b * args.dq_sb + (i64)q_idx * args.dq_ss + (i64)hq * args.dq_sh;
+    {
+      // tcgen05.ld is warp-collective: every lane runs it; only the stores are per-row
+      const bool store = row_valid && ok;
+      u16* drow = (u16*)args.dq + (i64)b * args.dq_sb + (i64)(store ? q_idx : 0) * args.dq_ss + (i64)hq * args.dq_sh;
 #pragma unroll
       for (int c = 0; c < AE_D / 32; ++c) {
         float r[32];
@@ -293,15 +295,17 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0.f;
         }
-        uint4* dst = (uint4*)(drow + c * 32);
+        if (store) {
+          uint4* dst = (uint4*)(drow + c * 32);
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 w;
-          w.x = pack2<AE_BF16>(r[v * 8 + 0], r[v * 8 + 1]);
-          w.y = pack2<AE_BF16>(r[v * 8 + 2], r[v * 8 + 3]);
-          w.z = pack2<AE_BF16>(r[v * 8 + 4], r[v * 8 + 5]);
-          w.w = pack2<AE_BF16>(r[v * 8 + 6], r[v * 8 + 7]);
-          dst[v] = w;
+          for (int v = 0; v < 4; ++v) {
+            uint4 w;
+            w.x = pack2<AE_BF16>(r[v * 8 + 0], r[v * 8 + 1]);
+            w.y = pack2<AE_BF16>(r[v * 8 + 2], r[v * 8 + 3]);
+            w.z = pack2<AE_BF16>(r[v * 8 + 4], r[v * 8 + 5]);
+            w.w = pack2<AE_BF16>(r[v * 8 + 6], r[v * 8 + 7]);
+            dst[v] = w;
+          }
         }
       }
     }

@@ -377,8 +377,10 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       ok = ok && mbar_wait(&bars->o_done[t], (n_done - 1) & 1, ctl, args.status, 11);
       tc_fence_after_sync();
     }
-    if (tile_valid && q_idx < args.Sq && ok) {
-      u16* orow = (u16*)args.o + (i64)b * args.o_sb + (i64)q_idx * args.o_ss + (i64)hq * args.o_sh;
+    // tcgen05.ld is warp-collective: every lane of the warp runs it; only the stores are per-row.
+    if (tile_valid) {
+      const bool store = (q_idx < args.Sq) && ok;
+      u16* orow = (u16*)args.o + (i64)b * args.o_sb + (i64)(store ? q_idx : 0) * args.o_ss + (i64)hq * args.o_sh;
 #pragma unroll
       for (int c = 0; c < AE_DV / 32; ++c) {
         float r[32];
@@ -388,23 +390,27 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0.f;
         }
-        uint4* dst = (uint4*)(orow + c * 32);
+        if (store) {
+          uint4* dst = (uint4*)(orow + c * 32);
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 w;
-          w.x = pack2<AE_BF16>(ae_epilogue_o((r[v * 8 + 0]), st), ae_epilogue_o((r[v * 8 + 1]), st));
-          w.y = pack2<AE_BF16>(ae_epilogue_o((r[v * 8 + 2]), st), ae_epilogue_o((r[v * 8 + 3]), st));
-          w.z = pack2<AE_BF16>(ae_epilogue_o((r[v * 8 + 4]), st), ae_epilogue_o((r[v * 8 + 5]), st));
-          w.w = pack2<AE_BF16>(ae_epilogue_o((r[v * 8 + 6]), st), ae_epilogue_o((r[v * 8 + 7]), st));
-          dst[v] = w;
+          for (int v = 0; v < 4; ++v) {
+            uint4 w;
+            w.x = pack2<AE_BF16>(ae_epilogue_o(r[v * 8 + 0], st), ae_epilogue_o(r[v * 8 + 1], st));
+            w.y = pack2<AE_BF16>(ae_epilogue_o(r[v * 8 + 2], st), ae_epilogue_o(r[v * 8 + 3], st));
+            w.z = pack2<AE_BF16>(ae_epilogue_o(r[v * 8 + 4], st), ae_epilogue_o(r[v * 8 + 5], st));
+            w.w = pack2<AE_BF16>(ae_epilogue_o(r[v * 8 + 6], st), ae_epilogue_o(r[v * 8 + 7], st));
+            dst[v] = w;
+          }
         }
       }
 #if AE_NFINAL > 0
-      float fr[AE_NFINAL];
-      ae_final_rowscales(st, fr);
+      if (store) {
+        float fr[AE_NFINAL];
+        ae_final_rowscales(st, fr);
 #pragma unroll
-      for (int i = 0; i < AE_NFINAL; ++i)
-        args.final_rs[i][((i64)b * args.Hq + hq) * args.Sq + q_idx] = fr[i];
+        for (int i = 0; i < AE_NFINAL; ++i)
+          args.final_rs[i][((i64)b * args.Hq + hq) * args.Sq + q_idx] = fr[i];
+      }
 #endif
     }
   }

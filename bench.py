@@ -1,0 +1,315 @@
+"""Benchmark of the fused attention forward + backward path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (one "step"): causal softmax attention forward + backward at the Llama-3.1-8B GQA shape
+B=8, Hq=32, Hkv=8, S=8192, D=DV=128, fp16, synthetic N(0,1) inputs.  FLOPs follow the reference's
+convention (attention_engine/benchmark/bench_utils.py:1185-1188): forward 4*B*Hq*S^2*D/2, backward
+2.5x that.  With N GPUs every rank runs the whole workload on its own data (independent (batch, head)
+shards, no collective on the data path): weak scaling, value = N * flops / max-over-ranks time.
+
+One JSON line is printed by rank 0.  ``--impl reference`` times the reference's naive PyTorch path
+(restated in oracle/attention_oracle.py) on the host cores on a bounded slice of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+CFG = dict(B=8, Hq=32, Hkv=8, S=8192, D=128)
+METRIC = "attention fwd+bwd throughput, Llama-3.1-8B GQA S=8K causal"
+
+
+def flops_fwd(B, Hq, S, D):
+    return 4.0 * B * Hq * S * S * D / 2
+
+
+def read_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
+
+    def __init__(self, index: int):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                       "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            out, _ = self.p.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+            out, _ = self.p.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_sample(n_slices: int, threads: int):
+    """The naive fp32 PyTorch reference (oracle port) on ``n_slices`` (batch, kv-group) slices of the workload:
+    each slice is 4 q-heads x S=8192 against one kv-head, forward + backward."""
+    import torch
+    from oracle import attention_oracle as orc
+    torch.set_num_threads(threads)
+    S, D, g = CFG["S"], CFG["D"], CFG["Hq"] // CFG["Hkv"]
+    gen = torch.Generator().manual_seed(0)
+    t = 0.0
+    for _ in range(n_slices):
+        q = torch.randn(1, S, g, D, generator=gen).to(torch.float16)
+        k = torch.randn(1, S, 1, D, generator=gen).to(torch.float16)
+        v = torch.randn(1, S, 1, D, generator=gen).to(torch.float16)
+        d_o = torch.randn(1, S, g, D, generator=gen).to(torch.float16)
+        t0 = time.perf_counter()
+        orc.fwd_bwd(lambda a, b, c: orc.softmax_attention(a, b, c, True), (q, k, v), d_o)
+        t += time.perf_counter() - t0
+    fl = 3.5 * flops_fwd(1, g, S, D) * n_slices
+    return fl / t / 1e12, t
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    import torch
+    threads = os.cpu_count() or 1
+    times = []
+    for i in range(args.warmup + args.steps):
+        tf, t = cpu_sample(1, threads)
+        if i >= args.warmup:
+            times.append(t)
+    g = CFG["Hq"] // CFG["Hkv"]
+    fl = 3.5 * flops_fwd(1, g, CFG["S"], CFG["D"])
+    ms = 1e3 * sum(times) / len(times)
+    value = fl / (ms / 1e3) / 1e12
+    sample = "1 of 64 (batch, kv-group) slices per step: 4 q-heads x S=8192 x D=128 vs one kv-head, fwd+bwd, fp32"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "llama3.1-8b-gqa causal softmax attention fwd+bwd, B=8 Hq=32 Hkv=8 S=8192 D=128 fp16",
+                       "sample": sample},
+            "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end pass (profiling runs)")
+    ap.add_argument("--batch", type=int, default=CFG["B"], help="batch size; the benchmark's is 8 (smaller for ncu captures)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import helpers
+    from attentionengine_b200 import runtime as rt
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, Hq, Hkv, S, D = (CFG[k] for k in ("B", "Hq", "Hkv", "S", "D"))
+    B = args.batch
+    dt = torch.float16
+    eng = helpers.softmax_engine(B, Hq, Hkv, S, D, D, dt, True)
+    eng.kernels.bwd  # compile / load before timing
+
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    host = {}
+    for name, shape in (("q", (B, S, Hq, D)), ("k", (B, S, Hkv, D)), ("v", (B, S, Hkv, D)), ("do", (B, S, Hq, D))):
+        t = torch.empty(shape, dtype=dt).pin_memory()
+        # fill in chunks to bound host memory for the fp32 temporaries
+        for b in range(B):
+            t[b].copy_(torch.randn(shape[1:], generator=gen).to(dt))
+        host[name] = t
+    q, k, v, d_o = (host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "do"))
+    q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+    torch.cuda.synchronize()
+
+    def step_resident():
+        q.grad = k.grad = v.grad = None
+        o = eng(q, k, v)
+        o.backward(d_o)
+        return o
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_resident()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_resident()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if sampler else None
+    eng.check_status()
+    tmax = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    ms = float(tmax.item())
+    fl_step = 3.5 * flops_fwd(B, Hq, S, D)
+    value = world * fl_step / (ms / 1e3) / 1e12
+
+    # ---- end to end: host buffers in, host buffers out, through the public operator call ----------
+    out_host = {n: torch.empty_like(host[n]).pin_memory() for n in ("q", "k", "v", "do")}
+
+    def step_e2e():
+        qd = host["q"].to(dev, non_blocking=True).requires_grad_()
+        kd = host["k"].to(dev, non_blocking=True).requires_grad_()
+        vd = host["v"].to(dev, non_blocking=True).requires_grad_()
+        dod = host["do"].to(dev, non_blocking=True)
+        o = eng(qd, kd, vd)
+        o.backward(dod)
+        out_host["do"].copy_(o.detach(), non_blocking=True)
+        out_host["q"].copy_(qd.grad, non_blocking=True)
+        out_host["k"].copy_(kd.grad, non_blocking=True)
+        out_host["v"].copy_(vd.grad, non_blocking=True)
+
+    n_e2e = 0 if args.no_e2e else max(1, min(args.steps, 3))
+    if n_e2e:
+        step_e2e()
+    barrier()
+    e0.record()
+    for _ in range(n_e2e):
+        step_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / max(n_e2e, 1)
+    t2 = torch.tensor([ms_e2e], device=dev)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    ms_e2e = float(t2.item())
+    io_bytes = sum(host[n].numel() * 2 for n in host)
+    e2e = None if not n_e2e else {"value": world * fl_step / (ms_e2e / 1e3) / 1e12, "unit": "TFLOPS",
+                                  "ms_per_step": ms_e2e, "h2d_bytes_per_step": io_bytes,
+                                  "d2h_bytes_per_step": io_bytes}
+
+    # ---- per-kernel times (CUDA events on the launching stream) and the roofline of the longest one -----
+    kernels = {}
+    if rank == 0:
+        o, finals = eng._launch_fwd(q.detach(), k.detach(), v.detach(), ())
+        import ctypes as C
+        from attentionengine_b200.attn_engine import attn_bwd as ab
+
+        def time_call(fn, n=3):
+            fn()
+            torch.cuda.synchronize()
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b_.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b_) / n
+
+        gemm = flops_fwd(B, Hq, S, D) / 2  # one S x S x D contraction over the causal half
+        kernels["ae_attn_fwd"] = {"ms": time_call(lambda: eng._launch_fwd(q.detach(), k.detach(), v.detach(), ())),
+                                  "flops": 2 * gemm}
+        # backward launches one by one
+        L = rt.lib()
+        kern = eng.kernels.bwd
+        p = rt.AttnBwdParams()
+        qd, kd, vd = q.detach(), k.detach(), v.detach()
+        dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+        delta = torch.empty(B, Hq, S, dtype=torch.float32, device=dev)
+        p.q, p.k, p.v, p.o, p.d_o = qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), d_o.data_ptr()
+        p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+        s3 = ab._s3
+        p.q_stride, p.k_stride, p.v_stride, p.o_stride, p.do_stride = s3(qd), s3(kd), s3(vd), s3(o), s3(d_o)
+        p.dq_stride, p.dk_stride, p.dv_stride = s3(dq), s3(dk), s3(dv)
+        p.final_rowscales[0] = finals[0].data_ptr()
+        p.delta = delta.data_ptr()
+        p.B, p.Hq, p.Hkv, p.Sq, p.Skv = B, Hq, Hkv, S, S
+        p.status = eng._get_status(dev).data_ptr()
+        st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        kernels["ae_attn_bwd_prep"] = {"ms": time_call(lambda: rt.check(L.ae_launch_attn_bwd_prep(kern.prep.handle, C.byref(p), st))),
+                                       "flops": 0.0, "bytes": 2.0 * B * S * Hq * D * 2 + B * Hq * S * 4}
+        kernels["ae_attn_bwd_dq"] = {"ms": time_call(lambda: rt.check(L.ae_launch_attn_bwd_dq(kern.dq.handle, C.byref(p), st))),
+                                     "flops": 1 * gemm, "executed_flops": 3 * gemm}
+        kernels["ae_attn_bwd_dkv"] = {"ms": time_call(lambda: rt.check(L.ae_launch_attn_bwd_dkv(kern.dkv.handle, C.byref(p), st))),
+                                      "flops": 4 * gemm, "executed_flops": 4 * gemm}
+        eng.check_status()
+
+    if rank == 0:
+        peaks, which = read_peaks()
+        dom = max((n for n in kernels if kernels[n]["flops"] > 0), key=lambda n: kernels[n]["ms"])
+        ach = kernels[dom]["flops"] / (kernels[dom]["ms"] / 1e3) / 1e12
+        peak = float(peaks.get("bf16_tflops", 1590.0))
+        roofline = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                    "frac": ach / peak, "peak_source": f"{which} cuBLAS bf16 burst", "traffic": None,
+                    "kernels": {n: {"ms": round(d["ms"], 4), "tflops": round(d["flops"] / (d["ms"] / 1e3) / 1e12, 1)}
+                                for n, d in kernels.items()}}
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            tf, t = cpu_sample(2, threads)
+            cpu = {"value": tf, "unit": "TFLOPS", "cores": threads, "kind": "port", "seconds": round(t, 2),
+                   "sample": "2 of 64 (batch, kv-group) slices: 4 q-heads x S=8192 x D=128 vs one kv-head, fwd+bwd, fp32 torch"}
+        line = {"metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": {"workload": f"llama3.1-8b-gqa causal softmax attention fwd+bwd, B={B} Hq=32 Hkv=8 S=8192 D=128 fp16",
+                           "per_gpu_batch": B, "l2": "inputs (1.3 GB per step) larger than L2",
+                           "flops_per_step": fl_step, "frac_of_nominal_fp16_peak": value / world / 2250.0},
+                "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps, "roofline": roofline,
+                "cpu_baseline": cpu}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

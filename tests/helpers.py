@@ -1,0 +1,116 @@
+"""Engine factories shared by the CPU and GPU tests: the reference's example programs
+(attn_script/mha.py, gqa.py, sigmoidattn.py, reluattn.py) written against this package."""
+import math
+
+import torch
+
+from attentionengine_b200 import AttentionEngine, CustomIO, OnlineFunc, SymbolScalar, Var, meta_tensor
+
+
+class OnlineSoftmax(OnlineFunc):
+    """attn_script/mha.py:27-84."""
+
+    def __init__(self):
+        super().__init__({"m": SymbolScalar("m", Var("-inf")), "r": SymbolScalar("r", Var("0.0"))},
+                         {"lse": SymbolScalar("lse", Var("0.0"))}, CustomIO())
+
+    @staticmethod
+    def online_fwd(scores, online_rowscales, b, h, q_idx):
+        m, r = online_rowscales["m"], online_rowscales["r"]
+        m_new = m.max(scores.get_reduce("max"))
+        scale_tmp = (m - m_new).exp()
+        r = r * scale_tmp
+        scores = (scores - m_new).exp()
+        r = r + scores.get_reduce("sum")
+        return scores, {"m": m_new, "r": r}, scale_tmp
+
+    @staticmethod
+    def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+        o_new = o / online_rowscales["r"]
+        lse = (online_rowscales["r"]).log() + online_rowscales["m"]
+        return o_new, {"lse": lse}
+
+    @staticmethod
+    def forward(scores, final_rowscales, b, h, q_idx, kv_idx):
+        return (scores - final_rowscales["lse"]).exp()
+
+    @staticmethod
+    def backward(dp, scores, final_rowscales, doosum_rowscales, b, h, q_idx, kv_idx):
+        return (dp - doosum_rowscales) * scores
+
+
+class OnlineIdentity(OnlineFunc):
+    """attn_script/sigmoidattn.py:24-49, reluattn.py:21-46."""
+
+    def __init__(self):
+        super().__init__({}, {}, CustomIO())
+
+    @staticmethod
+    def online_fwd(scores, online_rowscales, b, h, q_idx):
+        return scores, online_rowscales, SymbolScalar("o_scale", Var("1"))
+
+    @staticmethod
+    def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+        return o, {}
+
+    @staticmethod
+    def forward(scores, final_rowscales, b, h, q_idx, kv_idx):
+        return scores
+
+    @staticmethod
+    def backward(dp, scores, final_rowscales, doosum_rowscales, b, h, q_idx, kv_idx):
+        return dp
+
+
+def causal_mask(b, h, q_idx, kv_idx):
+    return q_idx >= kv_idx
+
+
+def metas(B, Hq, Hkv, S, D, DV, dtype):
+    return (meta_tensor(B, Hq, S, D, dtype=dtype), meta_tensor(B, Hkv, S, D, dtype=dtype),
+            meta_tensor(B, Hkv, S, DV, dtype=dtype))
+
+
+def softmax_engine(B, Hq, Hkv, S, D, DV, dtype, causal, scale=None, **kw):
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+
+    def score_mod(score, custom_fwd_inputs, b, h, q_idx, kv_idx):
+        return score * scale
+
+    return AttentionEngine(metas(B, Hq, Hkv, S, D, DV, dtype), CustomIO({}), score_mod=score_mod,
+                           mask_mod=causal_mask if causal else None, online_func=OnlineSoftmax(), **kw)
+
+
+def sigmoid_engine(B, H, S, D, dtype, causal, scale=None):
+    """P = sigmoid(score * scale + bias) in the reference's tanh form (attn_script/sigmoidattn.py:14-18);
+    bias arrives as the custom input ``softmax_bias`` of shape (1,)."""
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+
+    def score_mod(score, custom_fwd_inputs, b, h, q_idx, kv_idx):
+        softmax_bias = custom_fwd_inputs.input_tensors["softmax_bias"]
+        score = score * scale + softmax_bias
+        return ((score * 0.5).tanh() + 1) * 0.5
+
+    return AttentionEngine(metas(B, H, H, S, D, D, dtype), CustomIO({"softmax_bias": (1,)}), score_mod=score_mod,
+                           mask_mod=causal_mask if causal else None, online_func=OnlineIdentity())
+
+
+def relu_engine(B, H, S, D, dtype, causal=False, scale=None, post_scale=1.0):
+    """P = relu(score * scale) * post_scale (attn_script/reluattn.py:14-17)."""
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+
+    def score_mod(score, custom_fwd_inputs, b, h, q_idx, kv_idx):
+        score = (score * scale).max(0)
+        return score * post_scale if post_scale != 1.0 else score
+
+    return AttentionEngine(metas(B, H, H, S, D, D, dtype), CustomIO({}), score_mod=score_mod,
+                           mask_mod=causal_mask if causal else None, online_func=OnlineIdentity())
+
+
+def seeded_qkv(B, Hq, Hkv, S, D, DV, dtype, seed=0, device="cpu"):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, S, Hq, D, generator=g).to(dtype)
+    k = torch.randn(B, S, Hkv, D, generator=g).to(dtype)
+    v = torch.randn(B, S, Hkv, DV, generator=g).to(dtype)
+    d_o = torch.randn(B, S, Hq, DV, generator=g).to(dtype)
+    return [t.to(device) for t in (q, k, v, d_o)]

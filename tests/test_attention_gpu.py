@@ -1,0 +1,208 @@
+"""Parity of the CUDA attention path (through AttentionEngine -> C ABI -> sm_100a kernels) against the
+CPU oracle and the golden vectors.  Tolerance (stated by the benchmark spec): max-abs <= 2e-2 and
+rel-L2 <= 1e-3 for fp16 outputs and gradients.  For bf16 the oracle is rounded to bf16 first, because
+bf16 output rounding alone is a rel-L2 of about 1.7e-3, and rel-L2 <= 4e-3 is asked of the difference."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, REL_L2 = 2e-2, 1e-3
+
+
+def _check(name, got, ref, dtype):
+    if dtype == torch.bfloat16:
+        mx, rel = orc.error_stats(got, ref.to(torch.bfloat16))
+        assert mx <= 4 * MAX_ABS and rel <= 4e-3, f"{name}: max-abs {mx:.3e}, rel-L2 {rel:.3e} (bf16 protocol)"
+    else:
+        mx, rel = orc.error_stats(got, ref)
+        assert mx <= MAX_ABS and rel <= REL_L2, f"{name}: max-abs {mx:.3e}, rel-L2 {rel:.3e}"
+
+
+def _run(eng, q, k, v, d_o, custom=()):
+    qd, kd, vd = (t.cuda().requires_grad_() for t in (q, k, v))
+    o = eng(qd, kd, vd, *[c.cuda() for c in custom])
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    return o.detach().cpu(), qd.grad.cpu(), kd.grad.cpu(), vd.grad.cpu()
+
+
+@pytest.mark.parametrize("case", ["cfg1", "gqa_causal", "gqa_full", "mha_d128"])
+def test_softmax_against_reference_golden(golden_dir, case):
+    """Config 1 of the benchmark (B=1, H=4, S=512, D=64, causal, dO = ones) and three small variants,
+    against outputs of the reference's own naive attention."""
+    z = np.load(os.path.join(golden_dir, "softmax.npz"))
+    q, k, v, d_o = (torch.from_numpy(z[f"{case}.{n}"]) for n in ("q", "k", "v", "do"))
+    causal = bool(z[f"{case}.causal"])
+    B, S, Hq, D = q.shape
+    eng = helpers.softmax_engine(B, Hq, k.shape[2], S, D, D, torch.float16, causal)
+    got = _run(eng, q, k, v, d_o)
+    for name, g in zip(("o", "dq", "dk", "dv"), got):
+        _check(f"{case}.{name}", g, torch.from_numpy(z[f"{case}.{name}"]), torch.float16)
+
+
+SHAPES = [
+    # B, Hq, Hkv, S, D, causal, dtype
+    (2, 8, 2, 1024, 128, True, torch.float16),
+    (1, 4, 4, 512, 128, False, torch.bfloat16),
+    (1, 2, 2, 384, 64, True, torch.float16),
+    (1, 2, 2, 300, 64, True, torch.float16),      # ragged: last tile partly out of range
+    (1, 2, 1, 200, 128, False, torch.float16),    # ragged, non-causal, GQA
+    (1, 1, 1, 64, 64, True, torch.float16),       # shorter than one tile
+    (2, 4, 2, 129, 128, True, torch.bfloat16),    # one row past a tile
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,D,causal,dtype", SHAPES)
+def test_softmax_shapes_against_oracle(B, Hq, Hkv, S, D, causal, dtype):
+    q, k, v, d_o = helpers.seeded_qkv(B, Hq, Hkv, S, D, D, dtype, seed=S)
+    eng = helpers.softmax_engine(B, Hq, Hkv, S, D, D, dtype, causal)
+    got = _run(eng, q, k, v, d_o)
+    o, (dq, dk, dv) = orc.fwd_bwd(lambda a, b, c: orc.softmax_attention(a, b, c, causal), (q, k, v), d_o)
+    for name, g, r in zip(("o", "dq", "dk", "dv"), got, (o, dq, dk, dv)):
+        _check(name, g, r, dtype)
+
+
+def test_lse_is_saved_like_the_reference():
+    """final_rowscales['lse'] is the natural-log LSE of the scaled scores, [B, H, S] fp32 (lower.py:385-392)."""
+    B, Hq, Hkv, S, D = 1, 4, 2, 256, 64
+    q, k, v, _ = helpers.seeded_qkv(B, Hq, Hkv, S, D, D, torch.float16, seed=5)
+    eng = helpers.softmax_engine(B, Hq, Hkv, S, D, D, torch.float16, True)
+    o, finals = eng._launch_fwd(q.cuda(), k.cuda(), v.cuda(), ())
+    torch.cuda.synchronize()
+    _, lse = orc.softmax_attention(q, k, v, True, return_lse=True)
+    assert finals[0].shape == (B, Hq, S) and finals[0].dtype == torch.float32
+    torch.testing.assert_close(finals[0].cpu(), lse, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_sigmoid_attention(causal):
+    B, H, S, D, dtype = 1, 4, 512, 128, torch.bfloat16
+    q, k, v, d_o = helpers.seeded_qkv(B, H, H, S, D, D, dtype, seed=11)
+    bias = torch.tensor([-math.log(S)], dtype=torch.float32)
+    eng = helpers.sigmoid_engine(B, H, S, D, dtype, causal)
+    got = _run(eng, q, k, v, d_o, custom=(bias,))
+    o, (dq, dk, dv) = orc.fwd_bwd(lambda a, b, c: orc.sigmoid_attention(a, b, c, bias=float(bias), causal=causal),
+                                  (q, k, v), d_o)
+    for name, g, r in zip(("o", "dq", "dk", "dv"), got, (o, dq, dk, dv)):
+        _check(name, g, r, dtype)
+
+
+def test_relu_attention_against_reference_golden(golden_dir):
+    z = np.load(os.path.join(golden_dir, "relu.npz"))
+    q, k, v, d_o = (torch.from_numpy(z[n]) for n in ("q", "k", "v", "do"))
+    B, S, H, D = q.shape
+    eng = helpers.relu_engine(B, H, S, D, torch.float16)
+    got = _run(eng, q, k, v, d_o)
+    for name, g in zip(("o", "dq", "dk", "dv"), got):
+        ref = torch.from_numpy(z[name])
+        mx, rel = orc.error_stats(g, ref)
+        # un-normalised relu attention has outputs of magnitude ~S/2: the absolute bound scales with it
+        assert rel <= REL_L2 and mx <= MAX_ABS * max(1.0, ref.abs().max().item()), f"{name}: {mx:.3e} {rel:.3e}"
+
+
+def test_relu_attention_benchmark_form():
+    """P = relu(S / sqrt(D)) / S_len, non-causal, bf16 (config 3 of the benchmark, small)."""
+    B, H, S, D, dtype = 1, 2, 512, 128, torch.bfloat16
+    q, k, v, d_o = helpers.seeded_qkv(B, H, H, S, D, D, dtype, seed=12)
+    eng = helpers.relu_engine(B, H, S, D, dtype, post_scale=1.0 / S)
+    got = _run(eng, q, k, v, d_o)
+    o, (dq, dk, dv) = orc.fwd_bwd(lambda a, b, c: orc.relu_attention(a, b, c, post_scale=1.0 / S), (q, k, v), d_o)
+    for name, g, r in zip(("o", "dq", "dk", "dv"), got, (o, dq, dk, dv)):
+        _check(name, g, r, dtype)
+
+
+def test_sliding_window_block_sparse():
+    """mask_mod that is not causal-shaped: block lists skip empty tiles, partial tiles are masked per element."""
+    B, H, S, D, dtype = 1, 2, 1024, 64, torch.float16
+    W = 200
+
+    def window(b, h, q_idx, kv_idx):
+        return torch.logical_and(q_idx >= kv_idx, q_idx - kv_idx <= W)
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return score * (1 / math.sqrt(D))
+
+    from attentionengine_b200 import AttentionEngine, CustomIO
+    eng = AttentionEngine(helpers.metas(B, H, H, S, D, D, dtype), CustomIO({}), score_mod=score_mod, mask_mod=window,
+                          online_func=helpers.OnlineSoftmax())
+    assert eng.mask_mode == 2
+    q, k, v, d_o = helpers.seeded_qkv(B, H, H, S, D, D, dtype, seed=13)
+    got = _run(eng, q, k, v, d_o)
+
+    def ref(a, b, c):
+        s = torch.einsum("bqhd,bkhd->bhqk", a, b) / math.sqrt(D)
+        i = torch.arange(S)
+        keep = (i.view(-1, 1) >= i.view(1, -1)) & (i.view(-1, 1) - i.view(1, -1) <= W)
+        s = s.masked_fill(~keep, float("-inf"))
+        return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), c)
+
+    o, (dq, dk, dv) = orc.fwd_bwd(ref, (q, k, v), d_o)
+    for name, g, r in zip(("o", "dq", "dk", "dv"), got, (o, dq, dk, dv)):
+        _check(name, g, r, dtype)
+
+
+def test_run_to_run_determinism():
+    """No atomics anywhere on the path: two runs give bit-identical outputs and gradients."""
+    B, Hq, Hkv, S, D = 1, 4, 2, 512, 128
+    q, k, v, d_o = helpers.seeded_qkv(B, Hq, Hkv, S, D, D, torch.float16, seed=21)
+    eng = helpers.softmax_engine(B, Hq, Hkv, S, D, D, torch.float16, True)
+    a = _run(eng, q, k, v, d_o)
+    b = _run(eng, q, k, v, d_o)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def test_probe_gemms():
+    """The two tcgen05 operand paths the kernels rely on, in isolation."""
+    import ctypes as C
+    from attentionengine_b200 import runtime as rt
+    for bf16, dt in ((0, torch.float16), (1, torch.bfloat16)):
+        cfg = rt.KernelConfig(kind=rt.KIND_PROBE, dtype=bf16, head_dim=128, head_dim_v=128, threads=160,
+                              smem_bytes=65536 + 256 + 1024, stages=1, mask_mode=0)
+        m = rt.compile_module(rt.kernel_source("probe.cuh", prelude=f"#define AE_BF16 {bf16}\n"), "ae_probe", cfg)
+        g = torch.Generator().manual_seed(1)
+        a, b, p = (torch.randn(128, 128, generator=g).to(dt).cuda() for _ in range(3))
+        for mode in (0, 1):
+            d = torch.zeros(128, 128, device="cuda")
+            st = torch.zeros(1, dtype=torch.int32, device="cuda")
+            rt.check(rt.lib().ae_launch_probe(m.handle, a.data_ptr(), b.data_ptr(), p.data_ptr(), d.data_ptr(), mode,
+                                              st.data_ptr(), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            torch.cuda.synchronize()
+            assert st.item() == 0
+            ref = a.float() @ b.float().T if mode == 0 else p.float() @ b.float()
+            torch.testing.assert_close(d, ref, rtol=1e-4, atol=1e-3)
+
+
+def test_full_size_properties():
+    """At the benchmark's full shape the oracle is too slow; check size-independent properties instead:
+    rows of P sum to one (O of constant V is that constant), linearity in V and dO, and agreement of a
+    (batch, kv-group) slice with the oracle."""
+    B, Hq, Hkv, S, D = 2, 8, 2, 8192, 128
+    dt = torch.float16
+    eng = helpers.softmax_engine(B, Hq, Hkv, S, D, D, dt, True)
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(B, S, Hq, D, generator=g).to(dt).cuda()
+    k = torch.randn(B, S, Hkv, D, generator=g).to(dt).cuda()
+    v1 = torch.randn(B, S, Hkv, D, generator=g).to(dt).cuda()
+    ones = torch.ones_like(v1)
+    o_ones, _ = eng._launch_fwd(q, k, ones, ())
+    torch.testing.assert_close(o_ones.float(), torch.ones_like(o_ones).float(), rtol=2e-3, atol=2e-3)
+    o1, _ = eng._launch_fwd(q, k, v1, ())
+    o2, _ = eng._launch_fwd(q, k, (2 * v1), ())
+    torch.testing.assert_close(o2.float(), 2 * o1.float(), rtol=2e-3, atol=2e-3)
+    # one slice against the oracle (batch 1, kv head 1 -> q heads 4..7), first 1024 rows are self-contained
+    sl = slice(0, 1024)
+    qs, ks, vs = q[1:2, sl, 4:8].cpu(), k[1:2, sl, 1:2].cpu(), v1[1:2, sl, 1:2].cpu()
+    ref = orc.softmax_attention(qs, ks, vs, True)
+    _check("slice.o", o1[1:2, sl, 4:8].cpu(), ref, dt)
+    eng.check_status()

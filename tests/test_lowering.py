@@ -1,0 +1,88 @@
+"""Host-side logic: tracing, mask classification, lowering to CUDA functors, NVRTC compile (no GPU)."""
+import math
+
+import pytest
+import torch
+
+import attentionengine_b200 as ae
+from attentionengine_b200 import AttentionEngine, CustomIO, meta_tensor
+from attentionengine_b200.lower.cuda_lower import lower_attention
+
+import helpers
+
+
+def test_softmax_lowering_has_expected_pieces():
+    eng = helpers.softmax_engine(1, 4, 4, 512, 64, 64, torch.float16, True)
+    low = eng.lowered
+    assert eng.mask_mode == 1 and low.final_names == ["lse"] and low.uses_doosum and not low.o_scale_one
+    for piece in ("struct AeRow", "ae_score_mod", "ae_online_fwd", "ae_epilogue_o", "ae_final_rowscales",
+                  "ae_bwd_forward", "ae_bwd_backward", "ae_score_mod_bwd", "st_m = -1e38f"):
+        assert piece in low.prelude_bwd
+    assert "(q_idx >= kv_idx)" in low.prelude_fwd
+    assert eng.tl_code.count("tcgen05.mma") >= 2 and "cp.async.bulk.tensor" in eng.tl_code
+
+
+def test_identity_online_func_needs_no_rescale_and_no_delta():
+    eng = helpers.relu_engine(1, 2, 256, 64, torch.float16)
+    assert eng.lowered.o_scale_one and not eng.lowered.uses_doosum and eng.lowered.final_names == []
+    assert eng.mask_mode == 0
+
+
+def test_custom_input_binding():
+    eng = helpers.sigmoid_engine(1, 2, 256, 128, torch.bfloat16, True)
+    (spec,) = eng.lowered.custom
+    assert spec.name == "softmax_bias" and not spec.is_16bit and spec.dim_slots == [-1]
+    assert "((const float*)cu.p[0])[0]" in eng.lowered.prelude_fwd
+    assert "ae_tanh" in eng.lowered.prelude_fwd
+
+
+def test_mask_classification():
+    D = 64
+
+    def sm(score, c, b, h, q, kv):
+        return score * 0.125
+
+    def mk(mask, **kw):
+        return AttentionEngine(helpers.metas(1, 2, 2, 512, D, D, torch.float16), CustomIO({}), score_mod=sm,
+                               mask_mod=mask, online_func=helpers.OnlineSoftmax(), **kw)
+
+    assert mk(None).mask_mode == 0
+    assert mk(lambda b, h, q, kv: q >= kv).mask_mode == 1
+    assert mk(lambda b, h, q, kv: q >= kv + 128).mask_mode == 2
+    assert mk(lambda b, h, q, kv: q >= kv, infer_mask=False).mask_mode == 3
+    always = mk(lambda b, h, q, kv: q + kv >= 0)
+    assert always.mask_mode == 0
+    e = mk(lambda b, h, q, kv: torch.logical_and(q >= kv, q - kv <= 100))
+    assert e.mask_mode == 2 and e.block_mask.shape == (1, 2, 4, 4)
+    assert "&&" in e.lowered.prelude_fwd
+
+
+def test_block_lists_layout():
+    from attentionengine_b200.attn_engine.attn_engine import _block_lists
+    cnt = torch.tensor([[[[128 * 128, 0, 5], [0, 0, 0], [1, 128 * 128, 128 * 128]]]], dtype=torch.int32)
+    c, i, ct, it = _block_lists(cnt, 128, 128, 384, 384, 1, 1, "cpu")
+    assert c.tolist() == [[[2, 0, 3]]]
+    assert (i[0, 0, 0, :2] & 0x3fffffff).tolist() == [0, 2] and (i[0, 0, 0, :2] >> 30).tolist() == [0, 1]
+    assert (i[0, 0, 2, :3] >> 30).tolist() == [1, 0, 0]
+    assert ct.tolist() == [[[2, 1, 2]]] and (it[0, 0, 2, :2] & 0x3fffffff).tolist() == [0, 2]
+
+
+def test_unsupported_requests_fail_loudly():
+    with pytest.raises(NotImplementedError):
+        helpers.softmax_engine(1, 2, 2, 256, 256, 256, torch.float16, True)  # head dim > 128
+    with pytest.raises(NotImplementedError):
+        AttentionEngine(helpers.metas(1, 2, 2, 256, 64, 64, torch.float32), CustomIO({}),
+                        score_mod=lambda s, c, b, h, q, kv: s, mask_mod=None, online_func=helpers.OnlineSoftmax())
+    eng = helpers.softmax_engine(1, 2, 2, 256, 64, 64, torch.float16, True)
+    q = torch.zeros(1, 256, 2, 64, dtype=torch.float16)
+    with pytest.raises(Exception) as e:
+        eng(q, q, q)
+    assert "CUDA" in str(e.value)  # no CPU path
+
+
+def test_reference_import_names():
+    ae.install_reference_aliases()
+    from attn_engine import AttentionEngine as A2, OnlineFunc as O2  # noqa: F401
+    from core import CustomIO as C2, SymbolicArray, SymbolScalar, SymbolicTensor, Var, create_block_mask  # noqa: F401
+    from core.utils import meta_tensor as m2
+    assert A2 is AttentionEngine and m2 is meta_tensor
