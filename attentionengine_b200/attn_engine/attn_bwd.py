@@ -39,13 +39,13 @@ def compile_bwd(k) -> BwdKernels:
                           smem_bytes=0, stages=0, mask_mode=k.mask_mode)
     prep = rt.compile_module(rt.kernel_source("attn_bwd_prep.cuh", prelude=prelude), "ae_attn_bwd_prep", cfg)
     smem_dq = 128 * (D + DV) * 2 + stages * bn * (D + DV) * 2 + 512 + 1024
-    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DQ, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=192,
+    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DQ, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
                           smem_bytes=smem_dq, stages=stages, mask_mode=k.mask_mode)
     cfg.reserved[0] = bn
     dq = rt.compile_module(rt.kernel_source("attn_bwd_dq.cuh", prelude=prelude), "ae_attn_bwd_dq", cfg)
     ncs = len(low.final_names) + 1
     smem_kv = 128 * (D + DV) * 2 + stages * bn * (D + DV) * 2 + 2 * bn * ncs * 4 + 16 + 512 + 1024
-    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DKV, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=192,
+    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DKV, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
                           smem_bytes=smem_kv, stages=stages, mask_mode=k.mask_mode)
     cfg.reserved[0] = bn
     dkv = rt.compile_module(rt.kernel_source("attn_bwd_dkv.cuh", prelude=prelude), "ae_attn_bwd_dkv", cfg)

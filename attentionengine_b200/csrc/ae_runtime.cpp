@@ -269,6 +269,7 @@ int ae_compile(const char* cuda_src, const char* kernel_name, const char* arch, 
   o.push_back(std::string("--gpu-architecture=") + (arch ? arch : "sm_100a"));
   o.push_back("--std=c++17");
   o.push_back("-lineinfo");
+  o.push_back("-default-device");  // generic lambdas inside kernels are device code
   for (int i = 0; i < nopts; ++i) o.push_back(opts[i]);
   std::vector<const char*> oc;
   for (auto& s : o) oc.push_back(s.c_str());

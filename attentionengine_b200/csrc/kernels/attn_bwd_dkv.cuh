@@ -11,7 +11,9 @@
 //                as 16-bit pairs over S^T and dP^T
 //   dV += P^T dO   (TS MMA, dO tile read MN-major)     dK += dS^T Q  (TS MMA, Q tile read MN-major)
 // TMEM columns: dK | dV | AE_BWD_NBUF x (S^T | dP^T).
-// Roles: warps 0-3 row threads (thread = kv row = TMEM lane), warp 4 TMA producer, warp 5 MMA issuer.
+// Roles: warps 0-3 and 4-7 row threads (thread = kv row = TMEM lane; the two groups take alternate
+// 32-column chunks of every tile), warp 8 TMA producer, warp 9 MMA issuer.  The 16-bit pairs of a chunk
+// are written over the first 16 columns of that chunk, so a group only overwrites what it has read.
 
 #define AE_KV_BM 128
 #define AE_NSUBQ (128 / AE_BWD_BN)
@@ -46,12 +48,12 @@ struct AeDkvStep {
   bool partial; // needs the element-wise mask
 };
 
-extern "C" __global__ void __launch_bounds__(192, 1)
+extern "C" __global__ void __launch_bounds__(320, 1)
 ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
   extern __shared__ u8 smem_raw[];
   u8* smem = smem_align1024(smem_raw);
   AeDkvBars* bars = (AeDkvBars*)(smem + AE_KV_SMEM_BAR);
-  float* cs = (float*)(smem + AE_KV_SMEM_CS);  // [2][AE_BWD_BN][AE_NCS]: final rowscales..., delta per q column
+  float* cs = (float*)(smem + AE_KV_SMEM_CS);  // [2][AE_NCS][AE_BWD_BN]: final rowscales..., delta, per q column
   AeCtaCtl* ctl = &bars->ctl;
   const u32 warp = threadIdx.x >> 5;
   const u32 lane = threadIdx.x & 31;
@@ -128,11 +130,11 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
     }
     for (int i = 0; i < AE_BWD_NBUF; ++i) {
       mbar_init(&bars->sp_full[i], 1);
-      mbar_init(&bars->pds_full[i], 128);
+      mbar_init(&bars->pds_full[i], 256);
     }
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&ctl->tmem_base, 512);
     tmem_relinquish();
   }
@@ -142,7 +144,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
   const u32 tmem = ctl->tmem_base;
   const u32 TM_DK = 0, TM_DV = AE_D, TM_BUF = AE_D + AE_DV;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // =============================== TMA producer ===============================
     if (lane == 0) {
       tma_prefetch_desc(&args.tm_q);
@@ -171,7 +173,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         ++s;
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // =============================== MMA issuer =================================
     if (lane == 0) {
       const u32 idesc_s = umma_idesc_f16(AE_KV_BM, AE_BWD_BN, AE_BF16, 0, 0);
@@ -230,12 +232,12 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         const u32 da = do_addr + stage * AE_KV_DO_BYTES;
 #pragma unroll
         for (int kk = 0; kk < AE_BWD_BN / 16; ++kk) {
-          umma_ts(tmem + TM_DV, tm_p + kk * 8, umma_smem_desc_sw128(da + kk * 2048, AE_BWD_BN * 128, 1024), idesc_dv,
+          umma_ts(tmem + TM_DV, tm_p + (kk >> 1) * 32 + (kk & 1) * 8, umma_smem_desc_sw128(da + kk * 2048, AE_BWD_BN * 128, 1024), idesc_dv,
                   (s > 0) | (kk > 0));
         }
 #pragma unroll
         for (int kk = 0; kk < AE_BWD_BN / 16; ++kk) {
-          umma_ts(tmem + TM_DK, tm_ds + kk * 8, umma_smem_desc_sw128(qa + kk * 2048, AE_BWD_BN * 128, 1024), idesc_dk,
+          umma_ts(tmem + TM_DK, tm_ds + (kk >> 1) * 32 + (kk & 1) * 8, umma_smem_desc_sw128(qa + kk * 2048, AE_BWD_BN * 128, 1024), idesc_dk,
                   (s > 0) | (kk > 0));
         }
         umma_commit(&bars->qdo_empty[stage]);
@@ -245,6 +247,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
     }
   } else {
     // =============================== row threads ================================
+    const int wg = warp >> 2;  // the two row warpgroups split every tile by 32-column chunks
     const u32 row = threadIdx.x & 127;
     const u32 lane_base = ((warp & 3) * 32) << 16;
     const int kv_idx = kv0 + (int)row;
@@ -267,59 +270,71 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       const u32 tm_dp = tm_s + AE_BWD_BN;
       float* csb = cs + (s & 1) * (AE_BWD_BN * AE_NCS);
       // stage the per-column row scales of this q tile
-      if (row < AE_BWD_BN) {
+      if (threadIdx.x < AE_BWD_BN) {
         const int q = st.q0 + (int)row;
         const i64 off = ((i64)b * args.Hq + st.hq) * args.Sq + (q < args.Sq ? q : args.Sq - 1);
 #pragma unroll
-        for (int i = 0; i < AE_NFINAL; ++i) csb[row * AE_NCS + i] = args.final_rs[i][off];
+        for (int i = 0; i < AE_NFINAL; ++i) csb[i * AE_BWD_BN + row] = args.final_rs[i][off];
 #if AE_USES_DOOSUM
-        csb[row * AE_NCS + AE_NFINAL] = args.delta[off];
+        csb[AE_NFINAL * AE_BWD_BN + row] = args.delta[off];
 #else
-        csb[row * AE_NCS + AE_NFINAL] = 0.f;
+        csb[AE_NFINAL * AE_BWD_BN + row] = 0.f;
 #endif
       }
-      named_bar_sync(1, 128);
+      named_bar_sync(1, 256);
       ok = ok && mbar_wait(&bars->sp_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 36);
       tc_fence_after_sync();
-      const bool tail = st.q0 + AE_BWD_BN > args.Sq;
-#pragma unroll
-      for (int c = 0; c < AE_BWD_BN / 32; ++c) {
+      const bool tail = (st.q0 + AE_BWD_BN > args.Sq) || (kv0 + AE_KV_BM > args.Skv);
+      auto chunk = [&](auto masked_tag, int c) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
         float sv[32], dp[32];
-        tmem_ld_f32x32(tm_s + c * 32, sv);
-        tmem_ld_f32x32(tm_dp + c * 32, dp);
+        tmem_ld_2xf32x32(tm_s + c * 32, tm_dp + c * 32, sv, dp);
         u32 pk[16], dk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p2[2], ds2[2];
+        for (int i = 0; i < 32; i += 4) {
+          // per-column row scales of four q columns: one 128-bit broadcast load per scale
+          float4 cv[AE_NCS];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
+          for (int j = 0; j < AE_NCS; ++j) cv[j] = *(const float4*)(csb + j * AE_BWD_BN + c * 32 + i);
+          float p4[4], ds4[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
             const int col = c * 32 + i + e;
             const int q_idx = st.q0 + col;
-            const float* fr = csb + col * AE_NCS;
-            bool keep = row_valid;
-            if (tail) keep = keep && q_idx < args.Sq;
-#if AE_MASK_MODE != 0
-            if (st.partial) keep = keep && ae_mask(b, st.hq, q_idx, kv_idx);
-#endif
+            float fr[AE_NCS];
+#pragma unroll
+            for (int j = 0; j < AE_NCS; ++j) fr[j] = e == 0 ? cv[j].x : (e == 1 ? cv[j].y : (e == 2 ? cv[j].z : cv[j].w));
             const float sraw = sv[i + e];
-            const float t = ae_score_mod(sraw, b, st.hq, q_idx, kv_idx, cu);
-            float p = ae_bwd_forward(t, fr, b, st.hq, q_idx, kv_idx, cu);
+            float p = ae_bwd_p(sraw, fr, b, st.hq, q_idx, kv_idx, cu);
             float dpv = dp[i + e];
-            if (!keep) {
-              p = 0.f;
-              dpv = 0.f;
+            bool keep = true;
+            if (kMasked) {
+              keep = row_valid && q_idx < args.Sq;
+#if AE_MASK_MODE != 0
+              if (st.partial) keep = keep && ae_mask(b, st.hq, q_idx, kv_idx);
+#endif
+              if (!keep) {
+                p = 0.f;
+                dpv = 0.f;
+              }
             }
-            const float dT = ae_bwd_backward(dpv, p, fr, fr[AE_NFINAL], b, st.hq, q_idx, kv_idx, cu);
-            float dsv = ae_score_mod_bwd(sraw, dT, b, st.hq, q_idx, kv_idx, cu);
-            if (!keep) dsv = 0.f;
-            p2[e] = p;
-            ds2[e] = dsv;
+            float dsv = ae_bwd_ds(sraw, dpv, p, fr, fr[AE_NFINAL], b, st.hq, q_idx, kv_idx, cu);
+            if (kMasked && !keep) dsv = 0.f;
+            p4[e] = p;
+            ds4[e] = dsv;
           }
-          pk[i >> 1] = pack2<AE_BF16>(p2[0], p2[1]);
-          dk[i >> 1] = pack2<AE_BF16>(ds2[0], ds2[1]);
+          pk[(i >> 1) + 0] = pack2<AE_BF16>(p4[0], p4[1]);
+          pk[(i >> 1) + 1] = pack2<AE_BF16>(p4[2], p4[3]);
+          dk[(i >> 1) + 0] = pack2<AE_BF16>(ds4[0], ds4[1]);
+          dk[(i >> 1) + 1] = pack2<AE_BF16>(ds4[2], ds4[3]);
         }
-        tmem_st16(tm_s + c * 16, pk);
-        tmem_st16(tm_dp + c * 16, dk);
+        tmem_st16(tm_s + c * 32, pk);  // pairs go over this chunk's own first 16 columns
+        tmem_st16(tm_dp + c * 32, dk);
+      };
+      if (st.partial || tail) {
+        for (int c = wg; c < AE_BWD_BN / 32; c += 2) chunk(AeTrue{}, c);
+      } else {
+        for (int c = wg; c < AE_BWD_BN / 32; c += 2) chunk(AeFalse{}, c);
       }
       tc_wait_st();
       tc_fence_before_sync();
@@ -338,8 +353,8 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       const int kv_s = store ? kv_idx : 0;
       u16* dkrow = (u16*)args.dk + (i64)b * args.dk_sb + (i64)kv_s * args.dk_ss + (i64)hk * args.dk_sh;
       u16* dvrow = (u16*)args.dv + (i64)b * args.dv_sb + (i64)kv_s * args.dv_ss + (i64)hk * args.dv_sh;
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = wg;  // group 0 stores dK, group 1 stores dV
         const int ncol = which ? AE_DV : AE_D;
         u16* drow = which ? dvrow : dkrow;
         const u32 tm = tmem + (which ? TM_DV : TM_DK) + lane_base;
@@ -370,7 +385,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);
   }

@@ -14,10 +14,12 @@
 //   dQ += dS K    (TS MMA, K tile read MN-major)
 // TMEM columns: AE_BWD_NBUF x (S | dP) then dQ.  With two buffers the tensor pipe computes the
 // next tile's S / dP while the row threads work on the current one.
-// Roles: warps 0-3 row threads (thread = q row = TMEM lane), warp 4 TMA producer, warp 5 MMA issuer.
+// Roles: warps 0-3 and 4-7 row threads (thread = q row = TMEM lane; the two groups take alternate
+// 32-column chunks of every tile), warp 8 TMA producer, warp 9 MMA issuer.  The 16-bit dS pairs of a
+// chunk are written over the first 16 columns of that chunk, so a group only overwrites what it has read.
 
 #define AE_BM 128
-#define AE_NTHREADS_BWD 192
+#define AE_NTHREADS_BWD 320
 #define AE_NSUB (128 / AE_BWD_BN)
 
 #define AE_DQ_Q_BYTES (AE_BM * AE_D * 2)
@@ -100,11 +102,11 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
     }
     for (int i = 0; i < AE_BWD_NBUF; ++i) {
       mbar_init(&bars->sp_full[i], 1);
-      mbar_init(&bars->ds_full[i], 128);
+      mbar_init(&bars->ds_full[i], 256);
     }
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&ctl->tmem_base, 512);
     tmem_relinquish();
   }
@@ -114,7 +116,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
   const u32 tmem = ctl->tmem_base;
   const u32 TM_DQ = AE_BWD_NBUF * 2 * AE_BWD_BN;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // =============================== TMA producer ===============================
     if (lane == 0 && n_steps > 0) {
       tma_prefetch_desc(&args.tm_q);
@@ -144,7 +146,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
                       &bars->v_full[stage], dh * 64, hk, kv0, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // =============================== MMA issuer =================================
     if (lane == 0 && n_steps > 0) {
       const u32 idesc_s = umma_idesc_f16(AE_BM, AE_BWD_BN, AE_BF16, 0, 0);
@@ -195,7 +197,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
         const u32 ka = k_addr + stage * AE_DQ_K_BYTES;
 #pragma unroll
         for (int kk = 0; kk < AE_BWD_BN / 16; ++kk) {
-          umma_ts(tmem + TM_DQ, tm_ds + kk * 8, umma_smem_desc_sw128(ka + kk * 2048, AE_BWD_BN * 128, 1024), idesc_dq,
+          umma_ts(tmem + TM_DQ, tm_ds + (kk >> 1) * 32 + (kk & 1) * 8, umma_smem_desc_sw128(ka + kk * 2048, AE_BWD_BN * 128, 1024), idesc_dq,
                   (s > 0) | (kk > 0));
         }
         umma_commit(&bars->k_empty[stage]);
@@ -205,6 +207,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
     }
   } else {
     // =============================== row threads ================================
+    const int wg = warp >> 2;  // the two row warpgroups split every tile by 32-column chunks
     const u32 row = threadIdx.x & 127;
     const u32 lane_base = ((warp & 3) * 32) << 16;
     const int q_idx = q0 + (int)row;
@@ -238,11 +241,10 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       ok = ok && mbar_wait(&bars->sp_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 27);
       tc_fence_after_sync();
       const bool tail = kv0 + AE_BWD_BN > args.Skv;
-#pragma unroll
-      for (int c = 0; c < AE_BWD_BN / 32; ++c) {
+      auto chunk = [&](auto masked_tag, int c) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
         float sv[32], dp[32];
-        tmem_ld_f32x32(tm_s + c * 32, sv);
-        tmem_ld_f32x32(tm_dp + c * 32, dp);
+        tmem_ld_2xf32x32(tm_s + c * 32, tm_dp + c * 32, sv, dp);
         u32 pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -250,27 +252,32 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int kv_idx = kv0 + c * 32 + i + e;
-            bool keep = true;
-            if (tail) keep = kv_idx < args.Skv;
-#if AE_MASK_MODE != 0
-            if (partial) keep = keep && ae_mask(b, hq, q_idx, kv_idx);
-#endif
             const float sraw = sv[i + e];
-            const float t = ae_score_mod(sraw, b, hq, q_idx, kv_idx, cu);
-            float p = ae_bwd_forward(t, fr, b, hq, q_idx, kv_idx, cu);
+            float p = ae_bwd_p(sraw, fr, b, hq, q_idx, kv_idx, cu);
             float dpv = dp[i + e];
-            if (!keep) {
-              p = 0.f;
-              dpv = 0.f;
+            bool keep = true;
+            if (kMasked) {
+              keep = kv_idx < args.Skv;
+#if AE_MASK_MODE != 0
+              if (partial) keep = keep && ae_mask(b, hq, q_idx, kv_idx);
+#endif
+              if (!keep) {
+                p = 0.f;
+                dpv = 0.f;
+              }
             }
-            const float dT = ae_bwd_backward(dpv, p, fr, delta, b, hq, q_idx, kv_idx, cu);
-            float dsv = ae_score_mod_bwd(sraw, dT, b, hq, q_idx, kv_idx, cu);
-            if (!keep) dsv = 0.f;
+            float dsv = ae_bwd_ds(sraw, dpv, p, fr, delta, b, hq, q_idx, kv_idx, cu);
+            if (kMasked && !keep) dsv = 0.f;
             ds2[e] = dsv;
           }
           pk[i >> 1] = pack2<AE_BF16>(ds2[0], ds2[1]);
         }
-        tmem_st16(tm_s + c * 16, pk);
+        tmem_st16(tm_s + c * 32, pk);  // pairs go over this chunk's own first 16 columns
+      };
+      if (partial || tail) {
+        for (int c = wg; c < AE_BWD_BN / 32; c += 2) chunk(AeTrue{}, c);
+      } else {
+        for (int c = wg; c < AE_BWD_BN / 32; c += 2) chunk(AeFalse{}, c);
       }
       tc_wait_st();
       tc_fence_before_sync();
@@ -287,7 +294,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       const bool store = row_valid && ok;
       u16* drow = (u16*)args.dq + (i64)b * args.dq_sb + (i64)(store ? q_idx : 0) * args.dq_ss + (i64)hq * args.dq_sh;
 #pragma unroll
-      for (int c = 0; c < AE_D / 32; ++c) {
+      for (int c = wg * (AE_D / 64); c < (wg + 1) * (AE_D / 64); ++c) {
         float r[32];
         if (n_steps > 0) {
           tmem_ld_f32x32(tmem + TM_DQ + lane_base + c * 32, r);
@@ -313,7 +320,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);
   }

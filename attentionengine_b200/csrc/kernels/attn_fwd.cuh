@@ -17,7 +17,7 @@
 // Expects the generated prelude to define:
 //   AE_D, AE_DV (multiples of 64, <= 128), AE_BF16 (0/1), AE_STAGES,
 //   AE_MASK_MODE (0 none, 1 causal bounds, 2 block list), AE_NFINAL, AE_O_SCALE_ONE,
-//   struct AeRow, ae_mask(), ae_score_mod(), ae_online_fwd(), ae_epilogue_o(),
+//   struct AeRow, ae_mask(), ae_online_fwd() (score_mod fused in), ae_epilogue_o(),
 //   ae_final_rowscales().
 
 #define AE_BM 128
@@ -333,9 +333,6 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #endif
         }
       }
-#pragma unroll
-      for (int c = 0; c < AE_BN; ++c) s[c] = ae_score_mod(s[c], b, hq, q_idx, kv0 + c, cu);
-
       const float o_scale = ae_online_fwd<AE_BN>(s, st, b, hq, q_idx, kv0, cu);
 
       // P -> TMEM (16-bit pairs, column c/2 holds kv columns c, c+1)

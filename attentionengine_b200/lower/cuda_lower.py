@@ -54,10 +54,25 @@ def _is_number(s: str) -> bool:
 _RANK = {"const": 0, "uniform": 1, "row": 2, "tile": 3}
 
 
+class Scal:
+    """A non-tile scalar operand of an affine form: C++ expression plus its value when it is a
+    compile-time constant (None otherwise)."""
+    __slots__ = ("expr", "val")
+
+    def __init__(self, expr: str, val=None):
+        self.expr, self.val = expr, val
+
+
 class Emitter:
     """Emits C++ for a set of root values.  ``env`` maps id(leaf SymbolScalar) or a leaf's Var
     name to a (C++ expression, kind) pair; tile-kind leaf expressions contain ``{c}`` where the
-    column index goes."""
+    column index goes.
+
+    Tile values that are affine in another tile (x * a + b with row / uniform / constant a, b)
+    are carried symbolically and only materialised when a non-affine consumer needs them, so that
+    ``exp(score * scale - m)`` becomes one FFMA feeding ``ex2`` and ``rowmax(score * scale)``
+    becomes ``scale * rowmax(score)``.  Row reductions use four interleaved accumulators.
+    """
 
     def __init__(self, env_by_id: dict, env_by_name: dict, n_cols: str = "N", tile_mode: str = "array"):
         self.by_id = env_by_id
@@ -65,14 +80,59 @@ class Emitter:
         self.n = n_cols
         self.tile_mode = tile_mode  # "array": tiles are float[N]; "scalar": inside a per-element function
         self.lines: list[str] = []
-        self.names: dict[int, tuple[str, str]] = {}  # id(value) -> (expr, kind)
+        self.names: dict[int, tuple[str, str]] = {}   # id(value) -> (expr, kind), materialised
+        self.aff: dict[int, tuple] = {}               # id(value) -> (base (expr, kind), a Scal|None, b Scal|None)
         self.used_leaves: set[str] = set()
         self.k = 0
 
+    # -- helpers -------------------------------------------------------------------------------
     def _tmp(self) -> str:
         self.k += 1
         return f"t{self.k}"
 
+    def _scal(self, expr: str) -> Scal:
+        try:
+            return Scal(expr, float(expr.rstrip("f")))
+        except ValueError:
+            return Scal(expr, None)
+
+    def _emit_scalar(self, expr: str) -> Scal:
+        name = self._tmp()
+        self.lines.append(f"const float {name} = {expr};")
+        return Scal(name, None)
+
+    def _s_mul(self, x, y):
+        if x is None:
+            return y
+        if y is None:
+            return x
+        if x.val is not None and y.val is not None:
+            return Scal(_flit(x.val * y.val), x.val * y.val)
+        return self._emit_scalar(f"({x.expr} * {y.expr})")
+
+    def _s_add(self, x, y):
+        if x is None:
+            return y
+        if y is None:
+            return x
+        if x.val is not None and y.val is not None:
+            return Scal(_flit(x.val + y.val), x.val + y.val)
+        return self._emit_scalar(f"({x.expr} + {y.expr})")
+
+    def _s_neg(self, x):
+        if x is None:
+            return None
+        if x.val is not None:
+            return Scal(_flit(-x.val), -x.val)
+        return self._emit_scalar(f"(-{x.expr})")
+
+    def _s_div(self, x, y):
+        # x / y with x possibly None (= 1 for slope, = 0 for offset is handled by the caller)
+        if x.val is not None and y.val is not None:
+            return Scal(_flit(x.val / y.val), x.val / y.val)
+        return self._emit_scalar(f"__fdividef({x.expr}, {y.expr})")
+
+    # -- public ------------------------------------------------------------------------------------
     def ref(self, v: SymbolScalar, col: str = "c") -> str:
         expr, kind = self.value(v)
         if kind == "tile" and self.tile_mode == "array":
@@ -80,12 +140,55 @@ class Emitter:
         return expr
 
     def value(self, v: SymbolScalar) -> tuple[str, str]:
+        """Materialised (expression, kind) of ``v``."""
         if id(v) in self.names:
             return self.names[id(v)]
-        res = self._lower(v)
+        if id(v) not in self.aff:
+            self._lower(v)
+        if id(v) in self.names:
+            return self.names[id(v)]
+        base, a, b = self.aff[id(v)]
+        res = self._materialise(base, a, b)
         self.names[id(v)] = res
         return res
 
+    def affine(self, v: SymbolScalar):
+        """(base, a, b) with base a materialised tile, for tile-kind ``v``."""
+        if id(v) not in self.aff and id(v) not in self.names:
+            self._lower(v)
+        if id(v) in self.aff:
+            return self.aff[id(v)]
+        return (self.names[id(v)], None, None)
+
+    def _tile_ref(self, base, col="c"):
+        expr, _ = base
+        return expr.replace("{c}", col) if self.tile_mode == "array" else expr
+
+    def _affine_expr(self, base, a, b, col="c") -> str:
+        x = self._tile_ref(base, col)
+        if a is None and b is None:
+            return x
+        if a is None:
+            return f"({x} + {b.expr})"
+        if b is None:
+            return f"({x} * {a.expr})"
+        return f"fmaf({x}, {a.expr}, {b.expr})"
+
+    def _new_tile(self, expr_of_c: str) -> tuple[str, str]:
+        name = self._tmp()
+        if self.tile_mode == "array":
+            self.lines.append(f"float {name}[{self.n}];")
+            self.lines.append(f"#pragma unroll\nfor (int c = 0; c < {self.n}; ++c) {name}[c] = {expr_of_c};")
+            return name + "[{c}]", "tile"
+        self.lines.append(f"const float {name} = {expr_of_c};")
+        return name, "tile"
+
+    def _materialise(self, base, a, b):
+        if a is None and b is None:
+            return base
+        return self._new_tile(self._affine_expr(base, a, b))
+
+    # -- lowering ------------------------------------------------------------------------------------
     def _leaf(self, v: SymbolScalar) -> tuple[str, str]:
         if id(v) in self.by_id:
             e = self.by_id[id(v)]
@@ -106,39 +209,105 @@ class Emitter:
                 return _flit(nm), "const"
         raise KeyError(f"unbound symbolic value {v.varname!r} ({v.code})")
 
-    def _lower(self, v: SymbolScalar) -> tuple[str, str]:
+    def _kind_of(self, v: SymbolScalar) -> str:
+        if id(v) in self.names:
+            return self.names[id(v)][1]
+        if id(v) in self.aff:
+            return "tile"
+        self._lower(v)
+        return "tile" if id(v) in self.aff else self.names[id(v)][1]
+
+    def _reduce(self, t: str, src_of_c) -> str:
+        """Row reduction over the N columns with four interleaved accumulators."""
+        if self.tile_mode != "array":
+            raise NotImplementedError("row reduction outside of online_fwd")
+        name = self._tmp()
+        op = {"ReduceMax": "{a} = fmaxf({a}, {x});", "ReduceSum": "{a} += {x};", "ReduceAbsSum": "{a} += fabsf({x});"}[t]
+        if t == "ReduceMax":
+            inits = [src_of_c(str(i)) for i in range(4)]
+            start = 4
+        else:
+            inits = ["0.f"] * 4
+            start = 0
+        self.lines.append("float " + ", ".join(f"{name}_{i} = {inits[i]}" for i in range(4)) + ";")
+        body = " ".join(op.format(a=f"{name}_{i}", x=src_of_c(f"c + {i}")) for i in range(4))
+        self.lines.append(f"#pragma unroll\nfor (int c = {start}; c < {self.n}; c += 4) {{ {body} }}")
+        if t == "ReduceMax":
+            self.lines.append(f"const float {name} = fmaxf(fmaxf({name}_0, {name}_1), fmaxf({name}_2, {name}_3));")
+        else:
+            self.lines.append(f"const float {name} = ({name}_0 + {name}_1) + ({name}_2 + {name}_3);")
+        return name
+
+    def _lower(self, v: SymbolScalar):
         if not v.prev:
-            return self._leaf(v)
+            self.names[id(v)] = self._leaf(v)
+            return
         t = v.code.type
-        ops = [self.value(p) for p in v.prev]
-        kinds = [k for _, k in ops]
+        kinds = [self._kind_of(p) for p in v.prev]
+        # ---- row reductions ------------------------------------------------------------------
         if t in ("ReduceSum", "ReduceMax", "ReduceAbsSum"):
-            src = self.ref(v.prev[0], "c")
-            if kinds[0] != "tile" or self.tile_mode != "array":
-                raise NotImplementedError("row reduction outside of online_fwd")
-            name = self._tmp()
-            if t == "ReduceMax":
-                self.lines.append(f"float {name} = {self.ref(v.prev[0], '0')};")
-                self.lines.append(f"#pragma unroll\nfor (int c = 1; c < {self.n}; ++c) {name} = fmaxf({name}, {src});")
-            elif t == "ReduceSum":
-                self.lines.append(f"float {name} = 0.f;")
-                self.lines.append(f"#pragma unroll\nfor (int c = 0; c < {self.n}; ++c) {name} += {src};")
-            else:
-                self.lines.append(f"float {name} = 0.f;")
-                self.lines.append(f"#pragma unroll\nfor (int c = 0; c < {self.n}; ++c) {name} += fabsf({src});")
-            return name, "row"
+            if kinds[0] != "tile":
+                raise NotImplementedError("row reduction of a non-tile value")
+            base, a, b = self.affine(v.prev[0])
+            if t == "ReduceMax" and (a is None or (a.val is not None and a.val > 0)):
+                r = self._reduce(t, lambda col: self._tile_ref(base, col))
+                if a is None and b is None:
+                    self.names[id(v)] = (r, "row")
+                else:
+                    self.names[id(v)] = (self._emit_scalar(self._affine_expr((r, "row"), a, b)).expr, "row")
+                return
+            src = self.value(v.prev[0])
+            r = self._reduce(t, lambda col: self._tile_ref(src, col))
+            self.names[id(v)] = (r, "row")
+            return
         kind = max(kinds, key=lambda k: _RANK[k])
         if kind == "const":
             kind = "uniform"
-        a = [self.ref(p, "c") for p in v.prev]
-        expr = self._expr(t, a)
+        # ---- tile results: keep affine forms symbolic -----------------------------------------------------
+        if kind == "tile":
+            tiles = [i for i, k in enumerate(kinds) if k == "tile"]
+            if len(tiles) == 1 and t in ("Mul", "Add", "Sub", "Div", "Neg"):
+                i = tiles[0]
+                base, a, b = self.affine(v.prev[i])
+                if t == "Neg":
+                    one = Scal("1.0f", 1.0)
+                    self.aff[id(v)] = (base, self._s_neg(a if a is not None else one), self._s_neg(b))
+                    return
+                k = self._scal(self.ref(v.prev[1 - i]))
+                if t == "Mul":
+                    self.aff[id(v)] = (base, self._s_mul(a, k), self._s_mul(b, k) if b is not None else None)
+                    return
+                if t == "Add":
+                    self.aff[id(v)] = (base, a, self._s_add(b, k))
+                    return
+                if t == "Sub":
+                    if i == 0:
+                        self.aff[id(v)] = (base, a, self._s_add(b, self._s_neg(k)))
+                    else:
+                        one = Scal("1.0f", 1.0)
+                        self.aff[id(v)] = (base, self._s_neg(a if a is not None else one), self._s_add(k, self._s_neg(b)))
+                    return
+                if t == "Div" and i == 0:
+                    one = Scal("1.0f", 1.0)
+                    self.aff[id(v)] = (base, self._s_div(a if a is not None else one, k),
+                                       self._s_div(b, k) if b is not None else None)
+                    return
+            if t in ("Exp", "Exp2"):
+                base, a, b = self.affine(v.prev[0])
+                if t == "Exp":
+                    l2e = Scal("AE_LOG2E", 1.4426950408889634)
+                    a = self._s_mul(a if a is not None else Scal("1.0f", 1.0), l2e)
+                    b = self._s_mul(b, l2e) if b is not None else None
+                self.names[id(v)] = self._new_tile(f"ae_exp2({self._affine_expr(base, a, b)})")
+                return
+            args = [self.ref(p, "c") for p in v.prev]
+            self.names[id(v)] = self._new_tile(self._expr(t, args))
+            return
+        # ---- row / uniform scalars -----------------------------------------------------------------
+        args = [self.ref(p, "c") for p in v.prev]
         name = self._tmp()
-        if kind == "tile" and self.tile_mode == "array":
-            self.lines.append(f"float {name}[{self.n}];")
-            self.lines.append(f"#pragma unroll\nfor (int c = 0; c < {self.n}; ++c) {name}[c] = {expr};")
-            return name + "[{c}]", "tile"
-        self.lines.append(f"const float {name} = {expr};")
-        return name, kind
+        self.lines.append(f"const float {name} = {self._expr(t, args)};")
+        self.names[id(v)] = (name, kind)
 
     @staticmethod
     def _expr(t: str, a: list[str]) -> str:
@@ -340,10 +509,12 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     src.append("AE_DEVICE bool ae_mask(int b, int h, int q_idx, int kv_idx) { return %s; }\n" %
                (mask_expr if mask_expr is not None else "true"))
 
-    # ---- score_mod (per element) -----------------------------------------------------------------
-    def trace_score_mod():
-        scores = SymbolicArray("scores", Var("scores"), shape_idx=["block_M", "block_N"])
+    # ---- score_mod (per element; kept for kernels that want the plain composition) ---------------------
+    def trace_score_mod(scores=None):
+        scores = scores if scores is not None else SymbolicArray("scores", Var("scores"), shape_idx=["block_M", "block_N"])
         out = score_mod(scores, custom_fwd_inputs, sym_idx("b"), sym_idx("h"), sym_idx("q_idx"), sym_idx("kv_idx"))
+        if not isinstance(out, SymbolScalar):
+            out = SymbolScalar._wrap(out)
         return scores, out
 
     scores, out = trace_score_mod()
@@ -354,24 +525,7 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     src.append("AE_DEVICE float ae_score_mod(float s, int b, int h, int q_idx, int kv_idx, const AeCustom& cu) {\n"
                + em.body() + f"  return {res};\n}}\n")
 
-    # derivative of score_mod: dS = f'(S) * dT
-    scores_b, out_b = trace_score_mod()
-    seed = SymbolicArray("dT", Var("dT"), shape_idx=["block_M", "block_N"])
-    seed.require_grad = False
-    out_b.backward(seed)
-    env = _custom_env(specs, custom_fwd_inputs, bf16, "scalar")
-    env[id(scores_b)] = ("s", "tile")
-    env[id(seed)] = ("dT", "tile")
-    em = Emitter(env, idx_env, tile_mode="scalar")
-    if scores_b.grad is None:
-        gres = "0.f"
-    else:
-        gres = em.ref(scores_b.grad)
-    score_mod_bwd_src = (
-        "AE_DEVICE float ae_score_mod_bwd(float s, float dT, int b, int h, int q_idx, int kv_idx, const AeCustom& cu) {\n"
-        + em.body() + f"  return {gres};\n}}\n")
-
-    # ---- online_fwd (per row, N columns) ------------------------------------------------------------
+    # ---- online_fwd fused with score_mod (per row, N columns) --------------------------------------------
     state_names = list(online_func.online_rowscales.keys())
     state_init = {k: v.code.name if v.code.type == "Var" else str(v.code.value)
                   for k, v in online_func.online_rowscales.items()}
@@ -382,17 +536,19 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
         f"st_{k} = {_flit(state_init[k])};" for k in state_names) + " }\n};\n"
     src.append(row_struct)
 
-    t_scores = SymbolicArray("scores", Var("scores"), shape_idx=["block_M", "block_N"])
+    raw, t_scores = trace_score_mod()
     rs_in = {}
     env = _custom_env(specs, custom_fwd_inputs, bf16, "array")
     for k in state_names:
         v = SymbolScalar(k, Var(k), shape_idx=["block_M"])
         rs_in[k] = v
         env[id(v)] = (f"st.st_{k}", "row")
-    env[id(t_scores)] = ("s[{c}]", "tile")
+    env[id(raw)] = ("s[{c}]", "tile")
     new_scores, new_rs, o_scale = online_func.online_fwd(t_scores, dict(rs_in), sym_idx("b"), sym_idx("h"),
                                                           sym_idx("q_idx"))
-    em = Emitter(env, {"b": idx_env["b"], "h": idx_env["h"], "q_idx": idx_env["q_idx"]}, n_cols="N")
+    arr_idx_env = dict(idx_env)
+    arr_idx_env["kv_idx"] = ("(float)(kv0 + {c})", "tile")
+    em = Emitter(env, arr_idx_env, n_cols="N")
     o_expr, o_kind = em.value(o_scale)
     o_scale_one = (o_kind == "const" and float(o_expr.rstrip("f")) == 1.0)
     new_exprs = {k: em.ref(v) for k, v in new_rs.items()}
@@ -400,10 +556,11 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     body = em.body()
     body += "".join(f"  const float n_{k} = {e};\n" for k, e in new_exprs.items())
     body += f"  const float o_scale_ = {o_expr};\n"
-    if id(new_scores) != id(t_scores):
+    if p_expr != "s[c]":
         body += f"  #pragma unroll\nfor (int c = 0; c < N; ++c) s[c] = {p_expr};\n"
     body += "".join(f"  st.st_{k} = n_{k};\n" for k in new_exprs)
-    src.append("template <int N>\nAE_DEVICE float ae_online_fwd(float (&s)[N], AeRow& st, int b, int h, int q_idx, "
+    src.append("// s[] holds the raw (masked) scores q.k on entry and P on exit: score_mod and online_fwd in one pass\n"
+               "template <int N>\nAE_DEVICE float ae_online_fwd(float (&s)[N], AeRow& st, int b, int h, int q_idx, "
                "int kv0, const AeCustom& cu) {\n" + body + "  return o_scale_;\n}\n")
 
     # ---- epilogue --------------------------------------------------------------------------------------
@@ -427,36 +584,46 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     src.append("AE_DEVICE void ae_final_rowscales(const AeRow& st, float* out) {\n" + em.body()
                + "".join(f"  out[{i}] = {e};\n" for i, e in enumerate(fl)) + "}\n")
 
-    # ---- backward fragments ----------------------------------------------------------------------------------
+    # ---- backward fragments: P = forward(score_mod(S)); dS = score_mod'(S) * backward(dP, P) ---------------------
     bsrc = []
-    qkT = SymbolScalar("scores", Var("scores"), shape_idx=["block_M", "block_N"])
     fr = {}
-    env = _custom_env(specs, custom_fwd_inputs, bf16, "scalar")
+    fr_env = {}
     for i, k in enumerate(final_names):
         v = SymbolScalar(k, Var(k), shape_idx=["block_M"], require_grad=False)
         fr[k] = v
-        env[id(v)] = (f"fr[{i}]", "row")
-    env[id(qkT)] = ("t", "tile")
-    p_out = online_func.forward(qkT, fr, sym_idx("b"), sym_idx("h"), sym_idx("q_idx"), sym_idx("kv_idx"))
+        fr_env[id(v)] = (f"fr[{i}]", "row")
+    raw_p, t_p = trace_score_mod()
+    env = _custom_env(specs, custom_fwd_inputs, bf16, "scalar")
+    env.update(fr_env)
+    env[id(raw_p)] = ("s", "tile")
+    p_out = online_func.forward(t_p, fr, sym_idx("b"), sym_idx("h"), sym_idx("q_idx"), sym_idx("kv_idx"))
     em = Emitter(env, idx_env, tile_mode="scalar")
     res = em.ref(p_out)
-    bsrc.append("AE_DEVICE float ae_bwd_forward(float t, const float* fr, int b, int h, int q_idx, int kv_idx, "
+    bsrc.append("// P from the raw score: OnlineFunc.forward(score_mod(s)) with the saved final row scales\n"
+                "AE_DEVICE float ae_bwd_p(float s, const float* fr, int b, int h, int q_idx, int kv_idx, "
                 "const AeCustom& cu) {\n" + em.body() + f"  return {res};\n}}\n")
 
-    dp = SymbolScalar("dp", Var("dp"), shape_idx=["block_M", "block_N"])
-    pp = SymbolScalar("p", Var("p"), shape_idx=["block_M", "block_N"])
-    doosum = SymbolScalar("doosum", Var("doosum"), shape_idx=["block_M"])
-    env2 = dict(env)
-    env2[id(dp)] = ("dp", "tile")
-    env2[id(pp)] = ("p", "tile")
-    env2[id(doosum)] = ("doosum", "row")
-    ds = online_func.backward(dp, pp, fr, doosum, sym_idx("b"), sym_idx("h"), sym_idx("q_idx"), sym_idx("kv_idx"))
-    em = Emitter(env2, idx_env, tile_mode="scalar")
-    res = em.ref(ds)
+    dp = SymbolScalar("dp", Var("dp"), shape_idx=["block_M", "block_N"], require_grad=False)
+    pp = SymbolScalar("p", Var("p"), shape_idx=["block_M", "block_N"], require_grad=False)
+    doosum = SymbolScalar("doosum", Var("doosum"), shape_idx=["block_M"], require_grad=False)
+    d_t = online_func.backward(dp, pp, fr, doosum, sym_idx("b"), sym_idx("h"), sym_idx("q_idx"), sym_idx("kv_idx"))
+    if not isinstance(d_t, SymbolScalar):
+        d_t = SymbolScalar._wrap(d_t)
+    raw_b, out_b = trace_score_mod()
+    d_t.require_grad = False
+    out_b.backward(d_t)
+    env = _custom_env(specs, custom_fwd_inputs, bf16, "scalar")
+    env.update(fr_env)
+    env[id(raw_b)] = ("s", "tile")
+    env[id(dp)] = ("dp", "tile")
+    env[id(pp)] = ("p", "tile")
+    env[id(doosum)] = ("doosum", "row")
+    em = Emitter(env, idx_env, tile_mode="scalar")
+    gres = em.ref(raw_b.grad) if raw_b.grad is not None else "0.f"
     uses_doosum = "doosum" in em.used_leaves
-    bsrc.append("AE_DEVICE float ae_bwd_backward(float dp, float p, const float* fr, float doosum, int b, int h, "
-                "int q_idx, int kv_idx, const AeCustom& cu) {\n" + em.body() + f"  return {res};\n}}\n")
-    bsrc.append(score_mod_bwd_src)
+    bsrc.append("// dS from dP and P: score_mod'(s) * OnlineFunc.backward(dp, p, final row scales, doosum)\n"
+                "AE_DEVICE float ae_bwd_ds(float s, float dp, float p, const float* fr, float doosum, int b, int h, "
+                "int q_idx, int kv_idx, const AeCustom& cu) {\n" + em.body() + f"  return {gres};\n}}\n")
 
     defines = {
         "AE_D": D, "AE_DV": DV, "AE_BF16": int(bf16), "AE_STAGES": stages, "AE_MASK_MODE": mask_mode,

@@ -106,14 +106,14 @@ def run_reference(args, rank, world):
     threads = os.cpu_count() or 1
     times = []
     for i in range(args.warmup + args.steps):
-        tf, t = cpu_sample(1, threads)
+        tf, t = cpu_sample(4, threads)
         if i >= args.warmup:
             times.append(t)
     g = CFG["Hq"] // CFG["Hkv"]
-    fl = 3.5 * flops_fwd(1, g, CFG["S"], CFG["D"])
+    fl = 4 * 3.5 * flops_fwd(1, g, CFG["S"], CFG["D"])
     ms = 1e3 * sum(times) / len(times)
     value = fl / (ms / 1e3) / 1e12
-    sample = "1 of 64 (batch, kv-group) slices per step: 4 q-heads x S=8192 x D=128 vs one kv-head, fwd+bwd, fp32"
+    sample = "4 of 64 (batch, kv-group) slices per step: 4 q-heads x S=8192 x D=128 vs one kv-head, fwd+bwd, fp32"
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -294,9 +294,9 @@ def main():
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            tf, t = cpu_sample(2, threads)
+            tf, t = cpu_sample(16, threads)
             cpu = {"value": tf, "unit": "TFLOPS", "cores": threads, "kind": "port", "seconds": round(t, 2),
-                   "sample": "2 of 64 (batch, kv-group) slices: 4 q-heads x S=8192 x D=128 vs one kv-head, fwd+bwd, fp32 torch"}
+                   "sample": "16 of 64 (batch, kv-group) slices: 4 q-heads x S=8192 x D=128 vs one kv-head, fwd+bwd, fp32 torch"}
         line = {"metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",

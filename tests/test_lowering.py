@@ -16,7 +16,7 @@ def test_softmax_lowering_has_expected_pieces():
     low = eng.lowered
     assert eng.mask_mode == 1 and low.final_names == ["lse"] and low.uses_doosum and not low.o_scale_one
     for piece in ("struct AeRow", "ae_score_mod", "ae_online_fwd", "ae_epilogue_o", "ae_final_rowscales",
-                  "ae_bwd_forward", "ae_bwd_backward", "ae_score_mod_bwd", "st_m = -1e38f"):
+                  "ae_bwd_p", "ae_bwd_ds", "st_m = -1e38f"):
         assert piece in low.prelude_bwd
     assert "(q_idx >= kv_idx)" in low.prelude_fwd
     assert eng.tl_code.count("tcgen05.mma") >= 2 and "cp.async.bulk.tensor" in eng.tl_code
