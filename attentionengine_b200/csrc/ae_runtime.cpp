@@ -13,6 +13,7 @@
 
 #include "../../include/ae_b200.h"
 #include "kernels/ae_args.h"
+#include "ae_internal.h"
 
 namespace {
 
@@ -232,6 +233,8 @@ int check_attn_common(const Module* m, int kind, int B, int Hq, int Hkv, int Sq,
 }
 
 }  // namespace
+
+void ae_internal_set_error(const char* msg) { g_last_error = msg ? msg : ""; }
 
 extern "C" {
 

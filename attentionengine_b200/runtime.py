@@ -18,6 +18,7 @@ CACHE_DIR = Path(os.environ.get("AE_B200_CACHE", _PKG / "_cubin_cache"))
 
 AE_MAX_CUSTOM = 4
 AE_MAX_FINAL = 4
+STATIC_SCRATCH_MAX_ROWS = 8 * 1024 * 1024  # AE_STATIC_SCRATCH_MAX_ROWS in include/ae_b200.h
 
 KIND_PROBE, KIND_ATTN_FWD, KIND_ATTN_BWD_PREP, KIND_ATTN_BWD_DQ, KIND_ATTN_BWD_DKV = 0, 1, 2, 3, 4
 KIND_MLA_DECODE, KIND_MLA_COMBINE, KIND_LINEAR_FWD, KIND_LINEAR_BWD = 5, 6, 7, 8
@@ -73,7 +74,7 @@ _lib_lock = threading.Lock()
 
 EXPORTS = ["ae_compile", "ae_module_from_cubin", "ae_module_cubin", "ae_query", "ae_release", "ae_strerror",
            "ae_last_error", "ae_launch_attn_fwd", "ae_launch_attn_bwd_prep", "ae_launch_attn_bwd_dq",
-           "ae_launch_attn_bwd_dkv", "ae_launch_probe"]
+           "ae_launch_attn_bwd_dkv", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch"]
 
 
 def lib() -> C.CDLL:
@@ -97,6 +98,8 @@ def lib() -> C.CDLL:
             L.ae_launch_attn_fwd.argtypes = [C.c_void_p, C.POINTER(AttnParams), C.c_void_p]
             for n in ("ae_launch_attn_bwd_prep", "ae_launch_attn_bwd_dq", "ae_launch_attn_bwd_dkv"):
                 getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnBwdParams), C.c_void_p]
+            L.ae_launch_attn_bwd_static_scratch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(AttnBwdParams),
+                                                            C.c_void_p]
             L.ae_launch_probe.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                           C.c_void_p, C.c_void_p]
             _lib = L

@@ -153,6 +153,28 @@ int ae_launch_attn_bwd_prep(void* module, const AeAttnBwdParams* p, void* stream
 int ae_launch_attn_bwd_dq(void* module, const AeAttnBwdParams* p, void* stream);
 int ae_launch_attn_bwd_dkv(void* module, const AeAttnBwdParams* p, void* stream);
 
+/* ---- attention backward without a caller-provided scratch buffer --------------------
+ * No counterpart in the reference (there PyTorch allocates `delta` inside the generated
+ * autograd function).  For callers that cannot allocate device memory: programs that bind
+ * this ABI directly and own nothing but the input / output buffers they were handed, and
+ * serving runtimes whose memory plan is frozen (cudaMalloc would synchronise the device).
+ * Runs pre-pass + dQ pass + dK/dV pass like the three entry points above, but keeps
+ * delta = rowsum(O * dO) in a fixed device array inside the library image
+ * (AE_STATIC_SCRATCH_MAX_ROWS fp32 words = 32 MiB, held by every GPU that loads the
+ * library until the process exits).  `p->delta` is ignored.
+ *  - B * Hq * Sq above AE_STATIC_SCRATCH_MAX_ROWS is refused with AE_ERR_INVALID
+ *    (ae_last_error() names both numbers).
+ *  - Allocates nothing: no cudaMalloc / cudaFree, no allocating library call.
+ *  - The first call on a device resolves the array's device address
+ *    (cudaGetSymbolAddress) with that device current; make that first call outside any
+ *    stream capture.
+ *  - All calls on a device share the one array.  It keeps the previous call's contents;
+ *    every word a call reads is first rewritten by that call's pre-pass, so nothing needs
+ *    clearing, but two calls that overlap on the GPU (different streams) race on it. */
+#define AE_STATIC_SCRATCH_MAX_ROWS (8 * 1024 * 1024)
+int ae_launch_attn_bwd_static_scratch(void* prep_module, void* dq_module, void* dkv_module, const AeAttnBwdParams* p,
+                                      void* stream);
+
 /* ---- bring-up probe (tests only): one 128x128x128 tcgen05 GEMM -------------------
  * mode 0: d = a * b^T (a, b [128,128] 16-bit row-major);
  * mode 1: d = p * b   (p, b [128,128] 16-bit row-major). d is [128,128] fp32.
