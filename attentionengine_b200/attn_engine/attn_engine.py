@@ -165,8 +165,13 @@ class AttentionEngine:
         dynamic = any(isinstance(x, str) for x in (B, Hq, Sq, Skv))
 
         # shape-class dispatch, as attn_engine.py:218-332
+        self._mla = None
         if kv_shared:
-            raise NotImplementedError("kv_shared (MLA decode) kernels are not built yet")
+            from .mla_decode import MlaDecode
+            self._mla = MlaDecode(score_mod, online_func, self.custom_fwd_inputs, Hq, D, DV, self.dtype)
+            self.tl_code = self._mla.src
+            self.mask_mode = 0
+            return
         if not dynamic and Sq != Skv:
             raise NotImplementedError("decode (q_len != kv_len) kernels are not built yet")
         if isinstance(D, str) or isinstance(DV, str) or D % 64 or DV % 64 or D > 128 or DV > 128:
@@ -211,6 +216,8 @@ class AttentionEngine:
 
     def check_status(self):
         """Raise if a kernel of this engine recorded a bounded-wait timeout."""
+        if self._mla is not None:
+            self._status = self._mla._status
         if self._status is not None:
             code = int(self._status.item())
             if code:
@@ -301,6 +308,8 @@ class AttentionEngine:
         return launch_bwd(self, q, k, v, o, d_o, finals, custom)
 
     def __call__(self, *args, **kargs):
+        if self._mla is not None:
+            return self._mla(*args)
         block_mask = kargs.get("block_mask")
         if block_mask is not None:
             self.block_mask = block_mask

@@ -1,0 +1,94 @@
+"""MLA (kv_shared) decode path of AttentionEngine: ``mod(q, q_pe, kv, k_pe) -> o``.
+
+Reference: shape-class dispatch ``kv_shared`` (attention_engine/attn_engine/attn_engine.py:235-250),
+lowering core/lower/lower_decode_mla.py:25-38 and template core/template/tl_template/attn/mla_decode_tl.py.
+Unlike the reference, which ignores ``score_mod`` / ``online_func`` on this path and hard-codes
+softmax with scale 1/sqrt(576) (mla_decode_tl.py:30), the traced callables are honoured here, so the
+user's ``score * softmax_scale`` decides the scale.  Forward only, as in the reference (:337-339).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import runtime as rt
+from ..lower.cuda_lower import lower_attention, lower_combine
+
+MLA_BN = 64  # kv rows per tile (the query block takes 147 KB of shared memory, one 72 KB KV stage fits beside it)
+N_SM = 148
+
+
+class MlaDecode:
+    def __init__(self, score_mod, online_func, custom_fwd_inputs, H: int, D: int, DV: int, dtype):
+        if (D, DV) != (576, 512):
+            raise NotImplementedError(f"MLA decode is built for D = 512 + 64, DV = 512; got D={D}, DV={DV}")
+        if H > 128:
+            raise NotImplementedError("MLA decode handles up to 128 query heads per latent KV")
+        if custom_fwd_inputs.input_tensors:
+            raise NotImplementedError("custom inputs are not wired into the MLA decode kernel")
+        self.dtype = dtype
+        bf16 = dtype == torch.bfloat16
+        self.low = lower_attention(score_mod, None, online_func, custom_fwd_inputs, D=D, DV=DV, bf16=bf16, mask_mode=0)
+        tag = rt.DTYPE_BF16 if bf16 else rt.DTYPE_F16
+        prelude = self.low.prelude_fwd + f"#define AE_MLA_BN {MLA_BN}\n"
+        smem = 9 * 128 * 128 + 9 * MLA_BN * 128 + 256 + 1024
+        cfg = rt.KernelConfig(kind=rt.KIND_MLA_DECODE, dtype=tag, head_dim=D, head_dim_v=DV, threads=192,
+                              smem_bytes=smem, stages=1, mask_mode=0)
+        cfg.reserved[0] = MLA_BN
+        self.src = rt.kernel_source("mla_decode.cuh", prelude=prelude)
+        self.decode = rt.compile_module(self.src, "ae_mla_decode", cfg)
+        comb = (rt.KERNEL_DIR / "mla_combine.cuh").read_text().replace("//%%AE_COMBINE_FUNCTOR%%", lower_combine(online_func))
+        cfg2 = rt.KernelConfig(kind=rt.KIND_MLA_COMBINE, dtype=tag, head_dim=D, head_dim_v=DV, threads=128, smem_bytes=0)
+        head = (rt.KERNEL_DIR / "ae_sm100.cuh").read_text().replace("#pragma once\n", "") + (rt.KERNEL_DIR / "ae_args.h").read_text()
+        defs = f"#define AE_BF16 {int(bf16)}\n#define AE_NFINAL {len(self.low.final_names)}\n"
+        self.combine_src = head + defs + comb
+        self.combine = rt.compile_module(self.combine_src, "ae_mla_combine", cfg2)
+        self.num_split = None  # None = choose per call
+        self._status = None
+
+    @staticmethod
+    def pick_splits(B: int, S: int) -> int:
+        """Enough CTAs (2 per batch row and split) for about two waves of the 148 SMs, never an empty split."""
+        n_tiles = -(-S // MLA_BN)
+        want = max(1, -(-2 * N_SM // (2 * B)))
+        n = min(want, 32, n_tiles)
+        while n > 1 and (n - 1) * (-(-n_tiles // n)) >= n_tiles:
+            n -= 1
+        return n
+
+    def __call__(self, q, q_pe, kv, k_pe):
+        for name, t in (("q", q), ("q_pe", q_pe), ("kv", kv), ("k_pe", k_pe)):
+            if not t.is_cuda:
+                raise rt.AeError(f"{name} must be a CUDA tensor: this back end has no CPU path")
+            if t.dtype != self.dtype:
+                raise TypeError(f"{name} has dtype {t.dtype}, engine was built for {self.dtype}")
+        B, one, H, DV = q.shape
+        S = kv.shape[1]
+        if one != 1 or DV != 512 or q_pe.shape != (B, 1, H, 64) or kv.shape != (B, S, 1, 512) or k_pe.shape != (B, S, 1, 64):
+            raise ValueError("expected q [B,1,H,512], q_pe [B,1,H,64], kv [B,S,1,512], k_pe [B,S,1,64]")
+        q, q_pe, kv, k_pe = (t.contiguous() for t in (q, q_pe, kv, k_pe))
+        dev = q.device
+        n_split = self.num_split or self.pick_splits(B, S)
+        o = torch.empty(B, 1, H, 512, dtype=self.dtype, device=dev)
+        p = rt.MlaParams()
+        p.q, p.q_pe, p.kv, p.k_pe, p.o = q.data_ptr(), q_pe.data_ptr(), kv.data_ptr(), k_pe.data_ptr(), o.data_ptr()
+        keep = []
+        if n_split > 1:
+            part = torch.empty(B, n_split, H, 512, dtype=torch.float32, device=dev)
+            p.o_partial = part.data_ptr()
+            keep.append(part)
+            for i in range(len(self.low.final_names)):
+                f = torch.empty(B, n_split, H, dtype=torch.float32, device=dev)
+                p.rowscale_partial[i] = f.data_ptr()
+                keep.append(f)
+        p.B, p.H, p.S, p.n_split = B, H, S, n_split
+        if self._status is None or self._status.device != dev:
+            self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        p.status = self._status.data_ptr()
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        rt.check(rt.lib().ae_launch_mla_decode(self.decode.handle, C.byref(p), stream), "ae_launch_mla_decode")
+        if n_split > 1:
+            rt.check(rt.lib().ae_launch_mla_combine(self.combine.handle, C.byref(p), stream), "ae_launch_mla_combine")
+        self.last_num_split = n_split
+        return o

@@ -527,4 +527,79 @@ int ae_launch_attn_bwd_dkv(void* module, const AeAttnBwdParams* p, void* stream)
   return launch(m, (unsigned)a.n_kt, (unsigned)p->Hkv, (unsigned)p->B, &a, stream);
 }
 
+static int make_3d_map(AeTmaDesc* out, const void* base, int dtype, int64_t cols, int64_t rows, int64_t batch,
+                       int box_rows) {
+  Driver& d = driver();
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) {
+    set_error("tensor base address must be 16-byte aligned");
+    return AE_ERR_INVALID;
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * cols * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapDataType dt = dtype == AE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  AE_CU(d.cuTensorMapEncodeTiled(reinterpret_cast<CUtensorMap*>(out), dt, 3, const_cast<void*>(base), dims, strides,
+                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return AE_OK;
+}
+
+int ae_launch_mla_decode(void* module, const AeMlaParams* p, void* stream) {
+  if (!module || !p || !p->q || !p->q_pe || !p->kv || !p->k_pe || !p->o) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  if (m->cfg.kind != AE_KIND_MLA_DECODE) {
+    set_error("module kind does not match the entry point");
+    return AE_ERR_UNSUPPORTED;
+  }
+  const int bn = m->cfg.reserved[0];
+  if (p->B <= 0 || p->S <= 0 || p->H <= 0 || p->H > 128 || p->n_split < 1 || p->n_split > 32 || (bn != 64 && bn != 128)) {
+    set_error("MLA decode: need 1 <= H <= 128, S > 0, 1 <= n_split <= 32");
+    return AE_ERR_INVALID;
+  }
+  const int n_tiles = (p->S + bn - 1) / bn;
+  const int tps = (n_tiles + p->n_split - 1) / p->n_split;
+  if ((int64_t)(p->n_split - 1) * tps >= n_tiles) {
+    set_error("MLA decode: n_split leaves an empty split");
+    return AE_ERR_INVALID;
+  }
+  if (p->n_split > 1 && !p->o_partial) {
+    set_error("MLA decode: o_partial scratch required when n_split > 1");
+    return AE_ERR_INVALID;
+  }
+  int rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeMlaArgs a;
+  memset(&a, 0, sizeof a);
+  if ((rc = make_3d_map(&a.tm_q, p->q, m->cfg.dtype, 512, p->H, p->B, 128))) return rc;
+  if ((rc = make_3d_map(&a.tm_qpe, p->q_pe, m->cfg.dtype, 64, p->H, p->B, 128))) return rc;
+  if ((rc = make_3d_map(&a.tm_kv, p->kv, m->cfg.dtype, 512, p->S, p->B, bn))) return rc;
+  if ((rc = make_3d_map(&a.tm_kpe, p->k_pe, m->cfg.dtype, 64, p->S, p->B, bn))) return rc;
+  a.o = p->o;
+  a.o_part = p->o_partial;
+  for (int i = 0; i < AE_MAX_FINAL; ++i) a.fr_part[i] = p->rowscale_partial[i];
+  a.B = p->B; a.H = p->H; a.S = p->S; a.n_split = p->n_split; a.tiles_per_split = tps;
+  a.status = p->status;
+  return launch(m, 2, (unsigned)p->n_split, (unsigned)p->B, &a, stream);
+}
+
+int ae_launch_mla_combine(void* module, const AeMlaParams* p, void* stream) {
+  if (!module || !p || !p->o || !p->o_partial) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  if (m->cfg.kind != AE_KIND_MLA_COMBINE) {
+    set_error("module kind does not match the entry point");
+    return AE_ERR_UNSUPPORTED;
+  }
+  if (p->n_split < 1 || p->n_split > 32) return AE_ERR_INVALID;
+  int rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeMlaCombineArgs a;
+  memset(&a, 0, sizeof a);
+  a.o = p->o;
+  a.o_part = p->o_partial;
+  for (int i = 0; i < AE_MAX_FINAL; ++i) a.fr_part[i] = p->rowscale_partial[i];
+  a.B = p->B; a.H = p->H; a.DV = 512; a.n_split = p->n_split;
+  return launch(m, (unsigned)((p->H + 3) / 4), (unsigned)p->B, 1, &a, stream);
+}
+
 }  // extern "C"

@@ -80,6 +80,25 @@ struct AeAttnBwdArgs {
   u32* status;
 };
 
+// ---- MLA split-KV decode (kernels ae_mla_decode, ae_mla_combine) --------------------------
+struct AeMlaArgs {
+  AeTmaDesc tm_q;    // dims (512, H, B), box {64, 128, 1}
+  AeTmaDesc tm_qpe;  // dims (64, H, B),  box {64, 128, 1}
+  AeTmaDesc tm_kv;   // dims (512, S, B), box {64, BN, 1}
+  AeTmaDesc tm_kpe;  // dims (64, S, B),  box {64, BN, 1}
+  void* o;           // [B, H, 512] 16-bit                       (n_split == 1)
+  float* o_part;     // [B, n_split, H, 512] fp32, normalised   (n_split > 1)
+  float* fr_part[AE_MAX_FINAL];  // each [B, n_split, H]
+  int B, H, S, n_split, tiles_per_split;
+  u32* status;
+};
+struct AeMlaCombineArgs {
+  void* o;
+  const float* o_part;
+  const float* fr_part[AE_MAX_FINAL];
+  int B, H, DV, n_split;
+};
+
 // ---- UMMA / TMA probe kernels (bring-up checks, kernel ae_probe) -------------------
 struct AeProbeArgs {
   AeTmaDesc tm_a;  // [128 rows, KD] 16-bit, box {64, 128}

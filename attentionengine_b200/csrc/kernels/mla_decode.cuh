@@ -1,0 +1,257 @@
+// MLA (multi-head latent attention) split-KV decode for sm_100a.  Replaces the reference's
+// `flash_attn` / `flash_attn_split` kernels (attention_engine/core/template/tl_template/attn/
+// mla_decode_tl.py:38-177; CuTe variant cute_template_kvshared/kernels/splitkv_mla.cu:1061-1391).
+//
+// All H = 128 query heads of one batch row share one latent KV stream: rows of the MMA are heads.
+//   S = [q | q_pe] [kv | k_pe]^T   over 512 + 64 dims (9 K blocks of 64)        SS MMA, M = 128, N = BN
+//   row threads (thread = head): fused score_mod + online recurrence, P -> TMEM
+//   O_half += P kv[:, half]          over this CTA's 256 of the 512 value dims     TS MMA, N = 256
+// A [128 x 512] fp32 accumulator would fill all 512 TMEM columns, so the value dims are split
+// over two CTAs (blockIdx.x) that each recompute S; both read the same KV tiles, the second read
+// is an L2 hit.  blockIdx.y is the kv split, blockIdx.z the batch row.  With more than one split
+// the CTA stores its normalised partial O (fp32) and its final row scales; ae_mla_combine merges.
+// The query block (147 KB) is resident in shared memory, which leaves room for a single KV stage:
+// loads overlap compute only across CTAs of a wave, not inside one (the known limiter of this
+// first version).
+// Roles: warps 0-3 row threads, warp 4 TMA producer, warp 5 MMA issuer.
+// Expects AE_BF16, AE_NFINAL, AE_O_SCALE_ONE, AE_MLA_BN, struct AeRow, ae_online_fwd(),
+// ae_epilogue_o(), ae_final_rowscales().
+
+#define AE_MLA_H 128
+#define AE_MLA_DV 512
+#define AE_MLA_DPE 64
+#define AE_MLA_NBV (AE_MLA_DV / 64)
+#define AE_MLA_NBK (AE_MLA_NBV + AE_MLA_DPE / 64)
+#define AE_MLA_DVH (AE_MLA_DV / 2)
+
+#define AE_MLA_Q_BYTES (AE_MLA_NBK * AE_MLA_H * 128)
+#define AE_MLA_KV_BYTES (AE_MLA_NBK * AE_MLA_BN * 128)
+#define AE_MLA_SMEM_Q 0
+#define AE_MLA_SMEM_KV (AE_MLA_Q_BYTES)
+#define AE_MLA_SMEM_BAR (AE_MLA_SMEM_KV + AE_MLA_KV_BYTES)
+
+struct AeMlaBars {
+  u64 q_full;
+  u64 kv_full;
+  u64 kv_empty;
+  u64 s_full;
+  u64 p_full;
+  u64 o_done;
+  AeCtaCtl ctl;
+};
+
+extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_constant__ AeMlaArgs args) {
+  extern __shared__ u8 smem_raw[];
+  u8* smem = smem_align1024(smem_raw);
+  AeMlaBars* bars = (AeMlaBars*)(smem + AE_MLA_SMEM_BAR);
+  AeCtaCtl* ctl = &bars->ctl;
+  const u32 warp = threadIdx.x >> 5;
+  const u32 lane = threadIdx.x & 31;
+  const int dvh = blockIdx.x;    // which half of the value dims
+  const int split = blockIdx.y;
+  const int b = blockIdx.z;
+
+  const int n_tiles = (args.S + AE_MLA_BN - 1) / AE_MLA_BN;
+  const int t_begin = split * args.tiles_per_split;
+  int t_end = t_begin + args.tiles_per_split;
+  if (t_end > n_tiles) t_end = n_tiles;
+  const int n_steps = t_end > t_begin ? t_end - t_begin : 0;
+
+  if (threadIdx.x == 0) {
+    ctl->abort = 0;
+    mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->kv_full, 1);
+    mbar_init(&bars->kv_empty, 1);
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->p_full, 128);
+    mbar_init(&bars->o_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&ctl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const u32 tmem = ctl->tmem_base;
+  const u32 TM_S = 0, TM_O = 64;
+
+  if (warp == 4) {
+    // =============================== TMA producer ===============================
+    if (lane == 0 && n_steps > 0) {
+      tma_prefetch_desc(&args.tm_q);
+      tma_prefetch_desc(&args.tm_qpe);
+      tma_prefetch_desc(&args.tm_kv);
+      tma_prefetch_desc(&args.tm_kpe);
+      mbar_arrive_expect_tx(&bars->q_full, AE_MLA_Q_BYTES);
+      for (int blk = 0; blk < AE_MLA_NBV; ++blk)
+        tma_load_3d(smem + AE_MLA_SMEM_Q + blk * (AE_MLA_H * 128), &args.tm_q, &bars->q_full, blk * 64, 0, b);
+      tma_load_3d(smem + AE_MLA_SMEM_Q + AE_MLA_NBV * (AE_MLA_H * 128), &args.tm_qpe, &bars->q_full, 0, 0, b);
+      for (int s = 0; s < n_steps; ++s) {
+        if (!mbar_wait(&bars->kv_empty, (s & 1) ^ 1, ctl, args.status, 41)) break;
+        const int kv0 = (t_begin + s) * AE_MLA_BN;
+        mbar_arrive_expect_tx(&bars->kv_full, AE_MLA_KV_BYTES);
+        for (int blk = 0; blk < AE_MLA_NBV; ++blk)
+          tma_load_3d(smem + AE_MLA_SMEM_KV + blk * (AE_MLA_BN * 128), &args.tm_kv, &bars->kv_full, blk * 64, kv0, b);
+        tma_load_3d(smem + AE_MLA_SMEM_KV + AE_MLA_NBV * (AE_MLA_BN * 128), &args.tm_kpe, &bars->kv_full, 0, kv0, b);
+      }
+    }
+  } else if (warp == 5) {
+    // =============================== MMA issuer =================================
+    if (lane == 0 && n_steps > 0) {
+      const u32 idesc_s = umma_idesc_f16(AE_MLA_H, AE_MLA_BN, AE_BF16, 0, 0);
+      const u32 idesc_o = umma_idesc_f16(AE_MLA_H, AE_MLA_DVH, AE_BF16, 0, 1);
+      const u32 q_addr = smem_u32(smem + AE_MLA_SMEM_Q);
+      const u32 kv_addr = smem_u32(smem + AE_MLA_SMEM_KV);
+      bool ok = mbar_wait(&bars->q_full, 0, ctl, args.status, 42);
+      for (int s = 0; s < n_steps && ok; ++s) {
+        ok = mbar_wait(&bars->kv_full, s & 1, ctl, args.status, 43);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int blk = 0; blk < AE_MLA_NBK; ++blk) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            umma_ss(tmem + TM_S, umma_smem_desc_sw128(q_addr + blk * (AE_MLA_H * 128) + kk * 32, 16, 1024),
+                    umma_smem_desc_sw128(kv_addr + blk * (AE_MLA_BN * 128) + kk * 32, 16, 1024), idesc_s,
+                    (blk | kk) > 0);
+          }
+        }
+        umma_commit(&bars->s_full);
+        ok = mbar_wait(&bars->p_full, s & 1, ctl, args.status, 44);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // V = this half's four 64-wide blocks of the same tile, read MN-major
+        const u32 va = kv_addr + dvh * (AE_MLA_NBV / 2) * (AE_MLA_BN * 128);
+#pragma unroll
+        for (int kk = 0; kk < AE_MLA_BN / 16; ++kk) {
+          umma_ts(tmem + TM_O, tmem + TM_S + kk * 8, umma_smem_desc_sw128(va + kk * 2048, AE_MLA_BN * 128, 1024),
+                  idesc_o, (s > 0) | (kk > 0));
+        }
+        umma_commit(&bars->o_done);
+        umma_commit(&bars->kv_empty);
+      }
+    }
+  } else {
+    // =============================== row threads (one per head) =================
+    const u32 row = threadIdx.x & 127;
+    const u32 lane_base = ((warp & 3) * 32) << 16;
+    const u32 tm_s = tmem + TM_S + lane_base;
+    const u32 tm_o = tmem + TM_O + lane_base;
+    const int h = (int)row;
+    AeCustom cu;
+#pragma unroll
+    for (int i = 0; i < AE_MAX_CUSTOM; ++i) {
+      cu.p[i] = nullptr;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) cu.st[i][k] = 0;
+    }
+    AeRow st;
+    st.init();
+    bool ok = true;
+    for (int s = 0; s < n_steps; ++s) {
+      ok = ok && mbar_wait(&bars->s_full, s & 1, ctl, args.status, 45);
+      tc_fence_after_sync();
+      float sc[AE_MLA_BN];
+#if AE_MLA_BN == 64
+      tmem_ld_f32x64(tm_s, sc);
+#else
+      tmem_ld_f32x128(tm_s, sc);
+#endif
+      const int kv0 = (t_begin + s) * AE_MLA_BN;
+      if (kv0 + AE_MLA_BN > args.S) {
+#pragma unroll
+        for (int c = 0; c < AE_MLA_BN; ++c)
+          if (kv0 + c >= args.S) sc[c] = -__int_as_float(0x7f800000);
+      }
+      const float o_scale = ae_online_fwd<AE_MLA_BN>(sc, st, b, h, 0, kv0, cu);
+      {
+        u32 pk[32];
+#pragma unroll
+        for (int half = 0; half < AE_MLA_BN / 64; ++half) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pk[i] = pack2<AE_BF16>(sc[half * 64 + 2 * i], sc[half * 64 + 2 * i + 1]);
+          tmem_st32(tm_s + half * 32, pk);
+        }
+      }
+#if !AE_O_SCALE_ONE
+      if (s > 0) {
+        ok = ok && mbar_wait(&bars->o_done, (s - 1) & 1, ctl, args.status, 46);
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, o_scale != 1.0f)) {
+#pragma unroll
+          for (int c = 0; c < AE_MLA_DVH / 32; ++c) {
+            float f[32];
+            u32 r[32];
+            tmem_ld_f32x32(tm_o + c * 32, f);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(f[i] * o_scale);
+            tmem_st32(tm_o + c * 32, r);
+          }
+        }
+      }
+#endif
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->p_full);
+    }
+
+    if (n_steps > 0) {
+      ok = ok && mbar_wait(&bars->o_done, (n_steps - 1) & 1, ctl, args.status, 47);
+      tc_fence_after_sync();
+      const bool store = ok && h < args.H;
+      const int hs = store ? h : 0;
+      if (args.n_split == 1) {
+        u16* orow = (u16*)args.o + ((i64)b * args.H + hs) * AE_MLA_DV + dvh * AE_MLA_DVH;
+#pragma unroll
+        for (int c = 0; c < AE_MLA_DVH / 32; ++c) {
+          float r[32];
+          tmem_ld_f32x32(tm_o + c * 32, r);
+          if (store) {
+            uint4* dst = (uint4*)(orow + c * 32);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 w;
+              w.x = pack2<AE_BF16>(ae_epilogue_o(r[v * 8 + 0], st), ae_epilogue_o(r[v * 8 + 1], st));
+              w.y = pack2<AE_BF16>(ae_epilogue_o(r[v * 8 + 2], st), ae_epilogue_o(r[v * 8 + 3], st));
+              w.z = pack2<AE_BF16>(ae_epilogue_o(r[v * 8 + 4], st), ae_epilogue_o(r[v * 8 + 5], st));
+              w.w = pack2<AE_BF16>(ae_epilogue_o(r[v * 8 + 6], st), ae_epilogue_o(r[v * 8 + 7], st));
+              dst[v] = w;
+            }
+          }
+        }
+      } else {
+        float* prow = args.o_part + (((i64)b * args.n_split + split) * args.H + hs) * AE_MLA_DV + dvh * AE_MLA_DVH;
+#pragma unroll
+        for (int c = 0; c < AE_MLA_DVH / 32; ++c) {
+          float r[32];
+          tmem_ld_f32x32(tm_o + c * 32, r);
+          if (store) {
+            float4* dst = (float4*)(prow + c * 32);
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              dst[v] = make_float4(ae_epilogue_o(r[v * 4 + 0], st), ae_epilogue_o(r[v * 4 + 1], st),
+                                   ae_epilogue_o(r[v * 4 + 2], st), ae_epilogue_o(r[v * 4 + 3], st));
+          }
+        }
+      }
+#if AE_NFINAL > 0
+      if (store && dvh == 0) {
+        float fr[AE_NFINAL];
+        ae_final_rowscales(st, fr);
+#pragma unroll
+        for (int i = 0; i < AE_NFINAL; ++i)
+          if (args.fr_part[i]) args.fr_part[i][((i64)b * args.n_split + split) * args.H + h] = fr[i];
+      }
+#endif
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}

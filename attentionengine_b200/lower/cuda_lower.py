@@ -260,6 +260,17 @@ class Emitter:
             r = self._reduce(t, lambda col: self._tile_ref(src, col))
             self.names[id(v)] = (r, "row")
             return
+        if t in ("ColReduceSum", "ColReduceMax", "ColReduceAbsSum"):
+            # split-KV merge: one split per lane, reductions over the split dimension are warp reductions
+            if self.tile_mode != "lane":
+                raise NotImplementedError("column reductions only exist in OnlineFunc.combine")
+            x = self.ref(v.prev[0])
+            fn = {"ColReduceSum": f"ae_warp_sum({x})", "ColReduceMax": f"ae_warp_max({x})",
+                  "ColReduceAbsSum": f"ae_warp_sum(fabsf({x}))"}[t]
+            name = self._tmp()
+            self.lines.append(f"const float {name} = {fn};")
+            self.names[id(v)] = (name, "row")
+            return
         kind = max(kinds, key=lambda k: _RANK[k])
         if kind == "const":
             kind = "uniform"
@@ -481,6 +492,22 @@ AE_DEVICE float ae_ld16(const void* p, i64 idx) {
   return unpack_lo<kBf16>((u32)w);
 }
 """
+
+
+def lower_combine(online_func) -> str:
+    """``OnlineFunc.combine`` (split-KV merge weights) as a per-lane functor: lane k holds the final row
+    scales of split k; reductions over the split dimension become warp reductions.  Reference:
+    core/lower/lower_decode.py:287-317."""
+    from ..core.transform.core import SymbolicColReduceArray
+    fr, env = {}, {}
+    for i, (k, v) in enumerate(online_func.final_rowscales.items()):
+        s = SymbolicColReduceArray(k, Var(k), shape_idx=["num_split", "block_M2"])
+        fr[k] = s
+        env[id(s)] = (f"fr[{i}]", "tile")
+    w = online_func.combine(fr)
+    em = Emitter(env, {}, tile_mode="lane")
+    res = em.ref(w)
+    return ("AE_DEVICE float ae_combine(const float* fr) {\n" + em.body() + f"  return {res};\n}}\n")
 
 
 def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomIO, *, D: int, DV: int, bf16: bool,

@@ -69,12 +69,18 @@ class AttnBwdParams(C.Structure):
                 ("status", C.c_void_p)]
 
 
+class MlaParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("q_pe", C.c_void_p), ("kv", C.c_void_p), ("k_pe", C.c_void_p), ("o", C.c_void_p),
+                ("o_partial", C.c_void_p), ("rowscale_partial", C.c_void_p * AE_MAX_FINAL),
+                ("B", C.c_int32), ("H", C.c_int32), ("S", C.c_int32), ("n_split", C.c_int32), ("status", C.c_void_p)]
+
+
 _lib = None
 _lib_lock = threading.Lock()
 
 EXPORTS = ["ae_compile", "ae_module_from_cubin", "ae_module_cubin", "ae_query", "ae_release", "ae_strerror",
            "ae_last_error", "ae_launch_attn_fwd", "ae_launch_attn_bwd_prep", "ae_launch_attn_bwd_dq",
-           "ae_launch_attn_bwd_dkv", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch"]
+           "ae_launch_attn_bwd_dkv", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch", "ae_launch_mla_decode", "ae_launch_mla_combine"]
 
 
 def lib() -> C.CDLL:
@@ -100,6 +106,8 @@ def lib() -> C.CDLL:
                 getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnBwdParams), C.c_void_p]
             L.ae_launch_attn_bwd_static_scratch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(AttnBwdParams),
                                                             C.c_void_p]
+            L.ae_launch_mla_decode.argtypes = [C.c_void_p, C.POINTER(MlaParams), C.c_void_p]
+            L.ae_launch_mla_combine.argtypes = [C.c_void_p, C.POINTER(MlaParams), C.c_void_p]
             L.ae_launch_probe.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                           C.c_void_p, C.c_void_p]
             _lib = L

@@ -175,6 +175,26 @@ int ae_launch_attn_bwd_dkv(void* module, const AeAttnBwdParams* p, void* stream)
 int ae_launch_attn_bwd_static_scratch(void* prep_module, void* dq_module, void* dkv_module, const AeAttnBwdParams* p,
                                       void* stream);
 
+/* ---- MLA split-KV decode ------------------------------------------------------------
+ * Stands in for the generated MLA op `mod(q, q_pe, kv, k_pe) -> o`
+ * (core/template/tl_template/attn/mla_decode_tl.py:218-229, 326-335: `flash_attn_split` +
+ * `combine` with `glse` / `Output_partial` scratch) and for the CuTe path's
+ * `fwd_kvcache_mla` (cute_template_kvshared/flash_api.cpp:212-216).  All tensors contiguous. */
+typedef struct AeMlaParams {
+  const void* q;    /* [B, 1, H, 512] */
+  const void* q_pe; /* [B, 1, H, 64]  */
+  const void* kv;   /* [B, S, 1, 512] */
+  const void* k_pe; /* [B, S, 1, 64]  */
+  void* o;          /* [B, 1, H, 512] */
+  float* o_partial; /* [B, n_split, H, 512] fp32 scratch, used when n_split > 1 */
+  float* rowscale_partial[AE_MAX_FINAL_ROWSCALES]; /* each [B, n_split, H] fp32 scratch */
+  int32_t B, H, S, n_split;
+  uint32_t* status;
+} AeMlaParams;
+
+int ae_launch_mla_decode(void* module, const AeMlaParams* p, void* stream);
+int ae_launch_mla_combine(void* module, const AeMlaParams* p, void* stream);
+
 /* ---- bring-up probe (tests only): one 128x128x128 tcgen05 GEMM -------------------
  * mode 0: d = a * b^T (a, b [128,128] 16-bit row-major);
  * mode 1: d = p * b   (p, b [128,128] 16-bit row-major). d is [128,128] fp32.

@@ -114,3 +114,24 @@ def seeded_qkv(B, Hq, Hkv, S, D, DV, dtype, seed=0, device="cpu"):
     v = torch.randn(B, S, Hkv, DV, generator=g).to(dtype)
     d_o = torch.randn(B, S, Hq, DV, generator=g).to(dtype)
     return [t.to(device) for t in (q, k, v, d_o)]
+
+
+def mla_engine(B, H, S, dtype, scale):
+    """attn_script/mla_decode.py:88-118 with the scale chosen by the caller's score_mod."""
+    class OnlineSoftmaxSplit(OnlineSoftmax):
+        @staticmethod
+        def combine(final_rowscales):
+            lse = final_rowscales["lse"]
+            lse_max = lse.get_reduce("max")
+            row_sum = (lse - lse_max).exp()
+            row_sum_sum = row_sum.get_reduce("sum")
+            lse_sum = row_sum_sum.log() + lse_max
+            return (lse - lse_sum).exp()
+
+    def score_mod(score, custom_fwd_inputs, b, h, q_idx, kv_idx):
+        return score * scale
+
+    qkv = (meta_tensor(B, H, 1, 576, dtype=dtype), meta_tensor(B, 1, S, 576, dtype=dtype),
+           meta_tensor(B, 1, S, 512, dtype=dtype))
+    return AttentionEngine(qkv, CustomIO({}), score_mod=score_mod, mask_mod=None, online_func=OnlineSoftmaxSplit(),
+                           kv_shared=True)

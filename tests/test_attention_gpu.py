@@ -206,3 +206,46 @@ def test_full_size_properties():
     ref = orc.softmax_attention(qs, ks, vs, True)
     _check("slice.o", o1[1:2, sl, 4:8].cpu(), ref, dt)
     eng.check_status()
+
+
+# ---------------------------------------------------------------------------------------------------
+# MLA split-KV decode
+# ---------------------------------------------------------------------------------------------------
+def _mla_inputs(B, H, S, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(B, 1, H, 512, generator=g).to(dtype), torch.randn(B, 1, H, 64, generator=g).to(dtype),
+            torch.randn(B, S, 1, 512, generator=g).to(dtype), torch.randn(B, S, 1, 64, generator=g).to(dtype))
+
+
+@pytest.mark.parametrize("n_split", [1, 3])
+def test_mla_decode_against_reference_golden(golden_dir, n_split):
+    """Output of the reference's own `ref_program` (scale 1/sqrt(576)), H = 16 heads, S = 320."""
+    z = np.load(os.path.join(golden_dir, "mla_decode.npz"))
+    q, q_pe, kv, k_pe = (torch.from_numpy(z[n]) for n in ("q", "q_pe", "kv", "k_pe"))
+    B, H, _ = q.shape
+    S = kv.shape[1]
+    eng = helpers.mla_engine(B, H, S, torch.float16, 1 / math.sqrt(576))
+    eng._mla.num_split = n_split
+    o = eng(q.view(B, 1, H, 512).cuda(), q_pe.view(B, 1, H, 64).cuda(), kv.cuda(), k_pe.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    _check("mla.o", o.view(B, H, 512).cpu(), torch.from_numpy(z["o"]), torch.float16)
+
+
+@pytest.mark.parametrize("B,H,S,dtype,n_split", [
+    (2, 128, 1024, torch.float16, None),   # benchmark head count, automatic split
+    (3, 128, 333, torch.float16, 2),       # ragged kv length
+    (1, 64, 2048, torch.bfloat16, 1),
+    (4, 128, 4096, torch.float16, 1),
+])
+def test_mla_decode_against_oracle(B, H, S, dtype, n_split):
+    """DeepSeek-V3 absorbed shape with the benchmark's scale 1/sqrt(192), honoured through score_mod."""
+    scale = 1 / math.sqrt(192)
+    q, q_pe, kv, k_pe = _mla_inputs(B, H, S, dtype, seed=S)
+    eng = helpers.mla_engine(B, H, S, dtype, scale)
+    eng._mla.num_split = n_split
+    o = eng(q.cuda(), q_pe.cuda(), kv.cuda(), k_pe.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    ref = orc.mla_decode(q[:, 0], q_pe[:, 0], kv, k_pe, scale=scale)
+    _check("mla.o", o[:, 0].cpu(), ref, dtype)
