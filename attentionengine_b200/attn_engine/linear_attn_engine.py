@@ -1,8 +1,125 @@
-"""LinearAttentionEngine: operator API of the chunked linear-attention / SSD scan
-(reference: attention_engine/attn_engine/linear_attn_engine.py:10-52)."""
+"""LinearAttentionEngine: operator API of the chunked linear-attention / SSD scan.
+
+Same constructor and call as the reference (attention_engine/attn_engine/linear_attn_engine.py:10-52):
+``LinearAttentionEngine(qkv_meta, q_mod, k_mod, v_mod, decay_mod, custom_io, ...)`` and
+``mod(q, k, v, decay, *custom)`` with [B, H, T, D] tensors, decay [B, H, T] fp32, returning O [B, H, T, DV].
+
+As in the reference (core/template/tl_template/linear/linear_tl.py:1136-1144) the mods are traced once and
+run as eager PyTorch on the inputs; the scan itself (chunk cumulative sum, state recurrence, intra-chunk
+products) is one sm_100a kernel (csrc/kernels/linear_fwd.cuh).  Backward of the scan is not built yet:
+calling ``.backward()`` through the scan raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import runtime as rt
+from ..core.transform.core import CustomIO, SymbolScalar
+from ..core.transform.graph import Var
+from ..lower.torch_eval import evaluate
+
+_DIM_POS = {"batch": 0, "heads": 1, "seq_len": 2}
+
+
+def _align(t: torch.Tensor, names: tuple, ndim: int) -> torch.Tensor:
+    """View a custom tensor so that its named dims line up with [batch, heads, seq_len, (feature)]."""
+    shape = [1] * ndim
+    for size, name in zip(t.shape, names):
+        name = str(name)
+        if name in _DIM_POS:
+            shape[_DIM_POS[name]] = size
+        elif size != 1:
+            raise ValueError(f"custom input dim {name!r} of size {size} cannot be broadcast")
+    return t.reshape(shape)
+
+
+class _Scan(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, eng, q, k, v, a):
+        return eng._launch(q, k, v, a)
+
+    @staticmethod
+    def backward(ctx, d_o):
+        raise NotImplementedError("backward of the chunked linear-attention scan is not built yet")
 
 
 class LinearAttentionEngine:
     def __init__(self, qkv_meta, q_mod=None, k_mod=None, v_mod=None, decay_mod=None, custom_io=None, tune=False,
                  tune_filename="tune_result", tune_bwd=False):
-        raise NotImplementedError("the chunked linear-attention scan kernels are not built yet")
+        qm, km, vm = qkv_meta
+        self.dtype = qm.dtype
+        if self.dtype not in (torch.float16, torch.bfloat16):
+            raise NotImplementedError("fp16 / bf16 only")
+        self.B, self.HQ, self.T, self.DK = qm.shape
+        self.HK = km.shape[1]
+        self.H, self.DV = vm.shape[1], vm.shape[3]
+        if self.DK != 128 or self.DV not in (64, 128):
+            raise NotImplementedError(f"linear attention is built for DK = 128 and DV in (64, 128); got {self.DK}, {self.DV}")
+        self.custom_io = custom_io if custom_io is not None else CustomIO()
+        self.mods = {"q": q_mod, "k": k_mod, "v": v_mod, "decay": decay_mod}
+        self._traced = {}
+        for name, fn in self.mods.items():
+            if fn is None:
+                continue
+            leaf = SymbolScalar(name, Var(name), shape_idx=["batch", "heads", "seq_len"] + ([] if name == "decay" else ["dim"]))
+            self._traced[name] = (leaf, fn(leaf, self.custom_io))
+        bf16 = self.dtype == torch.bfloat16
+        stages = 2 if self.DV == 64 else 1
+        prelude = f"#define AE_BF16 {int(bf16)}\n#define AE_LIN_DV {self.DV}\n#define AE_LIN_STAGES {stages}\n"
+        smem = stages * (2 * 128 * 128 * 2 + 128 * self.DV * 2) + 128 * self.DV * 2 + 128 * self.DV * 2 + 1024 + 256 + 1024
+        cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_FWD, dtype=rt.DTYPE_BF16 if bf16 else rt.DTYPE_F16, head_dim=128,
+                              head_dim_v=self.DV, threads=192, smem_bytes=smem, stages=stages, mask_mode=0)
+        self.tl_code = rt.kernel_source("linear_fwd.cuh", prelude=prelude)
+        self.fwd = rt.compile_module(self.tl_code, "ae_linear_fwd", cfg)
+        self._status = None
+
+    def _apply_mod(self, name, x, custom):
+        if name not in self._traced:
+            return x
+        leaf, out = self._traced[name]
+        env = {id(leaf): x.float() if name == "decay" else x}
+        for (cname, sym), t in zip(self.custom_io.input_tensors.items(), custom):
+            env[id(sym)] = _align(t, tuple(sym.shape_idx), x.dim())
+        y = evaluate(out, env)
+        return y if name == "decay" else y.to(x.dtype)
+
+    def _launch(self, q, k, v, a):
+        B, HQ, T, DK = q.shape
+        H, DV = v.shape[1], v.shape[3]
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        a = a.float().contiguous()
+        o = torch.empty(B, H, T, DV, dtype=self.dtype, device=q.device)
+        p = rt.LinearParams()
+        p.q, p.k, p.v, p.a, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), o.data_ptr()
+        p.B, p.H, p.HQ, p.HK, p.T = B, H, HQ, k.shape[1], T
+        if self._status is None or self._status.device != q.device:
+            self._status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        p.status = self._status.data_ptr()
+        stream = C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
+        rt.check(rt.lib().ae_launch_linear_fwd(self.fwd.handle, C.byref(p), stream), "ae_launch_linear_fwd")
+        return o
+
+    def check_status(self):
+        if self._status is not None:
+            code = int(self._status.item())
+            if code:
+                self._status.zero_()
+                raise rt.AeError(f"kernel reported status 0x{code:x} (a bounded wait gave up)")
+
+    def __call__(self, q, k, v, decay, *custom):
+        for name, t in (("q", q), ("k", k), ("v", v), ("decay", decay)):
+            if not t.is_cuda:
+                raise rt.AeError(f"{name} must be a CUDA tensor: this back end has no CPU path")
+        if q.dtype != self.dtype or k.dtype != self.dtype or v.dtype != self.dtype:
+            raise TypeError(f"q/k/v must be {self.dtype}")
+        if len(custom) != len(self.custom_io.input_tensors):
+            raise TypeError(f"expected {len(self.custom_io.input_tensors)} custom input(s), got {len(custom)}")
+        if q.shape[3] != self.DK or v.shape[3] != self.DV or v.shape[1] % q.shape[1] or v.shape[1] % k.shape[1]:
+            raise ValueError("inconsistent q/k/v shapes")
+        a = self._apply_mod("decay", decay, custom)
+        qm = self._apply_mod("q", q, custom)
+        km = self._apply_mod("k", k, custom)
+        vm = self._apply_mod("v", v, custom)
+        return _Scan.apply(self, qm, km, vm, a)

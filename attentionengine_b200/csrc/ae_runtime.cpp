@@ -602,4 +602,53 @@ int ae_launch_mla_combine(void* module, const AeMlaParams* p, void* stream) {
   return launch(m, (unsigned)((p->H + 3) / 4), (unsigned)p->B, 1, &a, stream);
 }
 
+// Tensor map over a contiguous [B, H, T, D] tensor seen as (d, t, h, b), box {64, rows, 1, 1}.
+static int make_bhtd_map(AeTmaDesc* out, const void* base, int dtype, int64_t B, int64_t H, int64_t T, int64_t D,
+                         int rows) {
+  Driver& d = driver();
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || D % 8) {
+    set_error("tensor base address must be 16-byte aligned and the head dim a multiple of 8");
+    return AE_ERR_INVALID;
+  }
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)T * D * 2, (cuuint64_t)H * T * D * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMapDataType dt = dtype == AE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  AE_CU(d.cuTensorMapEncodeTiled(reinterpret_cast<CUtensorMap*>(out), dt, 4, const_cast<void*>(base), dims, strides,
+                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return AE_OK;
+}
+
+int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream) {
+  if (!module || !p || !p->q || !p->k || !p->v || !p->a || !p->o) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  if (m->cfg.kind != AE_KIND_LINEAR_FWD) {
+    set_error("module kind does not match the entry point");
+    return AE_ERR_UNSUPPORTED;
+  }
+  if (p->B <= 0 || p->H <= 0 || p->HQ <= 0 || p->HK <= 0 || p->T <= 0 || p->H % p->HQ || p->H % p->HK ||
+      m->cfg.head_dim != 128 || (m->cfg.head_dim_v != 64 && m->cfg.head_dim_v != 128)) {
+    set_error("linear attention: need H % HQ == 0, H % HK == 0, DK = 128, DV in {64, 128}");
+    return AE_ERR_INVALID;
+  }
+  if ((reinterpret_cast<uintptr_t>(p->o) & 15) || (reinterpret_cast<uintptr_t>(p->a) & 3)) {
+    set_error("linear attention: output must be 16-byte aligned");
+    return AE_ERR_INVALID;
+  }
+  int rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeLinearArgs a;
+  memset(&a, 0, sizeof a);
+  if ((rc = make_bhtd_map(&a.tm_q, p->q, m->cfg.dtype, p->B, p->HQ, p->T, 128, 128))) return rc;
+  if ((rc = make_bhtd_map(&a.tm_k, p->k, m->cfg.dtype, p->B, p->HK, p->T, 128, 128))) return rc;
+  if ((rc = make_bhtd_map(&a.tm_v, p->v, m->cfg.dtype, p->B, p->H, p->T, m->cfg.head_dim_v, 128))) return rc;
+  a.a = p->a;
+  a.o = p->o;
+  a.B = p->B; a.H = p->H; a.HQ = p->HQ; a.HK = p->HK; a.T = p->T;
+  a.status = p->status;
+  return launch(m, (unsigned)p->H, (unsigned)p->B, 1, &a, stream);
+}
+
 }  // extern "C"

@@ -99,6 +99,17 @@ struct AeMlaCombineArgs {
   int B, H, DV, n_split;
 };
 
+// ---- chunked linear attention / SSD scan forward (kernel ae_linear_fwd) -------------------
+struct AeLinearArgs {
+  AeTmaDesc tm_q;  // [B, HQ, T, DK] seen as (d, t, h, b), box {64, 128, 1, 1}
+  AeTmaDesc tm_k;  // [B, HK, T, DK]
+  AeTmaDesc tm_v;  // [B, H, T, DV]
+  const float* a;  // [B, H, T] fp32 log-decay per step (<= 0)
+  void* o;         // [B, H, T, DV] 16-bit
+  int B, H, HQ, HK, T;
+  u32* status;
+};
+
 // ---- UMMA / TMA probe kernels (bring-up checks, kernel ae_probe) -------------------
 struct AeProbeArgs {
   AeTmaDesc tm_a;  // [128 rows, KD] 16-bit, box {64, 128}

@@ -1,0 +1,325 @@
+// Chunked linear-attention / SSD scan, forward, for sm_100a.  Replaces the reference's
+// `chunk_local_cumsum_scalar_kernel` + `chunk_fwd_h` + `chunk_o` kernels
+// (attention_engine/core/template/tl_template/linear/linear_tl.py:25-49, 114-233, 283-410) with one
+// kernel that never writes the per-chunk states to HBM.
+//
+// Recurrence per (batch, head), with a_t <= 0 the log-decay of step t:
+//     S_t = exp(a_t) S_{t-1} + k_t^T v_t ,      o_t = q_t S_t
+// One CTA owns one (batch, head) and walks its chunks of 128 steps in order; the state S [DK x DV]
+// lives in TMEM as an fp32 accumulator for the whole sequence.  Per chunk, with g the inclusive
+// cumulative sum of a inside the chunk:
+//     A   = q k^T                                   (SS MMA)
+//     Oi  = q h                                     (SS MMA, h = bf16 copy of the incoming state)
+//     H   = exp(g_last) H + k^T (v * exp(g_last - g))    (SS MMA, k read MN-major as A)
+//     row threads: P_ij = A_ij exp(g_i - g_j) [i >= j] -> TMEM ; Oi_i *= exp(g_i)
+//     O   = Oi + P v                                (TS MMA)
+// The exponent g_i - g_j is only evaluated for j <= i (where it is <= 0), so nothing overflows; the
+// reference evaluates it everywhere and masks afterwards (linear_tl.py:372-378).
+// Roles: warps 0-3 row threads (thread r = step r of the chunk = state row r), warp 4 TMA producer,
+// warp 5 MMA issuer.  Expects AE_BF16, AE_LIN_DV (64 or 128), AE_LIN_STAGES; DK is 128.
+
+#define AE_LIN_C 128
+#define AE_LIN_DK 128
+
+#define AE_LIN_Q_BYTES (AE_LIN_C * AE_LIN_DK * 2)
+#define AE_LIN_V_BYTES (AE_LIN_C * AE_LIN_DV * 2)
+#define AE_LIN_STAGE_BYTES (2 * AE_LIN_Q_BYTES + AE_LIN_V_BYTES)
+#define AE_LIN_SMEM_STAGE 0
+#define AE_LIN_SMEM_V2 (AE_LIN_STAGES * AE_LIN_STAGE_BYTES)
+#define AE_LIN_SMEM_H (AE_LIN_SMEM_V2 + AE_LIN_V_BYTES)
+#define AE_LIN_SMEM_G (AE_LIN_SMEM_H + AE_LIN_DK * AE_LIN_DV * 2)
+#define AE_LIN_SMEM_BAR (AE_LIN_SMEM_G + 1024)
+
+struct AeLinBars {
+  u64 full[AE_LIN_STAGES];
+  u64 empty[AE_LIN_STAGES];
+  u64 s_full;
+  u64 prep_done;
+  u64 oi_full;
+  u64 p_full;
+  u64 o_done;
+  u64 h_done;
+  AeCtaCtl ctl;
+};
+
+// 16-byte chunk `ch` of row `r` inside a [rows][128 B] tile with the 128-byte swizzle
+AE_DEVICE u32 swz128(u32 r, u32 ch) { return r * 128 + ((ch ^ (r & 7)) << 4); }
+
+extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_constant__ AeLinearArgs args) {
+  extern __shared__ u8 smem_raw[];
+  u8* smem = smem_align1024(smem_raw);
+  AeLinBars* bars = (AeLinBars*)(smem + AE_LIN_SMEM_BAR);
+  float* gs = (float*)(smem + AE_LIN_SMEM_G);  // [128] cumulative log-decay of the chunk, [128..131] warp totals
+  AeCtaCtl* ctl = &bars->ctl;
+  const u32 warp = threadIdx.x >> 5;
+  const u32 lane = threadIdx.x & 31;
+  const int h = blockIdx.x;
+  const int b = blockIdx.y;
+  const int hq = h / (args.H / args.HQ);
+  const int hk = h / (args.H / args.HK);
+  const int n_chunks = (args.T + AE_LIN_C - 1) / AE_LIN_C;
+
+  if (threadIdx.x == 0) {
+    ctl->abort = 0;
+    for (int i = 0; i < AE_LIN_STAGES; ++i) {
+      mbar_init(&bars->full[i], 1);
+      mbar_init(&bars->empty[i], 1);
+    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->prep_done, 128);
+    mbar_init(&bars->oi_full, 1);
+    mbar_init(&bars->p_full, 128);
+    mbar_init(&bars->o_done, 1);
+    mbar_init(&bars->h_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&ctl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const u32 tmem = ctl->tmem_base;
+  const u32 TM_S = 0, TM_O = 128, TM_H = 128 + AE_LIN_DV;
+
+  if (warp == 4) {
+    // =============================== TMA producer ===============================
+    if (lane == 0) {
+      tma_prefetch_desc(&args.tm_q);
+      tma_prefetch_desc(&args.tm_k);
+      tma_prefetch_desc(&args.tm_v);
+      for (int c = 0; c < n_chunks; ++c) {
+        const int stage = c % AE_LIN_STAGES;
+        const u32 par = ((c / AE_LIN_STAGES) & 1) ^ 1;
+        if (!mbar_wait(&bars->empty[stage], par, ctl, args.status, 51)) break;
+        u8* st = smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES;
+        mbar_arrive_expect_tx(&bars->full[stage], AE_LIN_STAGE_BYTES);
+        for (int dh = 0; dh < AE_LIN_DK / 64; ++dh) {
+          tma_load_4d(st + dh * (AE_LIN_C * 128), &args.tm_q, &bars->full[stage], dh * 64, c * AE_LIN_C, hq, b);
+          tma_load_4d(st + AE_LIN_Q_BYTES + dh * (AE_LIN_C * 128), &args.tm_k, &bars->full[stage], dh * 64,
+                      c * AE_LIN_C, hk, b);
+        }
+        for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
+          tma_load_4d(st + 2 * AE_LIN_Q_BYTES + dh * (AE_LIN_C * 128), &args.tm_v, &bars->full[stage], dh * 64,
+                      c * AE_LIN_C, h, b);
+      }
+    }
+  } else if (warp == 5) {
+    // =============================== MMA issuer =================================
+    if (lane == 0 && n_chunks > 0) {
+      const u32 idesc_s = umma_idesc_f16(128, AE_LIN_C, AE_BF16, 0, 0);          // q k^T
+      const u32 idesc_oi = umma_idesc_f16(128, AE_LIN_DV, AE_BF16, 0, 1);        // q h, P v
+      const u32 idesc_h = umma_idesc_f16(AE_LIN_DK, AE_LIN_DV, AE_BF16, 1, 1);   // k^T v'
+      const u32 v2_addr = smem_u32(smem + AE_LIN_SMEM_V2);
+      const u32 h_addr = smem_u32(smem + AE_LIN_SMEM_H);
+      auto issue_s = [&](int c) -> bool {
+        const int stage = c % AE_LIN_STAGES;
+        if (!mbar_wait(&bars->full[stage], (c / AE_LIN_STAGES) & 1, ctl, args.status, 52)) return false;
+        tc_fence_after_sync();
+        const u32 qa = smem_u32(smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES);
+        const u32 ka = qa + AE_LIN_Q_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < AE_LIN_DK / 16; ++kk) {
+          const u32 off = (kk >> 2) * (AE_LIN_C * 128) + (kk & 3) * 32;
+          umma_ss(tmem + TM_S, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
+                  idesc_s, kk > 0);
+        }
+        umma_commit(&bars->s_full);
+        return true;
+      };
+      bool ok = issue_s(0);
+      for (int c = 0; c < n_chunks && ok; ++c) {
+        const int stage = c % AE_LIN_STAGES;
+        const u32 qa = smem_u32(smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES);
+        const u32 ka = qa + AE_LIN_Q_BYTES;
+        const u32 va = qa + 2 * AE_LIN_Q_BYTES;
+        ok = mbar_wait(&bars->prep_done, c & 1, ctl, args.status, 53);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (c > 0) {
+          // Oi = q h   (h: [DK rows][DV contiguous], MN-major B)
+#pragma unroll
+          for (int kk = 0; kk < AE_LIN_DK / 16; ++kk) {
+            const u32 off = (kk >> 2) * (AE_LIN_C * 128) + (kk & 3) * 32;
+            umma_ss(tmem + TM_O, umma_smem_desc_sw128(qa + off, 16, 1024),
+                    umma_smem_desc_sw128(h_addr + kk * 2048, AE_LIN_DK * 128, 1024), idesc_oi, kk > 0);
+          }
+        }
+        umma_commit(&bars->oi_full);
+        // H (+)= k^T v'   (k tile read MN-major as A: [chunk rows][DK contiguous]; v' likewise as B)
+#pragma unroll
+        for (int kk = 0; kk < AE_LIN_C / 16; ++kk) {
+          umma_ss(tmem + TM_H, umma_smem_desc_sw128(ka + kk * 2048, AE_LIN_C * 128, 1024),
+                  umma_smem_desc_sw128(v2_addr + kk * 2048, AE_LIN_C * 128, 1024), idesc_h, (c > 0) | (kk > 0));
+        }
+        umma_commit(&bars->h_done);
+        ok = mbar_wait(&bars->p_full, c & 1, ctl, args.status, 54);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < AE_LIN_C / 16; ++kk) {
+          umma_ts(tmem + TM_O, tmem + TM_S + kk * 8, umma_smem_desc_sw128(va + kk * 2048, AE_LIN_C * 128, 1024),
+                  idesc_oi, (c > 0) | (kk > 0));
+        }
+        umma_commit(&bars->o_done);
+        umma_commit(&bars->empty[stage]);
+        if (c + 1 < n_chunks) ok = issue_s(c + 1);
+      }
+    }
+  } else {
+    // =============================== row threads ================================
+    const u32 r = threadIdx.x & 127;
+    const u32 lane_base = ((warp & 3) * 32) << 16;
+    const float* a_row = args.a + ((i64)b * args.H + h) * args.T;
+    u16* o_base = (u16*)args.o + ((i64)b * args.H + h) * (i64)args.T * AE_LIN_DV;
+    bool ok = true;
+    for (int c = 0; c < n_chunks; ++c) {
+      const int stage = c % AE_LIN_STAGES;
+      const int t = c * AE_LIN_C + (int)r;
+      // ---- A: inclusive cumulative sum of the log-decay over the chunk ----------------------
+      float g = t < args.T ? a_row[t] : 0.f;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float n = __shfl_up_sync(0xffffffffu, g, o);
+        if (lane >= (u32)o) g += n;
+      }
+      if (lane == 31) gs[128 + (warp & 3)] = g;
+      named_bar_sync(1, 128);
+      {
+        float pre = 0.f;
+#pragma unroll
+        for (int w = 0; w < 3; ++w)
+          if ((u32)w < (warp & 3)) pre += gs[128 + w];
+        g += pre;
+      }
+      named_bar_sync(1, 128);  // warp totals consumed; also: last chunk's readers of gs[] are done
+      gs[r] = g;
+      named_bar_sync(1, 128);
+      const float g_last = gs[AE_LIN_C - 1];
+      // ---- B: incoming state -> bf16 copy for q h, and decay it in place --------------------
+      if (c > 0) {
+        ok = ok && mbar_wait(&bars->h_done, (c - 1) & 1, ctl, args.status, 55);
+        tc_fence_after_sync();
+        const float dec = ae_exp(g_last);
+        u8* hb = smem + AE_LIN_SMEM_H;
+#pragma unroll
+        for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+          float f[32];
+          u32 w[32];
+          tmem_ld_f32x32(tmem + TM_H + lane_base + cc * 32, f);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 pk;
+            pk.x = pack2<AE_BF16>(f[i * 8 + 0], f[i * 8 + 1]);
+            pk.y = pack2<AE_BF16>(f[i * 8 + 2], f[i * 8 + 3]);
+            pk.z = pack2<AE_BF16>(f[i * 8 + 4], f[i * 8 + 5]);
+            pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
+            const u32 col = cc * 32 + i * 8;  // element column of this 16-byte chunk
+            *(uint4*)(hb + (col >> 6) * (AE_LIN_DK * 128) + swz128(r, (col & 63) >> 3)) = pk;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(f[i] * dec);
+          tmem_st32(tmem + TM_H + lane_base + cc * 32, w);
+        }
+      }
+      // ---- C: v' = v * exp(g_last - g), second copy of the v tile ---------------------------
+      ok = ok && mbar_wait(&bars->full[stage], (c / AE_LIN_STAGES) & 1, ctl, args.status, 56);
+      {
+        const float wgt = ae_exp(g_last - g);
+        const u8* vt = smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES + 2 * AE_LIN_Q_BYTES;
+        u8* v2 = smem + AE_LIN_SMEM_V2;
+#pragma unroll
+        for (int ch = 0; ch < AE_LIN_DV / 8; ++ch) {
+          const u32 off = (ch >> 3) * (AE_LIN_C * 128) + swz128(r, ch & 7);
+          uint4 x = *(const uint4*)(vt + off);
+          u32* xw = (u32*)&x;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            xw[i] = pack2<AE_BF16>(unpack_lo<AE_BF16>(xw[i]) * wgt, unpack_hi<AE_BF16>(xw[i]) * wgt);
+          *(uint4*)(v2 + off) = x;
+        }
+      }
+      tc_wait_st();
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->prep_done);
+      // ---- D: P = A * exp(g_i - g_j) for j <= i -------------------------------------------------
+      ok = ok && mbar_wait(&bars->s_full, c & 1, ctl, args.status, 57);
+      tc_fence_after_sync();
+      {
+        float s[AE_LIN_C];
+        tmem_ld_f32x128(tmem + TM_S + lane_base, s);
+        u32 pk[32];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float4 gj = *(const float4*)(gs + half * 64 + 2 * i);
+            const float gv[4] = {gj.x, gj.y, gj.z, gj.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = half * 64 + 2 * i + e;
+              const float p = ((u32)j <= r) ? s[j] * ae_exp(g - gv[e]) : 0.f;
+              s[j] = p;
+            }
+            pk[i] = pack2<AE_BF16>(s[half * 64 + 2 * i], s[half * 64 + 2 * i + 1]);
+            pk[i + 1] = pack2<AE_BF16>(s[half * 64 + 2 * i + 2], s[half * 64 + 2 * i + 3]);
+          }
+          tmem_st32(tmem + TM_S + lane_base + half * 32, pk);
+        }
+      }
+      // ---- E: scale the inter-chunk part of O by exp(g_i) ---------------------------------------
+      ok = ok && mbar_wait(&bars->oi_full, c & 1, ctl, args.status, 58);
+      tc_fence_after_sync();
+      if (c > 0) {
+        const float eg = ae_exp(g);
+#pragma unroll
+        for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+          float f[32];
+          u32 w[32];
+          tmem_ld_f32x32(tmem + TM_O + lane_base + cc * 32, f);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(f[i] * eg);
+          tmem_st32(tmem + TM_O + lane_base + cc * 32, w);
+        }
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->p_full);
+      // ---- F: O rows out ---------------------------------------------------------------------------
+      ok = ok && mbar_wait(&bars->o_done, c & 1, ctl, args.status, 59);
+      tc_fence_after_sync();
+      {
+        const bool store = ok && t < args.T;
+        u16* orow = o_base + (i64)(store ? t : 0) * AE_LIN_DV;
+#pragma unroll
+        for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+          float f[32];
+          tmem_ld_f32x32(tmem + TM_O + lane_base + cc * 32, f);
+          if (store) {
+            uint4* dst = (uint4*)(orow + cc * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 pk;
+              pk.x = pack2<AE_BF16>(f[i * 8 + 0], f[i * 8 + 1]);
+              pk.y = pack2<AE_BF16>(f[i * 8 + 2], f[i * 8 + 3]);
+              pk.z = pack2<AE_BF16>(f[i * 8 + 4], f[i * 8 + 5]);
+              pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
+              dst[i] = pk;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      named_bar_sync(1, 128);  // every row has read O before the next chunk's q h overwrites it
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}

@@ -75,12 +75,18 @@ class MlaParams(C.Structure):
                 ("B", C.c_int32), ("H", C.c_int32), ("S", C.c_int32), ("n_split", C.c_int32), ("status", C.c_void_p)]
 
 
+class LinearParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("a", C.c_void_p), ("o", C.c_void_p),
+                ("B", C.c_int32), ("H", C.c_int32), ("HQ", C.c_int32), ("HK", C.c_int32), ("T", C.c_int32),
+                ("status", C.c_void_p)]
+
+
 _lib = None
 _lib_lock = threading.Lock()
 
 EXPORTS = ["ae_compile", "ae_module_from_cubin", "ae_module_cubin", "ae_query", "ae_release", "ae_strerror",
            "ae_last_error", "ae_launch_attn_fwd", "ae_launch_attn_bwd_prep", "ae_launch_attn_bwd_dq",
-           "ae_launch_attn_bwd_dkv", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch", "ae_launch_mla_decode", "ae_launch_mla_combine"]
+           "ae_launch_attn_bwd_dkv", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch", "ae_launch_mla_decode", "ae_launch_mla_combine", "ae_launch_linear_fwd"]
 
 
 def lib() -> C.CDLL:
@@ -108,6 +114,7 @@ def lib() -> C.CDLL:
                                                             C.c_void_p]
             L.ae_launch_mla_decode.argtypes = [C.c_void_p, C.POINTER(MlaParams), C.c_void_p]
             L.ae_launch_mla_combine.argtypes = [C.c_void_p, C.POINTER(MlaParams), C.c_void_p]
+            L.ae_launch_linear_fwd.argtypes = [C.c_void_p, C.POINTER(LinearParams), C.c_void_p]
             L.ae_launch_probe.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                           C.c_void_p, C.c_void_p]
             _lib = L

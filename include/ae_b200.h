@@ -195,6 +195,24 @@ typedef struct AeMlaParams {
 int ae_launch_mla_decode(void* module, const AeMlaParams* p, void* stream);
 int ae_launch_mla_combine(void* module, const AeMlaParams* p, void* stream);
 
+/* ---- chunked linear attention / SSD scan, forward ----------------------------------------
+ * Stands in for `LinearAttention.forward` after the q/k/v/decay mods
+ * (core/template/tl_template/linear/linear_tl.py:1129-1156): `chunk_local_cumsum_scalar`,
+ * `chunk_fwd_h_mod`, `chunk_fwd_o_mod`.  Layout [B, H, T, D] contiguous (as the reference);
+ * q has HQ heads, k has HK heads, v / a / o have H heads (H a multiple of HQ and HK);
+ * `a` is the per-step log-decay (fp32, <= 0).  DK = 128, DV = 64 or 128. */
+typedef struct AeLinearParams {
+  const void* q;  /* [B, HQ, T, DK] */
+  const void* k;  /* [B, HK, T, DK] */
+  const void* v;  /* [B, H, T, DV]  */
+  const float* a; /* [B, H, T]      */
+  void* o;        /* [B, H, T, DV]  */
+  int32_t B, H, HQ, HK, T;
+  uint32_t* status;
+} AeLinearParams;
+
+int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream);
+
 /* ---- bring-up probe (tests only): one 128x128x128 tcgen05 GEMM -------------------
  * mode 0: d = a * b^T (a, b [128,128] 16-bit row-major);
  * mode 1: d = p * b   (p, b [128,128] 16-bit row-major). d is [128,128] fp32.

@@ -15,6 +15,7 @@ mask front end imported from ``<ref>/attention_engine``:
 * MLA decode         ``ref_program``                   core/template/tl_template/attn/mla_decode_tl.py
 * block masks        create_block_mask, is_causal_mask, is_less_causal_mask   core/transform/core.py
 * symbolic autodiff  SymbolScalar.backward on the example score_mods          core/transform/core.py
+* linear scan        fla.ops.simple_gla.naive (the library the reference checks simple_gla against, bench_utils.py:552-566)
 
 Inputs are seeded; inputs and outputs are stored together so the fixtures do not depend on the
 random-number generator of the machine that reads them.
@@ -143,6 +144,17 @@ def main(ref_root: str):
             out[f"{nm}.{bm}x{bn}.is_causal"] = np.array(bool(rcore.is_causal_mask(bmask, bm, bn)))
             out[f"{nm}.{bm}x{bn}.is_less_causal"] = np.array(bool(rcore.is_less_causal_mask(bmask, bm, bn)))
     np.savez_compressed(os.path.join(HERE, "block_masks.npz"), **out)
+
+    # ---------------- linear scan: flash-linear-attention's naive recurrent form (the reference's checker library) --
+    from fla.ops.simple_gla.naive import naive_recurrent_simple_gla
+    g = torch.Generator().manual_seed(5)
+    B, H, T, DK, DV = 1, 2, 320, 128, 64
+    q, k, v = randn(g, B, H, T, DK, dtype=torch.bfloat16), randn(g, B, H, T, DK, dtype=torch.bfloat16), randn(g, B, H, T, DV, dtype=torch.bfloat16)
+    a = -torch.nn.functional.softplus(torch.randn(B, H, T, generator=g) - 2.0)
+    o, _ = naive_recurrent_simple_gla(q.float().transpose(1, 2), k.float().transpose(1, 2), v.float().transpose(1, 2),
+                                      a.transpose(1, 2), scale=1.0)
+    np.savez_compressed(os.path.join(HERE, "linear_scan.npz"), q=q.float().numpy(), k=k.float().numpy(),
+                        v=v.float().numpy(), a=a.numpy(), o=o.transpose(1, 2).float().numpy())
 
     from oracle.ir_eval import evaluate
     g = torch.Generator().manual_seed(4)

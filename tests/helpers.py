@@ -135,3 +135,30 @@ def mla_engine(B, H, S, dtype, scale):
            meta_tensor(B, 1, S, 512, dtype=dtype))
     return AttentionEngine(qkv, CustomIO({}), score_mod=score_mod, mask_mod=None, online_func=OnlineSoftmaxSplit(),
                            kv_shared=True)
+
+
+def mamba2_engine(B, H, T, DK, DV, dtype):
+    """attn_script/mamba2_ngroup1.py:26-63: decay_mod = decay * A, v_mod = v * dt, one q / k head (ngroups = 1)."""
+    from attentionengine_b200 import LinearAttentionEngine
+
+    def decay_mod(decay, custom_io):
+        return decay * custom_io.input_tensors["A"]
+
+    def v_mod(v, custom_io):
+        return v * custom_io.input_tensors["dt"]
+
+    metas_ = (meta_tensor(B, 1, T, DK, dtype=dtype), meta_tensor(B, 1, T, DK, dtype=dtype), meta_tensor(B, H, T, DV, dtype=dtype))
+    return LinearAttentionEngine(metas_, decay_mod=decay_mod, v_mod=v_mod,
+                                 custom_io=CustomIO({"A": (1, "heads"), "dt": ("batch", "heads", "seq_len")}))
+
+
+def mamba2_inputs(B, H, T, DK, DV, dtype, seed=0):
+    """The benchmark's distributions: x, B, C ~ N(0,1); dt = softplus(N(0,1) - 4); A = -exp(U(ln 1, ln 16))."""
+    import math
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, H, T, DV, generator=g).to(dtype)
+    Bm = torch.randn(B, 1, T, DK, generator=g).to(dtype)
+    Cm = torch.randn(B, 1, T, DK, generator=g).to(dtype)
+    dt = torch.nn.functional.softplus(torch.randn(B, H, T, generator=g) - 4.0)
+    A = -torch.exp(torch.rand(H, generator=g) * math.log(16.0))
+    return x, dt, A, Bm, Cm

@@ -128,3 +128,10 @@ def test_create_mask_dense_matches_blockwise():
     m = ae.core.create_mask(lambda b, h, q, kv: q >= kv, 1, 2, 200, 300, "cpu")
     assert m.shape == (1, 2, 200, 300)
     assert torch.equal(m[0, 0], torch.ones(200, 300, dtype=torch.bool).tril())
+
+
+def test_linear_scan_oracle_matches_fla_naive(golden_dir):
+    from oracle.linear_oracle import linear_scan
+    z = np.load(os.path.join(golden_dir, "linear_scan.npz"))
+    o = linear_scan(_t(z["q"]), _t(z["k"]), _t(z["v"]), _t(z["a"]))
+    torch.testing.assert_close(o.float(), _t(z["o"]), rtol=1e-4, atol=1e-4)
