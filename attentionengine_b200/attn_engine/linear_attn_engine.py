@@ -6,8 +6,8 @@ Same constructor and call as the reference (attention_engine/attn_engine/linear_
 
 As in the reference (core/template/tl_template/linear/linear_tl.py:1136-1144) the mods are traced once and
 run as eager PyTorch on the inputs; the scan itself (chunk cumulative sum, state recurrence, intra-chunk
-products) is one sm_100a kernel (csrc/kernels/linear_fwd.cuh).  Backward of the scan is not built yet:
-calling ``.backward()`` through the scan raises.
+products) is one sm_100a kernel (csrc/kernels/linear_fwd.cuh); its backward is a state-recompute pass
+(linear_states.cuh) and a reverse pass (linear_bwd.cuh), built for DV = 64.
 """
 from __future__ import annotations
 
@@ -36,13 +36,21 @@ def _align(t: torch.Tensor, names: tuple, ndim: int) -> torch.Tensor:
 
 
 class _Scan(torch.autograd.Function):
+    """The scan on the mod-ed tensors; gradients flow on into the eager mods through torch autograd
+    (the reference chains the traced mod derivatives by hand, linear_tl.py:1203-1214)."""
+
     @staticmethod
     def forward(ctx, eng, q, k, v, a):
+        q, k, v, a = q.contiguous(), k.contiguous(), v.contiguous(), a.float().contiguous()
+        ctx.eng = eng
+        ctx.save_for_backward(q, k, v, a)
         return eng._launch(q, k, v, a)
 
     @staticmethod
     def backward(ctx, d_o):
-        raise NotImplementedError("backward of the chunked linear-attention scan is not built yet")
+        q, k, v, a = ctx.saved_tensors
+        dq, dk, dv, da = ctx.eng._launch_bwd(q, k, v, a, d_o.contiguous())
+        return None, dq, dk, dv, da
 
 
 class LinearAttentionEngine:
@@ -74,6 +82,53 @@ class LinearAttentionEngine:
         self.tl_code = rt.kernel_source("linear_fwd.cuh", prelude=prelude)
         self.fwd = rt.compile_module(self.tl_code, "ae_linear_fwd", cfg)
         self._status = None
+        self._bwd = None
+        self._stages = stages
+        self._bf16 = bf16
+
+    def _bwd_kernels(self):
+        if self._bwd is None:
+            if self.DV != 64:
+                raise NotImplementedError("backward of the linear-attention scan is built for DV = 64")
+            tag = rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16
+            pre = f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {self.DV}\n#define AE_LIN_STAGES 2\n"
+            smem_s = 2 * (128 * 128 * 2 + 128 * self.DV * 2) + 128 * self.DV * 2 + 1024 + 256 + 1024
+            cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_STATES, dtype=tag, head_dim=128, head_dim_v=self.DV, threads=192,
+                                  smem_bytes=smem_s, stages=2, mask_mode=0)
+            states = rt.compile_module(rt.kernel_source("linear_states.cuh", prelude=pre), "ae_linear_states", cfg)
+            smem_b = (2 * 128 * 128 * 2 + 2 * 128 * self.DV * 2 + 128 * self.DV * 2 + 2 * 128 * 128 * 2
+                      + 128 * self.DV * 2 + 128 * self.DV * 2 + 1024 + 256 + 1024)
+            cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_BWD, dtype=tag, head_dim=128, head_dim_v=self.DV, threads=192,
+                                  smem_bytes=smem_b, stages=1, mask_mode=0)
+            bwd = rt.compile_module(rt.kernel_source("linear_bwd.cuh", prelude=pre), "ae_linear_bwd", cfg)
+            self._bwd = (states, bwd)
+        return self._bwd
+
+    def _launch_bwd(self, q, k, v, a, d_o):
+        states, bwd = self._bwd_kernels()
+        B, HQ, T, DK = q.shape
+        HK = k.shape[1]
+        H, DV = v.shape[1], v.shape[3]
+        dev = q.device
+        nc = -(-T // 128)
+        hs = torch.empty(B, H, nc, DK, DV, dtype=self.dtype, device=dev)
+        dq_h = torch.empty(B, H, T, DK, dtype=self.dtype, device=dev)
+        dk_h = torch.empty(B, H, T, DK, dtype=self.dtype, device=dev)
+        dv = torch.empty(B, H, T, DV, dtype=self.dtype, device=dev)
+        da = torch.empty(B, H, T, dtype=torch.float32, device=dev)
+        p = rt.LinearBwdParams()
+        p.q, p.k, p.v, p.a, p.d_o = q.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), d_o.data_ptr()
+        p.h_states, p.dq, p.dk, p.dv, p.da = hs.data_ptr(), dq_h.data_ptr(), dk_h.data_ptr(), dv.data_ptr(), da.data_ptr()
+        p.B, p.H, p.HQ, p.HK, p.T = B, H, HQ, HK, T
+        if self._status is None or self._status.device != dev:
+            self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        p.status = self._status.data_ptr()
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        rt.check(rt.lib().ae_launch_linear_states(states.handle, C.byref(p), stream), "ae_launch_linear_states")
+        rt.check(rt.lib().ae_launch_linear_bwd(bwd.handle, C.byref(p), stream), "ae_launch_linear_bwd")
+        dq = dq_h if HQ == H else dq_h.view(B, HQ, H // HQ, T, DK).sum(2, dtype=torch.float32).to(self.dtype)
+        dk = dk_h if HK == H else dk_h.view(B, HK, H // HK, T, DK).sum(2, dtype=torch.float32).to(self.dtype)
+        return dq, dk, dv, da
 
     def _apply_mod(self, name, x, custom):
         if name not in self._traced:

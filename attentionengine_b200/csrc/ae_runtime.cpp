@@ -651,4 +651,65 @@ int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream) {
   return launch(m, (unsigned)p->H, (unsigned)p->B, 1, &a, stream);
 }
 
+static int fill_linear_bwd(Module* m, const AeLinearBwdParams* p, AeLinearBwdArgs* a, int kind) {
+  if (m->cfg.kind != kind) {
+    set_error("module kind does not match the entry point");
+    return AE_ERR_UNSUPPORTED;
+  }
+  const int DV = m->cfg.head_dim_v;
+  if (p->B <= 0 || p->H <= 0 || p->HQ <= 0 || p->HK <= 0 || p->T <= 0 || p->H % p->HQ || p->H % p->HK ||
+      m->cfg.head_dim != 128 || (DV != 64 && DV != 128)) {
+    set_error("linear attention: need H % HQ == 0, H % HK == 0, DK = 128, DV in {64, 128}");
+    return AE_ERR_INVALID;
+  }
+  int rc = ensure_loaded(m);
+  if (rc) return rc;
+  memset(a, 0, sizeof *a);
+  const int64_t nc = (p->T + 127) / 128;
+  if ((rc = make_bhtd_map(&a->tm_k, p->k, m->cfg.dtype, p->B, p->HK, p->T, 128, 128))) return rc;
+  if ((rc = make_bhtd_map(&a->tm_v, p->v, m->cfg.dtype, p->B, p->H, p->T, DV, 128))) return rc;
+  if (kind == AE_KIND_LINEAR_BWD) {
+    if ((rc = make_bhtd_map(&a->tm_q, p->q, m->cfg.dtype, p->B, p->HQ, p->T, 128, 128))) return rc;
+    if ((rc = make_bhtd_map(&a->tm_do, p->d_o, m->cfg.dtype, p->B, p->H, p->T, DV, 128))) return rc;
+    if ((rc = make_3d_map(&a->tm_h, p->h_states, m->cfg.dtype, DV, 128, (int64_t)p->B * p->H * nc, 128))) return rc;
+  }
+  a->a = p->a;
+  a->h_states = p->h_states;
+  a->dq = p->dq; a->dk = p->dk; a->dv = p->dv; a->da = p->da;
+  a->B = p->B; a->H = p->H; a->HQ = p->HQ; a->HK = p->HK; a->T = p->T;
+  a->status = p->status;
+  return AE_OK;
+}
+
+int ae_launch_linear_states(void* module, const AeLinearBwdParams* p, void* stream) {
+  if (!module || !p || !p->k || !p->v || !p->a || !p->h_states) return AE_ERR_INVALID;
+  if (reinterpret_cast<uintptr_t>(p->h_states) & 15) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  AeLinearBwdArgs a;
+  int rc = fill_linear_bwd(m, p, &a, AE_KIND_LINEAR_STATES);
+  if (rc) return rc;
+  return launch(m, (unsigned)p->H, (unsigned)p->B, 1, &a, stream);
+}
+
+int ae_launch_linear_bwd(void* module, const AeLinearBwdParams* p, void* stream) {
+  if (!module || !p || !p->q || !p->k || !p->v || !p->a || !p->d_o || !p->h_states || !p->dq || !p->dk || !p->dv ||
+      !p->da)
+    return AE_ERR_INVALID;
+  const void* al[4] = {p->dq, p->dk, p->dv, p->h_states};
+  for (const void* x : al)
+    if (reinterpret_cast<uintptr_t>(x) & 15) {
+      set_error("linear attention backward: buffers must be 16-byte aligned");
+      return AE_ERR_INVALID;
+    }
+  Module* m = (Module*)module;
+  if (m->cfg.head_dim_v != 64) {
+    set_error("linear attention backward is built for DV = 64");
+    return AE_ERR_INVALID;
+  }
+  AeLinearBwdArgs a;
+  int rc = fill_linear_bwd(m, p, &a, AE_KIND_LINEAR_BWD);
+  if (rc) return rc;
+  return launch(m, (unsigned)p->H, (unsigned)p->B, 1, &a, stream);
+}
+
 }  // extern "C"

@@ -110,6 +110,23 @@ struct AeLinearArgs {
   u32* status;
 };
 
+// ---- chunked linear attention backward (kernels ae_linear_states, ae_linear_bwd) ---------
+struct AeLinearBwdArgs {
+  AeTmaDesc tm_q;   // [B, HQ, T, DK]
+  AeTmaDesc tm_k;   // [B, HK, T, DK]
+  AeTmaDesc tm_v;   // [B, H, T, DV]
+  AeTmaDesc tm_do;  // [B, H, T, DV]
+  AeTmaDesc tm_h;   // chunk start-states [B * H * n_chunks, DK, DV] 16-bit, dims (dv, dk, n), box {64, 128, 1}
+  const float* a;   // [B, H, T]
+  void* h_states;   // written by ae_linear_states, read (through tm_h) by ae_linear_bwd
+  void* dq;         // [B, H, T, DK] 16-bit, per head
+  void* dk;         // [B, H, T, DK] 16-bit, per head
+  void* dv;         // [B, H, T, DV] 16-bit
+  float* da;        // [B, H, T] fp32
+  int B, H, HQ, HK, T;
+  u32* status;
+};
+
 // ---- UMMA / TMA probe kernels (bring-up checks, kernel ae_probe) -------------------
 struct AeProbeArgs {
   AeTmaDesc tm_a;  // [128 rows, KD] 16-bit, box {64, 128}

@@ -376,3 +376,18 @@ AE_DEVICE void tmem_ld_2xf32x32(u32 taddr_a, u32 taddr_b, float (&a)[32], float 
       : "r"(taddr_a), "r"(taddr_b)
       : "memory");
 }
+
+// UMMA operand descriptors over tiles stored as 64-element-wide column blocks of [rows][128 B] with the
+// 128-byte swizzle (what a TMA box {64, rows} produces, and what the row threads write with swz128()).
+//   umma_desc_k : the contraction dim is the contiguous one (K-major); k-step kk covers 16 elements.
+//   umma_desc_mn: the contraction dim is the row index (MN-major); k-step kk covers 16 rows.
+AE_DEVICE u64 umma_desc_k(u32 base, int kk, int rows) {
+  return umma_smem_desc_sw128(base + (kk >> 2) * (rows * 128) + (kk & 3) * 32, 16, 1024);
+}
+AE_DEVICE u64 umma_desc_mn(u32 base, int kk, int rows) {
+  return umma_smem_desc_sw128(base + kk * 2048, rows * 128, 1024);
+}
+// byte offset of the 16-byte chunk `ch` of row `r` inside a [rows][128 B] swizzled block
+AE_DEVICE u32 swz128(u32 r, u32 ch) { return r * 128 + ((ch ^ (r & 7)) << 4); }
+// byte offset of element column `col` (multiple of 8) of row `r` in a tile of 64-wide blocks of `rows` rows
+AE_DEVICE u32 tile_off(u32 r, u32 col, u32 rows) { return (col >> 6) * (rows * 128) + swz128(r, (col & 63) >> 3); }

@@ -1,0 +1,386 @@
+// Chunked linear-attention / SSD scan, backward, for sm_100a.  Replaces the reference's
+// `chunk_bwd_kernel_dh`, `chunk_bwd_dqkg`, `chunk_bwd_kernel_dv` and `compute_final_dg` kernels
+// (attention_engine/core/template/tl_template/linear/linear_tl.py:447-545, 584-788, 827-930, 52-65).
+//
+// One CTA owns one (batch, head) and walks its 128-step chunks from the last to the first, carrying
+// dH, the gradient with respect to the state, as an fp32 TMEM accumulator.  With g the inclusive
+// cumulative log-decay inside the chunk, E_ij = exp(g_i - g_j) [i >= j], w_j = exp(g_last - g_j),
+// h the chunk's incoming state (recomputed by linear_states.cuh) and dH' the gradient of its outgoing state:
+//     A  = q k^T          dPr = dO v^T                          (SS MMAs into R0, R1)
+//     row threads: P = E o A, dS = E o dPr  -> 16-bit tiles in shared memory
+//     dq_i = exp(g_i) (dO h^T)_i + (dS k)_i                      (R0: inter MMA, row scaling, intra MMA on top)
+//     dk_j = w_j (v dH'^T)_j + (dS^T q)_j                        (R1, same scheme)
+//     dv_j = w_j (k dH')_j + (P^T dO)_j
+//     dH   = exp(g_last) dH' + q^T (dO o exp(g))
+//     d a_t = sum over s >= t of (q_s . dq_s - k_s . dk_s)       (suffix sum carried across chunks)
+// dq / dk are written per head; the caller sums them over a head group when q / k have fewer heads.
+// All transposed products read the same 16-bit tiles through MN-major descriptors: nothing is transposed in
+// registers.  Roles: warps 0-3 row threads (thread r = step r = state row r), warp 4 TMA, warp 5 MMA.
+// Expects AE_BF16, AE_LIN_DV (64).
+
+#define AE_LB_C 128
+#define AE_LB_DK 128
+#define AE_LB_QK_BYTES (AE_LB_C * AE_LB_DK * 2)
+#define AE_LB_V_BYTES (AE_LB_C * AE_LIN_DV * 2)
+#define AE_LB_H_BYTES (AE_LB_DK * AE_LIN_DV * 2)
+#define AE_LB_PP_BYTES (AE_LB_C * AE_LB_C * 2)
+#define AE_LB_SMEM_Q 0
+#define AE_LB_SMEM_K (AE_LB_SMEM_Q + AE_LB_QK_BYTES)
+#define AE_LB_SMEM_V (AE_LB_SMEM_K + AE_LB_QK_BYTES)
+#define AE_LB_SMEM_DO (AE_LB_SMEM_V + AE_LB_V_BYTES)
+#define AE_LB_SMEM_HC (AE_LB_SMEM_DO + AE_LB_V_BYTES)
+#define AE_LB_SMEM_P (AE_LB_SMEM_HC + AE_LB_H_BYTES)
+#define AE_LB_SMEM_DS (AE_LB_SMEM_P + AE_LB_PP_BYTES)
+#define AE_LB_SMEM_DHB (AE_LB_SMEM_DS + AE_LB_PP_BYTES)
+#define AE_LB_SMEM_DO2 (AE_LB_SMEM_DHB + AE_LB_H_BYTES)
+#define AE_LB_SMEM_G (AE_LB_SMEM_DO2 + AE_LB_V_BYTES)
+#define AE_LB_SMEM_BAR (AE_LB_SMEM_G + 1024)
+#define AE_LB_LOAD_BYTES (2 * AE_LB_QK_BYTES + 2 * AE_LB_V_BYTES + AE_LB_H_BYTES)
+
+struct AeLbBars {
+  u64 full;
+  u64 empty;
+  u64 s_full;
+  u64 prep_done;
+  u64 pds_full;
+  u64 inter_full;
+  u64 scaled_done;
+  u64 out_full;
+  AeCtaCtl ctl;
+};
+
+extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_constant__ AeLinearBwdArgs args) {
+  extern __shared__ u8 smem_raw[];
+  u8* smem = smem_align1024(smem_raw);
+  AeLbBars* bars = (AeLbBars*)(smem + AE_LB_SMEM_BAR);
+  float* gs = (float*)(smem + AE_LB_SMEM_G);  // [0..127] g of the chunk, [128..131] warp totals, [132..135] warp sums of dG
+  AeCtaCtl* ctl = &bars->ctl;
+  const u32 warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int hq = h / (args.H / args.HQ);
+  const int hk = h / (args.H / args.HK);
+  const int n_chunks = (args.T + AE_LB_C - 1) / AE_LB_C;
+
+  if (threadIdx.x == 0) {
+    ctl->abort = 0;
+    mbar_init(&bars->full, 1);
+    mbar_init(&bars->empty, 128);
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->prep_done, 128);
+    mbar_init(&bars->pds_full, 128);
+    mbar_init(&bars->inter_full, 1);
+    mbar_init(&bars->scaled_done, 128);
+    mbar_init(&bars->out_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&ctl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const u32 tmem = ctl->tmem_base;
+  const u32 TM_R0 = 0, TM_R1 = 128, TM_DV = 256, TM_DH = 256 + AE_LIN_DV;
+
+  if (warp == 4) {
+    // =============================== TMA producer ===============================
+    if (lane == 0) {
+      tma_prefetch_desc(&args.tm_q);
+      tma_prefetch_desc(&args.tm_k);
+      tma_prefetch_desc(&args.tm_v);
+      tma_prefetch_desc(&args.tm_do);
+      tma_prefetch_desc(&args.tm_h);
+      for (int it = 0; it < n_chunks; ++it) {
+        const int c = n_chunks - 1 - it;
+        if (!mbar_wait(&bars->empty, (it & 1) ^ 1, ctl, args.status, 71)) break;
+        mbar_arrive_expect_tx(&bars->full, AE_LB_LOAD_BYTES);
+        for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
+          tma_load_4d(smem + AE_LB_SMEM_Q + dh * (AE_LB_C * 128), &args.tm_q, &bars->full, dh * 64, c * AE_LB_C, hq, b);
+          tma_load_4d(smem + AE_LB_SMEM_K + dh * (AE_LB_C * 128), &args.tm_k, &bars->full, dh * 64, c * AE_LB_C, hk, b);
+        }
+        for (int dh = 0; dh < AE_LIN_DV / 64; ++dh) {
+          tma_load_4d(smem + AE_LB_SMEM_V + dh * (AE_LB_C * 128), &args.tm_v, &bars->full, dh * 64, c * AE_LB_C, h, b);
+          tma_load_4d(smem + AE_LB_SMEM_DO + dh * (AE_LB_C * 128), &args.tm_do, &bars->full, dh * 64, c * AE_LB_C, h, b);
+          tma_load_3d(smem + AE_LB_SMEM_HC + dh * (AE_LB_DK * 128), &args.tm_h, &bars->full, dh * 64, 0,
+                      (b * args.H + h) * n_chunks + c);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // =============================== MMA issuer =================================
+    if (lane == 0) {
+      const u32 Q = smem_u32(smem + AE_LB_SMEM_Q), K = smem_u32(smem + AE_LB_SMEM_K), V = smem_u32(smem + AE_LB_SMEM_V);
+      const u32 DO = smem_u32(smem + AE_LB_SMEM_DO), HC = smem_u32(smem + AE_LB_SMEM_HC);
+      const u32 P = smem_u32(smem + AE_LB_SMEM_P), DS = smem_u32(smem + AE_LB_SMEM_DS);
+      const u32 DHB = smem_u32(smem + AE_LB_SMEM_DHB), DO2 = smem_u32(smem + AE_LB_SMEM_DO2);
+      const u32 id_kk_128 = umma_idesc_f16(128, 128, AE_BF16, 0, 0);
+      const u32 id_kmn_dv = umma_idesc_f16(128, AE_LIN_DV, AE_BF16, 0, 1);
+      const u32 id_mnmn_dv = umma_idesc_f16(128, AE_LIN_DV, AE_BF16, 1, 1);
+      const u32 id_kmn_128 = umma_idesc_f16(128, 128, AE_BF16, 0, 1);
+      const u32 id_mnmn_128 = umma_idesc_f16(128, 128, AE_BF16, 1, 1);
+      bool ok = true;
+      for (int it = 0; it < n_chunks && ok; ++it) {
+        const u32 par = it & 1;
+        ok = mbar_wait(&bars->full, par, ctl, args.status, 72);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // A = q k^T -> R0 ; dPr = dO v^T -> R1
+#pragma unroll
+        for (int kk = 0; kk < AE_LB_DK / 16; ++kk)
+          umma_ss(tmem + TM_R0, umma_desc_k(Q, kk, 128), umma_desc_k(K, kk, 128), id_kk_128, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
+          umma_ss(tmem + TM_R1, umma_desc_k(DO, kk, 128), umma_desc_k(V, kk, 128), id_kk_128, kk > 0);
+        umma_commit(&bars->s_full);
+        ok = mbar_wait(&bars->prep_done, par, ctl, args.status, 73);
+        if (!ok) break;
+        ok = mbar_wait(&bars->pds_full, par, ctl, args.status, 74);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // inter-chunk parts (overwrite R0, R1, DV)
+#pragma unroll
+        for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
+          umma_ss(tmem + TM_R0, umma_desc_k(DO, kk, 128), umma_desc_k(HC, kk, 128), id_kk_128, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
+          umma_ss(tmem + TM_R1, umma_desc_k(V, kk, 128), umma_desc_k(DHB, kk, 128), id_kk_128, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < AE_LB_DK / 16; ++kk)
+          umma_ss(tmem + TM_DV, umma_desc_k(K, kk, 128), umma_desc_mn(DHB, kk, 128), id_kmn_dv, kk > 0);
+        umma_commit(&bars->inter_full);
+        // dH (+)= q^T (dO o exp(g))
+#pragma unroll
+        for (int kk = 0; kk < AE_LB_C / 16; ++kk)
+          umma_ss(tmem + TM_DH, umma_desc_mn(Q, kk, 128), umma_desc_mn(DO2, kk, 128), id_mnmn_dv, (it > 0) | (kk > 0));
+        ok = mbar_wait(&bars->scaled_done, par, ctl, args.status, 75);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // intra-chunk parts on top
+#pragma unroll
+        for (int kk = 0; kk < AE_LB_C / 16; ++kk)
+          umma_ss(tmem + TM_R0, umma_desc_k(DS, kk, 128), umma_desc_mn(K, kk, 128), id_kmn_128, 1);
+#pragma unroll
+        for (int kk = 0; kk < AE_LB_C / 16; ++kk)
+          umma_ss(tmem + TM_R1, umma_desc_mn(DS, kk, 128), umma_desc_mn(Q, kk, 128), id_mnmn_128, 1);
+#pragma unroll
+        for (int kk = 0; kk < AE_LB_C / 16; ++kk)
+          umma_ss(tmem + TM_DV, umma_desc_mn(P, kk, 128), umma_desc_mn(DO, kk, 128), id_mnmn_dv, 1);
+        umma_commit(&bars->out_full);
+      }
+    }
+  } else {
+    // =============================== row threads ================================
+    const u32 r = threadIdx.x & 127;
+    const u32 lane_base = ((warp & 3) * 32) << 16;
+    const i64 bh = (i64)b * args.H + h;
+    const float* a_row = args.a + bh * args.T;
+    float carry = 0.f;  // sum of dG over all later chunks
+    bool ok = true;
+    for (int it = 0; it < n_chunks; ++it) {
+      const int c = n_chunks - 1 - it;
+      const u32 par = it & 1;
+      const int t = c * AE_LB_C + (int)r;
+      const bool row_ok = t < args.T;
+      // ---- A: cumulative log-decay of the chunk -------------------------------------------------
+      float g = row_ok ? a_row[t] : 0.f;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float n = __shfl_up_sync(0xffffffffu, g, o);
+        if (lane >= (u32)o) g += n;
+      }
+      if (lane == 31) gs[128 + (warp & 3)] = g;
+      named_bar_sync(1, 128);
+      {
+        float pre = 0.f;
+#pragma unroll
+        for (int w = 0; w < 3; ++w)
+          if ((u32)w < (warp & 3)) pre += gs[128 + w];
+        g += pre;
+      }
+      gs[r] = g;
+      named_bar_sync(1, 128);
+      const float g_last = gs[AE_LB_C - 1];
+      const float eg = ae_exp(g), wj = ae_exp(g_last - g);
+      // ---- B: dH' -> 16-bit copy, then decay dH in place ------------------------------------------
+      {
+        u8* dhb = smem + AE_LB_SMEM_DHB;
+        if (it > 0) {
+          const float dec = ae_exp(g_last);
+#pragma unroll
+          for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+            float f[32];
+            u32 w[32];
+            tmem_ld_f32x32(tmem + TM_DH + lane_base + cc * 32, f);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 pk;
+              pk.x = pack2<AE_BF16>(f[i * 8 + 0], f[i * 8 + 1]);
+              pk.y = pack2<AE_BF16>(f[i * 8 + 2], f[i * 8 + 3]);
+              pk.z = pack2<AE_BF16>(f[i * 8 + 4], f[i * 8 + 5]);
+              pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
+              *(uint4*)(dhb + tile_off(r, cc * 32 + i * 8, AE_LB_DK)) = pk;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(f[i] * dec);
+            tmem_st32(tmem + TM_DH + lane_base + cc * 32, w);
+          }
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < AE_LIN_DV / 8; ++ch) *(uint4*)(dhb + tile_off(r, ch * 8, AE_LB_DK)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      // ---- C: dO2 = dO * exp(g) -----------------------------------------------------------------------
+      ok = ok && mbar_wait(&bars->full, par, ctl, args.status, 76);
+      {
+        const u8* dsrc = smem + AE_LB_SMEM_DO;
+        u8* d2 = smem + AE_LB_SMEM_DO2;
+#pragma unroll
+        for (int ch = 0; ch < AE_LIN_DV / 8; ++ch) {
+          const u32 off = tile_off(r, ch * 8, AE_LB_C);
+          uint4 x = *(const uint4*)(dsrc + off);
+          u32* xw = (u32*)&x;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            xw[i] = pack2<AE_BF16>(unpack_lo<AE_BF16>(xw[i]) * eg, unpack_hi<AE_BF16>(xw[i]) * eg);
+          *(uint4*)(d2 + off) = x;
+        }
+      }
+      tc_wait_st();
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->prep_done);
+      // ---- D: P = E o A, dS = E o dPr -> shared memory ------------------------------------------------
+      ok = ok && mbar_wait(&bars->s_full, par, ctl, args.status, 77);
+      tc_fence_after_sync();
+      {
+        u8* pt = smem + AE_LB_SMEM_P;
+        u8* dst = smem + AE_LB_SMEM_DS;
+#pragma unroll
+        for (int cc = 0; cc < AE_LB_C / 32; ++cc) {
+          float av[32], dv[32];
+          tmem_ld_2xf32x32(tmem + TM_R0 + lane_base + cc * 32, tmem + TM_R1 + lane_base + cc * 32, av, dv);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            u32 pw[4], dw[4];
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+              const int j0 = cc * 32 + i * 8 + e2 * 2;
+              const float2 gj = *(const float2*)(gs + j0);
+              const float e0 = ((u32)j0 <= r) ? ae_exp(g - gj.x) : 0.f;
+              const float e1 = ((u32)(j0 + 1) <= r) ? ae_exp(g - gj.y) : 0.f;
+              pw[e2] = pack2<AE_BF16>(av[i * 8 + e2 * 2] * e0, av[i * 8 + e2 * 2 + 1] * e1);
+              dw[e2] = pack2<AE_BF16>(dv[i * 8 + e2 * 2] * e0, dv[i * 8 + e2 * 2 + 1] * e1);
+            }
+            const u32 off = tile_off(r, cc * 32 + i * 8, AE_LB_C);
+            *(uint4*)(pt + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+            *(uint4*)(dst + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->pds_full);
+      // ---- E: row scaling of the inter-chunk parts ------------------------------------------------------
+      ok = ok && mbar_wait(&bars->inter_full, par, ctl, args.status, 78);
+      tc_fence_after_sync();
+#pragma unroll
+      for (int which = 0; which < 3; ++which) {
+        const u32 base = tmem + lane_base + (which == 0 ? TM_R0 : (which == 1 ? TM_R1 : TM_DV));
+        const int ncol = which == 2 ? AE_LIN_DV : 128;
+        const float sc = which == 0 ? eg : wj;
+#pragma unroll
+        for (int cc = 0; cc < ncol / 32; ++cc) {
+          float f[32];
+          u32 w[32];
+          tmem_ld_f32x32(base + cc * 32, f);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(f[i] * sc);
+          tmem_st32(base + cc * 32, w);
+        }
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->scaled_done);
+      // ---- F: outputs -------------------------------------------------------------------------------------
+      ok = ok && mbar_wait(&bars->out_full, par, ctl, args.status, 79);
+      tc_fence_after_sync();
+      float dg = 0.f;
+      {
+        const bool store = ok && row_ok;
+        const i64 trow = bh * args.T + (store ? t : 0);
+        u16* dq_row = (u16*)args.dq + trow * AE_LB_DK;
+        u16* dk_row = (u16*)args.dk + trow * AE_LB_DK;
+        u16* dv_row = (u16*)args.dv + trow * AE_LIN_DV;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const u8* src = smem + (which == 0 ? AE_LB_SMEM_Q : AE_LB_SMEM_K);
+          u16* orow = which == 0 ? dq_row : dk_row;
+          float dot = 0.f;
+#pragma unroll
+          for (int cc = 0; cc < AE_LB_DK / 32; ++cc) {
+            float f[32];
+            tmem_ld_f32x32(tmem + (which == 0 ? TM_R0 : TM_R1) + lane_base + cc * 32, f);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 x = *(const uint4*)(src + tile_off(r, cc * 32 + i * 8, AE_LB_C));
+              const u32 xw[4] = {x.x, x.y, x.z, x.w};
+              uint4 pk;
+              u32* pw = (u32*)&pk;
+#pragma unroll
+              for (int e2 = 0; e2 < 4; ++e2) {
+                dot += unpack_lo<AE_BF16>(xw[e2]) * f[i * 8 + e2 * 2] + unpack_hi<AE_BF16>(xw[e2]) * f[i * 8 + e2 * 2 + 1];
+                pw[e2] = pack2<AE_BF16>(f[i * 8 + e2 * 2], f[i * 8 + e2 * 2 + 1]);
+              }
+              if (store) *(uint4*)(orow + cc * 32 + i * 8) = pk;
+            }
+          }
+          dg += which == 0 ? dot : -dot;
+        }
+#pragma unroll
+        for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+          float f[32];
+          tmem_ld_f32x32(tmem + TM_DV + lane_base + cc * 32, f);
+          if (store) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 pk;
+              pk.x = pack2<AE_BF16>(f[i * 8 + 0], f[i * 8 + 1]);
+              pk.y = pack2<AE_BF16>(f[i * 8 + 2], f[i * 8 + 3]);
+              pk.z = pack2<AE_BF16>(f[i * 8 + 4], f[i * 8 + 5]);
+              pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
+              *(uint4*)(dv_row + cc * 32 + i * 8) = pk;
+            }
+          }
+        }
+        if (!row_ok) dg = 0.f;
+        // inclusive suffix sum of dG over the chunk, plus everything from later chunks
+        float sfx = dg;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float n = __shfl_down_sync(0xffffffffu, sfx, o);
+          if (lane + (u32)o < 32) sfx += n;
+        }
+        if (lane == 0) gs[132 + (warp & 3)] = sfx;
+        named_bar_sync(1, 128);
+        float after = 0.f, total = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float tw = gs[132 + w];
+          total += tw;
+          if ((u32)w > (warp & 3)) after += tw;
+        }
+        if (store) args.da[bh * args.T + t] = sfx + after + carry;
+        carry += total;
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&bars->empty);  // this chunk's tiles and accumulators are free
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}

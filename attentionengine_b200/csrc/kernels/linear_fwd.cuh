@@ -42,9 +42,6 @@ struct AeLinBars {
   AeCtaCtl ctl;
 };
 
-// 16-byte chunk `ch` of row `r` inside a [rows][128 B] tile with the 128-byte swizzle
-AE_DEVICE u32 swz128(u32 r, u32 ch) { return r * 128 + ((ch ^ (r & 7)) << 4); }
-
 extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_constant__ AeLinearArgs args) {
   extern __shared__ u8 smem_raw[];
   u8* smem = smem_align1024(smem_raw);

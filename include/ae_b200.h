@@ -52,6 +52,7 @@ enum {
   AE_KIND_MLA_COMBINE = 6,
   AE_KIND_LINEAR_FWD = 7,
   AE_KIND_LINEAR_BWD = 8,
+  AE_KIND_LINEAR_STATES = 9,
 };
 
 #define AE_MAX_CUSTOM_INPUTS 4
@@ -212,6 +213,31 @@ typedef struct AeLinearParams {
 } AeLinearParams;
 
 int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream);
+
+/* ---- chunked linear attention / SSD scan, backward -------------------------------------
+ * Stands in for the kernel part of `LinearAttention.backward`
+ * (core/template/tl_template/linear/linear_tl.py:1158-1216): `chunk_fwd_h_mod_2` (state
+ * recompute) = ae_launch_linear_states; `chunk_bwd_dh_mod` + `chunk_bwd_dqkg_mod` +
+ * `chunk_bwd_dv_mod` + `compute_final_dg` = ae_launch_linear_bwd.  Gradients are with respect
+ * to the kernel inputs (after the mods); dq / dk are per head of v and are summed by the
+ * caller when q / k have fewer heads, as the reference does (:1198-1201).  DK = 128, DV = 64. */
+typedef struct AeLinearBwdParams {
+  const void* q;   /* [B, HQ, T, DK] */
+  const void* k;   /* [B, HK, T, DK] */
+  const void* v;   /* [B, H, T, DV]  */
+  const float* a;  /* [B, H, T]      */
+  const void* d_o; /* [B, H, T, DV]  */
+  void* h_states;  /* scratch [B, H, ceil(T/128), DK, DV] 16-bit: chunk start-states */
+  void* dq;        /* [B, H, T, DK] 16-bit */
+  void* dk;        /* [B, H, T, DK] 16-bit */
+  void* dv;        /* [B, H, T, DV] 16-bit */
+  float* da;       /* [B, H, T] fp32 */
+  int32_t B, H, HQ, HK, T;
+  uint32_t* status;
+} AeLinearBwdParams;
+
+int ae_launch_linear_states(void* module, const AeLinearBwdParams* p, void* stream);
+int ae_launch_linear_bwd(void* module, const AeLinearBwdParams* p, void* stream);
 
 /* ---- bring-up probe (tests only): one 128x128x128 tcgen05 GEMM -------------------
  * mode 0: d = a * b^T (a, b [128,128] 16-bit row-major);

@@ -22,11 +22,11 @@ def linear_scan(q, k, v, a, dtype=torch.float64):
     q = q.repeat_interleave(H // q.shape[1], dim=1)
     k = k.repeat_interleave(H // k.shape[1], dim=1)
     S = torch.zeros(B, H, q.shape[-1], DV, dtype=dtype)
-    o = torch.empty(B, H, T, DV, dtype=dtype)
+    outs = []
     for t in range(T):
         S = S * a[:, :, t].exp()[..., None, None] + k[:, :, t, :, None] * v[:, :, t, None, :]
-        o[:, :, t] = torch.einsum("bhk,bhkv->bhv", q[:, :, t], S)
-    return o
+        outs.append(torch.einsum("bhk,bhkv->bhv", q[:, :, t], S))
+    return torch.stack(outs, dim=2)
 
 
 def mamba2_ssd(x, dt, A, Bm, Cm, D_skip=None):

@@ -287,3 +287,31 @@ def test_mamba2_ssd_forward_against_oracle(B, H, T, DV):
     v_mod = (x.float() * dt.to(dt_).float()[..., None]).to(dt_)
     ref = linear_scan(Cm, Bm, v_mod, a)
     _check("ssd.o", o.cpu(), ref.float(), dt_, unnormalised=True)
+
+
+@pytest.mark.parametrize("B,H,T", [(1, 2, 256), (2, 4, 512), (1, 3, 200)])
+def test_mamba2_ssd_backward_against_oracle(B, H, T):
+    """Gradients of the Mamba2 mapping (q = C, k = B, v = x * dt, a = dt * A, one q/k head shared by all heads)
+    against fp64 autograd through the step-by-step recurrence.  bf16 protocol: the tensor-core operands
+    (P, dS, v', the carried states) are rounded to bf16, so rel-L2 <= 1e-2 is asked of the tensor gradients
+    (measured about 3e-3 to 6e-3) and 5e-2 of dA, a sum of B * T cancelling terms per head (measured 1e-2 to 2e-2)."""
+    from oracle.linear_oracle import linear_scan
+    dt_ = torch.bfloat16
+    x, dt, A, Bm, Cm = helpers.mamba2_inputs(B, H, T, 128, 64, dt_, seed=T)
+    g = torch.Generator().manual_seed(7)
+    d_o = (0.1 * torch.randn(B, H, T, 64, generator=g)).to(dt_)
+    eng = helpers.mamba2_engine(B, H, T, 128, 64, dt_)
+    leaves = [t.cuda().requires_grad_() for t in (Cm, Bm, x, dt, A.view(1, H))]
+    dtb = dt.to(dt_).cuda().requires_grad_()
+    o = eng(*leaves, dtb)
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    C2, B2, x2, dt2, A2, dtb2 = [t.detach().double().cpu().requires_grad_() for t in (*leaves, dtb)]
+    oref = linear_scan(C2, B2, x2 * dtb2[..., None], dt2 * A2.view(1, H, 1))
+    oref.backward(d_o.double())
+    names = ("dC", "dB", "dx", "d(dt) via decay", "dA", "d(dt) via v_mod")
+    for name, got, ref in zip(names, [t.grad for t in leaves] + [dtb.grad], [C2.grad, B2.grad, x2.grad, dt2.grad, A2.grad, dtb2.grad]):
+        mx, rel = orc.error_stats(got.float().cpu(), ref.float())
+        lim = 5e-2 if name == "dA" else 1e-2
+        assert rel <= lim, f"{name}: rel-L2 {rel:.3e} (max-abs {mx:.3e})"
