@@ -124,6 +124,130 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def time_events(torch, fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def run_other(args):
+    """The benchmark's other configurations, one JSON line each (single GPU): cfg3 sigmoid / relu attention
+    (B=4, H=32, S=4096, D=128, bf16, non-causal, fwd+bwd), cfg4 Mamba2 SSD (B=8, L=8192, 80 heads, P=64, N=128, bf16,
+    fwd+bwd) and cfg5 MLA decode (B=128, H=128, S=8192, fp16, scale 1/sqrt(192))."""
+    import math
+    import torch
+    import helpers
+    from oracle import attention_oracle as orc
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    peaks, which = read_peaks()
+    wl = args.workload
+    sampler = ClockSampler(0)
+    if wl in ("cfg3_sigmoid", "cfg3_relu"):
+        B, H, S, D, dt = 4, 32, 4096, 128, torch.bfloat16
+        eng = (helpers.sigmoid_engine(B, H, S, D, dt, False) if wl == "cfg3_sigmoid"
+               else helpers.relu_engine(B, H, S, D, dt, False, post_scale=1.0 / S))
+        q, k, v, d_o = (torch.randn(B, S, H, D, device=dev, dtype=dt) for _ in range(4))
+        q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+        custom = (torch.tensor([-math.log(S)], device=dev),) if wl == "cfg3_sigmoid" else ()
+
+        def step():
+            q.grad = k.grad = v.grad = None
+            eng(q, k, v, *custom).backward(d_o)
+        ms = time_events(torch, step, args.steps, args.warmup)
+        eng.check_status()
+        work = 3.5 * 4.0 * B * H * S * S * D
+        value, unit, bound, peak = work / ms / 1e9, "TFLOPS", "tensor", float(peaks.get("bf16_tflops", 1590.0))
+        desc = f"{wl[5:]} attention fwd+bwd, B=4 H=32 S=4096 D=128 bf16 non-causal"
+        launches = 3 * args.steps
+        g = torch.Generator().manual_seed(0)
+        qs, ks, vs, ds = (torch.randn(1, S, 2, D, generator=g).to(dt) for _ in range(4))
+        fn = ((lambda a, b, c: orc.sigmoid_attention(a, b, c, bias=-math.log(S))) if wl == "cfg3_sigmoid"
+              else (lambda a, b, c: orc.relu_attention(a, b, c, post_scale=1.0 / S)))
+        t0 = time.perf_counter()
+        for _ in range(4):
+            orc.fwd_bwd(fn, (qs, ks, vs), ds)
+        tc = time.perf_counter() - t0
+        cpu = {"value": 4 * 3.5 * 4.0 * 2 * S * S * D / tc / 1e12, "unit": "TFLOPS", "cores": os.cpu_count(), "kind": "port",
+               "sample": "4 x (1 batch row, 2 of 32 heads), fwd+bwd, fp32 torch"}
+    elif wl == "cfg4":
+        B, H, T, DK, DV, dt = 8, 80, 8192, 128, 64, torch.bfloat16
+        eng = helpers.mamba2_engine(B, H, T, DK, DV, dt)
+        x = torch.randn(B, H, T, DV, device=dev, dtype=dt, requires_grad=True)
+        Bm = torch.randn(B, 1, T, DK, device=dev, dtype=dt, requires_grad=True)
+        Cm = torch.randn(B, 1, T, DK, device=dev, dtype=dt, requires_grad=True)
+        dts = torch.nn.functional.softplus(torch.randn(B, H, T, device=dev) - 4).requires_grad_()
+        A = (-torch.exp(torch.rand(H, device=dev) * math.log(16.0))).view(1, H).requires_grad_()
+        dtb = dts.detach().to(dt).requires_grad_()
+        d_o = torch.randn(B, H, T, DV, device=dev, dtype=dt)
+        leaves = (x, Bm, Cm, dts, A, dtb)
+
+        def step():
+            for t_ in leaves:
+                t_.grad = None
+            eng(Cm, Bm, x, dts, A, dtb).backward(d_o)
+        ms = time_events(torch, step, args.steps, args.warmup)
+        eng.check_status()
+        Q = 256
+        fwd = (2 * Q * Q * DK + 2 * Q * Q * DV + 4 * Q * DK * DV) * (T // Q) * H * B
+        work = 3.5 * fwd
+        value, unit, bound, peak = work / ms / 1e9, "TFLOPS", "tensor", float(peaks.get("bf16_tflops", 1590.0))
+        desc = ("Mamba2 SSD fwd+bwd (mods as eager torch + scan kernels), B=8 L=8192 H=80 P=64 N=128 ngroups=1 bf16; FLOPs by "
+                "the chunk-256 convention, fwd (2Q^2N+2Q^2P+4QNP) per chunk and head, bwd counted as 2.5x fwd")
+        launches = 3 * args.steps
+        from oracle.linear_oracle import linear_scan
+        xs, dt_s, As, Bs, Cs = helpers.mamba2_inputs(1, 2, 1024, DK, DV, dt, seed=0)
+        t0 = time.perf_counter()
+        l2 = [t_.double().requires_grad_() for t_ in (Cs, Bs, xs * dt_s[..., None].to(dt), dt_s * As.view(1, -1, 1))]
+        linear_scan(*l2).sum().backward()
+        tc = time.perf_counter() - t0
+        f_s = (2 * Q * Q * DK + 2 * Q * Q * DV + 4 * Q * DK * DV) * (1024 // Q) * 2
+        cpu = {"value": 3.5 * f_s / tc / 1e12, "unit": "TFLOPS", "cores": os.cpu_count(), "kind": "port",
+               "sample": "step-by-step recurrence, 1 batch row x 2 heads x 1024 steps, fwd+bwd, fp64 torch"}
+    elif wl == "cfg5":
+        B, H, S, dt = 128, 128, 8192, torch.float16
+        eng = helpers.mla_engine(B, H, S, dt, 1 / math.sqrt(192))
+        q = torch.randn(B, 1, H, 512, device=dev, dtype=dt)
+        q_pe = torch.randn(B, 1, H, 64, device=dev, dtype=dt)
+        kv = torch.randn(B, S, 1, 512, device=dev, dtype=dt)
+        k_pe = torch.randn(B, S, 1, 64, device=dev, dtype=dt)
+        ms = time_events(torch, lambda: eng(q, q_pe, kv, k_pe), args.steps, args.warmup)
+        eng.check_status()
+        work = (B * S * 576 + B * H * 576 + B * H * 512) * 2.0
+        value, unit, bound, peak = work / ms / 1e6, "GB/s", "hbm", float(peaks.get("hbm_gbs", 6650.0))
+        desc = "MLA decode, B=128 H=128 Skv=8192 D=512+64 DV=512 fp16, scale 1/sqrt(192)"
+        launches = (1 if eng._mla.last_num_split == 1 else 2) * args.steps
+        g = torch.Generator().manual_seed(0)
+        qs, ps = torch.randn(4, H, 512, generator=g).to(dt), torch.randn(4, H, 64, generator=g).to(dt)
+        kvs, kps = torch.randn(4, S, 1, 512, generator=g).to(dt), torch.randn(4, S, 1, 64, generator=g).to(dt)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            orc.mla_decode(qs, ps, kvs, kps, scale=1 / math.sqrt(192))
+        tc = time.perf_counter() - t0
+        cpu = {"value": 3 * (4 * S * 576 + 4 * H * 576 + 4 * H * 512) * 2.0 / tc / 1e9, "unit": "GB/s", "cores": os.cpu_count(),
+               "kind": "port", "sample": "3 x 4 of 128 batch rows, fp32 torch"}
+    else:
+        raise SystemExit(f"unknown workload {wl}")
+    clocks = sampler.stop()
+    ach = value / (1e3 if unit == "TFLOPS" and False else 1)
+    line = {"metric": desc, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if "fp16" not in desc else "f16", "data": "synthetic",
+            "config": {"workload": wl, "l2": "inputs larger than L2"}, "clocks": clocks, "e2e": None,
+            "gpu_launches": launches,
+            "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": "TFLOP/s" if unit == "TFLOPS" else "GB/s",
+                         "frac": ach / peak, "peak_source": f"{which}", "traffic": None, "kernel": "whole step"},
+            "cpu_baseline": cpu}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -132,6 +256,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end pass (profiling runs)")
+    ap.add_argument("--workload", default="cfg2", help="cfg2 (the headline, default) | cfg3_sigmoid | cfg3_relu | cfg4 | cfg5")
     ap.add_argument("--batch", type=int, default=CFG["B"], help="batch size; the benchmark's is 8 (smaller for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -141,6 +266,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload != "cfg2":
+        if rank == 0:
+            run_other(args)
         return
 
     import torch
@@ -203,19 +332,43 @@ def main():
     value = world * fl_step / (ms / 1e3) / 1e12
 
     # ---- end to end: host buffers in, host buffers out, through the public operator call ----------
+    # One operator call per batch row; the row's H2D copies, its forward + backward and its D2H copies run on
+    # three streams, so copies of neighbouring rows overlap the kernels (PCIe moves 1.34 GB each way per step).
     out_host = {n: torch.empty_like(host[n]).pin_memory() for n in ("q", "k", "v", "do")}
+    eng1 = helpers.softmax_engine(1, Hq, Hkv, S, D, D, dt, True)
+    eng1.kernels.bwd
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    main = torch.cuda.current_stream(dev)
 
     def step_e2e():
-        qd = host["q"].to(dev, non_blocking=True).requires_grad_()
-        kd = host["k"].to(dev, non_blocking=True).requires_grad_()
-        vd = host["v"].to(dev, non_blocking=True).requires_grad_()
-        dod = host["do"].to(dev, non_blocking=True)
-        o = eng(qd, kd, vd)
-        o.backward(dod)
-        out_host["do"].copy_(o.detach(), non_blocking=True)
-        out_host["q"].copy_(qd.grad, non_blocking=True)
-        out_host["k"].copy_(kd.grad, non_blocking=True)
-        out_host["v"].copy_(vd.grad, non_blocking=True)
+        pending = []
+        for bi in range(B):
+            with torch.cuda.stream(s_in):
+                qd = host["q"][bi:bi + 1].to(dev, non_blocking=True)
+                kd = host["k"][bi:bi + 1].to(dev, non_blocking=True)
+                vd = host["v"][bi:bi + 1].to(dev, non_blocking=True)
+                dod = host["do"][bi:bi + 1].to(dev, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            main.wait_event(ready)
+            for t_ in (qd, kd, vd, dod):
+                t_.record_stream(main)
+            qd.requires_grad_(); kd.requires_grad_(); vd.requires_grad_()
+            o = eng1(qd, kd, vd)
+            o.backward(dod)
+            done = torch.cuda.Event()
+            done.record(main)
+            s_out.wait_event(done)
+            with torch.cuda.stream(s_out):
+                res = (o.detach(), qd.grad, kd.grad, vd.grad)
+                for t_ in res:
+                    t_.record_stream(s_out)
+                out_host["do"][bi:bi + 1].copy_(res[0], non_blocking=True)
+                out_host["q"][bi:bi + 1].copy_(res[1], non_blocking=True)
+                out_host["k"][bi:bi + 1].copy_(res[2], non_blocking=True)
+                out_host["v"][bi:bi + 1].copy_(res[3], non_blocking=True)
+            pending.append(res)
+        main.wait_stream(s_out)
 
     n_e2e = 0 if args.no_e2e else max(1, min(args.steps, 3))
     if n_e2e:
@@ -234,7 +387,10 @@ def main():
     io_bytes = sum(host[n].numel() * 2 for n in host)
     e2e = None if not n_e2e else {"value": world * fl_step / (ms_e2e / 1e3) / 1e12, "unit": "TFLOPS",
                                   "ms_per_step": ms_e2e, "h2d_bytes_per_step": io_bytes,
-                                  "d2h_bytes_per_step": io_bytes}
+                                  "d2h_bytes_per_step": io_bytes,
+                                  "gpu_launches": 4 * B * n_e2e,
+                                  "how": "per batch row: H2D, operator call + backward, D2H on three streams"}
+    eng1.check_status()
 
     # ---- per-kernel times (CUDA events on the launching stream) and the roofline of the longest one -----
     kernels = {}
