@@ -31,6 +31,24 @@ def flops_fwd(B, Hq, S, D):
     return 4.0 * B * Hq * S * S * D / 2
 
 
+def max_over_ranks(value: float, device=None) -> float:
+    """Largest ``value`` over all ranks of the default process group (the identity without one)."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def aggregate_throughput(work_per_rank: float, ms_local: float, world: int, device=None) -> tuple:
+    """Weak scaling: every rank does ``work_per_rank``; the job's throughput is the total work over the slowest
+    rank's time.  Returns (units per second, that time in ms)."""
+    ms = max_over_ranks(ms_local, device)
+    return world * work_per_rank / (ms / 1e3), ms
+
+
 def read_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -324,12 +342,9 @@ def main():
     ms = e0.elapsed_time(e1) / args.steps
     clocks = sampler.stop() if sampler else None
     eng.check_status()
-    tmax = torch.tensor([ms], device=dev)
-    if world > 1:
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    ms = float(tmax.item())
     fl_step = 3.5 * flops_fwd(B, Hq, S, D)
-    value = world * fl_step / (ms / 1e3) / 1e12
+    per_s, ms = aggregate_throughput(fl_step, ms, world, dev)
+    value = per_s / 1e12
 
     # ---- end to end: host buffers in, host buffers out, through the public operator call ----------
     # One operator call per batch row; the row's H2D copies, its forward + backward and its D2H copies run on
@@ -380,10 +395,7 @@ def main():
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1) / max(n_e2e, 1)
-    t2 = torch.tensor([ms_e2e], device=dev)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    ms_e2e = float(t2.item())
+    ms_e2e = max_over_ranks(ms_e2e, dev)
     io_bytes = sum(host[n].numel() * 2 for n in host)
     e2e = None if not n_e2e else {"value": world * fl_step / (ms_e2e / 1e3) / 1e12, "unit": "TFLOPS",
                                   "ms_per_step": ms_e2e, "h2d_bytes_per_step": io_bytes,
