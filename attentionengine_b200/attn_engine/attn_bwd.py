@@ -7,6 +7,7 @@ Stands in for the generated ``_attention.backward`` of the reference
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 
 import torch
@@ -35,14 +36,18 @@ def compile_bwd(k) -> BwdKernels:
     bn, nbuf, stages = bwd_tile_config(D, DV)
     defs = f"#define AE_BWD_BN {bn}\n#define AE_BWD_NBUF {nbuf}\n#define AE_BWD_STAGES {stages}\n"
     prelude = low.prelude_bwd + defs
+    # the dQ pass has TMEM room for a third S/dP buffer (3 x 128 + 128 columns)
+    nbuf_dq = int(os.environ.get("AE_B200_DQ_NBUF", nbuf))
+    stages_dq = max(stages, nbuf_dq + 1) if max(D, DV) > 64 else stages
+    prelude_dq = low.prelude_bwd + f"#define AE_BWD_BN {bn}\n#define AE_BWD_NBUF {nbuf_dq}\n#define AE_BWD_STAGES {stages_dq}\n"
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_PREP, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=256,
                           smem_bytes=0, stages=0, mask_mode=k.mask_mode)
     prep = rt.compile_module(rt.kernel_source("attn_bwd_prep.cuh", prelude=prelude), "ae_attn_bwd_prep", cfg)
-    smem_dq = 128 * (D + DV) * 2 + stages * bn * (D + DV) * 2 + 512 + 1024
+    smem_dq = 128 * (D + DV) * 2 + stages_dq * bn * (D + DV) * 2 + 512 + 1024
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DQ, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
-                          smem_bytes=smem_dq, stages=stages, mask_mode=k.mask_mode)
+                          smem_bytes=smem_dq, stages=stages_dq, mask_mode=k.mask_mode)
     cfg.reserved[0] = bn
-    dq = rt.compile_module(rt.kernel_source("attn_bwd_dq.cuh", prelude=prelude), "ae_attn_bwd_dq", cfg)
+    dq = rt.compile_module(rt.kernel_source("attn_bwd_dq.cuh", prelude=prelude_dq), "ae_attn_bwd_dq", cfg)
     ncs = len(low.final_names) + 1
     smem_kv = 128 * (D + DV) * 2 + stages * bn * (D + DV) * 2 + 2 * bn * ncs * 4 + 16 + 512 + 1024
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DKV, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=320,

@@ -58,14 +58,27 @@ AE_DEVICE void mbar_fence_init() {
 AE_DEVICE void mbar_arrive(u64* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival per warp: all lanes have finished their part (their own fences included), lane 0 arrives for
+// the warp.  Barriers used this way are initialised with the number of warps, not threads: a few arrivals
+// on the shared-memory word instead of 128 or 256 serialised ones.
+AE_DEVICE void mbar_arrive_warp(u64* bar) {
+  __syncwarp();
+  if (lane_id() == 0) mbar_arrive(bar);
+}
 AE_DEVICE void mbar_arrive_expect_tx(u64* bar, u32 bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
+// One poll of an mbarrier phase.  AE_WAIT_MODE selects the instruction:
+//   0  mbarrier.try_wait with a suspend-time hint (the thread may be parked by the hardware; fewest issue slots)
+//   1  mbarrier.try_wait without a hint
+//   2  mbarrier.test_wait (never blocks; lowest wake-up latency, most issue slots)
+#ifndef AE_WAIT_MODE
+#define AE_WAIT_MODE 0
+#endif
 AE_DEVICE bool mbar_try_wait(u64* bar, u32 parity) {
-  // potentially blocking poll: the thread may be suspended by the hardware up to the time hint
-  // (in ns) before the instruction reports "not yet", so a waiting warp does not hog issue slots
   u32 ok;
+#if AE_WAIT_MODE == 0
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -75,6 +88,27 @@ AE_DEVICE bool mbar_try_wait(u64* bar, u32 parity) {
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
       : "memory");
+#elif AE_WAIT_MODE == 1
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+#else
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+#endif
   return ok != 0;
 }
 
@@ -83,6 +117,10 @@ struct AeTrue {
 };
 struct AeFalse {
   static constexpr bool value = false;
+};
+template <int N>
+struct AeInt {
+  static constexpr int value = N;
 };
 
 // Shared per-CTA control block used by the bounded waits.
@@ -326,6 +364,29 @@ AE_DEVICE float ae_rcp(float x) {
 #define AE_LOG2E 1.4426950408889634f
 #define AE_LN2 0.6931471805599453f
 AE_DEVICE float ae_exp(float x) { return ae_exp2(x * AE_LOG2E); }
+// 2^x on the FMA / ALU pipes instead of the XU (ex2) pipe: round-to-nearest range reduction with the
+// 1.5 * 2^23 trick, degree-3 polynomial for 2^f on [-0.5, 0.5] (max relative error 7.7e-5, below half an
+// ulp of fp16), exponent added in integer arithmetic.  Valid for x in [-126, 126]; smaller x is clamped.
+AE_DEVICE float ae_exp2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float xi = x + 12582912.0f;
+  const float f = x - (xi - 12582912.0f);
+  float p = fmaf(0.05508868396282196f, f, 0.24260404706001282f);
+  p = fmaf(p, f, 0.6932762265205383f);
+  p = fmaf(p, f, 0.9999289512634277f);
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(xi) << 23));
+}
+// Every AE_EXP_POLY_PERIOD-th element (by its compile-time index) takes the polynomial, the rest ex2.approx:
+// spreads the exponentials of a tile over two pipes.  0 = always ex2.approx.
+#ifndef AE_EXP_POLY_PERIOD
+#define AE_EXP_POLY_PERIOD 0
+#endif
+AE_DEVICE float ae_exp2_mix(float x, int idx) {
+#if AE_EXP_POLY_PERIOD > 0
+  if ((idx % AE_EXP_POLY_PERIOD) == AE_EXP_POLY_PERIOD - 1) return ae_exp2_poly(x);
+#endif
+  return ae_exp2(x);
+}
 AE_DEVICE float ae_log(float x) { return ae_log2(x) * AE_LN2; }
 
 // 4 x (32 lanes x 32 columns) TMEM load followed by tcgen05.wait::ld in ONE asm statement, so the
@@ -379,14 +440,17 @@ AE_DEVICE void tmem_ld_2xf32x32(u32 taddr_a, u32 taddr_b, float (&a)[32], float 
 
 // UMMA operand descriptors over tiles stored as 64-element-wide column blocks of [rows][128 B] with the
 // 128-byte swizzle (what a TMA box {64, rows} produces, and what the row threads write with swz128()).
-//   umma_desc_k : the contraction dim is the contiguous one (K-major); k-step kk covers 16 elements.
-//   umma_desc_mn: the contraction dim is the row index (MN-major); k-step kk covers 16 rows.
-AE_DEVICE u64 umma_desc_k(u32 base, int kk, int rows) {
-  return umma_smem_desc_sw128(base + (kk >> 2) * (rows * 128) + (kk & 3) * 32, 16, 1024);
+//   K-major : the contraction dim is the contiguous one; k-step kk covers 16 elements.
+//   MN-major: the contraction dim is the row index; k-step kk covers 16 rows.
+// The MMA-issuing thread is a single thread, so every instruction between two tcgen05.mma is on the critical
+// path: a tile's descriptor is built once (umma_base_*), each k-step only adds a compile-time constant to it
+// (the address field holds bytes / 16 and never carries out of its 14 bits inside one CTA's shared memory).
+AE_DEVICE u64 umma_base_k(u32 addr) { return umma_smem_desc_sw128(addr, 16, 1024); }
+AE_DEVICE u64 umma_base_mn(u32 addr, int rows) { return umma_smem_desc_sw128(addr, rows * 128, 1024); }
+AE_DEVICE u64 umma_step_k(u64 d0, int kk, int rows) {
+  return d0 + (u64)(((kk >> 2) * (rows * 128) + (kk & 3) * 32) >> 4);
 }
-AE_DEVICE u64 umma_desc_mn(u32 base, int kk, int rows) {
-  return umma_smem_desc_sw128(base + kk * 2048, rows * 128, 1024);
-}
+AE_DEVICE u64 umma_step_mn(u64 d0, int kk) { return d0 + (u64)(kk * 128); }
 // byte offset of the 16-byte chunk `ch` of row `r` inside a [rows][128 B] swizzled block
 AE_DEVICE u32 swz128(u32 r, u32 ch) { return r * 128 + ((ch ^ (r & 7)) << 4); }
 // byte offset of element column `col` (multiple of 8) of row `r` in a tile of 64-wide blocks of `rows` rows

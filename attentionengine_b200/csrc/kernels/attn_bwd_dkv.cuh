@@ -130,7 +130,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
     }
     for (int i = 0; i < AE_BWD_NBUF; ++i) {
       mbar_init(&bars->sp_full[i], 1);
-      mbar_init(&bars->pds_full[i], 256);
+      mbar_init(&bars->pds_full[i], 8);
     }
     mbar_fence_init();
   }
@@ -184,6 +184,9 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       const u32 q_addr = smem_u32(smem + AE_KV_SMEM_Q);
       const u32 do_addr = smem_u32(smem + AE_KV_SMEM_DO);
 
+      const u64 dk0 = umma_base_k(k_addr), dv0 = umma_base_k(v_addr);
+      const u64 dq0 = umma_base_k(q_addr), ddo0 = umma_base_k(do_addr);
+      const u64 dqmn0 = umma_base_mn(q_addr, AE_BWD_BN), ddomn0 = umma_base_mn(do_addr, AE_BWD_BN);
       auto issue_sp = [&](int s) -> bool {
         const int stage = s % AE_BWD_STAGES;
         const u32 par = (s / AE_BWD_STAGES) & 1;
@@ -192,20 +195,16 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         const u32 tm_dp = tm_s + AE_BWD_BN;
         if (!mbar_wait(&bars->q_full[stage], par, ctl, args.status, 32)) return false;
         tc_fence_after_sync();
-        const u32 qa = q_addr + stage * AE_KV_Q_BYTES;
+        const u64 dqq = dq0 + (u64)((stage * AE_KV_Q_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < AE_D / 16; ++kk) {
-          umma_ss(tm_s, umma_smem_desc_sw128(k_addr + (kk >> 2) * (AE_KV_BM * 128) + (kk & 3) * 32, 16, 1024),
-                  umma_smem_desc_sw128(qa + (kk >> 2) * (AE_BWD_BN * 128) + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < AE_D / 16; ++kk)
+          umma_ss(tm_s, umma_step_k(dk0, kk, AE_KV_BM), umma_step_k(dqq, kk, AE_BWD_BN), idesc_s, kk > 0);
         if (!mbar_wait(&bars->do_full[stage], par, ctl, args.status, 33)) return false;
         tc_fence_after_sync();
-        const u32 da = do_addr + stage * AE_KV_DO_BYTES;
+        const u64 ddd = ddo0 + (u64)((stage * AE_KV_DO_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < AE_DV / 16; ++kk) {
-          umma_ss(tm_dp, umma_smem_desc_sw128(v_addr + (kk >> 2) * (AE_KV_BM * 128) + (kk & 3) * 32, 16, 1024),
-                  umma_smem_desc_sw128(da + (kk >> 2) * (AE_BWD_BN * 128) + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < AE_DV / 16; ++kk)
+          umma_ss(tm_dp, umma_step_k(dv0, kk, AE_KV_BM), umma_step_k(ddd, kk, AE_BWD_BN), idesc_s, kk > 0);
         umma_commit(&bars->sp_full[buf]);
         return true;
       };
@@ -228,18 +227,14 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         tc_fence_after_sync();
         const u32 tm_p = tmem + TM_BUF + buf * 2 * AE_BWD_BN;
         const u32 tm_ds = tm_p + AE_BWD_BN;
-        const u32 qa = q_addr + stage * AE_KV_Q_BYTES;
-        const u32 da = do_addr + stage * AE_KV_DO_BYTES;
+        const u64 dqm = dqmn0 + (u64)((stage * AE_KV_Q_BYTES) >> 4);
+        const u64 ddm = ddomn0 + (u64)((stage * AE_KV_DO_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < AE_BWD_BN / 16; ++kk) {
-          umma_ts(tmem + TM_DV, tm_p + (kk >> 1) * 32 + (kk & 1) * 8, umma_smem_desc_sw128(da + kk * 2048, AE_BWD_BN * 128, 1024), idesc_dv,
-                  (s > 0) | (kk > 0));
-        }
+        for (int kk = 0; kk < AE_BWD_BN / 16; ++kk)
+          umma_ts(tmem + TM_DV, tm_p + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(ddm, kk), idesc_dv, (s > 0) | (kk > 0));
 #pragma unroll
-        for (int kk = 0; kk < AE_BWD_BN / 16; ++kk) {
-          umma_ts(tmem + TM_DK, tm_ds + (kk >> 1) * 32 + (kk & 1) * 8, umma_smem_desc_sw128(qa + kk * 2048, AE_BWD_BN * 128, 1024), idesc_dk,
-                  (s > 0) | (kk > 0));
-        }
+        for (int kk = 0; kk < AE_BWD_BN / 16; ++kk)
+          umma_ts(tmem + TM_DK, tm_ds + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(dqm, kk), idesc_dk, (s > 0) | (kk > 0));
         umma_commit(&bars->qdo_empty[stage]);
         if (s + 1 == n_steps) umma_commit(&bars->acc_done);
         if (AE_BWD_NBUF == 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
@@ -264,24 +259,40 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
     bool ok = true;
     int s = 0;
     AeDkvStep st;
-    while (next_step(st)) {
+    // per-column row scales (final row scales..., delta) of a q tile, fetched by the first AE_BWD_BN threads
+    float cs_next[AE_NCS];
+    auto fetch_cs = [&](const AeDkvStep& w) {
+      if (threadIdx.x < AE_BWD_BN) {
+        const int q = w.q0 + (int)row;
+        const i64 off = ((i64)b * args.Hq + w.hq) * args.Sq + (q < args.Sq ? q : args.Sq - 1);
+#pragma unroll
+        for (int i = 0; i < AE_NFINAL; ++i) cs_next[i] = args.final_rs[i][off];
+#if AE_USES_DOOSUM
+        cs_next[AE_NFINAL] = args.delta[off];
+#else
+        cs_next[AE_NFINAL] = 0.f;
+#endif
+      }
+    };
+    // the walk is consumed one step ahead so that the next tile's scales can be requested early
+    AeDkvStep st_next;
+    bool have = next_step(st_next);
+    if (have) fetch_cs(st_next);
+    while (have) {
+      st = st_next;
       const int buf = s % AE_BWD_NBUF;
       const u32 tm_s = tmem + TM_BUF + buf * 2 * AE_BWD_BN + lane_base;
       const u32 tm_dp = tm_s + AE_BWD_BN;
       float* csb = cs + (s & 1) * (AE_BWD_BN * AE_NCS);
       // stage the per-column row scales of this q tile
       if (threadIdx.x < AE_BWD_BN) {
-        const int q = st.q0 + (int)row;
-        const i64 off = ((i64)b * args.Hq + st.hq) * args.Sq + (q < args.Sq ? q : args.Sq - 1);
+        // values were fetched from HBM one step ahead (below); only the shared-memory store is on the path
 #pragma unroll
-        for (int i = 0; i < AE_NFINAL; ++i) csb[i * AE_BWD_BN + row] = args.final_rs[i][off];
-#if AE_USES_DOOSUM
-        csb[AE_NFINAL * AE_BWD_BN + row] = args.delta[off];
-#else
-        csb[AE_NFINAL * AE_BWD_BN + row] = 0.f;
-#endif
+        for (int i = 0; i < AE_NCS; ++i) csb[i * AE_BWD_BN + row] = cs_next[i];
       }
       named_bar_sync(1, 256);
+      have = next_step(st_next);
+      if (have) fetch_cs(st_next);  // in flight while this tile is processed
       ok = ok && mbar_wait(&bars->sp_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 36);
       tc_fence_after_sync();
       const bool tail = (st.q0 + AE_BWD_BN > args.Sq) || (kv0 + AE_KV_BM > args.Skv);
@@ -305,7 +316,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
 #pragma unroll
             for (int j = 0; j < AE_NCS; ++j) fr[j] = e == 0 ? cv[j].x : (e == 1 ? cv[j].y : (e == 2 ? cv[j].z : cv[j].w));
             const float sraw = sv[i + e];
-            float p = ae_bwd_p(sraw, fr, b, st.hq, q_idx, kv_idx, cu);
+            float p = ae_bwd_p(sraw, fr, b, st.hq, q_idx, kv_idx, cu, i + e);
             float dpv = dp[i + e];
             bool keep = true;
             if (kMasked) {
@@ -338,7 +349,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       }
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&bars->pds_full[buf]);
+      mbar_arrive_warp(&bars->pds_full[buf]);
       ++s;
     }
 

@@ -20,6 +20,13 @@
 
 #define AE_BM 128
 #define AE_NTHREADS_BWD 320
+// Optional phase trace of CTA (0, 0, 0): 32-bit clock stamps behind the status word (bring-up / tuning only).
+#ifdef AE_TRACE
+#define AE_TR(cond, region, slot) \
+  if (trace_on && (cond) && (slot) < 1024) args.status[64 + (region) * 4096 + (slot)] = (u32)clock64();
+#else
+#define AE_TR(cond, region, slot)
+#endif
 #define AE_NSUB (128 / AE_BWD_BN)
 
 #define AE_DQ_Q_BYTES (AE_BM * AE_D * 2)
@@ -59,6 +66,9 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
   const int hk = hq / (args.Hq / args.Hkv);
   const int q0 = qt * AE_BM;
   const int n_kt_bn = (args.Skv + AE_BWD_BN - 1) / AE_BWD_BN;
+#ifdef AE_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0;
+#endif
 
   // ---- kv schedule ------------------------------------------------------------------
   int n_steps;
@@ -102,7 +112,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
     }
     for (int i = 0; i < AE_BWD_NBUF; ++i) {
       mbar_init(&bars->sp_full[i], 1);
-      mbar_init(&bars->ds_full[i], 256);
+      mbar_init(&bars->ds_full[i], 8);
     }
     mbar_fence_init();
   }
@@ -156,6 +166,9 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       const u32 k_addr = smem_u32(smem + AE_DQ_SMEM_K);
       const u32 v_addr = smem_u32(smem + AE_DQ_SMEM_V);
       bool ok = mbar_wait(&bars->qdo_full, 0, ctl, args.status, 23);
+      const u64 dq0 = umma_base_k(q_addr), ddo0 = umma_base_k(do_addr);
+      const u64 dk0 = umma_base_k(k_addr), dv0 = umma_base_k(v_addr);
+      const u64 dkmn0 = umma_base_mn(k_addr, AE_BWD_BN);
 
       auto issue_sp = [&](int s) -> bool {
         const int stage = s % AE_BWD_STAGES;
@@ -163,24 +176,26 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
         const int buf = s % AE_BWD_NBUF;
         const u32 tm_s = tmem + buf * 2 * AE_BWD_BN;
         const u32 tm_dp = tm_s + AE_BWD_BN;
+        AE_TR(true, 3, s * 8 + 0)
         if (!mbar_wait(&bars->k_full[stage], par, ctl, args.status, 24)) return false;
         tc_fence_after_sync();
-        const u32 ka = k_addr + stage * AE_DQ_K_BYTES;
+        AE_TR(true, 3, s * 8 + 1)
+        const u64 dkk = dk0 + (u64)((stage * AE_DQ_K_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < AE_D / 16; ++kk) {
-          umma_ss(tm_s, umma_smem_desc_sw128(q_addr + (kk >> 2) * (AE_BM * 128) + (kk & 3) * 32, 16, 1024),
-                  umma_smem_desc_sw128(ka + (kk >> 2) * (AE_BWD_BN * 128) + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < AE_D / 16; ++kk)
+          umma_ss(tm_s, umma_step_k(dq0, kk, AE_BM), umma_step_k(dkk, kk, AE_BWD_BN), idesc_s, kk > 0);
+        AE_TR(true, 3, s * 8 + 2)
         if (!mbar_wait(&bars->v_full[stage], par, ctl, args.status, 25)) return false;
         tc_fence_after_sync();
-        const u32 va = v_addr + stage * AE_DQ_V_BYTES;
+        AE_TR(true, 3, s * 8 + 3)
+        const u64 dvv = dv0 + (u64)((stage * AE_DQ_V_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < AE_DV / 16; ++kk) {
-          umma_ss(tm_dp, umma_smem_desc_sw128(do_addr + (kk >> 2) * (AE_BM * 128) + (kk & 3) * 32, 16, 1024),
-                  umma_smem_desc_sw128(va + (kk >> 2) * (AE_BWD_BN * 128) + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < AE_DV / 16; ++kk)
+          umma_ss(tm_dp, umma_step_k(ddo0, kk, AE_BM), umma_step_k(dvv, kk, AE_BWD_BN), idesc_s, kk > 0);
+        AE_TR(true, 3, s * 8 + 4)
         umma_commit(&bars->sp_full[buf]);
         umma_commit(&bars->v_empty[stage]);
+        AE_TR(true, 3, s * 8 + 5)
         return true;
       };
 
@@ -190,18 +205,19 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
         const int buf = s % AE_BWD_NBUF;
         if (AE_BWD_NBUF > 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
         if (!ok) break;
+        AE_TR(true, 0, s * 4 + 0)
         ok = mbar_wait(&bars->ds_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 26);
         if (!ok) break;
+        AE_TR(true, 0, s * 4 + 1)
         tc_fence_after_sync();
         const u32 tm_ds = tmem + buf * 2 * AE_BWD_BN;  // dS pairs over the S columns
-        const u32 ka = k_addr + stage * AE_DQ_K_BYTES;
+        const u64 dkm = dkmn0 + (u64)((stage * AE_DQ_K_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < AE_BWD_BN / 16; ++kk) {
-          umma_ts(tmem + TM_DQ, tm_ds + (kk >> 1) * 32 + (kk & 1) * 8, umma_smem_desc_sw128(ka + kk * 2048, AE_BWD_BN * 128, 1024), idesc_dq,
-                  (s > 0) | (kk > 0));
-        }
+        for (int kk = 0; kk < AE_BWD_BN / 16; ++kk)
+          umma_ts(tmem + TM_DQ, tm_ds + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(dkm, kk), idesc_dq, (s > 0) | (kk > 0));
         umma_commit(&bars->k_empty[stage]);
         if (s + 1 == n_steps) umma_commit(&bars->dq_done);
+        AE_TR(true, 0, s * 4 + 2)
         if (AE_BWD_NBUF == 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
       }
     }
@@ -238,8 +254,10 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       const int buf = s % AE_BWD_NBUF;
       const u32 tm_s = tmem + buf * 2 * AE_BWD_BN + lane_base;
       const u32 tm_dp = tm_s + AE_BWD_BN;
+      AE_TR((warp & 3) == 0, 1 + wg, s * 4 + 0)
       ok = ok && mbar_wait(&bars->sp_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 27);
       tc_fence_after_sync();
+      AE_TR((warp & 3) == 0, 1 + wg, s * 4 + 1)
       const bool tail = kv0 + AE_BWD_BN > args.Skv;
       auto chunk = [&](auto masked_tag, int c) {
         constexpr bool kMasked = decltype(masked_tag)::value;
@@ -253,7 +271,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
           for (int e = 0; e < 2; ++e) {
             const int kv_idx = kv0 + c * 32 + i + e;
             const float sraw = sv[i + e];
-            float p = ae_bwd_p(sraw, fr, b, hq, q_idx, kv_idx, cu);
+            float p = ae_bwd_p(sraw, fr, b, hq, q_idx, kv_idx, cu, i + e);
             float dpv = dp[i + e];
             bool keep = true;
             if (kMasked) {
@@ -279,9 +297,11 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       } else {
         for (int c = wg; c < AE_BWD_BN / 32; c += 2) chunk(AeFalse{}, c);
       }
+      AE_TR((warp & 3) == 0, 1 + wg, s * 4 + 2)
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&bars->ds_full[buf]);
+      mbar_arrive_warp(&bars->ds_full[buf]);
+      AE_TR((warp & 3) == 0, 1 + wg, s * 4 + 3)
     }
 
     // ---- epilogue: dQ rows -------------------------------------------------------------

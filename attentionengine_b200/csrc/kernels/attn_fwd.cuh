@@ -144,7 +144,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->q_full[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->p_full[i], 128);
+      mbar_init(&bars->p_full[i], 4);
       mbar_init(&bars->o_done[i], 1);
     }
     for (int i = 0; i < AE_STAGES; ++i) {
@@ -203,26 +203,25 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       const u32 q_addr = smem_u32(smem + AE_SMEM_Q);
       const u32 k_addr = smem_u32(smem + AE_SMEM_K);
       const u32 v_addr = smem_u32(smem + AE_SMEM_V);
-      const u32 tm_s[2] = {tmem + TM_S0, tmem + TM_S1};
-      const u32 tm_o[2] = {tmem + TM_O0, tmem + TM_O1};
-
-      auto issue_s = [&](int t, int stage) {
-        const u32 qa = q_addr + t * AE_Q_BYTES;
-        const u32 ka = k_addr + stage * AE_K_BYTES;
+      const u64 dk0 = umma_base_k(k_addr);
+      const u64 dv0 = umma_base_mn(v_addr, AE_BN);
+      // q tile index as a compile-time constant: every per-tile quantity stays in a named register
+      auto issue_s = [&](auto T, int stage) {
+        constexpr int t = decltype(T)::value;
+        const u64 da = umma_base_k(q_addr + t * AE_Q_BYTES);
+        const u64 db = dk0 + (u64)((stage * AE_K_BYTES) >> 4);
+        const u32 d = tmem + (t ? TM_S1 : TM_S0);
 #pragma unroll
-        for (int kk = 0; kk < AE_D / 16; ++kk) {
-          const u32 off = (kk >> 2) * (AE_BM * 128) + (kk & 3) * 32;
-          umma_ss(tm_s[t], umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
-                  idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < AE_D / 16; ++kk)
+          umma_ss(d, umma_step_k(da, kk, AE_BM), umma_step_k(db, kk, AE_BN), idesc_s, kk > 0);
       };
-      auto issue_pv = [&](int t, int stage, u32 acc) {
-        const u32 va = v_addr + stage * AE_V_BYTES;
+      auto issue_pv = [&](auto T, int stage, u32 acc) {
+        constexpr int t = decltype(T)::value;
+        const u64 db = dv0 + (u64)((stage * AE_V_BYTES) >> 4);
+        const u32 d = tmem + (t ? TM_O1 : TM_O0);
+        const u32 a = tmem + (t ? TM_S1 : TM_S0);
 #pragma unroll
-        for (int kk = 0; kk < AE_BN / 16; ++kk) {
-          umma_ts(tm_o[t], tm_s[t] + kk * 8, umma_smem_desc_sw128(va + kk * 2048, AE_BN * 128, 1024), idesc_o,
-                  acc | (kk > 0));
-        }
+        for (int kk = 0; kk < AE_BN / 16; ++kk) umma_ts(d, a + kk * 8, umma_step_mn(db, kk), idesc_o, acc | (kk > 0));
       };
 
       // The walk is consumed one step ahead for the S GEMMs.
@@ -230,18 +229,20 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       bool ok = true;
       bool have = next_step(cur);
       int it = 0;
-      u32 np[2] = {0, 0};  // P tiles consumed per q tile
+      u32 np0 = 0, np1 = 0;  // P tiles consumed per q tile
+      auto first_s = [&](auto T) {
+        constexpr int t = decltype(T)::value;
+        if (!ok || !(cur.flags & (1u << t))) return;
+        ok = mbar_wait(&bars->q_full[t], 0, ctl, args.status, 4);
+        tc_fence_after_sync();
+        issue_s(T, 0);
+        umma_commit(&bars->s_full[t]);
+      };
       if (have) {
         ok = mbar_wait(&bars->k_full[0], 0, ctl, args.status, 3);
         tc_fence_after_sync();
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (cur.flags & (1u << t)) {
-            ok = mbar_wait(&bars->q_full[t], 0, ctl, args.status, 4);
-            tc_fence_after_sync();
-            issue_s(t, 0);
-            umma_commit(&bars->s_full[t]);
-          }
-        }
+        first_s(AeInt<0>{});
+        first_s(AeInt<1>{});
         umma_commit(&bars->k_empty[0]);
       }
       while (have && ok) {
@@ -251,33 +252,38 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         const int nstage = (it + 1) % AE_STAGES;
         const u32 npar = ((it + 1) / AE_STAGES) & 1;
         bool v_ready = false, k_ready = false;
-        for (int t = 0; t < 2 && ok; ++t) {
+        auto tile_step = [&](auto T, u32& np) {
+          constexpr int t = decltype(T)::value;
+          if (!ok) return;
           if (cur.flags & (1u << t)) {
-            ok = mbar_wait(&bars->p_full[t], np[t] & 1, ctl, args.status, 5);
-            if (!ok) break;
+            ok = mbar_wait(&bars->p_full[t], np & 1, ctl, args.status, 5);
+            if (!ok) return;
             if (!v_ready) {
               ok = mbar_wait(&bars->v_full[stage], par, ctl, args.status, 6);
-              if (!ok) break;
+              if (!ok) return;
               v_ready = true;
             }
             tc_fence_after_sync();
-            issue_pv(t, stage, np[t] > 0);
+            issue_pv(T, stage, np > 0);
             umma_commit(&bars->o_done[t]);
-            np[t]++;
+            np++;
           }
           if (have_n && (nxt.flags & (1u << t))) {
             if (!k_ready) {
               ok = mbar_wait(&bars->k_full[nstage], npar, ctl, args.status, 7);
-              if (!ok) break;
+              if (!ok) return;
               k_ready = true;
             }
             ok = mbar_wait(&bars->q_full[t], 0, ctl, args.status, 8);  // Q landed (phase 0 stays complete)
-            if (!ok) break;
+            if (!ok) return;
             tc_fence_after_sync();
-            issue_s(t, nstage);
+            issue_s(T, nstage);
             umma_commit(&bars->s_full[t]);
           }
-        }
+        };
+        tile_step(AeInt<0>{}, np0);
+        tile_step(AeInt<1>{}, np1);
+        if (!ok) break;
         umma_commit(&bars->v_empty[stage]);
         if (have_n) umma_commit(&bars->k_empty[nstage]);
         cur = nxt;
@@ -365,7 +371,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #endif
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&bars->p_full[t]);
+      mbar_arrive_warp(&bars->p_full[t]);
       ++n_done;
     }
 

@@ -64,12 +64,12 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
   if (threadIdx.x == 0) {
     ctl->abort = 0;
     mbar_init(&bars->full, 1);
-    mbar_init(&bars->empty, 128);
+    mbar_init(&bars->empty, 4);
     mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->prep_done, 128);
-    mbar_init(&bars->pds_full, 128);
+    mbar_init(&bars->prep_done, 4);
+    mbar_init(&bars->pds_full, 4);
     mbar_init(&bars->inter_full, 1);
-    mbar_init(&bars->scaled_done, 128);
+    mbar_init(&bars->scaled_done, 4);
     mbar_init(&bars->out_full, 1);
     mbar_fence_init();
   }
@@ -114,6 +114,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       const u32 DO = smem_u32(smem + AE_LB_SMEM_DO), HC = smem_u32(smem + AE_LB_SMEM_HC);
       const u32 P = smem_u32(smem + AE_LB_SMEM_P), DS = smem_u32(smem + AE_LB_SMEM_DS);
       const u32 DHB = smem_u32(smem + AE_LB_SMEM_DHB), DO2 = smem_u32(smem + AE_LB_SMEM_DO2);
+      const u64 kQ = umma_base_k(Q), kK = umma_base_k(K), kV = umma_base_k(V), kDO = umma_base_k(DO), kHC = umma_base_k(HC);
+      const u64 kDHB = umma_base_k(DHB), kDS = umma_base_k(DS);
+      const u64 mQ = umma_base_mn(Q, 128), mK = umma_base_mn(K, 128), mDO = umma_base_mn(DO, 128), mDO2 = umma_base_mn(DO2, 128);
+      const u64 mDHB = umma_base_mn(DHB, 128), mDS = umma_base_mn(DS, 128), mP = umma_base_mn(P, 128);
       const u32 id_kk_128 = umma_idesc_f16(128, 128, AE_BF16, 0, 0);
       const u32 id_kmn_dv = umma_idesc_f16(128, AE_LIN_DV, AE_BF16, 0, 1);
       const u32 id_mnmn_dv = umma_idesc_f16(128, AE_LIN_DV, AE_BF16, 1, 1);
@@ -128,10 +132,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         // A = q k^T -> R0 ; dPr = dO v^T -> R1
 #pragma unroll
         for (int kk = 0; kk < AE_LB_DK / 16; ++kk)
-          umma_ss(tmem + TM_R0, umma_desc_k(Q, kk, 128), umma_desc_k(K, kk, 128), id_kk_128, kk > 0);
+          umma_ss(tmem + TM_R0, umma_step_k(kQ, kk, 128), umma_step_k(kK, kk, 128), id_kk_128, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
-          umma_ss(tmem + TM_R1, umma_desc_k(DO, kk, 128), umma_desc_k(V, kk, 128), id_kk_128, kk > 0);
+          umma_ss(tmem + TM_R1, umma_step_k(kDO, kk, 128), umma_step_k(kV, kk, 128), id_kk_128, kk > 0);
         umma_commit(&bars->s_full);
         ok = mbar_wait(&bars->prep_done, par, ctl, args.status, 73);
         if (!ok) break;
@@ -141,31 +145,31 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         // inter-chunk parts (overwrite R0, R1, DV)
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
-          umma_ss(tmem + TM_R0, umma_desc_k(DO, kk, 128), umma_desc_k(HC, kk, 128), id_kk_128, kk > 0);
+          umma_ss(tmem + TM_R0, umma_step_k(kDO, kk, 128), umma_step_k(kHC, kk, 128), id_kk_128, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
-          umma_ss(tmem + TM_R1, umma_desc_k(V, kk, 128), umma_desc_k(DHB, kk, 128), id_kk_128, kk > 0);
+          umma_ss(tmem + TM_R1, umma_step_k(kV, kk, 128), umma_step_k(kDHB, kk, 128), id_kk_128, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < AE_LB_DK / 16; ++kk)
-          umma_ss(tmem + TM_DV, umma_desc_k(K, kk, 128), umma_desc_mn(DHB, kk, 128), id_kmn_dv, kk > 0);
+          umma_ss(tmem + TM_DV, umma_step_k(kK, kk, 128), umma_step_mn(mDHB, kk), id_kmn_dv, kk > 0);
         umma_commit(&bars->inter_full);
         // dH (+)= q^T (dO o exp(g))
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
-          umma_ss(tmem + TM_DH, umma_desc_mn(Q, kk, 128), umma_desc_mn(DO2, kk, 128), id_mnmn_dv, (it > 0) | (kk > 0));
+          umma_ss(tmem + TM_DH, umma_step_mn(mQ, kk), umma_step_mn(mDO2, kk), id_mnmn_dv, (it > 0) | (kk > 0));
         ok = mbar_wait(&bars->scaled_done, par, ctl, args.status, 75);
         if (!ok) break;
         tc_fence_after_sync();
         // intra-chunk parts on top
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
-          umma_ss(tmem + TM_R0, umma_desc_k(DS, kk, 128), umma_desc_mn(K, kk, 128), id_kmn_128, 1);
+          umma_ss(tmem + TM_R0, umma_step_k(kDS, kk, 128), umma_step_mn(mK, kk), id_kmn_128, 1);
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
-          umma_ss(tmem + TM_R1, umma_desc_mn(DS, kk, 128), umma_desc_mn(Q, kk, 128), id_mnmn_128, 1);
+          umma_ss(tmem + TM_R1, umma_step_mn(mDS, kk), umma_step_mn(mQ, kk), id_mnmn_128, 1);
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
-          umma_ss(tmem + TM_DV, umma_desc_mn(P, kk, 128), umma_desc_mn(DO, kk, 128), id_mnmn_dv, 1);
+          umma_ss(tmem + TM_DV, umma_step_mn(mP, kk), umma_step_mn(mDO, kk), id_mnmn_dv, 1);
         umma_commit(&bars->out_full);
       }
     }
@@ -249,7 +253,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       tc_wait_st();
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(&bars->prep_done);
+      mbar_arrive_warp(&bars->prep_done);
       // ---- D: P = E o A, dS = E o dPr -> shared memory ------------------------------------------------
       ok = ok && mbar_wait(&bars->s_full, par, ctl, args.status, 77);
       tc_fence_after_sync();
@@ -280,7 +284,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(&bars->pds_full);
+      mbar_arrive_warp(&bars->pds_full);
       // ---- E: row scaling of the inter-chunk parts ------------------------------------------------------
       ok = ok && mbar_wait(&bars->inter_full, par, ctl, args.status, 78);
       tc_fence_after_sync();
@@ -301,7 +305,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       }
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&bars->scaled_done);
+      mbar_arrive_warp(&bars->scaled_done);
       // ---- F: outputs -------------------------------------------------------------------------------------
       ok = ok && mbar_wait(&bars->out_full, par, ctl, args.status, 79);
       tc_fence_after_sync();
@@ -374,7 +378,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         carry += total;
       }
       tc_fence_before_sync();
-      mbar_arrive(&bars->empty);  // this chunk's tiles and accumulators are free
+      mbar_arrive_warp(&bars->empty);  // this chunk's tiles and accumulators are free
     }
   }
   tc_fence_before_sync();

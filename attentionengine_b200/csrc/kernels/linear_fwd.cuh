@@ -63,9 +63,9 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       mbar_init(&bars->empty[i], 1);
     }
     mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->prep_done, 128);
+    mbar_init(&bars->prep_done, 4);
     mbar_init(&bars->oi_full, 1);
-    mbar_init(&bars->p_full, 128);
+    mbar_init(&bars->p_full, 4);
     mbar_init(&bars->o_done, 1);
     mbar_init(&bars->h_done, 1);
     mbar_fence_init();
@@ -110,55 +110,47 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       const u32 idesc_h = umma_idesc_f16(AE_LIN_DK, AE_LIN_DV, AE_BF16, 1, 1);   // k^T v'
       const u32 v2_addr = smem_u32(smem + AE_LIN_SMEM_V2);
       const u32 h_addr = smem_u32(smem + AE_LIN_SMEM_H);
+      const u32 st_addr = smem_u32(smem + AE_LIN_SMEM_STAGE);
+      const u64 bq = umma_base_k(st_addr), bk = umma_base_k(st_addr + AE_LIN_Q_BYTES);
+      const u64 bk_mn = umma_base_mn(st_addr + AE_LIN_Q_BYTES, AE_LIN_C);
+      const u64 bv_mn = umma_base_mn(st_addr + 2 * AE_LIN_Q_BYTES, AE_LIN_C);
+      const u64 bh_mn = umma_base_mn(h_addr, AE_LIN_DK), bv2_mn = umma_base_mn(v2_addr, AE_LIN_C);
       auto issue_s = [&](int c) -> bool {
         const int stage = c % AE_LIN_STAGES;
         if (!mbar_wait(&bars->full[stage], (c / AE_LIN_STAGES) & 1, ctl, args.status, 52)) return false;
         tc_fence_after_sync();
-        const u32 qa = smem_u32(smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES);
-        const u32 ka = qa + AE_LIN_Q_BYTES;
+        const u64 so = (u64)((stage * AE_LIN_STAGE_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < AE_LIN_DK / 16; ++kk) {
-          const u32 off = (kk >> 2) * (AE_LIN_C * 128) + (kk & 3) * 32;
-          umma_ss(tmem + TM_S, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
-                  idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < AE_LIN_DK / 16; ++kk)
+          umma_ss(tmem + TM_S, umma_step_k(bq + so, kk, AE_LIN_C), umma_step_k(bk + so, kk, AE_LIN_C), idesc_s, kk > 0);
         umma_commit(&bars->s_full);
         return true;
       };
       bool ok = issue_s(0);
       for (int c = 0; c < n_chunks && ok; ++c) {
         const int stage = c % AE_LIN_STAGES;
-        const u32 qa = smem_u32(smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES);
-        const u32 ka = qa + AE_LIN_Q_BYTES;
-        const u32 va = qa + 2 * AE_LIN_Q_BYTES;
+        const u64 so = (u64)((stage * AE_LIN_STAGE_BYTES) >> 4);
         ok = mbar_wait(&bars->prep_done, c & 1, ctl, args.status, 53);
         if (!ok) break;
         tc_fence_after_sync();
         if (c > 0) {
           // Oi = q h   (h: [DK rows][DV contiguous], MN-major B)
 #pragma unroll
-          for (int kk = 0; kk < AE_LIN_DK / 16; ++kk) {
-            const u32 off = (kk >> 2) * (AE_LIN_C * 128) + (kk & 3) * 32;
-            umma_ss(tmem + TM_O, umma_smem_desc_sw128(qa + off, 16, 1024),
-                    umma_smem_desc_sw128(h_addr + kk * 2048, AE_LIN_DK * 128, 1024), idesc_oi, kk > 0);
-          }
+          for (int kk = 0; kk < AE_LIN_DK / 16; ++kk)
+            umma_ss(tmem + TM_O, umma_step_k(bq + so, kk, AE_LIN_C), umma_step_mn(bh_mn, kk), idesc_oi, kk > 0);
         }
         umma_commit(&bars->oi_full);
         // H (+)= k^T v'   (k tile read MN-major as A: [chunk rows][DK contiguous]; v' likewise as B)
 #pragma unroll
-        for (int kk = 0; kk < AE_LIN_C / 16; ++kk) {
-          umma_ss(tmem + TM_H, umma_smem_desc_sw128(ka + kk * 2048, AE_LIN_C * 128, 1024),
-                  umma_smem_desc_sw128(v2_addr + kk * 2048, AE_LIN_C * 128, 1024), idesc_h, (c > 0) | (kk > 0));
-        }
+        for (int kk = 0; kk < AE_LIN_C / 16; ++kk)
+          umma_ss(tmem + TM_H, umma_step_mn(bk_mn + so, kk), umma_step_mn(bv2_mn, kk), idesc_h, (c > 0) | (kk > 0));
         umma_commit(&bars->h_done);
         ok = mbar_wait(&bars->p_full, c & 1, ctl, args.status, 54);
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
-        for (int kk = 0; kk < AE_LIN_C / 16; ++kk) {
-          umma_ts(tmem + TM_O, tmem + TM_S + kk * 8, umma_smem_desc_sw128(va + kk * 2048, AE_LIN_C * 128, 1024),
-                  idesc_oi, (c > 0) | (kk > 0));
-        }
+        for (int kk = 0; kk < AE_LIN_C / 16; ++kk)
+          umma_ts(tmem + TM_O, tmem + TM_S + kk * 8, umma_step_mn(bv_mn + so, kk), idesc_oi, (c > 0) | (kk > 0));
         umma_commit(&bars->o_done);
         umma_commit(&bars->empty[stage]);
         if (c + 1 < n_chunks) ok = issue_s(c + 1);
@@ -240,7 +232,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       tc_wait_st();
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(&bars->prep_done);
+      mbar_arrive_warp(&bars->prep_done);
       // ---- D: P = A * exp(g_i - g_j) for j <= i -------------------------------------------------
       ok = ok && mbar_wait(&bars->s_full, c & 1, ctl, args.status, 57);
       tc_fence_after_sync();
@@ -283,7 +275,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       }
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&bars->p_full);
+      mbar_arrive_warp(&bars->p_full);
       // ---- F: O rows out ---------------------------------------------------------------------------
       ok = ok && mbar_wait(&bars->o_done, c & 1, ctl, args.status, 59);
       tc_fence_after_sync();

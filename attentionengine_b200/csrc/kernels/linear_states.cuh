@@ -40,7 +40,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_states(const __gr
       mbar_init(&bars->full[i], 1);
       mbar_init(&bars->empty[i], 1);
     }
-    mbar_init(&bars->prep_done, 128);
+    mbar_init(&bars->prep_done, 4);
     mbar_init(&bars->h_done, 1);
     mbar_fence_init();
   }
@@ -73,16 +73,17 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_states(const __gr
     if (lane == 0) {
       const u32 idesc_h = umma_idesc_f16(AE_LS_DK, AE_LIN_DV, AE_BF16, 1, 1);
       const u32 v2_addr = smem_u32(smem + AE_LS_SMEM_V2);
+      const u64 bk_mn = umma_base_mn(smem_u32(smem), AE_LS_C), bv2_mn = umma_base_mn(v2_addr, AE_LS_C);
       bool ok = true;
       for (int c = 0; c < n_chunks && ok; ++c) {
         const int stage = c % AE_LIN_STAGES;
-        const u32 ka = smem_u32(smem + stage * AE_LS_STAGE_BYTES);
+        const u64 so = (u64)((stage * AE_LS_STAGE_BYTES) >> 4);
         ok = mbar_wait(&bars->prep_done, c & 1, ctl, args.status, 62);
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < AE_LS_C / 16; ++kk)
-          umma_ss(tmem, umma_desc_mn(ka, kk, AE_LS_C), umma_desc_mn(v2_addr, kk, AE_LS_C), idesc_h, (c > 0) | (kk > 0));
+          umma_ss(tmem, umma_step_mn(bk_mn + so, kk), umma_step_mn(bv2_mn, kk), idesc_h, (c > 0) | (kk > 0));
         umma_commit(&bars->h_done);
         umma_commit(&bars->empty[stage]);
       }
@@ -162,7 +163,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_states(const __gr
       tc_wait_st();
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(&bars->prep_done);
+      mbar_arrive_warp(&bars->prep_done);
       // v2 may only be rewritten once this chunk's update has read it: next iteration waits on h_done(c)
       // before touching TMEM, but v2 is written after that wait as well (program order), so it is safe.
     }

@@ -63,7 +63,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
     mbar_init(&bars->kv_full, 1);
     mbar_init(&bars->kv_empty, 1);
     mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->p_full, 128);
+    mbar_init(&bars->p_full, 4);
     mbar_init(&bars->o_done, 1);
     mbar_fence_init();
   }
@@ -105,6 +105,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
       const u32 q_addr = smem_u32(smem + AE_MLA_SMEM_Q);
       const u32 kv_addr = smem_u32(smem + AE_MLA_SMEM_KV);
       bool ok = mbar_wait(&bars->q_full, 0, ctl, args.status, 42);
+      const u64 dq0 = umma_base_k(q_addr), dk0 = umma_base_k(kv_addr);
+      const u64 dv0 = umma_base_mn(kv_addr + dvh * (AE_MLA_NBV / 2) * (AE_MLA_BN * 128), AE_MLA_BN);
       for (int s = 0; s < n_steps && ok; ++s) {
         ok = mbar_wait(&bars->kv_full, s & 1, ctl, args.status, 43);
         if (!ok) break;
@@ -112,23 +114,18 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
 #pragma unroll
         for (int blk = 0; blk < AE_MLA_NBK; ++blk) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            umma_ss(tmem + TM_S, umma_smem_desc_sw128(q_addr + blk * (AE_MLA_H * 128) + kk * 32, 16, 1024),
-                    umma_smem_desc_sw128(kv_addr + blk * (AE_MLA_BN * 128) + kk * 32, 16, 1024), idesc_s,
-                    (blk | kk) > 0);
-          }
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(tmem + TM_S, dq0 + (u64)((blk * (AE_MLA_H * 128) + kk * 32) >> 4),
+                    dk0 + (u64)((blk * (AE_MLA_BN * 128) + kk * 32) >> 4), idesc_s, (blk | kk) > 0);
         }
         umma_commit(&bars->s_full);
         ok = mbar_wait(&bars->p_full, s & 1, ctl, args.status, 44);
         if (!ok) break;
         tc_fence_after_sync();
         // V = this half's four 64-wide blocks of the same tile, read MN-major
-        const u32 va = kv_addr + dvh * (AE_MLA_NBV / 2) * (AE_MLA_BN * 128);
 #pragma unroll
-        for (int kk = 0; kk < AE_MLA_BN / 16; ++kk) {
-          umma_ts(tmem + TM_O, tmem + TM_S + kk * 8, umma_smem_desc_sw128(va + kk * 2048, AE_MLA_BN * 128, 1024),
-                  idesc_o, (s > 0) | (kk > 0));
-        }
+        for (int kk = 0; kk < AE_MLA_BN / 16; ++kk)
+          umma_ts(tmem + TM_O, tmem + TM_S + kk * 8, umma_step_mn(dv0, kk), idesc_o, (s > 0) | (kk > 0));
         umma_commit(&bars->o_done);
         umma_commit(&bars->kv_empty);
       }
@@ -194,7 +191,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
 #endif
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&bars->p_full);
+      mbar_arrive_warp(&bars->p_full);
     }
 
     if (n_steps > 0) {

@@ -309,7 +309,8 @@ class Emitter:
                     l2e = Scal("AE_LOG2E", 1.4426950408889634)
                     a = self._s_mul(a if a is not None else Scal("1.0f", 1.0), l2e)
                     b = self._s_mul(b, l2e) if b is not None else None
-                self.names[id(v)] = self._new_tile(f"ae_exp2({self._affine_expr(base, a, b)})")
+                idx = "c" if self.tile_mode == "array" else "sel"
+                self.names[id(v)] = self._new_tile(f"ae_exp2_mix({self._affine_expr(base, a, b)}, {idx})")
                 return
             args = [self.ref(p, "c") for p in v.prev]
             self.names[id(v)] = self._new_tile(self._expr(t, args))
@@ -507,7 +508,7 @@ def lower_combine(online_func) -> str:
     w = online_func.combine(fr)
     em = Emitter(env, {}, tile_mode="lane")
     res = em.ref(w)
-    return ("AE_DEVICE float ae_combine(const float* fr) {\n" + em.body() + f"  return {res};\n}}\n")
+    return ("AE_DEVICE float ae_combine(const float* fr) {\n  const int sel = 0; (void)sel;\n" + em.body() + f"  return {res};\n}}\n")
 
 
 def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomIO, *, D: int, DV: int, bf16: bool,
@@ -549,7 +550,7 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     env[id(scores)] = ("s", "tile")
     em = Emitter(env, idx_env, tile_mode="scalar")
     res = em.ref(out)
-    src.append("AE_DEVICE float ae_score_mod(float s, int b, int h, int q_idx, int kv_idx, const AeCustom& cu) {\n"
+    src.append("AE_DEVICE float ae_score_mod(float s, int b, int h, int q_idx, int kv_idx, const AeCustom& cu) {\n  const int sel = 0; (void)sel;\n"
                + em.body() + f"  return {res};\n}}\n")
 
     # ---- online_fwd fused with score_mod (per row, N columns) --------------------------------------------
@@ -602,13 +603,13 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     o_new, finals = online_func.online_fwd_epilogue(o_sym, rs_ep, sym_idx("b"), sym_idx("h"), sym_idx("q_idx"))
     em = Emitter(env, {}, tile_mode="scalar")
     res = em.ref(o_new)
-    src.append("AE_DEVICE float ae_epilogue_o(float o, const AeRow& st) {\n" + em.body() + f"  return {res};\n}}\n")
+    src.append("AE_DEVICE float ae_epilogue_o(float o, const AeRow& st) {\n  const int sel = 0; (void)sel;\n" + em.body() + f"  return {res};\n}}\n")
     final_names = list(finals.keys())
     if len(final_names) > 4:
         raise NotImplementedError("at most 4 final rowscales are supported")
     em = Emitter(env, {}, tile_mode="scalar")
     fl = [em.ref(v) for v in finals.values()]
-    src.append("AE_DEVICE void ae_final_rowscales(const AeRow& st, float* out) {\n" + em.body()
+    src.append("AE_DEVICE void ae_final_rowscales(const AeRow& st, float* out) {\n  const int sel = 0; (void)sel;\n" + em.body()
                + "".join(f"  out[{i}] = {e};\n" for i, e in enumerate(fl)) + "}\n")
 
     # ---- backward fragments: P = forward(score_mod(S)); dS = score_mod'(S) * backward(dP, P) ---------------------
@@ -628,7 +629,7 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     res = em.ref(p_out)
     bsrc.append("// P from the raw score: OnlineFunc.forward(score_mod(s)) with the saved final row scales\n"
                 "AE_DEVICE float ae_bwd_p(float s, const float* fr, int b, int h, int q_idx, int kv_idx, "
-                "const AeCustom& cu) {\n" + em.body() + f"  return {res};\n}}\n")
+                "const AeCustom& cu, const int sel = 0) {\n" + em.body() + f"  return {res};\n}}\n")
 
     dp = SymbolScalar("dp", Var("dp"), shape_idx=["block_M", "block_N"], require_grad=False)
     pp = SymbolScalar("p", Var("p"), shape_idx=["block_M", "block_N"], require_grad=False)
@@ -650,7 +651,7 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     uses_doosum = "doosum" in em.used_leaves
     bsrc.append("// dS from dP and P: score_mod'(s) * OnlineFunc.backward(dp, p, final row scales, doosum)\n"
                 "AE_DEVICE float ae_bwd_ds(float s, float dp, float p, const float* fr, float doosum, int b, int h, "
-                "int q_idx, int kv_idx, const AeCustom& cu) {\n" + em.body() + f"  return {gres};\n}}\n")
+                "int q_idx, int kv_idx, const AeCustom& cu) {\n  const int sel = 0; (void)sel;\n" + em.body() + f"  return {gres};\n}}\n")
 
     defines = {
         "AE_D": D, "AE_DV": DV, "AE_BF16": int(bf16), "AE_STAGES": stages, "AE_MASK_MODE": mask_mode,

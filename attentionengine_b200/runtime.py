@@ -136,9 +136,18 @@ def check(rc: int, what: str = ""):
         raise AeError(f"{what}: {L.ae_strerror(rc).decode()} - {L.ae_last_error().decode()}")
 
 
+def exp_poly_period() -> int:
+    """Every n-th exponential of a score tile is evaluated with the FMA-pipe polynomial instead of ex2.approx
+    (0 = none).  Tunable through AE_B200_EXP_POLY; see ae_exp2_mix in csrc/kernels/ae_sm100.cuh."""
+    return int(os.environ.get("AE_B200_EXP_POLY", "0"))
+
+
 def kernel_source(*files: str, prelude: str = "") -> str:
     """Common header + argument blocks + generated prelude + kernel template(s), as one translation unit."""
-    parts = [(KERNEL_DIR / "ae_sm100.cuh").read_text().replace("#pragma once\n", ""),
+    parts = [f"#define AE_EXP_POLY_PERIOD {exp_poly_period()}\n#define AE_WAIT_MODE {int(os.environ.get('AE_B200_WAIT_MODE', '0'))}\n"
+             + ("#define AE_TRACE 1\n" if os.environ.get("AE_B200_TRACE") else "")
+             + ("#define AE_SELFCHECK 1\n" if os.environ.get("AE_B200_SELFCHECK") else ""),
+             (KERNEL_DIR / "ae_sm100.cuh").read_text().replace("#pragma once\n", ""),
              (KERNEL_DIR / "ae_args.h").read_text(), prelude]
     parts += [(KERNEL_DIR / f).read_text() for f in files]
     return "\n".join(parts)
