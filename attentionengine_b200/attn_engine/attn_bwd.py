@@ -28,7 +28,21 @@ class BwdKernels:
 def bwd_tile_config(D: int, DV: int):
     """(streamed tile rows, TMEM buffers, ring depth).  Two S/dP buffers of 64 columns fit next to
     the accumulators in the 512 TMEM columns and let the tensor pipe run ahead of the row threads."""
+    cfg = os.environ.get("AE_B200_BWD_TILE")  # "bn,nbuf,stages": tuning override
+    if cfg:
+        bn, nbuf, stages = (int(x) for x in cfg.split(","))
+        return bn, nbuf, stages
     return 64, 2, 4 if max(D, DV) <= 64 else 3
+
+
+def dkv_tile_config(D: int, DV: int):
+    """(streamed q-tile rows, Q ring depth, dO ring depth, row warpgroups) of the dK/dV pass: one 128 x 128 S^T and
+    dP^T region next to the two accumulators fill the 512 TMEM columns; K, V, three Q and two dO stages fill shared
+    memory at head dim 128 (a Q slot is released last in a step and needed first, so it gets the extra stage)."""
+    cfg = os.environ.get("AE_B200_DKV_TILE")  # "bn,q stages,dO stages,row groups": tuning override
+    if cfg:
+        return tuple(int(x) for x in cfg.split(","))
+    return (128, 3, 2, 4) if max(D, DV) > 64 else (128, 3, 3, 4)
 
 
 def compile_bwd(k) -> BwdKernels:
@@ -49,11 +63,21 @@ def compile_bwd(k) -> BwdKernels:
     cfg.reserved[0] = bn
     dq = rt.compile_module(rt.kernel_source("attn_bwd_dq.cuh", prelude=prelude_dq), "ae_attn_bwd_dq", cfg)
     ncs = len(low.final_names) + 1
-    smem_kv = 128 * (D + DV) * 2 + stages * bn * (D + DV) * 2 + 2 * bn * ncs * 4 + 16 + 512 + 1024
-    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DKV, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
-                          smem_bytes=smem_kv, stages=stages, mask_mode=k.mask_mode)
-    cfg.reserved[0] = bn
-    dkv = rt.compile_module(rt.kernel_source("attn_bwd_dkv.cuh", prelude=prelude), "ae_attn_bwd_dkv", cfg)
+    bn_kv, qst, dost, nwg = dkv_tile_config(D, DV)
+    prelude_kv = low.prelude_bwd + (f"#define AE_BWD_BN {bn_kv}\n#define AE_KV_QSTAGES {qst}\n"
+                                    f"#define AE_KV_DOSTAGES {dost}\n#define AE_KV_NWG {nwg}\n")
+    smem_kv = 128 * (D + DV) * 2 + bn_kv * (qst * D + dost * DV) * 2 + 2 * bn_kv * ncs * 4 + 256
+    # 1 KiB of slack lets the kernel align its base itself; where that would exceed the 227 KiB a CTA can have, the
+    # base must already be aligned (the kernel checks and reports status 0x200 instead of running misaligned)
+    slack = smem_kv + 1024 <= 232448
+    if smem_kv > 232448:
+        raise NotImplementedError("dK/dV pass: the streamed tiles do not fit in shared memory")
+    smem_kv += 1024 if slack else 0
+    prelude_kv += f"#define AE_KV_ALIGN_SLACK {int(slack)}\n"
+    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DKV, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV,
+                          threads=nwg * 128 + 64, smem_bytes=smem_kv, stages=qst, mask_mode=k.mask_mode)
+    cfg.reserved[0] = bn_kv
+    dkv = rt.compile_module(rt.kernel_source("attn_bwd_dkv.cuh", prelude=prelude_kv), "ae_attn_bwd_dkv", cfg)
     return BwdKernels(prep, dq, dkv, bn, nbuf, stages)
 
 

@@ -150,6 +150,11 @@ AE_DEVICE bool mbar_wait(u64* bar, u32 parity, AeCtaCtl* ctl, u32* g_status, u32
   }
 }
 
+// The same wait run by every lane of a warp; the result is made warp-uniform by a vote.
+AE_DEVICE bool mbar_wait_w(u64* bar, u32 parity, AeCtaCtl* ctl, u32* g_status, u32 site) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctl, g_status, site));
+}
+
 // ---------------------------------------------------------------------------
 // proxies / fences
 // ---------------------------------------------------------------------------
@@ -262,10 +267,22 @@ AE_DEVICE void umma_ts(u32 tmem_d, u32 tmem_a, u64 desc_b, u32 idesc, u32 accumu
       "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Warp-level forms for an MMA-issuing warp whose 32 lanes all run the control flow: operands (descriptors, TMEM
+// addresses, loop counters) then stay warp-uniform, which lets them live in uniform registers, the operand class
+// tcgen05.mma takes; only the instruction itself is issued by one elected lane.
+AE_DEVICE void umma_ss_w(u32 tmem_d, u64 desc_a, u64 desc_b, u32 idesc, u32 accumulate) {
+  if (elect_one()) umma_ss(tmem_d, desc_a, desc_b, idesc, accumulate);
+}
+AE_DEVICE void umma_ts_w(u32 tmem_d, u32 tmem_a, u64 desc_b, u32 idesc, u32 accumulate) {
+  if (elect_one()) umma_ts(tmem_d, tmem_a, desc_b, idesc, accumulate);
+}
 // All MMAs issued so far by this thread arrive on `bar` when they complete.
 AE_DEVICE void umma_commit(u64* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
+}
+AE_DEVICE void umma_commit_w(u64* bar) {
+  if (elect_one()) umma_commit(bar);
 }
 
 // ---------------------------------------------------------------------------

@@ -6,16 +6,28 @@
 // in the CTA's own TMEM accumulators: no atomics (the reference adds half-precision atomics
 // across the group, attn_gqa_tl.py:345-348).  Per q tile, with rows = kv and columns = q:
 //   S^T  = K  Q^T  (SS MMA)      dP^T = V dO^T  (SS MMA)
-//   row threads: P^T = forward(score_mod(S^T)); dS^T = score_mod'(S^T) * backward(dP^T, P^T)
-//                (per-column lse / delta come from shared memory); both written back to TMEM
-//                as 16-bit pairs over S^T and dP^T
+//   row threads, phase A: P^T = forward(score_mod(S^T)), written over S^T as 16-bit pairs and kept in
+//                registers; phase B: dS^T = score_mod'(S^T) * backward(dP^T, P^T), written over dP^T
+//                (per-column lse / delta come from shared memory)
 //   dV += P^T dO   (TS MMA, dO tile read MN-major)     dK += dS^T Q  (TS MMA, Q tile read MN-major)
-// TMEM columns: dK | dV | AE_BWD_NBUF x (S^T | dP^T).
-// Roles: warps 0-3 and 4-7 row threads (thread = kv row = TMEM lane; the two groups take alternate
-// 32-column chunks of every tile), warp 8 TMA producer, warp 9 MMA issuer.  The 16-bit pairs of a chunk
-// are written over the first 16 columns of that chunk, so a group only overwrites what it has read.
+// TMEM columns: dK | dV | S^T | dP^T.  The tensor pipe executes MMAs in issue order, so one S^T and one
+// dP^T region are enough to keep it busy: the issue order per q tile s is
+//   dV_s (after phase A of s) , S^T_{s+1} , dK_s (after phase B of s) , dP^T_{s+1}
+// and the row threads run phase B of s under dV_s / S^T_{s+1} and phase A of s+1 under dK_s / dP^T_{s+1}.
+// Roles: AE_KV_NWG row warpgroups (thread = kv row = TMEM lane; the groups take alternate 32-column chunks
+// of every tile), then one producer warp (TMA loads of Q / dO by one lane, per-column row scales by all
+// lanes) and one MMA-issuing warp.  The 16-bit pairs of a chunk are written over the first 16 columns of
+// that chunk, so a group only overwrites what it has read.
+// Expects AE_BWD_BN (q rows per tile), AE_KV_QSTAGES / AE_KV_DOSTAGES (ring depths), AE_KV_NWG (2 or 4).
 
 #define AE_KV_BM 128
+// Optional phase trace of CTA (0, 0, 0): 32-bit clock stamps behind the status word (bring-up / tuning only).
+#ifdef AE_TRACE
+#define AE_TRK(cond, region, slot) \
+  if (trace_on && (cond) && (slot) < 2048) args.status[64 + (region) * 4096 + (slot)] = (u32)clock64();
+#else
+#define AE_TRK(cond, region, slot)
+#endif
 #define AE_NSUBQ (128 / AE_BWD_BN)
 #define AE_NCS (AE_NFINAL + 1)
 
@@ -26,18 +38,22 @@
 #define AE_KV_SMEM_K 0
 #define AE_KV_SMEM_V (AE_KV_K_BYTES)
 #define AE_KV_SMEM_Q (AE_KV_SMEM_V + AE_KV_V_BYTES)
-#define AE_KV_SMEM_DO (AE_KV_SMEM_Q + AE_BWD_STAGES * AE_KV_Q_BYTES)
-#define AE_KV_SMEM_CS (AE_KV_SMEM_DO + AE_BWD_STAGES * AE_KV_DO_BYTES)
+#define AE_KV_SMEM_DO (AE_KV_SMEM_Q + AE_KV_QSTAGES * AE_KV_Q_BYTES)
+#define AE_KV_SMEM_CS (AE_KV_SMEM_DO + AE_KV_DOSTAGES * AE_KV_DO_BYTES)
 #define AE_KV_CS_BYTES (2 * AE_BWD_BN * AE_NCS * 4)
+#define AE_KV_NROW (AE_KV_NWG * 128)
+#define AE_KV_NTHREADS (AE_KV_NROW + 64)
 #define AE_KV_SMEM_BAR (AE_KV_SMEM_CS + ((AE_KV_CS_BYTES + 15) / 16) * 16)
 
 struct AeDkvBars {
   u64 kv_full;
-  u64 q_full[AE_BWD_STAGES];
-  u64 do_full[AE_BWD_STAGES];
-  u64 qdo_empty[AE_BWD_STAGES];
-  u64 sp_full[AE_BWD_NBUF];
-  u64 pds_full[AE_BWD_NBUF];
+  u64 q_full[AE_KV_QSTAGES];
+  u64 cs_full[2], cs_empty[2];  // per-column row scales of a q tile (two slots)
+  u64 q_empty[AE_KV_QSTAGES];
+  u64 do_full[AE_KV_DOSTAGES];
+  u64 do_empty[AE_KV_DOSTAGES];
+  u64 s_full, dp_full;  // S^T / dP^T of a step are in TMEM
+  u64 p_full, ds_full;  // the row threads have written P^T / dS^T
   u64 acc_done;
   AeCtaCtl ctl;
 };
@@ -48,10 +64,19 @@ struct AeDkvStep {
   bool partial; // needs the element-wise mask
 };
 
-extern "C" __global__ void __launch_bounds__(320, 1)
+extern "C" __global__ void __launch_bounds__(AE_KV_NTHREADS, 1)
 ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
   extern __shared__ u8 smem_raw[];
+#if AE_KV_ALIGN_SLACK
   u8* smem = smem_align1024(smem_raw);
+#else
+  // the carve-up fills the CTA's shared memory: the launch gave no slack, so the base must be aligned already
+  u8* smem = smem_raw;
+  if (smem_u32(smem_raw) & 1023u) {
+    if (threadIdx.x == 0 && args.status) atomicCAS(args.status, 0u, 0x200u);
+    return;
+  }
+#endif
   AeDkvBars* bars = (AeDkvBars*)(smem + AE_KV_SMEM_BAR);
   float* cs = (float*)(smem + AE_KV_SMEM_CS);  // [2][AE_NCS][AE_BWD_BN]: final rowscales..., delta, per q column
   AeCtaCtl* ctl = &bars->ctl;
@@ -64,6 +89,9 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
   const int G = args.Hq / args.Hkv;
   const int kv0 = kt * AE_KV_BM;
   const int n_q_bn = (args.Sq + AE_BWD_BN - 1) / AE_BWD_BN;
+#ifdef AE_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0;
+#endif
 
   // ---- q schedule: heads of the group outer, q tiles inner ---------------------------
 #if AE_MASK_MODE == 1
@@ -123,18 +151,25 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
     ctl->abort = 0;
     mbar_init(&bars->kv_full, 1);
     mbar_init(&bars->acc_done, 1);
-    for (int i = 0; i < AE_BWD_STAGES; ++i) {
+    for (int i = 0; i < AE_KV_QSTAGES; ++i) {
       mbar_init(&bars->q_full[i], 1);
+      mbar_init(&bars->q_empty[i], 1);
+    }
+    for (int i = 0; i < AE_KV_DOSTAGES; ++i) {
       mbar_init(&bars->do_full[i], 1);
-      mbar_init(&bars->qdo_empty[i], 1);
+      mbar_init(&bars->do_empty[i], 1);
     }
-    for (int i = 0; i < AE_BWD_NBUF; ++i) {
-      mbar_init(&bars->sp_full[i], 1);
-      mbar_init(&bars->pds_full[i], 8);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->cs_full[i], 32);
+      mbar_init(&bars->cs_empty[i], AE_KV_NWG * 4);
     }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->p_full, AE_KV_NWG * 4);
+    mbar_init(&bars->ds_full, AE_KV_NWG * 4);
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == AE_KV_NWG * 4 + 1) {
     tmem_alloc(&ctl->tmem_base, 512);
     tmem_relinquish();
   }
@@ -142,10 +177,11 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
   __syncthreads();
   tc_fence_after_sync();
   const u32 tmem = ctl->tmem_base;
-  const u32 TM_DK = 0, TM_DV = AE_D, TM_BUF = AE_D + AE_DV;
+  const u32 TM_DK = 0, TM_DV = AE_D, TM_S = AE_D + AE_DV, TM_DP = TM_S + AE_BWD_BN;
 
-  if (warp == 8) {
-    // =============================== TMA producer ===============================
+  if (warp == AE_KV_NWG * 4) {
+    // =============================== producer ====================================
+    // All lanes walk the schedule; lane 0 issues the TMA loads, every lane fetches the row scales of four q columns.
     if (lane == 0) {
       tma_prefetch_desc(&args.tm_q);
       tma_prefetch_desc(&args.tm_k);
@@ -156,26 +192,49 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         tma_load_4d(smem + AE_KV_SMEM_K + dh * (AE_KV_BM * 128), &args.tm_k, &bars->kv_full, dh * 64, hk, kv0, b);
       for (int dh = 0; dh < AE_DV / 64; ++dh)
         tma_load_4d(smem + AE_KV_SMEM_V + dh * (AE_KV_BM * 128), &args.tm_v, &bars->kv_full, dh * 64, hk, kv0, b);
-      AeDkvStep st;
-      int s = 0;
-      while (next_step(st)) {
-        const int stage = s % AE_BWD_STAGES;
-        const u32 par = ((s / AE_BWD_STAGES) & 1) ^ 1;
-        if (!mbar_wait(&bars->qdo_empty[stage], par, ctl, args.status, 31)) break;
-        mbar_arrive_expect_tx(&bars->q_full[stage], AE_KV_Q_BYTES);
-        for (int dh = 0; dh < AE_D / 64; ++dh)
-          tma_load_4d(smem + AE_KV_SMEM_Q + stage * AE_KV_Q_BYTES + dh * (AE_BWD_BN * 128), &args.tm_q,
-                      &bars->q_full[stage], dh * 64, st.hq, st.q0, b);
-        mbar_arrive_expect_tx(&bars->do_full[stage], AE_KV_DO_BYTES);
-        for (int dh = 0; dh < AE_DV / 64; ++dh)
-          tma_load_4d(smem + AE_KV_SMEM_DO + stage * AE_KV_DO_BYTES + dh * (AE_BWD_BN * 128), &args.tm_do,
-                      &bars->do_full[stage], dh * 64, st.hq, st.q0, b);
-        ++s;
-      }
     }
-  } else if (warp == 9) {
+    AeDkvStep st;
+    int s = 0;
+    while (next_step(st)) {
+      const int sq = s % AE_KV_QSTAGES, sd = s % AE_KV_DOSTAGES;
+      if (!mbar_wait_w(&bars->q_empty[sq], ((s / AE_KV_QSTAGES) & 1) ^ 1, ctl, args.status, 31)) break;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&bars->q_full[sq], AE_KV_Q_BYTES);
+        for (int dh = 0; dh < AE_D / 64; ++dh)
+          tma_load_4d(smem + AE_KV_SMEM_Q + sq * AE_KV_Q_BYTES + dh * (AE_BWD_BN * 128), &args.tm_q, &bars->q_full[sq],
+                      dh * 64, st.hq, st.q0, b);
+      }
+      {
+        if (!mbar_wait_w(&bars->cs_empty[s & 1], ((s >> 1) & 1) ^ 1, ctl, args.status, 42)) break;
+        float* csb = cs + (s & 1) * (AE_BWD_BN * AE_NCS);
+        const i64 base = ((i64)b * args.Hq + st.hq) * args.Sq;
+#pragma unroll
+        for (int j = 0; j < AE_BWD_BN / 32; ++j) {
+          const int col = j * 32 + (int)lane;
+          const int q = st.q0 + col;
+          const i64 off = base + (q < args.Sq ? q : args.Sq - 1);
+#pragma unroll
+          for (int i = 0; i < AE_NFINAL; ++i) csb[i * AE_BWD_BN + col] = args.final_rs[i][off];
+#if AE_USES_DOOSUM
+          csb[AE_NFINAL * AE_BWD_BN + col] = args.delta[off];
+#else
+          csb[AE_NFINAL * AE_BWD_BN + col] = 0.f;
+#endif
+        }
+        mbar_arrive(&bars->cs_full[s & 1]);
+      }
+      if (!mbar_wait_w(&bars->do_empty[sd], ((s / AE_KV_DOSTAGES) & 1) ^ 1, ctl, args.status, 38)) break;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&bars->do_full[sd], AE_KV_DO_BYTES);
+        for (int dh = 0; dh < AE_DV / 64; ++dh)
+          tma_load_4d(smem + AE_KV_SMEM_DO + sd * AE_KV_DO_BYTES + dh * (AE_BWD_BN * 128), &args.tm_do,
+                      &bars->do_full[sd], dh * 64, st.hq, st.q0, b);
+      }
+      ++s;
+    }
+  } else if (warp == AE_KV_NWG * 4 + 1) {
     // =============================== MMA issuer =================================
-    if (lane == 0) {
+    {  // all 32 lanes run the control flow; single MMAs and commits are issued by an elected lane
       const u32 idesc_s = umma_idesc_f16(AE_KV_BM, AE_BWD_BN, AE_BF16, 0, 0);
       const u32 idesc_dk = umma_idesc_f16(AE_KV_BM, AE_D, AE_BF16, 0, 1);
       const u32 idesc_dv = umma_idesc_f16(AE_KV_BM, AE_DV, AE_BF16, 0, 1);
@@ -187,25 +246,26 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       const u64 dk0 = umma_base_k(k_addr), dv0 = umma_base_k(v_addr);
       const u64 dq0 = umma_base_k(q_addr), ddo0 = umma_base_k(do_addr);
       const u64 dqmn0 = umma_base_mn(q_addr, AE_BWD_BN), ddomn0 = umma_base_mn(do_addr, AE_BWD_BN);
-      auto issue_sp = [&](int s) -> bool {
-        const int stage = s % AE_BWD_STAGES;
-        const u32 par = (s / AE_BWD_STAGES) & 1;
-        const int buf = s % AE_BWD_NBUF;
-        const u32 tm_s = tmem + TM_BUF + buf * 2 * AE_BWD_BN;
-        const u32 tm_dp = tm_s + AE_BWD_BN;
-        if (!mbar_wait(&bars->q_full[stage], par, ctl, args.status, 32)) return false;
+      auto issue_s = [&](int s) -> bool {  // S^T_s = K Q_s^T
+        const int stage = s % AE_KV_QSTAGES;
+        if (!mbar_wait_w(&bars->q_full[stage], (s / AE_KV_QSTAGES) & 1, ctl, args.status, 32)) return false;
         tc_fence_after_sync();
         const u64 dqq = dq0 + (u64)((stage * AE_KV_Q_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_D / 16; ++kk)
-          umma_ss(tm_s, umma_step_k(dk0, kk, AE_KV_BM), umma_step_k(dqq, kk, AE_BWD_BN), idesc_s, kk > 0);
-        if (!mbar_wait(&bars->do_full[stage], par, ctl, args.status, 33)) return false;
+          umma_ss_w(tmem + TM_S, umma_step_k(dk0, kk, AE_KV_BM), umma_step_k(dqq, kk, AE_BWD_BN), idesc_s, kk > 0);
+        umma_commit_w(&bars->s_full);
+        return true;
+      };
+      auto issue_dp = [&](int s) -> bool {  // dP^T_s = V dO_s^T
+        const int stage = s % AE_KV_DOSTAGES;
+        if (!mbar_wait_w(&bars->do_full[stage], (s / AE_KV_DOSTAGES) & 1, ctl, args.status, 33)) return false;
         tc_fence_after_sync();
         const u64 ddd = ddo0 + (u64)((stage * AE_KV_DO_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_DV / 16; ++kk)
-          umma_ss(tm_dp, umma_step_k(dv0, kk, AE_KV_BM), umma_step_k(ddd, kk, AE_BWD_BN), idesc_s, kk > 0);
-        umma_commit(&bars->sp_full[buf]);
+          umma_ss_w(tmem + TM_DP, umma_step_k(dv0, kk, AE_KV_BM), umma_step_k(ddd, kk, AE_BWD_BN), idesc_s, kk > 0);
+        umma_commit_w(&bars->dp_full);
         return true;
       };
 
@@ -215,34 +275,48 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         AeDkvStep st;
         while (next_step(st)) ++n_steps;
       }
-      bool ok = n_steps > 0 && mbar_wait(&bars->kv_full, 0, ctl, args.status, 34);
-      if (ok) ok = issue_sp(0);
+      bool ok = n_steps > 0 && mbar_wait_w(&bars->kv_full, 0, ctl, args.status, 34);
+      if (ok) ok = issue_s(0);
+      if (ok) ok = issue_dp(0);
       for (int s = 0; s < n_steps && ok; ++s) {
-        const int stage = s % AE_BWD_STAGES;
-        const int buf = s % AE_BWD_NBUF;
-        if (AE_BWD_NBUF > 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
-        if (!ok) break;
-        ok = mbar_wait(&bars->pds_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 35);
+        const int sq = s % AE_KV_QSTAGES, sd = s % AE_KV_DOSTAGES;
+        const u32 par = s & 1;
+        // dV += P^T dO_s, then the next S^T goes over P^T (in issue order, so after it has been read)
+        AE_TRK(true, 0, s * 8 + 0)
+        ok = mbar_wait_w(&bars->p_full, par, ctl, args.status, 35);
         if (!ok) break;
         tc_fence_after_sync();
-        const u32 tm_p = tmem + TM_BUF + buf * 2 * AE_BWD_BN;
-        const u32 tm_ds = tm_p + AE_BWD_BN;
-        const u64 dqm = dqmn0 + (u64)((stage * AE_KV_Q_BYTES) >> 4);
-        const u64 ddm = ddomn0 + (u64)((stage * AE_KV_DO_BYTES) >> 4);
+        AE_TRK(true, 0, s * 8 + 1)
+        const u64 ddm = ddomn0 + (u64)((sd * AE_KV_DO_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_BWD_BN / 16; ++kk)
-          umma_ts(tmem + TM_DV, tm_p + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(ddm, kk), idesc_dv, (s > 0) | (kk > 0));
+          umma_ts_w(tmem + TM_DV, tmem + TM_S + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(ddm, kk), idesc_dv,
+                  (s > 0) | (kk > 0));
+        umma_commit_w(&bars->do_empty[sd]);
+        AE_TRK(true, 0, s * 8 + 2)
+        if (s + 1 < n_steps) ok = issue_s(s + 1);
+        if (!ok) break;
+        AE_TRK(true, 0, s * 8 + 3)
+        // dK += dS^T Q_s, then the next dP^T goes over dS^T
+        ok = mbar_wait_w(&bars->ds_full, par, ctl, args.status, 39);
+        if (!ok) break;
+        tc_fence_after_sync();
+        AE_TRK(true, 0, s * 8 + 4)
+        const u64 dqm = dqmn0 + (u64)((sq * AE_KV_Q_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_BWD_BN / 16; ++kk)
-          umma_ts(tmem + TM_DK, tm_ds + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(dqm, kk), idesc_dk, (s > 0) | (kk > 0));
-        umma_commit(&bars->qdo_empty[stage]);
-        if (s + 1 == n_steps) umma_commit(&bars->acc_done);
-        if (AE_BWD_NBUF == 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
+          umma_ts_w(tmem + TM_DK, tmem + TM_DP + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(dqm, kk), idesc_dk,
+                  (s > 0) | (kk > 0));
+        umma_commit_w(&bars->q_empty[sq]);
+        if (s + 1 == n_steps) umma_commit_w(&bars->acc_done);
+        AE_TRK(true, 0, s * 8 + 5)
+        if (s + 1 < n_steps) ok = issue_dp(s + 1);
+        AE_TRK(true, 0, s * 8 + 6)
       }
     }
   } else {
     // =============================== row threads ================================
-    const int wg = warp >> 2;  // the two row warpgroups split every tile by 32-column chunks
+    const int wg = warp >> 2;  // the row warpgroups split every tile by 32-column chunks
     const u32 row = threadIdx.x & 127;
     const u32 lane_base = ((warp & 3) * 32) << 16;
     const int kv_idx = kv0 + (int)row;
@@ -259,97 +333,127 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
     bool ok = true;
     int s = 0;
     AeDkvStep st;
-    // per-column row scales (final row scales..., delta) of a q tile, fetched by the first AE_BWD_BN threads
-    float cs_next[AE_NCS];
-    auto fetch_cs = [&](const AeDkvStep& w) {
-      if (threadIdx.x < AE_BWD_BN) {
-        const int q = w.q0 + (int)row;
-        const i64 off = ((i64)b * args.Hq + w.hq) * args.Sq + (q < args.Sq ? q : args.Sq - 1);
-#pragma unroll
-        for (int i = 0; i < AE_NFINAL; ++i) cs_next[i] = args.final_rs[i][off];
-#if AE_USES_DOOSUM
-        cs_next[AE_NFINAL] = args.delta[off];
-#else
-        cs_next[AE_NFINAL] = 0.f;
-#endif
-      }
-    };
-    // the walk is consumed one step ahead so that the next tile's scales can be requested early
     AeDkvStep st_next;
     bool have = next_step(st_next);
-    if (have) fetch_cs(st_next);
+    constexpr int NCH = AE_BWD_BN / 32 / AE_KV_NWG;  // 32-column chunks per group and tile
+    const u32 tm_s = tmem + TM_S + lane_base;
+    const u32 tm_dp = tmem + TM_DP + lane_base;
     while (have) {
       st = st_next;
-      const int buf = s % AE_BWD_NBUF;
-      const u32 tm_s = tmem + TM_BUF + buf * 2 * AE_BWD_BN + lane_base;
-      const u32 tm_dp = tm_s + AE_BWD_BN;
-      float* csb = cs + (s & 1) * (AE_BWD_BN * AE_NCS);
-      // stage the per-column row scales of this q tile
-      if (threadIdx.x < AE_BWD_BN) {
-        // values were fetched from HBM one step ahead (below); only the shared-memory store is on the path
-#pragma unroll
-        for (int i = 0; i < AE_NCS; ++i) csb[i * AE_BWD_BN + row] = cs_next[i];
-      }
-      named_bar_sync(1, 256);
+      const float* csb = cs + (s & 1) * (AE_BWD_BN * AE_NCS);
       have = next_step(st_next);
-      if (have) fetch_cs(st_next);  // in flight while this tile is processed
-      ok = ok && mbar_wait(&bars->sp_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 36);
-      tc_fence_after_sync();
       const bool tail = (st.q0 + AE_BWD_BN > args.Sq) || (kv0 + AE_KV_BM > args.Skv);
-      auto chunk = [&](auto masked_tag, int c) {
-        constexpr bool kMasked = decltype(masked_tag)::value;
-        float sv[32], dp[32];
-        tmem_ld_2xf32x32(tm_s + c * 32, tm_dp + c * 32, sv, dp);
-        u32 pk[16], dk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          // per-column row scales of four q columns: one 128-bit broadcast load per scale
-          float4 cv[AE_NCS];
-#pragma unroll
-          for (int j = 0; j < AE_NCS; ++j) cv[j] = *(const float4*)(csb + j * AE_BWD_BN + c * 32 + i);
-          float p4[4], ds4[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = c * 32 + i + e;
-            const int q_idx = st.q0 + col;
-            float fr[AE_NCS];
-#pragma unroll
-            for (int j = 0; j < AE_NCS; ++j) fr[j] = e == 0 ? cv[j].x : (e == 1 ? cv[j].y : (e == 2 ? cv[j].z : cv[j].w));
-            const float sraw = sv[i + e];
-            float p = ae_bwd_p(sraw, fr, b, st.hq, q_idx, kv_idx, cu, i + e);
-            float dpv = dp[i + e];
-            bool keep = true;
-            if (kMasked) {
-              keep = row_valid && q_idx < args.Sq;
-#if AE_MASK_MODE != 0
-              if (st.partial) keep = keep && ae_mask(b, st.hq, q_idx, kv_idx);
+      const bool masked = st.partial || tail;
+      float pkeep[NCH][32];
+#if AE_DS_USES_S
+      float skeep[NCH][32];
 #endif
-              if (!keep) {
-                p = 0.f;
-                dpv = 0.f;
-              }
-            }
-            float dsv = ae_bwd_ds(sraw, dpv, p, fr, fr[AE_NFINAL], b, st.hq, q_idx, kv_idx, cu);
-            if (kMasked && !keep) dsv = 0.f;
-            p4[e] = p;
-            ds4[e] = dsv;
-          }
-          pk[(i >> 1) + 0] = pack2<AE_BF16>(p4[0], p4[1]);
-          pk[(i >> 1) + 1] = pack2<AE_BF16>(p4[2], p4[3]);
-          dk[(i >> 1) + 0] = pack2<AE_BF16>(ds4[0], ds4[1]);
-          dk[(i >> 1) + 1] = pack2<AE_BF16>(ds4[2], ds4[3]);
-        }
-        tmem_st16(tm_s + c * 32, pk);  // pairs go over this chunk's own first 16 columns
-        tmem_st16(tm_dp + c * 32, dk);
+      auto col_scales = [&](int c, int i, int e, float (&fr)[AE_NCS], const float4 (&cv)[AE_NCS]) {
+#pragma unroll
+        for (int j = 0; j < AE_NCS; ++j) fr[j] = e == 0 ? cv[j].x : (e == 1 ? cv[j].y : (e == 2 ? cv[j].z : cv[j].w));
       };
-      if (st.partial || tail) {
-        for (int c = wg; c < AE_BWD_BN / 32; c += 2) chunk(AeTrue{}, c);
-      } else {
-        for (int c = wg; c < AE_BWD_BN / 32; c += 2) chunk(AeFalse{}, c);
-      }
+      auto keep_of = [&](int q_idx) -> bool {
+        bool keep = row_valid && q_idx < args.Sq;
+#if AE_MASK_MODE != 0
+        if (st.partial) keep = keep && ae_mask(b, st.hq, q_idx, kv_idx);
+#endif
+        return keep;
+      };
+
+      // ---- phase A: P^T from S^T ---------------------------------------------------------------
+      AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 0)
+      ok = ok && mbar_wait(&bars->cs_full[s & 1], (s >> 1) & 1, ctl, args.status, 41);
+      ok = ok && mbar_wait(&bars->s_full, s & 1, ctl, args.status, 36);
+      tc_fence_after_sync();
+      AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 1)
+      auto phase_a = [&](auto masked_tag) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
+#pragma unroll
+        for (int ci = 0; ci < NCH; ++ci) {
+          const int c = wg + AE_KV_NWG * ci;
+          float sv[32];
+          tmem_ld_f32x32(tm_s + c * 32, sv);
+          u32 pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float4 cv[AE_NCS];
+#pragma unroll
+            for (int j = 0; j < AE_NCS; ++j) cv[j] = *(const float4*)(csb + j * AE_BWD_BN + c * 32 + i);
+            float p4[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int q_idx = st.q0 + c * 32 + i + e;
+              float fr[AE_NCS];
+              col_scales(c, i, e, fr, cv);
+              float p = ae_bwd_p(sv[i + e], fr, b, st.hq, q_idx, kv_idx, cu, i + e);
+              if (kMasked && !keep_of(q_idx)) p = 0.f;
+              p4[e] = p;
+              pkeep[ci][i + e] = p;
+#if AE_DS_USES_S
+              skeep[ci][i + e] = sv[i + e];
+#endif
+            }
+            pk[(i >> 1) + 0] = pack2<AE_BF16>(p4[0], p4[1]);
+            pk[(i >> 1) + 1] = pack2<AE_BF16>(p4[2], p4[3]);
+          }
+          tmem_st16(tm_s + c * 32, pk);  // pairs go over this chunk's own first 16 columns
+        }
+      };
+      if (masked) phase_a(AeTrue{}); else phase_a(AeFalse{});
+      AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 2)
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive_warp(&bars->pds_full[buf]);
+      mbar_arrive_warp(&bars->p_full);
+      AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 3)
+
+      // ---- phase B: dS^T from dP^T and the P^T kept in registers --------------------------------
+      ok = ok && mbar_wait(&bars->dp_full, s & 1, ctl, args.status, 40);
+      tc_fence_after_sync();
+      AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 4)
+      auto phase_b = [&](auto masked_tag) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
+#pragma unroll
+        for (int ci = 0; ci < NCH; ++ci) {
+          const int c = wg + AE_KV_NWG * ci;
+          float dp[32];
+          tmem_ld_f32x32(tm_dp + c * 32, dp);
+          u32 dk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float4 cv[AE_NCS];
+#pragma unroll
+            for (int j = 0; j < AE_NCS; ++j) cv[j] = *(const float4*)(csb + j * AE_BWD_BN + c * 32 + i);
+            float ds4[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int q_idx = st.q0 + c * 32 + i + e;
+              float fr[AE_NCS];
+              col_scales(c, i, e, fr, cv);
+#if AE_DS_USES_S
+              const float sraw = skeep[ci][i + e];
+#else
+              const float sraw = 0.f;
+#endif
+              bool keep = true;
+              if (kMasked) keep = keep_of(q_idx);
+              float dsv = ae_bwd_ds(sraw, keep ? dp[i + e] : 0.f, pkeep[ci][i + e], fr, fr[AE_NFINAL], b, st.hq, q_idx,
+                                    kv_idx, cu);
+              if (kMasked && !keep) dsv = 0.f;
+              ds4[e] = dsv;
+            }
+            dk[(i >> 1) + 0] = pack2<AE_BF16>(ds4[0], ds4[1]);
+            dk[(i >> 1) + 1] = pack2<AE_BF16>(ds4[2], ds4[3]);
+          }
+          tmem_st16(tm_dp + c * 32, dk);
+        }
+      };
+      if (masked) phase_b(AeTrue{}); else phase_b(AeFalse{});
+      AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 5)
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive_warp(&bars->ds_full);
+      mbar_arrive_warp(&bars->cs_empty[s & 1]);
+      AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 6)
       ++s;
     }
 
@@ -364,30 +468,27 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       const int kv_s = store ? kv_idx : 0;
       u16* dkrow = (u16*)args.dk + (i64)b * args.dk_sb + (i64)kv_s * args.dk_ss + (i64)hk * args.dk_sh;
       u16* dvrow = (u16*)args.dv + (i64)b * args.dv_sb + (i64)kv_s * args.dv_ss + (i64)hk * args.dv_sh;
-      {
-        const int which = wg;  // group 0 stores dK, group 1 stores dV
-        const int ncol = which ? AE_DV : AE_D;
-        u16* drow = which ? dvrow : dkrow;
-        const u32 tm = tmem + (which ? TM_DV : TM_DK) + lane_base;
-        for (int c = 0; c < ncol / 32; ++c) {
-          float r[32];
-          if (s > 0) {
-            tmem_ld_f32x32(tm + c * 32, r);
-          } else {
+      // the groups take alternate 32-column chunks of [dK | dV] (adjacent in TMEM)
+      for (int cc = wg; cc < (AE_D + AE_DV) / 32; cc += AE_KV_NWG) {
+        const bool is_dv = cc * 32 >= AE_D;
+        u16* drow = is_dv ? dvrow + (cc * 32 - AE_D) : dkrow + cc * 32;
+        float r[32];
+        if (s > 0) {
+          tmem_ld_f32x32(tmem + TM_DK + lane_base + cc * 32, r);
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0.f;
-          }
-          if (store) {
-            uint4* dst = (uint4*)(drow + c * 32);
+          for (int i = 0; i < 32; ++i) r[i] = 0.f;
+        }
+        if (store) {
+          uint4* dst = (uint4*)drow;
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 w;
-              w.x = pack2<AE_BF16>(r[v * 8 + 0], r[v * 8 + 1]);
-              w.y = pack2<AE_BF16>(r[v * 8 + 2], r[v * 8 + 3]);
-              w.z = pack2<AE_BF16>(r[v * 8 + 4], r[v * 8 + 5]);
-              w.w = pack2<AE_BF16>(r[v * 8 + 6], r[v * 8 + 7]);
-              dst[v] = w;
-            }
+          for (int v = 0; v < 4; ++v) {
+            uint4 w;
+            w.x = pack2<AE_BF16>(r[v * 8 + 0], r[v * 8 + 1]);
+            w.y = pack2<AE_BF16>(r[v * 8 + 2], r[v * 8 + 3]);
+            w.z = pack2<AE_BF16>(r[v * 8 + 4], r[v * 8 + 5]);
+            w.w = pack2<AE_BF16>(r[v * 8 + 6], r[v * 8 + 7]);
+            dst[v] = w;
           }
         }
       }
@@ -396,7 +497,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == AE_KV_NWG * 4 + 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);
   }

@@ -158,14 +158,14 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
     }
   } else if (warp == 9) {
     // =============================== MMA issuer =================================
-    if (lane == 0 && n_steps > 0) {
+    if (n_steps > 0) {  // all 32 lanes run the control flow; single MMAs and commits are issued by an elected lane
       const u32 idesc_s = umma_idesc_f16(AE_BM, AE_BWD_BN, AE_BF16, 0, 0);
       const u32 idesc_dq = umma_idesc_f16(AE_BM, AE_D, AE_BF16, 0, 1);
       const u32 q_addr = smem_u32(smem + AE_DQ_SMEM_Q);
       const u32 do_addr = smem_u32(smem + AE_DQ_SMEM_DO);
       const u32 k_addr = smem_u32(smem + AE_DQ_SMEM_K);
       const u32 v_addr = smem_u32(smem + AE_DQ_SMEM_V);
-      bool ok = mbar_wait(&bars->qdo_full, 0, ctl, args.status, 23);
+      bool ok = mbar_wait_w(&bars->qdo_full, 0, ctl, args.status, 23);
       const u64 dq0 = umma_base_k(q_addr), ddo0 = umma_base_k(do_addr);
       const u64 dk0 = umma_base_k(k_addr), dv0 = umma_base_k(v_addr);
       const u64 dkmn0 = umma_base_mn(k_addr, AE_BWD_BN);
@@ -177,24 +177,24 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
         const u32 tm_s = tmem + buf * 2 * AE_BWD_BN;
         const u32 tm_dp = tm_s + AE_BWD_BN;
         AE_TR(true, 3, s * 8 + 0)
-        if (!mbar_wait(&bars->k_full[stage], par, ctl, args.status, 24)) return false;
+        if (!mbar_wait_w(&bars->k_full[stage], par, ctl, args.status, 24)) return false;
         tc_fence_after_sync();
         AE_TR(true, 3, s * 8 + 1)
         const u64 dkk = dk0 + (u64)((stage * AE_DQ_K_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_D / 16; ++kk)
-          umma_ss(tm_s, umma_step_k(dq0, kk, AE_BM), umma_step_k(dkk, kk, AE_BWD_BN), idesc_s, kk > 0);
+          umma_ss_w(tm_s, umma_step_k(dq0, kk, AE_BM), umma_step_k(dkk, kk, AE_BWD_BN), idesc_s, kk > 0);
         AE_TR(true, 3, s * 8 + 2)
-        if (!mbar_wait(&bars->v_full[stage], par, ctl, args.status, 25)) return false;
+        if (!mbar_wait_w(&bars->v_full[stage], par, ctl, args.status, 25)) return false;
         tc_fence_after_sync();
         AE_TR(true, 3, s * 8 + 3)
         const u64 dvv = dv0 + (u64)((stage * AE_DQ_V_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_DV / 16; ++kk)
-          umma_ss(tm_dp, umma_step_k(ddo0, kk, AE_BM), umma_step_k(dvv, kk, AE_BWD_BN), idesc_s, kk > 0);
+          umma_ss_w(tm_dp, umma_step_k(ddo0, kk, AE_BM), umma_step_k(dvv, kk, AE_BWD_BN), idesc_s, kk > 0);
         AE_TR(true, 3, s * 8 + 4)
-        umma_commit(&bars->sp_full[buf]);
-        umma_commit(&bars->v_empty[stage]);
+        umma_commit_w(&bars->sp_full[buf]);
+        umma_commit_w(&bars->v_empty[stage]);
         AE_TR(true, 3, s * 8 + 5)
         return true;
       };
@@ -206,7 +206,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
         if (AE_BWD_NBUF > 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
         if (!ok) break;
         AE_TR(true, 0, s * 4 + 0)
-        ok = mbar_wait(&bars->ds_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 26);
+        ok = mbar_wait_w(&bars->ds_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 26);
         if (!ok) break;
         AE_TR(true, 0, s * 4 + 1)
         tc_fence_after_sync();
@@ -214,9 +214,9 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
         const u64 dkm = dkmn0 + (u64)((stage * AE_DQ_K_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_BWD_BN / 16; ++kk)
-          umma_ts(tmem + TM_DQ, tm_ds + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(dkm, kk), idesc_dq, (s > 0) | (kk > 0));
-        umma_commit(&bars->k_empty[stage]);
-        if (s + 1 == n_steps) umma_commit(&bars->dq_done);
+          umma_ts_w(tmem + TM_DQ, tm_ds + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(dkm, kk), idesc_dq, (s > 0) | (kk > 0));
+        umma_commit_w(&bars->k_empty[stage]);
+        if (s + 1 == n_steps) umma_commit_w(&bars->dq_done);
         AE_TR(true, 0, s * 4 + 2)
         if (AE_BWD_NBUF == 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
       }

@@ -16,6 +16,7 @@ does not depend on operand order the way the reference's in-place buffer reuse d
 from __future__ import annotations
 
 import math
+import re
 from dataclasses import dataclass, field
 from typing import Callable, Optional
 
@@ -649,6 +650,9 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     em = Emitter(env, idx_env, tile_mode="scalar")
     gres = em.ref(raw_b.grad) if raw_b.grad is not None else "0.f"
     uses_doosum = "doosum" in em.used_leaves
+    ds_body = em.body()
+    # score_mod'(s) needs the raw score again only when score_mod is not affine in it
+    ds_uses_s = re.search(r"\bs\b", ds_body + str(gres)) is not None
     bsrc.append("// dS from dP and P: score_mod'(s) * OnlineFunc.backward(dp, p, final row scales, doosum)\n"
                 "AE_DEVICE float ae_bwd_ds(float s, float dp, float p, const float* fr, float doosum, int b, int h, "
                 "int q_idx, int kv_idx, const AeCustom& cu) {\n  const int sel = 0; (void)sel;\n" + em.body() + f"  return {gres};\n}}\n")
@@ -656,6 +660,7 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     defines = {
         "AE_D": D, "AE_DV": DV, "AE_BF16": int(bf16), "AE_STAGES": stages, "AE_MASK_MODE": mask_mode,
         "AE_NFINAL": len(final_names), "AE_O_SCALE_ONE": int(o_scale_one), "AE_USES_DOOSUM": int(uses_doosum),
+        "AE_DS_USES_S": int(ds_uses_s),
         "AE_MASK_NEG_INF": int(str(mask_value).strip() in ("-inf", "-float('inf')")),
     }
     head = "".join(f"#define {k} {v}\n" for k, v in defines.items()) + "struct AeCustom;\n"
