@@ -26,13 +26,13 @@ class BwdKernels:
 
 
 def bwd_tile_config(D: int, DV: int):
-    """(streamed tile rows, TMEM buffers, ring depth).  Two S/dP buffers of 64 columns fit next to
-    the accumulators in the 512 TMEM columns and let the tensor pipe run ahead of the row threads."""
+    """(streamed kv-tile rows, unused, K / V ring depth) of the dQ pass: Q and dO live in TMEM next to one S and one
+    dP region of 128 columns and the dQ accumulator; three 128-row K and V slots fill shared memory at head dim 128."""
     cfg = os.environ.get("AE_B200_BWD_TILE")  # "bn,nbuf,stages": tuning override
     if cfg:
         bn, nbuf, stages = (int(x) for x in cfg.split(","))
         return bn, nbuf, stages
-    return 64, 2, 4 if max(D, DV) <= 64 else 3
+    return 128, 1, 3
 
 
 def dkv_tile_config(D: int, DV: int):
@@ -50,14 +50,12 @@ def compile_bwd(k) -> BwdKernels:
     bn, nbuf, stages = bwd_tile_config(D, DV)
     defs = f"#define AE_BWD_BN {bn}\n#define AE_BWD_NBUF {nbuf}\n#define AE_BWD_STAGES {stages}\n"
     prelude = low.prelude_bwd + defs
-    # the dQ pass has TMEM room for a third S/dP buffer (3 x 128 + 128 columns)
-    nbuf_dq = int(os.environ.get("AE_B200_DQ_NBUF", nbuf))
-    stages_dq = max(stages, nbuf_dq + 1) if max(D, DV) > 64 else stages
-    prelude_dq = low.prelude_bwd + f"#define AE_BWD_BN {bn}\n#define AE_BWD_NBUF {nbuf_dq}\n#define AE_BWD_STAGES {stages_dq}\n"
+    stages_dq = stages
+    prelude_dq = prelude
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_PREP, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=256,
                           smem_bytes=0, stages=0, mask_mode=k.mask_mode)
     prep = rt.compile_module(rt.kernel_source("attn_bwd_prep.cuh", prelude=prelude), "ae_attn_bwd_prep", cfg)
-    smem_dq = 128 * (D + DV) * 2 + stages_dq * bn * (D + DV) * 2 + 512 + 1024
+    smem_dq = stages_dq * bn * (D + DV) * 2 + 512 + 1024  # Q / dO land in the last K / V slot
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DQ, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
                           smem_bytes=smem_dq, stages=stages_dq, mask_mode=k.mask_mode)
     cfg.reserved[0] = bn

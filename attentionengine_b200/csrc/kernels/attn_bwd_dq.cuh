@@ -7,46 +7,53 @@
 // recomputed in both passes.
 //
 // One CTA owns one 128-row q tile of one (batch, q-head) and streams K/V tiles of AE_BWD_BN
-// rows.  Per kv tile:
-//   S  = Q  K^T   (SS MMA)        dP = dO V^T   (SS MMA)
-//   row threads: T = score_mod(S); P = OnlineFunc.forward(T); mask; dT = OnlineFunc.backward(dP, P);
-//                dS = score_mod'(S) dT  -> 16-bit pairs written over S in TMEM
+// (= 128) rows.  Q and dO are copied once from shared memory into TMEM as 16-bit pairs, so every MMA
+// of the loop takes its A operand from TMEM and only the streamed K / V tile is read from shared
+// memory (an MMA with both operands there is bound by shared-memory bandwidth).  Per kv tile s:
+//   S  = Q  K^T   (TS MMA)        dP = dO V^T   (TS MMA)
+//   row threads, phase A: T = score_mod(S); P = OnlineFunc.forward(T), kept in registers;
+//                phase B: dT = OnlineFunc.backward(dP, P); dS = score_mod'(S) dT -> 16-bit pairs over dP
 //   dQ += dS K    (TS MMA, K tile read MN-major)
-// TMEM columns: AE_BWD_NBUF x (S | dP) then dQ.  With two buffers the tensor pipe computes the
-// next tile's S / dP while the row threads work on the current one.
+// TMEM columns: Q | dO | S | dP | dQ.  The tensor pipe executes MMAs in issue order; the issue order is
+//   S_{s+1} (after phase A of s has read S_s) , dQ_s (after phase B of s) , dP_{s+1}
+// so the row threads run phase B of s under S_{s+1} and phase A of s+1 under dQ_s / dP_{s+1}.
 // Roles: warps 0-3 and 4-7 row threads (thread = q row = TMEM lane; the two groups take alternate
 // 32-column chunks of every tile), warp 8 TMA producer, warp 9 MMA issuer.  The 16-bit dS pairs of a
-// chunk are written over the first 16 columns of that chunk, so a group only overwrites what it has read.
+// chunk are written over the first 16 columns of that chunk of dP, so a group only overwrites what it has read.
+// Shared memory: AE_BWD_STAGES (= 3) slots each for K and V; the last slot of each is where Q and dO land
+// first and becomes a ring slot once they have been copied to TMEM.
 
 #define AE_BM 128
 #define AE_NTHREADS_BWD 320
 // Optional phase trace of CTA (0, 0, 0): 32-bit clock stamps behind the status word (bring-up / tuning only).
 #ifdef AE_TRACE
 #define AE_TR(cond, region, slot) \
-  if (trace_on && (cond) && (slot) < 1024) args.status[64 + (region) * 4096 + (slot)] = (u32)clock64();
+  if (trace_on && (cond) && (slot) < 2048) args.status[64 + (region) * 4096 + (slot)] = (u32)clock64();
 #else
 #define AE_TR(cond, region, slot)
 #endif
 #define AE_NSUB (128 / AE_BWD_BN)
 
-#define AE_DQ_Q_BYTES (AE_BM * AE_D * 2)
-#define AE_DQ_DO_BYTES (AE_BM * AE_DV * 2)
 #define AE_DQ_K_BYTES (AE_BWD_BN * AE_D * 2)
 #define AE_DQ_V_BYTES (AE_BWD_BN * AE_DV * 2)
-#define AE_DQ_SMEM_Q 0
-#define AE_DQ_SMEM_DO (AE_DQ_Q_BYTES)
-#define AE_DQ_SMEM_K (AE_DQ_SMEM_DO + AE_DQ_DO_BYTES)
-#define AE_DQ_SMEM_V (AE_DQ_SMEM_K + AE_BWD_STAGES * AE_DQ_K_BYTES)
+#define AE_DQ_SMEM_K 0
+#define AE_DQ_SMEM_V (AE_BWD_STAGES * AE_DQ_K_BYTES)
+#define AE_DQ_SMEM_Q (AE_DQ_SMEM_K + (AE_BWD_STAGES - 1) * AE_DQ_K_BYTES)   // = last K slot
+#define AE_DQ_SMEM_DO (AE_DQ_SMEM_V + (AE_BWD_STAGES - 1) * AE_DQ_V_BYTES)  // = last V slot
 #define AE_DQ_SMEM_BAR (AE_DQ_SMEM_V + AE_BWD_STAGES * AE_DQ_V_BYTES)
+#if AE_BWD_BN != 128
+#error "the dQ pass streams 128-row K / V tiles"
+#endif
 
 struct AeDqBars {
-  u64 qdo_full;
+  u64 qdo_full;   // Q and dO landed in shared memory
+  u64 qdo_tmem;   // ... and were copied to TMEM (their shared-memory slots are free)
   u64 k_full[AE_BWD_STAGES];
   u64 k_empty[AE_BWD_STAGES];
   u64 v_full[AE_BWD_STAGES];
   u64 v_empty[AE_BWD_STAGES];
-  u64 sp_full[AE_BWD_NBUF];
-  u64 ds_full[AE_BWD_NBUF];
+  u64 s_full, dp_full;  // S / dP of a step are in TMEM
+  u64 a_done, ds_full;  // the row threads have read S / written dS
   u64 dq_done;
   AeCtaCtl ctl;
 };
@@ -103,6 +110,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
   if (threadIdx.x == 0) {
     ctl->abort = 0;
     mbar_init(&bars->qdo_full, 1);
+    mbar_init(&bars->qdo_tmem, 8);
     mbar_init(&bars->dq_done, 1);
     for (int i = 0; i < AE_BWD_STAGES; ++i) {
       mbar_init(&bars->k_full[i], 1);
@@ -110,10 +118,10 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       mbar_init(&bars->v_full[i], 1);
       mbar_init(&bars->v_empty[i], 1);
     }
-    for (int i = 0; i < AE_BWD_NBUF; ++i) {
-      mbar_init(&bars->sp_full[i], 1);
-      mbar_init(&bars->ds_full[i], 8);
-    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->a_done, 8);
+    mbar_init(&bars->ds_full, 8);
     mbar_fence_init();
   }
   if (warp == 9) {
@@ -124,7 +132,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
   __syncthreads();
   tc_fence_after_sync();
   const u32 tmem = ctl->tmem_base;
-  const u32 TM_DQ = AE_BWD_NBUF * 2 * AE_BWD_BN;
+  const u32 TM_Q = 0, TM_DO = AE_D / 2, TM_S = (AE_D + AE_DV) / 2, TM_DP = TM_S + AE_BWD_BN, TM_DQ = TM_DP + AE_BWD_BN;
 
   if (warp == 8) {
     // =============================== TMA producer ===============================
@@ -133,7 +141,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       tma_prefetch_desc(&args.tm_k);
       tma_prefetch_desc(&args.tm_v);
       tma_prefetch_desc(&args.tm_do);
-      mbar_arrive_expect_tx(&bars->qdo_full, AE_DQ_Q_BYTES + AE_DQ_DO_BYTES);
+      mbar_arrive_expect_tx(&bars->qdo_full, AE_BM * (AE_D + AE_DV) * 2);
       for (int dh = 0; dh < AE_D / 64; ++dh)
         tma_load_4d(smem + AE_DQ_SMEM_Q + dh * (AE_BM * 128), &args.tm_q, &bars->qdo_full, dh * 64, hq, q0, b);
       for (int dh = 0; dh < AE_DV / 64; ++dh)
@@ -144,6 +152,8 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
         step_info(s, kv0, partial);
         const int stage = s % AE_BWD_STAGES;
         const u32 par = ((s / AE_BWD_STAGES) & 1) ^ 1;
+        // the last slot holds Q / dO until the row threads have moved them to TMEM
+        if (s == AE_BWD_STAGES - 1 && !mbar_wait(&bars->qdo_tmem, 0, ctl, args.status, 20)) break;
         if (!mbar_wait(&bars->k_empty[stage], par, ctl, args.status, 21)) break;
         mbar_arrive_expect_tx(&bars->k_full[stage], AE_DQ_K_BYTES);
         for (int dh = 0; dh < AE_D / 64; ++dh)
@@ -161,64 +171,68 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
     if (n_steps > 0) {  // all 32 lanes run the control flow; single MMAs and commits are issued by an elected lane
       const u32 idesc_s = umma_idesc_f16(AE_BM, AE_BWD_BN, AE_BF16, 0, 0);
       const u32 idesc_dq = umma_idesc_f16(AE_BM, AE_D, AE_BF16, 0, 1);
-      const u32 q_addr = smem_u32(smem + AE_DQ_SMEM_Q);
-      const u32 do_addr = smem_u32(smem + AE_DQ_SMEM_DO);
       const u32 k_addr = smem_u32(smem + AE_DQ_SMEM_K);
       const u32 v_addr = smem_u32(smem + AE_DQ_SMEM_V);
-      bool ok = mbar_wait_w(&bars->qdo_full, 0, ctl, args.status, 23);
-      const u64 dq0 = umma_base_k(q_addr), ddo0 = umma_base_k(do_addr);
       const u64 dk0 = umma_base_k(k_addr), dv0 = umma_base_k(v_addr);
       const u64 dkmn0 = umma_base_mn(k_addr, AE_BWD_BN);
 
-      auto issue_sp = [&](int s) -> bool {
+      auto issue_s = [&](int s) -> bool {  // S_s = Q K_s^T
         const int stage = s % AE_BWD_STAGES;
-        const u32 par = (s / AE_BWD_STAGES) & 1;
-        const int buf = s % AE_BWD_NBUF;
-        const u32 tm_s = tmem + buf * 2 * AE_BWD_BN;
-        const u32 tm_dp = tm_s + AE_BWD_BN;
-        AE_TR(true, 3, s * 8 + 0)
-        if (!mbar_wait_w(&bars->k_full[stage], par, ctl, args.status, 24)) return false;
+        if (!mbar_wait_w(&bars->k_full[stage], (s / AE_BWD_STAGES) & 1, ctl, args.status, 24)) return false;
         tc_fence_after_sync();
-        AE_TR(true, 3, s * 8 + 1)
+        AE_TR(s > 0, 0, (s - 1) * 8 + 6)
         const u64 dkk = dk0 + (u64)((stage * AE_DQ_K_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_D / 16; ++kk)
-          umma_ss_w(tm_s, umma_step_k(dq0, kk, AE_BM), umma_step_k(dkk, kk, AE_BWD_BN), idesc_s, kk > 0);
-        AE_TR(true, 3, s * 8 + 2)
-        if (!mbar_wait_w(&bars->v_full[stage], par, ctl, args.status, 25)) return false;
+          umma_ts_w(tmem + TM_S, tmem + TM_Q + kk * 8, umma_step_k(dkk, kk, AE_BWD_BN), idesc_s, kk > 0);
+        umma_commit_w(&bars->s_full);
+        return true;
+      };
+      auto issue_dp = [&](int s) -> bool {  // dP_s = dO V_s^T
+        const int stage = s % AE_BWD_STAGES;
+        if (!mbar_wait_w(&bars->v_full[stage], (s / AE_BWD_STAGES) & 1, ctl, args.status, 25)) return false;
         tc_fence_after_sync();
-        AE_TR(true, 3, s * 8 + 3)
+        AE_TR(s > 0, 0, (s - 1) * 8 + 7)
         const u64 dvv = dv0 + (u64)((stage * AE_DQ_V_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_DV / 16; ++kk)
-          umma_ss_w(tm_dp, umma_step_k(ddo0, kk, AE_BM), umma_step_k(dvv, kk, AE_BWD_BN), idesc_s, kk > 0);
-        AE_TR(true, 3, s * 8 + 4)
-        umma_commit_w(&bars->sp_full[buf]);
+          umma_ts_w(tmem + TM_DP, tmem + TM_DO + kk * 8, umma_step_k(dvv, kk, AE_BWD_BN), idesc_s, kk > 0);
+        umma_commit_w(&bars->dp_full);
         umma_commit_w(&bars->v_empty[stage]);
-        AE_TR(true, 3, s * 8 + 5)
         return true;
       };
 
-      if (ok) ok = issue_sp(0);
+      bool ok = mbar_wait_w(&bars->qdo_tmem, 0, ctl, args.status, 23);
+      tc_fence_after_sync();
+      if (ok) ok = issue_s(0);
+      if (ok) ok = issue_dp(0);
       for (int s = 0; s < n_steps && ok; ++s) {
         const int stage = s % AE_BWD_STAGES;
-        const int buf = s % AE_BWD_NBUF;
-        if (AE_BWD_NBUF > 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
+        const u32 par = s & 1;
+        AE_TR(true, 0, s * 8 + 0)
+        // the next S goes over S_s once the row threads have read it
+        ok = mbar_wait_w(&bars->a_done, par, ctl, args.status, 26);
         if (!ok) break;
-        AE_TR(true, 0, s * 4 + 0)
-        ok = mbar_wait_w(&bars->ds_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 26);
-        if (!ok) break;
-        AE_TR(true, 0, s * 4 + 1)
         tc_fence_after_sync();
-        const u32 tm_ds = tmem + buf * 2 * AE_BWD_BN;  // dS pairs over the S columns
+        AE_TR(true, 0, s * 8 + 1)
+        if (s + 1 < n_steps) ok = issue_s(s + 1);
+        if (!ok) break;
+        AE_TR(true, 0, s * 8 + 2)
+        // dQ += dS_s K_s, then the next dP goes over dS_s
+        ok = mbar_wait_w(&bars->ds_full, par, ctl, args.status, 29);
+        if (!ok) break;
+        tc_fence_after_sync();
+        AE_TR(true, 0, s * 8 + 3)
         const u64 dkm = dkmn0 + (u64)((stage * AE_DQ_K_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_BWD_BN / 16; ++kk)
-          umma_ts_w(tmem + TM_DQ, tm_ds + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(dkm, kk), idesc_dq, (s > 0) | (kk > 0));
+          umma_ts_w(tmem + TM_DQ, tmem + TM_DP + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(dkm, kk), idesc_dq,
+                    (s > 0) | (kk > 0));
         umma_commit_w(&bars->k_empty[stage]);
         if (s + 1 == n_steps) umma_commit_w(&bars->dq_done);
-        AE_TR(true, 0, s * 4 + 2)
-        if (AE_BWD_NBUF == 1 && s + 1 < n_steps) ok = issue_sp(s + 1);
+        AE_TR(true, 0, s * 8 + 4)
+        if (s + 1 < n_steps) ok = issue_dp(s + 1);
+        AE_TR(true, 0, s * 8 + 5)
       }
     }
   } else {
@@ -229,6 +243,30 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
     const int q_idx = q0 + (int)row;
     const bool row_valid = q_idx < args.Sq;
     const i64 rs_off = ((i64)b * args.Hq + hq) * args.Sq + (row_valid ? q_idx : 0);
+    bool ok = true;
+
+    // ---- Q (group 0) and dO (group 1) rows: shared memory -> TMEM, once ------------------------
+    if (n_steps > 0) {
+      ok = mbar_wait(&bars->qdo_full, 0, ctl, args.status, 19);
+      const u8* src = smem + (wg ? AE_DQ_SMEM_DO : AE_DQ_SMEM_Q);
+      const int nblk = (wg ? AE_DV : AE_D) / 64;
+      const u32 tm = tmem + (wg ? TM_DO : TM_Q) + lane_base;
+      for (int blk = 0; blk < nblk; ++blk) {
+        u32 w[32];
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint4 v = *(const uint4*)(src + blk * (AE_BM * 128) + swz128(row, ch));
+          w[ch * 4 + 0] = v.x;
+          w[ch * 4 + 1] = v.y;
+          w[ch * 4 + 2] = v.z;
+          w[ch * 4 + 3] = v.w;
+        }
+        tmem_st32(tm + blk * 32, w);  // column c of a row holds its elements 2c, 2c + 1: the A-operand layout
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive_warp(&bars->qdo_tmem);
+    }
 
     AeCustom cu;
 #pragma unroll
@@ -246,62 +284,95 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
     const float delta = 0.f;
 #endif
 
-    bool ok = true;
+    constexpr int NCH = AE_BWD_BN / 64;  // 32-column chunks per group and tile
+    const u32 tm_s = tmem + TM_S + lane_base;
+    const u32 tm_dp = tmem + TM_DP + lane_base;
     for (int s = 0; s < n_steps; ++s) {
       int kv0;
       bool partial;
       step_info(s, kv0, partial);
-      const int buf = s % AE_BWD_NBUF;
-      const u32 tm_s = tmem + buf * 2 * AE_BWD_BN + lane_base;
-      const u32 tm_dp = tm_s + AE_BWD_BN;
-      AE_TR((warp & 3) == 0, 1 + wg, s * 4 + 0)
-      ok = ok && mbar_wait(&bars->sp_full[buf], (s / AE_BWD_NBUF) & 1, ctl, args.status, 27);
-      tc_fence_after_sync();
-      AE_TR((warp & 3) == 0, 1 + wg, s * 4 + 1)
-      const bool tail = kv0 + AE_BWD_BN > args.Skv;
-      auto chunk = [&](auto masked_tag, int c) {
-        constexpr bool kMasked = decltype(masked_tag)::value;
-        float sv[32], dp[32];
-        tmem_ld_2xf32x32(tm_s + c * 32, tm_dp + c * 32, sv, dp);
-        u32 pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float ds2[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int kv_idx = kv0 + c * 32 + i + e;
-            const float sraw = sv[i + e];
-            float p = ae_bwd_p(sraw, fr, b, hq, q_idx, kv_idx, cu, i + e);
-            float dpv = dp[i + e];
-            bool keep = true;
-            if (kMasked) {
-              keep = kv_idx < args.Skv;
-#if AE_MASK_MODE != 0
-              if (partial) keep = keep && ae_mask(b, hq, q_idx, kv_idx);
+      const bool masked = partial || (kv0 + AE_BWD_BN > args.Skv);
+      float pkeep[NCH][32];
+#if AE_DS_USES_S
+      float skeep[NCH][32];
 #endif
-              if (!keep) {
-                p = 0.f;
-                dpv = 0.f;
-              }
-            }
-            float dsv = ae_bwd_ds(sraw, dpv, p, fr, delta, b, hq, q_idx, kv_idx, cu);
-            if (kMasked && !keep) dsv = 0.f;
-            ds2[e] = dsv;
-          }
-          pk[i >> 1] = pack2<AE_BF16>(ds2[0], ds2[1]);
-        }
-        tmem_st16(tm_s + c * 32, pk);  // pairs go over this chunk's own first 16 columns
+      auto keep_of = [&](int kv_idx) -> bool {
+        bool keep = kv_idx < args.Skv;
+#if AE_MASK_MODE != 0
+        if (partial) keep = keep && ae_mask(b, hq, q_idx, kv_idx);
+#endif
+        return keep;
       };
-      if (partial || tail) {
-        for (int c = wg; c < AE_BWD_BN / 32; c += 2) chunk(AeTrue{}, c);
-      } else {
-        for (int c = wg; c < AE_BWD_BN / 32; c += 2) chunk(AeFalse{}, c);
-      }
-      AE_TR((warp & 3) == 0, 1 + wg, s * 4 + 2)
+
+      // ---- phase A: P from S -------------------------------------------------------------------
+      AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 0)
+      ok = ok && mbar_wait(&bars->s_full, s & 1, ctl, args.status, 27);
+      tc_fence_after_sync();
+      AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 1)
+      auto phase_a = [&](auto masked_tag) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
+#pragma unroll
+        for (int ci = 0; ci < NCH; ++ci) {
+          const int c = wg + 2 * ci;
+          float sv[32];
+          tmem_ld_f32x32(tm_s + c * 32, sv);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kv_idx = kv0 + c * 32 + i;
+            float p = ae_bwd_p(sv[i], fr, b, hq, q_idx, kv_idx, cu, i);
+            if (kMasked && !keep_of(kv_idx)) p = 0.f;
+            pkeep[ci][i] = p;
+#if AE_DS_USES_S
+            skeep[ci][i] = sv[i];
+#endif
+          }
+        }
+      };
+      if (masked) phase_a(AeTrue{}); else phase_a(AeFalse{});
+      tc_fence_before_sync();
+      mbar_arrive_warp(&bars->a_done);  // S_s has been read: the next S may overwrite it
+      AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 2)
+
+      // ---- phase B: dS from dP and the P kept in registers ----------------------------------------
+      ok = ok && mbar_wait(&bars->dp_full, s & 1, ctl, args.status, 18);
+      tc_fence_after_sync();
+      AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 3)
+      auto phase_b = [&](auto masked_tag) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
+#pragma unroll
+        for (int ci = 0; ci < NCH; ++ci) {
+          const int c = wg + 2 * ci;
+          float dp[32];
+          tmem_ld_f32x32(tm_dp + c * 32, dp);
+          u32 pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float ds2[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int kv_idx = kv0 + c * 32 + i + e;
+#if AE_DS_USES_S
+              const float sraw = skeep[ci][i + e];
+#else
+              const float sraw = 0.f;
+#endif
+              bool keep = true;
+              if (kMasked) keep = keep_of(kv_idx);
+              float dsv = ae_bwd_ds(sraw, keep ? dp[i + e] : 0.f, pkeep[ci][i + e], fr, delta, b, hq, q_idx, kv_idx, cu);
+              if (kMasked && !keep) dsv = 0.f;
+              ds2[e] = dsv;
+            }
+            pk[i >> 1] = pack2<AE_BF16>(ds2[0], ds2[1]);
+          }
+          tmem_st16(tm_dp + c * 32, pk);  // pairs go over this chunk's own first 16 columns
+        }
+      };
+      if (masked) phase_b(AeTrue{}); else phase_b(AeFalse{});
+      AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 4)
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive_warp(&bars->ds_full[buf]);
-      AE_TR((warp & 3) == 0, 1 + wg, s * 4 + 3)
+      mbar_arrive_warp(&bars->ds_full);
+      AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 5)
     }
 
     // ---- epilogue: dQ rows -------------------------------------------------------------
