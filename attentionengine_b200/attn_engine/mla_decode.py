@@ -49,9 +49,10 @@ class MlaDecode:
 
     @staticmethod
     def pick_splits(B: int, S: int) -> int:
-        """Enough CTAs (2 per batch row and split) for about two waves of the 148 SMs, never an empty split."""
+        """Enough CTAs (2 per batch row and split) to cover the 148 SMs once, never an empty split: a second split
+        re-reads nothing but adds the combine pass, which measured slower as soon as one wave was full."""
         n_tiles = -(-S // MLA_BN)
-        want = max(1, -(-2 * N_SM // (2 * B)))
+        want = max(1, -(-N_SM // (2 * B)))
         n = min(want, 32, n_tiles)
         while n > 1 and (n - 1) * (-(-n_tiles // n)) >= n_tiles:
             n -= 1

@@ -230,10 +230,12 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       bool have = next_step(cur);
       int it = 0;
       u32 np0 = 0, np1 = 0;  // P tiles consumed per q tile
+      u32 q_ready = 0;       // bit t: Q tile t has landed
       auto first_s = [&](auto T) {
         constexpr int t = decltype(T)::value;
         if (!ok || !(cur.flags & (1u << t))) return;
         ok = mbar_wait(&bars->q_full[t], 0, ctl, args.status, 4);
+        q_ready |= 1u << t;
         tc_fence_after_sync();
         issue_s(T, 0);
         umma_commit(&bars->s_full[t]);
@@ -274,8 +276,11 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
               if (!ok) return;
               k_ready = true;
             }
-            ok = mbar_wait(&bars->q_full[t], 0, ctl, args.status, 8);  // Q landed (phase 0 stays complete)
-            if (!ok) return;
+            if (!(q_ready & (1u << t))) {  // Q of this tile is awaited once
+              ok = mbar_wait(&bars->q_full[t], 0, ctl, args.status, 8);
+              if (!ok) return;
+              q_ready |= 1u << t;
+            }
             tc_fence_after_sync();
             issue_s(T, nstage);
             umma_commit(&bars->s_full[t]);
