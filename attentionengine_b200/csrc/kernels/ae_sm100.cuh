@@ -405,6 +405,14 @@ AE_DEVICE float ae_exp2_mix(float x, int idx) {
   return ae_exp2(x);
 }
 AE_DEVICE float ae_log(float x) { return ae_log2(x) * AE_LN2; }
+// Running maximum that is only replaced when it would grow by more than AE_LAZY_TAU: with the softmax family of
+// recurrences every result is unchanged (the states enter through differences that cancel), the rescale factor of the
+// output accumulator is exactly 1 on most tiles, and P stays below e^AE_LAZY_TAU.  Used only where the lowering has
+// verified that invariance numerically on the traced recurrence.
+#ifndef AE_LAZY_TAU
+#define AE_LAZY_TAU 5.0f
+#endif
+AE_DEVICE float ae_lazy_max(float old_v, float x) { return (x - old_v > AE_LAZY_TAU) ? x : old_v; }
 
 // 4 x (32 lanes x 32 columns) TMEM load followed by tcgen05.wait::ld in ONE asm statement, so the
 // compiler cannot schedule a use of the destination registers before the wait.

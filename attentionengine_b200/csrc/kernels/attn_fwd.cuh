@@ -357,20 +357,19 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         }
       }
 #if !AE_O_SCALE_ONE
-      if (n_done > 0) {
-        // O of the previous step must be complete before it is rescaled
+      // O is rescaled only when some row of the warp needs it; only then must the previous step's P V have
+      // completed.  (A skipped wait cannot alias: o_done runs at most one phase ahead of this warp's arrivals.)
+      if (n_done > 0 && __any_sync(0xffffffffu, o_scale != 1.0f)) {
         ok = ok && mbar_wait(&bars->o_done[t], (n_done - 1) & 1, ctl, args.status, 10);
         tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, o_scale != 1.0f)) {
 #pragma unroll
-          for (int c = 0; c < AE_DV / 32; ++c) {
-            float f[32];
-            u32 r[32];
-            tmem_ld_f32x32(tm_o + c * 32, f);
+        for (int c = 0; c < AE_DV / 32; ++c) {
+          float f[32];
+          u32 r[32];
+          tmem_ld_f32x32(tm_o + c * 32, f);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(f[i] * o_scale);
-            tmem_st32(tm_o + c * 32, r);
-          }
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(f[i] * o_scale);
+          tmem_st32(tm_o + c * 32, r);
         }
       }
 #endif

@@ -84,6 +84,7 @@ class Emitter:
         self.names: dict[int, tuple[str, str]] = {}   # id(value) -> (expr, kind), materialised
         self.aff: dict[int, tuple] = {}               # id(value) -> (base (expr, kind), a Scal|None, b Scal|None)
         self.used_leaves: set[str] = set()
+        self.lazy_max: dict[int, int] = {}  # id(Max node) -> index of the operand that is the previous state
         self.k = 0
 
     # -- helpers -------------------------------------------------------------------------------
@@ -319,7 +320,11 @@ class Emitter:
         # ---- row / uniform scalars -----------------------------------------------------------------
         args = [self.ref(p, "c") for p in v.prev]
         name = self._tmp()
-        self.lines.append(f"const float {name} = {self._expr(t, args)};")
+        if id(v) in self.lazy_max:  # running maximum kept while it grows by less than AE_LAZY_TAU
+            i_old = self.lazy_max[id(v)]
+            self.lines.append(f"const float {name} = ae_lazy_max({args[i_old]}, {args[1 - i_old]});")
+        else:
+            self.lines.append(f"const float {name} = {self._expr(t, args)};")
         self.names[id(v)] = (name, kind)
 
     @staticmethod
@@ -512,6 +517,65 @@ def lower_combine(online_func) -> str:
     return ("AE_DEVICE float ae_combine(const float* fr) {\n  const int sel = 0; (void)sel;\n" + em.body() + f"  return {res};\n}}\n")
 
 
+LAZY_TAU = 5.0  # a running maximum is kept while it would grow by less than this (P then stays below e^5 = 148)
+
+
+def _lazy_max_candidates(rs_in: dict, new_rs: dict) -> dict[int, int]:
+    """Row states updated as max(previous value, something): id(Max node) -> operand index of the previous value."""
+    out = {}
+    for k, v in new_rs.items():
+        if isinstance(v, SymbolScalar) and v.code.type == "Max" and len(v.prev) == 2 and k in rs_in:
+            for i in (0, 1):
+                if v.prev[i] is rs_in[k]:
+                    out[id(v)] = i
+    return out
+
+
+def _lazy_max_is_invariant(online_func, raw, t_scores, rs_in, new_scores, new_rs, o_scale, lazy) -> bool:
+    """Numerical test, on the traced recurrence itself, that keeping a stale running maximum changes no result:
+    runs the tile-by-tile recurrence (O = O * o_scale + P V) on random scores with and without the lazy rule and
+    compares the epilogue's outputs and final row scales.  True for the softmax family (the states are only used
+    through differences that cancel), False for anything else, which then keeps the exact maximum."""
+    from .torch_eval import evaluate
+    try:
+        g = torch.Generator().manual_seed(7)
+        R, N, T, DV = 16, 32, 6, 8
+        scores = [torch.randn(R, N, generator=g, dtype=torch.float64) * (1.0 + 3.0 * t) for t in range(T)]
+        vals = [torch.randn(N, DV, generator=g, dtype=torch.float64) for _ in range(T)]
+        init = {k: float(str(v.code.name if v.code.type == "Var" else v.code.value).replace("inf", "1e30"))
+                for k, v in online_func.online_rowscales.items()}
+        zero = {id(x): torch.zeros(1, dtype=torch.float64) for x in ()}
+
+        def run(lazy_on: bool):
+            st = {k: torch.full((R, 1), init[k], dtype=torch.float64) for k in rs_in}
+            o = torch.zeros(R, DV, dtype=torch.float64)
+            hooks = None
+            if lazy_on:
+                def mk(i_old):
+                    return lambda a: torch.where(a[1 - i_old] - a[i_old] > LAZY_TAU, a[1 - i_old] + 0 * a[i_old], a[i_old] + 0 * a[1 - i_old])
+                hooks = {nid: mk(i) for nid, i in lazy.items()}
+            for t in range(T):
+                env = {id(rs_in[k]): st[k] for k in rs_in}
+                env[id(raw)] = scores[t]
+                cache = {}
+                p = evaluate(new_scores, env, cache, hooks)
+                osc = evaluate(o_scale, env, cache, hooks)
+                st = {k: torch.as_tensor(evaluate(v, env, cache, hooks), dtype=torch.float64).expand(R, 1).clone()
+                      for k, v in new_rs.items()}
+                o = o * osc + torch.as_tensor(p) @ vals[t]
+            o_sym = SymbolicArray("o", Var("o"), shape_idx=["block_M", "dimv"])
+            rs_ep = {k: SymbolScalar(k, Var(k), shape_idx=["block_M"]) for k in rs_in}
+            o_new, finals = online_func.online_fwd_epilogue(o_sym, rs_ep, None, None, None)
+            env = {id(rs_ep[k]): st[k] for k in rs_in}
+            env[id(o_sym)] = o
+            return [torch.as_tensor(evaluate(o_new, env))] + [torch.as_tensor(evaluate(f, env)) for f in finals.values()]
+
+        a, b_ = run(False), run(True)
+        return all(torch.isfinite(x).all() and torch.allclose(x, y, rtol=1e-9, atol=1e-9) for x, y in zip(a, b_))
+    except Exception:  # anything the eager evaluator cannot run keeps the exact maximum
+        return False
+
+
 def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomIO, *, D: int, DV: int, bf16: bool,
                     mask_mode: int, stages: int = 2, mask_value: str = "-inf") -> LoweredAttention:
     """Trace the user callables and produce the kernel preludes.
@@ -578,6 +642,9 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     arr_idx_env = dict(idx_env)
     arr_idx_env["kv_idx"] = ("(float)(kv0 + {c})", "tile")
     em = Emitter(env, arr_idx_env, n_cols="N")
+    lazy = _lazy_max_candidates(rs_in, new_rs)
+    if lazy and not specs and _lazy_max_is_invariant(online_func, raw, t_scores, rs_in, new_scores, new_rs, o_scale, lazy):
+        em.lazy_max = lazy
     o_expr, o_kind = em.value(o_scale)
     o_scale_one = (o_kind == "const" and float(o_expr.rstrip("f")) == 1.0)
     new_exprs = {k: em.ref(v) for k, v in new_rs.items()}

@@ -9,7 +9,8 @@ from __future__ import annotations
 import torch
 
 
-def evaluate(v, env: dict, cache: dict | None = None):
+def evaluate(v, env: dict, cache: dict | None = None, hooks: dict | None = None):
+    """`hooks` maps id(node) -> callable(list of evaluated operands) that replaces the node's own rule."""
     cache = {} if cache is None else cache
     key = id(v)
     if key in cache:
@@ -26,9 +27,17 @@ def evaluate(v, env: dict, cache: dict | None = None):
             raise KeyError(f"unbound symbolic value {v.varname!r}")
         cache[key] = r
         return r
-    a = [evaluate(p, env, cache) for p in v.prev]
+    a = [evaluate(p, env, cache, hooks) for p in v.prev]
     T = torch.as_tensor
-    if t == "Add":
+    if hooks and key in hooks:
+        r = hooks[key](a)
+    elif t == "ReduceSum":
+        r = T(a[0]).sum(-1, keepdim=True)
+    elif t == "ReduceMax":
+        r = T(a[0]).amax(-1, keepdim=True)
+    elif t == "ReduceAbsSum":
+        r = T(a[0]).abs().sum(-1, keepdim=True)
+    elif t == "Add":
         r = a[0] + a[1]
     elif t == "Sub":
         r = a[0] - a[1]
