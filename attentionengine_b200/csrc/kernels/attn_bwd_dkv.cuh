@@ -18,7 +18,8 @@
 // of every tile), then one producer warp (TMA loads of Q / dO by one lane, per-column row scales by all
 // lanes) and one MMA-issuing warp.  The 16-bit pairs of a chunk are written over the first 16 columns of
 // that chunk, so a group only overwrites what it has read.
-// Expects AE_BWD_BN (q rows per tile), AE_KV_QSTAGES / AE_KV_DOSTAGES (ring depths), AE_KV_NWG (2 or 4).
+// Expects AE_BWD_BN (q rows per tile), AE_KV_QSTAGES / AE_KV_DOSTAGES (ring depths), AE_KV_NWG (2 or 4),
+// AE_KV_TS (1: K and V resident in TMEM, needs AE_BWD_BN = 64 at head dim 128 for the TMEM budget).
 
 #define AE_KV_BM 128
 // Optional phase trace of CTA (0, 0, 0): 32-bit clock stamps behind the status word (bring-up / tuning only).
@@ -35,10 +36,23 @@
 #define AE_KV_V_BYTES (AE_KV_BM * AE_DV * 2)
 #define AE_KV_Q_BYTES (AE_BWD_BN * AE_D * 2)
 #define AE_KV_DO_BYTES (AE_BWD_BN * AE_DV * 2)
+#ifndef AE_KV_TS
+#define AE_KV_TS 0
+#endif
+#if AE_KV_TS
+// K and V go to TMEM once (S^T and dP^T become TS MMAs, which leave the shared-memory bandwidth to the streamed
+// tiles); they land in the last ring slots of Q / dO, which join the rings after the copy.
+#define AE_KV_SLOTS (AE_KV_BM / AE_BWD_BN)  // ring slots one resident tile covers
+#define AE_KV_SMEM_Q 0
+#define AE_KV_SMEM_DO (AE_KV_QSTAGES * AE_KV_Q_BYTES)
+#define AE_KV_SMEM_K (AE_KV_SMEM_Q + (AE_KV_QSTAGES - AE_KV_SLOTS) * AE_KV_Q_BYTES)
+#define AE_KV_SMEM_V (AE_KV_SMEM_DO + (AE_KV_DOSTAGES - AE_KV_SLOTS) * AE_KV_DO_BYTES)
+#else
 #define AE_KV_SMEM_K 0
 #define AE_KV_SMEM_V (AE_KV_K_BYTES)
 #define AE_KV_SMEM_Q (AE_KV_SMEM_V + AE_KV_V_BYTES)
 #define AE_KV_SMEM_DO (AE_KV_SMEM_Q + AE_KV_QSTAGES * AE_KV_Q_BYTES)
+#endif
 #define AE_KV_SMEM_CS (AE_KV_SMEM_DO + AE_KV_DOSTAGES * AE_KV_DO_BYTES)
 #define AE_KV_CS_BYTES (2 * AE_BWD_BN * AE_NCS * 4)
 #define AE_KV_NROW (AE_KV_NWG * 128)
@@ -47,6 +61,7 @@
 
 struct AeDkvBars {
   u64 kv_full;
+  u64 kv_tmem;  // K and V were copied to TMEM (AE_KV_TS)
   u64 q_full[AE_KV_QSTAGES];
   u64 cs_full[2], cs_empty[2];  // per-column row scales of a q tile (two slots)
   u64 q_empty[AE_KV_QSTAGES];
@@ -150,6 +165,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
   if (threadIdx.x == 0) {
     ctl->abort = 0;
     mbar_init(&bars->kv_full, 1);
+    mbar_init(&bars->kv_tmem, 8);
     mbar_init(&bars->acc_done, 1);
     for (int i = 0; i < AE_KV_QSTAGES; ++i) {
       mbar_init(&bars->q_full[i], 1);
@@ -177,7 +193,12 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
   __syncthreads();
   tc_fence_after_sync();
   const u32 tmem = ctl->tmem_base;
-  const u32 TM_DK = 0, TM_DV = AE_D, TM_S = AE_D + AE_DV, TM_DP = TM_S + AE_BWD_BN;
+#if AE_KV_TS
+  const u32 TM_K = 0, TM_V = AE_D / 2, TM_DK = (AE_D + AE_DV) / 2;
+#else
+  const u32 TM_DK = 0;
+#endif
+  const u32 TM_DV = TM_DK + AE_D, TM_S = TM_DV + AE_DV, TM_DP = TM_S + AE_BWD_BN;
 
   if (warp == AE_KV_NWG * 4) {
     // =============================== producer ====================================
@@ -197,6 +218,9 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
     int s = 0;
     while (next_step(st)) {
       const int sq = s % AE_KV_QSTAGES, sd = s % AE_KV_DOSTAGES;
+#if AE_KV_TS
+      if (s == AE_KV_QSTAGES - AE_KV_SLOTS && !mbar_wait_w(&bars->kv_tmem, 0, ctl, args.status, 43)) break;
+#endif
       if (!mbar_wait_w(&bars->q_empty[sq], ((s / AE_KV_QSTAGES) & 1) ^ 1, ctl, args.status, 31)) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(&bars->q_full[sq], AE_KV_Q_BYTES);
@@ -223,6 +247,9 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         }
         mbar_arrive(&bars->cs_full[s & 1]);
       }
+#if AE_KV_TS
+      if (s == AE_KV_DOSTAGES - AE_KV_SLOTS && !mbar_wait_w(&bars->kv_tmem, 0, ctl, args.status, 44)) break;
+#endif
       if (!mbar_wait_w(&bars->do_empty[sd], ((s / AE_KV_DOSTAGES) & 1) ^ 1, ctl, args.status, 38)) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(&bars->do_full[sd], AE_KV_DO_BYTES);
@@ -253,7 +280,11 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         const u64 dqq = dq0 + (u64)((stage * AE_KV_Q_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_D / 16; ++kk)
+#if AE_KV_TS
+          umma_ts_w(tmem + TM_S, tmem + TM_K + kk * 8, umma_step_k(dqq, kk, AE_BWD_BN), idesc_s, kk > 0);
+#else
           umma_ss_w(tmem + TM_S, umma_step_k(dk0, kk, AE_KV_BM), umma_step_k(dqq, kk, AE_BWD_BN), idesc_s, kk > 0);
+#endif
         umma_commit_w(&bars->s_full);
         return true;
       };
@@ -264,7 +295,11 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         const u64 ddd = ddo0 + (u64)((stage * AE_KV_DO_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_DV / 16; ++kk)
+#if AE_KV_TS
+          umma_ts_w(tmem + TM_DP, tmem + TM_V + kk * 8, umma_step_k(ddd, kk, AE_BWD_BN), idesc_s, kk > 0);
+#else
           umma_ss_w(tmem + TM_DP, umma_step_k(dv0, kk, AE_KV_BM), umma_step_k(ddd, kk, AE_BWD_BN), idesc_s, kk > 0);
+#endif
         umma_commit_w(&bars->dp_full);
         return true;
       };
@@ -275,7 +310,12 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         AeDkvStep st;
         while (next_step(st)) ++n_steps;
       }
+#if AE_KV_TS
+      bool ok = n_steps > 0 && mbar_wait_w(&bars->kv_tmem, 0, ctl, args.status, 34);
+      tc_fence_after_sync();
+#else
       bool ok = n_steps > 0 && mbar_wait_w(&bars->kv_full, 0, ctl, args.status, 34);
+#endif
       if (ok) ok = issue_s(0);
       if (ok) ok = issue_dp(0);
       for (int s = 0; s < n_steps && ok; ++s) {
@@ -331,6 +371,32 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
     }
 
     bool ok = true;
+#if AE_KV_TS
+    // ---- K (group 0) and V (group 1) rows: shared memory -> TMEM, once ------------------------------
+    {
+      ok = mbar_wait(&bars->kv_full, 0, ctl, args.status, 45);
+      const u8* src = smem + (wg ? AE_KV_SMEM_V : AE_KV_SMEM_K);
+      const int nblk = (wg ? AE_DV : AE_D) / 64;
+      const u32 tm = tmem + (wg ? TM_V : TM_K) + lane_base;
+      if (wg < 2) {
+        for (int blk = 0; blk < nblk; ++blk) {
+          u32 w[32];
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint4 v = *(const uint4*)(src + blk * (AE_KV_BM * 128) + swz128(row, ch));
+            w[ch * 4 + 0] = v.x;
+            w[ch * 4 + 1] = v.y;
+            w[ch * 4 + 2] = v.z;
+            w[ch * 4 + 3] = v.w;
+          }
+          tmem_st32(tm + blk * 32, w);  // column c of a row holds its elements 2c, 2c + 1: the A-operand layout
+        }
+        tc_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive_warp(&bars->kv_tmem);
+      }
+    }
+#endif
     int s = 0;
     AeDkvStep st;
     AeDkvStep st_next;

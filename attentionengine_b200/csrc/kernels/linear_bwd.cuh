@@ -109,7 +109,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
     }
   } else if (warp == 5) {
     // =============================== MMA issuer =================================
-    if (lane == 0) {
+    {  // all 32 lanes run the control flow; MMAs and commits are issued by an elected lane
       const u32 Q = smem_u32(smem + AE_LB_SMEM_Q), K = smem_u32(smem + AE_LB_SMEM_K), V = smem_u32(smem + AE_LB_SMEM_V);
       const u32 DO = smem_u32(smem + AE_LB_SMEM_DO), HC = smem_u32(smem + AE_LB_SMEM_HC);
       const u32 P = smem_u32(smem + AE_LB_SMEM_P), DS = smem_u32(smem + AE_LB_SMEM_DS);
@@ -126,51 +126,51 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       bool ok = true;
       for (int it = 0; it < n_chunks && ok; ++it) {
         const u32 par = it & 1;
-        ok = mbar_wait(&bars->full, par, ctl, args.status, 72);
+        ok = mbar_wait_w(&bars->full, par, ctl, args.status, 72);
         if (!ok) break;
         tc_fence_after_sync();
         // A = q k^T -> R0 ; dPr = dO v^T -> R1
 #pragma unroll
         for (int kk = 0; kk < AE_LB_DK / 16; ++kk)
-          umma_ss(tmem + TM_R0, umma_step_k(kQ, kk, 128), umma_step_k(kK, kk, 128), id_kk_128, kk > 0);
+          umma_ss_w(tmem + TM_R0, umma_step_k(kQ, kk, 128), umma_step_k(kK, kk, 128), id_kk_128, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
-          umma_ss(tmem + TM_R1, umma_step_k(kDO, kk, 128), umma_step_k(kV, kk, 128), id_kk_128, kk > 0);
-        umma_commit(&bars->s_full);
-        ok = mbar_wait(&bars->prep_done, par, ctl, args.status, 73);
+          umma_ss_w(tmem + TM_R1, umma_step_k(kDO, kk, 128), umma_step_k(kV, kk, 128), id_kk_128, kk > 0);
+        umma_commit_w(&bars->s_full);
+        ok = mbar_wait_w(&bars->prep_done, par, ctl, args.status, 73);
         if (!ok) break;
-        ok = mbar_wait(&bars->pds_full, par, ctl, args.status, 74);
+        ok = mbar_wait_w(&bars->pds_full, par, ctl, args.status, 74);
         if (!ok) break;
         tc_fence_after_sync();
         // inter-chunk parts (overwrite R0, R1, DV)
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
-          umma_ss(tmem + TM_R0, umma_step_k(kDO, kk, 128), umma_step_k(kHC, kk, 128), id_kk_128, kk > 0);
+          umma_ss_w(tmem + TM_R0, umma_step_k(kDO, kk, 128), umma_step_k(kHC, kk, 128), id_kk_128, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
-          umma_ss(tmem + TM_R1, umma_step_k(kV, kk, 128), umma_step_k(kDHB, kk, 128), id_kk_128, kk > 0);
+          umma_ss_w(tmem + TM_R1, umma_step_k(kV, kk, 128), umma_step_k(kDHB, kk, 128), id_kk_128, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < AE_LB_DK / 16; ++kk)
-          umma_ss(tmem + TM_DV, umma_step_k(kK, kk, 128), umma_step_mn(mDHB, kk), id_kmn_dv, kk > 0);
-        umma_commit(&bars->inter_full);
+          umma_ss_w(tmem + TM_DV, umma_step_k(kK, kk, 128), umma_step_mn(mDHB, kk), id_kmn_dv, kk > 0);
+        umma_commit_w(&bars->inter_full);
         // dH (+)= q^T (dO o exp(g))
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
-          umma_ss(tmem + TM_DH, umma_step_mn(mQ, kk), umma_step_mn(mDO2, kk), id_mnmn_dv, (it > 0) | (kk > 0));
-        ok = mbar_wait(&bars->scaled_done, par, ctl, args.status, 75);
+          umma_ss_w(tmem + TM_DH, umma_step_mn(mQ, kk), umma_step_mn(mDO2, kk), id_mnmn_dv, (it > 0) | (kk > 0));
+        ok = mbar_wait_w(&bars->scaled_done, par, ctl, args.status, 75);
         if (!ok) break;
         tc_fence_after_sync();
         // intra-chunk parts on top
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
-          umma_ss(tmem + TM_R0, umma_step_k(kDS, kk, 128), umma_step_mn(mK, kk), id_kmn_128, 1);
+          umma_ss_w(tmem + TM_R0, umma_step_k(kDS, kk, 128), umma_step_mn(mK, kk), id_kmn_128, 1);
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
-          umma_ss(tmem + TM_R1, umma_step_mn(mDS, kk), umma_step_mn(mQ, kk), id_mnmn_128, 1);
+          umma_ss_w(tmem + TM_R1, umma_step_mn(mDS, kk), umma_step_mn(mQ, kk), id_mnmn_128, 1);
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
-          umma_ss(tmem + TM_DV, umma_step_mn(mP, kk), umma_step_mn(mDO, kk), id_mnmn_dv, 1);
-        umma_commit(&bars->out_full);
+          umma_ss_w(tmem + TM_DV, umma_step_mn(mP, kk), umma_step_mn(mDO, kk), id_mnmn_dv, 1);
+        umma_commit_w(&bars->out_full);
       }
     }
   } else {

@@ -104,7 +104,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
     }
   } else if (warp == 5) {
     // =============================== MMA issuer =================================
-    if (lane == 0 && n_chunks > 0) {
+    if (n_chunks > 0) {  // all 32 lanes run the control flow; MMAs and commits are issued by an elected lane
       const u32 idesc_s = umma_idesc_f16(128, AE_LIN_C, AE_BF16, 0, 0);          // q k^T
       const u32 idesc_oi = umma_idesc_f16(128, AE_LIN_DV, AE_BF16, 0, 1);        // q h, P v
       const u32 idesc_h = umma_idesc_f16(AE_LIN_DK, AE_LIN_DV, AE_BF16, 1, 1);   // k^T v'
@@ -117,42 +117,42 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       const u64 bh_mn = umma_base_mn(h_addr, AE_LIN_DK), bv2_mn = umma_base_mn(v2_addr, AE_LIN_C);
       auto issue_s = [&](int c) -> bool {
         const int stage = c % AE_LIN_STAGES;
-        if (!mbar_wait(&bars->full[stage], (c / AE_LIN_STAGES) & 1, ctl, args.status, 52)) return false;
+        if (!mbar_wait_w(&bars->full[stage], (c / AE_LIN_STAGES) & 1, ctl, args.status, 52)) return false;
         tc_fence_after_sync();
         const u64 so = (u64)((stage * AE_LIN_STAGE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_DK / 16; ++kk)
-          umma_ss(tmem + TM_S, umma_step_k(bq + so, kk, AE_LIN_C), umma_step_k(bk + so, kk, AE_LIN_C), idesc_s, kk > 0);
-        umma_commit(&bars->s_full);
+          umma_ss_w(tmem + TM_S, umma_step_k(bq + so, kk, AE_LIN_C), umma_step_k(bk + so, kk, AE_LIN_C), idesc_s, kk > 0);
+        umma_commit_w(&bars->s_full);
         return true;
       };
       bool ok = issue_s(0);
       for (int c = 0; c < n_chunks && ok; ++c) {
         const int stage = c % AE_LIN_STAGES;
         const u64 so = (u64)((stage * AE_LIN_STAGE_BYTES) >> 4);
-        ok = mbar_wait(&bars->prep_done, c & 1, ctl, args.status, 53);
+        ok = mbar_wait_w(&bars->prep_done, c & 1, ctl, args.status, 53);
         if (!ok) break;
         tc_fence_after_sync();
         if (c > 0) {
           // Oi = q h   (h: [DK rows][DV contiguous], MN-major B)
 #pragma unroll
           for (int kk = 0; kk < AE_LIN_DK / 16; ++kk)
-            umma_ss(tmem + TM_O, umma_step_k(bq + so, kk, AE_LIN_C), umma_step_mn(bh_mn, kk), idesc_oi, kk > 0);
+            umma_ss_w(tmem + TM_O, umma_step_k(bq + so, kk, AE_LIN_C), umma_step_mn(bh_mn, kk), idesc_oi, kk > 0);
         }
-        umma_commit(&bars->oi_full);
+        umma_commit_w(&bars->oi_full);
         // H (+)= k^T v'   (k tile read MN-major as A: [chunk rows][DK contiguous]; v' likewise as B)
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_C / 16; ++kk)
-          umma_ss(tmem + TM_H, umma_step_mn(bk_mn + so, kk), umma_step_mn(bv2_mn, kk), idesc_h, (c > 0) | (kk > 0));
-        umma_commit(&bars->h_done);
-        ok = mbar_wait(&bars->p_full, c & 1, ctl, args.status, 54);
+          umma_ss_w(tmem + TM_H, umma_step_mn(bk_mn + so, kk), umma_step_mn(bv2_mn, kk), idesc_h, (c > 0) | (kk > 0));
+        umma_commit_w(&bars->h_done);
+        ok = mbar_wait_w(&bars->p_full, c & 1, ctl, args.status, 54);
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_C / 16; ++kk)
-          umma_ts(tmem + TM_O, tmem + TM_S + kk * 8, umma_step_mn(bv_mn + so, kk), idesc_oi, (c > 0) | (kk > 0));
-        umma_commit(&bars->o_done);
-        umma_commit(&bars->empty[stage]);
+          umma_ts_w(tmem + TM_O, tmem + TM_S + kk * 8, umma_step_mn(bv_mn + so, kk), idesc_oi, (c > 0) | (kk > 0));
+        umma_commit_w(&bars->o_done);
+        umma_commit_w(&bars->empty[stage]);
         if (c + 1 < n_chunks) ok = issue_s(c + 1);
       }
     }

@@ -99,35 +99,35 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
     }
   } else if (warp == 5) {
     // =============================== MMA issuer =================================
-    if (lane == 0 && n_steps > 0) {
+    if (n_steps > 0) {  // all 32 lanes run the control flow; MMAs and commits are issued by an elected lane
       const u32 idesc_s = umma_idesc_f16(AE_MLA_H, AE_MLA_BN, AE_BF16, 0, 0);
       const u32 idesc_o = umma_idesc_f16(AE_MLA_H, AE_MLA_DVH, AE_BF16, 0, 1);
       const u32 q_addr = smem_u32(smem + AE_MLA_SMEM_Q);
       const u32 kv_addr = smem_u32(smem + AE_MLA_SMEM_KV);
-      bool ok = mbar_wait(&bars->q_full, 0, ctl, args.status, 42);
+      bool ok = mbar_wait_w(&bars->q_full, 0, ctl, args.status, 42);
       const u64 dq0 = umma_base_k(q_addr), dk0 = umma_base_k(kv_addr);
       const u64 dv0 = umma_base_mn(kv_addr + dvh * (AE_MLA_NBV / 2) * (AE_MLA_BN * 128), AE_MLA_BN);
       for (int s = 0; s < n_steps && ok; ++s) {
-        ok = mbar_wait(&bars->kv_full, s & 1, ctl, args.status, 43);
+        ok = mbar_wait_w(&bars->kv_full, s & 1, ctl, args.status, 43);
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int blk = 0; blk < AE_MLA_NBK; ++blk) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tmem + TM_S, dq0 + (u64)((blk * (AE_MLA_H * 128) + kk * 32) >> 4),
+            umma_ss_w(tmem + TM_S, dq0 + (u64)((blk * (AE_MLA_H * 128) + kk * 32) >> 4),
                     dk0 + (u64)((blk * (AE_MLA_BN * 128) + kk * 32) >> 4), idesc_s, (blk | kk) > 0);
         }
-        umma_commit(&bars->s_full);
-        ok = mbar_wait(&bars->p_full, s & 1, ctl, args.status, 44);
+        umma_commit_w(&bars->s_full);
+        ok = mbar_wait_w(&bars->p_full, s & 1, ctl, args.status, 44);
         if (!ok) break;
         tc_fence_after_sync();
         // V = this half's four 64-wide blocks of the same tile, read MN-major
 #pragma unroll
         for (int kk = 0; kk < AE_MLA_BN / 16; ++kk)
-          umma_ts(tmem + TM_O, tmem + TM_S + kk * 8, umma_step_mn(dv0, kk), idesc_o, (s > 0) | (kk > 0));
-        umma_commit(&bars->o_done);
-        umma_commit(&bars->kv_empty);
+          umma_ts_w(tmem + TM_O, tmem + TM_S + kk * 8, umma_step_mn(dv0, kk), idesc_o, (s > 0) | (kk > 0));
+        umma_commit_w(&bars->o_done);
+        umma_commit_w(&bars->kv_empty);
       }
     }
   } else {

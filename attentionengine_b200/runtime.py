@@ -142,9 +142,11 @@ def exp_poly_period() -> int:
     return int(os.environ.get("AE_B200_EXP_POLY", "0"))
 
 
-def kernel_source(*files: str, prelude: str = "") -> str:
-    """Common header + argument blocks + generated prelude + kernel template(s), as one translation unit."""
-    parts = [f"#define AE_EXP_POLY_PERIOD {exp_poly_period()}\n#define AE_WAIT_MODE {int(os.environ.get('AE_B200_WAIT_MODE', '0'))}\n"
+def kernel_source(*files: str, prelude: str = "", exp_poly: int | None = None) -> str:
+    """Common header + argument blocks + generated prelude + kernel template(s), as one translation unit.
+    `exp_poly` is the kernel's own default for AE_EXP_POLY_PERIOD (the environment variable still wins)."""
+    poly = exp_poly_period() if (exp_poly is None or "AE_B200_EXP_POLY" in os.environ) else exp_poly
+    parts = [f"#define AE_EXP_POLY_PERIOD {poly}\n#define AE_WAIT_MODE {int(os.environ.get('AE_B200_WAIT_MODE', '0'))}\n"
              + ("#define AE_TRACE 1\n" if os.environ.get("AE_B200_TRACE") else "")
              + ("#define AE_SELFCHECK 1\n" if os.environ.get("AE_B200_SELFCHECK") else ""),
              (KERNEL_DIR / "ae_sm100.cuh").read_text().replace("#pragma once\n", ""),
