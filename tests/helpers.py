@@ -162,3 +162,41 @@ def mamba2_inputs(B, H, T, DK, DV, dtype, seed=0):
     dt = torch.nn.functional.softplus(torch.randn(B, H, T, generator=g) - 4.0)
     A = -torch.exp(torch.rand(H, generator=g) * math.log(16.0))
     return x, dt, A, Bm, Cm
+
+
+class OnlineRetention(OnlineFunc):
+    """Row normaliser max(sum |score|, 1), the recurrence of attn_script/retention.py:19-71."""
+
+    def __init__(self):
+        super().__init__({"r_wo_clamp": SymbolScalar("r_wo_clamp", Var("0.0")), "r": SymbolScalar("r", Var("0.0"))},
+                         {"r": SymbolScalar("r", Var("0.0"))}, CustomIO())
+
+    @staticmethod
+    def online_fwd(scores, online_rowscales, b, h, q_idx):
+        r_wo_clamp = online_rowscales["r_wo_clamp"] + scores.get_reduce("abssum")
+        r_new = r_wo_clamp.max(1.0)
+        o_scale = online_rowscales["r"] / r_new
+        return scores / r_new, {"r_wo_clamp": r_wo_clamp, "r": r_new}, o_scale
+
+    @staticmethod
+    def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+        return o, {"r": online_rowscales["r"]}
+
+    @staticmethod
+    def forward(scores, final_rowscales, b, h, q_idx, kv_idx):
+        return scores / final_rowscales["r"]
+
+    @staticmethod
+    def backward(dp, scores, final_rowscales, doosum_rowscales, b, h, q_idx, kv_idx):
+        return dp / final_rowscales["r"]
+
+
+def retention_engine(B, H, S, D, DV, dtype):
+    """Parallel retention (attn_script/retention.py:14-17, 93-104): the decay mask is a tile-shaped custom input
+    [1, heads, seq_len, seq_len_kv] multiplied into the scores; causal mask with additive mask value 0."""
+
+    def score_mod(score, custom_fwd_inputs, b, h, q_idx, kv_idx):
+        return score * custom_fwd_inputs.input_tensors["mask"]
+
+    return AttentionEngine(metas(B, H, H, S, D, DV, dtype), CustomIO({"mask": (1, "heads", "seq_len", "seq_len_kv")}),
+                           score_mod=score_mod, mask_mod=causal_mask, online_func=OnlineRetention(), mask_value="0")

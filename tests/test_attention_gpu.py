@@ -12,6 +12,7 @@ import torch
 from oracle import attention_oracle as orc
 
 import helpers
+from attentionengine_b200 import AttentionEngine, CustomIO
 
 pytestmark = pytest.mark.gpu
 
@@ -314,4 +315,60 @@ def test_mamba2_ssd_backward_against_oracle(B, H, T):
     for name, got, ref in zip(names, [t.grad for t in leaves] + [dtb.grad], [C2.grad, B2.grad, x2.grad, dt2.grad, A2.grad, dtb2.grad]):
         mx, rel = orc.error_stats(got.float().cpu(), ref.float())
         lim = 5e-2 if name == "dA" else 1e-2
-        assert rel <= lim, f"{name}: rel-L2 {rel:.3e} (max-abs {mx:.3e})"
+        assert rel <= lim, f"{name}: rel-L2 {rel:.3e} (max-abs {mx:.3e})"@pytest.mark.gpu
+@pytest.mark.parametrize("S,causal", [(384, True), (200, False)])
+def test_softcap_score_mod_keeps_the_raw_score_for_the_backward(S, causal):
+    """score_mod = cap * tanh(score * scale / cap): its derivative needs the raw score again, so the backward passes
+    keep it next to P between their two row phases (the autodiff of Tanh is the reference's, core.py:129-195)."""
+    B, Hq, Hkv, D, dtype, cap = 1, 4, 2, 128, torch.float16, 20.0
+    scale = 1.0 / math.sqrt(D)
+
+    def score_mod(score, custom_fwd_inputs, b, h, q_idx, kv_idx):
+        return (score * (scale / cap)).tanh() * cap
+
+    eng = AttentionEngine(helpers.metas(B, Hq, Hkv, S, D, D, dtype), CustomIO({}), score_mod=score_mod,
+                          mask_mod=helpers.causal_mask if causal else None, online_func=helpers.OnlineSoftmax())
+    assert eng.lowered.defines["AE_DS_USES_S"] == 1
+    q, k, v, d_o = helpers.seeded_qkv(B, Hq, Hkv, S, D, D, dtype, seed=77)
+    q = q * 3.0  # scores large enough for the cap to bend them
+    got = _run(eng, q, k, v, d_o)
+
+    def ref(a, b_, c):
+        g = Hq // Hkv
+        s = torch.einsum("bqhd,bkhd->bhqk", a, b_.repeat_interleave(g, dim=2)) * scale
+        s = torch.tanh(s / cap) * cap
+        if causal:
+            i = torch.arange(S)
+            s = s.masked_fill(i[:, None] < i[None, :], float("-inf"))
+        return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), c.repeat_interleave(g, dim=2))
+
+    o, (dq, dk, dv) = orc.fwd_bwd(ref, (q, k, v), d_o)
+    for name, g_, r in zip(("o", "dq", "dk", "dv"), got, (o, dq, dk, dv)):
+        _check(name, g_, r, dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("S", [256, 384])
+def test_retention_parallel_with_tile_shaped_custom_input(S):
+    """attn_script/retention.py: score * decay mask (custom input [1, H, S, S] in the input dtype), rows normalised by
+    max(sum |.|, 1); forward and the three gradients against the oracle (bench_utils.py:1062-1067)."""
+    B, H, D, DV, dtype = 1, 2, 128, 128, torch.float16
+    q, k, v, d_o = helpers.seeded_qkv(B, H, H, S, D, DV, dtype, seed=21)
+    q, k = q * 0.25, k * 0.25
+    idx = torch.arange(S)
+    gamma = 1.0 - 2.0 ** (-5.0 - torch.arange(H, dtype=torch.float32))
+    dist = (idx[:, None] - idx[None, :]).clamp(min=0).float()
+    mask = (gamma.view(H, 1, 1) ** dist) * (idx[:, None] >= idx[None, :])
+    mask = mask.view(1, H, S, S).to(dtype)
+    eng = helpers.retention_engine(B, H, S, D, DV, dtype)
+    qd, kd, vd = (t.cuda().requires_grad_() for t in (q, k, v))
+    o = eng(qd, kd, vd, mask.cuda())
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    ro, (rq, rk, rv) = orc.fwd_bwd(lambda a, b, c: orc.retention_parallel(a, b, c, mask), (q, k, v), d_o)
+    for name, g, r in zip(("o", "dq", "dk", "dv"), (o, qd.grad, kd.grad, vd.grad), (ro, rq, rk, rv)):
+        _check(name, g.detach().cpu(), r, dtype)
+
+
+
