@@ -15,7 +15,7 @@ import torch
 from .. import runtime as rt
 from ..lower.cuda_lower import lower_attention, lower_combine
 
-MLA_BN = 64  # kv rows per tile (the query block takes 147 KB of shared memory, one 72 KB KV stage fits beside it)
+MLA_BN = 64  # kv rows per tile: five of the nine query blocks (80 KB) and two 72 KB KV stages fill shared memory
 N_SM = 148
 
 
@@ -32,7 +32,7 @@ class MlaDecode:
         self.low = lower_attention(score_mod, None, online_func, custom_fwd_inputs, D=D, DV=DV, bf16=bf16, mask_mode=0)
         tag = rt.DTYPE_BF16 if bf16 else rt.DTYPE_F16
         prelude = self.low.prelude_fwd + f"#define AE_MLA_BN {MLA_BN}\n"
-        smem = 9 * 128 * 128 + 9 * MLA_BN * 128 + 256 + 1024
+        smem = 5 * 128 * 128 + 2 * 9 * MLA_BN * 128 + 256 + 1024  # 230,656 B of the 232,448 a CTA can have
         cfg = rt.KernelConfig(kind=rt.KIND_MLA_DECODE, dtype=tag, head_dim=D, head_dim_v=DV, threads=192,
                               smem_bytes=smem, stages=1, mask_mode=0)
         cfg.reserved[0] = MLA_BN

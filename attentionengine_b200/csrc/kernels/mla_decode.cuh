@@ -3,39 +3,53 @@
 // mla_decode_tl.py:38-177; CuTe variant cute_template_kvshared/kernels/splitkv_mla.cu:1061-1391).
 //
 // All H = 128 query heads of one batch row share one latent KV stream: rows of the MMA are heads.
-//   S = [q | q_pe] [kv | k_pe]^T   over 512 + 64 dims (9 K blocks of 64)        SS MMA, M = 128, N = BN
+//   S = [q | q_pe] [kv | k_pe]^T   over 512 + 64 dims (9 K blocks of 64)        TS / SS MMAs, M = 128, N = BN
 //   row threads (thread = head): fused score_mod + online recurrence, P -> TMEM
 //   O_half += P kv[:, half]          over this CTA's 256 of the 512 value dims     TS MMA, N = 256
 // A [128 x 512] fp32 accumulator would fill all 512 TMEM columns, so the value dims are split
 // over two CTAs (blockIdx.x) that each recompute S; both read the same KV tiles, the second read
 // is an L2 hit.  blockIdx.y is the kv split, blockIdx.z the batch row.  With more than one split
 // the CTA stores its normalised partial O (fp32) and its final row scales; ae_mla_combine merges.
-// The query block (147 KB) is resident in shared memory, which leaves room for a single KV stage:
-// loads overlap compute only across CTAs of a wave, not inside one (the known limiter of this
-// first version).
+// The first AE_MLA_QT (= 4) 64-wide blocks of the query block live in TMEM (16-bit pairs, the A-operand layout of a
+// TS MMA), the other five in shared memory: that leaves room for two KV stages and two S regions, so the loads of
+// tile s+1, its S GEMM and the row work of tile s overlap.  The TMEM-resident blocks first land in KV stage 0.
+// TMEM columns: S0 | S1 | O half (256) | Q blocks 0-3 (128) = 512.
 // Roles: warps 0-3 row threads, warp 4 TMA producer, warp 5 MMA issuer.
-// Expects AE_BF16, AE_NFINAL, AE_O_SCALE_ONE, AE_MLA_BN, struct AeRow, ae_online_fwd(),
+// Expects AE_BF16, AE_NFINAL, AE_O_SCALE_ONE, AE_MLA_BN (64), AE_MLA_ALIGN_SLACK, struct AeRow, ae_online_fwd(),
 // ae_epilogue_o(), ae_final_rowscales().
 
+// Optional phase trace of CTA (0, 0, 0): 32-bit clock stamps behind the status word (bring-up / tuning only).
+#ifdef AE_TRACE
+#define AE_TRM(cond, region, slot) \
+  if (trace_on && (cond) && (slot) < 2048) args.status[64 + (region) * 4096 + (slot)] = (u32)clock64();
+#else
+#define AE_TRM(cond, region, slot)
+#endif
 #define AE_MLA_H 128
 #define AE_MLA_DV 512
 #define AE_MLA_DPE 64
 #define AE_MLA_NBV (AE_MLA_DV / 64)
 #define AE_MLA_NBK (AE_MLA_NBV + AE_MLA_DPE / 64)
 #define AE_MLA_DVH (AE_MLA_DV / 2)
+#define AE_MLA_QT 4        // query blocks resident in TMEM
+#define AE_MLA_STAGES 2
+#if AE_MLA_BN != 64
+#error "the MLA decode kernel streams 64-row KV tiles"
+#endif
 
-#define AE_MLA_Q_BYTES (AE_MLA_NBK * AE_MLA_H * 128)
+#define AE_MLA_QS_BYTES ((AE_MLA_NBK - AE_MLA_QT) * AE_MLA_H * 128)  // query blocks kept in shared memory
 #define AE_MLA_KV_BYTES (AE_MLA_NBK * AE_MLA_BN * 128)
-#define AE_MLA_SMEM_Q 0
-#define AE_MLA_SMEM_KV (AE_MLA_Q_BYTES)
-#define AE_MLA_SMEM_BAR (AE_MLA_SMEM_KV + AE_MLA_KV_BYTES)
+#define AE_MLA_SMEM_QS 0
+#define AE_MLA_SMEM_KV (AE_MLA_QS_BYTES)
+#define AE_MLA_SMEM_BAR (AE_MLA_SMEM_KV + AE_MLA_STAGES * AE_MLA_KV_BYTES)
 
 struct AeMlaBars {
-  u64 q_full;
-  u64 kv_full;
-  u64 kv_empty;
-  u64 s_full;
-  u64 p_full;
+  u64 q_full;   // the whole query block landed in shared memory
+  u64 q_tmem;   // its first blocks were copied to TMEM (KV stage 0 is free)
+  u64 kv_full[AE_MLA_STAGES];
+  u64 kv_empty[AE_MLA_STAGES];
+  u64 s_full[2];
+  u64 p_full[2];
   u64 o_done;
   AeCtaCtl ctl;
 };
@@ -51,6 +65,9 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
   const int split = blockIdx.y;
   const int b = blockIdx.z;
 
+#ifdef AE_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0;
+#endif
   const int n_tiles = (args.S + AE_MLA_BN - 1) / AE_MLA_BN;
   const int t_begin = split * args.tiles_per_split;
   int t_end = t_begin + args.tiles_per_split;
@@ -60,11 +77,14 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
   if (threadIdx.x == 0) {
     ctl->abort = 0;
     mbar_init(&bars->q_full, 1);
-    mbar_init(&bars->kv_full, 1);
-    mbar_init(&bars->kv_empty, 1);
-    mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->p_full, 4);
+    mbar_init(&bars->q_tmem, 4);
     mbar_init(&bars->o_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->kv_full[i], 1);
+      mbar_init(&bars->kv_empty[i], 1);
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->p_full[i], 4);
+    }
     mbar_fence_init();
   }
   if (warp == 5) {
@@ -75,7 +95,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
   __syncthreads();
   tc_fence_after_sync();
   const u32 tmem = ctl->tmem_base;
-  const u32 TM_S = 0, TM_O = 64;
+  const u32 TM_S = 0, TM_O = 128, TM_Q = 384;  // S buffer i at TM_S + 64 i
 
   if (warp == 4) {
     // =============================== TMA producer ===============================
@@ -84,17 +104,23 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
       tma_prefetch_desc(&args.tm_qpe);
       tma_prefetch_desc(&args.tm_kv);
       tma_prefetch_desc(&args.tm_kpe);
-      mbar_arrive_expect_tx(&bars->q_full, AE_MLA_Q_BYTES);
-      for (int blk = 0; blk < AE_MLA_NBV; ++blk)
-        tma_load_3d(smem + AE_MLA_SMEM_Q + blk * (AE_MLA_H * 128), &args.tm_q, &bars->q_full, blk * 64, 0, b);
-      tma_load_3d(smem + AE_MLA_SMEM_Q + AE_MLA_NBV * (AE_MLA_H * 128), &args.tm_qpe, &bars->q_full, 0, 0, b);
+      mbar_arrive_expect_tx(&bars->q_full, AE_MLA_NBK * AE_MLA_H * 128);
+      // blocks 0 .. QT-1 pass through KV stage 0 on their way to TMEM, the rest stay in their own area
+      for (int blk = 0; blk < AE_MLA_QT; ++blk)
+        tma_load_3d(smem + AE_MLA_SMEM_KV + blk * (AE_MLA_H * 128), &args.tm_q, &bars->q_full, blk * 64, 0, b);
+      for (int blk = AE_MLA_QT; blk < AE_MLA_NBV; ++blk)
+        tma_load_3d(smem + AE_MLA_SMEM_QS + (blk - AE_MLA_QT) * (AE_MLA_H * 128), &args.tm_q, &bars->q_full, blk * 64, 0, b);
+      tma_load_3d(smem + AE_MLA_SMEM_QS + (AE_MLA_NBV - AE_MLA_QT) * (AE_MLA_H * 128), &args.tm_qpe, &bars->q_full, 0, 0, b);
       for (int s = 0; s < n_steps; ++s) {
-        if (!mbar_wait(&bars->kv_empty, (s & 1) ^ 1, ctl, args.status, 41)) break;
+        const int stage = s % AE_MLA_STAGES;
+        if (s == 0 && !mbar_wait(&bars->q_tmem, 0, ctl, args.status, 40)) break;
+        if (!mbar_wait(&bars->kv_empty[stage], ((s / AE_MLA_STAGES) & 1) ^ 1, ctl, args.status, 41)) break;
         const int kv0 = (t_begin + s) * AE_MLA_BN;
-        mbar_arrive_expect_tx(&bars->kv_full, AE_MLA_KV_BYTES);
+        u8* dst = smem + AE_MLA_SMEM_KV + stage * AE_MLA_KV_BYTES;
+        mbar_arrive_expect_tx(&bars->kv_full[stage], AE_MLA_KV_BYTES);
         for (int blk = 0; blk < AE_MLA_NBV; ++blk)
-          tma_load_3d(smem + AE_MLA_SMEM_KV + blk * (AE_MLA_BN * 128), &args.tm_kv, &bars->kv_full, blk * 64, kv0, b);
-        tma_load_3d(smem + AE_MLA_SMEM_KV + AE_MLA_NBV * (AE_MLA_BN * 128), &args.tm_kpe, &bars->kv_full, 0, kv0, b);
+          tma_load_3d(dst + blk * (AE_MLA_BN * 128), &args.tm_kv, &bars->kv_full[stage], blk * 64, kv0, b);
+        tma_load_3d(dst + AE_MLA_NBV * (AE_MLA_BN * 128), &args.tm_kpe, &bars->kv_full[stage], 0, kv0, b);
       }
     }
   } else if (warp == 5) {
@@ -102,41 +128,89 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
     if (n_steps > 0) {  // all 32 lanes run the control flow; MMAs and commits are issued by an elected lane
       const u32 idesc_s = umma_idesc_f16(AE_MLA_H, AE_MLA_BN, AE_BF16, 0, 0);
       const u32 idesc_o = umma_idesc_f16(AE_MLA_H, AE_MLA_DVH, AE_BF16, 0, 1);
-      const u32 q_addr = smem_u32(smem + AE_MLA_SMEM_Q);
+      const u32 qs_addr = smem_u32(smem + AE_MLA_SMEM_QS);
       const u32 kv_addr = smem_u32(smem + AE_MLA_SMEM_KV);
-      bool ok = mbar_wait_w(&bars->q_full, 0, ctl, args.status, 42);
-      const u64 dq0 = umma_base_k(q_addr), dk0 = umma_base_k(kv_addr);
+      const u64 dq0 = umma_base_k(qs_addr), dk0 = umma_base_k(kv_addr);
       const u64 dv0 = umma_base_mn(kv_addr + dvh * (AE_MLA_NBV / 2) * (AE_MLA_BN * 128), AE_MLA_BN);
-      for (int s = 0; s < n_steps && ok; ++s) {
-        ok = mbar_wait_w(&bars->kv_full, s & 1, ctl, args.status, 43);
-        if (!ok) break;
+      auto issue_s = [&](int s, bool landed) -> bool {  // S_s into region s & 1
+        const int stage = s % AE_MLA_STAGES;
+        AE_TRM(true, 0, s * 8 + 0)
+        if (!landed && !mbar_wait_w(&bars->kv_full[stage], (s / AE_MLA_STAGES) & 1, ctl, args.status, 43)) return false;
         tc_fence_after_sync();
+        AE_TRM(true, 0, s * 8 + 1)
+        const u32 d = tmem + TM_S + (s & 1) * 64;
+        const u64 dks = dk0 + (u64)((stage * AE_MLA_KV_BYTES) >> 4);
 #pragma unroll
         for (int blk = 0; blk < AE_MLA_NBK; ++blk) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ss_w(tmem + TM_S, dq0 + (u64)((blk * (AE_MLA_H * 128) + kk * 32) >> 4),
-                    dk0 + (u64)((blk * (AE_MLA_BN * 128) + kk * 32) >> 4), idesc_s, (blk | kk) > 0);
+          for (int kk = 0; kk < 4; ++kk) {
+            const u64 db = dks + (u64)((blk * (AE_MLA_BN * 128) + kk * 32) >> 4);
+            if (blk < AE_MLA_QT)
+              umma_ts_w(d, tmem + TM_Q + blk * 32 + kk * 8, db, idesc_s, (blk | kk) > 0);
+            else
+              umma_ss_w(d, dq0 + (u64)(((blk - AE_MLA_QT) * (AE_MLA_H * 128) + kk * 32) >> 4), db, idesc_s, 1);
+          }
         }
-        umma_commit_w(&bars->s_full);
-        ok = mbar_wait_w(&bars->p_full, s & 1, ctl, args.status, 44);
+        umma_commit_w(&bars->s_full[s & 1]);
+        AE_TRM(true, 0, s * 8 + 2)
+        return true;
+      };
+      bool ok = mbar_wait_w(&bars->q_tmem, 0, ctl, args.status, 42);  // implies q_full
+      tc_fence_after_sync();
+      if (ok) ok = issue_s(0, false);
+      for (int s = 0; s < n_steps && ok; ++s) {
+        const int stage = s % AE_MLA_STAGES;
+        // The next S GEMM goes first if its KV tile has already landed (the other S region held P of tile s-1, whose
+        // P V GEMM was issued in the previous iteration); otherwise P V of this tile must not wait behind the load.
+        bool early = false;
+        if (s + 1 < n_steps) {
+          early = __all_sync(0xffffffffu, mbar_try_wait(&bars->kv_full[(s + 1) % AE_MLA_STAGES], ((s + 1) / AE_MLA_STAGES) & 1));
+          if (early) ok = issue_s(s + 1, true);
+        }
+        if (!ok) break;
+        AE_TRM(true, 0, s * 8 + 3)
+        ok = mbar_wait_w(&bars->p_full[s & 1], (s >> 1) & 1, ctl, args.status, 44);
         if (!ok) break;
         tc_fence_after_sync();
+        AE_TRM(true, 0, s * 8 + 4)
         // V = this half's four 64-wide blocks of the same tile, read MN-major
+        const u64 dvs = dv0 + (u64)((stage * AE_MLA_KV_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_MLA_BN / 16; ++kk)
-          umma_ts_w(tmem + TM_O, tmem + TM_S + kk * 8, umma_step_mn(dv0, kk), idesc_o, (s > 0) | (kk > 0));
+          umma_ts_w(tmem + TM_O, tmem + TM_S + (s & 1) * 64 + kk * 8, umma_step_mn(dvs, kk), idesc_o, (s > 0) | (kk > 0));
         umma_commit_w(&bars->o_done);
-        umma_commit_w(&bars->kv_empty);
+        umma_commit_w(&bars->kv_empty[stage]);
+        AE_TRM(true, 0, s * 8 + 5)
+        if (s + 1 < n_steps && !early) ok = issue_s(s + 1, false);
       }
     }
   } else {
     // =============================== row threads (one per head) =================
     const u32 row = threadIdx.x & 127;
     const u32 lane_base = ((warp & 3) * 32) << 16;
-    const u32 tm_s = tmem + TM_S + lane_base;
     const u32 tm_o = tmem + TM_O + lane_base;
     const int h = (int)row;
+    bool ok = true;
+    // ---- query blocks 0 .. QT-1 of this head: shared memory (KV stage 0) -> TMEM, once -----------------
+    if (n_steps > 0) {
+      ok = mbar_wait(&bars->q_full, 0, ctl, args.status, 48);
+      const u8* src = smem + AE_MLA_SMEM_KV;
+      for (int blk = 0; blk < AE_MLA_QT; ++blk) {
+        u32 w[32];
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint4 v = *(const uint4*)(src + blk * (AE_MLA_H * 128) + swz128(row, ch));
+          w[ch * 4 + 0] = v.x;
+          w[ch * 4 + 1] = v.y;
+          w[ch * 4 + 2] = v.z;
+          w[ch * 4 + 3] = v.w;
+        }
+        tmem_st32(tmem + TM_Q + lane_base + blk * 32, w);  // column c holds elements 2c, 2c + 1 of the row
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive_warp(&bars->q_tmem);
+    }
     AeCustom cu;
 #pragma unroll
     for (int i = 0; i < AE_MAX_CUSTOM; ++i) {
@@ -146,16 +220,14 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
     }
     AeRow st;
     st.init();
-    bool ok = true;
     for (int s = 0; s < n_steps; ++s) {
-      ok = ok && mbar_wait(&bars->s_full, s & 1, ctl, args.status, 45);
+      const u32 tm_s = tmem + TM_S + (s & 1) * 64 + lane_base;
+      AE_TRM(warp == 0, 1, s * 8 + 0)
+      ok = ok && mbar_wait(&bars->s_full[s & 1], (s >> 1) & 1, ctl, args.status, 45);
       tc_fence_after_sync();
+      AE_TRM(warp == 0, 1, s * 8 + 1)
       float sc[AE_MLA_BN];
-#if AE_MLA_BN == 64
       tmem_ld_f32x64(tm_s, sc);
-#else
-      tmem_ld_f32x128(tm_s, sc);
-#endif
       const int kv0 = (t_begin + s) * AE_MLA_BN;
       if (kv0 + AE_MLA_BN > args.S) {
 #pragma unroll
@@ -173,25 +245,26 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
         }
       }
 #if !AE_O_SCALE_ONE
-      if (s > 0) {
+      // O is rescaled only when some row of the warp needs it; only then must the previous P V GEMM have completed
+      // (a skipped wait cannot alias: o_done runs at most one phase ahead of this warp's arrivals)
+      if (s > 0 && __any_sync(0xffffffffu, o_scale != 1.0f)) {
         ok = ok && mbar_wait(&bars->o_done, (s - 1) & 1, ctl, args.status, 46);
         tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, o_scale != 1.0f)) {
 #pragma unroll
-          for (int c = 0; c < AE_MLA_DVH / 32; ++c) {
-            float f[32];
-            u32 r[32];
-            tmem_ld_f32x32(tm_o + c * 32, f);
+        for (int c = 0; c < AE_MLA_DVH / 32; ++c) {
+          float f[32];
+          u32 r[32];
+          tmem_ld_f32x32(tm_o + c * 32, f);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(f[i] * o_scale);
-            tmem_st32(tm_o + c * 32, r);
-          }
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(f[i] * o_scale);
+          tmem_st32(tm_o + c * 32, r);
         }
       }
 #endif
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive_warp(&bars->p_full);
+      mbar_arrive_warp(&bars->p_full[s & 1]);
+      AE_TRM(warp == 0, 1, s * 8 + 2)
     }
 
     if (n_steps > 0) {
