@@ -23,6 +23,7 @@ class BwdKernels:
     bn: int
     nbuf: int
     stages: int
+    sources: dict | None = None  # kernel name -> generated CUDA source (kept for inspection and build checks)
 
 
 def bwd_tile_config(D: int, DV: int):
@@ -54,13 +55,15 @@ def compile_bwd(k) -> BwdKernels:
     prelude_dq = prelude
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_PREP, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=256,
                           smem_bytes=0, stages=0, mask_mode=k.mask_mode)
-    prep = rt.compile_module(rt.kernel_source("attn_bwd_prep.cuh", prelude=prelude), "ae_attn_bwd_prep", cfg)
+    src_prep = rt.kernel_source("attn_bwd_prep.cuh", prelude=prelude)
+    prep = rt.compile_module(src_prep, "ae_attn_bwd_prep", cfg)
     smem_dq = stages_dq * bn * (D + DV) * 2 + 512 + 1024  # Q / dO land in the last K / V slot
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DQ, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
                           smem_bytes=smem_dq, stages=stages_dq, mask_mode=k.mask_mode)
     cfg.reserved[0] = bn
     # every 4th exponential of the dQ pass runs on the FMA pipe (measured 3 % faster there, slower in the other kernels)
-    dq = rt.compile_module(rt.kernel_source("attn_bwd_dq.cuh", prelude=prelude_dq, exp_poly=4), "ae_attn_bwd_dq", cfg)
+    src_dq = rt.kernel_source("attn_bwd_dq.cuh", prelude=prelude_dq, exp_poly=4)
+    dq = rt.compile_module(src_dq, "ae_attn_bwd_dq", cfg)
     ncs = len(low.final_names) + 1
     bn_kv, qst, dost, nwg, ts = dkv_tile_config(D, DV)
     prelude_kv = low.prelude_bwd + (f"#define AE_BWD_BN {bn_kv}\n#define AE_KV_QSTAGES {qst}\n"
@@ -77,8 +80,10 @@ def compile_bwd(k) -> BwdKernels:
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DKV, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV,
                           threads=nwg * 128 + 64, smem_bytes=smem_kv, stages=qst, mask_mode=k.mask_mode)
     cfg.reserved[0] = bn_kv
-    dkv = rt.compile_module(rt.kernel_source("attn_bwd_dkv.cuh", prelude=prelude_kv), "ae_attn_bwd_dkv", cfg)
-    return BwdKernels(prep, dq, dkv, bn, nbuf, stages)
+    src_dkv = rt.kernel_source("attn_bwd_dkv.cuh", prelude=prelude_kv)
+    dkv = rt.compile_module(src_dkv, "ae_attn_bwd_dkv", cfg)
+    return BwdKernels(prep, dq, dkv, bn, nbuf, stages,
+                      {"attn_bwd_prep": src_prep, "attn_bwd_dq": src_dq, "attn_bwd_dkv": src_dkv})
 
 
 def _s3(t):
