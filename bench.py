@@ -235,7 +235,7 @@ def run_other(args):
         cpu = {"value": 4 * 3.5 * 4.0 * 2 * S * S * D / tc / 1e12, "unit": "TFLOPS", "cores": os.cpu_count(), "kind": "port",
                "sample": "4 x (1 batch row, 2 of 32 heads), fwd+bwd, fp32 torch"}
     elif wl == "cfg4":
-        B, H, T, DK, DV, dt = 8, 80, 8192, 128, 64, torch.bfloat16
+        B, H, T, DK, DV, dt = args.batch or 8, 80, 8192, 128, 64, torch.bfloat16
         eng = helpers.mamba2_engine(B, H, T, DK, DV, dt)
         x = torch.randn(B, H, T, DV, device=dev, dtype=dt, requires_grad=True)
         Bm = torch.randn(B, 1, T, DK, device=dev, dtype=dt, requires_grad=True)
@@ -258,6 +258,7 @@ def run_other(args):
         value, unit, bound, peak = work / ms / 1e9, "TFLOPS", "tensor", float(peaks.get("bf16_tflops", 1590.0))
         desc = ("Mamba2 SSD fwd+bwd (mods as eager torch + scan kernels), B=8 L=8192 H=80 P=64 N=128 ngroups=1 bf16; FLOPs by "
                 "the chunk-256 convention, fwd (2Q^2N+2Q^2P+4QNP) per chunk and head, bwd counted as 2.5x fwd")
+        desc = desc.replace("B=8 ", f"B={B} ")
         launches = 3 * args.steps
         from oracle.linear_oracle import linear_scan
         xs, dt_s, As, Bs, Cs = helpers.mamba2_inputs(1, 2, 1024, DK, DV, dt, seed=0)
@@ -269,7 +270,7 @@ def run_other(args):
         cpu = {"value": 3.5 * f_s / tc / 1e12, "unit": "TFLOPS", "cores": os.cpu_count(), "kind": "port",
                "sample": "step-by-step recurrence, 1 batch row x 2 heads x 1024 steps, fwd+bwd, fp64 torch"}
     elif wl == "cfg5":
-        B, H, S, dt = 128, 128, 8192, torch.float16
+        B, H, S, dt = args.batch or 128, 128, 8192, torch.float16
         eng = helpers.mla_engine(B, H, S, dt, 1 / math.sqrt(192))
         q = torch.randn(B, 1, H, 512, device=dev, dtype=dt)
         q_pe = torch.randn(B, 1, H, 64, device=dev, dtype=dt)
@@ -279,7 +280,7 @@ def run_other(args):
         eng.check_status()
         work = (B * S * 576 + B * H * 576 + B * H * 512) * 2.0
         value, unit, bound, peak = work / ms / 1e6, "GB/s", "hbm", float(peaks.get("hbm_gbs", 6650.0))
-        desc = "MLA decode, B=128 H=128 Skv=8192 D=512+64 DV=512 fp16, scale 1/sqrt(192)"
+        desc = f"MLA decode, B={B} H=128 Skv=8192 D=512+64 DV=512 fp16, scale 1/sqrt(192)"
         launches = (1 if eng._mla.last_num_split == 1 else 2) * args.steps
         g = torch.Generator().manual_seed(0)
         qs, ps = torch.randn(4, H, 512, generator=g).to(dt), torch.randn(4, H, 64, generator=g).to(dt)
@@ -314,7 +315,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end pass (profiling runs)")
     ap.add_argument("--workload", default="cfg2", help="cfg2 (the headline, default) | cfg3_sigmoid | cfg3_relu | cfg4 | cfg5")
-    ap.add_argument("--batch", type=int, default=CFG["B"], help="batch size; the benchmark's is 8 (smaller for ncu captures)")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="batch size; default = the benchmark's (8; cfg5: 128). Smaller values are for ncu captures")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -339,7 +341,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     B, Hq, Hkv, S, D = (CFG[k] for k in ("B", "Hq", "Hkv", "S", "D"))
-    B = args.batch
+    B = args.batch or CFG["B"]
     dt = torch.float16
     eng = helpers.softmax_engine(B, Hq, Hkv, S, D, D, dt, True)
     eng.kernels.bwd  # compile / load before timing
