@@ -26,13 +26,13 @@ class BwdKernels:
 
 
 def dq_tile_config(D: int, DV: int):
-    """(streamed kv-tile rows, K / V ring depth) of the dQ pass: Q and dO live in TMEM next to one S and one dP region
-    of 128 columns and the dQ accumulator; three 128-row K and V slots fill shared memory at head dim 128."""
-    cfg = os.environ.get("AE_B200_BWD_TILE")  # "bn,stages": tuning override
+    """(streamed kv-tile rows, K ring depth, V ring depth) of the dQ pass: Q and dO live in TMEM next to one S and one
+    dP region of 128 columns and the dQ accumulator; four 128-row K slots and three V slots fill shared memory at head
+    dim 128 (a K slot is held until the dQ GEMM of its tile, a V slot only until the dP GEMM)."""
+    cfg = os.environ.get("AE_B200_BWD_TILE")  # "bn,K stages,V stages": tuning override
     if cfg:
-        bn, stages = (int(x) for x in cfg.split(","))
-        return bn, stages
-    return 128, 3
+        return tuple(int(x) for x in cfg.split(","))
+    return 128, 4, 3
 
 
 def dkv_tile_config(D: int, DV: int):
@@ -47,16 +47,16 @@ def dkv_tile_config(D: int, DV: int):
 
 def compile_bwd(k) -> BwdKernels:
     D, DV, low = k.D, k.DV, k.low
-    bn, stages = dq_tile_config(D, DV)
-    defs = f"#define AE_BWD_BN {bn}\n#define AE_BWD_STAGES {stages}\n"
+    bn, kst, vst = dq_tile_config(D, DV)
+    defs = f"#define AE_BWD_BN {bn}\n#define AE_DQ_KSTAGES {kst}\n#define AE_DQ_VSTAGES {vst}\n"
     prelude = low.prelude_bwd + defs
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_PREP, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=256,
                           smem_bytes=0, stages=0, mask_mode=k.mask_mode)
     src_prep = rt.kernel_source("attn_bwd_prep.cuh", prelude=prelude)
     prep = rt.compile_module(src_prep, "ae_attn_bwd_prep", cfg)
-    smem_dq = stages * bn * (D + DV) * 2 + 512 + 1024  # Q / dO land in the last K / V slot
+    smem_dq = bn * (kst * D + vst * DV) * 2 + 512 + 1024  # Q / dO land in the last K / V slot
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_DQ, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
-                          smem_bytes=smem_dq, stages=stages, mask_mode=k.mask_mode)
+                          smem_bytes=smem_dq, stages=kst, mask_mode=k.mask_mode)
     cfg.reserved[0] = bn
     # every 4th exponential of the dQ pass runs on the FMA pipe (measured 3 % faster there, slower in the other kernels)
     src_dq = rt.kernel_source("attn_bwd_dq.cuh", prelude=prelude, exp_poly=4)
@@ -79,7 +79,7 @@ def compile_bwd(k) -> BwdKernels:
     cfg.reserved[0] = bn_kv
     src_dkv = rt.kernel_source("attn_bwd_dkv.cuh", prelude=prelude_kv)
     dkv = rt.compile_module(src_dkv, "ae_attn_bwd_dkv", cfg)
-    return BwdKernels(prep, dq, dkv, bn, stages,
+    return BwdKernels(prep, dq, dkv, bn, kst,
                       {"attn_bwd_prep": src_prep, "attn_bwd_dq": src_dq, "attn_bwd_dkv": src_dkv})
 
 

@@ -192,9 +192,10 @@ int make_bshd_map(AeTmaDesc* out, const void* base, int dtype, int64_t B, int64_
       set_error("tensor strides must be multiples of 8 elements");
       return AE_ERR_INVALID;
     }
-  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
-  cuuint64_t strides[3] = {(cuuint64_t)st[2] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)(B == 1 ? S * st[1] : st[0]) * 2};
-  cuuint32_t box[4] = {64, 1, (cuuint32_t)rows, 1};
+  // dimension order (d, s, h, b): the rows of a box are the second dimension
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)st[1] * 2, (cuuint64_t)st[2] * 2, (cuuint64_t)(B == 1 ? S * st[1] : st[0]) * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUtensorMapDataType dt = dtype == AE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   AE_CU(d.cuTensorMapEncodeTiled(reinterpret_cast<CUtensorMap*>(out), dt, 4, const_cast<void*>(base), dims, strides,

@@ -179,6 +179,11 @@ AE_DEVICE void tma_load_4d(void* smem_dst, const AeTmaDesc* d, u64* bar, int c0,
       ::"r"(smem_u32(smem_dst)), "l"((u64)d), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// A [rows x 64 elements] box of a [B, S, H, D] tensor (any strides): the tensor map's dimensions are ordered
+// (d, s, h, b), so the box is {64, rows, 1, 1} and its rows are the map's second dimension.
+AE_DEVICE void tma_load_bshd(void* smem_dst, const AeTmaDesc* d, u64* bar, int d0, int h, int s0, int b) {
+  tma_load_4d(smem_dst, d, bar, d0, s0, h, b);
+}
 AE_DEVICE void tma_load_3d(void* smem_dst, const AeTmaDesc* d, u64* bar, int c0, int c1, int c2) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"

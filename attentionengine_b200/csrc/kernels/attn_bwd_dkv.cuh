@@ -210,9 +210,9 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       tma_prefetch_desc(&args.tm_do);
       mbar_arrive_expect_tx(&bars->kv_full, AE_KV_K_BYTES + AE_KV_V_BYTES);
       for (int dh = 0; dh < AE_D / 64; ++dh)
-        tma_load_4d(smem + AE_KV_SMEM_K + dh * (AE_KV_BM * 128), &args.tm_k, &bars->kv_full, dh * 64, hk, kv0, b);
+        tma_load_bshd(smem + AE_KV_SMEM_K + dh * (AE_KV_BM * 128), &args.tm_k, &bars->kv_full, dh * 64, hk, kv0, b);
       for (int dh = 0; dh < AE_DV / 64; ++dh)
-        tma_load_4d(smem + AE_KV_SMEM_V + dh * (AE_KV_BM * 128), &args.tm_v, &bars->kv_full, dh * 64, hk, kv0, b);
+        tma_load_bshd(smem + AE_KV_SMEM_V + dh * (AE_KV_BM * 128), &args.tm_v, &bars->kv_full, dh * 64, hk, kv0, b);
     }
     AeDkvStep st;
     int s = 0;
@@ -225,7 +225,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       if (lane == 0) {
         mbar_arrive_expect_tx(&bars->q_full[sq], AE_KV_Q_BYTES);
         for (int dh = 0; dh < AE_D / 64; ++dh)
-          tma_load_4d(smem + AE_KV_SMEM_Q + sq * AE_KV_Q_BYTES + dh * (AE_BWD_BN * 128), &args.tm_q, &bars->q_full[sq],
+          tma_load_bshd(smem + AE_KV_SMEM_Q + sq * AE_KV_Q_BYTES + dh * (AE_BWD_BN * 128), &args.tm_q, &bars->q_full[sq],
                       dh * 64, st.hq, st.q0, b);
       }
       {
@@ -254,7 +254,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       if (lane == 0) {
         mbar_arrive_expect_tx(&bars->do_full[sd], AE_KV_DO_BYTES);
         for (int dh = 0; dh < AE_DV / 64; ++dh)
-          tma_load_4d(smem + AE_KV_SMEM_DO + sd * AE_KV_DO_BYTES + dh * (AE_BWD_BN * 128), &args.tm_do,
+          tma_load_bshd(smem + AE_KV_SMEM_DO + sd * AE_KV_DO_BYTES + dh * (AE_BWD_BN * 128), &args.tm_do,
                       &bars->do_full[sd], dh * 64, st.hq, st.q0, b);
       }
       ++s;

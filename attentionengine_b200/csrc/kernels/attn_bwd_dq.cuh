@@ -20,8 +20,10 @@
 // Roles: warps 0-3 and 4-7 row threads (thread = q row = TMEM lane; the two groups take alternate
 // 32-column chunks of every tile), warp 8 TMA producer, warp 9 MMA issuer.  The 16-bit dS pairs of a
 // chunk are written over the first 16 columns of that chunk of dP, so a group only overwrites what it has read.
-// Shared memory: AE_BWD_STAGES (= 3) slots each for K and V; the last slot of each is where Q and dO land
-// first and becomes a ring slot once they have been copied to TMEM.
+// Shared memory: AE_DQ_KSTAGES (= 4) slots for K and AE_DQ_VSTAGES (= 3) for V; the last slot of each is where Q and
+// dO land first and becomes a ring slot once they have been copied to TMEM.  A K slot is held until the dQ GEMM of
+// its tile, a V slot only until the dP GEMM; a load takes about 4000 clk from issue to arrival when the SMs are busy,
+// more than one tile period, so two tiles of each must be in flight.
 
 #define AE_BM 128
 #define AE_NTHREADS_BWD 320
@@ -37,10 +39,10 @@
 #define AE_DQ_K_BYTES (AE_BWD_BN * AE_D * 2)
 #define AE_DQ_V_BYTES (AE_BWD_BN * AE_DV * 2)
 #define AE_DQ_SMEM_K 0
-#define AE_DQ_SMEM_V (AE_BWD_STAGES * AE_DQ_K_BYTES)
-#define AE_DQ_SMEM_Q (AE_DQ_SMEM_K + (AE_BWD_STAGES - 1) * AE_DQ_K_BYTES)   // = last K slot
-#define AE_DQ_SMEM_DO (AE_DQ_SMEM_V + (AE_BWD_STAGES - 1) * AE_DQ_V_BYTES)  // = last V slot
-#define AE_DQ_SMEM_BAR (AE_DQ_SMEM_V + AE_BWD_STAGES * AE_DQ_V_BYTES)
+#define AE_DQ_SMEM_V (AE_DQ_KSTAGES * AE_DQ_K_BYTES)
+#define AE_DQ_SMEM_Q (AE_DQ_SMEM_K + (AE_DQ_KSTAGES - 1) * AE_DQ_K_BYTES)   // = last K slot
+#define AE_DQ_SMEM_DO (AE_DQ_SMEM_V + (AE_DQ_VSTAGES - 1) * AE_DQ_V_BYTES)  // = last V slot
+#define AE_DQ_SMEM_BAR (AE_DQ_SMEM_V + AE_DQ_VSTAGES * AE_DQ_V_BYTES)
 #if AE_BWD_BN != 128
 #error "the dQ pass streams 128-row K / V tiles"
 #endif
@@ -48,10 +50,10 @@
 struct AeDqBars {
   u64 qdo_full;   // Q and dO landed in shared memory
   u64 qdo_tmem;   // ... and were copied to TMEM (their shared-memory slots are free)
-  u64 k_full[AE_BWD_STAGES];
-  u64 k_empty[AE_BWD_STAGES];
-  u64 v_full[AE_BWD_STAGES];
-  u64 v_empty[AE_BWD_STAGES];
+  u64 k_full[AE_DQ_KSTAGES];
+  u64 k_empty[AE_DQ_KSTAGES];
+  u64 v_full[AE_DQ_VSTAGES];
+  u64 v_empty[AE_DQ_VSTAGES];
   u64 s_full, dp_full;  // S / dP of a step are in TMEM
   u64 a_done, ds_full;  // the row threads have read S / written dS
   u64 dq_done;
@@ -112,9 +114,11 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
     mbar_init(&bars->qdo_full, 1);
     mbar_init(&bars->qdo_tmem, 8);
     mbar_init(&bars->dq_done, 1);
-    for (int i = 0; i < AE_BWD_STAGES; ++i) {
+    for (int i = 0; i < AE_DQ_KSTAGES; ++i) {
       mbar_init(&bars->k_full[i], 1);
       mbar_init(&bars->k_empty[i], 1);
+    }
+    for (int i = 0; i < AE_DQ_VSTAGES; ++i) {
       mbar_init(&bars->v_full[i], 1);
       mbar_init(&bars->v_empty[i], 1);
     }
@@ -143,27 +147,30 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       tma_prefetch_desc(&args.tm_do);
       mbar_arrive_expect_tx(&bars->qdo_full, AE_BM * (AE_D + AE_DV) * 2);
       for (int dh = 0; dh < AE_D / 64; ++dh)
-        tma_load_4d(smem + AE_DQ_SMEM_Q + dh * (AE_BM * 128), &args.tm_q, &bars->qdo_full, dh * 64, hq, q0, b);
+        tma_load_bshd(smem + AE_DQ_SMEM_Q + dh * (AE_BM * 128), &args.tm_q, &bars->qdo_full, dh * 64, hq, q0, b);
       for (int dh = 0; dh < AE_DV / 64; ++dh)
-        tma_load_4d(smem + AE_DQ_SMEM_DO + dh * (AE_BM * 128), &args.tm_do, &bars->qdo_full, dh * 64, hq, q0, b);
+        tma_load_bshd(smem + AE_DQ_SMEM_DO + dh * (AE_BM * 128), &args.tm_do, &bars->qdo_full, dh * 64, hq, q0, b);
       for (int s = 0; s < n_steps; ++s) {
         int kv0;
         bool partial;
         step_info(s, kv0, partial);
-        const int stage = s % AE_BWD_STAGES;
-        const u32 par = ((s / AE_BWD_STAGES) & 1) ^ 1;
-        // the last slot holds Q / dO until the row threads have moved them to TMEM
-        if (s == AE_BWD_STAGES - 1 && !mbar_wait(&bars->qdo_tmem, 0, ctl, args.status, 20)) break;
-        if (!mbar_wait(&bars->k_empty[stage], par, ctl, args.status, 21)) break;
-        mbar_arrive_expect_tx(&bars->k_full[stage], AE_DQ_K_BYTES);
+        const int ks = s % AE_DQ_KSTAGES, vs = s % AE_DQ_VSTAGES;
+        // the last slots hold Q / dO until the row threads have moved them to TMEM
+        if ((s == AE_DQ_KSTAGES - 1 || s == AE_DQ_VSTAGES - 1) && !mbar_wait(&bars->qdo_tmem, 0, ctl, args.status, 20)) break;
+        AE_TR(true, 3, s * 8 + 0)
+        if (!mbar_wait(&bars->k_empty[ks], ((s / AE_DQ_KSTAGES) & 1) ^ 1, ctl, args.status, 21)) break;
+        AE_TR(true, 3, s * 8 + 1)
+        mbar_arrive_expect_tx(&bars->k_full[ks], AE_DQ_K_BYTES);
         for (int dh = 0; dh < AE_D / 64; ++dh)
-          tma_load_4d(smem + AE_DQ_SMEM_K + stage * AE_DQ_K_BYTES + dh * (AE_BWD_BN * 128), &args.tm_k,
-                      &bars->k_full[stage], dh * 64, hk, kv0, b);
-        if (!mbar_wait(&bars->v_empty[stage], par, ctl, args.status, 22)) break;
-        mbar_arrive_expect_tx(&bars->v_full[stage], AE_DQ_V_BYTES);
+          tma_load_bshd(smem + AE_DQ_SMEM_K + ks * AE_DQ_K_BYTES + dh * (AE_BWD_BN * 128), &args.tm_k,
+                      &bars->k_full[ks], dh * 64, hk, kv0, b);
+        AE_TR(true, 3, s * 8 + 2)
+        if (!mbar_wait(&bars->v_empty[vs], ((s / AE_DQ_VSTAGES) & 1) ^ 1, ctl, args.status, 22)) break;
+        AE_TR(true, 3, s * 8 + 3)
+        mbar_arrive_expect_tx(&bars->v_full[vs], AE_DQ_V_BYTES);
         for (int dh = 0; dh < AE_DV / 64; ++dh)
-          tma_load_4d(smem + AE_DQ_SMEM_V + stage * AE_DQ_V_BYTES + dh * (AE_BWD_BN * 128), &args.tm_v,
-                      &bars->v_full[stage], dh * 64, hk, kv0, b);
+          tma_load_bshd(smem + AE_DQ_SMEM_V + vs * AE_DQ_V_BYTES + dh * (AE_BWD_BN * 128), &args.tm_v,
+                      &bars->v_full[vs], dh * 64, hk, kv0, b);
       }
     }
   } else if (warp == 9) {
@@ -177,8 +184,8 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       const u64 dkmn0 = umma_base_mn(k_addr, AE_BWD_BN);
 
       auto issue_s = [&](int s) -> bool {  // S_s = Q K_s^T
-        const int stage = s % AE_BWD_STAGES;
-        if (!mbar_wait_w(&bars->k_full[stage], (s / AE_BWD_STAGES) & 1, ctl, args.status, 24)) return false;
+        const int stage = s % AE_DQ_KSTAGES;
+        if (!mbar_wait_w(&bars->k_full[stage], (s / AE_DQ_KSTAGES) & 1, ctl, args.status, 24)) return false;
         tc_fence_after_sync();
         AE_TR(s > 0, 0, (s - 1) * 8 + 6)
         const u64 dkk = dk0 + (u64)((stage * AE_DQ_K_BYTES) >> 4);
@@ -189,8 +196,8 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
         return true;
       };
       auto issue_dp = [&](int s) -> bool {  // dP_s = dO V_s^T
-        const int stage = s % AE_BWD_STAGES;
-        if (!mbar_wait_w(&bars->v_full[stage], (s / AE_BWD_STAGES) & 1, ctl, args.status, 25)) return false;
+        const int stage = s % AE_DQ_VSTAGES;
+        if (!mbar_wait_w(&bars->v_full[stage], (s / AE_DQ_VSTAGES) & 1, ctl, args.status, 25)) return false;
         tc_fence_after_sync();
         AE_TR(s > 0, 0, (s - 1) * 8 + 7)
         const u64 dvv = dv0 + (u64)((stage * AE_DQ_V_BYTES) >> 4);
@@ -207,7 +214,7 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       if (ok) ok = issue_s(0);
       if (ok) ok = issue_dp(0);
       for (int s = 0; s < n_steps && ok; ++s) {
-        const int stage = s % AE_BWD_STAGES;
+        const int stage = s % AE_DQ_KSTAGES;
         const u32 par = s & 1;
         AE_TR(true, 0, s * 8 + 0)
         // the next S goes over S_s once the row threads have read it

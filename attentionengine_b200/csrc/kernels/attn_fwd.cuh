@@ -174,7 +174,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       for (int t = 0; t < 2; ++t) {
         mbar_arrive_expect_tx(&bars->q_full[t], AE_Q_BYTES);
         for (int dh = 0; dh < AE_D / 64; ++dh)
-          tma_load_4d(smem + AE_SMEM_Q + t * AE_Q_BYTES + dh * (AE_BM * 128), &args.tm_q, &bars->q_full[t], dh * 64,
+          tma_load_bshd(smem + AE_SMEM_Q + t * AE_Q_BYTES + dh * (AE_BM * 128), &args.tm_q, &bars->q_full[t], dh * 64,
                       hq, (qt0 + t) * AE_BM, b);
       }
       AeKvStep st;
@@ -185,12 +185,12 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         if (!mbar_wait(&bars->k_empty[stage], par, ctl, args.status, 1)) break;
         mbar_arrive_expect_tx(&bars->k_full[stage], AE_K_BYTES);
         for (int dh = 0; dh < AE_D / 64; ++dh)
-          tma_load_4d(smem + AE_SMEM_K + stage * AE_K_BYTES + dh * (AE_BN * 128), &args.tm_k, &bars->k_full[stage],
+          tma_load_bshd(smem + AE_SMEM_K + stage * AE_K_BYTES + dh * (AE_BN * 128), &args.tm_k, &bars->k_full[stage],
                       dh * 64, hk, st.kt * AE_BN, b);
         if (!mbar_wait(&bars->v_empty[stage], par, ctl, args.status, 2)) break;
         mbar_arrive_expect_tx(&bars->v_full[stage], AE_V_BYTES);
         for (int dh = 0; dh < AE_DV / 64; ++dh)
-          tma_load_4d(smem + AE_SMEM_V + stage * AE_V_BYTES + dh * (AE_BN * 128), &args.tm_v, &bars->v_full[stage],
+          tma_load_bshd(smem + AE_SMEM_V + stage * AE_V_BYTES + dh * (AE_BN * 128), &args.tm_v, &bars->v_full[stage],
                       dh * 64, hk, st.kt * AE_BN, b);
         ++it;
       }

@@ -155,7 +155,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
         AE_TRM(true, 0, s * 8 + 2)
         return true;
       };
-      bool ok = mbar_wait_w(&bars->q_tmem, 0, ctl, args.status, 42);  // implies q_full
+      // the blocks that stay in shared memory are read by the MMAs themselves: this warp waits for the TMA barrier
+      // too, not only for the row threads that saw it
+      bool ok = mbar_wait_w(&bars->q_full, 0, ctl, args.status, 49);
+      ok = ok && mbar_wait_w(&bars->q_tmem, 0, ctl, args.status, 42);
       tc_fence_after_sync();
       if (ok) ok = issue_s(0, false);
       for (int s = 0; s < n_steps && ok; ++s) {
@@ -245,20 +248,31 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
         }
       }
 #if !AE_O_SCALE_ONE
-      // O is rescaled only when some row of the warp needs it; only then must the previous P V GEMM have completed
-      // (a skipped wait cannot alias: o_done runs at most one phase ahead of this warp's arrivals)
-      if (s > 0 && __any_sync(0xffffffffu, o_scale != 1.0f)) {
+      // O is rescaled only when some row of the warp needs it; only then must the previous P V GEMM have completed.
+      // Phase bookkeeping of the skipped waits: S_s may be issued before P V of tile s-1, so s_full(s) only implies
+      // that P V of tile s-2 has completed: o_done has then completed s-1 or s phases, and a parity wait for phase
+      // s-1 cannot alias.  The wait after the loop asks for phase n-1 and would alias if only n-2 had completed, so
+      // the last step always waits for its predecessor.
+      const bool rescale = __any_sync(0xffffffffu, o_scale != 1.0f);
+      if (s > 0 && (rescale || s + 1 == n_steps)) {
         ok = ok && mbar_wait(&bars->o_done, (s - 1) & 1, ctl, args.status, 46);
         tc_fence_after_sync();
+        if (rescale) {
 #pragma unroll
-        for (int c = 0; c < AE_MLA_DVH / 32; ++c) {
-          float f[32];
-          u32 r[32];
-          tmem_ld_f32x32(tm_o + c * 32, f);
+          for (int c = 0; c < AE_MLA_DVH / 32; ++c) {
+            float f[32];
+            u32 r[32];
+            tmem_ld_f32x32(tm_o + c * 32, f);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(f[i] * o_scale);
-          tmem_st32(tm_o + c * 32, r);
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(f[i] * o_scale);
+            tmem_st32(tm_o + c * 32, r);
+          }
         }
+      }
+#else
+      if (s > 0 && s + 1 == n_steps) {  // same phase bookkeeping: the wait after the loop must not find o_done two phases behind
+        ok = ok && mbar_wait(&bars->o_done, (s - 1) & 1, ctl, args.status, 46);
+        tc_fence_after_sync();
       }
 #endif
       tc_wait_st();
