@@ -366,9 +366,11 @@ int ae_launch_probe(void* module, const void* a, const void* b, const void* p, f
   if (rc) return rc;
   args.p = p;
   args.d = d_out;
-  args.mode = mode;
+  args.mode = mode & 0xffff;
   args.status = status;
-  return launch(m, 1, 1, 1, &args, stream);
+  // bits 16.. of `mode`: number of CTAs (0 = one); only the rate micro-benchmarks use more than one
+  const unsigned grid = (unsigned)(mode >> 16) ? (unsigned)(mode >> 16) : 1u;
+  return launch(m, grid, 1, 1, &args, stream);
 }
 
 int ae_launch_attn_fwd(void* module, const AeAttnParams* p, void* stream) {

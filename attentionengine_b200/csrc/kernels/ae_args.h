@@ -27,7 +27,7 @@ struct AeCustom {
 
 // ---- fused attention forward (kernel ae_attn_fwd) --------------------------------
 struct AeAttnFwdArgs {
-  AeTmaDesc tm_q;  // dims (d, h, s, b), box {64, 1, 128, 1}, 128-byte swizzle
+  AeTmaDesc tm_q;  // dims (d, s, h, b), box {64, 128, 1, 1}, 128-byte swizzle
   AeTmaDesc tm_k;
   AeTmaDesc tm_v;
   void* o;

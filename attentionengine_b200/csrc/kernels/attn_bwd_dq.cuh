@@ -11,7 +11,8 @@
 // of the loop takes its A operand from TMEM and only the streamed K / V tile is read from shared
 // memory (an MMA with both operands there is bound by shared-memory bandwidth).  Per kv tile s:
 //   S  = Q  K^T   (TS MMA)        dP = dO V^T   (TS MMA)
-//   row threads, phase A: T = score_mod(S); P = OnlineFunc.forward(T), kept in registers;
+//   row threads, phase A: S -> registers (S is released at once); T = score_mod(S); P = OnlineFunc.forward(T), kept
+//                in registers;
 //                phase B: dT = OnlineFunc.backward(dP, P); dS = score_mod'(S) dT -> 16-bit pairs over dP
 //   dQ += dS K    (TS MMA, K tile read MN-major)
 // TMEM columns: Q | dO | S | dP | dQ.  The tensor pipe executes MMAs in issue order; the issue order is
@@ -20,10 +21,9 @@
 // Roles: warps 0-3 and 4-7 row threads (thread = q row = TMEM lane; the two groups take alternate
 // 32-column chunks of every tile), warp 8 TMA producer, warp 9 MMA issuer.  The 16-bit dS pairs of a
 // chunk are written over the first 16 columns of that chunk of dP, so a group only overwrites what it has read.
-// Shared memory: AE_DQ_KSTAGES (= 4) slots for K and AE_DQ_VSTAGES (= 3) for V; the last slot of each is where Q and
-// dO land first and becomes a ring slot once they have been copied to TMEM.  A K slot is held until the dQ GEMM of
-// its tile, a V slot only until the dP GEMM; a load takes about 4000 clk from issue to arrival when the SMs are busy,
-// more than one tile period, so two tiles of each must be in flight.
+// Shared memory: AE_DQ_KSTAGES slots for K and AE_DQ_VSTAGES for V (3 each by default); the last slot of each is
+// where Q and dO land first and becomes a ring slot once they have been copied to TMEM.  With equal depths K and V
+// of a step share one barrier pair; otherwise a V slot is released after the dP GEMM and a K slot after the dQ GEMM.
 
 #define AE_BM 128
 #define AE_NTHREADS_BWD 320
@@ -91,8 +91,20 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
 #else
   n_steps = n_kt_bn;
 #endif
-  // step -> (first kv column, needs element mask)
+  // step -> (first kv column, needs element mask).  dQ is a plain sum over the kv tiles, so every CTA walks them
+  // from its own starting point (AE_DQ_ROTATE): CTAs that run together then read different tiles at any one time
+  // instead of all asking L2 for the same lines.
+#ifndef AE_DQ_ROTATE
+#define AE_DQ_ROTATE 1
+#endif
+#if AE_DQ_ROTATE
+  const int rot = n_steps > 0 ? (int)(((u32)qt * 2654435761u + (u32)hq * 40503u + (u32)b * 9973u) >> 8) % n_steps : 0;
+#else
+  const int rot = 0;
+#endif
   auto step_info = [&](int s, int& kv0, bool& partial) {
+    s += rot;
+    if (s >= n_steps) s -= n_steps;
 #if AE_MASK_MODE == 2
     const int e = list[s / AE_NSUB];
     kv0 = (e & 0x3fffffff) * 128 + (s % AE_NSUB) * AE_BWD_BN;
@@ -160,17 +172,28 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
         AE_TR(true, 3, s * 8 + 0)
         if (!mbar_wait(&bars->k_empty[ks], ((s / AE_DQ_KSTAGES) & 1) ^ 1, ctl, args.status, 21)) break;
         AE_TR(true, 3, s * 8 + 1)
+#if AE_DQ_KSTAGES == AE_DQ_VSTAGES
+        // equal ring depths: K and V of a step share one barrier pair, which saves the MMA warp a wait per step
+        // (a wait costs it 200 - 400 clk even when the data is there)
+        mbar_arrive_expect_tx(&bars->k_full[ks], AE_DQ_K_BYTES + AE_DQ_V_BYTES);
+#else
         mbar_arrive_expect_tx(&bars->k_full[ks], AE_DQ_K_BYTES);
+#endif
         for (int dh = 0; dh < AE_D / 64; ++dh)
           tma_load_bshd(smem + AE_DQ_SMEM_K + ks * AE_DQ_K_BYTES + dh * (AE_BWD_BN * 128), &args.tm_k,
                       &bars->k_full[ks], dh * 64, hk, kv0, b);
         AE_TR(true, 3, s * 8 + 2)
+#if AE_DQ_KSTAGES == AE_DQ_VSTAGES
+        u64* vbar = &bars->k_full[ks];
+#else
         if (!mbar_wait(&bars->v_empty[vs], ((s / AE_DQ_VSTAGES) & 1) ^ 1, ctl, args.status, 22)) break;
+        u64* vbar = &bars->v_full[vs];
+        mbar_arrive_expect_tx(vbar, AE_DQ_V_BYTES);
+#endif
         AE_TR(true, 3, s * 8 + 3)
-        mbar_arrive_expect_tx(&bars->v_full[vs], AE_DQ_V_BYTES);
         for (int dh = 0; dh < AE_DV / 64; ++dh)
-          tma_load_bshd(smem + AE_DQ_SMEM_V + vs * AE_DQ_V_BYTES + dh * (AE_BWD_BN * 128), &args.tm_v,
-                      &bars->v_full[vs], dh * 64, hk, kv0, b);
+          tma_load_bshd(smem + AE_DQ_SMEM_V + vs * AE_DQ_V_BYTES + dh * (AE_BWD_BN * 128), &args.tm_v, vbar, dh * 64, hk,
+                      kv0, b);
       }
     }
   } else if (warp == 9) {
@@ -186,8 +209,9 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       auto issue_s = [&](int s) -> bool {  // S_s = Q K_s^T
         const int stage = s % AE_DQ_KSTAGES;
         if (!mbar_wait_w(&bars->k_full[stage], (s / AE_DQ_KSTAGES) & 1, ctl, args.status, 24)) return false;
-        tc_fence_after_sync();
         AE_TR(s > 0, 0, (s - 1) * 8 + 6)
+        tc_fence_after_sync();
+        AE_TR(s > 0, 0, (s - 1) * 8 + 7)
         const u64 dkk = dk0 + (u64)((stage * AE_DQ_K_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_D / 16; ++kk)
@@ -197,15 +221,18 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       };
       auto issue_dp = [&](int s) -> bool {  // dP_s = dO V_s^T
         const int stage = s % AE_DQ_VSTAGES;
+#if AE_DQ_KSTAGES != AE_DQ_VSTAGES
         if (!mbar_wait_w(&bars->v_full[stage], (s / AE_DQ_VSTAGES) & 1, ctl, args.status, 25)) return false;
         tc_fence_after_sync();
-        AE_TR(s > 0, 0, (s - 1) * 8 + 7)
+#endif
         const u64 dvv = dv0 + (u64)((stage * AE_DQ_V_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_DV / 16; ++kk)
           umma_ts_w(tmem + TM_DP, tmem + TM_DO + kk * 8, umma_step_k(dvv, kk, AE_BWD_BN), idesc_s, kk > 0);
         umma_commit_w(&bars->dp_full);
+#if AE_DQ_KSTAGES != AE_DQ_VSTAGES
         umma_commit_w(&bars->v_empty[stage]);
+#endif
         return true;
       };
 
@@ -316,29 +343,32 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       ok = ok && mbar_wait(&bars->s_full, s & 1, ctl, args.status, 27);
       tc_fence_after_sync();
       AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 1)
+      // S_s goes to registers first and is released at once (the next S GEMM then runs under this tile's row work);
+      // P is computed from the registers afterwards.
+      static_assert(NCH == 2, "phase A loads its two chunks with one paired TMEM load");
+      float sv[NCH][32];
+      tmem_ld_2xf32x32(tm_s + wg * 32, tm_s + (wg + 2) * 32, sv[0], sv[1]);
+      tc_fence_before_sync();
+      mbar_arrive_warp(&bars->a_done);  // S_s has been read: the next S may overwrite it
+      AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 2)
       auto phase_a = [&](auto masked_tag) {
         constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
         for (int ci = 0; ci < NCH; ++ci) {
           const int c = wg + 2 * ci;
-          float sv[32];
-          tmem_ld_f32x32(tm_s + c * 32, sv);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int kv_idx = kv0 + c * 32 + i;
-            float p = ae_bwd_p(sv[i], fr, b, hq, q_idx, kv_idx, cu, i);
+            float p = ae_bwd_p(sv[ci][i], fr, b, hq, q_idx, kv_idx, cu, i);
             if (kMasked && !keep_of(kv_idx)) p = 0.f;
             pkeep[ci][i] = p;
 #if AE_DS_USES_S
-            skeep[ci][i] = sv[i];
+            skeep[ci][i] = sv[ci][i];
 #endif
           }
         }
       };
       if (masked) phase_a(AeTrue{}); else phase_a(AeFalse{});
-      tc_fence_before_sync();
-      mbar_arrive_warp(&bars->a_done);  // S_s has been read: the next S may overwrite it
-      AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 2)
 
       // ---- phase B: dS from dP and the P kept in registers ----------------------------------------
       ok = ok && mbar_wait(&bars->dp_full, s & 1, ctl, args.status, 18);

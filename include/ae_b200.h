@@ -242,6 +242,8 @@ int ae_launch_linear_bwd(void* module, const AeLinearBwdParams* p, void* stream)
 /* ---- bring-up probe (tests only): one 128x128x128 tcgen05 GEMM -------------------
  * mode 0: d = a * b^T (a, b [128,128] 16-bit row-major);
  * mode 1: d = p * b   (p, b [128,128] 16-bit row-major). d is [128,128] fp32.
+ * The rate micro-benchmarks (mma_rate.cuh, tma_rate.cuh) are launched through the same entry: the low 16 bits of
+ * `mode` are their repeat count, bits 16.. the number of CTAs (0 = one).
  * No counterpart in the reference. */
 int ae_launch_probe(void* module, const void* a, const void* b, const void* p, float* d, int mode, uint32_t* status,
                     void* stream);
