@@ -163,6 +163,12 @@ AE_DEVICE void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thre
 AE_DEVICE void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 AE_DEVICE void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 AE_DEVICE void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Non-blocking arrival on a named barrier (the waiting side calls named_bar_sync with the same id and count).
+// A named barrier costs the waiting warp about 20 clk, an mbarrier wait 100 - 400 clk; it has no time-out, so it is
+// only used where the arriving side is guaranteed to arrive (row threads arrive in every iteration, aborted or not).
+AE_DEVICE void named_bar_arrive(u32 id, u32 nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 AE_DEVICE void named_bar_sync(u32 id, u32 nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

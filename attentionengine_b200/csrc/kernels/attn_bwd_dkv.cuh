@@ -55,6 +55,8 @@
 #endif
 #define AE_KV_SMEM_CS (AE_KV_SMEM_DO + AE_KV_DOSTAGES * AE_KV_DO_BYTES)
 #define AE_KV_CS_BYTES (2 * AE_BWD_BN * AE_NCS * 4)
+// equal ring depths: Q and dO of a step share one barrier pair (one wait less per step for the MMA warp)
+#define AE_KV_ONE_BAR (AE_KV_QSTAGES == AE_KV_DOSTAGES && !AE_KV_TS)
 #define AE_KV_NROW (AE_KV_NWG * 128)
 #define AE_KV_NTHREADS (AE_KV_NROW + 64)
 #define AE_KV_SMEM_BAR (AE_KV_SMEM_CS + ((AE_KV_CS_BYTES + 15) / 16) * 16)
@@ -223,7 +225,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
 #endif
       if (!mbar_wait_w(&bars->q_empty[sq], ((s / AE_KV_QSTAGES) & 1) ^ 1, ctl, args.status, 31)) break;
       if (lane == 0) {
-        mbar_arrive_expect_tx(&bars->q_full[sq], AE_KV_Q_BYTES);
+        mbar_arrive_expect_tx(&bars->q_full[sq], AE_KV_ONE_BAR ? AE_KV_Q_BYTES + AE_KV_DO_BYTES : AE_KV_Q_BYTES);
         for (int dh = 0; dh < AE_D / 64; ++dh)
           tma_load_bshd(smem + AE_KV_SMEM_Q + sq * AE_KV_Q_BYTES + dh * (AE_BWD_BN * 128), &args.tm_q, &bars->q_full[sq],
                       dh * 64, st.hq, st.q0, b);
@@ -250,6 +252,13 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
 #if AE_KV_TS
       if (s == AE_KV_DOSTAGES - AE_KV_SLOTS && !mbar_wait_w(&bars->kv_tmem, 0, ctl, args.status, 44)) break;
 #endif
+#if AE_KV_ONE_BAR
+      if (lane == 0) {  // the slot pair was released by q_empty; dO completes the same barrier as Q
+        for (int dh = 0; dh < AE_DV / 64; ++dh)
+          tma_load_bshd(smem + AE_KV_SMEM_DO + sd * AE_KV_DO_BYTES + dh * (AE_BWD_BN * 128), &args.tm_do,
+                      &bars->q_full[sq], dh * 64, st.hq, st.q0, b);
+      }
+#else
       if (!mbar_wait_w(&bars->do_empty[sd], ((s / AE_KV_DOSTAGES) & 1) ^ 1, ctl, args.status, 38)) break;
       if (lane == 0) {
         mbar_arrive_expect_tx(&bars->do_full[sd], AE_KV_DO_BYTES);
@@ -257,6 +266,7 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
           tma_load_bshd(smem + AE_KV_SMEM_DO + sd * AE_KV_DO_BYTES + dh * (AE_BWD_BN * 128), &args.tm_do,
                       &bars->do_full[sd], dh * 64, st.hq, st.q0, b);
       }
+#endif
       ++s;
     }
   } else if (warp == AE_KV_NWG * 4 + 1) {
@@ -275,8 +285,9 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       const u64 dqmn0 = umma_base_mn(q_addr, AE_BWD_BN), ddomn0 = umma_base_mn(do_addr, AE_BWD_BN);
       auto issue_s = [&](int s) -> bool {  // S^T_s = K Q_s^T
         const int stage = s % AE_KV_QSTAGES;
+        // (no tcgen05 fence after a wait for shared-memory operands: the TMEM hazards of this GEMM were fenced with
+        // the p_full / ds_full waits that precede it in program order)
         if (!mbar_wait_w(&bars->q_full[stage], (s / AE_KV_QSTAGES) & 1, ctl, args.status, 32)) return false;
-        tc_fence_after_sync();
         const u64 dqq = dq0 + (u64)((stage * AE_KV_Q_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_D / 16; ++kk)
@@ -290,8 +301,9 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       };
       auto issue_dp = [&](int s) -> bool {  // dP^T_s = V dO_s^T
         const int stage = s % AE_KV_DOSTAGES;
+#if !AE_KV_ONE_BAR
         if (!mbar_wait_w(&bars->do_full[stage], (s / AE_KV_DOSTAGES) & 1, ctl, args.status, 33)) return false;
-        tc_fence_after_sync();
+#endif
         const u64 ddd = ddo0 + (u64)((stage * AE_KV_DO_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < AE_DV / 16; ++kk)
@@ -332,7 +344,9 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         for (int kk = 0; kk < AE_BWD_BN / 16; ++kk)
           umma_ts_w(tmem + TM_DV, tmem + TM_S + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(ddm, kk), idesc_dv,
                   (s > 0) | (kk > 0));
+#if !AE_KV_ONE_BAR
         umma_commit_w(&bars->do_empty[sd]);
+#endif
         AE_TRK(true, 0, s * 8 + 2)
         if (s + 1 < n_steps) ok = issue_s(s + 1);
         if (!ok) break;

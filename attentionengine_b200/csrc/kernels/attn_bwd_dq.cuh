@@ -27,6 +27,11 @@
 
 #define AE_BM 128
 #define AE_NTHREADS_BWD 320
+// Row warps -> MMA warp hand-offs (S read, dS written) through named barriers instead of mbarriers.  The MMA warp
+// stops syncing when it aborts; the row warps never block on these barriers, and they arrive in every iteration.
+#ifndef AE_DQ_NAMED_BAR
+#define AE_DQ_NAMED_BAR 1
+#endif
 // Optional phase trace of CTA (0, 0, 0): 32-bit clock stamps behind the status word (bring-up / tuning only).
 #ifdef AE_TRACE
 #define AE_TR(cond, region, slot) \
@@ -208,9 +213,10 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
 
       auto issue_s = [&](int s) -> bool {  // S_s = Q K_s^T
         const int stage = s % AE_DQ_KSTAGES;
+        // (no tcgen05 fence here: the operands waited for are in shared memory; the TMEM hazard of this GEMM, the row
+        // threads' reads of the previous S, was fenced with the a_done wait)
         if (!mbar_wait_w(&bars->k_full[stage], (s / AE_DQ_KSTAGES) & 1, ctl, args.status, 24)) return false;
         AE_TR(s > 0, 0, (s - 1) * 8 + 6)
-        tc_fence_after_sync();
         AE_TR(s > 0, 0, (s - 1) * 8 + 7)
         const u64 dkk = dk0 + (u64)((stage * AE_DQ_K_BYTES) >> 4);
 #pragma unroll
@@ -245,16 +251,24 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
         const u32 par = s & 1;
         AE_TR(true, 0, s * 8 + 0)
         // the next S goes over S_s once the row threads have read it
+#if AE_DQ_NAMED_BAR
+        named_bar_sync(1, 256 + 32);  // the 8 row warps arrive in every iteration, whatever happened: no time-out needed
+#else
         ok = mbar_wait_w(&bars->a_done, par, ctl, args.status, 26);
         if (!ok) break;
+#endif
         tc_fence_after_sync();
         AE_TR(true, 0, s * 8 + 1)
         if (s + 1 < n_steps) ok = issue_s(s + 1);
         if (!ok) break;
         AE_TR(true, 0, s * 8 + 2)
         // dQ += dS_s K_s, then the next dP goes over dS_s
+#if AE_DQ_NAMED_BAR
+        named_bar_sync(2, 256 + 32);
+#else
         ok = mbar_wait_w(&bars->ds_full, par, ctl, args.status, 29);
         if (!ok) break;
+#endif
         tc_fence_after_sync();
         AE_TR(true, 0, s * 8 + 3)
         const u64 dkm = dkmn0 + (u64)((stage * AE_DQ_K_BYTES) >> 4);
@@ -349,7 +363,11 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       float sv[NCH][32];
       tmem_ld_2xf32x32(tm_s + wg * 32, tm_s + (wg + 2) * 32, sv[0], sv[1]);
       tc_fence_before_sync();
-      mbar_arrive_warp(&bars->a_done);  // S_s has been read: the next S may overwrite it
+#if AE_DQ_NAMED_BAR
+      named_bar_arrive(1, 256 + 32);  // S_s has been read: the next S may overwrite it
+#else
+      mbar_arrive_warp(&bars->a_done);
+#endif
       AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 2)
       auto phase_a = [&](auto masked_tag) {
         constexpr bool kMasked = decltype(masked_tag)::value;
@@ -408,7 +426,11 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
       AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 4)
       tc_wait_st();
       tc_fence_before_sync();
+#if AE_DQ_NAMED_BAR
+      named_bar_arrive(2, 256 + 32);
+#else
       mbar_arrive_warp(&bars->ds_full);
+#endif
       AE_TR((warp & 3) == 0, 1 + wg, s * 8 + 5)
     }
 

@@ -281,7 +281,8 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
               if (!ok) return;
               q_ready |= 1u << t;
             }
-            tc_fence_after_sync();
+            // (no tcgen05 fence: the waits above are for shared-memory operands; the S region's last TMEM accesses by
+            // other threads were fenced with the p_full wait of the step that made them)
             issue_s(T, nstage);
             umma_commit(&bars->s_full[t]);
           }
