@@ -57,6 +57,11 @@
 #define AE_KV_CS_BYTES (2 * AE_BWD_BN * AE_NCS * 4)
 // equal ring depths: Q and dO of a step share one barrier pair (one wait less per step for the MMA warp)
 #define AE_KV_ONE_BAR (AE_KV_QSTAGES == AE_KV_DOSTAGES && !AE_KV_TS)
+// Row warps -> MMA warp hand-offs (P^T written, dS^T written) through named barriers instead of mbarriers: the MMA
+// warp stops syncing when it aborts, the row warps never block on them and arrive in every iteration.
+#ifndef AE_KV_NAMED_BAR
+#define AE_KV_NAMED_BAR 1
+#endif
 #define AE_KV_NROW (AE_KV_NWG * 128)
 #define AE_KV_NTHREADS (AE_KV_NROW + 64)
 #define AE_KV_SMEM_BAR (AE_KV_SMEM_CS + ((AE_KV_CS_BYTES + 15) / 16) * 16)
@@ -333,10 +338,15 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       for (int s = 0; s < n_steps && ok; ++s) {
         const int sq = s % AE_KV_QSTAGES, sd = s % AE_KV_DOSTAGES;
         const u32 par = s & 1;
+        (void)par;
         // dV += P^T dO_s, then the next S^T goes over P^T (in issue order, so after it has been read)
         AE_TRK(true, 0, s * 8 + 0)
+#if AE_KV_NAMED_BAR
+        named_bar_sync(1, AE_KV_NROW + 32);
+#else
         ok = mbar_wait_w(&bars->p_full, par, ctl, args.status, 35);
         if (!ok) break;
+#endif
         tc_fence_after_sync();
         AE_TRK(true, 0, s * 8 + 1)
         const u64 ddm = ddomn0 + (u64)((sd * AE_KV_DO_BYTES) >> 4);
@@ -352,8 +362,12 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
         if (!ok) break;
         AE_TRK(true, 0, s * 8 + 3)
         // dK += dS^T Q_s, then the next dP^T goes over dS^T
+#if AE_KV_NAMED_BAR
+        named_bar_sync(2, AE_KV_NROW + 32);
+#else
         ok = mbar_wait_w(&bars->ds_full, par, ctl, args.status, 39);
         if (!ok) break;
+#endif
         tc_fence_after_sync();
         AE_TRK(true, 0, s * 8 + 4)
         const u64 dqm = dqmn0 + (u64)((sq * AE_KV_Q_BYTES) >> 4);
@@ -483,7 +497,11 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 2)
       tc_wait_st();
       tc_fence_before_sync();
+#if AE_KV_NAMED_BAR
+      named_bar_arrive(1, AE_KV_NROW + 32);
+#else
       mbar_arrive_warp(&bars->p_full);
+#endif
       AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 3)
 
       // ---- phase B: dS^T from dP^T and the P^T kept in registers --------------------------------
@@ -531,7 +549,11 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
       AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 5)
       tc_wait_st();
       tc_fence_before_sync();
+#if AE_KV_NAMED_BAR
+      named_bar_arrive(2, AE_KV_NROW + 32);
+#else
       mbar_arrive_warp(&bars->ds_full);
+#endif
       mbar_arrive_warp(&bars->cs_empty[s & 1]);
       AE_TRK((warp & 3) == 0, 1 + wg, s * 8 + 6)
       ++s;
