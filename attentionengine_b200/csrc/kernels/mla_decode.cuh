@@ -49,7 +49,6 @@ struct AeMlaBars {
   u64 kv_full[AE_MLA_STAGES];
   u64 kv_empty[AE_MLA_STAGES];
   u64 s_full[2];
-  u64 p_full[2];
   u64 o_done;
   AeCtaCtl ctl;
 };
@@ -83,7 +82,6 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
       mbar_init(&bars->kv_full[i], 1);
       mbar_init(&bars->kv_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->p_full[i], 4);
     }
     mbar_fence_init();
   }
@@ -172,8 +170,9 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
         }
         if (!ok) break;
         AE_TRM(true, 0, s * 8 + 3)
-        ok = mbar_wait_w(&bars->p_full[s & 1], (s >> 1) & 1, ctl, args.status, 44);
-        if (!ok) break;
+        // P of tile s: a named barrier (the four row warps arrive in every iteration, whatever happened; about 20 clk
+        // for this warp against 100 - 400 clk for an mbarrier wait)
+        named_bar_sync(1 + (s & 1), 128 + 32);
         tc_fence_after_sync();
         AE_TRM(true, 0, s * 8 + 4)
         // V = this half's four 64-wide blocks of the same tile, read MN-major
@@ -277,7 +276,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
 #endif
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive_warp(&bars->p_full[s & 1]);
+      named_bar_arrive(1 + (s & 1), 128 + 32);
       AE_TRM(warp == 0, 1, s * 8 + 2)
     }
 
