@@ -181,6 +181,11 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch at B=2, Hq=32, Hkv=8, S=8192, D=128 (ncu, one B200)
+NCU_DRAM_BYTES_AT_BATCH2 = {"ae_attn_fwd": 301.5e6, "ae_attn_bwd_dq": 450.9e6, "ae_attn_bwd_dkv": 396.6e6,
+                            "ae_attn_bwd_prep": 273.6e6}
+
+
 def time_events(torch, fn, steps, warmup):
     for _ in range(warmup):
         fn()
@@ -497,7 +502,11 @@ def main():
         ach = kernels[dom]["flops"] / (kernels[dom]["ms"] / 1e3) / 1e12
         peak = float(peaks.get("bf16_tflops", 1590.0))
         roofline = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                    "frac": ach / peak, "peak_source": f"{which} cuBLAS bf16 burst", "traffic": None,
+                    "frac": ach / peak, "peak_source": f"{which} cuBLAS bf16 burst",
+                    # DRAM bytes per launch of that kernel (dram__bytes_read.sum + dram__bytes_write.sum): taken from an
+                    # ncu capture at batch 2 (profiles/attention_kernels_cfg2_batch2.md) and scaled by the batch, to
+                    # which the traffic is proportional
+                    "traffic": NCU_DRAM_BYTES_AT_BATCH2.get(dom, 0.0) * (B / 2.0) or None,
                     "kernels": {n: {"ms": round(d["ms"], 4), "tflops": round(d["flops"] / (d["ms"] / 1e3) / 1e12, 1)}
                                 for n, d in kernels.items()}}
         cpu = None
