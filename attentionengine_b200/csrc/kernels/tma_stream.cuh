@@ -4,7 +4,9 @@
 // AE_TS_DEPTH steps in flight and reports bytes per clock in final_rs[0][linear CTA index].
 // AE_TS_MMA = 1 / 2 adds a second warp that issues TS / SS MMAs (M = 128, N = 128, operands in a shared-memory
 // region of its own, results discarded) for as long as the loads run: does tensor-core operand traffic slow the fill?
-// Expects AE_D, AE_DV, AE_TS_DEPTH, AE_TS_ROTATE, AE_TS_MMA.
+// AE_TS_LD = 1 adds a third warp that times tcgen05.ld (32 lanes x 32 columns, with its wait) in a loop while the
+// other two run: what a row thread's TMEM read costs under tensor-pipe load (reported in final_rs[1]).
+// Expects AE_D, AE_DV, AE_TS_DEPTH, AE_TS_ROTATE, AE_TS_MMA, AE_TS_LD.
 
 #define AE_TS_SLOTS 3
 #define AE_TS_K_BYTES (128 * AE_D * 2)
@@ -19,7 +21,7 @@ struct AeTsBars {
 };
 #define AE_TS_OPER (AE_TS_SLOTS * AE_TS_STEP)  // 32 KB of MMA operands behind the ring
 
-extern "C" __global__ void __launch_bounds__(64, 1) ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
+extern "C" __global__ void __launch_bounds__(96, 1) ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
   extern __shared__ u8 smem_raw[];
   u8* smem = smem_align1024(smem_raw);
   AeTsBars* bars = (AeTsBars*)(smem + AE_TS_OPER + 32768);
@@ -64,8 +66,37 @@ extern "C" __global__ void __launch_bounds__(64, 1) ae_attn_fwd(const __grid_con
       phase ^= 1;
     }
     tc_fence_before_sync();
+#if AE_TS_LD
+    named_bar_sync(5, 64);  // the reading warp has issued its last TMEM load
+    tc_fence_after_sync();
+#endif
     __syncwarp();
     tmem_dealloc(tmem, 512);
+    return;
+  }
+#endif
+#if AE_TS_MMA && AE_TS_LD
+  if (warp == 2) {
+    const u32 tmem = ctl->tmem_base;
+    const u32 lane_base = (2u * 32u) << 16;  // warp 2 reads TMEM lanes 64..95
+    float acc = 0.f;
+    i64 total = 0;
+    int n = 0;
+    for (int it = 0; it < 4096 && !bars->stop; ++it) {
+      float r[32];
+      const i64 t0 = clock64();
+      tmem_ld_f32x32(tmem + lane_base + (it & 3) * 32, r);
+      const i64 t1 = clock64();
+      acc += r[it & 31];
+      total += t1 - t0;
+      ++n;
+    }
+    if ((threadIdx.x & 31) == 0) {
+      const i64 cta = ((i64)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+      args.final_rs[1][cta] = n ? (float)total / n + 0.f * acc : 0.f;
+    }
+    tc_fence_before_sync();
+    named_bar_sync(5, 64);  // lets the allocating warp free TMEM
     return;
   }
 #endif
