@@ -63,6 +63,8 @@ class H100:
     always targets B200."""
 
 
+MAX_LIST_KV_TILES = 2048  # kv tiles a block list may cover (AE_MAX_KT of attn_fwd.cuh): 262,144 keys
+
 _TORCH_DTYPES = {torch.float16: rt.DTYPE_F16, torch.bfloat16: rt.DTYPE_BF16}
 
 
@@ -104,6 +106,8 @@ class _AttnKernels:
         self.low = low
         self.D, self.DV, self.dtype_tag, self.mask_mode, self.stages = D, DV, dtype_tag, mask_mode, stages
         smem = 2 * 128 * D * 2 + stages * 128 * (D + DV) * 2 + 512 + 1024
+        if mask_mode == 2:
+            smem += 4 * MAX_LIST_KV_TILES  # the CTA's merged tile walk
         cfg = rt.KernelConfig(kind=rt.KIND_ATTN_FWD, dtype=dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
                               smem_bytes=smem, stages=stages, mask_mode=mask_mode)
         self.fwd_src = rt.kernel_source("attn_fwd.cuh", prelude=low.prelude_fwd)

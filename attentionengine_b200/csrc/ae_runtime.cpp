@@ -382,6 +382,10 @@ int ae_launch_attn_fwd(void* module, const AeAttnParams* p, void* stream) {
     set_error("block lists required for mask_mode 2");
     return AE_ERR_INVALID;
   }
+  if (m->cfg.mask_mode == 2 && (p->Skv + 127) / 128 > 2048) {
+    set_error("block lists cover at most 2048 kv tiles (262144 keys)");
+    return AE_ERR_INVALID;
+  }
   rc = ensure_loaded(m);
   if (rc) return rc;
   AeAttnFwdArgs args;

@@ -32,7 +32,8 @@
 #define AE_SMEM_K (2 * AE_Q_BYTES)
 #define AE_SMEM_V (AE_SMEM_K + AE_STAGES * AE_K_BYTES)
 #define AE_SMEM_BAR (AE_SMEM_V + AE_STAGES * AE_V_BYTES)
-#define AE_SMEM_TOTAL (AE_SMEM_BAR + 512)
+#define AE_SMEM_STEPS (AE_SMEM_BAR + 512)  // mask mode 2 only: one word per kv tile
+#define AE_MAX_KT 2048                    // kv tiles a block list may cover (4 * AE_MAX_KT bytes of shared memory)
 
 struct AeFwdBars {
   u64 q_full[2];
@@ -44,15 +45,18 @@ struct AeFwdBars {
   u64 p_full[2];
   u64 o_done[2];
   AeCtaCtl ctl;
+  int n_steps;  // mask mode 2: length of the merged walk
 };
 
 // kv tile schedule of one q tile --------------------------------------------------
 // The CTA walks the union of its two tiles' lists; entry `j` of the walk gives the kv
 // tile index and, per q tile, whether it takes part and whether it needs the
-// element-wise mask.
+// element-wise mask.  With block lists (mask mode 2) the union is built once per CTA in
+// shared memory (a flag word per kv tile, then compacted in place), so that the roles
+// read the same table instead of each merging the two lists from global memory.
 struct AeKvStep {
   int kt;        // kv tile index
-  u32 flags;     // bit t: tile t active; bit 2+t: tile t needs element mask
+  u32 flags;     // bit t: tile t active; bit 2+t: tile t needs element mask; bit 4+t: tile t's P is zero
 };
 
 AE_DEVICE int ae_causal_ntiles(int qt, int n_kt) {
@@ -84,13 +88,8 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
   int n_t1 = (qt0 + 1 < args.n_qt) ? ae_causal_ntiles(qt0 + 1, args.n_kt) : 0;
   n_steps = n_t0 > n_t1 ? n_t0 : n_t1;
 #elif AE_MASK_MODE == 2
-  const int* cnt_base = args.blk_cnt + ((i64)b * args.Hq + hq) * args.n_qt;
-  const int* idx_base = args.blk_idx + ((i64)b * args.Hq + hq) * args.n_qt * (i64)args.n_kt;
-  const int n_t0 = cnt_base[qt0];
-  const int n_t1 = (qt0 + 1 < args.n_qt) ? cnt_base[qt0 + 1] : 0;
-  const int* list0 = idx_base + (i64)qt0 * args.n_kt;
-  const int* list1 = idx_base + (i64)(qt0 + 1) * args.n_kt;
-  n_steps = 0;  // computed by the merge walk below (same code in every role)
+  const u32* steps = (const u32*)(smem + AE_SMEM_STEPS);
+  n_steps = 0;  // read from shared memory after the set-up barrier
 #else
   int n_t0 = args.n_kt;
   int n_t1 = (qt0 + 1 < args.n_qt) ? args.n_kt : 0;
@@ -99,24 +98,14 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 
   // step iterator: all roles call next() in lockstep order
   struct Walk {
-    int j, i0, i1;
-  } walk = {0, 0, 0};
+    int j;
+  } walk = {0};
   auto next_step = [&](AeKvStep& st) -> bool {
 #if AE_MASK_MODE == 2
-    int a = walk.i0 < n_t0 ? (list0[walk.i0] & 0x3fffffff) : 0x7fffffff;
-    int c = walk.i1 < n_t1 ? (list1[walk.i1] & 0x3fffffff) : 0x7fffffff;
-    int kt = a < c ? a : c;
-    if (kt == 0x7fffffff) return false;
-    st.kt = kt;
-    st.flags = 0;
-    if (a == kt) {
-      st.flags |= 1u | (((u32)list0[walk.i0] >> 30) & 1u) << 2;
-      walk.i0++;
-    }
-    if (c == kt) {
-      st.flags |= 2u | (((u32)list1[walk.i1] >> 30) & 1u) << 3;
-      walk.i1++;
-    }
+    if (walk.j >= n_steps) return false;
+    const u32 e = steps[walk.j];
+    st.kt = (int)(e & 0xffffffu);
+    st.flags = e >> 24;
     walk.j++;
     return true;
 #else
@@ -155,6 +144,61 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     }
     mbar_fence_init();
   }
+#if AE_MASK_MODE == 2
+  {
+    // flag word per kv tile: bit t = tile t takes part, bit 2+t = it needs the element mask.  The lists come from the
+    // caller: a count or an entry outside the tile grid empties this CTA's walk and is reported through the status word.
+    u32* tab = (u32*)(smem + AE_SMEM_STEPS);
+    const int* cnt_base = args.blk_cnt + ((i64)b * args.Hq + hq) * args.n_qt;
+    const int* idx_base = args.blk_idx + ((i64)b * args.Hq + hq) * args.n_qt * (i64)args.n_kt;
+    const int n_t0 = cnt_base[qt0];
+    const int n_t1 = (qt0 + 1 < args.n_qt) ? cnt_base[qt0 + 1] : 0;
+    const int* list0 = idx_base + (i64)qt0 * args.n_kt;
+    const int* list1 = idx_base + (i64)(qt0 + 1) * args.n_kt;
+    bool bad = args.n_kt > AE_MAX_KT || n_t0 < 0 || n_t0 > args.n_kt || n_t1 < 0 || n_t1 > args.n_kt;
+    if (!bad)
+      for (int i = threadIdx.x; i < args.n_kt; i += AE_NTHREADS) tab[i] = 0u;
+    __syncthreads();
+    if (!bad) {
+      for (int i = threadIdx.x; i < n_t0 + n_t1; i += AE_NTHREADS) {
+        const bool second = i >= n_t0;
+        const u32 e = (u32)(second ? list1[i - n_t0] : list0[i]);
+        const u32 kt = e & 0x3fffffffu;
+        const u32 part = (e >> 30) & 1u;
+        if (kt >= (u32)args.n_kt)
+          bad = true;
+        else
+          atomicOr(&tab[kt], second ? (2u | part << 3) : (1u | part << 2));
+      }
+    }
+    const int any_bad = __syncthreads_or(bad ? 1 : 0);
+    if (warp == 0) {
+      int n = 0;
+      if (!any_bad) {
+        // in-place compaction: entry kt moves to a position <= kt, and a chunk is read by every lane before it is written
+        for (int base = 0; base < args.n_kt; base += 32) {
+          const int kt = base + (int)lane;
+          const u32 f = kt < args.n_kt ? tab[kt] : 0u;
+          const u32 m = __ballot_sync(0xffffffffu, f != 0u);
+          if (f) {
+            // A kv tile listed for one q tile only is still run for both (bits 4, 5: the other tile's P is zero):
+            // the MMA and TMA roles then see the step pattern of an unmasked walk, whatever the lists hold.
+            u32 g = f;
+            if (!(f & 1u)) g |= 1u | 16u;
+            if (!(f & 2u) && qt0 + 1 < args.n_qt) g |= 2u | 32u;
+            tab[n + __popc(m & ((1u << lane) - 1u))] = (u32)kt | g << 24;
+          }
+          n += __popc(m);
+          __syncwarp();
+        }
+      }
+      if (lane == 0) {
+        bars->n_steps = n;
+        if (any_bad && args.status) atomicCAS(args.status, 0u, 0x400u);
+      }
+    }
+  }
+#endif
   if (warp == 9) {
     tmem_alloc(&ctl->tmem_base, 512);
     tmem_relinquish();
@@ -163,6 +207,9 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
   __syncthreads();
   tc_fence_after_sync();
   const u32 tmem = ctl->tmem_base;
+#if AE_MASK_MODE == 2
+  n_steps = bars->n_steps;
+#endif
   const u32 TM_S0 = 0, TM_S1 = 128, TM_O0 = 256, TM_O1 = 256 + AE_DV;
 
   if (warp == 8) {
@@ -324,6 +371,21 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       if (!(step.flags & (1u << t))) continue;
       ok = ok && mbar_wait(&bars->s_full[t], n_done & 1, ctl, args.status, 9);
       tc_fence_after_sync();
+#if AE_MASK_MODE == 2
+      if ((step.flags >> (4 + t)) & 1u) {
+        // kv tile of the other q tile's list: P = 0, the row state and O stay as they are
+        u32 z[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) z[i] = 0u;
+#pragma unroll
+        for (int half = 0; half < AE_BN / 64; ++half) tmem_st32(tm_s + half * 32, z);
+        tc_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive_warp(&bars->p_full[t]);
+        ++n_done;
+        continue;
+      }
+#endif
       float s[AE_BN];
       tmem_ld_f32x128(tm_s, s);
       const int kv0 = step.kt * AE_BN;

@@ -115,7 +115,9 @@ typedef struct AeAttnParams {
   const void* custom[AE_MAX_CUSTOM_INPUTS];
   int64_t custom_stride[AE_MAX_CUSTOM_INPUTS][4]; /* over (b, h, q, kv); 0 = broadcast */
   const int32_t* block_count; /* [B, Hq, n_qt]        (mask_mode 2) */
-  const int32_t* block_index; /* [B, Hq, n_qt, n_kt]  (mask_mode 2) */
+  const int32_t* block_index; /* [B, Hq, n_qt, n_kt]  (mask_mode 2): kv tile | partial << 30; the first block_count
+                                 entries of a row count, in any order; at most 2048 kv tiles (AE_ERR_INVALID beyond);
+                                 an entry outside the grid sets status 0x400 and that CTA writes nothing useful */
   int32_t B, Hq, Hkv, Sq, Skv;
   uint32_t* status;
 } AeAttnParams;

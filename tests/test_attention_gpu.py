@@ -316,6 +316,66 @@ def test_mamba2_ssd_backward_against_oracle(B, H, T):
         mx, rel = orc.error_stats(got.float().cpu(), ref.float())
         lim = 5e-2 if name == "dA" else 1e-2
         assert rel <= lim, f"{name}: rel-L2 {rel:.3e} (max-abs {mx:.3e})"@pytest.mark.gpu
+@pytest.mark.parametrize("D", [64, 128])
+def test_extern_block_mask_given_at_call_time(D):
+    """attn_script/blocksparseattn.py: the engine is built with extern_block_mask=True and no mask_mod, the int8 block
+    mask [B, H, S/128, S/128] arrives with the call; listed blocks are complete blocks.  Forward and gradients
+    against dense softmax attention under the expanded mask."""
+    B, H, S, dtype = 1, 2, 640, torch.float16
+    g = torch.Generator().manual_seed(5)
+    n = S // 128
+    bm = (torch.rand(B, H, n, n, generator=g) < 0.5)
+    bm |= torch.eye(n, dtype=torch.bool)          # no empty row: a row without blocks is 0 / 0 in the softmax epilogue
+    scale = 1.0 / math.sqrt(D)
+    eng = AttentionEngine(helpers.metas(B, H, H, S, D, D, dtype), CustomIO({}),
+                          score_mod=lambda s, c, b, h, q, kv: s * scale, mask_mod=None,
+                          online_func=helpers.OnlineSoftmax(), extern_block_mask=True)
+    q, k, v, d_o = helpers.seeded_qkv(B, H, H, S, D, D, dtype, seed=31)
+    qd, kd, vd = (t.cuda().requires_grad_() for t in (q, k, v))
+    o = eng(qd, kd, vd, block_mask=bm.to(torch.int8).cuda())
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    dense = bm.repeat_interleave(128, 2).repeat_interleave(128, 3)  # [B, H, S, S]
+
+    def ref(a, b_, c):
+        s_ = torch.einsum("bqhd,bkhd->bhqk", a, b_) * scale
+        s_ = s_.masked_fill(~dense, float("-inf"))
+        p = torch.softmax(s_, -1)
+        p = torch.nan_to_num(p, nan=0.0)               # rows with no block at all
+        return torch.einsum("bhqk,bkhd->bqhd", p, c)
+
+    ro, (rq, rk, rv) = orc.fwd_bwd(ref, (q, k, v), d_o)
+    for name, got, r in zip(("o", "dq", "dk", "dv"), (o, qd.grad, kd.grad, vd.grad), (ro, rq, rk, rv)):
+        _check(name, got.detach().cpu(), r, dtype)
+
+
+@pytest.mark.gpu
+def test_element_mask_without_block_inference():
+    """infer_mask=False: every tile is visited and masked element by element (mask mode 3); a banded mask that the
+    block inference would have turned into tile lists."""
+    B, H, S, D, dtype, W = 1, 2, 384, 64, torch.float16, 100
+    scale = 1.0 / math.sqrt(D)
+    band = lambda b, h, q_idx, kv_idx: torch.logical_and(q_idx >= kv_idx, q_idx - kv_idx < W)  # noqa: E731
+    eng = AttentionEngine(helpers.metas(B, H, H, S, D, D, dtype), CustomIO({}),
+                          score_mod=lambda s, c, b, h, q, kv: s * scale, mask_mod=band,
+                          online_func=helpers.OnlineSoftmax(), infer_mask=False)
+    assert eng.mask_mode == 3
+    q, k, v, d_o = helpers.seeded_qkv(B, H, H, S, D, D, dtype, seed=32)
+    got = _run(eng, q, k, v, d_o)
+    i = torch.arange(S)
+    keep = (i[:, None] >= i[None, :]) & (i[:, None] - i[None, :] < W)
+
+    def ref(a, b_, c):
+        s_ = torch.einsum("bqhd,bkhd->bhqk", a, b_) * scale
+        return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s_.masked_fill(~keep, float("-inf")), -1), c)
+
+    ro, grads = orc.fwd_bwd(ref, (q, k, v), d_o)
+    for name, g_, r in zip(("o", "dq", "dk", "dv"), got, (ro,) + tuple(grads)):
+        _check(name, g_, r, dtype)
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("S,causal", [(384, True), (200, False)])
 def test_softcap_score_mod_keeps_the_raw_score_for_the_backward(S, causal):
     """score_mod = cap * tanh(score * scale / cap): its derivative needs the raw score again, so the backward passes
