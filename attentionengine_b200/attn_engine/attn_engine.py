@@ -63,6 +63,7 @@ class H100:
     always targets B200."""
 
 
+_DYN_PROBE = 1024  # sequence length on which a dynamic-shape engine classifies its mask
 MAX_LIST_KV_TILES = 2048  # kv tiles a block list may cover (AE_MAX_KT of attn_fwd.cuh): 262,144 keys
 
 _TORCH_DTYPES = {torch.float16: rt.DTYPE_F16, torch.bfloat16: rt.DTYPE_BF16}
@@ -167,9 +168,12 @@ class AttentionEngine:
         self._lists = None
         self._status = None
         dynamic = any(isinstance(x, str) for x in (B, Hq, Sq, Skv))
+        self._dynamic = dynamic
+        self._lists_by_shape = {}
 
         # shape-class dispatch, as attn_engine.py:218-332
         self._mla = None
+        self._decode = None
         if kv_shared:
             from .mla_decode import MlaDecode
             self._mla = MlaDecode(score_mod, online_func, self.custom_fwd_inputs, Hq, D, DV, self.dtype)
@@ -177,7 +181,15 @@ class AttentionEngine:
             self.mask_mode = 0
             return
         if not dynamic and Sq != Skv:
-            raise NotImplementedError("decode (q_len != kv_len) kernels are not built yet")
+            # decode shape classes (reference: attn_engine.py:252-286): split-KV kernel + OnlineFunc.combine
+            if Sq > Skv:
+                raise NotImplementedError("q_len > kv_len is not an attention shape the reference defines")
+            from .attn_decode import AttnDecode
+            self._decode = AttnDecode(score_mod, mask_mod, online_func, self.custom_fwd_inputs, Hq, Hkv, Sq, D, DV,
+                                      self.dtype, mask_value)
+            self.tl_code = self._decode.src
+            self.mask_mode = 0
+            return
         if isinstance(D, str) or isinstance(DV, str) or D % 64 or DV % 64 or D > 128 or DV > 128:
             raise NotImplementedError(f"head dims D={D}, DV={DV}: multiples of 64 up to 128 are supported")
         if not isinstance(Hq, str) and not isinstance(Hkv, str):
@@ -201,6 +213,13 @@ class AttentionEngine:
                     self._mask_counts = cnt
                 if infer_mask_block_M == 128 and infer_mask_block_N == 128:
                     self.block_mask = (cnt > 0).to(torch.int8).expand(B, Hq, cnt.shape[2], cnt.shape[3])
+            elif infer_mask:
+                # Dynamic shapes (named dims, reference: lower.py:626-629): the kernels do not depend on B, H or S, only
+                # the tile lists do.  The mask is classified on a probe shape: exactly causal there -> analytic bounds
+                # for every length; anything else -> lists, built per runtime shape at the first call with it.
+                probe = block_mask_counts(mask_mod, 2, 2, _DYN_PROBE, _DYN_PROBE, "cpu", 128, 128)
+                causal_cnt = block_mask_counts(lambda b, h, q, kv: q >= kv, 1, 1, _DYN_PROBE, _DYN_PROBE, "cpu", 128, 128)
+                mask_mode = 1 if probe.shape[:2] == (1, 1) and torch.equal(probe, causal_cnt) else 2
             else:
                 mask_mode = 3  # no block information: visit every tile, mask every element
         self.mask_mode = mask_mode
@@ -222,6 +241,8 @@ class AttentionEngine:
         """Raise if a kernel of this engine recorded a bounded-wait timeout."""
         if self._mla is not None:
             self._status = self._mla._status
+        if self._decode is not None:
+            self._status = self._decode._status
         if self._status is not None:
             code = int(self._status.item())
             if code:
@@ -240,6 +261,14 @@ class AttentionEngine:
                 cols = torch.clamp(Skv - torch.arange(nk) * 128, max=128).view(1, 1, 1, nk)
                 cnt = (cnt > 0).to(torch.int32) * rows * cols
             return _block_lists(cnt, 128, 128, Sq, Skv, B, Hq, device)
+        if self._dynamic and self.mask_mod is not None:
+            key = (B, Hq, Sq, Skv, str(device))
+            if key not in self._lists_by_shape:
+                if len(self._lists_by_shape) >= 16:  # a serving loop over many lengths must not grow without bound
+                    self._lists_by_shape.pop(next(iter(self._lists_by_shape)))
+                cnt = block_mask_counts(self.mask_mod, B, Hq, Sq, Skv, "cpu", 128, 128)
+                self._lists_by_shape[key] = _block_lists(cnt, 128, 128, Sq, Skv, B, Hq, device)
+            return self._lists_by_shape[key]
         if self._lists is None or self._lists[0].device != device:
             if self._mask_counts is None:
                 raise ValueError("this engine needs block_mask= at call time (extern_block_mask=True)")
@@ -314,6 +343,8 @@ class AttentionEngine:
     def __call__(self, *args, **kargs):
         if self._mla is not None:
             return self._mla(*args)
+        if self._decode is not None:
+            return self._decode(*args)
         block_mask = kargs.get("block_mask")
         if block_mask is not None:
             self.block_mask = block_mask

@@ -609,6 +609,102 @@ int ae_launch_mla_combine(void* module, const AeMlaParams* p, void* stream) {
   return launch(m, (unsigned)((p->H + 3) / 4), (unsigned)p->B, 1, &a, stream);
 }
 
+int ae_launch_attn_decode(void* module, const AeDecodeParams* p, void* stream) {
+  if (!module || !p || !p->q || !p->k || !p->v || !p->o) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  int rc = check_attn_common(m, AE_KIND_ATTN_DECODE, p->B, p->Hq, p->Hkv, p->Sq, p->Skv);
+  if (rc) return rc;
+  const int gq = p->Hq / p->Hkv;
+  const int rows = gq > 1 ? gq : p->Sq;
+  const int n_kt = (p->Skv + 127) / 128;
+  if (gq > 1 && p->Sq != 1) {
+    set_error("decode with grouped query heads takes one query position");
+    return AE_ERR_UNSUPPORTED;
+  }
+  if (rows > 256) {
+    set_error("decode packs at most 256 query rows per head unit");
+    return AE_ERR_UNSUPPORTED;
+  }
+  if (m->cfg.mask_mode != 0) return AE_ERR_UNSUPPORTED;
+  if (p->n_split < 1 || p->n_split > 32 || p->n_split > n_kt) return AE_ERR_INVALID;
+  const int tps = (n_kt + p->n_split - 1) / p->n_split;
+  if ((p->n_split - 1) * tps >= n_kt) {
+    set_error("n_split leaves a split without kv tiles");
+    return AE_ERR_INVALID;
+  }
+  if (p->n_split > 1) {
+    if (!p->o_partial) return AE_ERR_INVALID;
+    for (int i = 0; i < m->cfg.reserved[1] && i < AE_MAX_FINAL; ++i)
+      if (!p->rowscale_partial[i]) return AE_ERR_INVALID;
+  }
+  rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeAttnFwdArgs args;
+  memset(&args, 0, sizeof args);
+  const int D = m->cfg.head_dim, DV = m->cfg.head_dim_v;
+  if (gq > 1) {
+    // rows of the q tile = the query heads of one kv head: (d, head in group, kv head, b)
+    const int64_t qs[3] = {p->q_stride[0], p->q_stride[2], (int64_t)gq * p->q_stride[2]};
+    rc = make_bshd_map(&args.tm_q, p->q, m->cfg.dtype, p->B, gq, p->Hkv, D, qs, 128);
+  } else {
+    rc = make_bshd_map(&args.tm_q, p->q, m->cfg.dtype, p->B, p->Sq, p->Hq, D, p->q_stride, 128);
+  }
+  if (rc) return rc;
+  rc = make_bshd_map(&args.tm_k, p->k, m->cfg.dtype, p->B, p->Skv, p->Hkv, D, p->k_stride, 128);
+  if (rc) return rc;
+  rc = make_bshd_map(&args.tm_v, p->v, m->cfg.dtype, p->B, p->Skv, p->Hkv, DV, p->v_stride, 128);
+  if (rc) return rc;
+  if (reinterpret_cast<uintptr_t>(p->o) & 15) {
+    set_error("output must be 16-byte aligned");
+    return AE_ERR_INVALID;
+  }
+  args.o = p->o;  // contiguous [B, Sq, Hq, DV]
+  args.o_sh = DV;
+  args.o_ss = (int64_t)p->Hq * DV;
+  args.o_sb = (int64_t)p->Sq * p->Hq * DV;
+  args.o_part = p->o_partial;
+  for (int i = 0; i < AE_MAX_FINAL; ++i) args.fr_part[i] = p->rowscale_partial[i];
+  for (int i = 0; i < AE_MAX_CUSTOM; ++i) {
+    args.custom[i] = p->custom[i];
+    for (int k = 0; k < 4; ++k) args.custom_st[i][k] = p->custom_stride[i][k];
+  }
+  args.B = p->B;
+  args.Hq = p->Hq;
+  args.Hkv = p->Hkv;
+  args.Sq = p->Sq;
+  args.Skv = p->Skv;
+  args.n_qt = (rows + 127) / 128;
+  args.n_kt = n_kt;
+  args.status = p->status;
+  args.n_split = p->n_split;
+  args.tiles_per_split = tps;
+  args.gq = gq;
+  args.rows = rows;
+  return launch(m, (unsigned)p->n_split, (unsigned)(gq > 1 ? p->Hkv : p->Hq), (unsigned)p->B, &args, stream);
+}
+
+int ae_launch_decode_combine(void* module, const AeDecodeParams* p, void* stream) {
+  if (!module || !p || !p->o || !p->o_partial) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  if (m->cfg.kind != AE_KIND_MLA_COMBINE) {
+    set_error("module kind does not match the entry point");
+    return AE_ERR_UNSUPPORTED;
+  }
+  if (p->n_split < 2 || p->n_split > 32 || m->cfg.head_dim_v % 4) return AE_ERR_INVALID;
+  int rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeMlaCombineArgs a;
+  memset(&a, 0, sizeof a);
+  a.o = p->o;
+  a.o_part = p->o_partial;
+  for (int i = 0; i < AE_MAX_FINAL; ++i) a.fr_part[i] = p->rowscale_partial[i];
+  a.B = p->B;
+  a.H = p->Sq * p->Hq;  // one output row per (query position, head)
+  a.DV = m->cfg.head_dim_v;
+  a.n_split = p->n_split;
+  return launch(m, (unsigned)((a.H + 3) / 4), (unsigned)p->B, 1, &a, stream);
+}
+
 // Tensor map over a contiguous [B, H, T, D] tensor seen as (d, t, h, b), box {64, rows, 1, 1}.
 static int make_bhtd_map(AeTmaDesc* out, const void* base, int dtype, int64_t B, int64_t H, int64_t T, int64_t D,
                          int rows) {

@@ -40,6 +40,14 @@ struct AeAttnFwdArgs {
   int B, Hq, Hkv, Sq, Skv;
   int n_qt, n_kt;  // number of 128-row q tiles / 128-column kv tiles
   u32* status;
+  // Split-KV decode (the same kernel built with AE_DECODE): one CTA per (split, head unit, batch) owns ALL query rows
+  // of its unit (at most 256) and the kv tiles [split * tiles_per_split, ...).  gq > 1: the unit is a kv head and the
+  // rows are the gq query heads of its group (Sq == 1; tm_q is built over (d, head in group, kv head, b)); gq == 1:
+  // the unit is a head and the rows are its Sq query positions.
+  float* o_part;                 // [B, n_split, Sq * Hq, DV] fp32, after the epilogue (n_split > 1)
+  float* fr_part[AE_MAX_FINAL];  // each [B, n_split, Sq * Hq]
+  int n_split, tiles_per_split;
+  int gq, rows;
 };
 
 // ---- attention backward ------------------------------------------------------------

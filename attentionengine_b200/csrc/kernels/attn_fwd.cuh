@@ -23,6 +23,12 @@
 #define AE_BM 128
 #define AE_BN 128
 #define AE_NTHREADS 320
+#ifndef AE_DECODE
+#define AE_DECODE 0  // 1: split-KV decode (reference: attn_decode_tl.py:34-141 / attn_gqa_decode_tl.py), see AeAttnFwdArgs
+#endif
+#if AE_DECODE && AE_MASK_MODE != 0
+#error "the decode build takes no mask"
+#endif
 
 // shared memory carve-up (dynamic, 1024-byte aligned by the launch)
 #define AE_Q_BYTES (AE_BM * AE_D * 2)
@@ -74,12 +80,22 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
   const u32 warp = threadIdx.x >> 5;
   const u32 lane = threadIdx.x & 31;
 
+#if AE_DECODE
+  const int split = blockIdx.x;
+  const int hq = blockIdx.y;  // head unit: a kv head (gq > 1) or a head with its own K/V (gq == 1)
+  const int b = blockIdx.z;
+  const int hk = hq;
+  const int qt0 = 0;
+  const int kt_off = split * args.tiles_per_split;
+#else
   // heaviest (latest) q tiles first: better tail under a causal mask
   const int qpair = (int)gridDim.x - 1 - (int)blockIdx.x;
   const int hq = blockIdx.y;
   const int b = blockIdx.z;
   const int hk = hq / (args.Hq / args.Hkv);
   const int qt0 = qpair * 2;
+  const int kt_off = 0;
+#endif
 
   // ---- kv schedule (uniform over the CTA) ---------------------------------------
   int n_steps;
@@ -90,6 +106,10 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #elif AE_MASK_MODE == 2
   const u32* steps = (const u32*)(smem + AE_SMEM_STEPS);
   n_steps = 0;  // read from shared memory after the set-up barrier
+#elif AE_DECODE
+  int n_t0 = args.n_kt - kt_off < args.tiles_per_split ? args.n_kt - kt_off : args.tiles_per_split;
+  int n_t1 = (1 < args.n_qt) ? n_t0 : 0;
+  n_steps = n_t0;
 #else
   int n_t0 = args.n_kt;
   int n_t1 = (qt0 + 1 < args.n_qt) ? args.n_kt : 0;
@@ -110,7 +130,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     return true;
 #else
     if (walk.j >= n_steps) return false;
-    st.kt = walk.j;
+    st.kt = kt_off + walk.j;
     st.flags = 0;
     if (walk.j < n_t0) st.flags |= 1u;
     if (walk.j < n_t1) st.flags |= 2u;
@@ -351,8 +371,19 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     const u32 lane_base = ((warp & 3) * 32) << 16;
     const u32 tm_s = tmem + (t ? TM_S1 : TM_S0) + lane_base;
     const u32 tm_o = tmem + (t ? TM_O1 : TM_O0) + lane_base;
-    const int q_idx = (qt0 + t) * AE_BM + (int)row;
     const bool tile_valid = (qt0 + t) < args.n_qt;
+#if AE_DECODE
+    // packed rows: the query heads of the kv head's group (one query position), or the positions of one head;
+    // rows past the last valid one compute on zero-filled Q with the indices of row 0 and are never stored
+    const int r_idx = t * AE_BM + (int)row;
+    const bool row_valid = r_idx < args.rows;
+    const int h_row = (args.gq > 1) ? hq * args.gq + (row_valid ? r_idx : 0) : hq;
+    const int q_idx = (args.gq > 1 || !row_valid) ? 0 : r_idx;
+#else
+    const int q_idx = (qt0 + t) * AE_BM + (int)row;
+    const bool row_valid = q_idx < args.Sq;
+    const int h_row = hq;
+#endif
 
     AeCustom cu;
 #pragma unroll
@@ -397,7 +428,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
           const int kv_idx = kv0 + c;
           bool keep = kv_idx < args.Skv;
 #if AE_MASK_MODE != 0
-          if (partial) keep = keep && ae_mask(b, hq, q_idx, kv_idx);
+          if (partial) keep = keep && ae_mask(b, h_row, q_idx, kv_idx);
 #endif
 #if AE_MASK_NEG_INF
           if (!keep) s[c] = -__int_as_float(0x7f800000);
@@ -407,7 +438,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #endif
         }
       }
-      const float o_scale = ae_online_fwd<AE_BN>(s, st, b, hq, q_idx, kv0, cu);
+      const float o_scale = ae_online_fwd<AE_BN>(s, st, b, h_row, q_idx, kv0, cu);
 
       // P -> TMEM (16-bit pairs, column c/2 holds kv columns c, c+1)
       {
@@ -449,8 +480,14 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     }
     // tcgen05.ld is warp-collective: every lane of the warp runs it; only the stores are per-row.
     if (tile_valid) {
-      const bool store = (q_idx < args.Sq) && ok;
-      u16* orow = (u16*)args.o + (i64)b * args.o_sb + (i64)(store ? q_idx : 0) * args.o_ss + (i64)hq * args.o_sh;
+      const bool store = row_valid && ok;
+      u16* orow = (u16*)args.o + (i64)b * args.o_sb + (i64)(store ? q_idx : 0) * args.o_ss + (i64)h_row * args.o_sh;
+#if AE_DECODE
+      // more than one split: this split's normalised O and final row scales go to fp32 staging, merged by the combine pass
+      const i64 part_row = ((i64)b * args.n_split + split) * ((i64)args.Sq * args.Hq) + (i64)q_idx * args.Hq + h_row;
+      float* prow = args.o_part + part_row * AE_DV;
+      const bool staged = args.n_split > 1;
+#endif
 #pragma unroll
       for (int c = 0; c < AE_DV / 32; ++c) {
         float r[32];
@@ -460,6 +497,15 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0.f;
         }
+#if AE_DECODE
+        if (store && staged) {
+          float4* dst = (float4*)(prow + c * 32);
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            dst[v] = make_float4(ae_epilogue_o(r[v * 4 + 0], st), ae_epilogue_o(r[v * 4 + 1], st),
+                                 ae_epilogue_o(r[v * 4 + 2], st), ae_epilogue_o(r[v * 4 + 3], st));
+        } else
+#endif
         if (store) {
           uint4* dst = (uint4*)(orow + c * 32);
 #pragma unroll
@@ -478,8 +524,16 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         float fr[AE_NFINAL];
         ae_final_rowscales(st, fr);
 #pragma unroll
-        for (int i = 0; i < AE_NFINAL; ++i)
+        for (int i = 0; i < AE_NFINAL; ++i) {
+#if AE_DECODE
+          if (staged)
+            args.fr_part[i][part_row] = fr[i];
+          else if (args.final_rs[i])
+            args.final_rs[i][((i64)b * args.Hq + h_row) * args.Sq + q_idx] = fr[i];
+#else
           args.final_rs[i][((i64)b * args.Hq + hq) * args.Sq + q_idx] = fr[i];
+#endif
+        }
       }
 #endif
     }

@@ -32,19 +32,26 @@ extern "C" __global__ void __launch_bounds__(128) ae_mla_combine(const AeMlaComb
   float w = ae_combine(fr);
   if (lane >= args.n_split) w = 0.f;
   u16* orow = (u16*)args.o + ((i64)b * args.H + h) * args.DV;
-  for (int d0 = lane * 4; d0 < args.DV; d0 += 128) {
+  // the loop bounds are warp-uniform: every lane takes part in the shuffles, also when DV < 128 leaves it no columns
+  for (int base = 0; base < args.DV; base += 128) {
+    const int d0 = base + lane * 4;
+    const bool active = d0 < args.DV;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < args.n_split; ++k) {
       const float wk = __shfl_sync(0xffffffffu, w, k);
-      const float4 v = *(const float4*)(args.o_part + (((i64)b * args.n_split + k) * args.H + h) * args.DV + d0);
-      acc.x += wk * v.x;
-      acc.y += wk * v.y;
-      acc.z += wk * v.z;
-      acc.w += wk * v.w;
+      if (active) {
+        const float4 v = *(const float4*)(args.o_part + (((i64)b * args.n_split + k) * args.H + h) * args.DV + d0);
+        acc.x += wk * v.x;
+        acc.y += wk * v.y;
+        acc.z += wk * v.z;
+        acc.w += wk * v.w;
+      }
     }
-    uint2 o2;
-    o2.x = pack2<AE_BF16>(acc.x, acc.y);
-    o2.y = pack2<AE_BF16>(acc.z, acc.w);
-    *(uint2*)(orow + d0) = o2;
+    if (active) {
+      uint2 o2;
+      o2.x = pack2<AE_BF16>(acc.x, acc.y);
+      o2.y = pack2<AE_BF16>(acc.z, acc.w);
+      *(uint2*)(orow + d0) = o2;
+    }
   }
 }

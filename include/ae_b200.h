@@ -53,6 +53,7 @@ enum {
   AE_KIND_LINEAR_FWD = 7,
   AE_KIND_LINEAR_BWD = 8,
   AE_KIND_LINEAR_STATES = 9,
+  AE_KIND_ATTN_DECODE = 10,
 };
 
 #define AE_MAX_CUSTOM_INPUTS 4
@@ -197,6 +198,33 @@ typedef struct AeMlaParams {
 
 int ae_launch_mla_decode(void* module, const AeMlaParams* p, void* stream);
 int ae_launch_mla_combine(void* module, const AeMlaParams* p, void* stream);
+
+/* ---- split-KV decode for MHA / GQA -----------------------------------------------------
+ * Stands in for the reference's decode modules: `flashattn_gqa_decode` / `flashattn` split + `combine`
+ * (core/template/tl_template/attn/attn_decode_tl.py:34-206, attn_gqa_decode_tl.py; dispatch
+ * attn_engine/attn_engine.py:252-286; scripts attn_script/gqa_inference.py, mha_inference.py).
+ * Query rows of one head unit share a tile: Hq > Hkv needs Sq == 1 (the Hq / Hkv query heads of a kv
+ * head are the rows), Hq == Hkv takes Sq <= 256 query positions.  n_split CTAs per unit each walk
+ * ceil(n_kv_tiles / n_split) kv tiles of 128 keys (the caller chooses n_split so that no split is
+ * empty); n_split == 1 writes `o` directly, otherwise the splits write normalised fp32 partials and
+ * their final row scales, and `ae_launch_decode_combine` (module kind AE_KIND_MLA_COMBINE, the traced
+ * `OnlineFunc.combine`) merges them into `o`.  No mask.  `o` is contiguous. */
+typedef struct AeDecodeParams {
+  const void* q; /* [B, Sq, Hq, D]    */
+  const void* k; /* [B, Skv, Hkv, D]  */
+  const void* v; /* [B, Skv, Hkv, DV] */
+  void* o;       /* [B, Sq, Hq, DV] contiguous */
+  int64_t q_stride[3], k_stride[3], v_stride[3]; /* (batch, seq, head) */
+  float* o_partial;                                /* [B, n_split, Sq * Hq, DV] fp32 (n_split > 1) */
+  float* rowscale_partial[AE_MAX_FINAL_ROWSCALES]; /* each [B, n_split, Sq * Hq]    (n_split > 1) */
+  const void* custom[AE_MAX_CUSTOM_INPUTS];
+  int64_t custom_stride[AE_MAX_CUSTOM_INPUTS][4];
+  int32_t B, Hq, Hkv, Sq, Skv, n_split;
+  uint32_t* status;
+} AeDecodeParams;
+
+int ae_launch_attn_decode(void* module, const AeDecodeParams* p, void* stream);
+int ae_launch_decode_combine(void* module, const AeDecodeParams* p, void* stream);
 
 /* ---- chunked linear attention / SSD scan, forward ----------------------------------------
  * Stands in for `LinearAttention.forward` after the q/k/v/decay mods

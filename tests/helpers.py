@@ -71,6 +71,28 @@ def metas(B, Hq, Hkv, S, D, DV, dtype):
             meta_tensor(B, Hkv, S, DV, dtype=dtype))
 
 
+class OnlineSoftmaxSplit(OnlineSoftmax):
+    """Online softmax with the split-KV merge of attn_script/gqa_inference.py:72-80 / mla_decode.py."""
+
+    @staticmethod
+    def combine(final_rowscales):
+        lse = final_rowscales["lse"]
+        lse_max = lse.get_reduce("max")
+        row_sum = (lse - lse_max).exp()
+        row_sum_sum = row_sum.get_reduce("sum")
+        lse_sum = row_sum_sum.log() + lse_max
+        return (lse - lse_sum).exp()
+
+
+def decode_engine(B, Hq, Hkv, Sq, Skv, D, dtype, scale=None, online=None):
+    """q_len != kv_len: the split-KV decode path (reference scripts gqa_inference.py / mha_inference.py)."""
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    metas_ = (meta_tensor(B, Hq, Sq, D, dtype=dtype), meta_tensor(B, Hkv, Skv, D, dtype=dtype),
+              meta_tensor(B, Hkv, Skv, D, dtype=dtype))
+    return AttentionEngine(metas_, CustomIO({}), score_mod=lambda s, c, b, h, q, kv: s * scale, mask_mod=None,
+                           online_func=online if online is not None else OnlineSoftmaxSplit())
+
+
 def softmax_engine(B, Hq, Hkv, S, D, DV, dtype, causal, scale=None, **kw):
     scale = 1.0 / math.sqrt(D) if scale is None else scale
 
@@ -118,16 +140,6 @@ def seeded_qkv(B, Hq, Hkv, S, D, DV, dtype, seed=0, device="cpu"):
 
 def mla_engine(B, H, S, dtype, scale):
     """attn_script/mla_decode.py:88-118 with the scale chosen by the caller's score_mod."""
-    class OnlineSoftmaxSplit(OnlineSoftmax):
-        @staticmethod
-        def combine(final_rowscales):
-            lse = final_rowscales["lse"]
-            lse_max = lse.get_reduce("max")
-            row_sum = (lse - lse_max).exp()
-            row_sum_sum = row_sum.get_reduce("sum")
-            lse_sum = row_sum_sum.log() + lse_max
-            return (lse - lse_sum).exp()
-
     def score_mod(score, custom_fwd_inputs, b, h, q_idx, kv_idx):
         return score * scale
 

@@ -155,6 +155,90 @@ def test_sliding_window_block_sparse():
         _check(name, g, r, dtype)
 
 
+def test_dynamic_shape_engine_runs_several_lengths():
+    """One engine built from named dims serves different batch sizes and lengths: causal (analytic bounds) and a
+    sliding window (tile lists rebuilt per shape)."""
+    from attentionengine_b200 import AttentionEngine, CustomIO, meta_tensor
+    D, H, dtype, W = 64, 2, torch.float16, 150
+    scale = 1 / math.sqrt(D)
+    metas = tuple(meta_tensor("B", "H", "S", D, dtype=dtype) for _ in range(3))
+    masks = {"causal": lambda b, h, q_idx, kv_idx: q_idx >= kv_idx,
+             "window": lambda b, h, q_idx, kv_idx: torch.logical_and(q_idx >= kv_idx, q_idx - kv_idx <= W)}
+    for kind, mask in masks.items():
+        eng = AttentionEngine(metas, CustomIO({}), score_mod=lambda s, c, b, h, q, kv: s * scale, mask_mod=mask,
+                              online_func=helpers.OnlineSoftmax())
+        assert eng.mask_mode == (1 if kind == "causal" else 2)
+        for B, S in ((1, 300), (2, 640)):
+            q, k, v, d_o = helpers.seeded_qkv(B, H, H, S, D, D, dtype, seed=40 + S)
+            got = _run(eng, q, k, v, d_o)
+            i = torch.arange(S)
+            keep = i.view(-1, 1) >= i.view(1, -1)
+            if kind == "window":
+                keep = keep & (i.view(-1, 1) - i.view(1, -1) <= W)
+
+            def ref(a, b, c):
+                s_ = (torch.einsum("bqhd,bkhd->bhqk", a, b) * scale).masked_fill(~keep, float("-inf"))
+                return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s_, -1), c)
+
+            o, grads = orc.fwd_bwd(ref, (q, k, v), d_o)
+            for name, g, r in zip(("o", "dq", "dk", "dv"), got, (o, *grads)):
+                _check(f"{kind} S={S} {name}", g, r, dtype)
+
+
+@pytest.mark.parametrize("n_split", [1, None, 5])
+def test_gqa_decode_split_kv(n_split):
+    """attn_script/gqa_inference.py: one query position, Hq > Hkv, K / V of a kv head streamed once for its group;
+    1 split (no combine), the default split count and a forced ragged one (1000 keys = 8 tiles over 5 splits -> 4)."""
+    B, Hq, Hkv, S, D, dtype = 2, 32, 8, 1000, 128, torch.float16
+    eng = helpers.decode_engine(B, Hq, Hkv, 1, S, D, dtype)
+    eng._decode.num_split = 4 if n_split == 5 else n_split
+    g = torch.Generator().manual_seed(50)
+    q = torch.randn(B, 1, Hq, D, generator=g).to(dtype)
+    k = torch.randn(B, S, Hkv, D, generator=g).to(dtype)
+    v = torch.randn(B, S, Hkv, D, generator=g).to(dtype)
+    o = eng(q.cuda(), k.cuda(), v.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert eng._decode.last_num_split == (1 if n_split == 1 else 4 if n_split == 5 else eng._decode.pick_splits(B, S))
+    _check("o", o.cpu(), orc.softmax_attention(q, k, v, False), dtype)
+
+
+@pytest.mark.parametrize("Sq", [1, 3, 200])
+def test_mha_decode_split_kv(Sq):
+    """attn_script/mha_inference.py shape class: Hq == Hkv, a few query positions against a long KV range; 200 rows
+    use both row tiles of the CTA.  bf16, D = 64."""
+    B, H, S, D, dtype = 2, 4, 2048 + 77, 64, torch.bfloat16
+    eng = helpers.decode_engine(B, H, H, Sq, S, D, dtype)
+    g = torch.Generator().manual_seed(51)
+    q = torch.randn(B, Sq, H, D, generator=g).to(dtype)
+    k = torch.randn(B, S, H, D, generator=g).to(dtype)
+    v = torch.randn(B, S, H, D, generator=g).to(dtype)
+    o = eng(q.cuda(), k.cuda(), v.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert eng._decode.last_num_split > 1
+    _check("o", o.cpu(), orc.softmax_attention(q, k, v, False), dtype)
+
+
+def test_decode_with_identity_online_func_sums_the_splits():
+    """OnlineFunc.combine left at its default (weight 1 per split): relu attention, whose partial outputs add up."""
+    B, Hq, Hkv, S, D, dtype = 1, 8, 2, 1536, 128, torch.float16
+    scale = 1 / math.sqrt(D)
+    metas = (helpers.meta_tensor(B, Hq, 1, D, dtype=dtype), helpers.meta_tensor(B, Hkv, S, D, dtype=dtype),
+             helpers.meta_tensor(B, Hkv, S, D, dtype=dtype))
+    eng = AttentionEngine(metas, CustomIO({}), score_mod=lambda s, c, b, h, q, kv: (s * scale).max(0) * (1.0 / S),
+                          mask_mod=None, online_func=helpers.OnlineIdentity(), mask_value="0")
+    g = torch.Generator().manual_seed(52)
+    q = torch.randn(B, 1, Hq, D, generator=g).to(dtype)
+    k = torch.randn(B, S, Hkv, D, generator=g).to(dtype)
+    v = torch.randn(B, S, Hkv, D, generator=g).to(dtype)
+    o = eng(q.cuda(), k.cuda(), v.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert eng._decode.last_num_split > 1
+    _check("o", o.cpu(), orc.relu_attention(q, k, v, post_scale=1.0 / S), dtype)
+
+
 def test_run_to_run_determinism():
     """No atomics anywhere on the path: two runs give bit-identical outputs and gradients."""
     B, Hq, Hkv, S, D = 1, 4, 2, 512, 128

@@ -57,6 +57,28 @@ def test_mask_classification():
     assert "&&" in e.lowered.prelude_fwd
 
 
+def test_dynamic_shape_engine_classifies_on_a_probe_and_builds_lists_per_shape():
+    """meta_tensor with named dims (reference: attn_script/mha.py:92-94, lower.py:626-629): one engine for every
+    batch / length; the mask is classified once, the tile lists are built per runtime shape."""
+    from attentionengine_b200 import meta_tensor
+    D = 64
+    metas = tuple(meta_tensor("B", "H", "S", D, dtype=torch.float16) for _ in range(3))
+
+    def mk(mask):
+        return AttentionEngine(metas, CustomIO({}), score_mod=lambda s, c, b, h, q, kv: s * 0.125, mask_mod=mask,
+                               online_func=helpers.OnlineSoftmax())
+
+    assert mk(None).mask_mode == 0
+    assert mk(lambda b, h, q, kv: q >= kv).mask_mode == 1
+    e = mk(lambda b, h, q, kv: torch.logical_and(q >= kv, q - kv <= 100))
+    assert e.mask_mode == 2
+    c1 = e._ensure_lists("cpu", None, 1, 2, 256, 256)[0]
+    c2 = e._ensure_lists("cpu", None, 2, 2, 640, 640)[0]
+    assert c1.shape == (1, 2, 2) and c1[0, 0].tolist() == [1, 2]
+    assert c2.shape == (2, 2, 5) and c2[1, 1].tolist() == [1, 2, 2, 2, 2]
+    assert e._ensure_lists("cpu", None, 1, 2, 256, 256)[0] is c1  # cached per shape
+
+
 def test_block_lists_layout():
     from attentionengine_b200.attn_engine.attn_engine import _block_lists
     cnt = torch.tensor([[[[128 * 128, 0, 5], [0, 0, 0], [1, 128 * 128, 128 * 128]]]], dtype=torch.int32)
