@@ -71,15 +71,23 @@ class AttnDecode:
         self._status = None
 
     def pick_splits(self, B: int, Skv: int) -> int:
-        """Enough CTAs to cover the SMs once, never an empty split, one split when there is no combine."""
+        """Split count that minimises waves x (kv tiles per split + 3): a CTA occupies an SM alone, so the CTAs run in
+        waves of 148, and each CTA pays about three tile periods to fill its pipeline and write its partials (measured
+        at B = 16: 2 splits 0.131 ms, 8 splits 0.139 ms).  No empty split; one split when the online function has row
+        state but no combine of its own."""
         if self.combine is None:
             return 1
         units = B * (self.Hkv if self.Hq > self.Hkv else self.Hq)
         n_tiles = -(-Skv // 128)
-        n = min(max(1, -(-N_SM // units)), 32, n_tiles)
-        while n > 1 and (n - 1) * (-(-n_tiles // n)) >= n_tiles:
-            n -= 1
-        return n
+        best, best_cost = 1, None
+        for n in range(1, min(32, n_tiles) + 1):
+            tps = -(-n_tiles // n)
+            if (n - 1) * tps >= n_tiles:
+                continue
+            cost = -(-units * n // N_SM) * (tps + 3)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = n, cost
+        return best
 
     def __call__(self, q, k, v, *custom):
         for name, t in (("q", q), ("k", k), ("v", v)):

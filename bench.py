@@ -296,6 +296,29 @@ def run_other(args):
         tc = time.perf_counter() - t0
         cpu = {"value": 3 * (4 * S * 576 + 4 * H * 576 + 4 * H * 512) * 2.0 / tc / 1e9, "unit": "GB/s", "cores": os.cpu_count(),
                "kind": "port", "sample": "3 x 4 of 128 batch rows, fp32 torch"}
+    elif wl == "gqa_decode":
+        # the shape of the reference's attn_script/gqa_inference.py (H=32, 8 kv heads, S=8192, D=128, fp16, one query
+        # position) at batch 16 by default: K + V = 537 MB per step, larger than L2 (batch 1 is 33.5 MB and L2-resident)
+        B, Hq, Hkv, S, D, dt = args.batch or 16, 32, 8, 8192, 128, torch.float16
+        eng = helpers.decode_engine(B, Hq, Hkv, 1, S, D, dt)
+        q = torch.randn(B, 1, Hq, D, device=dev, dtype=dt)
+        k = torch.randn(B, S, Hkv, D, device=dev, dtype=dt)
+        v = torch.randn(B, S, Hkv, D, device=dev, dtype=dt)
+        ms = time_events(torch, lambda: eng(q, k, v), args.steps, args.warmup)
+        eng.check_status()
+        work = (2 * B * S * Hkv * D + 2 * B * Hq * D) * 2.0
+        value, unit, bound, peak = work / ms / 1e6, "GB/s", "hbm", float(peaks.get("hbm_gbs", 6650.0))
+        desc = f"GQA decode (split-KV + combine), B={B} Hq=32 Hkv=8 Skv=8192 D=128 fp16, {eng._decode.last_num_split} splits"
+        launches = (1 if eng._decode.last_num_split == 1 else 2) * args.steps
+        g = torch.Generator().manual_seed(0)
+        qs = torch.randn(2, 1, Hq, D, generator=g).to(dt)
+        ks, vs = torch.randn(2, S, Hkv, D, generator=g).to(dt), torch.randn(2, S, Hkv, D, generator=g).to(dt)
+        t0 = time.perf_counter()
+        for _ in range(5):
+            orc.softmax_attention(qs, ks, vs, False)
+        tc = time.perf_counter() - t0
+        cpu = {"value": 5 * (2 * 2 * S * Hkv * D + 2 * 2 * Hq * D) * 2.0 / tc / 1e9, "unit": "GB/s", "cores": os.cpu_count(),
+               "kind": "port", "sample": "5 x 2 batch rows, fp32 torch"}
     else:
         raise SystemExit(f"unknown workload {wl}")
     clocks = sampler.stop()
@@ -319,7 +342,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end pass (profiling runs)")
-    ap.add_argument("--workload", default="cfg2", help="cfg2 (the headline, default) | cfg3_sigmoid | cfg3_relu | cfg4 | cfg5")
+    ap.add_argument("--workload", default="cfg2", help="cfg2 (the headline, default) | cfg3_sigmoid | cfg3_relu | cfg4 | cfg5 | gqa_decode")
     ap.add_argument("--batch", type=int, default=None,
                     help="batch size; default = the benchmark's (8; cfg5: 128). Smaller values are for ncu captures")
     args = ap.parse_args()
