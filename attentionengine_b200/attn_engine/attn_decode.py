@@ -43,11 +43,15 @@ class AttnDecode:
         tag = rt.DTYPE_BF16 if bf16 else rt.DTYPE_F16
         self.low = lower_attention(score_mod, None, online_func, custom_fwd_inputs, D=D, DV=DV, bf16=bf16, mask_mode=0,
                                    stages=2, mask_value=mask_value)
-        smem = 2 * 128 * D * 2 + 2 * 128 * (D + DV) * 2 + 512 + 1024
+        # at most 128 rows: one q tile in shared memory, its space goes to a third K / V stage
+        nq, stages = (1, 3) if self.rows <= 128 else (2, 2)
+        smem = nq * 128 * D * 2 + stages * 128 * (D + DV) * 2 + 512 + 1024
         cfg = rt.KernelConfig(kind=rt.KIND_ATTN_DECODE, dtype=tag, head_dim=D, head_dim_v=DV, threads=320,
-                              smem_bytes=smem, stages=2, mask_mode=0)
+                              smem_bytes=smem, stages=stages, mask_mode=0)
         cfg.reserved[1] = len(self.low.final_names)
-        self.src = rt.kernel_source("attn_fwd.cuh", prelude=self.low.prelude_fwd + "#define AE_DECODE 1\n")
+        prelude = self.low.prelude_fwd.replace("#define AE_STAGES 2\n", f"#define AE_STAGES {stages}\n")
+        assert f"#define AE_STAGES {stages}\n" in prelude
+        self.src = rt.kernel_source("attn_fwd.cuh", prelude=prelude + f"#define AE_DECODE 1\n#define AE_NQ {nq}\n")
         self.kernel = rt.compile_module(self.src, "ae_attn_fwd", cfg)
         self.combine = None
         self.combine_src = None

@@ -63,8 +63,9 @@ class LinearAttentionEngine:
         self.B, self.HQ, self.T, self.DK = qm.shape
         self.HK = km.shape[1]
         self.H, self.DV = vm.shape[1], vm.shape[3]
-        if self.DK != 128 or self.DV not in (64, 128):
-            raise NotImplementedError(f"linear attention is built for DK = 128 and DV in (64, 128); got {self.DK}, {self.DV}")
+        if self.DK % 128 or self.DK > 512 or self.DV % 64 or self.DV > 1024:
+            raise NotImplementedError("linear attention takes DK in (128, 256, 384, 512) and DV a multiple of 64 up to "
+                                      f"1024; got {self.DK}, {self.DV}")
         self.custom_io = custom_io if custom_io is not None else CustomIO()
         self.mods = {"q": q_mod, "k": k_mod, "v": v_mod, "decay": decay_mod}
         self._traced = {}
@@ -73,38 +74,46 @@ class LinearAttentionEngine:
                 continue
             leaf = SymbolScalar(name, Var(name), shape_idx=["batch", "heads", "seq_len"] + ([] if name == "decay" else ["dim"]))
             self._traced[name] = (leaf, fn(leaf, self.custom_io))
-        bf16 = self.dtype == torch.bfloat16
-        stages = 2 if self.DV == 64 else 1
-        prelude = f"#define AE_BF16 {int(bf16)}\n#define AE_LIN_DV {self.DV}\n#define AE_LIN_STAGES {stages}\n"
-        smem = stages * (2 * 128 * 128 * 2 + 128 * self.DV * 2) + 128 * self.DV * 2 + 128 * self.DV * 2 + 1024 + 256 + 1024
-        cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_FWD, dtype=rt.DTYPE_BF16 if bf16 else rt.DTYPE_F16, head_dim=128,
-                              head_dim_v=self.DV, threads=192, smem_bytes=smem, stages=stages, mask_mode=0)
-        self.tl_code = rt.kernel_source("linear_fwd.cuh", prelude=prelude)
-        self.fwd = rt.compile_module(self.tl_code, "ae_linear_fwd", cfg)
+        self._bf16 = self.dtype == torch.bfloat16
         self._status = None
         self._bwd = None
-        self._stages = stages
-        self._bf16 = bf16
+        self._fwd_by_dv = {}
+        # The kernels work on blocks of 128 key dims x 64 or 128 value dims.  Larger heads (simple_gla / retention_linear
+        # of the reference use D = 256, DV = 512) are sums over key blocks of independent value blocks, see _scan().
+        self._dv_block = self.DV if self.DV in (64, 128) else (128 if self.DV % 128 == 0 else 64)
+        self.fwd, self.tl_code = self._fwd_kernel(self._dv_block)
+
+    def _fwd_kernel(self, dv: int):
+        if dv not in self._fwd_by_dv:
+            stages = 2 if dv == 64 else 1
+            prelude = f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {dv}\n#define AE_LIN_STAGES {stages}\n"
+            smem = stages * (2 * 128 * 128 * 2 + 128 * dv * 2) + 128 * dv * 2 + 128 * dv * 2 + 1024 + 256 + 1024
+            cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_FWD, dtype=rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16,
+                                  head_dim=128, head_dim_v=dv, threads=192, smem_bytes=smem, stages=stages, mask_mode=0)
+            src = rt.kernel_source("linear_fwd.cuh", prelude=prelude)
+            self._fwd_by_dv[dv] = (rt.compile_module(src, "ae_linear_fwd", cfg), src)
+        return self._fwd_by_dv[dv]
 
     def _bwd_kernels(self):
         if self._bwd is None:
-            if self.DV != 64:
-                raise NotImplementedError("backward of the linear-attention scan is built for DV = 64")
+            DV = 64  # the backward kernels are built for value blocks of 64
             tag = rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16
-            pre = f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {self.DV}\n#define AE_LIN_STAGES 2\n"
-            smem_s = 2 * (128 * 128 * 2 + 128 * self.DV * 2) + 128 * self.DV * 2 + 1024 + 256 + 1024
-            cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_STATES, dtype=tag, head_dim=128, head_dim_v=self.DV, threads=192,
+            pre = f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {DV}\n#define AE_LIN_STAGES 2\n"
+            smem_s = 2 * (128 * 128 * 2 + 128 * DV * 2) + 128 * DV * 2 + 1024 + 256 + 1024
+            cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_STATES, dtype=tag, head_dim=128, head_dim_v=DV, threads=192,
                                   smem_bytes=smem_s, stages=2, mask_mode=0)
             states = rt.compile_module(rt.kernel_source("linear_states.cuh", prelude=pre), "ae_linear_states", cfg)
-            smem_b = (2 * 128 * 128 * 2 + 2 * 128 * self.DV * 2 + 128 * self.DV * 2 + 2 * 128 * 128 * 2
-                      + 128 * self.DV * 2 + 128 * self.DV * 2 + 1024 + 256 + 1024)
-            cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_BWD, dtype=tag, head_dim=128, head_dim_v=self.DV, threads=192,
+            smem_b = (2 * 128 * 128 * 2 + 2 * 128 * DV * 2 + 128 * DV * 2 + 2 * 128 * 128 * 2
+                      + 128 * DV * 2 + 128 * DV * 2 + 1024 + 256 + 1024)
+            cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_BWD, dtype=tag, head_dim=128, head_dim_v=DV, threads=192,
                                   smem_bytes=smem_b, stages=1, mask_mode=0)
             bwd = rt.compile_module(rt.kernel_source("linear_bwd.cuh", prelude=pre), "ae_linear_bwd", cfg)
             self._bwd = (states, bwd)
         return self._bwd
 
     def _launch_bwd(self, q, k, v, a, d_o):
+        if v.shape[3] != 64:
+            raise NotImplementedError("backward of the linear-attention scan runs on value blocks of 64")
         states, bwd = self._bwd_kernels()
         B, HQ, T, DK = q.shape
         HK = k.shape[1]
@@ -153,7 +162,31 @@ class LinearAttentionEngine:
             self._status = torch.zeros(1, dtype=torch.int32, device=q.device)
         p.status = self._status.data_ptr()
         stream = C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
-        rt.check(rt.lib().ae_launch_linear_fwd(self.fwd.handle, C.byref(p), stream), "ae_launch_linear_fwd")
+        rt.check(rt.lib().ae_launch_linear_fwd(self._fwd_kernel(DV)[0].handle, C.byref(p), stream), "ae_launch_linear_fwd")
+        return o
+
+    def _scan(self, q, k, v, a):
+        """The scan on heads of any supported size, from kernels that take 128 key dims and 64 / 128 value dims.
+        Value blocks are independent problems sharing q, k and the decay (o[:, block] depends on v[:, block] only): they
+        become extra heads.  Key blocks add up: S = [S_1; S_2] row-wise and o = q_1 S_1 + q_2 S_2, one launch per key
+        block, summed in fp32.  Blocks of 64 value dims when gradients are wanted (the backward kernels' size)."""
+        B, H, T, DV = v.shape
+        DK = q.shape[3]
+        want_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, a))
+        dvb = 64 if (want_grad or DV % 128) else 128
+        if DK == 128 and DV == dvb:
+            return _Scan.apply(self, q, k, v, a)
+        n_dv = DV // dvb
+        if n_dv > 1:
+            v = v.view(B, H, T, n_dv, dvb).permute(0, 1, 3, 2, 4).reshape(B, H * n_dv, T, dvb)
+            a = a.repeat_interleave(n_dv, dim=1)
+        o = None
+        for j in range(DK // 128):
+            oj = _Scan.apply(self, q[..., j * 128:(j + 1) * 128], k[..., j * 128:(j + 1) * 128], v, a)
+            o = oj.float() if o is None else o + oj.float()
+        o = o.to(self.dtype)
+        if n_dv > 1:
+            o = o.view(B, H, n_dv, T, dvb).permute(0, 1, 3, 2, 4).reshape(B, H, T, DV)
         return o
 
     def check_status(self):
@@ -177,4 +210,4 @@ class LinearAttentionEngine:
         qm = self._apply_mod("q", q, custom)
         km = self._apply_mod("k", k, custom)
         vm = self._apply_mod("v", v, custom)
-        return _Scan.apply(self, qm, km, vm, a)
+        return self._scan(qm, km, vm, a)

@@ -29,13 +29,17 @@
 #if AE_DECODE && AE_MASK_MODE != 0
 #error "the decode build takes no mask"
 #endif
+#ifndef AE_NQ
+#define AE_NQ 2  // q tiles held in shared memory; 1 in a decode build whose head units have at most 128 rows (the
+                 // space goes to a third K / V stage: more bytes in flight per SM while a tile's chain runs)
+#endif
 
 // shared memory carve-up (dynamic, 1024-byte aligned by the launch)
 #define AE_Q_BYTES (AE_BM * AE_D * 2)
 #define AE_K_BYTES (AE_BN * AE_D * 2)
 #define AE_V_BYTES (AE_BN * AE_DV * 2)
 #define AE_SMEM_Q 0
-#define AE_SMEM_K (2 * AE_Q_BYTES)
+#define AE_SMEM_K (AE_NQ * AE_Q_BYTES)
 #define AE_SMEM_V (AE_SMEM_K + AE_STAGES * AE_K_BYTES)
 #define AE_SMEM_BAR (AE_SMEM_V + AE_STAGES * AE_V_BYTES)
 #define AE_SMEM_STEPS (AE_SMEM_BAR + 512)  // mask mode 2 only: one word per kv tile
@@ -238,7 +242,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       tma_prefetch_desc(&args.tm_q);
       tma_prefetch_desc(&args.tm_k);
       tma_prefetch_desc(&args.tm_v);
-      for (int t = 0; t < 2; ++t) {
+      for (int t = 0; t < AE_NQ; ++t) {
         mbar_arrive_expect_tx(&bars->q_full[t], AE_Q_BYTES);
         for (int dh = 0; dh < AE_D / 64; ++dh)
           tma_load_bshd(smem + AE_SMEM_Q + t * AE_Q_BYTES + dh * (AE_BM * 128), &args.tm_q, &bars->q_full[t], dh * 64,

@@ -399,7 +399,55 @@ def test_mamba2_ssd_backward_against_oracle(B, H, T):
     for name, got, ref in zip(names, [t.grad for t in leaves] + [dtb.grad], [C2.grad, B2.grad, x2.grad, dt2.grad, A2.grad, dtb2.grad]):
         mx, rel = orc.error_stats(got.float().cpu(), ref.float())
         lim = 5e-2 if name == "dA" else 1e-2
-        assert rel <= lim, f"{name}: rel-L2 {rel:.3e} (max-abs {mx:.3e})"@pytest.mark.gpu
+        assert rel <= lim, f"{name}: rel-L2 {rel:.3e} (max-abs {mx:.3e})"
+
+
+@pytest.mark.parametrize("variant", ["simple_gla", "retention_linear"])
+def test_linear_variants_with_large_heads(variant):
+    """attn_script/simple_gla.py (q_mod = q * scale, the decay input is already a log-decay) and retention_linear.py
+    (decay_mod = log of a per-head decay factor) at their head sizes class: D = 256 (two key blocks, summed) and
+    DV = 256 (value blocks as extra heads).  Forward without gradients (128-wide value blocks) and forward + backward
+    (64-wide value blocks) against fp64 autograd through the step-by-step recurrence; bf16 protocol as for the SSD
+    backward test."""
+    from attentionengine_b200 import LinearAttentionEngine, meta_tensor
+    from oracle.linear_oracle import linear_scan
+    B, H, T, D, DV, dt_ = 1, 2, 384, 256, 256, torch.bfloat16
+    scale = 1 / math.sqrt(D)
+    metas = (meta_tensor(B, H, T, D, dtype=dt_), meta_tensor(B, H, T, D, dtype=dt_), meta_tensor(B, H, T, DV, dtype=dt_))
+    mods = {"q_mod": lambda q, io: q * scale}
+    g = torch.Generator().manual_seed(60)
+    if variant == "retention_linear":
+        mods["decay_mod"] = lambda decay, io: decay.log()
+        decay = (1 - torch.exp2(-5 - torch.arange(H, dtype=torch.float32))).view(1, H, 1).expand(B, H, T).contiguous()
+        to_log = torch.log
+    else:
+        decay = torch.nn.functional.logsigmoid(torch.randn(B, H, T, generator=g)) / 16
+        to_log = lambda x: x  # noqa: E731
+    eng = LinearAttentionEngine(metas, custom_io=CustomIO({}), **mods)
+    q, k = (torch.randn(B, H, T, D, generator=g).to(dt_) for _ in range(2))
+    v = torch.randn(B, H, T, DV, generator=g).to(dt_)
+    d_o = (0.1 * torch.randn(B, H, T, DV, generator=g)).to(dt_)
+
+    with torch.no_grad():
+        o_ng = eng(q.cuda(), k.cuda(), v.cuda(), decay.cuda())
+    leaves = [t.cuda().requires_grad_() for t in (q, k, v, decay)]
+    o = eng(*leaves)
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+
+    q2, k2, v2, g2 = [t.detach().double().cpu().requires_grad_() for t in leaves]
+    # the engine rounds the mod-ed q to bf16 before the scan: the rounded value, with the gradient of the exact product
+    q_round = (q2 * scale).detach().to(dt_).double()
+    oref = linear_scan(q_round + (q2 * scale - (q2 * scale).detach()), k2, v2, to_log(g2))
+    oref.backward(d_o.double())
+    _check("o (no grad, 128-wide value blocks)", o_ng.cpu(), oref.detach().float(), dt_, unnormalised=True)
+    _check("o", o.detach().cpu(), oref.detach().float(), dt_, unnormalised=True)
+    for name, got, ref in zip(("dq", "dk", "dv", "d(decay)"), [t.grad for t in leaves], [q2.grad, k2.grad, v2.grad, g2.grad]):
+        mx, rel = orc.error_stats(got.float().cpu(), ref.float())
+        assert rel <= (5e-2 if name == "d(decay)" else 1e-2), f"{name}: rel-L2 {rel:.3e} (max-abs {mx:.3e})"
+
+
 @pytest.mark.parametrize("D", [64, 128])
 def test_extern_block_mask_given_at_call_time(D):
     """attn_script/blocksparseattn.py: the engine is built with extern_block_mask=True and no mask_mod, the int8 block
