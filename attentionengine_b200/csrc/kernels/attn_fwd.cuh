@@ -33,6 +33,13 @@
 #define AE_NQ 2  // q tiles held in shared memory; 1 in a decode build whose head units have at most 128 rows (the
                  // space goes to a third K / V stage: more bytes in flight per SM while a tile's chain runs)
 #endif
+// One q tile per CTA leaves the second S region of TMEM free: the scores of kv tile n go to region n & 1 and the S GEMM
+// runs two tiles ahead of P V, so the row threads find the next tile's scores ready when they finish a tile
+// (S MMA -> row pass -> P V MMA is no longer one chain per tile).
+#define AE_PINGPONG (AE_DECODE && AE_NQ == 1)
+#if AE_PINGPONG && AE_STAGES < 3
+#error "the two-ahead S GEMM needs three K / V stages"
+#endif
 
 // shared memory carve-up (dynamic, 1024-byte aligned by the launch)
 #define AE_Q_BYTES (AE_BM * AE_D * 2)
@@ -295,6 +302,53 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         for (int kk = 0; kk < AE_BN / 16; ++kk) umma_ts(d, a + kk * 8, umma_step_mn(db, kk), idesc_o, acc | (kk > 0));
       };
 
+#if AE_PINGPONG
+      // kv tiles kt_off .. kt_off + n_steps - 1 in order (no mask in a decode build); tile n uses K / V stage n % AE_STAGES,
+      // S region n & 1 and phase n >> 1 of that region's s_full / p_full; O (region 0) takes every P V.
+      auto s_into = [&](int n) {
+        const int stage = n % AE_STAGES;
+        const u64 da = umma_base_k(q_addr);
+        const u64 db = dk0 + (u64)((stage * AE_K_BYTES) >> 4);
+        const u32 d = tmem + ((n & 1) ? TM_S1 : TM_S0);
+#pragma unroll
+        for (int kk = 0; kk < AE_D / 16; ++kk)
+          umma_ss(d, umma_step_k(da, kk, AE_BM), umma_step_k(db, kk, AE_BN), idesc_s, kk > 0);
+        umma_commit(&bars->s_full[n & 1]);
+        umma_commit(&bars->k_empty[stage]);
+      };
+      bool ok = mbar_wait(&bars->q_full[0], 0, ctl, args.status, 4);
+      for (int n = 0; n < 2 && n < n_steps && ok; ++n) {
+        ok = mbar_wait(&bars->k_full[n % AE_STAGES], 0, ctl, args.status, 3);
+        if (!ok) break;
+        tc_fence_after_sync();
+        s_into(n);
+      }
+      for (int n = 0; n < n_steps && ok; ++n) {
+        const int stage = n % AE_STAGES;
+        const u32 par = (n / AE_STAGES) & 1;
+        ok = mbar_wait(&bars->p_full[n & 1], (n >> 1) & 1, ctl, args.status, 5);
+        if (!ok) break;
+        ok = mbar_wait(&bars->v_full[stage], par, ctl, args.status, 6);
+        if (!ok) break;
+        tc_fence_after_sync();
+        {
+          const u64 db = dv0 + (u64)((stage * AE_V_BYTES) >> 4);
+          const u32 d = tmem + TM_O0;
+          const u32 a = tmem + ((n & 1) ? TM_S1 : TM_S0);
+#pragma unroll
+          for (int kk = 0; kk < AE_BN / 16; ++kk)
+            umma_ts(d, a + kk * 8, umma_step_mn(db, kk), idesc_o, (u32)(n > 0) | (kk > 0));
+        }
+        umma_commit(&bars->o_done[0]);
+        umma_commit(&bars->v_empty[stage]);
+        if (n + 2 < n_steps) {
+          // the region of tile n is free once its P V (just issued) has read P: MMAs run in issue order
+          ok = mbar_wait(&bars->k_full[(n + 2) % AE_STAGES], ((n + 2) / AE_STAGES) & 1, ctl, args.status, 7);
+          if (!ok) break;
+          s_into(n + 2);
+        }
+      }
+#else
       // The walk is consumed one step ahead for the S GEMMs.
       AeKvStep cur, nxt;
       bool ok = true;
@@ -367,6 +421,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         have = have_n;
         ++it;
       }
+#endif  // AE_PINGPONG
     }
   } else {
     // =============================== row warpgroups =============================
@@ -404,7 +459,20 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     AeKvStep step;
     while (next_step(step)) {
       if (!(step.flags & (1u << t))) continue;
-      ok = ok && mbar_wait(&bars->s_full[t], n_done & 1, ctl, args.status, 9);
+#if AE_PINGPONG
+      // scores of this group's n-th tile: region n & 1, phase n >> 1 of that region's barriers
+      const u32 rgn = n_done & 1u;
+      const u32 tm_s_n = tmem + (rgn ? TM_S1 : TM_S0) + lane_base;
+      u64* const s_bar = &bars->s_full[rgn];
+      u64* const p_bar = &bars->p_full[rgn];
+      const u32 s_par = (n_done >> 1) & 1u;
+#else
+      const u32 tm_s_n = tm_s;
+      u64* const s_bar = &bars->s_full[t];
+      u64* const p_bar = &bars->p_full[t];
+      const u32 s_par = n_done & 1u;
+#endif
+      ok = ok && mbar_wait(s_bar, s_par, ctl, args.status, 9);
       tc_fence_after_sync();
 #if AE_MASK_MODE == 2
       if ((step.flags >> (4 + t)) & 1u) {
@@ -413,16 +481,16 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) z[i] = 0u;
 #pragma unroll
-        for (int half = 0; half < AE_BN / 64; ++half) tmem_st32(tm_s + half * 32, z);
+        for (int half = 0; half < AE_BN / 64; ++half) tmem_st32(tm_s_n + half * 32, z);
         tc_wait_st();
         tc_fence_before_sync();
-        mbar_arrive_warp(&bars->p_full[t]);
+        mbar_arrive_warp(p_bar);
         ++n_done;
         continue;
       }
 #endif
       float s[AE_BN];
-      tmem_ld_f32x128(tm_s, s);
+      tmem_ld_f32x128(tm_s_n, s);
       const int kv0 = step.kt * AE_BN;
       const bool tail = (kv0 + AE_BN > args.Skv);
       const bool partial = (step.flags >> (2 + t)) & 1u;
@@ -451,7 +519,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         for (int half = 0; half < AE_BN / 64; ++half) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) pk[i] = pack2<AE_BF16>(s[half * 64 + 2 * i], s[half * 64 + 2 * i + 1]);
-          tmem_st32(tm_s + half * 32, pk);
+          tmem_st32(tm_s_n + half * 32, pk);
         }
       }
 #if !AE_O_SCALE_ONE
@@ -473,7 +541,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #endif
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive_warp(&bars->p_full[t]);
+      mbar_arrive_warp(p_bar);
       ++n_done;
     }
 
