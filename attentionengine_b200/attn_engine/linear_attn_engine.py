@@ -53,6 +53,27 @@ class _Scan(torch.autograd.Function):
         return None, dq, dk, dv, da
 
 
+class _RowScale(torch.autograd.Function):
+    """y = x * s[..., None] for x [B, H, T, D] 16-bit and s [B, H, T]: the `v * dt` shape of mod, as one streaming
+    kernel each way (csrc/kernels/rowscale.cuh) instead of PyTorch's broadcast multiply and 64-wide reduction."""
+
+    @staticmethod
+    def forward(ctx, eng, x, s):
+        x, s = x.contiguous(), s.contiguous()
+        ctx.eng = eng
+        ctx.save_for_backward(x, s)
+        y = torch.empty_like(x)
+        eng._rowscale("fwd", x, s, y=y)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        x, s = ctx.saved_tensors
+        gx, gs = torch.empty_like(x), torch.empty_like(s)
+        ctx.eng._rowscale("bwd", x, s, g=g.contiguous(), gx=gx, gs=gs)
+        return None, gx, gs
+
+
 class LinearAttentionEngine:
     def __init__(self, qkv_meta, q_mod=None, k_mod=None, v_mod=None, decay_mod=None, custom_io=None, tune=False,
                  tune_filename="tune_result", tune_bwd=False):
@@ -78,6 +99,7 @@ class LinearAttentionEngine:
         self._status = None
         self._bwd = None
         self._fwd_by_dv = {}
+        self._rowscale_mods = {}
         # The kernels work on blocks of 128 key dims x 64 or 128 value dims.  Larger heads (simple_gla / retention_linear
         # of the reference use D = 256, DV = 512) are sums over key blocks of independent value blocks, see _scan().
         self._dv_block = self.DV if self.DV in (64, 128) else (128 if self.DV % 128 == 0 else 64)
@@ -139,9 +161,47 @@ class LinearAttentionEngine:
         dk = dk_h if HK == H else dk_h.view(B, HK, H // HK, T, DK).sum(2, dtype=torch.float32).to(self.dtype)
         return dq, dk, dv, da
 
+    def _rowscale(self, which, x, s, **out):
+        D = x.shape[-1]
+        s16 = s.dtype == self.dtype
+        key = (which, D, s16)
+        if key not in self._rowscale_mods:
+            pre = f"#define AE_BF16 {int(self._bf16)}\n#define AE_RS_D {D}\n#define AE_RS_S16 {int(s16)}\n"
+            cfg = rt.KernelConfig(kind=rt.KIND_ROWSCALE, dtype=rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16, head_dim=D,
+                                  head_dim_v=D, threads=256, smem_bytes=0, stages=1, mask_mode=0)
+            cfg.reserved[0] = int(s16)
+            self._rowscale_mods[key] = rt.compile_module(rt.kernel_source("rowscale.cuh", prelude=pre),
+                                                         f"ae_rowscale_{which}", cfg)
+        p = rt.RowScaleParams()
+        p.x, p.s, p.n_rows = x.data_ptr(), s.data_ptr(), x.numel() // D
+        for k_, t in out.items():
+            setattr(p, k_, t.data_ptr())
+        stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+        rt.check(rt.lib().ae_launch_rowscale(self._rowscale_mods[key].handle, C.byref(p), stream), "ae_launch_rowscale")
+
+    def _rowscale_operand(self, name, x, custom):
+        """The custom tensor s when the traced mod is exactly ``x * s`` with s indexed by (batch, heads, seq_len) and of
+        x's leading shape in fp32 or x's dtype; None otherwise (the mod then runs as eager PyTorch)."""
+        leaf, out = self._traced[name]
+        if name == "decay" or out.code.type != "Mul" or len(out.prev) != 2 or x.shape[-1] not in (64, 128, 256):
+            return None
+        other = out.prev[1] if out.prev[0] is leaf else out.prev[0] if out.prev[1] is leaf else None
+        if other is None:
+            return None
+        for (cname, sym), t in zip(self.custom_io.input_tensors.items(), custom):
+            if sym is other:
+                names = tuple(str(n) for n in sym.shape_idx)
+                if names == ("batch", "heads", "seq_len") and tuple(t.shape) == tuple(x.shape[:3]) and \
+                        t.dtype in (torch.float32, self.dtype) and x.dtype == self.dtype:
+                    return t
+        return None
+
     def _apply_mod(self, name, x, custom):
         if name not in self._traced:
             return x
+        s = self._rowscale_operand(name, x, custom)
+        if s is not None:
+            return _RowScale.apply(self, x, s)
         leaf, out = self._traced[name]
         env = {id(leaf): x.float() if name == "decay" else x}
         for (cname, sym), t in zip(self.custom_io.input_tensors.items(), custom):

@@ -705,6 +705,35 @@ int ae_launch_decode_combine(void* module, const AeDecodeParams* p, void* stream
   return launch(m, (unsigned)((a.H + 3) / 4), (unsigned)p->B, 1, &a, stream);
 }
 
+int ae_launch_rowscale(void* module, const AeRowScaleParams* p, void* stream) {
+  if (!module || !p || !p->x || !p->s || p->n_rows < 0) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  if (m->cfg.kind != AE_KIND_ROWSCALE) {
+    set_error("module kind does not match the entry point");
+    return AE_ERR_UNSUPPORTED;
+  }
+  const bool bwd = m->kernel == "ae_rowscale_bwd";
+  if (bwd ? (!p->g || !p->gx || !p->gs) : !p->y) return AE_ERR_INVALID;
+  const void* ptrs[5] = {p->x, p->y, p->g, p->gx, nullptr};
+  for (const void* q : ptrs)
+    if (q && (reinterpret_cast<uintptr_t>(q) & 15)) {
+      set_error("row-scale tensors must be 16-byte aligned");
+      return AE_ERR_INVALID;
+    }
+  if (p->n_rows == 0) return AE_OK;
+  int rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeRowScaleArgs a;
+  memset(&a, 0, sizeof a);
+  a.x = p->x; a.s = p->s; a.y = p->y; a.g = p->g; a.gx = p->gx; a.gs = p->gs;
+  a.n_rows = p->n_rows;
+  // 16 bytes per lane, 256 threads per CTA, up to 16 CTAs per SM's worth of blocks; the kernels stride over the rest
+  const int64_t lanes = p->n_rows * (m->cfg.head_dim / 8);
+  int64_t blocks = (lanes + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch(m, (unsigned)blocks, 1, 1, &a, stream);
+}
+
 // Tensor map over a contiguous [B, H, T, D] tensor seen as (d, t, h, b), box {64, rows, 1, 1}.
 static int make_bhtd_map(AeTmaDesc* out, const void* base, int dtype, int64_t B, int64_t H, int64_t T, int64_t D,
                          int rows) {

@@ -135,6 +135,17 @@ struct AeLinearBwdArgs {
   u32* status;
 };
 
+// ---- row-scale mod and its backward (kernels ae_rowscale_fwd, ae_rowscale_bwd) ---------------
+struct AeRowScaleArgs {
+  const void* x;  // [n_rows, D] 16-bit
+  const void* s;  // [n_rows] fp32 or 16-bit
+  void* y;        // forward:  x * s
+  const void* g;  // backward: gradient of y
+  void* gx;       // backward: g * s
+  void* gs;       // backward: sum_d g * x, in the type of s
+  i64 n_rows;
+};
+
 // ---- UMMA / TMA probe kernels (bring-up checks, kernel ae_probe) -------------------
 struct AeProbeArgs {
   AeTmaDesc tm_a;  // [128 rows, KD] 16-bit, box {64, 128}

@@ -1,0 +1,81 @@
+// Row-scale mod of the linear-attention engine and its backward, as two streaming kernels:
+//   forward   y[r, :] = x[r, :] * s[r]
+//   backward  gx[r, :] = g[r, :] * s[r],   gs[r] = sum_d g[r, d] * x[r, d]
+// x, y, g, gx are [n_rows, AE_RS_D] 16-bit, s / gs one value per row (fp32, or the 16-bit type when AE_RS_S16).
+// This is the shape of `v_mod = v * dt` of the reference's Mamba2 script (attn_script/mamba2_ngroup1.py:31-33), which
+// the reference runs as eager PyTorch statements (core/template/tl_template/linear/linear_tl.py:1136-1144, backward
+// :1203-1214); a broadcast multiply and a reduction over 64 contiguous elements are what PyTorch's generic kernels do
+// worst (measured 3 to 5 times the time of the bytes moved).
+// A row is shared by AE_RS_D / 8 lanes (16 bytes per lane); the loop bounds are warp-uniform so that the shuffles of the
+// row reduction are always executed by all 32 lanes.
+// Expects AE_BF16, AE_RS_D (64, 128 or 256), AE_RS_S16.
+
+#define AE_RS_TPR (AE_RS_D / 8)        // lanes per row
+#define AE_RS_RPW (32 / AE_RS_TPR)     // rows per warp and iteration
+#if AE_RS_D != 64 && AE_RS_D != 128 && AE_RS_D != 256
+#error "row length must be 64, 128 or 256"
+#endif
+
+AE_DEVICE float ae_rs_load_s(const void* s, i64 row) {
+#if AE_RS_S16
+  return unpack_lo<AE_BF16>((u32)((const u16*)s)[row]);
+#else
+  return ((const float*)s)[row];
+#endif
+}
+
+extern "C" __global__ void __launch_bounds__(256) ae_rowscale_fwd(const AeRowScaleArgs a) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp0 = ((i64)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const i64 n_warps = ((i64)gridDim.x * 256) >> 5;
+  for (i64 base = warp0 * AE_RS_RPW; base < a.n_rows; base += n_warps * AE_RS_RPW) {
+    const i64 row = base + lane / AE_RS_TPR;
+    if (row < a.n_rows) {
+      const i64 off = row * AE_RS_D + (lane % AE_RS_TPR) * 8;
+      const uint4 v = *(const uint4*)((const u16*)a.x + off);
+      const float sc = ae_rs_load_s(a.s, row);
+      uint4 o;
+      o.x = pack2<AE_BF16>(unpack_lo<AE_BF16>(v.x) * sc, unpack_hi<AE_BF16>(v.x) * sc);
+      o.y = pack2<AE_BF16>(unpack_lo<AE_BF16>(v.y) * sc, unpack_hi<AE_BF16>(v.y) * sc);
+      o.z = pack2<AE_BF16>(unpack_lo<AE_BF16>(v.z) * sc, unpack_hi<AE_BF16>(v.z) * sc);
+      o.w = pack2<AE_BF16>(unpack_lo<AE_BF16>(v.w) * sc, unpack_hi<AE_BF16>(v.w) * sc);
+      *(uint4*)((u16*)a.y + off) = o;
+    }
+  }
+}
+
+extern "C" __global__ void __launch_bounds__(256) ae_rowscale_bwd(const AeRowScaleArgs a) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp0 = ((i64)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const i64 n_warps = ((i64)gridDim.x * 256) >> 5;
+  for (i64 base = warp0 * AE_RS_RPW; base < a.n_rows; base += n_warps * AE_RS_RPW) {
+    const i64 row = base + lane / AE_RS_TPR;
+    const bool valid = row < a.n_rows;
+    float dot = 0.f;
+    if (valid) {
+      const i64 off = row * AE_RS_D + (lane % AE_RS_TPR) * 8;
+      const uint4 g = *(const uint4*)((const u16*)a.g + off);
+      const uint4 x = *(const uint4*)((const u16*)a.x + off);
+      const float sc = ae_rs_load_s(a.s, row);
+      const u32 gw[4] = {g.x, g.y, g.z, g.w}, xw[4] = {x.x, x.y, x.z, x.w};
+      u32 ow[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float g0 = unpack_lo<AE_BF16>(gw[i]), g1 = unpack_hi<AE_BF16>(gw[i]);
+        dot = fmaf(g0, unpack_lo<AE_BF16>(xw[i]), dot);
+        dot = fmaf(g1, unpack_hi<AE_BF16>(xw[i]), dot);
+        ow[i] = pack2<AE_BF16>(g0 * sc, g1 * sc);
+      }
+      *(uint4*)((u16*)a.gx + off) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+#pragma unroll
+    for (int o = AE_RS_TPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (valid && (lane % AE_RS_TPR) == 0) {
+#if AE_RS_S16
+      ((u16*)a.gs)[row] = (u16)(pack2<AE_BF16>(dot, 0.f) & 0xffffu);
+#else
+      ((float*)a.gs)[row] = dot;
+#endif
+    }
+  }
+}

@@ -23,6 +23,7 @@ STATIC_SCRATCH_MAX_ROWS = 8 * 1024 * 1024  # AE_STATIC_SCRATCH_MAX_ROWS in inclu
 KIND_PROBE, KIND_ATTN_FWD, KIND_ATTN_BWD_PREP, KIND_ATTN_BWD_DQ, KIND_ATTN_BWD_DKV = 0, 1, 2, 3, 4
 KIND_MLA_DECODE, KIND_MLA_COMBINE, KIND_LINEAR_FWD, KIND_LINEAR_BWD, KIND_LINEAR_STATES = 5, 6, 7, 8, 9
 KIND_ATTN_DECODE = 10
+KIND_ROWSCALE = 11
 DTYPE_F16, DTYPE_BF16 = 0, 1
 
 
@@ -85,6 +86,11 @@ class DecodeParams(C.Structure):
                 ("n_split", C.c_int32), ("status", C.c_void_p)]
 
 
+class RowScaleParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("s", C.c_void_p), ("y", C.c_void_p), ("g", C.c_void_p), ("gx", C.c_void_p),
+                ("gs", C.c_void_p), ("n_rows", C.c_int64)]
+
+
 class LinearParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("a", C.c_void_p), ("o", C.c_void_p),
                 ("B", C.c_int32), ("H", C.c_int32), ("HQ", C.c_int32), ("HK", C.c_int32), ("T", C.c_int32),
@@ -103,7 +109,7 @@ _lib_lock = threading.Lock()
 
 EXPORTS = ["ae_compile", "ae_module_from_cubin", "ae_module_cubin", "ae_query", "ae_release", "ae_strerror",
            "ae_last_error", "ae_launch_attn_fwd", "ae_launch_attn_bwd_prep", "ae_launch_attn_bwd_dq",
-           "ae_launch_attn_bwd_dkv", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch", "ae_launch_mla_decode", "ae_launch_mla_combine", "ae_launch_attn_decode", "ae_launch_decode_combine", "ae_launch_linear_fwd", "ae_launch_linear_states", "ae_launch_linear_bwd"]
+           "ae_launch_attn_bwd_dkv", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch", "ae_launch_mla_decode", "ae_launch_mla_combine", "ae_launch_attn_decode", "ae_launch_decode_combine", "ae_launch_rowscale", "ae_launch_linear_fwd", "ae_launch_linear_states", "ae_launch_linear_bwd"]
 
 
 def lib() -> C.CDLL:
@@ -133,6 +139,7 @@ def lib() -> C.CDLL:
             L.ae_launch_mla_combine.argtypes = [C.c_void_p, C.POINTER(MlaParams), C.c_void_p]
             L.ae_launch_attn_decode.argtypes = [C.c_void_p, C.POINTER(DecodeParams), C.c_void_p]
             L.ae_launch_decode_combine.argtypes = [C.c_void_p, C.POINTER(DecodeParams), C.c_void_p]
+            L.ae_launch_rowscale.argtypes = [C.c_void_p, C.POINTER(RowScaleParams), C.c_void_p]
             L.ae_launch_linear_fwd.argtypes = [C.c_void_p, C.POINTER(LinearParams), C.c_void_p]
             L.ae_launch_linear_states.argtypes = [C.c_void_p, C.POINTER(LinearBwdParams), C.c_void_p]
             L.ae_launch_linear_bwd.argtypes = [C.c_void_p, C.POINTER(LinearBwdParams), C.c_void_p]

@@ -54,6 +54,7 @@ enum {
   AE_KIND_LINEAR_BWD = 8,
   AE_KIND_LINEAR_STATES = 9,
   AE_KIND_ATTN_DECODE = 10,
+  AE_KIND_ROWSCALE = 11,
 };
 
 #define AE_MAX_CUSTOM_INPUTS 4
@@ -243,6 +244,26 @@ typedef struct AeLinearParams {
 } AeLinearParams;
 
 int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream);
+
+/* ---- row-scale mod of the linear-attention operator ---------------------------------------
+ * Stands in for the eager PyTorch statements the reference generates for a mod of the form
+ * `v * custom[b, h, t]` and for their hand-chained derivatives in `LinearAttention.forward / backward`
+ * (core/template/tl_template/linear/linear_tl.py:1136-1144, 1203-1214; Mamba2's `v_mod = v * dt`,
+ * attn_script/mamba2_ngroup1.py:31-33).  x, y, g, gx: [n_rows, head_dim] 16-bit contiguous (head_dim of the
+ * module: 64, 128 or 256); s, gs: one value per row, fp32 or (module config reserved[0] = 1) the 16-bit type.
+ * The module's kernel name selects the direction: "ae_rowscale_fwd" writes y = x * s; "ae_rowscale_bwd"
+ * writes gx = g * s and gs = sum_d g * x. */
+typedef struct AeRowScaleParams {
+  const void* x;
+  const void* s;
+  void* y;
+  const void* g;
+  void* gx;
+  void* gs;
+  int64_t n_rows;
+} AeRowScaleParams;
+
+int ae_launch_rowscale(void* module, const AeRowScaleParams* p, void* stream);
 
 /* ---- chunked linear attention / SSD scan, backward -------------------------------------
  * Stands in for the kernel part of `LinearAttention.backward`
