@@ -79,6 +79,36 @@ def test_dynamic_shape_engine_classifies_on_a_probe_and_builds_lists_per_shape()
     assert e._ensure_lists("cpu", None, 1, 2, 256, 256)[0] is c1  # cached per shape
 
 
+def test_decode_shapes_dispatch_to_the_split_kv_path():
+    """q_len != kv_len (reference: attn_engine.py:252-286): grouped heads need one query position; the split count never
+    leaves a split empty and is 1 when a stateful online function has no combine of its own."""
+    e = helpers.decode_engine(1, 32, 8, 1, 8192, 128, torch.float16)
+    assert e._decode is not None and e._decode.rows == 4 and e._decode.combine is not None
+    assert "AE_DECODE 1" in e.tl_code and "AE_NQ 1" in e.tl_code and "#define AE_STAGES 3" in e.tl_code
+    for B, S in ((1, 8192), (16, 8192), (64, 8192), (2, 1000), (3, 130)):
+        n = e._decode.pick_splits(B, S)
+        tiles = -(-S // 128)
+        assert 1 <= n <= min(32, tiles) and (n - 1) * (-(-tiles // n)) < tiles
+    two_tiles = helpers.decode_engine(1, 4, 4, 200, 4096, 64, torch.bfloat16)
+    assert two_tiles._decode.rows == 200 and "AE_NQ 2" in two_tiles.tl_code
+    no_combine = helpers.decode_engine(1, 8, 2, 1, 4096, 64, torch.float16, online=helpers.OnlineSoftmax())
+    assert no_combine._decode.combine is None and no_combine._decode.pick_splits(1, 4096) == 1
+    with pytest.raises(NotImplementedError):
+        helpers.decode_engine(1, 8, 2, 2, 4096, 64, torch.float16)       # grouped heads with two query positions
+    with pytest.raises(NotImplementedError):
+        helpers.decode_engine(1, 4, 4, 300, 4096, 64, torch.float16)     # more than 256 rows per head unit
+
+
+def test_row_scale_mod_is_recognised_in_the_trace():
+    """`v * custom[batch, heads, seq_len]` (Mamba2's v_mod) goes to the row-scale kernels; other mods stay eager."""
+    e = helpers.mamba2_engine(2, 4, 256, 128, 64, torch.bfloat16)
+    x = torch.zeros(2, 4, 256, 64, dtype=torch.bfloat16)
+    A, dt = torch.zeros(1, 4), torch.zeros(2, 4, 256, dtype=torch.bfloat16)
+    assert e._rowscale_operand("v", x, (A, dt)) is dt
+    assert e._rowscale_operand("decay", torch.zeros(2, 4, 256), (A, dt)) is None
+    assert e._rowscale_operand("v", x, (A, dt[:1])) is None  # a broadcast batch dim is left to PyTorch
+
+
 def test_block_lists_layout():
     from attentionengine_b200.attn_engine.attn_engine import _block_lists
     cnt = torch.tensor([[[[128 * 128, 0, 5], [0, 0, 0], [1, 128 * 128, 128 * 128]]]], dtype=torch.int32)
