@@ -336,12 +336,27 @@ class AttentionEngine:
         self._last_lists = lists
         return o, finals
 
+    def decode_paged(self, q, kcache, block_table, cache_seqlens, num_split=None):
+        """kv_shared engines: decode over a paged KV pool with one length per batch row, returns (out, lse)."""
+        if self._mla is None:
+            raise NotImplementedError("paged decode is built for kv_shared (MLA) engines")
+        return self._mla.paged(q, kcache, block_table, cache_seqlens, num_split)
+
     def _launch_bwd(self, q, k, v, o, d_o, finals, custom):
         from .attn_bwd import launch_bwd
         return launch_bwd(self, q, k, v, o, d_o, finals, custom)
 
     def __call__(self, *args, **kargs):
         if self._mla is not None:
+            if len(args) == 2:
+                # mod(q [B, 1, H, 576], kcache [B * S / 64, 64, 1, 576]) -> (out, lse): the call of the reference's
+                # CuTe kv-shared script (attn_script/mla_decode_cute.py:295-303), pages in batch order, full rows
+                q, kcache = args
+                B = q.shape[0]
+                pages = kcache.shape[0] // B
+                table = torch.arange(B * pages, dtype=torch.int32, device=q.device).view(B, pages)
+                lens = torch.full((B,), pages * 64, dtype=torch.int32, device=q.device)
+                return self._mla.paged(q, kcache, table, lens)
             return self._mla(*args)
         if self._decode is not None:
             return self._decode(*args)

@@ -93,3 +93,63 @@ class MlaDecode:
             rt.check(rt.lib().ae_launch_mla_combine(self.combine.handle, C.byref(p), stream), "ae_launch_mla_combine")
         self.last_num_split = n_split
         return o
+
+    def paged(self, q, kcache, block_table, cache_seqlens, num_split=None):
+        """Decode over a paged KV pool with one length per batch row; returns (o [B, 1, H, 512], lse [B, H] fp32).
+
+        The call of the reference's CuTe kv-shared path (core/template/cute_template_kvshared/flash_mla_interface.py:73-113,
+        attn_script/mla_decode_cute.py:295-303): q [B, 1, H, 576] (latent 512 + rope 64), kcache [num_pages, 64, 1, 576]
+        or [num_pages, 64, 576], block_table [B, max_pages] int32 (page of each 64-key tile), cache_seqlens [B] int32.
+        Every row gets the same split count over the longest row's tiles."""
+        if list(self.low.final_names) != ["lse"]:
+            raise NotImplementedError("the paged call returns the log-sum-exp: the online function must have the final row scale 'lse'")
+        for name, t in (("q", q), ("kcache", kcache)):
+            if not t.is_cuda:
+                raise rt.AeError(f"{name} must be a CUDA tensor: this back end has no CPU path")
+            if t.dtype != self.dtype:
+                raise TypeError(f"{name} has dtype {t.dtype}, engine was built for {self.dtype}")
+        B, one, H, D = q.shape
+        if one != 1 or D != 576 or H > 128:
+            raise ValueError("expected q [B, 1, H <= 128, 576]")
+        if kcache.dim() == 4:
+            if kcache.shape[2] != 1:
+                raise ValueError("expected kcache [num_pages, 64, 1, 576]")
+            kcache = kcache[:, :, 0]
+        if kcache.shape[1:] != (64, 576) or not kcache.is_contiguous():
+            raise ValueError("expected a contiguous kcache of 64-key pages, [num_pages, 64, (1,) 576]")
+        dev = q.device
+        block_table = block_table.to(device=dev, dtype=torch.int32).contiguous()
+        cache_seqlens = cache_seqlens.to(device=dev, dtype=torch.int32).contiguous()
+        if block_table.shape[0] != B or cache_seqlens.shape != (B,):
+            raise ValueError("block_table is [B, max_pages], cache_seqlens is [B]")
+        max_pages = block_table.shape[1]
+        max_seqlen = int(cache_seqlens.max().item())  # host read: the grid and the split ranges depend on it
+        if max_seqlen < 1 or int(cache_seqlens.min().item()) < 1 or max_seqlen > max_pages * 64:
+            raise ValueError("cache_seqlens must lie in [1, max_pages * 64]")
+        q_nope = q[:, 0, :, :512].contiguous()
+        q_pe = q[:, 0, :, 512:].contiguous()
+        n_split = num_split or self.num_split or self.pick_splits(B, max_seqlen)
+        o = torch.empty(B, 1, H, 512, dtype=self.dtype, device=dev)
+        fr = torch.empty(B, n_split, H, dtype=torch.float32, device=dev)
+        p = rt.MlaPagedParams()
+        p.q, p.q_pe, p.kcache, p.o = q_nope.data_ptr(), q_pe.data_ptr(), kcache.data_ptr(), o.data_ptr()
+        p.block_table, p.cache_seqlens = block_table.data_ptr(), cache_seqlens.data_ptr()
+        p.rowscale_partial[0] = fr.data_ptr()
+        part = None
+        if n_split > 1:
+            part = torch.empty(B, n_split, H, 512, dtype=torch.float32, device=dev)
+            p.o_partial = part.data_ptr()
+        p.B, p.H, p.num_pages, p.max_pages, p.max_seqlen, p.n_split = B, H, kcache.shape[0], max_pages, max_seqlen, n_split
+        if self._status is None or self._status.device != dev:
+            self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        p.status = self._status.data_ptr()
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        rt.check(rt.lib().ae_launch_mla_decode_paged(self.decode.handle, C.byref(p), stream), "ae_launch_mla_decode_paged")
+        if n_split > 1:
+            pc = rt.MlaParams()
+            pc.o, pc.o_partial = o.data_ptr(), part.data_ptr()
+            pc.rowscale_partial[0] = fr.data_ptr()
+            pc.B, pc.H, pc.S, pc.n_split = B, H, max_seqlen, n_split
+            rt.check(rt.lib().ae_launch_mla_combine(self.combine.handle, C.byref(pc), stream), "ae_launch_mla_combine")
+        self.last_num_split = n_split
+        return o, torch.logsumexp(fr, dim=1)

@@ -535,14 +535,15 @@ int ae_launch_attn_bwd_dkv(void* module, const AeAttnBwdParams* p, void* stream)
 }
 
 static int make_3d_map(AeTmaDesc* out, const void* base, int dtype, int64_t cols, int64_t rows, int64_t batch,
-                       int box_rows) {
+                       int box_rows, int64_t row_stride = 0) {
   Driver& d = driver();
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) {
     set_error("tensor base address must be 16-byte aligned");
     return AE_ERR_INVALID;
   }
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
-  cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * cols * 2};
+  if (row_stride == 0) row_stride = cols;  // elements between rows; larger when the rows are slices of wider ones
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)rows * row_stride * 2};
   cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUtensorMapDataType dt = dtype == AE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -587,6 +588,54 @@ int ae_launch_mla_decode(void* module, const AeMlaParams* p, void* stream) {
   for (int i = 0; i < AE_MAX_FINAL; ++i) a.fr_part[i] = p->rowscale_partial[i];
   a.B = p->B; a.H = p->H; a.S = p->S; a.n_split = p->n_split; a.tiles_per_split = tps;
   a.status = p->status;
+  return launch(m, 2, (unsigned)p->n_split, (unsigned)p->B, &a, stream);
+}
+
+int ae_launch_mla_decode_paged(void* module, const AeMlaPagedParams* p, void* stream) {
+  if (!module || !p || !p->q || !p->q_pe || !p->kcache || !p->block_table || !p->cache_seqlens || !p->o)
+    return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  if (m->cfg.kind != AE_KIND_MLA_DECODE) {
+    set_error("module kind does not match the entry point");
+    return AE_ERR_UNSUPPORTED;
+  }
+  if (m->cfg.reserved[0] != 64) {
+    set_error("paged MLA decode: pages hold 64 keys, the kernel must stream 64-row tiles");
+    return AE_ERR_UNSUPPORTED;
+  }
+  if (p->B <= 0 || p->H <= 0 || p->H > 128 || p->num_pages <= 0 || p->max_pages <= 0 || p->max_seqlen <= 0 ||
+      p->max_seqlen > (int64_t)p->max_pages * 64 || p->n_split < 1 || p->n_split > 32) {
+    set_error("paged MLA decode: need 1 <= H <= 128, 1 <= max_seqlen <= max_pages * 64, 1 <= n_split <= 32");
+    return AE_ERR_INVALID;
+  }
+  const int n_tiles = (p->max_seqlen + 63) / 64;
+  const int tps = (n_tiles + p->n_split - 1) / p->n_split;
+  if ((int64_t)(p->n_split - 1) * tps >= n_tiles) {
+    set_error("MLA decode: n_split leaves an empty split");
+    return AE_ERR_INVALID;
+  }
+  if (p->n_split > 1 && !p->o_partial) {
+    set_error("MLA decode: o_partial scratch required when n_split > 1");
+    return AE_ERR_INVALID;
+  }
+  int rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeMlaArgs a;
+  memset(&a, 0, sizeof a);
+  const int64_t pool_rows = (int64_t)p->num_pages * 64;
+  if ((rc = make_3d_map(&a.tm_q, p->q, m->cfg.dtype, 512, p->H, p->B, 128))) return rc;
+  if ((rc = make_3d_map(&a.tm_qpe, p->q_pe, m->cfg.dtype, 64, p->H, p->B, 128))) return rc;
+  // the pool as one batch of num_pages * 64 rows of 576 elements: latent part and rope part are column slices
+  if ((rc = make_3d_map(&a.tm_kv, p->kcache, m->cfg.dtype, 512, pool_rows, 1, 64, 576))) return rc;
+  if ((rc = make_3d_map(&a.tm_kpe, (const char*)p->kcache + 512 * 2, m->cfg.dtype, 64, pool_rows, 1, 64, 576))) return rc;
+  a.o = p->o;
+  a.o_part = p->o_partial;
+  for (int i = 0; i < AE_MAX_FINAL; ++i) a.fr_part[i] = p->rowscale_partial[i];
+  a.B = p->B; a.H = p->H; a.S = p->max_seqlen; a.n_split = p->n_split; a.tiles_per_split = tps;
+  a.status = p->status;
+  a.block_table = p->block_table;
+  a.seqlens = p->cache_seqlens;
+  a.max_pages = p->max_pages;
   return launch(m, 2, (unsigned)p->n_split, (unsigned)p->B, &a, stream);
 }
 

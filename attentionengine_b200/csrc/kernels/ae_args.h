@@ -99,6 +99,12 @@ struct AeMlaArgs {
   float* fr_part[AE_MAX_FINAL];  // each [B, n_split, H]
   int B, H, S, n_split, tiles_per_split;
   u32* status;
+  // paged KV (null = the dense layout above): tm_kv / tm_kpe then cover the page pool as rows (page * 64 + r) of one
+  // batch, tile i of batch row b is page block_table[b * max_pages + i], and row b holds seqlens[b] keys
+  // (S = the longest row; a split that starts past a row's last tile writes zero partials with -inf row scales).
+  const int* block_table;
+  const int* seqlens;
+  int max_pages;
 };
 struct AeMlaCombineArgs {
   void* o;

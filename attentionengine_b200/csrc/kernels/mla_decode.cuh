@@ -67,7 +67,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
 #ifdef AE_TRACE
   const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0;
 #endif
-  const int n_tiles = (args.S + AE_MLA_BN - 1) / AE_MLA_BN;
+  const int S_b = args.seqlens ? args.seqlens[b] : args.S;  // keys of this batch row
+  const int n_tiles = (S_b + AE_MLA_BN - 1) / AE_MLA_BN;
   const int t_begin = split * args.tiles_per_split;
   int t_end = t_begin + args.tiles_per_split;
   if (t_end > n_tiles) t_end = n_tiles;
@@ -113,12 +114,18 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
         const int stage = s % AE_MLA_STAGES;
         if (s == 0 && !mbar_wait(&bars->q_tmem, 0, ctl, args.status, 40)) break;
         if (!mbar_wait(&bars->kv_empty[stage], ((s / AE_MLA_STAGES) & 1) ^ 1, ctl, args.status, 41)) break;
-        const int kv0 = (t_begin + s) * AE_MLA_BN;
+        // dense: rows (tile * 64 ..) of batch b; paged: the tile's page in the pool (a page index outside the pool
+        // reads the fill value, it cannot fault)
+        int kv0 = (t_begin + s) * AE_MLA_BN, kb = b;
+        if (args.block_table) {
+          kv0 = args.block_table[(i64)b * args.max_pages + (t_begin + s)] * AE_MLA_BN;
+          kb = 0;
+        }
         u8* dst = smem + AE_MLA_SMEM_KV + stage * AE_MLA_KV_BYTES;
         mbar_arrive_expect_tx(&bars->kv_full[stage], AE_MLA_KV_BYTES);
         for (int blk = 0; blk < AE_MLA_NBV; ++blk)
-          tma_load_3d(dst + blk * (AE_MLA_BN * 128), &args.tm_kv, &bars->kv_full[stage], blk * 64, kv0, b);
-        tma_load_3d(dst + AE_MLA_NBV * (AE_MLA_BN * 128), &args.tm_kpe, &bars->kv_full[stage], 0, kv0, b);
+          tma_load_3d(dst + blk * (AE_MLA_BN * 128), &args.tm_kv, &bars->kv_full[stage], blk * 64, kv0, kb);
+        tma_load_3d(dst + AE_MLA_NBV * (AE_MLA_BN * 128), &args.tm_kpe, &bars->kv_full[stage], 0, kv0, kb);
       }
     }
   } else if (warp == 5) {
@@ -231,10 +238,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
       float sc[AE_MLA_BN];
       tmem_ld_f32x64(tm_s, sc);
       const int kv0 = (t_begin + s) * AE_MLA_BN;
-      if (kv0 + AE_MLA_BN > args.S) {
+      if (kv0 + AE_MLA_BN > S_b) {
 #pragma unroll
         for (int c = 0; c < AE_MLA_BN; ++c)
-          if (kv0 + c >= args.S) sc[c] = -__int_as_float(0x7f800000);
+          if (kv0 + c >= S_b) sc[c] = -__int_as_float(0x7f800000);
       }
       const float o_scale = ae_online_fwd<AE_MLA_BN>(sc, st, b, h, 0, kv0, cu);
       {
@@ -327,6 +334,16 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
         for (int i = 0; i < AE_NFINAL; ++i)
           if (args.fr_part[i]) args.fr_part[i][((i64)b * args.n_split + split) * args.H + h] = fr[i];
       }
+#endif
+    } else if (args.n_split > 1 && h < args.H) {
+      // rows of different lengths: this split starts past the row's last tile.  Its partial is zero with -inf row
+      // scales, which the combine pass weighs with exp(-inf - ...) = 0.
+      float4* dst = (float4*)(args.o_part + (((i64)b * args.n_split + split) * args.H + h) * AE_MLA_DV + dvh * AE_MLA_DVH);
+      for (int v = 0; v < AE_MLA_DVH / 4; ++v) dst[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+#if AE_NFINAL > 0
+      if (dvh == 0)
+        for (int i = 0; i < AE_NFINAL; ++i)
+          if (args.fr_part[i]) args.fr_part[i][((i64)b * args.n_split + split) * args.H + h] = -__int_as_float(0x7f800000);
 #endif
     }
   }

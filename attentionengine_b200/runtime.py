@@ -91,6 +91,14 @@ class RowScaleParams(C.Structure):
                 ("gs", C.c_void_p), ("n_rows", C.c_int64)]
 
 
+class MlaPagedParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("q_pe", C.c_void_p), ("kcache", C.c_void_p), ("block_table", C.c_void_p),
+                ("cache_seqlens", C.c_void_p), ("o", C.c_void_p), ("o_partial", C.c_void_p),
+                ("rowscale_partial", C.c_void_p * AE_MAX_FINAL),
+                ("B", C.c_int32), ("H", C.c_int32), ("num_pages", C.c_int32), ("max_pages", C.c_int32),
+                ("max_seqlen", C.c_int32), ("n_split", C.c_int32), ("status", C.c_void_p)]
+
+
 class LinearParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("a", C.c_void_p), ("o", C.c_void_p),
                 ("B", C.c_int32), ("H", C.c_int32), ("HQ", C.c_int32), ("HK", C.c_int32), ("T", C.c_int32),
@@ -109,7 +117,7 @@ _lib_lock = threading.Lock()
 
 EXPORTS = ["ae_compile", "ae_module_from_cubin", "ae_module_cubin", "ae_query", "ae_release", "ae_strerror",
            "ae_last_error", "ae_launch_attn_fwd", "ae_launch_attn_bwd_prep", "ae_launch_attn_bwd_dq",
-           "ae_launch_attn_bwd_dkv", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch", "ae_launch_mla_decode", "ae_launch_mla_combine", "ae_launch_attn_decode", "ae_launch_decode_combine", "ae_launch_rowscale", "ae_launch_linear_fwd", "ae_launch_linear_states", "ae_launch_linear_bwd"]
+           "ae_launch_attn_bwd_dkv", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch", "ae_launch_mla_decode", "ae_launch_mla_combine", "ae_launch_mla_decode_paged", "ae_launch_attn_decode", "ae_launch_decode_combine", "ae_launch_rowscale", "ae_launch_linear_fwd", "ae_launch_linear_states", "ae_launch_linear_bwd"]
 
 
 def lib() -> C.CDLL:
@@ -137,6 +145,7 @@ def lib() -> C.CDLL:
                                                             C.c_void_p]
             L.ae_launch_mla_decode.argtypes = [C.c_void_p, C.POINTER(MlaParams), C.c_void_p]
             L.ae_launch_mla_combine.argtypes = [C.c_void_p, C.POINTER(MlaParams), C.c_void_p]
+            L.ae_launch_mla_decode_paged.argtypes = [C.c_void_p, C.POINTER(MlaPagedParams), C.c_void_p]
             L.ae_launch_attn_decode.argtypes = [C.c_void_p, C.POINTER(DecodeParams), C.c_void_p]
             L.ae_launch_decode_combine.argtypes = [C.c_void_p, C.POINTER(DecodeParams), C.c_void_p]
             L.ae_launch_rowscale.argtypes = [C.c_void_p, C.POINTER(RowScaleParams), C.c_void_p]

@@ -200,6 +200,27 @@ typedef struct AeMlaParams {
 int ae_launch_mla_decode(void* module, const AeMlaParams* p, void* stream);
 int ae_launch_mla_combine(void* module, const AeMlaParams* p, void* stream);
 
+/* The same decode over a paged KV pool with one length per batch row: the call of the reference's CuTe kv-shared
+ * path, `flash_mla_with_kvcache(q, k_cache, block_table, cache_seqlens, ...)`
+ * (core/template/cute_template_kvshared/flash_mla_interface.py:73-113; script attn_script/mla_decode_cute.py:295-303),
+ * whose scheduler metadata (`get_mla_metadata`) has no counterpart here: every batch row gets the same n_split over
+ * the longest row's tiles, and a split that starts past a shorter row's end contributes nothing.  Pages hold 64 keys.
+ * The merge is `ae_launch_mla_combine` with q / kv unused (fill o, o_partial, rowscale_partial, B, H, n_split). */
+typedef struct AeMlaPagedParams {
+  const void* q;                /* [B, H, 512] contiguous: the latent part of the query */
+  const void* q_pe;             /* [B, H, 64]  contiguous: its rope part */
+  const void* kcache;           /* [num_pages, 64, 576]: dims 0..511 latent kv (keys and values), 512..575 rope keys */
+  const int32_t* block_table;   /* [B, max_pages]: page of the i-th 64-key tile of a batch row */
+  const int32_t* cache_seqlens; /* [B]: keys of each batch row, 1 <= len <= max_pages * 64 */
+  void* o;                      /* [B, H, 512] */
+  float* o_partial;             /* [B, n_split, H, 512] fp32 (n_split > 1) */
+  float* rowscale_partial[AE_MAX_FINAL_ROWSCALES]; /* each [B, n_split, H]; with n_split == 1 the final row scales */
+  int32_t B, H, num_pages, max_pages, max_seqlen, n_split;
+  uint32_t* status;
+} AeMlaPagedParams;
+
+int ae_launch_mla_decode_paged(void* module, const AeMlaPagedParams* p, void* stream);
+
 /* ---- split-KV decode for MHA / GQA -----------------------------------------------------
  * Stands in for the reference's decode modules: `flashattn_gqa_decode` / `flashattn` split + `combine`
  * (core/template/tl_template/attn/attn_decode_tl.py:34-206, attn_gqa_decode_tl.py; dispatch

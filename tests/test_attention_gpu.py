@@ -402,6 +402,50 @@ def test_mamba2_ssd_backward_against_oracle(B, H, T):
         assert rel <= lim, f"{name}: rel-L2 {rel:.3e} (max-abs {mx:.3e})"
 
 
+@pytest.mark.parametrize("n_split", [None, 1, 3])
+def test_mla_decode_paged_kv_with_ragged_lengths(n_split):
+    """The call of the reference's CuTe kv-shared path (flash_mla_interface.py:73-113): a pool of 64-key pages in
+    shuffled order, a block table per batch row, one length per row (one row a single key, one exactly full pages, one
+    shorter than the splits reach).  Output and log-sum-exp per row against the oracle on that row's gathered keys."""
+    B, H, dtype, scale = 4, 128, torch.float16, 1 / math.sqrt(192)
+    lens = [1, 640, 1000, 130]
+    max_pages = 16
+    g = torch.Generator().manual_seed(70)
+    n_pages = B * max_pages + 3
+    kcache = torch.randn(n_pages, 64, 1, 576, generator=g).to(dtype)
+    perm = torch.randperm(n_pages, generator=g)[:B * max_pages].to(torch.int32).view(B, max_pages)
+    q = torch.randn(B, 1, H, 576, generator=g).to(dtype)
+    eng = helpers.mla_engine(B, H, max_pages * 64, dtype, scale)
+    o, lse = eng.decode_paged(q.cuda(), kcache.cuda(), perm.cuda(), torch.tensor(lens, dtype=torch.int32).cuda(),
+                              num_split=n_split)
+    torch.cuda.synchronize()
+    eng.check_status()
+    if n_split:
+        assert eng._mla.last_num_split == n_split
+    for b, L in enumerate(lens):
+        rows = kcache[perm[b].long(), :, 0].reshape(-1, 576)[:L]          # [L, 576] in logical order
+        ro, rl = orc.mla_decode(q[b:b + 1, 0, :, :512], q[b:b + 1, 0, :, 512:], rows[None, :, None, :512],
+                                rows[None, :, None, 512:], scale=scale, return_lse=True)
+        _check(f"row {b} o", o[b:b + 1, 0].cpu(), ro, dtype)
+        assert (lse[b].cpu() - rl[0]).abs().max().item() <= 2e-3, f"row {b} lse"
+
+
+def test_mla_two_argument_call_reads_the_cache_in_batch_order():
+    """mod(q, kcache) as in attn_script/mla_decode_cute.py:295-303: pages of a batch row are consecutive, rows full."""
+    B, H, S, dtype, scale = 2, 64, 512, torch.bfloat16, 1 / math.sqrt(576)
+    g = torch.Generator().manual_seed(71)
+    kcache = torch.randn(B * S // 64, 64, 1, 576, generator=g).to(dtype)
+    q = torch.randn(B, 1, H, 576, generator=g).to(dtype)
+    eng = helpers.mla_engine(B, H, S, dtype, scale)
+    o, lse = eng(q.cuda(), kcache.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    kv = kcache.view(B, S, 1, 576)
+    ro, rl = orc.mla_decode(q[:, 0, :, :512], q[:, 0, :, 512:], kv[..., :512], kv[..., 512:], scale=scale, return_lse=True)
+    _check("o", o[:, 0].cpu(), ro, dtype)
+    assert (lse.cpu() - rl).abs().max().item() <= 2e-2
+
+
 @pytest.mark.parametrize("variant", ["simple_gla", "retention_linear"])
 def test_linear_variants_with_large_heads(variant):
     """attn_script/simple_gla.py (q_mod = q * scale, the decay input is already a log-decay) and retention_linear.py
