@@ -7,7 +7,8 @@ Same constructor and call as the reference (attention_engine/attn_engine/linear_
 As in the reference (core/template/tl_template/linear/linear_tl.py:1136-1144) the mods are traced once and
 run as eager PyTorch on the inputs; the scan itself (chunk cumulative sum, state recurrence, intra-chunk
 products) is one sm_100a kernel (csrc/kernels/linear_fwd.cuh); its backward is a state-recompute pass
-(linear_states.cuh) and a reverse pass (linear_bwd.cuh), built for DV = 64.
+(linear_states.cuh) and a reverse pass (linear_bwd.cuh) on value blocks of 64; heads larger than one block of
+128 key dims x 64 / 128 value dims are decomposed into blocks (``_scan``).
 """
 from __future__ import annotations
 
