@@ -180,9 +180,11 @@ class AttentionEngine:
             self.tl_code = self._mla.src
             self.mask_mode = 0
             return
-        if not dynamic and Sq != Skv:
-            # decode shape classes (reference: attn_engine.py:252-286): split-KV kernel + OnlineFunc.combine
-            if Sq > Skv:
+        ints = all(isinstance(x, int) for x in (Hq, Hkv, Sq))
+        if ints and Sq != Skv and (isinstance(Skv, str) or not dynamic):
+            # decode shape classes (reference: attn_engine.py:252-286): split-KV kernel + OnlineFunc.combine.  The KV
+            # length (and the batch) may be named dims: a serving loop calls one engine with a growing cache.
+            if isinstance(Skv, int) and Sq > Skv:
                 raise NotImplementedError("q_len > kv_len is not an attention shape the reference defines")
             from .attn_decode import AttnDecode
             self._decode = AttnDecode(score_mod, mask_mod, online_func, self.custom_fwd_inputs, Hq, Hkv, Sq, D, DV,

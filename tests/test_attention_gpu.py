@@ -203,6 +203,21 @@ def test_gqa_decode_split_kv(n_split):
     _check("o", o.cpu(), orc.softmax_attention(q, k, v, False), dtype)
 
 
+def test_decode_engine_with_a_named_kv_length_serves_a_growing_cache():
+    """meta_tensor(B, Hkv, "S_kv", D): one decode engine, calls with different KV lengths and batch sizes."""
+    Hq, Hkv, D, dtype = 16, 4, 128, torch.float16
+    eng = helpers.decode_engine("B", Hq, Hkv, 1, "S_kv", D, dtype)
+    g = torch.Generator().manual_seed(53)
+    for B, S in ((1, 300), (3, 1500), (2, 64)):
+        q = torch.randn(B, 1, Hq, D, generator=g).to(dtype)
+        k = torch.randn(B, S, Hkv, D, generator=g).to(dtype)
+        v = torch.randn(B, S, Hkv, D, generator=g).to(dtype)
+        o = eng(q.cuda(), k.cuda(), v.cuda())
+        torch.cuda.synchronize()
+        eng.check_status()
+        _check(f"B={B} S={S} o", o.cpu(), orc.softmax_attention(q, k, v, False), dtype)
+
+
 @pytest.mark.parametrize("Sq", [1, 3, 200])
 def test_mha_decode_split_kv(Sq):
     """attn_script/mha_inference.py shape class: Hq == Hkv, a few query positions against a long KV range; 200 rows

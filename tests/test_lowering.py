@@ -93,6 +93,8 @@ def test_decode_shapes_dispatch_to_the_split_kv_path():
     assert two_tiles._decode.rows == 200 and "AE_NQ 2" in two_tiles.tl_code
     no_combine = helpers.decode_engine(1, 8, 2, 1, 4096, 64, torch.float16, online=helpers.OnlineSoftmax())
     assert no_combine._decode.combine is None and no_combine._decode.pick_splits(1, 4096) == 1
+    growing = helpers.decode_engine("B", 32, 8, 1, "S_kv", 128, torch.float16)  # named batch and KV length
+    assert growing._decode is not None and growing._decode.rows == 4
     with pytest.raises(NotImplementedError):
         helpers.decode_engine(1, 8, 2, 2, 4096, 64, torch.float16)       # grouped heads with two query positions
     with pytest.raises(NotImplementedError):
