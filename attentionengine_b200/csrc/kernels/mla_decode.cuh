@@ -46,8 +46,14 @@
 struct AeMlaBars {
   u64 q_full;   // the whole query block landed in shared memory
   u64 q_tmem;   // its first blocks were copied to TMEM (KV stage 0 is free)
-  u64 kv_full[AE_MLA_STAGES];
-  u64 kv_empty[AE_MLA_STAGES];
+  // A KV stage is two parts with their own barriers: the CTA's own half of the value dims (4 blocks, held until the
+  // tile's P V GEMM has run) and the rest (the other half and the rope block, 5 blocks, free as soon as the S GEMM has
+  // read them).  With two stages the refill of a stage used to wait for P V of the tile before; now 40 of its 72 KB
+  // are requested one S GEMM earlier, and only the value part's 32 KB sit on the chain P V -> load -> next S GEMM.
+  u64 kv_full[AE_MLA_STAGES];    // the value part landed
+  u64 kv_empty[AE_MLA_STAGES];   // ... and was read by P V
+  u64 kx_full[AE_MLA_STAGES];    // the rest landed
+  u64 kx_empty[AE_MLA_STAGES];   // ... and was read by the S GEMM
   u64 s_full[2];
   u64 o_done;
   AeCtaCtl ctl;
@@ -82,6 +88,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->kv_full[i], 1);
       mbar_init(&bars->kv_empty[i], 1);
+      mbar_init(&bars->kx_full[i], 1);
+      mbar_init(&bars->kx_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
     }
     mbar_fence_init();
@@ -113,7 +121,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
       for (int s = 0; s < n_steps; ++s) {
         const int stage = s % AE_MLA_STAGES;
         if (s == 0 && !mbar_wait(&bars->q_tmem, 0, ctl, args.status, 40)) break;
-        if (!mbar_wait(&bars->kv_empty[stage], ((s / AE_MLA_STAGES) & 1) ^ 1, ctl, args.status, 41)) break;
+        if (!mbar_wait(&bars->kx_empty[stage], ((s / AE_MLA_STAGES) & 1) ^ 1, ctl, args.status, 41)) break;
         // dense: rows (tile * 64 ..) of batch b; paged: the tile's page in the pool (a page index outside the pool
         // reads the fill value, it cannot fault)
         int kv0 = (t_begin + s) * AE_MLA_BN, kb = b;
@@ -122,10 +130,16 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
           kb = 0;
         }
         u8* dst = smem + AE_MLA_SMEM_KV + stage * AE_MLA_KV_BYTES;
-        mbar_arrive_expect_tx(&bars->kv_full[stage], AE_MLA_KV_BYTES);
+        const int v_lo = dvh * (AE_MLA_NBV / 2), v_hi = v_lo + AE_MLA_NBV / 2;  // this CTA's value blocks
+        mbar_arrive_expect_tx(&bars->kx_full[stage], (AE_MLA_NBK - AE_MLA_NBV / 2) * (AE_MLA_BN * 128));
         for (int blk = 0; blk < AE_MLA_NBV; ++blk)
+          if (blk < v_lo || blk >= v_hi)
+            tma_load_3d(dst + blk * (AE_MLA_BN * 128), &args.tm_kv, &bars->kx_full[stage], blk * 64, kv0, kb);
+        tma_load_3d(dst + AE_MLA_NBV * (AE_MLA_BN * 128), &args.tm_kpe, &bars->kx_full[stage], 0, kv0, kb);
+        if (!mbar_wait(&bars->kv_empty[stage], ((s / AE_MLA_STAGES) & 1) ^ 1, ctl, args.status, 41)) break;
+        mbar_arrive_expect_tx(&bars->kv_full[stage], (AE_MLA_NBV / 2) * (AE_MLA_BN * 128));
+        for (int blk = v_lo; blk < v_hi; ++blk)
           tma_load_3d(dst + blk * (AE_MLA_BN * 128), &args.tm_kv, &bars->kv_full[stage], blk * 64, kv0, kb);
-        tma_load_3d(dst + AE_MLA_NBV * (AE_MLA_BN * 128), &args.tm_kpe, &bars->kv_full[stage], 0, kv0, kb);
       }
     }
   } else if (warp == 5) {
@@ -140,7 +154,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
       auto issue_s = [&](int s, bool landed) -> bool {  // S_s into region s & 1
         const int stage = s % AE_MLA_STAGES;
         AE_TRM(true, 0, s * 8 + 0)
-        if (!landed && !mbar_wait_w(&bars->kv_full[stage], (s / AE_MLA_STAGES) & 1, ctl, args.status, 43)) return false;
+        if (!landed) {
+          if (!mbar_wait_w(&bars->kx_full[stage], (s / AE_MLA_STAGES) & 1, ctl, args.status, 43)) return false;
+          if (!mbar_wait_w(&bars->kv_full[stage], (s / AE_MLA_STAGES) & 1, ctl, args.status, 44)) return false;
+        }
         tc_fence_after_sync();
         AE_TRM(true, 0, s * 8 + 1)
         const u32 d = tmem + TM_S + (s & 1) * 64;
@@ -156,6 +173,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
               umma_ss_w(d, dq0 + (u64)(((blk - AE_MLA_QT) * (AE_MLA_H * 128) + kk * 32) >> 4), db, idesc_s, 1);
           }
         }
+        umma_commit_w(&bars->kx_empty[stage]);  // the five blocks that only the S GEMM reads can be refilled
         umma_commit_w(&bars->s_full[s & 1]);
         AE_TRM(true, 0, s * 8 + 2)
         return true;
@@ -168,11 +186,14 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_mla_decode(const __grid_
       if (ok) ok = issue_s(0, false);
       for (int s = 0; s < n_steps && ok; ++s) {
         const int stage = s % AE_MLA_STAGES;
-        // The next S GEMM goes first if its KV tile has already landed (the other S region held P of tile s-1, whose
-        // P V GEMM was issued in the previous iteration); otherwise P V of this tile must not wait behind the load.
+        // The next S GEMM goes first if both parts of its KV tile have already landed (the other S region held P of tile
+        // s-1, whose P V GEMM was issued in the previous iteration); otherwise P V of this tile must not wait behind the
+        // load.
         bool early = false;
         if (s + 1 < n_steps) {
-          early = __all_sync(0xffffffffu, mbar_try_wait(&bars->kv_full[(s + 1) % AE_MLA_STAGES], ((s + 1) / AE_MLA_STAGES) & 1));
+          const int ns = (s + 1) % AE_MLA_STAGES;
+          const u32 np = ((s + 1) / AE_MLA_STAGES) & 1;
+          early = __all_sync(0xffffffffu, mbar_try_wait(&bars->kx_full[ns], np) && mbar_try_wait(&bars->kv_full[ns], np));
           if (early) ok = issue_s(s + 1, true);
         }
         if (!ok) break;
