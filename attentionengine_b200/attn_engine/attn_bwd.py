@@ -88,7 +88,7 @@ def _s3(t):
     return (C.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
 
 
-def launch_bwd(eng, q, k, v, o, d_o, finals, custom):
+def launch_bwd(eng, q, k, v, o, d_o, finals, custom, lists=None):
     kern = eng.kernels.bwd
     B, Sq, Hq, Skv, Hkv = eng._check_qkv(q, k, v)
     dev = q.device
@@ -109,7 +109,8 @@ def launch_bwd(eng, q, k, v, o, d_o, finals, custom):
         delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=dev)
         p.delta = delta.data_ptr()
     p.custom, p.custom_stride, keep = eng._custom_args(custom, Sq, Skv)
-    lists = eng._ensure_lists(dev, eng.block_mask if eng.extern_block_mask else None, B, Hq, Sq, Skv)
+    if lists is None:  # direct callers; the autograd path hands over the lists its forward walked
+        lists = eng._ensure_lists(dev, eng.block_mask if eng.extern_block_mask else None, B, Hq, Sq, Skv)
     if lists is not None:
         p.block_count, p.block_index = lists[0].data_ptr(), lists[1].data_ptr()
         p.block_count_t, p.block_index_t = lists[2].data_ptr(), lists[3].data_ptr()

@@ -126,8 +126,11 @@ class _AttnKernels:
 class _AttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, eng, q, k, v, *custom):
-        o, finals = eng._launch_fwd(q, k, v, custom)
+        eng._check_qkv(q, k, v)
+        with torch.cuda.device(q.device):  # the C ABI launches on the current device's context
+            o, finals, lists = eng._launch_fwd(q, k, v, custom, block_mask=eng._call_block_mask, return_lists=True)
         ctx.eng = eng
+        ctx.lists = lists  # the tile lists this forward walked: its backward walks the same ones
         ctx.n_custom = len(custom)
         ctx.save_for_backward(q, k, v, o, *finals, *custom)
         ctx.n_final = len(finals)
@@ -140,7 +143,8 @@ class _AttentionFn(torch.autograd.Function):
         q, k, v, o = saved[:4]
         finals = saved[4:4 + ctx.n_final]
         custom = saved[4 + ctx.n_final:]
-        dq, dk, dv = eng._launch_bwd(q, k, v, o, d_o, finals, custom)
+        with torch.cuda.device(q.device):
+            dq, dk, dv = eng._launch_bwd(q, k, v, o, d_o, finals, custom, ctx.lists)
         return (None, dq, dk, dv) + (None,) * ctx.n_custom
 
 
@@ -165,6 +169,7 @@ class AttentionEngine:
         self.mask_value = mask_value
         self.extern_block_mask = extern_block_mask
         self.block_mask = None
+        self._call_block_mask = None
         self._lists = None
         self._status = None
         dynamic = any(isinstance(x, str) for x in (B, Hq, Sq, Skv))
@@ -252,13 +257,19 @@ class AttentionEngine:
                 raise rt.AeError(f"kernel reported status 0x{code:x} (a bounded wait gave up)")
 
     def _ensure_lists(self, device, block_mask: Optional[torch.Tensor], B, Hq, Sq, Skv):
+        """Tile lists (count, index, transposed count, transposed index) of a mode-2 engine for one call, or None.
+        The kernels index the lists with the runtime tile grid, so every source is checked against it here."""
         if self.mask_mode != 2:
             return None
+        nq, nk = -(-Sq // 128), -(-Skv // 128)
         if block_mask is not None:
+            if block_mask.dim() != 4 or tuple(block_mask.shape[2:]) != (nq, nk) or \
+                    block_mask.shape[0] not in (1, B) or block_mask.shape[1] not in (1, Hq):
+                raise ValueError(f"block_mask has shape {tuple(block_mask.shape)}; expected [1 or {B}, 1 or {Hq}, {nq}, {nk}] "
+                                 f"(one entry per 128 x 128 tile of the {Sq} x {Skv} score matrix)")
             cnt = block_mask.to(torch.int32).cpu()
             if self.mask_mod is None:
                 # listed blocks are complete blocks
-                nq, nk = cnt.shape[2], cnt.shape[3]
                 rows = torch.clamp(Sq - torch.arange(nq) * 128, max=128).view(1, 1, nq, 1)
                 cols = torch.clamp(Skv - torch.arange(nk) * 128, max=128).view(1, 1, 1, nk)
                 cnt = (cnt > 0).to(torch.int32) * rows * cols
@@ -271,9 +282,13 @@ class AttentionEngine:
                 cnt = block_mask_counts(self.mask_mod, B, Hq, Sq, Skv, "cpu", 128, 128)
                 self._lists_by_shape[key] = _block_lists(cnt, 128, 128, Sq, Skv, B, Hq, device)
             return self._lists_by_shape[key]
+        if self._mask_counts is None:
+            raise ValueError("this engine needs block_mask= at call time (extern_block_mask=True)")
+        if (B, Hq, Sq, Skv) != (self.B, self.Hq, self.Sq, self.Skv):
+            raise ValueError(f"this engine's tile lists were inferred for (B, Hq, Sq, Skv) = "
+                             f"{(self.B, self.Hq, self.Sq, self.Skv)}; the call has {(B, Hq, Sq, Skv)}. "
+                             "Build the engine with named dims (meta_tensor('B', 'H', 'S', D)) for varying shapes")
         if self._lists is None or self._lists[0].device != device:
-            if self._mask_counts is None:
-                raise ValueError("this engine needs block_mask= at call time (extern_block_mask=True)")
             self._lists = _block_lists(self._mask_counts, 128, 128, Sq, Skv, B, Hq, device)
         return self._lists
 
@@ -315,7 +330,7 @@ class AttentionEngine:
             raise ValueError("inconsistent q/k/v shapes")
         return B, Sq, Hq, Skv, Hkv
 
-    def _launch_fwd(self, q, k, v, custom, block_mask=None):
+    def _launch_fwd(self, q, k, v, custom, block_mask=None, return_lists=False):
         B, Sq, Hq, Skv, Hkv = self._check_qkv(q, k, v)
         dev = q.device
         o = torch.empty(B, Sq, Hq, self.DV, dtype=self.dtype, device=dev)
@@ -335,8 +350,7 @@ class AttentionEngine:
         stream = torch.cuda.current_stream(dev).cuda_stream
         rt.check(rt.lib().ae_launch_attn_fwd(self.kernels.fwd.handle, C.byref(p), C.c_void_p(stream)),
                  "ae_launch_attn_fwd")
-        self._last_lists = lists
-        return o, finals
+        return (o, finals, lists) if return_lists else (o, finals)
 
     def decode_paged(self, q, kcache, block_table, cache_seqlens, num_split=None):
         """kv_shared engines: decode over a paged KV pool with one length per batch row, returns (out, lse)."""
@@ -344,9 +358,9 @@ class AttentionEngine:
             raise NotImplementedError("paged decode is built for kv_shared (MLA) engines")
         return self._mla.paged(q, kcache, block_table, cache_seqlens, num_split)
 
-    def _launch_bwd(self, q, k, v, o, d_o, finals, custom):
+    def _launch_bwd(self, q, k, v, o, d_o, finals, custom, lists=None):
         from .attn_bwd import launch_bwd
-        return launch_bwd(self, q, k, v, o, d_o, finals, custom)
+        return launch_bwd(self, q, k, v, o, d_o, finals, custom, lists)
 
     def __call__(self, *args, **kargs):
         if self._mla is not None:
@@ -364,9 +378,14 @@ class AttentionEngine:
             return self._decode(*args)
         block_mask = kargs.get("block_mask")
         if block_mask is not None:
-            self.block_mask = block_mask
-            self.extern_block_mask = True
             if self.mask_mode != 2:
                 raise ValueError("block_mask= needs an engine built with extern_block_mask=True")
+            self.block_mask = block_mask  # kept as the reference keeps it; the call below uses its own copy
+            self.extern_block_mask = True
         q, k, v, *custom = args
-        return _AttentionFn.apply(self, q, k, v, *custom)
+        self._call_block_mask = block_mask if block_mask is not None else (
+            self.block_mask if self.extern_block_mask else None)
+        try:
+            return _AttentionFn.apply(self, q, k, v, *custom)
+        finally:
+            self._call_block_mask = None

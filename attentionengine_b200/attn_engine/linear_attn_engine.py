@@ -4,6 +4,11 @@ Same constructor and call as the reference (attention_engine/attn_engine/linear_
 ``LinearAttentionEngine(qkv_meta, q_mod, k_mod, v_mod, decay_mod, custom_io, ...)`` and
 ``mod(q, k, v, decay, *custom)`` with [B, H, T, D] tensors, decay [B, H, T] fp32, returning O [B, H, T, DV].
 
+One keyword beyond the reference: ``o_mod(o, v, custom_io)``, applied to the scan output with the un-modded v at
+hand.  The benchmark's Mamba2 configuration has a skip connection ``o + D_skip[h] * x`` that the reference's operator
+cannot express (its harness passes D=None, benchmark/bench_utils.py:304-308); ``o_mod = lambda o, v, io: o + v *
+io.input_tensors["D"]`` with ``"D": (1, "heads")`` states it, and that form runs as one streaming kernel each way.
+
 As in the reference (core/template/tl_template/linear/linear_tl.py:1136-1144) the mods are traced once and
 run as eager PyTorch on the inputs; the scan itself (chunk cumulative sum, state recurrence, intra-chunk
 products) is one sm_100a kernel (csrc/kernels/linear_fwd.cuh); its backward is a state-recompute pass
@@ -75,9 +80,33 @@ class _RowScale(torch.autograd.Function):
         return None, gx, gs
 
 
+class _Skip(torch.autograd.Function):
+    """y = o + x * d[head] for o, x [B, H, T, D] 16-bit and d [1, H] or [H] fp32 (csrc/kernels/rowscale.cuh)."""
+
+    @staticmethod
+    def forward(ctx, eng, o, x, d):
+        o, x = o.contiguous(), x.contiguous()
+        df = d.detach().float().reshape(-1).contiguous()
+        ctx.eng, ctx.d_shape, ctx.d_dtype = eng, d.shape, d.dtype
+        ctx.save_for_backward(x, df)
+        y = torch.empty_like(o)
+        eng._rowscale("skip_fwd", x, df, g=o, y=y, rows_per_head=x.shape[2], n_heads=x.shape[1])
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        x, df = ctx.saved_tensors
+        g = g.contiguous()
+        gx = torch.empty_like(x)
+        rows = torch.empty(x.shape[:3], dtype=torch.float32, device=x.device)
+        ctx.eng._rowscale("skip_bwd", x, df, g=g, gx=gx, gs=rows, rows_per_head=x.shape[2], n_heads=x.shape[1])
+        gd = rows.sum(dim=(0, 2)).reshape(ctx.d_shape).to(ctx.d_dtype)
+        return None, g, gx, gd
+
+
 class LinearAttentionEngine:
     def __init__(self, qkv_meta, q_mod=None, k_mod=None, v_mod=None, decay_mod=None, custom_io=None, tune=False,
-                 tune_filename="tune_result", tune_bwd=False):
+                 tune_filename="tune_result", tune_bwd=False, o_mod=None):
         qm, km, vm = qkv_meta
         self.dtype = qm.dtype
         if self.dtype not in (torch.float16, torch.bfloat16):
@@ -96,6 +125,11 @@ class LinearAttentionEngine:
                 continue
             leaf = SymbolScalar(name, Var(name), shape_idx=["batch", "heads", "seq_len"] + ([] if name == "decay" else ["dim"]))
             self._traced[name] = (leaf, fn(leaf, self.custom_io))
+        self.o_mod = o_mod
+        if o_mod is not None:
+            dims = ["batch", "heads", "seq_len", "dim"]
+            self._o_leaves = (SymbolScalar("o", Var("o"), shape_idx=dims), SymbolScalar("v", Var("v"), shape_idx=dims))
+            self._o_traced = o_mod(*self._o_leaves, self.custom_io)
         self._bf16 = self.dtype == torch.bfloat16
         self._status = None
         self._bwd = None
@@ -162,19 +196,23 @@ class LinearAttentionEngine:
         dk = dk_h if HK == H else dk_h.view(B, HK, H // HK, T, DK).sum(2, dtype=torch.float32).to(self.dtype)
         return dq, dk, dv, da
 
-    def _rowscale(self, which, x, s, **out):
+    def _rowscale(self, which, x, s, rows_per_head=0, n_heads=0, **out):
+        """Launch one of the streaming kernels of rowscale.cuh: "fwd" / "bwd" (one scale per row) or "skip_fwd" /
+        "skip_bwd" (one fp32 scale per head)."""
         D = x.shape[-1]
-        s16 = s.dtype == self.dtype
+        skip = which.startswith("skip")
+        s16 = s.dtype == self.dtype and not skip
         key = (which, D, s16)
         if key not in self._rowscale_mods:
             pre = f"#define AE_BF16 {int(self._bf16)}\n#define AE_RS_D {D}\n#define AE_RS_S16 {int(s16)}\n"
             cfg = rt.KernelConfig(kind=rt.KIND_ROWSCALE, dtype=rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16, head_dim=D,
                                   head_dim_v=D, threads=256, smem_bytes=0, stages=1, mask_mode=0)
             cfg.reserved[0] = int(s16)
-            self._rowscale_mods[key] = rt.compile_module(rt.kernel_source("rowscale.cuh", prelude=pre),
-                                                         f"ae_rowscale_{which}", cfg)
+            name = f"ae_{which}" if skip else f"ae_rowscale_{which}"
+            self._rowscale_mods[key] = rt.compile_module(rt.kernel_source("rowscale.cuh", prelude=pre), name, cfg)
         p = rt.RowScaleParams()
         p.x, p.s, p.n_rows = x.data_ptr(), s.data_ptr(), x.numel() // D
+        p.rows_per_head, p.n_heads = rows_per_head, n_heads
         for k_, t in out.items():
             setattr(p, k_, t.data_ptr())
         stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
@@ -209,6 +247,33 @@ class LinearAttentionEngine:
             env[id(sym)] = _align(t, tuple(sym.shape_idx), x.dim())
         y = evaluate(out, env)
         return y if name == "decay" else y.to(x.dtype)
+
+    def _skip_operand(self, custom):
+        """The custom tensor d when the traced o_mod is exactly ``o + v * d`` with d indexed by heads only (fp32,
+        [1, H] or [H]); None otherwise (the mod then runs as eager PyTorch)."""
+        o_leaf, v_leaf = self._o_leaves
+        out = self._o_traced
+        if out.code.type != "Add" or len(out.prev) != 2:
+            return None
+        mul = out.prev[1] if out.prev[0] is o_leaf else out.prev[0] if out.prev[1] is o_leaf else None
+        if mul is None or mul.code.type != "Mul" or len(mul.prev) != 2:
+            return None
+        other = mul.prev[1] if mul.prev[0] is v_leaf else mul.prev[0] if mul.prev[1] is v_leaf else None
+        for (cname, sym), t in zip(self.custom_io.input_tensors.items(), custom):
+            if sym is other:
+                names = tuple(str(n) for n in sym.shape_idx if str(n) != "1")
+                if names == ("heads",) and t.numel() == self.H and t.dtype == torch.float32 and self.DV in (64, 128, 256):
+                    return t
+        return None
+
+    def _apply_o_mod(self, o, v, custom):
+        d = self._skip_operand(custom)
+        if d is not None and v.dtype == self.dtype:
+            return _Skip.apply(self, o, v, d)
+        env = {id(self._o_leaves[0]): o, id(self._o_leaves[1]): v}
+        for (cname, sym), t in zip(self.custom_io.input_tensors.items(), custom):
+            env[id(sym)] = _align(t, tuple(sym.shape_idx), o.dim())
+        return evaluate(self._o_traced, env).to(o.dtype)
 
     def _launch(self, q, k, v, a):
         B, HQ, T, DK = q.shape
@@ -271,4 +336,5 @@ class LinearAttentionEngine:
         qm = self._apply_mod("q", q, custom)
         km = self._apply_mod("k", k, custom)
         vm = self._apply_mod("v", v, custom)
-        return self._scan(qm, km, vm, a)
+        o = self._scan(qm, km, vm, a)
+        return o if self.o_mod is None else self._apply_o_mod(o, v, custom)

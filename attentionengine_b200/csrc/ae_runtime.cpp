@@ -366,11 +366,10 @@ int ae_launch_probe(void* module, const void* a, const void* b, const void* p, f
   if (rc) return rc;
   args.p = p;
   args.d = d_out;
-  args.mode = mode & 0xffff;
+  if (mode != 0 && mode != 1) return AE_ERR_INVALID;
+  args.mode = mode;
   args.status = status;
-  // bits 16.. of `mode`: number of CTAs (0 = one); only the rate micro-benchmarks use more than one
-  const unsigned grid = (unsigned)(mode >> 16) ? (unsigned)(mode >> 16) : 1u;
-  return launch(m, grid, 1, 1, &args, stream);
+  return launch(m, 1, 1, 1, &args, stream);
 }
 
 int ae_launch_attn_fwd(void* module, const AeAttnParams* p, void* stream) {
@@ -761,8 +760,13 @@ int ae_launch_rowscale(void* module, const AeRowScaleParams* p, void* stream) {
     set_error("module kind does not match the entry point");
     return AE_ERR_UNSUPPORTED;
   }
-  const bool bwd = m->kernel == "ae_rowscale_bwd";
+  const bool skip = m->kernel == "ae_skip_fwd" || m->kernel == "ae_skip_bwd";
+  const bool bwd = m->kernel == "ae_rowscale_bwd" || m->kernel == "ae_skip_bwd";
   if (bwd ? (!p->g || !p->gx || !p->gs) : !p->y) return AE_ERR_INVALID;
+  if (skip && (!p->g || p->rows_per_head <= 0 || p->n_heads <= 0)) {
+    set_error("skip kernels need g, rows_per_head > 0 and n_heads > 0");
+    return AE_ERR_INVALID;
+  }
   const void* ptrs[5] = {p->x, p->y, p->g, p->gx, nullptr};
   for (const void* q : ptrs)
     if (q && (reinterpret_cast<uintptr_t>(q) & 15)) {
@@ -776,6 +780,8 @@ int ae_launch_rowscale(void* module, const AeRowScaleParams* p, void* stream) {
   memset(&a, 0, sizeof a);
   a.x = p->x; a.s = p->s; a.y = p->y; a.g = p->g; a.gx = p->gx; a.gs = p->gs;
   a.n_rows = p->n_rows;
+  a.rows_per_head = skip ? p->rows_per_head : 1;
+  a.n_heads = skip ? p->n_heads : 1;
   // 16 bytes per lane, 256 threads per CTA, up to 16 CTAs per SM's worth of blocks; the kernels stride over the rest
   const int64_t lanes = p->n_rows * (m->cfg.head_dim / 8);
   int64_t blocks = (lanes + 255) / 256;

@@ -68,8 +68,14 @@ int ae_launch_attn_bwd_static_scratch(void* prep_module, void* dq_module, void* 
     ae_internal_set_error("null module or parameter block");
     return AE_ERR_INVALID;
   }
+  if (p->B <= 0 || p->Hq <= 0 || p->Sq <= 0) {
+    char msg[160];
+    snprintf(msg, sizeof msg, "B, Hq and Sq must be positive (got %d, %d, %d)", p->B, p->Hq, p->Sq);
+    ae_internal_set_error(msg);
+    return AE_ERR_INVALID;
+  }
   const long long rows = (long long)p->B * p->Hq * p->Sq;
-  if (p->B <= 0 || p->Hq <= 0 || p->Sq <= 0 || rows > AE_STATIC_DELTA_MAX_ROWS) {
+  if (rows > AE_STATIC_DELTA_MAX_ROWS) {
     char msg[256];
     snprintf(msg, sizeof msg,
              "B * Hq * Sq = %lld rows exceeds the built-in scratch of %lld rows; use ae_launch_attn_bwd_prep/_dq/_dkv "

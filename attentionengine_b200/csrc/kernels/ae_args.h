@@ -150,6 +150,9 @@ struct AeRowScaleArgs {
   void* gx;       // backward: g * s
   void* gs;       // backward: sum_d g * x, in the type of s
   i64 n_rows;
+  // per-head skip kernels (ae_skip_fwd / ae_skip_bwd): s is [n_heads] fp32, a row's head is (row / rows_per_head) % n_heads
+  i64 rows_per_head;
+  int n_heads;
 };
 
 // ---- UMMA / TMA probe kernels (bring-up checks, kernel ae_probe) -------------------

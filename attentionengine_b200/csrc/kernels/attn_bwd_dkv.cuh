@@ -130,11 +130,20 @@ ae_attn_bwd_dkv(const __grid_constant__ AeAttnBwdArgs args) {
     while (walk.g < G) {
       const int hq = hk * G + walk.g;
       const i64 base = ((i64)b * args.Hq + hq) * args.n_kt + kt;
-      const int n = args.blkT_cnt[base];
+      int n = args.blkT_cnt[base];
+      if (n < 0 || n > args.n_qt) {  // a count that would walk past the list: empty walk, status 0x400
+        if (args.status) atomicCAS(args.status, 0u, 0x400u);
+        n = 0;
+      }
       if (walk.e < n) {
         const int ent = args.blkT_idx[base * args.n_qt + walk.e];
         st.hq = hq;
-        st.q0 = (ent & 0x3fffffff) * 128 + walk.sub * AE_BWD_BN;
+        int qt = ent & 0x3fffffff;
+        if (qt >= args.n_qt) {  // an entry outside the tile grid: keep every access in range, report status 0x400
+          if (args.status) atomicCAS(args.status, 0u, 0x400u);
+          qt = args.n_qt - 1;
+        }
+        st.q0 = qt * 128 + walk.sub * AE_BWD_BN;
         st.partial = ((u32)ent >> 30) & 1u;
         if (++walk.sub == AE_NSUBQ) {
           walk.sub = 0;

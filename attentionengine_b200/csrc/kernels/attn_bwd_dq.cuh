@@ -90,7 +90,12 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
   n_steps = (q0 + AE_BM + AE_BWD_BN - 1) / AE_BWD_BN;
   if (n_steps > n_kt_bn) n_steps = n_kt_bn;
 #elif AE_MASK_MODE == 2
-  const int n_list = args.blk_cnt[((i64)b * args.Hq + hq) * args.n_qt + qt];
+  // a count outside [0, n_kt] would walk past the list: such a tile gets an empty walk and status 0x400, as in the forward
+  int n_list = args.blk_cnt[((i64)b * args.Hq + hq) * args.n_qt + qt];
+  if (n_list < 0 || n_list > args.n_kt) {
+    if (threadIdx.x == 0 && args.status) atomicCAS(args.status, 0u, 0x400u);
+    n_list = 0;
+  }
   const int* list = args.blk_idx + (((i64)b * args.Hq + hq) * args.n_qt + qt) * (i64)args.n_kt;
   n_steps = n_list * AE_NSUB;
 #else
@@ -112,7 +117,12 @@ ae_attn_bwd_dq(const __grid_constant__ AeAttnBwdArgs args) {
     if (s >= n_steps) s -= n_steps;
 #if AE_MASK_MODE == 2
     const int e = list[s / AE_NSUB];
-    kv0 = (e & 0x3fffffff) * 128 + (s % AE_NSUB) * AE_BWD_BN;
+    int kt = e & 0x3fffffff;
+    if (kt >= args.n_kt) {  // an entry outside the tile grid: keep every access in range, report status 0x400
+      if (args.status) atomicCAS(args.status, 0u, 0x400u);
+      kt = args.n_kt - 1;
+    }
+    kv0 = kt * 128 + (s % AE_NSUB) * AE_BWD_BN;
     partial = ((u32)e >> 30) & 1u;
 #else
     kv0 = s * AE_BWD_BN;

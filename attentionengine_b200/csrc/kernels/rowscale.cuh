@@ -9,6 +9,13 @@
 // A row is shared by AE_RS_D / 8 lanes (16 bytes per lane); the loop bounds are warp-uniform so that the shuffles of the
 // row reduction are always executed by all 32 lanes.
 // Expects AE_BF16, AE_RS_D (64, 128 or 256), AE_RS_S16.
+//
+// The same file holds the per-head skip connection of the Mamba2 block (o += D_skip[h] * x, the benchmark's config 4;
+// the reference's harness passes D=None, benchmark/bench_utils.py:304-308), for rows ordered (batch, head, step):
+//   forward   y[r, :] = o[r, :] + x[r, :] * d[head(r)]                      (ae_skip_fwd:  o arrives in `g`)
+//   backward  gx[r, :] = g[r, :] * d[head(r)],  gs[r] = sum_d g[r, d] * x[r, d]   (ae_skip_bwd: gs is fp32; the caller
+//             sums it over batch and steps to get the gradient of d)
+// with head(r) = (r / rows_per_head) % n_heads and d [n_heads] fp32 in `s`.
 
 #define AE_RS_TPR (AE_RS_D / 8)        // lanes per row
 #define AE_RS_RPW (32 / AE_RS_TPR)     // rows per warp and iteration
@@ -77,5 +84,61 @@ extern "C" __global__ void __launch_bounds__(256) ae_rowscale_bwd(const AeRowSca
       ((float*)a.gs)[row] = dot;
 #endif
     }
+  }
+}
+
+AE_DEVICE float ae_rs_head_scale(const AeRowScaleArgs& a, i64 row) {
+  return ((const float*)a.s)[(row / a.rows_per_head) % a.n_heads];
+}
+
+extern "C" __global__ void __launch_bounds__(256) ae_skip_fwd(const AeRowScaleArgs a) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp0 = ((i64)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const i64 n_warps = ((i64)gridDim.x * 256) >> 5;
+  for (i64 base = warp0 * AE_RS_RPW; base < a.n_rows; base += n_warps * AE_RS_RPW) {
+    const i64 row = base + lane / AE_RS_TPR;
+    if (row < a.n_rows) {
+      const i64 off = row * AE_RS_D + (lane % AE_RS_TPR) * 8;
+      const uint4 x = *(const uint4*)((const u16*)a.x + off);
+      const uint4 o = *(const uint4*)((const u16*)a.g + off);
+      const float sc = ae_rs_head_scale(a, row);
+      const u32 xw[4] = {x.x, x.y, x.z, x.w}, ow[4] = {o.x, o.y, o.z, o.w};
+      u32 yw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        yw[i] = pack2<AE_BF16>(fmaf(unpack_lo<AE_BF16>(xw[i]), sc, unpack_lo<AE_BF16>(ow[i])),
+                               fmaf(unpack_hi<AE_BF16>(xw[i]), sc, unpack_hi<AE_BF16>(ow[i])));
+      *(uint4*)((u16*)a.y + off) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
+    }
+  }
+}
+
+extern "C" __global__ void __launch_bounds__(256) ae_skip_bwd(const AeRowScaleArgs a) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp0 = ((i64)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const i64 n_warps = ((i64)gridDim.x * 256) >> 5;
+  for (i64 base = warp0 * AE_RS_RPW; base < a.n_rows; base += n_warps * AE_RS_RPW) {
+    const i64 row = base + lane / AE_RS_TPR;
+    const bool valid = row < a.n_rows;
+    float dot = 0.f;
+    if (valid) {
+      const i64 off = row * AE_RS_D + (lane % AE_RS_TPR) * 8;
+      const uint4 g = *(const uint4*)((const u16*)a.g + off);
+      const uint4 x = *(const uint4*)((const u16*)a.x + off);
+      const float sc = ae_rs_head_scale(a, row);
+      const u32 gw[4] = {g.x, g.y, g.z, g.w}, xw[4] = {x.x, x.y, x.z, x.w};
+      u32 ow[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float g0 = unpack_lo<AE_BF16>(gw[i]), g1 = unpack_hi<AE_BF16>(gw[i]);
+        dot = fmaf(g0, unpack_lo<AE_BF16>(xw[i]), dot);
+        dot = fmaf(g1, unpack_hi<AE_BF16>(xw[i]), dot);
+        ow[i] = pack2<AE_BF16>(g0 * sc, g1 * sc);
+      }
+      *(uint4*)((u16*)a.gx + off) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+#pragma unroll
+    for (int o = AE_RS_TPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (valid && (lane % AE_RS_TPR) == 0) ((float*)a.gs)[row] = dot;
   }
 }

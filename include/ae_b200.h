@@ -14,7 +14,8 @@
  *  - every function returns 0 on success or an AE_ERR_* code (ae_strerror() gives
  *    text); nothing here calls exit() or traps;
  *  - `stream` is a cudaStream_t / CUstream passed as void*;
- *  - all tensors are owned by the caller; the library allocates no device memory;
+ *  - all tensors are owned by the caller; the library allocates no device memory (the one exception is the
+ *    fixed 32 MiB array behind ae_launch_attn_bwd_static_scratch, which is part of the library image);
  *  - runtime tensors are [B, S, H, D] with the last dimension contiguous; strides
  *    are in elements, ordered (batch, seq, head);
  *  - `status` is an optional device word the kernels write when a bounded wait gives
@@ -169,10 +170,15 @@ int ae_launch_attn_bwd_dkv(void* module, const AeAttnBwdParams* p, void* stream)
  * library until the process exits).  `p->delta` is ignored.
  *  - B * Hq * Sq above AE_STATIC_SCRATCH_MAX_ROWS is refused with AE_ERR_INVALID
  *    (ae_last_error() names both numbers).
- *  - Allocates nothing: no cudaMalloc / cudaFree, no allocating library call.
- *  - The first call on a device resolves the array's device address
- *    (cudaGetSymbolAddress) with that device current; make that first call outside any
- *    stream capture.
+ *  - Calls no cudaMalloc / cudaFree and no allocating library routine.  The array is part of
+ *    the library image all the same: with CUDA's default lazy module loading the FIRST call
+ *    on a device (cudaGetSymbolAddress, made with that device current) loads that image,
+ *    which reserves the 32 MiB on that GPU, may synchronise the device and can fail with
+ *    AE_ERR_CUDA on a GPU with no memory left.  Make that first call during start-up, as a
+ *    warm-up, and outside any stream capture; later calls only launch kernels.
+ *  - The target device must be current for every call (as for every entry point here).
+ *  - The pre-pass always runs, so all three modules must be given, also for an OnlineFunc
+ *    whose backward does not read delta.
  *  - All calls on a device share the one array.  It keeps the previous call's contents;
  *    every word a call reads is first rewritten by that call's pre-pass, so nothing needs
  *    clearing, but two calls that overlap on the GPU (different streams) race on it. */
@@ -273,7 +279,12 @@ int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream);
  * attn_script/mamba2_ngroup1.py:31-33).  x, y, g, gx: [n_rows, head_dim] 16-bit contiguous (head_dim of the
  * module: 64, 128 or 256); s, gs: one value per row, fp32 or (module config reserved[0] = 1) the 16-bit type.
  * The module's kernel name selects the direction: "ae_rowscale_fwd" writes y = x * s; "ae_rowscale_bwd"
- * writes gx = g * s and gs = sum_d g * x. */
+ * writes gx = g * s and gs = sum_d g * x.
+ * Two more kernels of the same module kind add the per-head skip connection of the Mamba2 block (benchmark config 4:
+ * o += D_skip[h] * x; no counterpart in the reference, whose harness passes D=None, benchmark/bench_utils.py:304-308),
+ * for rows ordered (batch, head, step): s is then [n_heads] fp32 and a row's head is (row / rows_per_head) % n_heads.
+ * "ae_skip_fwd" writes y = g + x * s[head] (g carries the scan output); "ae_skip_bwd" writes gx = g * s[head] and
+ * gs[row] = sum_d g * x in fp32 (summed over batch and steps by the caller for the gradient of s). */
 typedef struct AeRowScaleParams {
   const void* x;
   const void* s;
@@ -282,6 +293,8 @@ typedef struct AeRowScaleParams {
   void* gx;
   void* gs;
   int64_t n_rows;
+  int64_t rows_per_head; /* skip kernels only */
+  int32_t n_heads;       /* skip kernels only */
 } AeRowScaleParams;
 
 int ae_launch_rowscale(void* module, const AeRowScaleParams* p, void* stream);
@@ -314,8 +327,6 @@ int ae_launch_linear_bwd(void* module, const AeLinearBwdParams* p, void* stream)
 /* ---- bring-up probe (tests only): one 128x128x128 tcgen05 GEMM -------------------
  * mode 0: d = a * b^T (a, b [128,128] 16-bit row-major);
  * mode 1: d = p * b   (p, b [128,128] 16-bit row-major). d is [128,128] fp32.
- * The rate micro-benchmarks (mma_rate.cuh, tma_rate.cuh) are launched through the same entry: the low 16 bits of
- * `mode` are their repeat count, bits 16.. the number of CTAs (0 = one).
  * No counterpart in the reference. */
 int ae_launch_probe(void* module, const void* a, const void* b, const void* p, float* d, int mode, uint32_t* status,
                     void* stream);

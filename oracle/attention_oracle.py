@@ -4,8 +4,9 @@ inputs, gradients by autograd.  TEST INFRASTRUCTURE ONLY (see oracle/__init__.py
 Each function restates the reference's own checker for that variant; citations are paths inside
 microsoft/AttentionEngine.  Pinning: ``tests/golden/*.npz`` hold outputs of the reference's own
 reference functions executed from its source tree by ``tests/golden/make_golden.py``;
-``tests/test_oracle_golden.py`` compares this file against them.  Variants whose reference checker
-is a third-party GPU library (sigmoid: flash_sigmoid; SSD: mamba_ssm) are marked "parity unpinned".
+``tests/test_oracle_golden.py`` compares this file against them.  Sigmoid attention, whose checker in the
+reference is the third-party flash_sigmoid package, is pinned through the reference's own score_mod instead:
+``sigmoid.npz`` holds that score_mod and its symbolic derivative evaluated by the reference's IR front end.
 """
 from __future__ import annotations
 
@@ -57,8 +58,9 @@ def relu_attention(q, k, v, scale: float | None = None, post_scale: float = 1.0,
 
 def sigmoid_attention(q, k, v, scale: float | None = None, bias: float = 0.0, causal: bool = False):
     """P = sigmoid(q k^T * scale + bias) written as (tanh(x / 2) + 1) / 2 as in
-    attn_script/sigmoidattn.py:14-18; no row normalisation.  Parity unpinned: the reference checks this
-    variant against the third-party flash_sigmoid package only (bench_utils.py:736-744)."""
+    attn_script/sigmoidattn.py:14-18; no row normalisation.  Pinned by tests/golden/sigmoid.npz (the reference's
+    score_mod and its derivative evaluated by the reference's IR); the reference itself checks this variant against
+    the third-party flash_sigmoid package only (bench_utils.py:736-744)."""
     q, k, v = q.float(), k.float(), v.float()
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     g = q.shape[2] // k.shape[2]

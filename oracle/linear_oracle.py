@@ -8,7 +8,10 @@ The step-by-step recurrence the reference's kernels implement in chunked form
 Parity: the reference checks this path only against third-party GPU kernels (mamba_ssm for Mamba2, absent here;
 flash-linear-attention for simple_gla, bench_utils.py:552-566).  ``tests/golden/linear_scan.npz`` holds the output
 of flash-linear-attention's own naive recurrent form (fla.ops.simple_gla.naive) run on CPU, which pins the
-recurrence; the Mamba2 mapping on top of it (a = dt * A, v = x * dt, D_skip) is **parity unpinned**.
+recurrence; ``tests/golden/mamba2.npz`` pins the Mamba2 mapping on top of it: the reference's own ``decay_mod`` /
+``v_mod`` (attn_script/mamba2_ngroup1.py:26-33) evaluated by the reference's IR front end and fed to that recurrence.
+The D_skip term has no counterpart in the reference (its harness passes D=None, bench_utils.py:304-308); it is the
+benchmark configuration's ``o += D_skip[h] * x``.
 """
 from __future__ import annotations
 

@@ -16,6 +16,10 @@ mask front end imported from ``<ref>/attention_engine``:
 * block masks        create_block_mask, is_causal_mask, is_less_causal_mask   core/transform/core.py
 * symbolic autodiff  SymbolScalar.backward on the example score_mods          core/transform/core.py
 * linear scan        fla.ops.simple_gla.naive (the library the reference checks simple_gla against, bench_utils.py:552-566)
+* sigmoid attention  score_mod of attn_script/sigmoidattn.py traced and differentiated by the reference's IR, inside
+                     the un-normalised P V composition its OnlineIdentity defines
+* Mamba2 mapping     decay_mod / v_mod of attn_script/mamba2_ngroup1.py traced by the reference's IR, fed to fla's naive
+                     recurrence (q = C, k = B)
 
 Inputs are seeded; inputs and outputs are stored together so the fixtures do not depend on the
 random-number generator of the machine that reads them.
@@ -68,6 +72,16 @@ def grads(fn, inputs, d_out):
 
 def np16(t):
     return t.detach().to(torch.float16).numpy() if t.dtype in (torch.float16,) else t.detach().float().numpy()
+
+
+def script_defs(ref_root: str, name: str) -> dict:
+    """The definitions part of one of the reference's example programs (everything above its ``eval()`` /
+    ``__main__`` section), executed against the reference's own ``attn_engine`` / ``core`` packages."""
+    src = open(os.path.join(ref_root, "attn_script", name)).read()
+    cut = min(i for i in (src.find("\ndef eval("), src.find("\nif __name__"), len(src)) if i >= 0)
+    env = {"__name__": "attn_script_defs"}
+    exec(compile(src[:cut], name, "exec"), env)
+    return env
 
 
 def main(ref_root: str):
@@ -186,6 +200,49 @@ def main(ref_root: str):
         out[f"{nm}.y"] = torch.as_tensor(evaluate(y, env)).expand_as(x).numpy()
         out[f"{nm}.dx"] = torch.as_tensor(evaluate(s.grad, env)).expand_as(x).numpy()
     np.savez_compressed(os.path.join(HERE, "autodiff.npz"), **out)
+
+    # ---------------- sigmoid attention: the reference's score_mod and its symbolic derivative ----------------------
+    defs = script_defs(ref_root, "sigmoidattn.py")
+    B, H, S, D = 1, 2, 256, 64
+    g = torch.Generator().manual_seed(6)
+    q, k, v, d_o = (randn(g, B, S, H, D) for _ in range(4))
+    q = (q.float() * D ** -0.5).to(torch.float16)   # the script's score_mod has no scale of its own
+    bias = -math.log(S)
+    s_sym = rcore.SymbolicArray("scores", rcore.Var("scores"), shape_idx=["block_M", "block_N"])
+    cio = defs["custom_fwd_inputs"]
+    y = defs["score_mod"](s_sym, cio, None, None, None, None)
+    d_sym = rcore.SymbolScalar("d", rcore.Var("d"), shape_idx=["block_M", "block_N"])
+    y.backward(d_sym)
+    sc = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float())
+    dp = torch.einsum("bqhd,bkhd->bhqk", d_o.float(), v.float())
+    env = {id(s_sym): sc, id(cio.input_tensors["softmax_bias"]): torch.tensor(bias), id(d_sym): dp}
+    p = torch.as_tensor(evaluate(y, env))
+    ds = torch.as_tensor(evaluate(s_sym.grad, env))
+    np.savez_compressed(os.path.join(HERE, "sigmoid.npz"), q=np16(q), k=np16(k), v=np16(v), do=np16(d_o),
+                        bias=np.array(bias), o=torch.einsum("bhqk,bkhd->bqhd", p, v.float()).numpy(),
+                        dq=torch.einsum("bhqk,bkhd->bqhd", ds, k.float()).numpy(),
+                        dk=torch.einsum("bhqk,bqhd->bkhd", ds, q.float()).numpy(),
+                        dv=torch.einsum("bhqk,bqhd->bkhd", p, d_o.float()).numpy())
+
+    # ---------------- Mamba2 operator mapping: the reference's decay_mod / v_mod in front of fla's recurrence --------
+    defs = script_defs(ref_root, "mamba2_ngroup1.py")
+    B, H, T, N, P = 1, 3, 320, 128, 64
+    g = torch.Generator().manual_seed(7)
+    x = randn(g, B, H, T, P, dtype=torch.bfloat16)
+    Bm, Cm = randn(g, B, 1, T, N, dtype=torch.bfloat16), randn(g, B, 1, T, N, dtype=torch.bfloat16)
+    dt = F.softplus(torch.randn(B, H, T, generator=g) - 4.0)
+    A = -torch.exp(torch.rand(H, generator=g) * math.log(16.0))
+    cio = rcore.CustomIO({"A": (1, "heads"), "dt": ("batch", "heads", "seq_len")})
+    dec_sym = rcore.SymbolicArray("decay", rcore.Var("decay"), shape_idx=["B", "H", "T"])
+    v_sym = rcore.SymbolicArray("v", rcore.Var("v"), shape_idx=["B", "H", "T", "D"])
+    a = torch.as_tensor(evaluate(defs["decay_mod"](dec_sym, cio),
+                                 {id(dec_sym): dt, id(cio.input_tensors["A"]): A.view(1, H, 1)}))
+    vm = torch.as_tensor(evaluate(defs["v_mod"](v_sym, cio),
+                                  {id(v_sym): x.float(), id(cio.input_tensors["dt"]): dt[..., None]}))
+    o, _ = naive_recurrent_simple_gla(Cm.float().expand(B, H, T, N).transpose(1, 2), Bm.float().expand(B, H, T, N).transpose(1, 2),
+                                      vm.transpose(1, 2), a.transpose(1, 2), scale=1.0)
+    np.savez_compressed(os.path.join(HERE, "mamba2.npz"), x=x.float().numpy(), dt=dt.numpy(), A=A.numpy(),
+                        Bm=Bm.float().numpy(), Cm=Cm.float().numpy(), o=o.transpose(1, 2).float().numpy())
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 

@@ -1,7 +1,7 @@
 """Parity of the CUDA attention path (through AttentionEngine -> C ABI -> sm_100a kernels) against the
-CPU oracle and the golden vectors.  Tolerance (stated by the benchmark spec): max-abs <= 2e-2 and
-rel-L2 <= 1e-3 for fp16 outputs and gradients.  For bf16 the oracle is rounded to bf16 first, because
-bf16 output rounding alone is a rel-L2 of about 1.7e-3, and rel-L2 <= 4e-3 is asked of the difference."""
+CPU oracle and the golden vectors.  Acceptance rule (tests/parity.py): max-abs <= 2e-2 and rel-L2 <= 1e-3 for fp16
+outputs and gradients, as the benchmark specification states; bf16 results are held to a multiple of the bf16
+rounding floor measured on the tensor itself."""
 import math
 import os
 
@@ -12,23 +12,21 @@ import torch
 from oracle import attention_oracle as orc
 
 import helpers
+import parity
 from attentionengine_b200 import AttentionEngine, CustomIO
 
 pytestmark = pytest.mark.gpu
 
-MAX_ABS, REL_L2 = 2e-2, 1e-3
+MAX_ABS, REL_L2 = parity.MAX_ABS, parity.REL_L2
 
 
-def _check(name, got, ref, dtype, unnormalised=False):
-    """``unnormalised``: outputs that are plain sums over the sequence (linear attention) grow like sqrt(T);
-    the absolute bound is then taken relative to the largest reference magnitude."""
-    mag = max(1.0, ref.abs().max().item()) if unnormalised else 1.0
-    if dtype == torch.bfloat16:
-        mx, rel = orc.error_stats(got, ref.to(torch.bfloat16))
-        assert mx <= 4 * MAX_ABS * mag and rel <= 4e-3, f"{name}: max-abs {mx:.3e}, rel-L2 {rel:.3e} (bf16 protocol)"
-    else:
-        mx, rel = orc.error_stats(got, ref)
-        assert mx <= MAX_ABS * mag and rel <= REL_L2, f"{name}: max-abs {mx:.3e}, rel-L2 {rel:.3e}"
+def _check(name, got, ref, dtype, unnormalised=False, stages=None):
+    """bf16 rounding stages of the attention kernels: O and dV = (P rounded) x operand, stored -> 2; dQ and dK =
+    (dS rounded) x operand, stored, with dS built from delta = rowsum(O dO) of the rounded O -> 3.  The linear-attention
+    results (``unnormalised``) pass through P / dS, the carried state, the rescaled values and the store -> 4."""
+    if stages is None:
+        stages = 4 if unnormalised else (3 if name.split(".")[-1].split()[-1] in ("dq", "dk") else 2)
+    parity.check(name, got, ref, dtype, stages=stages, unnormalised=unnormalised)
 
 
 def _run(eng, q, k, v, d_o, custom=()):
@@ -392,9 +390,9 @@ def test_mamba2_ssd_forward_against_oracle(B, H, T, DV):
 @pytest.mark.parametrize("B,H,T", [(1, 2, 256), (2, 4, 512), (1, 3, 200)])
 def test_mamba2_ssd_backward_against_oracle(B, H, T):
     """Gradients of the Mamba2 mapping (q = C, k = B, v = x * dt, a = dt * A, one q/k head shared by all heads)
-    against fp64 autograd through the step-by-step recurrence.  bf16 protocol: the tensor-core operands
-    (P, dS, v', the carried states) are rounded to bf16, so rel-L2 <= 1e-2 is asked of the tensor gradients
-    (measured about 3e-3 to 6e-3) and 5e-2 of dA, a sum of B * T cancelling terms per head (measured 1e-2 to 2e-2)."""
+    against fp64 autograd through the step-by-step recurrence.  The tensor gradients follow the bf16 rule of
+    tests/parity.py with four rounding stages (P / dS, v', the carried states, the stored result); the gradients of dt
+    are asked rel-L2 <= 2e-2 and dA, a sum of B * T cancelling terms per head, 5e-2."""
     from oracle.linear_oracle import linear_scan
     dt_ = torch.bfloat16
     x, dt, A, Bm, Cm = helpers.mamba2_inputs(B, H, T, 128, 64, dt_, seed=T)
@@ -412,9 +410,10 @@ def test_mamba2_ssd_backward_against_oracle(B, H, T):
     oref.backward(d_o.double())
     names = ("dC", "dB", "dx", "d(dt) via decay", "dA", "d(dt) via v_mod")
     for name, got, ref in zip(names, [t.grad for t in leaves] + [dtb.grad], [C2.grad, B2.grad, x2.grad, dt2.grad, A2.grad, dtb2.grad]):
-        mx, rel = orc.error_stats(got.float().cpu(), ref.float())
-        lim = 5e-2 if name == "dA" else 1e-2
-        assert rel <= lim, f"{name}: rel-L2 {rel:.3e} (max-abs {mx:.3e})"
+        if name in ("dC", "dB", "dx"):
+            parity.check(f"ssd T={T} {name}", got, ref, dt_, stages=4, unnormalised=True)
+        else:  # fp32 sums of many cancelling bf16 terms (per step over 64 dims, per head over B * T steps)
+            parity.check(f"ssd T={T} {name}", got, ref, dt_, rel_limit=5e-2 if name == "dA" else 2e-2)
 
 
 @pytest.mark.parametrize("n_split", [None, 1, 3])
@@ -503,8 +502,10 @@ def test_linear_variants_with_large_heads(variant):
     _check("o (no grad, 128-wide value blocks)", o_ng.cpu(), oref.detach().float(), dt_, unnormalised=True)
     _check("o", o.detach().cpu(), oref.detach().float(), dt_, unnormalised=True)
     for name, got, ref in zip(("dq", "dk", "dv", "d(decay)"), [t.grad for t in leaves], [q2.grad, k2.grad, v2.grad, g2.grad]):
-        mx, rel = orc.error_stats(got.float().cpu(), ref.float())
-        assert rel <= (5e-2 if name == "d(decay)" else 1e-2), f"{name}: rel-L2 {rel:.3e} (max-abs {mx:.3e})"
+        if name == "d(decay)":
+            parity.check(f"{variant} {name}", got, ref, dt_, rel_limit=5e-2)
+        else:  # two key blocks are summed in fp32 and stored once more -> one stage on top of the scan's four
+            parity.check(f"{variant} {name}", got, ref, dt_, stages=5, unnormalised=True)
 
 
 @pytest.mark.parametrize("D", [64, 128])
@@ -623,3 +624,34 @@ def test_retention_parallel_with_tile_shaped_custom_input(S):
 
 
 
+
+def test_backward_uses_the_block_mask_of_its_own_forward():
+    """Two forward calls with different call-time block masks, then both backward calls: each gradient must follow the
+    mask its own forward walked, not the one the engine saw last."""
+    B, H, S, D, dtype = 1, 2, 512, 64, torch.float16
+    n = S // 128
+    scale = 1.0 / math.sqrt(D)
+    eng = AttentionEngine(helpers.metas(B, H, H, S, D, D, dtype), CustomIO({}),
+                          score_mod=lambda s, c, b, h, q, kv: s * scale, mask_mod=None,
+                          online_func=helpers.OnlineSoftmax(), extern_block_mask=True)
+    g = torch.Generator().manual_seed(8)
+    masks = [torch.eye(n, dtype=torch.bool).expand(B, H, n, n) | (torch.rand(B, H, n, n, generator=g) < p) for p in (0.3, 0.7)]
+    q, k, v, d_o = helpers.seeded_qkv(B, H, H, S, D, D, dtype, seed=33)
+    runs = []
+    for bm in masks:
+        leaves = [t.cuda().requires_grad_() for t in (q, k, v)]
+        runs.append((leaves, eng(*leaves, block_mask=bm.to(torch.int8).cuda())))
+    for leaves, o in runs:          # backward calls only after both forwards
+        o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    eng.check_status()
+    for bm, (leaves, o) in zip(masks, runs):
+        dense = bm.repeat_interleave(128, 2).repeat_interleave(128, 3)
+
+        def ref(a, b_, c):
+            s_ = (torch.einsum("bqhd,bkhd->bhqk", a, b_) * scale).masked_fill(~dense, float("-inf"))
+            return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s_, -1), c)
+
+        ro, grads = orc.fwd_bwd(ref, (q, k, v), d_o)
+        for name, got, r in zip(("o", "dq", "dk", "dv"), (o, *[t.grad for t in leaves]), (ro, *grads)):
+            _check(name, got.detach().cpu(), r, dtype)

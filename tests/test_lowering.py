@@ -140,3 +140,27 @@ def test_reference_import_names():
     from core import CustomIO as C2, SymbolicArray, SymbolScalar, SymbolicTensor, Var, create_block_mask  # noqa: F401
     from core.utils import meta_tensor as m2
     assert A2 is AttentionEngine and m2 is meta_tensor
+
+
+def test_block_mask_of_the_wrong_shape_is_refused_on_the_host():
+    """The kernels index the tile lists with the runtime tile grid: a call-time block_mask with other dimensions, or a
+    non-dynamic engine called at a shape other than the one its lists were inferred for, must not reach a launch."""
+    B, H, S, D = 1, 2, 640, 64
+    eng = AttentionEngine(helpers.metas(B, H, H, S, D, D, torch.float16), CustomIO({}),
+                          score_mod=lambda s, c, b, h, q, kv: s * 0.125, mask_mod=None,
+                          online_func=helpers.OnlineSoftmax(), extern_block_mask=True)
+    ok = torch.ones(B, H, 5, 5, dtype=torch.int8)
+    lists = eng._ensure_lists("cpu", ok, B, H, S, S)
+    assert lists[0].shape == (B, H, 5) and lists[1].shape == (B, H, 5, 5)
+    for bad in (torch.ones(B, H, 4, 5, dtype=torch.int8), torch.ones(B, H, 5, 6, dtype=torch.int8),
+                torch.ones(3, H, 5, 5, dtype=torch.int8), torch.ones(H, 5, 5, dtype=torch.int8)):
+        with pytest.raises(ValueError, match="block_mask has shape"):
+            eng._ensure_lists("cpu", bad, B, H, S, S)
+    win = AttentionEngine(helpers.metas(B, H, H, 1024, D, D, torch.float16), CustomIO({}),
+                          score_mod=lambda s, c, b, h, q, kv: s * 0.125,
+                          mask_mod=lambda b, h, q, kv: torch.logical_and(q >= kv, q - kv <= 200),
+                          online_func=helpers.OnlineSoftmax())
+    assert win.mask_mode == 2
+    assert win._ensure_lists("cpu", None, B, H, 1024, 1024)[0].shape == (B, H, 8)
+    with pytest.raises(ValueError, match="inferred for"):
+        win._ensure_lists("cpu", None, B, H, 2048, 2048)

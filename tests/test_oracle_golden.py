@@ -135,3 +135,30 @@ def test_linear_scan_oracle_matches_fla_naive(golden_dir):
     z = np.load(os.path.join(golden_dir, "linear_scan.npz"))
     o = linear_scan(_t(z["q"]), _t(z["k"]), _t(z["v"]), _t(z["a"]))
     torch.testing.assert_close(o.float(), _t(z["o"]), rtol=1e-4, atol=1e-4)
+
+
+def test_sigmoid_oracle_matches_reference_score_mod(golden_dir):
+    """sigmoid.npz: the score_mod of the reference's attn_script/sigmoidattn.py, traced and differentiated by the
+    reference's own IR, inside the un-normalised P V composition; the oracle writes the same function in torch."""
+    z = np.load(os.path.join(golden_dir, "sigmoid.npz"))
+    q, k, v, d_o = (_t(z[n]) for n in ("q", "k", "v", "do"))
+    o, (dq, dk, dv) = orc.fwd_bwd(lambda a, b, c: orc.sigmoid_attention(a, b, c, scale=1.0, bias=float(z["bias"])),
+                                  (q, k, v), d_o)
+    for name, got in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
+        torch.testing.assert_close(got, _t(z[name]), rtol=1e-4, atol=1e-4, msg=lambda m: f"{name}: {m}")
+    # and the textbook form: (tanh(x / 2) + 1) / 2 is the logistic function
+    x = torch.linspace(-12, 12, 97)
+    torch.testing.assert_close((torch.tanh(x * 0.5) + 1) * 0.5, torch.sigmoid(x), rtol=1e-6, atol=1e-7)
+
+
+def test_mamba2_mapping_matches_reference_mods(golden_dir):
+    """mamba2.npz: decay_mod / v_mod of the reference's attn_script/mamba2_ngroup1.py evaluated by the reference's IR
+    and fed to flash-linear-attention's naive recurrence with q = C, k = B; the oracle's mamba2_ssd is the same map."""
+    from oracle.linear_oracle import mamba2_ssd
+    z = np.load(os.path.join(golden_dir, "mamba2.npz"))
+    x, dt, A, Bm, Cm = (_t(z[n]) for n in ("x", "dt", "A", "Bm", "Cm"))
+    o = mamba2_ssd(x, dt, A, Bm, Cm)
+    torch.testing.assert_close(o.float(), _t(z["o"]), rtol=1e-4, atol=1e-4)
+    # the skip connection is a per-head multiple of the raw input added to that output
+    Dk = torch.tensor([0.5, -1.25, 2.0])
+    torch.testing.assert_close(mamba2_ssd(x, dt, A, Bm, Cm, Dk), o + Dk.view(1, -1, 1, 1) * x.double())

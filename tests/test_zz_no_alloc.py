@@ -40,8 +40,10 @@ def _params(eng, q, k, v, o, d_o, finals, dq, dk, dv, delta):
     return p
 
 
-def test_static_scratch_backward_matches_regular_backward_twice():
-    B, Hq, Hkv, S, D = 2, 4, 2, 384, 128
+@pytest.mark.parametrize("S", [384, 200])
+def test_static_scratch_backward_matches_regular_backward_twice(S):
+    """S = 200 is ragged: the last tile's rows past the end read clamped delta words of the shared array."""
+    B, Hq, Hkv, D = 2, 4, 2, 128
     eng = helpers.softmax_engine(B, Hq, Hkv, S, D, D, torch.float16, True)
     kern = eng.kernels.bwd
     L = rt.lib()
@@ -77,3 +79,6 @@ def test_static_scratch_refuses_oversize():
     assert rc == 1
     msg = rt.lib().ae_last_error().decode()
     assert str(rt.STATIC_SCRATCH_MAX_ROWS) in msg and "exceeds" in msg
+    p.B = 0
+    rc = rt.lib().ae_launch_attn_bwd_static_scratch(kern.prep.handle, kern.dq.handle, kern.dkv.handle, C.byref(p), None)
+    assert rc == 1 and "positive" in rt.lib().ae_last_error().decode()
