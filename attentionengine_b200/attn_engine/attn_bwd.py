@@ -1,8 +1,16 @@
-"""Backward launches of AttentionEngine: delta pre-pass, dQ pass, dK/dV pass.
+"""Backward launches of AttentionEngine.
 
 Stands in for the generated ``_attention.backward`` of the reference
 (attention_engine/core/template/tl_template/attn/attn_tl.py:582-601): ``mod_prep`` (only when
-``OnlineFunc.backward`` reads doosum), ``mod_bwd`` and ``mod_post``.
+``OnlineFunc.backward`` reads doosum), ``mod_bwd`` and ``mod_post``.  Two forms:
+
+* ``"fused"``: the reference's scheme.  One kv-stationary kernel (attn_bwd_fused.cuh) computes dK and dV and adds its
+  dQ tiles in fp32 into a [B, S, Hq, D] buffer, a cast kernel converts that buffer: five contractions per tile.
+  dQ is summed in an order that varies from run to run.
+* ``"split"``: a dQ pass and a dK/dV pass that each recompute S and dP (seven contractions), no atomics,
+  bit-reproducible, no fp32 buffer.
+
+``AttentionEngine.bwd_mode`` picks one per engine; the default comes from ``AE_B200_BWD`` (``split`` unless set).
 """
 from __future__ import annotations
 
@@ -15,6 +23,10 @@ import torch
 from .. import runtime as rt
 
 
+DEFAULT_MODE = os.environ.get("AE_B200_BWD", "split")
+SMEM_MAX = 232448  # dynamic shared memory a CTA can have on sm_100 (227 KiB)
+
+
 @dataclass
 class BwdKernels:
     prep: rt.Module
@@ -23,6 +35,56 @@ class BwdKernels:
     bn: int      # kv rows per streamed tile of the dQ pass
     stages: int  # its K / V ring depth
     sources: dict | None = None  # kernel name -> generated CUDA source (kept for inspection and build checks)
+
+
+@dataclass
+class FusedBwdKernels:
+    prep: rt.Module
+    fused: rt.Module
+    cast: rt.Module
+    config: tuple  # (Q ring depth, dO ring depth, row warpgroups)
+    sources: dict | None = None
+
+
+def fused_tile_config(D: int, DV: int, ncs: int):
+    """(Q ring depth, dO ring depth, row warpgroups) of the one-pass backward.  K, V and the 128 x 128 dS tile are
+    resident; a Q tile is needed first in a step (S^T of the next tile) and released last (dK), a dO tile is read by
+    dP^T and dV only, so at head dim 128 Q gets three slots and dO one; smaller heads take deeper rings."""
+    cfg = os.environ.get("AE_B200_FUSED_TILE")  # "Q stages,dO stages,row groups": tuning override
+    if cfg:
+        return tuple(int(x) for x in cfg.split(","))
+    for qst, dost in ((4, 2), (3, 2), (3, 1), (2, 1)):
+        if fused_smem_bytes(D, DV, ncs, qst, dost) <= SMEM_MAX:
+            return qst, dost, 4
+    raise NotImplementedError("one-pass backward: the tiles do not fit in shared memory")
+
+
+def fused_smem_bytes(D, DV, ncs, qst, dost):
+    """tiles + row-scale slots + 1008: enough for the kernel's carve-up from any 16-byte aligned base (the barrier
+    block sits behind the slots or in the alignment gap)."""
+    tiles = 128 * (D + DV) * 2 + 128 * (qst * D + dost * DV) * 2 + 128 * 128 * 2
+    return tiles + 2 * 128 * ncs * 4 + 1008
+
+
+def compile_fused(k) -> FusedBwdKernels:
+    D, DV, low = k.D, k.DV, k.low
+    ncs = len(low.final_names) + 1
+    qst, dost, nwg = fused_tile_config(D, DV, ncs)
+    smem = fused_smem_bytes(D, DV, ncs, qst, dost)
+    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_PREP, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=256,
+                          smem_bytes=0, stages=0, mask_mode=k.mask_mode)
+    src_prep = rt.kernel_source("attn_bwd_prep.cuh", prelude=low.prelude_bwd)
+    prep = rt.compile_module(src_prep, "ae_attn_bwd_prep", cfg)
+    prelude = low.prelude_bwd + (f"#define AE_FU_QSTAGES {qst}\n#define AE_FU_DOSTAGES {dost}\n#define AE_FU_NWG {nwg}\n"
+                                 f"#define AE_FU_SMEM {smem}\n")
+    src = rt.kernel_source("attn_bwd_fused.cuh", prelude=prelude)
+    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_FUSED, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV,
+                          threads=nwg * 128 + 64, smem_bytes=smem, stages=qst, mask_mode=k.mask_mode)
+    fused = rt.compile_module(src, "ae_attn_bwd_fused", cfg)
+    cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_CAST, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=256,
+                          smem_bytes=0, stages=0, mask_mode=k.mask_mode)
+    cast = rt.compile_module(src, "ae_attn_bwd_dq_cast", cfg)
+    return FusedBwdKernels(prep, fused, cast, (qst, dost, nwg), {"attn_bwd_prep": src_prep, "attn_bwd_fused": src})
 
 
 def dq_tile_config(D: int, DV: int):
@@ -89,7 +151,10 @@ def _s3(t):
 
 
 def launch_bwd(eng, q, k, v, o, d_o, finals, custom, lists=None):
-    kern = eng.kernels.bwd
+    mode = getattr(eng, "bwd_mode", None) or DEFAULT_MODE
+    if mode not in ("fused", "split"):
+        raise ValueError(f"bwd_mode {mode!r}: 'fused' or 'split'")
+    kern = eng.kernels.bwd_fused if mode == "fused" else eng.kernels.bwd
     B, Sq, Hq, Skv, Hkv = eng._check_qkv(q, k, v)
     dev = q.device
     if d_o.stride(3) != 1 or d_o.stride(2) % 8 or d_o.stride(1) % 8 or d_o.data_ptr() % 16:
@@ -120,6 +185,12 @@ def launch_bwd(eng, q, k, v, o, d_o, finals, custom, lists=None):
     L = rt.lib()
     if delta is not None:
         rt.check(L.ae_launch_attn_bwd_prep(kern.prep.handle, C.byref(p), stream), "ae_launch_attn_bwd_prep")
-    rt.check(L.ae_launch_attn_bwd_dq(kern.dq.handle, C.byref(p), stream), "ae_launch_attn_bwd_dq")
-    rt.check(L.ae_launch_attn_bwd_dkv(kern.dkv.handle, C.byref(p), stream), "ae_launch_attn_bwd_dkv")
+    if mode == "fused":
+        acc = torch.empty(B, Sq, Hq, eng.D, dtype=torch.float32, device=dev)  # cleared by the launcher on the stream
+        p.dq_accum = acc.data_ptr()
+        rt.check(L.ae_launch_attn_bwd_fused(kern.fused.handle, C.byref(p), stream), "ae_launch_attn_bwd_fused")
+        rt.check(L.ae_launch_attn_bwd_dq_cast(kern.cast.handle, C.byref(p), stream), "ae_launch_attn_bwd_dq_cast")
+    else:
+        rt.check(L.ae_launch_attn_bwd_dq(kern.dq.handle, C.byref(p), stream), "ae_launch_attn_bwd_dq")
+        rt.check(L.ae_launch_attn_bwd_dkv(kern.dkv.handle, C.byref(p), stream), "ae_launch_attn_bwd_dkv")
     return dq, dk, dv

@@ -114,13 +114,23 @@ class _AttnKernels:
         self.fwd_src = rt.kernel_source("attn_fwd.cuh", prelude=low.prelude_fwd)
         self.fwd = rt.compile_module(self.fwd_src, "ae_attn_fwd", cfg)
         self._bwd = None
+        self._bwd_fused = None
 
     @property
     def bwd(self):
+        """The two-pass backward (dQ pass + dK/dV pass)."""
         if self._bwd is None:
             from .attn_bwd import compile_bwd
             self._bwd = compile_bwd(self)
         return self._bwd
+
+    @property
+    def bwd_fused(self):
+        """The one-pass backward (kv-stationary kernel with fp32 dQ accumulation + cast)."""
+        if self._bwd_fused is None:
+            from .attn_bwd import compile_fused
+            self._bwd_fused = compile_fused(self)
+        return self._bwd_fused
 
 
 class _AttentionFn(torch.autograd.Function):
@@ -168,6 +178,7 @@ class AttentionEngine:
         self.score_mod, self.mask_mod, self.online_func = score_mod, mask_mod, online_func
         self.mask_value = mask_value
         self.extern_block_mask = extern_block_mask
+        self.bwd_mode = None  # "fused" | "split"; None = the package default (attn_bwd.DEFAULT_MODE)
         self.block_mask = None
         self._call_block_mask = None
         self._lists = None

@@ -27,6 +27,8 @@ struct Driver {
   CUresult (*cuInit)(unsigned) = nullptr;
   CUresult (*cuCtxGetCurrent)(CUcontext*) = nullptr;
   CUresult (*cuCtxSetCurrent)(CUcontext) = nullptr;
+  CUresult (*cuCtxPushCurrent)(CUcontext) = nullptr;
+  CUresult (*cuCtxPopCurrent)(CUcontext*) = nullptr;
   CUresult (*cuDeviceGet)(CUdevice*, int) = nullptr;
   CUresult (*cuDevicePrimaryCtxRetain)(CUcontext*, CUdevice) = nullptr;
   CUresult (*cuModuleLoadData)(CUmodule*, const void*) = nullptr;
@@ -37,6 +39,7 @@ struct Driver {
   CUresult (*cuLaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                              CUstream, void**, void**) = nullptr;
   CUresult (*cuGetErrorString)(CUresult, const char**) = nullptr;
+  CUresult (*cuMemsetD32Async)(CUdeviceptr, unsigned, size_t, CUstream) = nullptr;
   CUresult (*cuTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
@@ -56,6 +59,8 @@ Driver& driver() {
     AE_SYM(cuInit, "cuInit")
     AE_SYM(cuCtxGetCurrent, "cuCtxGetCurrent")
     AE_SYM(cuCtxSetCurrent, "cuCtxSetCurrent")
+    AE_SYM(cuCtxPushCurrent, "cuCtxPushCurrent_v2")
+    AE_SYM(cuCtxPopCurrent, "cuCtxPopCurrent_v2")
     AE_SYM(cuDeviceGet, "cuDeviceGet")
     AE_SYM(cuDevicePrimaryCtxRetain, "cuDevicePrimaryCtxRetain")
     AE_SYM(cuModuleLoadData, "cuModuleLoadData")
@@ -65,6 +70,7 @@ Driver& driver() {
     AE_SYM(cuFuncGetAttribute, "cuFuncGetAttribute")
     AE_SYM(cuLaunchKernel, "cuLaunchKernel")
     AE_SYM(cuGetErrorString, "cuGetErrorString")
+    AE_SYM(cuMemsetD32Async, "cuMemsetD32Async")
     AE_SYM(cuTensorMapEncodeTiled, "cuTensorMapEncodeTiled")
 #undef AE_SYM
     d.ok = (d.cuInit(0) == CUDA_SUCCESS);
@@ -130,16 +136,25 @@ Nvrtc& nvrtc() {
 }
 
 // ------------------------------------------------------------------ module
+// A cubin is loaded once per CUDA context it is launched in (one context per device under the runtime API): an engine
+// first used on one GPU and later given tensors of another gets that GPU's own function handle.
+struct Loaded {
+  CUcontext ctx = nullptr;
+  CUmodule mod = nullptr;
+  CUfunction fn = nullptr;
+};
 struct Module {
   std::vector<char> cubin;
   std::string kernel;
   AeKernelConfig cfg{};
   std::mutex mu;
-  CUmodule mod = nullptr;
-  CUfunction fn = nullptr;
+  std::vector<Loaded> loaded;
 };
 
-int ensure_context() {
+// function handle of the last ensure_loaded() of this thread: launch() follows it directly
+thread_local CUfunction g_fn = nullptr;
+
+int ensure_context(CUcontext* out) {
   Driver& d = driver();
   if (!d.ok) {
     set_error("libcuda.so.1 not available or cuInit failed");
@@ -153,26 +168,36 @@ int ensure_context() {
     AE_CU(d.cuDevicePrimaryCtxRetain(&ctx, dev));
     AE_CU(d.cuCtxSetCurrent(ctx));
   }
+  *out = ctx;
   return AE_OK;
 }
 
 int ensure_loaded(Module* m) {
-  std::lock_guard<std::mutex> lk(m->mu);
-  if (m->fn) return AE_OK;
-  int rc = ensure_context();
+  CUcontext ctx = nullptr;
+  int rc = ensure_context(&ctx);
   if (rc) return rc;
+  std::lock_guard<std::mutex> lk(m->mu);
+  for (const Loaded& l : m->loaded)
+    if (l.ctx == ctx) {
+      g_fn = l.fn;
+      return AE_OK;
+    }
   Driver& d = driver();
-  AE_CU(d.cuModuleLoadData(&m->mod, m->cubin.data()));
-  AE_CU(d.cuModuleGetFunction(&m->fn, m->mod, m->kernel.c_str()));
+  Loaded l;
+  l.ctx = ctx;
+  AE_CU(d.cuModuleLoadData(&l.mod, m->cubin.data()));
+  AE_CU(d.cuModuleGetFunction(&l.fn, l.mod, m->kernel.c_str()));
   if (m->cfg.smem_bytes > 48 * 1024)
-    AE_CU(d.cuFuncSetAttribute(m->fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, m->cfg.smem_bytes));
+    AE_CU(d.cuFuncSetAttribute(l.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, m->cfg.smem_bytes));
+  m->loaded.push_back(l);
+  g_fn = l.fn;
   return AE_OK;
 }
 
 int launch(Module* m, unsigned gx, unsigned gy, unsigned gz, void* args, void* stream) {
   Driver& d = driver();
   void* params[] = {args};
-  AE_CU(d.cuLaunchKernel(m->fn, gx, gy, gz, (unsigned)m->cfg.threads, 1, 1, (unsigned)m->cfg.smem_bytes,
+  AE_CU(d.cuLaunchKernel(g_fn, gx, gy, gz, (unsigned)m->cfg.threads, 1, 1, (unsigned)m->cfg.smem_bytes,
                          (CUstream)stream, params, nullptr));
   return AE_OK;
 }
@@ -331,18 +356,24 @@ int ae_query(void* module, AeKernelInfo* info) {
   int rc = ensure_loaded(m);
   if (rc) return rc;
   Driver& d = driver();
-  AE_CU(d.cuFuncGetAttribute(&info->num_regs, CU_FUNC_ATTRIBUTE_NUM_REGS, m->fn));
-  AE_CU(d.cuFuncGetAttribute(&info->static_smem_bytes, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, m->fn));
-  AE_CU(d.cuFuncGetAttribute(&info->max_dynamic_smem_bytes, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, m->fn));
-  AE_CU(d.cuFuncGetAttribute(&info->local_bytes, CU_FUNC_ATTRIBUTE_LOCAL_SIZE_BYTES, m->fn));
-  AE_CU(d.cuFuncGetAttribute(&info->max_threads, CU_FUNC_ATTRIBUTE_MAX_THREADS_PER_BLOCK, m->fn));
+  AE_CU(d.cuFuncGetAttribute(&info->num_regs, CU_FUNC_ATTRIBUTE_NUM_REGS, g_fn));
+  AE_CU(d.cuFuncGetAttribute(&info->static_smem_bytes, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, g_fn));
+  AE_CU(d.cuFuncGetAttribute(&info->max_dynamic_smem_bytes, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, g_fn));
+  AE_CU(d.cuFuncGetAttribute(&info->local_bytes, CU_FUNC_ATTRIBUTE_LOCAL_SIZE_BYTES, g_fn));
+  AE_CU(d.cuFuncGetAttribute(&info->max_threads, CU_FUNC_ATTRIBUTE_MAX_THREADS_PER_BLOCK, g_fn));
   return AE_OK;
 }
 
 void ae_release(void* module) {
   if (!module) return;
   Module* m = (Module*)module;
-  if (m->mod) driver().cuModuleUnload(m->mod);
+  Driver& d = driver();
+  for (const Loaded& l : m->loaded) {  // a module is unloaded with its own context current
+    if (d.cuCtxPushCurrent(l.ctx) != CUDA_SUCCESS) continue;
+    d.cuModuleUnload(l.mod);
+    CUcontext popped = nullptr;
+    d.cuCtxPopCurrent(&popped);
+  }
   delete m;
 }
 
@@ -531,6 +562,54 @@ int ae_launch_attn_bwd_dkv(void* module, const AeAttnBwdParams* p, void* stream)
   rc = fill_bwd_args(m, p, &a, bn, 128);
   if (rc) return rc;
   return launch(m, (unsigned)a.n_kt, (unsigned)p->Hkv, (unsigned)p->B, &a, stream);
+}
+
+int ae_launch_attn_bwd_fused(void* module, const AeAttnBwdParams* p, void* stream) {
+  if (!module || !p || !p->q || !p->k || !p->v || !p->d_o || !p->dk || !p->dv || !p->dq_accum) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  int rc = check_attn_common(m, AE_KIND_ATTN_BWD_FUSED, p->B, p->Hq, p->Hkv, p->Sq, p->Skv);
+  if (rc) return rc;
+  if (m->cfg.mask_mode == 2 && (!p->block_count_t || !p->block_index_t)) {
+    set_error("transposed block lists required for mask_mode 2");
+    return AE_ERR_INVALID;
+  }
+  if (reinterpret_cast<uintptr_t>(p->dq_accum) & 15) {
+    set_error("dq_accum must be 16-byte aligned");
+    return AE_ERR_INVALID;
+  }
+  rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeAttnBwdArgs a;
+  rc = fill_bwd_args(m, p, &a, 128, 128);
+  if (rc) return rc;
+  a.dq_acc = p->dq_accum;
+  const size_t words = (size_t)p->B * p->Sq * p->Hq * m->cfg.head_dim;
+  AE_CU(driver().cuMemsetD32Async((CUdeviceptr)(uintptr_t)p->dq_accum, 0u, words, (CUstream)stream));
+  return launch(m, (unsigned)a.n_kt, (unsigned)p->Hkv, (unsigned)p->B, &a, stream);
+}
+
+int ae_launch_attn_bwd_dq_cast(void* module, const AeAttnBwdParams* p, void* stream) {
+  if (!module || !p || !p->dq || !p->dq_accum) return AE_ERR_INVALID;
+  Module* m = (Module*)module;
+  int rc = check_attn_common(m, AE_KIND_ATTN_BWD_CAST, p->B, p->Hq, p->Hkv > 0 ? p->Hkv : 1, p->Sq, p->Skv > 0 ? p->Skv : 1);
+  if (rc) return rc;
+  if ((reinterpret_cast<uintptr_t>(p->dq_accum) & 15) || (reinterpret_cast<uintptr_t>(p->dq) & 15) ||
+      p->dq_stride[0] % 8 || p->dq_stride[1] % 8 || p->dq_stride[2] % 8) {
+    set_error("dq / dq_accum must be 16-byte aligned, dq strides multiples of 8 elements");
+    return AE_ERR_INVALID;
+  }
+  rc = ensure_loaded(m);
+  if (rc) return rc;
+  AeAttnBwdArgs a;
+  memset(&a, 0, sizeof a);
+  a.dq = p->dq;
+  a.dq_sb = p->dq_stride[0]; a.dq_ss = p->dq_stride[1]; a.dq_sh = p->dq_stride[2];
+  a.dq_acc = p->dq_accum;
+  a.B = p->B; a.Hq = p->Hq; a.Sq = p->Sq;
+  const int64_t vecs = (int64_t)p->B * p->Sq * p->Hq * (m->cfg.head_dim / 8);
+  int64_t blocks = (vecs + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch(m, (unsigned)blocks, 1, 1, &a, stream);
 }
 
 static int make_3d_map(AeTmaDesc* out, const void* base, int dtype, int64_t cols, int64_t rows, int64_t batch,

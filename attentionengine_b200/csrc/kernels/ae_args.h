@@ -86,6 +86,7 @@ struct AeAttnBwdArgs {
   int B, Hq, Hkv, Sq, Skv;
   int n_qt, n_kt;
   u32* status;
+  float* dq_acc;  // [B, Sq, Hq, D] fp32, contiguous: dQ accumulator of the one-pass backward (ae_attn_bwd_fused)
 };
 
 // ---- MLA split-KV decode (kernels ae_mla_decode, ae_mla_combine) --------------------------

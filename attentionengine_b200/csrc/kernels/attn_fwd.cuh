@@ -250,6 +250,12 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       tma_prefetch_desc(&args.tm_k);
       tma_prefetch_desc(&args.tm_v);
       for (int t = 0; t < AE_NQ; ++t) {
+        // a q tile past the end is never waited for: fetching it would leave a bulk copy in flight when the CTA retires
+#if AE_DECODE
+        if (t > 0 && t * AE_BM >= args.rows) break;
+#else
+        if (qt0 + t >= args.n_qt) break;
+#endif
         mbar_arrive_expect_tx(&bars->q_full[t], AE_Q_BYTES);
         for (int dh = 0; dh < AE_D / 64; ++dh)
           tma_load_bshd(smem + AE_SMEM_Q + t * AE_Q_BYTES + dh * (AE_BM * 128), &args.tm_q, &bars->q_full[t], dh * 64,
@@ -348,6 +354,12 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
           s_into(n + 2);
         }
       }
+      // every commit of this thread has arrived before the CTA may retire (the last slot releases have no other waiter)
+      if (ok && n_steps > 0) {
+        const int l = n_steps - 1;
+        ok = mbar_wait(&bars->v_empty[l % AE_STAGES], (l / AE_STAGES) & 1, ctl, args.status, 12) &&
+             mbar_wait(&bars->k_empty[l % AE_STAGES], (l / AE_STAGES) & 1, ctl, args.status, 13);
+      }
 #else
       // The walk is consumed one step ahead for the S GEMMs.
       AeKvStep cur, nxt;
@@ -420,6 +432,12 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         cur = nxt;
         have = have_n;
         ++it;
+      }
+      // every commit of this thread has arrived before the CTA may retire (the last slot releases have no other waiter)
+      if (ok && it > 0) {
+        const int l = it - 1;
+        ok = mbar_wait(&bars->v_empty[l % AE_STAGES], (l / AE_STAGES) & 1, ctl, args.status, 12) &&
+             mbar_wait(&bars->k_empty[l % AE_STAGES], (l / AE_STAGES) & 1, ctl, args.status, 13);
       }
 #endif  // AE_PINGPONG
     }

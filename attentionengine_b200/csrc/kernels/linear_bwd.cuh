@@ -12,7 +12,10 @@
 //     dk_j = w_j (v dH'^T)_j + (dS^T q)_j                        (R1, same scheme)
 //     dv_j = w_j (k dH')_j + (P^T dO)_j
 //     dH   = exp(g_last) dH' + q^T (dO o exp(g))
-//     d a_t = sum over s >= t of (q_s . dq_s - k_s . dk_s)       (suffix sum carried across chunks)
+//     d a_t = sum over s >= t of (q_s . dq_s - k_s . dk_s): a suffix sum inside the chunk; what the later chunks add
+//             is <dH, h> of the next chunk (the state that crosses the boundary times its gradient), computed there
+//             directly.  Carrying the running sum across chunks instead lets the rounding of the 16-bit operands
+//             random-walk over the whole sequence (28 % error on dA at 8192 steps).
 // dq / dk are written per head; the caller sums them over a head group when q / k have fewer heads.
 // All transposed products read the same 16-bit tiles through MN-major descriptors: nothing is transposed in
 // registers.  Roles: warps 0-3 row threads (thread r = step r = state row r), warp 4 TMA, warp 5 MMA.
@@ -53,7 +56,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
   extern __shared__ u8 smem_raw[];
   u8* smem = smem_align1024(smem_raw);
   AeLbBars* bars = (AeLbBars*)(smem + AE_LB_SMEM_BAR);
-  float* gs = (float*)(smem + AE_LB_SMEM_G);  // [0..127] g of the chunk, [128..131] warp totals, [132..135] warp sums of dG
+  float* gs = (float*)(smem + AE_LB_SMEM_G);  // [0..127] g of the chunk, [128..131] warp totals, [132..135] warp sums of dG,
+                                              // [136..139] warp sums of <dH, h>
   AeCtaCtl* ctl = &bars->ctl;
   const u32 warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x, b = blockIdx.y;
@@ -179,7 +183,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
     const u32 lane_base = ((warp & 3) * 32) << 16;
     const i64 bh = (i64)b * args.H + h;
     const float* a_row = args.a + bh * args.T;
-    float carry = 0.f;  // sum of dG over all later chunks
+    float carry = 0.f;  // sum of dG over all later chunks = <dH, h> at the boundary to the next chunk
     bool ok = true;
     for (int it = 0; it < n_chunks; ++it) {
       const int c = n_chunks - 1 - it;
@@ -358,6 +362,27 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
           }
         }
         if (!row_ok) dg = 0.f;
+        // <dH, h> of this chunk (row r of both), the carry for the chunk before it
+        float hd = 0.f;
+        {
+          const u8* hc = smem + AE_LB_SMEM_HC;
+#pragma unroll
+          for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+            float f[32];
+            tmem_ld_f32x32(tmem + TM_DH + lane_base + cc * 32, f);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 x = *(const uint4*)(hc + tile_off(r, cc * 32 + i * 8, AE_LB_DK));
+              const u32 xw[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+              for (int e2 = 0; e2 < 4; ++e2)
+                hd += unpack_lo<AE_BF16>(xw[e2]) * f[i * 8 + e2 * 2] + unpack_hi<AE_BF16>(xw[e2]) * f[i * 8 + e2 * 2 + 1];
+            }
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) hd += __shfl_xor_sync(0xffffffffu, hd, o);
+          if (lane == 0) gs[136 + (warp & 3)] = hd;
+        }
         // inclusive suffix sum of dG over the chunk, plus everything from later chunks
         float sfx = dg;
 #pragma unroll
@@ -367,15 +392,14 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         }
         if (lane == 0) gs[132 + (warp & 3)] = sfx;
         named_bar_sync(1, 128);
-        float after = 0.f, total = 0.f;
+        float after = 0.f, next_carry = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-          const float tw = gs[132 + w];
-          total += tw;
-          if ((u32)w > (warp & 3)) after += tw;
+          if ((u32)w > (warp & 3)) after += gs[132 + w];
+          next_carry += gs[136 + w];
         }
         if (store) args.da[bh * args.T + t] = sfx + after + carry;
-        carry += total;
+        carry = next_carry;
       }
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->empty);  // this chunk's tiles and accumulators are free

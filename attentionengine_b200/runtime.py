@@ -24,6 +24,7 @@ KIND_PROBE, KIND_ATTN_FWD, KIND_ATTN_BWD_PREP, KIND_ATTN_BWD_DQ, KIND_ATTN_BWD_D
 KIND_MLA_DECODE, KIND_MLA_COMBINE, KIND_LINEAR_FWD, KIND_LINEAR_BWD, KIND_LINEAR_STATES = 5, 6, 7, 8, 9
 KIND_ATTN_DECODE = 10
 KIND_ROWSCALE = 11
+KIND_ATTN_BWD_FUSED, KIND_ATTN_BWD_CAST = 12, 13
 DTYPE_F16, DTYPE_BF16 = 0, 1
 
 
@@ -68,7 +69,7 @@ class AttnBwdParams(C.Structure):
                 ("block_count", C.c_void_p), ("block_index", C.c_void_p),
                 ("block_count_t", C.c_void_p), ("block_index_t", C.c_void_p),
                 ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("Sq", C.c_int32), ("Skv", C.c_int32),
-                ("status", C.c_void_p)]
+                ("status", C.c_void_p), ("dq_accum", C.c_void_p)]
 
 
 class MlaParams(C.Structure):
@@ -117,7 +118,7 @@ _lib_lock = threading.Lock()
 
 EXPORTS = ["ae_compile", "ae_module_from_cubin", "ae_module_cubin", "ae_query", "ae_release", "ae_strerror",
            "ae_last_error", "ae_launch_attn_fwd", "ae_launch_attn_bwd_prep", "ae_launch_attn_bwd_dq",
-           "ae_launch_attn_bwd_dkv", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch", "ae_launch_mla_decode", "ae_launch_mla_combine", "ae_launch_mla_decode_paged", "ae_launch_attn_decode", "ae_launch_decode_combine", "ae_launch_rowscale", "ae_launch_linear_fwd", "ae_launch_linear_states", "ae_launch_linear_bwd"]
+           "ae_launch_attn_bwd_dkv", "ae_launch_attn_bwd_fused", "ae_launch_attn_bwd_dq_cast", "ae_launch_probe", "ae_launch_attn_bwd_static_scratch", "ae_launch_mla_decode", "ae_launch_mla_combine", "ae_launch_mla_decode_paged", "ae_launch_attn_decode", "ae_launch_decode_combine", "ae_launch_rowscale", "ae_launch_linear_fwd", "ae_launch_linear_states", "ae_launch_linear_bwd"]
 
 
 def lib() -> C.CDLL:
@@ -139,7 +140,8 @@ def lib() -> C.CDLL:
             L.ae_release.argtypes = [C.c_void_p]
             L.ae_release.restype = None
             L.ae_launch_attn_fwd.argtypes = [C.c_void_p, C.POINTER(AttnParams), C.c_void_p]
-            for n in ("ae_launch_attn_bwd_prep", "ae_launch_attn_bwd_dq", "ae_launch_attn_bwd_dkv"):
+            for n in ("ae_launch_attn_bwd_prep", "ae_launch_attn_bwd_dq", "ae_launch_attn_bwd_dkv",
+                      "ae_launch_attn_bwd_fused", "ae_launch_attn_bwd_dq_cast"):
                 getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnBwdParams), C.c_void_p]
             L.ae_launch_attn_bwd_static_scratch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(AttnBwdParams),
                                                             C.c_void_p]

@@ -56,6 +56,8 @@ enum {
   AE_KIND_LINEAR_STATES = 9,
   AE_KIND_ATTN_DECODE = 10,
   AE_KIND_ROWSCALE = 11,
+  AE_KIND_ATTN_BWD_FUSED = 12,
+  AE_KIND_ATTN_BWD_CAST = 13,
 };
 
 #define AE_MAX_CUSTOM_INPUTS 4
@@ -130,8 +132,11 @@ int ae_launch_attn_fwd(void* module, const AeAttnParams* p, void* stream);
 /* ---- attention backward -----------------------------------------------------------
  * Stands in for `_attention.backward` (attn_tl.py:582-601): `mod_prep(o, dO)` (K2,
  * attn_tl.py:196-223), `mod_bwd(...)` (K3, :239-415) and `mod_post(dq)` (K4, :436-455).
- * Here the dQ and the dK/dV parts are two launches with no atomics and no fp32 dQ
- * staging buffer, so there is no post kernel. */
+ * Two forms.  Two-pass (ae_launch_attn_bwd_dq + _dkv): the dQ and the dK/dV parts are two
+ * launches with no atomics and no fp32 dQ staging buffer, bit-reproducible, at the cost of
+ * computing S and dP in both.  One-pass (ae_launch_attn_bwd_fused + _dq_cast): the reference's
+ * own scheme, one kv-stationary kernel that adds dQ in fp32 into `dq_accum`, and the post
+ * kernel that converts it; five contractions per tile instead of seven, dQ not bit-reproducible. */
 typedef struct AeAttnBwdParams {
   const void* q;
   const void* k;
@@ -153,11 +158,19 @@ typedef struct AeAttnBwdParams {
   const int32_t* block_index_t;
   int32_t B, Hq, Hkv, Sq, Skv;
   uint32_t* status;
+  float* dq_accum; /* [B, Sq, Hq, D] fp32 contiguous scratch (one-pass form only; 16-byte aligned) */
 } AeAttnBwdParams;
 
 int ae_launch_attn_bwd_prep(void* module, const AeAttnBwdParams* p, void* stream);
 int ae_launch_attn_bwd_dq(void* module, const AeAttnBwdParams* p, void* stream);
 int ae_launch_attn_bwd_dkv(void* module, const AeAttnBwdParams* p, void* stream);
+/* One-pass form (`mod_bwd` with its fp32 dQ atomics, attn_tl.py:239-415): clears p->dq_accum on `stream`, then runs
+ * the kv-stationary kernel, which writes dk, dv and adds dQ into dq_accum.  Module kind AE_KIND_ATTN_BWD_FUSED
+ * (kernel "ae_attn_bwd_fused"); p->delta as for the two-pass form. */
+int ae_launch_attn_bwd_fused(void* module, const AeAttnBwdParams* p, void* stream);
+/* `mod_post` (attn_tl.py:436-455): dq = p->dq_accum converted to the 16-bit type.  Module kind
+ * AE_KIND_ATTN_BWD_CAST (kernel "ae_attn_bwd_dq_cast"). */
+int ae_launch_attn_bwd_dq_cast(void* module, const AeAttnBwdParams* p, void* stream);
 
 /* ---- attention backward without a caller-provided scratch buffer --------------------
  * No counterpart in the reference (there PyTorch allocates `delta` inside the generated

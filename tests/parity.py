@@ -25,7 +25,7 @@ import torch
 from oracle import attention_oracle as orc
 
 MAX_ABS, REL_L2 = 2e-2, 1e-3
-K_BF16 = 1.5
+K_BF16 = 1.15
 
 
 def check(name, got, ref, dtype, stages=1, unnormalised=False, rel_limit=None):
