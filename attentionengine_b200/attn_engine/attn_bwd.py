@@ -10,7 +10,9 @@ Stands in for the generated ``_attention.backward`` of the reference
 * ``"split"``: a dQ pass and a dK/dV pass that each recompute S and dP (seven contractions), no atomics,
   bit-reproducible, no fp32 buffer.
 
-``AttentionEngine.bwd_mode`` picks one per engine; the default comes from ``AE_B200_BWD`` (``split`` unless set).
+``AttentionEngine.bwd_mode`` picks one per engine; the tuned-config table (attentionengine_b200/tune.py) can name
+one per problem; otherwise the default comes from ``AE_B200_BWD`` (``fused`` unless set: measured faster on every swept
+shape, 4 % at head dim 128 and 16 % at head dim 64).
 """
 from __future__ import annotations
 
@@ -23,7 +25,7 @@ import torch
 from .. import runtime as rt
 
 
-DEFAULT_MODE = os.environ.get("AE_B200_BWD", "split")
+DEFAULT_MODE = os.environ.get("AE_B200_BWD", "fused")
 SMEM_MAX = 232448  # dynamic shared memory a CTA can have on sm_100 (227 KiB)
 
 
@@ -46,13 +48,16 @@ class FusedBwdKernels:
     sources: dict | None = None
 
 
-def fused_tile_config(D: int, DV: int, ncs: int):
-    """(Q ring depth, dO ring depth, row warpgroups) of the one-pass backward.  K, V and the 128 x 128 dS tile are
-    resident; a Q tile is needed first in a step (S^T of the next tile) and released last (dK), a dO tile is read by
-    dP^T and dV only, so at head dim 128 Q gets three slots and dO one; smaller heads take deeper rings."""
+def fused_tile_config(D: int, DV: int, ncs: int, tuned: dict | None = None):
+    """(Q ring depth, dO ring depth, row warpgroups) of the one-pass backward.  K, V, the 128 x 128 dS tile and the
+    32 KB of dQ staging boxes are resident; a Q tile is needed first in a step (S^T of the next tile) and released last
+    (dK), a dO tile is read by dP^T and dV only, so at head dim 128 what is left holds two Q slots and one dO slot;
+    smaller heads take deeper rings."""
     cfg = os.environ.get("AE_B200_FUSED_TILE")  # "Q stages,dO stages,row groups": tuning override
     if cfg:
         return tuple(int(x) for x in cfg.split(","))
+    if tuned and tuned.get("fused_tile"):
+        return tuple(tuned["fused_tile"])
     for qst, dost in ((4, 2), (3, 2), (3, 1), (2, 1)):
         if fused_smem_bytes(D, DV, ncs, qst, dost) <= SMEM_MAX:
             return qst, dost, 4
@@ -62,14 +67,14 @@ def fused_tile_config(D: int, DV: int, ncs: int):
 def fused_smem_bytes(D, DV, ncs, qst, dost):
     """tiles + row-scale slots + 1008: enough for the kernel's carve-up from any 16-byte aligned base (the barrier
     block sits behind the slots or in the alignment gap)."""
-    tiles = 128 * (D + DV) * 2 + 128 * (qst * D + dost * DV) * 2 + 128 * 128 * 2
+    tiles = 128 * (D + DV) * 2 + 128 * (qst * D + dost * DV) * 2 + 128 * 128 * 2 + 4 * 2 * 4096  # + dQ staging boxes
     return tiles + 2 * 128 * ncs * 4 + 1008
 
 
 def compile_fused(k) -> FusedBwdKernels:
     D, DV, low = k.D, k.DV, k.low
     ncs = len(low.final_names) + 1
-    qst, dost, nwg = fused_tile_config(D, DV, ncs)
+    qst, dost, nwg = fused_tile_config(D, DV, ncs, k.tuned)
     smem = fused_smem_bytes(D, DV, ncs, qst, dost)
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_PREP, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=256,
                           smem_bytes=0, stages=0, mask_mode=k.mask_mode)
@@ -79,7 +84,7 @@ def compile_fused(k) -> FusedBwdKernels:
                                  f"#define AE_FU_SMEM {smem}\n")
     src = rt.kernel_source("attn_bwd_fused.cuh", prelude=prelude)
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_FUSED, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV,
-                          threads=nwg * 128 + 64, smem_bytes=smem, stages=qst, mask_mode=k.mask_mode)
+                          threads=nwg * 128 + 64 + 128, smem_bytes=smem, stages=qst, mask_mode=k.mask_mode)
     fused = rt.compile_module(src, "ae_attn_bwd_fused", cfg)
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_CAST, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=256,
                           smem_bytes=0, stages=0, mask_mode=k.mask_mode)
@@ -87,7 +92,7 @@ def compile_fused(k) -> FusedBwdKernels:
     return FusedBwdKernels(prep, fused, cast, (qst, dost, nwg), {"attn_bwd_prep": src_prep, "attn_bwd_fused": src})
 
 
-def dq_tile_config(D: int, DV: int):
+def dq_tile_config(D: int, DV: int, tuned: dict | None = None):
     """(streamed kv-tile rows, K ring depth, V ring depth) of the dQ pass: Q and dO live in TMEM next to one S and one
     dP region of 128 columns and the dQ accumulator; three 128-row K and V slots fill 192 KB of shared memory at head
     dim 128.  With equal depths K and V of a step share one barrier pair (one wait less per step for the MMA warp);
@@ -95,22 +100,26 @@ def dq_tile_config(D: int, DV: int):
     cfg = os.environ.get("AE_B200_BWD_TILE")  # "bn,K stages,V stages": tuning override
     if cfg:
         return tuple(int(x) for x in cfg.split(","))
+    if tuned and tuned.get("dq_tile"):
+        return tuple(tuned["dq_tile"])
     return 128, 3, 3
 
 
-def dkv_tile_config(D: int, DV: int):
+def dkv_tile_config(D: int, DV: int, tuned: dict | None = None):
     """(streamed q-tile rows, Q ring depth, dO ring depth, row warpgroups) of the dK/dV pass: one 128 x 128 S^T and
     dP^T region next to the two accumulators fill the 512 TMEM columns; K, V, three Q and two dO stages fill shared
     memory at head dim 128 (a Q slot is released last in a step and needed first, so it gets the extra stage)."""
     cfg = os.environ.get("AE_B200_DKV_TILE")  # "bn,q stages,dO stages,row groups,ts": tuning override
     if cfg:
         return tuple(int(x) for x in cfg.split(","))
+    if tuned and tuned.get("dkv_tile"):
+        return tuple(tuned["dkv_tile"])
     return (128, 3, 2, 4, 0) if max(D, DV) > 64 else (128, 3, 3, 4, 0)
 
 
 def compile_bwd(k) -> BwdKernels:
     D, DV, low = k.D, k.DV, k.low
-    bn, kst, vst = dq_tile_config(D, DV)
+    bn, kst, vst = dq_tile_config(D, DV, k.tuned)
     defs = f"#define AE_BWD_BN {bn}\n#define AE_DQ_KSTAGES {kst}\n#define AE_DQ_VSTAGES {vst}\n"
     prelude = low.prelude_bwd + defs
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_PREP, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV, threads=256,
@@ -125,7 +134,7 @@ def compile_bwd(k) -> BwdKernels:
     src_dq = rt.kernel_source("attn_bwd_dq.cuh", prelude=prelude, exp_poly=4)
     dq = rt.compile_module(src_dq, "ae_attn_bwd_dq", cfg)
     ncs = len(low.final_names) + 1
-    bn_kv, qst, dost, nwg, ts = dkv_tile_config(D, DV)
+    bn_kv, qst, dost, nwg, ts = dkv_tile_config(D, DV, k.tuned)
     prelude_kv = low.prelude_bwd + (f"#define AE_BWD_BN {bn_kv}\n#define AE_KV_QSTAGES {qst}\n"
                                     f"#define AE_KV_DOSTAGES {dost}\n#define AE_KV_NWG {nwg}\n#define AE_KV_TS {ts}\n")
     # with K / V resident in TMEM they only pass through the last ring slots

@@ -103,9 +103,11 @@ def _block_lists(cnt: torch.Tensor, q_blk: int, kv_blk: int, Sq: int, Skv: int, 
 class _AttnKernels:
     """Compiled kernels of one engine instance."""
 
-    def __init__(self, low: LoweredAttention, D: int, DV: int, dtype_tag: int, mask_mode: int, stages: int):
+    def __init__(self, low: LoweredAttention, D: int, DV: int, dtype_tag: int, mask_mode: int, stages: int,
+                 tuned: Optional[dict] = None):
         self.low = low
         self.D, self.DV, self.dtype_tag, self.mask_mode, self.stages = D, DV, dtype_tag, mask_mode, stages
+        self.tuned = tuned or {}  # tile choices of the backward kernels (attentionengine_b200/tune.py)
         smem = 2 * 128 * D * 2 + stages * 128 * (D + DV) * 2 + 512 + 1024
         if mask_mode == 2:
             smem += 4 * MAX_LIST_KV_TILES  # the CTA's merged tile walk
@@ -162,7 +164,7 @@ class AttentionEngine:
     def __init__(self, qkv_meta, custom_fwd_inputs, score_mod, mask_mod, online_func, mask_value="-inf",
                  device=None, backend="tl", tune=False, tune_file="", tune_bwd=False, tune_file_bwd="",
                  infer_mask=True, infer_mask_block_M=128, infer_mask_block_N=128, extern_block_mask=False,
-                 kv_shared=False):
+                 kv_shared=False, tuned_config=None):
         if backend not in ("tl", "b200"):
             raise NotImplementedError(f"backend={backend!r}: only the B200 back end exists here "
                                       "(the reference's 'cute' sm_90a path is not part of it)")
@@ -242,11 +244,24 @@ class AttentionEngine:
                 mask_mode = 3  # no block information: visit every tile, mask every element
         self.mask_mode = mask_mode
 
+        # tile / stage choices (reference: the tuned-config json of attn_tl.py:474-500).  `tuned_config` is what the
+        # sweep itself passes; otherwise the caller's tune_file (filled by a sweep when tune=True), then the package's
+        # own table, then the built-in defaults.
+        if tuned_config is None:
+            from .. import tune as _tune
+            keys = _tune.problem_keys(B, Hq, Hkv, Sq, Skv, D, DV, self.dtype, mask_mode)
+            tuned_config = _tune.resolve(dict(score_mod=score_mod, mask_mod=mask_mod, online_func=online_func,
+                                              custom_io=self.custom_fwd_inputs, mask_value=mask_value), keys,
+                                         bool(tune) and not dynamic, tune_file)
+        self.tuned_config = tuned_config
+        stages = int(tuned_config.get("stages", 2))
         low = lower_attention(score_mod, mask_mod, online_func, self.custom_fwd_inputs, D=D, DV=DV,
-                              bf16=self.dtype == torch.bfloat16, mask_mode=mask_mode, stages=2,
+                              bf16=self.dtype == torch.bfloat16, mask_mode=mask_mode, stages=stages,
                               mask_value=mask_value)
         self.lowered = low
-        self.kernels = _AttnKernels(low, D, DV, _TORCH_DTYPES[self.dtype], mask_mode, 2)
+        self.kernels = _AttnKernels(low, D, DV, _TORCH_DTYPES[self.dtype], mask_mode, stages, tuned_config)
+        if tuned_config.get("mode") in ("fused", "split"):
+            self.bwd_mode = tuned_config["mode"]
         self.tl_code = self.kernels.fwd_src  # name kept from the reference (attn_engine.py:365): generated source
 
     # ------------------------------------------------------------------------------------------
@@ -368,6 +383,18 @@ class AttentionEngine:
         if self._mla is None:
             raise NotImplementedError("paged decode is built for kv_shared (MLA) engines")
         return self._mla.paged(q, kcache, block_table, cache_seqlens, num_split)
+
+    def decode_schedule(self, cache_seqlens, device=None):
+        """Decode engines: the work list for rows of these lengths (see AttnDecode.schedule); reuse it across layers."""
+        if self._decode is None:
+            raise NotImplementedError("decode_schedule belongs to decode engines (q_len != kv_len)")
+        return self._decode.schedule(cache_seqlens, device)
+
+    def decode_varlen(self, q, k, v, cache_seqlens, *custom, block_table=None, metadata=None):
+        """Decode engines (MHA / GQA): one length per batch row, dense or paged (128-key pages) K / V."""
+        if self._decode is None:
+            raise NotImplementedError("decode_varlen belongs to decode engines (q_len != kv_len)")
+        return self._decode.decode_varlen(q, k, v, cache_seqlens, *custom, block_table=block_table, metadata=metadata)
 
     def _launch_bwd(self, q, k, v, o, d_o, finals, custom, lists=None):
         from .attn_bwd import launch_bwd

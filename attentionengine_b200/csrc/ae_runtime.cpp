@@ -583,6 +583,18 @@ int ae_launch_attn_bwd_fused(void* module, const AeAttnBwdParams* p, void* strea
   rc = fill_bwd_args(m, p, &a, 128, 128);
   if (rc) return rc;
   a.dq_acc = p->dq_accum;
+  {
+    // fp32 [B, Sq, Hq, D] seen as (d, s, h, b): boxes of 32 floats x 32 q rows, 128-byte swizzle
+    const cuuint64_t D = (cuuint64_t)m->cfg.head_dim;
+    cuuint64_t dims[4] = {D, (cuuint64_t)p->Sq, (cuuint64_t)p->Hq, (cuuint64_t)p->B};
+    cuuint64_t strides[3] = {(cuuint64_t)p->Hq * D * 4, D * 4, (cuuint64_t)p->Sq * p->Hq * D * 4};
+    cuuint32_t box[4] = {32, 32, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    AE_CU(driver().cuTensorMapEncodeTiled(reinterpret_cast<CUtensorMap*>(&a.tm_dqacc), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
+                                          p->dq_accum, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  }
   const size_t words = (size_t)p->B * p->Sq * p->Hq * m->cfg.head_dim;
   AE_CU(driver().cuMemsetD32Async((CUdeviceptr)(uintptr_t)p->dq_accum, 0u, words, (CUstream)stream));
   return launch(m, (unsigned)a.n_kt, (unsigned)p->Hkv, (unsigned)p->B, &a, stream);
@@ -752,17 +764,29 @@ int ae_launch_attn_decode(void* module, const AeDecodeParams* p, void* stream) {
     set_error("decode packs at most 256 query rows per head unit");
     return AE_ERR_UNSUPPORTED;
   }
-  if (m->cfg.mask_mode != 0) return AE_ERR_UNSUPPORTED;
-  if (p->n_split < 1 || p->n_split > 32 || p->n_split > n_kt) return AE_ERR_INVALID;
-  const int tps = (n_kt + p->n_split - 1) / p->n_split;
-  if ((p->n_split - 1) * tps >= n_kt) {
-    set_error("n_split leaves a split without kv tiles");
-    return AE_ERR_INVALID;
+  if (m->cfg.mask_mode != 0 && m->cfg.mask_mode != 3) return AE_ERR_UNSUPPORTED;
+  const bool varlen = p->work != nullptr;
+  int tps = 0;
+  if (varlen) {
+    if (!p->seqlens || !p->part_off || p->n_items <= 0 || !p->o_partial) {
+      set_error("a work list needs seqlens, part_off, n_items > 0 and the partial buffers");
+      return AE_ERR_INVALID;
+    }
+  } else {
+    if (p->n_split < 1 || p->n_split > 32 || p->n_split > n_kt) return AE_ERR_INVALID;
+    tps = (n_kt + p->n_split - 1) / p->n_split;
+    if ((p->n_split - 1) * tps >= n_kt) {
+      set_error("n_split leaves a split without kv tiles");
+      return AE_ERR_INVALID;
+    }
+    if (p->n_split > 1 && !p->o_partial) return AE_ERR_INVALID;
   }
-  if (p->n_split > 1) {
-    if (!p->o_partial) return AE_ERR_INVALID;
+  if (varlen || p->n_split > 1)
     for (int i = 0; i < m->cfg.reserved[1] && i < AE_MAX_FINAL; ++i)
       if (!p->rowscale_partial[i]) return AE_ERR_INVALID;
+  if (p->block_table && (p->max_pages <= 0 || p->num_pages <= 0)) {
+    set_error("paged K / V need max_pages and num_pages");
+    return AE_ERR_INVALID;
   }
   rc = ensure_loaded(m);
   if (rc) return rc;
@@ -777,10 +801,23 @@ int ae_launch_attn_decode(void* module, const AeDecodeParams* p, void* stream) {
     rc = make_bshd_map(&args.tm_q, p->q, m->cfg.dtype, p->B, p->Sq, p->Hq, D, p->q_stride, 128);
   }
   if (rc) return rc;
-  rc = make_bshd_map(&args.tm_k, p->k, m->cfg.dtype, p->B, p->Skv, p->Hkv, D, p->k_stride, 128);
-  if (rc) return rc;
-  rc = make_bshd_map(&args.tm_v, p->v, m->cfg.dtype, p->B, p->Skv, p->Hkv, DV, p->v_stride, 128);
-  if (rc) return rc;
+  if (p->block_table) {
+    // pools [num_pages, 128, Hkv, D] seen as one batch of num_pages * 128 rows (a page's keys are contiguous rows)
+    if (p->k_stride[0] != 128 * p->k_stride[1] || p->v_stride[0] != 128 * p->v_stride[1]) {
+      set_error("paged K / V: a page must hold 128 keys at a constant stride");
+      return AE_ERR_INVALID;
+    }
+    const int64_t ks[3] = {0, p->k_stride[1], p->k_stride[2]}, vs[3] = {0, p->v_stride[1], p->v_stride[2]};
+    rc = make_bshd_map(&args.tm_k, p->k, m->cfg.dtype, 1, (int64_t)p->num_pages * 128, p->Hkv, D, ks, 128);
+    if (rc) return rc;
+    rc = make_bshd_map(&args.tm_v, p->v, m->cfg.dtype, 1, (int64_t)p->num_pages * 128, p->Hkv, DV, vs, 128);
+    if (rc) return rc;
+  } else {
+    rc = make_bshd_map(&args.tm_k, p->k, m->cfg.dtype, p->B, p->Skv, p->Hkv, D, p->k_stride, 128);
+    if (rc) return rc;
+    rc = make_bshd_map(&args.tm_v, p->v, m->cfg.dtype, p->B, p->Skv, p->Hkv, DV, p->v_stride, 128);
+    if (rc) return rc;
+  }
   if (reinterpret_cast<uintptr_t>(p->o) & 15) {
     set_error("output must be 16-byte aligned");
     return AE_ERR_INVALID;
@@ -807,7 +844,14 @@ int ae_launch_attn_decode(void* module, const AeDecodeParams* p, void* stream) {
   args.tiles_per_split = tps;
   args.gq = gq;
   args.rows = rows;
-  return launch(m, (unsigned)p->n_split, (unsigned)(gq > 1 ? p->Hkv : p->Hq), (unsigned)p->B, &args, stream);
+  args.work = reinterpret_cast<const AeWorkItem*>(p->work);
+  args.seqlens = p->seqlens;
+  args.part_off = p->part_off;
+  args.block_table = p->block_table;
+  args.max_pages = p->max_pages;
+  const unsigned units = (unsigned)(gq > 1 ? p->Hkv : p->Hq);
+  if (varlen) return launch(m, (unsigned)p->n_items, units, 1, &args, stream);
+  return launch(m, (unsigned)p->n_split, units, (unsigned)p->B, &args, stream);
 }
 
 int ae_launch_decode_combine(void* module, const AeDecodeParams* p, void* stream) {
@@ -817,7 +861,7 @@ int ae_launch_decode_combine(void* module, const AeDecodeParams* p, void* stream
     set_error("module kind does not match the entry point");
     return AE_ERR_UNSUPPORTED;
   }
-  if (p->n_split < 2 || p->n_split > 32 || m->cfg.head_dim_v % 4) return AE_ERR_INVALID;
+  if ((!p->part_off && (p->n_split < 2 || p->n_split > 32)) || m->cfg.head_dim_v % 4) return AE_ERR_INVALID;
   int rc = ensure_loaded(m);
   if (rc) return rc;
   AeMlaCombineArgs a;
@@ -829,6 +873,7 @@ int ae_launch_decode_combine(void* module, const AeDecodeParams* p, void* stream
   a.H = p->Sq * p->Hq;  // one output row per (query position, head)
   a.DV = m->cfg.head_dim_v;
   a.n_split = p->n_split;
+  a.part_off = p->part_off;  // rows of different lengths: each row's own number of partial slots
   return launch(m, (unsigned)((a.H + 3) / 4), (unsigned)p->B, 1, &a, stream);
 }
 

@@ -17,6 +17,13 @@ struct alignas(64) AeTmaDesc {
 #define AE_MAX_CUSTOM 4
 #define AE_MAX_FINAL 4
 
+struct alignas(16) AeWorkItem {  // one CTA's share of a split-KV decode over rows of different lengths
+  int row;         // batch row
+  int split;       // index of this share among the row's splits
+  int tile_begin;  // first 128-key tile
+  int n_tiles;     // tiles of this share (>= 1)
+};
+
 #ifdef AE_DEVICE
 // custom inputs as seen by the generated functors
 struct AeCustom {
@@ -48,6 +55,12 @@ struct AeAttnFwdArgs {
   float* fr_part[AE_MAX_FINAL];  // each [B, n_split, Sq * Hq]
   int n_split, tiles_per_split;
   int gq, rows;
+  // Rows of different lengths and paged K / V (decode build; all null = one length, dense K / V):
+  const AeWorkItem* work;  // [n_items]: one CTA per item and head unit
+  const int* seqlens;      // [B] keys of each row
+  const int* part_off;     // [B + 1] first partial-result slot of each row (its splits are consecutive slots)
+  const int* block_table;  // [B, max_pages] page of each 128-key tile of a row; K / V are then pools [pages * 128, Hkv, D]
+  int max_pages;
 };
 
 // ---- attention backward ------------------------------------------------------------
@@ -87,6 +100,7 @@ struct AeAttnBwdArgs {
   int n_qt, n_kt;
   u32* status;
   float* dq_acc;  // [B, Sq, Hq, D] fp32, contiguous: dQ accumulator of the one-pass backward (ae_attn_bwd_fused)
+  AeTmaDesc tm_dqacc;  // the same buffer as (d, s, h, b) fp32, box {32, 32, 1, 1}, 128-byte swizzle (TMA reduce-add)
 };
 
 // ---- MLA split-KV decode (kernels ae_mla_decode, ae_mla_combine) --------------------------
@@ -112,6 +126,8 @@ struct AeMlaCombineArgs {
   const float* o_part;
   const float* fr_part[AE_MAX_FINAL];
   int B, H, DV, n_split;
+  const int* part_off;  // [B + 1] or null: row b owns the partial slots part_off[b] .. part_off[b + 1] - 1 (at most 32);
+                        // null = n_split slots per row.  A row with a single slot was written directly and is skipped.
 };
 
 // ---- chunked linear attention / SSD scan forward (kernel ae_linear_fwd) -------------------

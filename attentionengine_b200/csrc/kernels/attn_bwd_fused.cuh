@@ -12,15 +12,21 @@
 //   row threads, phase B: dS^T = score_mod'(S^T) * backward(dP^T, P^T) -> SHARED memory, 16-bit, [kv][q] swizzled
 //   dQ_s = dS K   (SS: the dS^T tile read MN-major as A, K read MN-major as B) -> the TMEM columns of dP^T
 //   dK  += dS^T Q (SS: the same dS^T tile read K-major as A, Q read MN-major as B)
-//   row threads, drain: dQ_s (lanes = q rows) -> fp32 `red.global.add.v4.f32` into dq_acc [B, Sq, Hq, D]
+//   drain warps: dQ_s (lanes = q rows) -> fp32 staging boxes in shared memory -> TMA reduce-add
+//                (`cp.reduce.async.bulk.tensor ... .add`) into dq_acc [B, Sq, Hq, D].
+// Why TMA and warps of their own: the adds of a tile are 64 KB of fp32 and the L2 atomic units take about 16 bytes per
+// clock and SM of them (measured: `red.global.add.f32` from the 16 row warps, 128-byte coalesced, 4200 clk per tile
+// during which those warps do nothing else; from 4 dedicated warps 10500 clk, each warp waits ~80 clk per
+// instruction; 16-byte vector adds per thread 2x worse again).  A bulk reduce costs the issuing lane one instruction
+// per 4 KB and runs behind the row work.
 // TMEM columns: dK | dV | S^T / P^T | dP^T / dQ_s = 512 at head dim 128: dQ_s aliases dP^T, so dP^T of the next tile
 // is issued once the row threads have drained dQ_s.  Issue order of the MMA warp per tile s:
 //   [P^T written]  dV_s , S^T_{s+1}   [dS^T written]  dQ_s , dK_s   [dQ_s drained]  dP^T_{s+1}
-// and of the row threads: phase B(s), phase A(s+1) (under dQ_s / dK_s), drain(s), phase B(s+1).
+// and of the row threads: phase B(s), phase A(s+1) (under dQ_s / dK_s), phase B(s+1).
 // The fp32 accumulator dq_acc must be zero when the kernel starts (the launcher clears it); ae_attn_bwd_dq_cast turns
 // it into the 16-bit dQ.  Accumulation order across CTAs varies from run to run, so dQ is not bit-reproducible.
-// Roles: AE_FU_NWG row warpgroups (thread = kv row = TMEM lane in phases A / B, = q row in the drain; the groups take
-// alternate 32-column chunks), one producer warp, one MMA-issuing warp.
+// Roles: AE_FU_NWG row warpgroups (thread = kv row = TMEM lane; the groups take alternate 32-column chunks), one
+// producer warp, one MMA-issuing warp, four drain warps (one per 32 TMEM lanes).
 // Expects AE_FU_QSTAGES / AE_FU_DOSTAGES (ring depths), AE_FU_NWG (2 or 4), AE_FU_SMEM (the launch's dynamic bytes).
 
 #define AE_FU_BM 128  // kv rows per CTA
@@ -43,11 +49,15 @@
 #define AE_FU_SMEM_Q (AE_FU_SMEM_V + AE_FU_V_BYTES)
 #define AE_FU_SMEM_DO (AE_FU_SMEM_Q + AE_FU_QSTAGES * AE_FU_Q_BYTES)
 #define AE_FU_SMEM_DS (AE_FU_SMEM_DO + AE_FU_DOSTAGES * AE_FU_DO_BYTES)
-#define AE_FU_TILE_BYTES (AE_FU_SMEM_DS + AE_FU_DS_BYTES)
+// dQ staging: per drain warp two boxes of [32 q rows][32 floats] (128-byte rows, 128-byte swizzle: what the TMA reduce reads)
+#define AE_FU_DQS_BOX 4096
+#define AE_FU_SMEM_DQS (AE_FU_SMEM_DS + AE_FU_DS_BYTES)
+#define AE_FU_TILE_BYTES (AE_FU_SMEM_DQS + 4 * 2 * AE_FU_DQS_BOX)
 #define AE_FU_CS_BYTES (2 * AE_FU_BN * AE_NCS * 4)
 #define AE_FU_BAR_BYTES 256
 #define AE_FU_NROW (AE_FU_NWG * 128)
-#define AE_FU_NTHREADS (AE_FU_NROW + 64)
+#define AE_FU_NDRAIN 128  // threads of the drain warps
+#define AE_FU_NTHREADS (AE_FU_NROW + 64 + AE_FU_NDRAIN)
 
 struct AeFuBars {
   u64 kv_full;
@@ -320,7 +330,7 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
       if (s + 1 == n_steps) umma_commit_w(&bars->acc_done);
       AE_TRF(true, 0, s * 8 + 4)
       if (s + 1 < n_steps) {
-        named_bar_sync(3, AE_FU_NROW + 32);  // dQ_s has left TMEM
+        named_bar_sync(3, AE_FU_NDRAIN + 32);  // dQ_s has left TMEM
         tc_fence_after_sync();
         AE_TRF(true, 0, s * 8 + 5)
         ok = issue_dp(s + 1);
@@ -335,6 +345,67 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
            mbar_wait_w(&bars->q_empty[l % AE_FU_QSTAGES], (l / AE_FU_QSTAGES) & 1, ctl, args.status, 45) &&
            mbar_wait_w(&bars->do_empty[l % AE_FU_DOSTAGES], (l / AE_FU_DOSTAGES) & 1, ctl, args.status, 46);
     }
+  } else if (warp >= AE_FU_NWG * 4 + 2) {
+    // =============================== drain warps ================================
+    // dQ_s out of TMEM into the fp32 accumulator in global memory.  Warp w owns TMEM lanes 32 (w % 4) ... = 32 q rows of
+    // the tile and moves them as AE_D / 32 boxes of [32 rows][32 floats]: registers -> one of its two staging boxes ->
+    // TMA reduce-add, one bulk group per box.  A box is rewritten once the group that read it two boxes earlier has
+    // finished reading (wait_group.read 1).  The first two boxes go through staging at once, the others wait in
+    // registers, so the TMEM columns are handed back (named barrier 3) after two issues, not after the whole tile.
+    const u32 wq = warp & 3;
+    const u32 tm_dp = tmem + TM_DP + ((wq * 32) << 16);
+    u8* box0 = smem + AE_FU_SMEM_DQS + wq * (2 * AE_FU_DQS_BOX);
+    constexpr int NBOX = AE_D / 32;
+    constexpr int NKEEP = NBOX > 2 ? NBOX - 2 : 0;
+    bool ok = true;
+    AeFuStep st, st_next;
+    bool have = next_step(st);
+    if (lane == 0) tma_prefetch_desc(&args.tm_dqacc);
+    auto push_box = [&](const float (&v)[32], int c, const AeFuStep& stp) {
+      // slot c & 1: wait until the bulk group issued two boxes ago has read it, fill it, hand it to the TMA
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      __syncwarp();
+      u8* box = box0 + (c & 1) * AE_FU_DQS_BOX;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)
+        *(float4*)(box + swz128(lane, ch)) = make_float4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (ok)
+          asm volatile(
+              "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                  (u64)&args.tm_dqacc),
+              "r"(smem_u32(box)), "r"(c * 32), "r"(stp.q0 + (int)wq * 32), "r"(stp.hq), "r"(b)
+              : "memory");
+        tma_store_commit();  // an empty group when the CTA is aborting: the slot accounting stays the same
+      }
+    };
+    for (int s = 0; have; ++s) {
+      const bool more = next_step(st_next);
+      ok = ok && mbar_wait(&bars->dq_full, s & 1, ctl, args.status, 43);
+      tc_fence_after_sync();
+      AE_TRF(lane == 0, 5, s * 8 + wq * 2)
+      float keep[NKEEP > 0 ? NKEEP : 1][32];
+#pragma unroll
+      for (int c = 0; c < NBOX && c < 2; ++c) {
+        float v[32];
+        tmem_ld_f32x32(tm_dp + c * 32, v);
+        push_box(v, c, st);
+      }
+#pragma unroll
+      for (int c = 2; c < NBOX; ++c) tmem_ld_f32x32(tm_dp + c * 32, keep[c - 2]);
+      tc_fence_before_sync();
+      if (more) named_bar_arrive(3, AE_FU_NDRAIN + 32);  // the columns may be overwritten by the next dP^T
+#pragma unroll
+      for (int c = 2; c < NBOX; ++c) push_box(keep[c - 2], c, st);
+      AE_TRF(lane == 0, 5, s * 8 + wq * 2 + 1)
+      st = st_next;
+      have = more;
+    }
+    // the staging boxes belong to this CTA until the bulk engine has read them; the adds themselves complete on their own
+    if (lane == 0) tma_store_wait_read();
+    __syncwarp();
   } else {
     // =============================== row threads ================================
     const int wg = warp >> 2;  // the row warpgroups split every tile by 32-column chunks
@@ -485,37 +556,6 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
       AE_TRF((warp & 3) == 0, 1 + wg, s * 8 + 4)
     };
 
-    // ---- drain of step s: dQ_s rows (this thread's TMEM lane is q row `row` of the tile) -> fp32 adds ------
-    auto drain_step = [&](const AeFuStep& st, int s, bool more) {
-      ok = ok && mbar_wait(&bars->dq_full, s & 1, ctl, args.status, 43);
-      tc_fence_after_sync();
-      AE_TRF((warp & 3) == 0, 1 + wg, s * 8 + 5)
-      const int q_idx = st.q0 + (int)row;
-      const bool add = ok && q_idx < args.Sq;
-      float* dst = args.dq_acc + (((i64)b * args.Sq + (add ? q_idx : 0)) * args.Hq + st.hq) * AE_D;
-      constexpr int NDQ = (AE_D / 32 + AE_FU_NWG - 1) / AE_FU_NWG;
-      float r[NDQ][32];
-#pragma unroll
-      for (int ci = 0; ci < NDQ; ++ci) {
-        const int cc = wg + AE_FU_NWG * ci;
-        if (cc < AE_D / 32) tmem_ld_f32x32(tm_dp + cc * 32, r[ci]);  // warp-uniform condition
-      }
-      tc_fence_before_sync();
-      if (more) named_bar_arrive(3, AE_FU_NROW + 32);  // the columns may be overwritten by the next dP^T
-#pragma unroll
-      for (int ci = 0; ci < NDQ; ++ci) {
-        const int cc = wg + AE_FU_NWG * ci;
-        if (cc < AE_D / 32 && add) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + cc * 32 + i), "f"(r[ci][i]),
-                         "f"(r[ci][i + 1]), "f"(r[ci][i + 2]), "f"(r[ci][i + 3])
-                         : "memory");
-        }
-      }
-      AE_TRF((warp & 3) == 0, 1 + wg, s * 8 + 6)
-    };
-
     int s = 0;
     AeFuStep st, st_next;
     bool have = next_step(st);
@@ -524,7 +564,6 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
       phase_b_step(st, s);
       const bool more = next_step(st_next);
       if (more) phase_a_step(st_next, s + 1);
-      drain_step(st, s, more);
       st = st_next;
       have = more;
       ++s;

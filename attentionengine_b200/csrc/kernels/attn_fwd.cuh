@@ -26,8 +26,8 @@
 #ifndef AE_DECODE
 #define AE_DECODE 0  // 1: split-KV decode (reference: attn_decode_tl.py:34-141 / attn_gqa_decode_tl.py), see AeAttnFwdArgs
 #endif
-#if AE_DECODE && AE_MASK_MODE != 0
-#error "the decode build takes no mask"
+#if AE_DECODE && AE_MASK_MODE != 0 && AE_MASK_MODE != 3
+#error "the decode build takes no mask, or an element-wise one (mask mode 3)"
 #endif
 #ifndef AE_NQ
 #define AE_NQ 2  // q tiles held in shared memory; 1 in a decode build whose head units have at most 128 rows (the
@@ -92,13 +92,35 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
   const u32 lane = threadIdx.x & 31;
 
 #if AE_DECODE
-  const int split = blockIdx.x;
+  // Uniform split: CTA (split, head unit, batch row).  With a work list (rows of different lengths, args.work): CTA
+  // (item, head unit), item = {batch row, split of that row, first kv tile, kv tiles}; the row's length comes from
+  // args.seqlens and its partial results go to slot args.part_off[row] + split.
   const int hq = blockIdx.y;  // head unit: a kv head (gq > 1) or a head with its own K/V (gq == 1)
-  const int b = blockIdx.z;
   const int hk = hq;
   const int qt0 = 0;
-  const int kt_off = split * args.tiles_per_split;
+  int split, b, kt_off, dec_tiles, skv, part_slot;
+  bool staged;
+  if (args.work) {
+    const AeWorkItem w = args.work[blockIdx.x];
+    b = w.row;
+    split = w.split;
+    kt_off = w.tile_begin;
+    dec_tiles = w.n_tiles;
+    skv = args.seqlens[b];
+    part_slot = args.part_off[b] + split;
+    staged = args.part_off[b + 1] - args.part_off[b] > 1;
+  } else {
+    split = blockIdx.x;
+    b = blockIdx.z;
+    kt_off = split * args.tiles_per_split;
+    dec_tiles = args.n_kt - kt_off < args.tiles_per_split ? args.n_kt - kt_off : args.tiles_per_split;
+    skv = args.Skv;
+    part_slot = b * args.n_split + split;
+    staged = args.n_split > 1;
+  }
+#define AE_SKV skv
 #else
+#define AE_SKV args.Skv
   // heaviest (latest) q tiles first: better tail under a causal mask
   const int qpair = (int)gridDim.x - 1 - (int)blockIdx.x;
   const int hq = blockIdx.y;
@@ -118,7 +140,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
   const u32* steps = (const u32*)(smem + AE_SMEM_STEPS);
   n_steps = 0;  // read from shared memory after the set-up barrier
 #elif AE_DECODE
-  int n_t0 = args.n_kt - kt_off < args.tiles_per_split ? args.n_kt - kt_off : args.tiles_per_split;
+  int n_t0 = dec_tiles;
   int n_t1 = (1 < args.n_qt) ? n_t0 : 0;
   n_steps = n_t0;
 #else
@@ -266,16 +288,24 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       while (next_step(st)) {
         const int stage = it % AE_STAGES;
         const u32 par = ((it / AE_STAGES) & 1) ^ 1;
+#if AE_DECODE
+        // paged K / V (args.block_table): the pool is one batch of num_pages * 128 rows, tile kt of row b is a page
+        const int kv_row0 = args.block_table ? args.block_table[(i64)b * args.max_pages + st.kt] * AE_BN : st.kt * AE_BN;
+        const int kv_b = args.block_table ? 0 : b;
+#else
+        const int kv_row0 = st.kt * AE_BN;
+        const int kv_b = b;
+#endif
         if (!mbar_wait(&bars->k_empty[stage], par, ctl, args.status, 1)) break;
         mbar_arrive_expect_tx(&bars->k_full[stage], AE_K_BYTES);
         for (int dh = 0; dh < AE_D / 64; ++dh)
           tma_load_bshd(smem + AE_SMEM_K + stage * AE_K_BYTES + dh * (AE_BN * 128), &args.tm_k, &bars->k_full[stage],
-                      dh * 64, hk, st.kt * AE_BN, b);
+                      dh * 64, hk, kv_row0, kv_b);
         if (!mbar_wait(&bars->v_empty[stage], par, ctl, args.status, 2)) break;
         mbar_arrive_expect_tx(&bars->v_full[stage], AE_V_BYTES);
         for (int dh = 0; dh < AE_DV / 64; ++dh)
           tma_load_bshd(smem + AE_SMEM_V + stage * AE_V_BYTES + dh * (AE_BN * 128), &args.tm_v, &bars->v_full[stage],
-                      dh * 64, hk, st.kt * AE_BN, b);
+                      dh * 64, hk, kv_row0, kv_b);
         ++it;
       }
     }
@@ -510,20 +540,20 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       float s[AE_BN];
       tmem_ld_f32x128(tm_s_n, s);
       const int kv0 = step.kt * AE_BN;
-      const bool tail = (kv0 + AE_BN > args.Skv);
+      const bool tail = (kv0 + AE_BN > AE_SKV);
       const bool partial = (step.flags >> (2 + t)) & 1u;
       if (partial || tail) {
 #pragma unroll
         for (int c = 0; c < AE_BN; ++c) {
           const int kv_idx = kv0 + c;
-          bool keep = kv_idx < args.Skv;
+          bool keep = kv_idx < AE_SKV;
 #if AE_MASK_MODE != 0
           if (partial) keep = keep && ae_mask(b, h_row, q_idx, kv_idx);
 #endif
 #if AE_MASK_NEG_INF
           if (!keep) s[c] = -__int_as_float(0x7f800000);
 #else
-          if (kv_idx >= args.Skv) s[c] = 0.f;  // additive mask value 0: scores stay as they are
+          if (kv_idx >= AE_SKV) s[c] = 0.f;  // additive mask value 0: scores stay as they are
           (void)keep;
 #endif
         }
@@ -574,9 +604,8 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       u16* orow = (u16*)args.o + (i64)b * args.o_sb + (i64)(store ? q_idx : 0) * args.o_ss + (i64)h_row * args.o_sh;
 #if AE_DECODE
       // more than one split: this split's normalised O and final row scales go to fp32 staging, merged by the combine pass
-      const i64 part_row = ((i64)b * args.n_split + split) * ((i64)args.Sq * args.Hq) + (i64)q_idx * args.Hq + h_row;
+      const i64 part_row = (i64)part_slot * ((i64)args.Sq * args.Hq) + (i64)q_idx * args.Hq + h_row;
       float* prow = args.o_part + part_row * AE_DV;
-      const bool staged = args.n_split > 1;
 #endif
 #pragma unroll
       for (int c = 0; c < AE_DV / 32; ++c) {

@@ -24,23 +24,25 @@ extern "C" __global__ void __launch_bounds__(128) ae_mla_combine(const AeMlaComb
   const int h = blockIdx.x * 4 + warp;
   const int b = blockIdx.y;
   if (h >= args.H) return;  // warp-uniform
+  const int n_split = args.part_off ? args.part_off[b + 1] - args.part_off[b] : args.n_split;
+  const i64 slot0 = args.part_off ? (i64)args.part_off[b] : (i64)b * args.n_split;
+  if (args.part_off && n_split <= 1) return;  // written directly by the split kernel
   float fr[AE_NFINAL > 0 ? AE_NFINAL : 1];
 #pragma unroll
   for (int i = 0; i < AE_NFINAL; ++i)
-    fr[i] = lane < args.n_split ? args.fr_part[i][((i64)b * args.n_split + lane) * args.H + h]
-                                : -__int_as_float(0x7f800000);
+    fr[i] = lane < n_split ? args.fr_part[i][(slot0 + lane) * args.H + h] : -__int_as_float(0x7f800000);
   float w = ae_combine(fr);
-  if (lane >= args.n_split) w = 0.f;
+  if (lane >= n_split) w = 0.f;
   u16* orow = (u16*)args.o + ((i64)b * args.H + h) * args.DV;
   // the loop bounds are warp-uniform: every lane takes part in the shuffles, also when DV < 128 leaves it no columns
   for (int base = 0; base < args.DV; base += 128) {
     const int d0 = base + lane * 4;
     const bool active = d0 < args.DV;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int k = 0; k < args.n_split; ++k) {
+    for (int k = 0; k < n_split; ++k) {
       const float wk = __shfl_sync(0xffffffffu, w, k);
       if (active) {
-        const float4 v = *(const float4*)(args.o_part + (((i64)b * args.n_split + k) * args.H + h) * args.DV + d0);
+        const float4 v = *(const float4*)(args.o_part + ((slot0 + k) * args.H + h) * args.DV + d0);
         acc.x += wk * v.x;
         acc.y += wk * v.y;
         acc.z += wk * v.z;

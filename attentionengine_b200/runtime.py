@@ -84,7 +84,9 @@ class DecodeParams(C.Structure):
                 ("o_partial", C.c_void_p), ("rowscale_partial", C.c_void_p * AE_MAX_FINAL),
                 ("custom", C.c_void_p * AE_MAX_CUSTOM), ("custom_stride", (C.c_int64 * 4) * AE_MAX_CUSTOM),
                 ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("Sq", C.c_int32), ("Skv", C.c_int32),
-                ("n_split", C.c_int32), ("status", C.c_void_p)]
+                ("n_split", C.c_int32), ("status", C.c_void_p),
+                ("work", C.c_void_p), ("n_items", C.c_int32), ("seqlens", C.c_void_p), ("part_off", C.c_void_p),
+                ("block_table", C.c_void_p), ("max_pages", C.c_int32), ("num_pages", C.c_int32)]
 
 
 class RowScaleParams(C.Structure):

@@ -5,8 +5,9 @@
 Workload (one "step"): causal softmax attention forward + backward at the Llama-3.1-8B GQA shape
 B=8, Hq=32, Hkv=8, S=8192, D=DV=128, fp16, synthetic N(0,1) inputs.  FLOPs follow the reference's
 convention (attention_engine/benchmark/bench_utils.py:1185-1188): forward 4*B*Hq*S^2*D/2, backward
-2.5x that.  With N GPUs every rank runs the whole workload on its own data (independent (batch, head)
-shards, no collective on the data path): weak scaling, value = N * flops / max-over-ranks time.
+2.5x that.  With N GPUs the B=8 workload is sharded by batch rows over the ranks (8 / N rows each; independent
+(batch, kv-group) units, no collective on the data path): strong scaling, value = flops of the whole workload /
+max-over-ranks time.  ``--scaling weak`` runs the whole workload on every rank instead (value = N * flops / time).
 
 One JSON line is printed by rank 0.  ``--impl reference`` times the reference's naive PyTorch path
 (restated in oracle/attention_oracle.py) on the host cores on a bounded slice of the same workload.
@@ -42,10 +43,19 @@ def max_over_ranks(value: float, device=None) -> float:
 
 
 def aggregate_throughput(work_per_rank: float, ms_local: float, world: int, device=None) -> tuple:
-    """Weak scaling: every rank does ``work_per_rank``; the job's throughput is the total work over the slowest
-    rank's time.  Returns (units per second, that time in ms)."""
+    """Every rank does ``work_per_rank`` (its shard under strong scaling, a full copy under weak scaling); the job's
+    throughput is the total work over the slowest rank's time.  Returns (units per second, that time in ms)."""
     ms = max_over_ranks(ms_local, device)
     return world * work_per_rank / (ms / 1e3), ms
+
+
+def shard_batch(total: int, world: int, scaling: str) -> int:
+    """Batch rows per rank: the stated workload split over the ranks (strong), or all of it on each (weak)."""
+    if scaling == "weak" or world == 1:
+        return total
+    if total % world:
+        raise SystemExit(f"--gpus {world} does not divide the workload's {total} batch rows")
+    return total // world
 
 
 def read_peaks():
@@ -171,18 +181,18 @@ def run_reference(args, rank, world):
     value = fl / (ms / 1e3) / 1e12
     sample = "4 of 64 (batch, kv-group) slices per step: 4 q-heads x S=8192 x D=128 vs one kv-head, fwd+bwd, fp32"
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "llama3.1-8b-gqa causal softmax attention fwd+bwd, B=8 Hq=32 Hkv=8 S=8192 D=128 fp16",
-                       "sample": sample},
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "llama3.1-8b-gqa causal softmax attention fwd+bwd, B=8 Hq=32 Hkv=8 S=8192 D=128 fp16"},
             "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch at B=2, Hq=32, Hkv=8, S=8192, D=128 (ncu, one B200)
-NCU_DRAM_BYTES_AT_BATCH2 = {"ae_attn_fwd": 301.5e6, "ae_attn_bwd_dq": 450.9e6, "ae_attn_bwd_dkv": 396.6e6,
-                            "ae_attn_bwd_prep": 273.6e6}
+# kernel -> (batch of the capture, dram__bytes_read.sum + dram__bytes_write.sum of one launch) at Hq=32, Hkv=8,
+# S=8192, D=128, from ncu captures on one B200 (the summaries under profiles/ name the commands)
+NCU_DRAM_BYTES = {"ae_attn_fwd": (2, 301.5e6), "ae_attn_bwd_dq": (2, 450.9e6), "ae_attn_bwd_dkv": (2, 396.6e6),
+                  "ae_attn_bwd_prep": (2, 273.6e6), "ae_attn_bwd_fused": (1, 475.2e6)}
 
 
 def time_events(torch, fn, steps, warmup):
@@ -345,6 +355,9 @@ def main():
     ap.add_argument("--workload", default="cfg2", help="cfg2 (the headline, default) | cfg3_sigmoid | cfg3_relu | cfg4 | cfg5 | gqa_decode")
     ap.add_argument("--batch", type=int, default=None,
                     help="batch size; default = the benchmark's (8; cfg5: 128). Smaller values are for ncu captures")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N > 1: split the workload's batch rows over the ranks (strong) or replicate it (weak)")
+    ap.add_argument("--bwd", default=None, choices=["fused", "split"], help="backward form (default: the package's)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -359,20 +372,26 @@ def main():
             run_other(args)
         return
 
+    import ctypes as C
+
     import torch
     import torch.distributed as dist
     from attentionengine_b200 import examples as helpers
     from attentionengine_b200 import runtime as rt
+    from attentionengine_b200.attn_engine import attn_bwd as ab
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    B, Hq, Hkv, S, D = (CFG[k] for k in ("B", "Hq", "Hkv", "S", "D"))
-    B = args.batch or CFG["B"]
+    Hq, Hkv, S, D = (CFG[k] for k in ("Hq", "Hkv", "S", "D"))
+    B_total = args.batch or CFG["B"]
+    B = shard_batch(B_total, world, args.scaling)
+    mode = args.bwd or ab.DEFAULT_MODE
     dt = torch.float16
     eng = helpers.softmax_engine(B, Hq, Hkv, S, D, D, dt, True)
-    eng.kernels.bwd  # compile / load before timing
+    eng.bwd_mode = mode
+    kern = eng.kernels.bwd_fused if mode == "fused" else eng.kernels.bwd  # compile / load before timing
 
     gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
     host = {}
@@ -411,21 +430,21 @@ def main():
     ms = e0.elapsed_time(e1) / args.steps
     clocks = sampler.stop() if sampler else None
     eng.check_status()
-    fl_step = 3.5 * flops_fwd(B, Hq, S, D)
+    fl_step = 3.5 * flops_fwd(B, Hq, S, D)  # this rank's share
     per_s, ms = aggregate_throughput(fl_step, ms, world, dev)
     value = per_s / 1e12
 
     # ---- end to end: host buffers in, host buffers out, through the public operator call ----------
     # One operator call per batch row; the row's H2D copies, its forward + backward and its D2H copies run on
-    # three streams, so copies of neighbouring rows overlap the kernels (PCIe moves 1.34 GB each way per step).
+    # three streams, so copies of neighbouring rows overlap the kernels.  The same loop without the operator call
+    # gives the time the copies alone need on this host (`copy_only_ms`): the floor of any end-to-end figure.
     out_host = {n: torch.empty_like(host[n]).pin_memory() for n in ("q", "k", "v", "do")}
     eng1 = helpers.softmax_engine(1, Hq, Hkv, S, D, D, dt, True)
-    eng1.kernels.bwd
+    eng1.bwd_mode = mode
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    main = torch.cuda.current_stream(dev)
+    main_s = torch.cuda.current_stream(dev)
 
-    def step_e2e():
-        pending = []
+    def step_e2e(compute=True):
         for bi in range(B):
             with torch.cuda.stream(s_in):
                 qd = host["q"][bi:bi + 1].to(dev, non_blocking=True)
@@ -434,51 +453,55 @@ def main():
                 dod = host["do"][bi:bi + 1].to(dev, non_blocking=True)
                 ready = torch.cuda.Event()
                 ready.record(s_in)
-            main.wait_event(ready)
+            main_s.wait_event(ready)
             for t_ in (qd, kd, vd, dod):
-                t_.record_stream(main)
-            qd.requires_grad_(); kd.requires_grad_(); vd.requires_grad_()
-            o = eng1(qd, kd, vd)
-            o.backward(dod)
+                t_.record_stream(main_s)
+            if compute:
+                qd.requires_grad_(); kd.requires_grad_(); vd.requires_grad_()
+                o = eng1(qd, kd, vd)
+                o.backward(dod)
+                res = (o.detach(), qd.grad, kd.grad, vd.grad)
+            else:
+                res = (dod, qd, kd, vd)
             done = torch.cuda.Event()
-            done.record(main)
+            done.record(main_s)
             s_out.wait_event(done)
             with torch.cuda.stream(s_out):
-                res = (o.detach(), qd.grad, kd.grad, vd.grad)
                 for t_ in res:
                     t_.record_stream(s_out)
                 out_host["do"][bi:bi + 1].copy_(res[0], non_blocking=True)
                 out_host["q"][bi:bi + 1].copy_(res[1], non_blocking=True)
                 out_host["k"][bi:bi + 1].copy_(res[2], non_blocking=True)
                 out_host["v"][bi:bi + 1].copy_(res[3], non_blocking=True)
-            pending.append(res)
-        main.wait_stream(s_out)
+        main_s.wait_stream(s_out)
+
+    def time_e2e(compute, n):
+        step_e2e(compute)
+        barrier()
+        e0.record()
+        for _ in range(n):
+            step_e2e(compute)
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / n, dev)
 
     n_e2e = 0 if args.no_e2e else max(1, min(args.steps, 3))
+    e2e = None
     if n_e2e:
-        step_e2e()
-    barrier()
-    e0.record()
-    for _ in range(n_e2e):
-        step_e2e()
-    e1.record()
-    barrier()
-    ms_e2e = e0.elapsed_time(e1) / max(n_e2e, 1)
-    ms_e2e = max_over_ranks(ms_e2e, dev)
-    io_bytes = sum(host[n].numel() * 2 for n in host)
-    e2e = None if not n_e2e else {"value": world * fl_step / (ms_e2e / 1e3) / 1e12, "unit": "TFLOPS",
-                                  "ms_per_step": ms_e2e, "h2d_bytes_per_step": io_bytes,
-                                  "d2h_bytes_per_step": io_bytes,
-                                  "gpu_launches": 4 * B * n_e2e,
-                                  "how": "per batch row: H2D, operator call + backward, D2H on three streams"}
-    eng1.check_status()
+        ms_e2e = time_e2e(True, n_e2e)
+        ms_copy = time_e2e(False, n_e2e)
+        io_bytes = sum(host[n].numel() * 2 for n in host)
+        e2e = {"value": world * fl_step / (ms_e2e / 1e3) / 1e12, "unit": "TFLOPS", "ms_per_step": ms_e2e,
+               "copy_only_ms": ms_copy, "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
+               "gpu_launches": 4 * B * n_e2e,
+               "how": "per batch row: H2D, operator call + backward, D2H on three streams; copy_only_ms = the same "
+                      "loop without the operator call (the host-link floor); bytes are per rank"}
+        eng1.check_status()
 
     # ---- per-kernel times (CUDA events on the launching stream) and the roofline of the longest one -----
     kernels = {}
     if rank == 0:
         o, finals = eng._launch_fwd(q.detach(), k.detach(), v.detach(), ())
-        import ctypes as C
-        from attentionengine_b200.attn_engine import attn_bwd as ab
 
         def time_call(fn, n=3):
             fn()
@@ -494,9 +517,8 @@ def main():
         gemm = flops_fwd(B, Hq, S, D) / 2  # one S x S x D contraction over the causal half
         kernels["ae_attn_fwd"] = {"ms": time_call(lambda: eng._launch_fwd(q.detach(), k.detach(), v.detach(), ())),
                                   "flops": 2 * gemm}
-        # backward launches one by one
+        # backward launches one by one, through the C ABI
         L = rt.lib()
-        kern = eng.kernels.bwd
         p = rt.AttnBwdParams()
         qd, kd, vd = q.detach(), k.detach(), v.detach()
         dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
@@ -513,10 +535,19 @@ def main():
         st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         kernels["ae_attn_bwd_prep"] = {"ms": time_call(lambda: rt.check(L.ae_launch_attn_bwd_prep(kern.prep.handle, C.byref(p), st))),
                                        "flops": 0.0, "bytes": 2.0 * B * S * Hq * D * 2 + B * Hq * S * 4}
-        kernels["ae_attn_bwd_dq"] = {"ms": time_call(lambda: rt.check(L.ae_launch_attn_bwd_dq(kern.dq.handle, C.byref(p), st))),
-                                     "flops": 1 * gemm, "executed_flops": 3 * gemm}
-        kernels["ae_attn_bwd_dkv"] = {"ms": time_call(lambda: rt.check(L.ae_launch_attn_bwd_dkv(kern.dkv.handle, C.byref(p), st))),
-                                      "flops": 4 * gemm, "executed_flops": 4 * gemm}
+        if mode == "fused":
+            acc = torch.empty(B, S, Hq, D, dtype=torch.float32, device=dev)
+            p.dq_accum = acc.data_ptr()
+            # the launcher clears the fp32 accumulator on the stream before the kernel: that clear is inside this time
+            kernels["ae_attn_bwd_fused"] = {"ms": time_call(lambda: rt.check(L.ae_launch_attn_bwd_fused(kern.fused.handle, C.byref(p), st))),
+                                            "flops": 5 * gemm, "executed_flops": 5 * gemm}
+            kernels["ae_attn_bwd_dq_cast"] = {"ms": time_call(lambda: rt.check(L.ae_launch_attn_bwd_dq_cast(kern.cast.handle, C.byref(p), st))),
+                                              "flops": 0.0, "bytes": B * S * Hq * D * 6.0}
+        else:
+            kernels["ae_attn_bwd_dq"] = {"ms": time_call(lambda: rt.check(L.ae_launch_attn_bwd_dq(kern.dq.handle, C.byref(p), st))),
+                                         "flops": 1 * gemm, "executed_flops": 3 * gemm}
+            kernels["ae_attn_bwd_dkv"] = {"ms": time_call(lambda: rt.check(L.ae_launch_attn_bwd_dkv(kern.dkv.handle, C.byref(p), st))),
+                                          "flops": 4 * gemm, "executed_flops": 4 * gemm}
         eng.check_status()
 
     if rank == 0:
@@ -526,10 +557,10 @@ def main():
         peak = float(peaks.get("bf16_tflops", 1590.0))
         roofline = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                     "frac": ach / peak, "peak_source": f"{which} cuBLAS bf16 burst",
-                    # DRAM bytes per launch of that kernel (dram__bytes_read.sum + dram__bytes_write.sum): taken from an
-                    # ncu capture at batch 2 (profiles/attention_kernels_cfg2_batch2.md) and scaled by the batch, to
-                    # which the traffic is proportional
-                    "traffic": NCU_DRAM_BYTES_AT_BATCH2.get(dom, 0.0) * (B / 2.0) or None,
+                    # DRAM bytes per launch of that kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
+                    # capture at the batch size of NCU_DRAM_BYTES), scaled by the batch, to which it is proportional
+                    "traffic": (NCU_DRAM_BYTES[dom][1] * (B / NCU_DRAM_BYTES[dom][0])) if dom in NCU_DRAM_BYTES else None,
+                    "whole_step_frac": value / world / peak,
                     "kernels": {n: {"ms": round(d["ms"], 4), "tflops": round(d["flops"] / (d["ms"] / 1e3) / 1e12, 1)}
                                 for n, d in kernels.items()}}
         cpu = None
@@ -538,13 +569,15 @@ def main():
             tf, t = cpu_sample(16, threads)
             cpu = {"value": tf, "unit": "TFLOPS", "cores": threads, "kind": "port", "seconds": round(t, 2),
                    "sample": "16 of 64 (batch, kv-group) slices: 4 q-heads x S=8192 x D=128 vs one kv-head, fwd+bwd, fp32 torch"}
+        n_launch = (4 if mode == "fused" else 4) * args.steps  # fwd, prep, fused + cast | fwd, prep, dQ pass, dK/dV pass
         line = {"metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": args.scaling,
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": f"llama3.1-8b-gqa causal softmax attention fwd+bwd, B={B} Hq=32 Hkv=8 S=8192 D=128 fp16",
-                           "per_gpu_batch": B, "l2": "inputs (1.3 GB per step) larger than L2",
-                           "flops_per_step": fl_step, "frac_of_nominal_fp16_peak": value / world / 2250.0},
-                "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps, "roofline": roofline,
+                "config": {"workload": f"llama3.1-8b-gqa causal softmax attention fwd+bwd, B={B_total} Hq=32 Hkv=8 S=8192 D=128 fp16",
+                           "per_gpu_batch": B, "backward": mode,
+                           "l2": f"inputs ({1.34 * B / 8:.2f} GB per rank and step) larger than L2",
+                           "flops_per_step": fl_step * world, "frac_of_nominal_fp16_peak": value / world / 2250.0},
+                "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch, "roofline": roofline,
                 "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)
     if world > 1:

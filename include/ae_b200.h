@@ -249,7 +249,20 @@ int ae_launch_mla_decode_paged(void* module, const AeMlaPagedParams* p, void* st
  * ceil(n_kv_tiles / n_split) kv tiles of 128 keys (the caller chooses n_split so that no split is
  * empty); n_split == 1 writes `o` directly, otherwise the splits write normalised fp32 partials and
  * their final row scales, and `ae_launch_decode_combine` (module kind AE_KIND_MLA_COMBINE, the traced
- * `OnlineFunc.combine`) merges them into `o`.  No mask.  `o` is contiguous. */
+ * `OnlineFunc.combine`) merges them into `o`.  `o` is contiguous.  A module built with mask mode 3 applies the
+ * traced mask_mod element by element (the dense mask input of the reference's TL decode,
+ * core/lower/lower_decode_gqa.py:390-396).
+ * Rows of different lengths (the varlen scheduling of the reference's kv-shared path,
+ * cute_template_kvshared/kernels/get_mla_metadata.cu:8-75, flash_mla_interface.py:73-113): give `seqlens`, a
+ * work list and `part_off`.  Each work item is one CTA's share {row, split of that row, first 128-key tile,
+ * tiles}; row b's shares write the partial slots part_off[b] .. part_off[b + 1] - 1 (at most 32), a row with one
+ * share writes `o` directly.  Build the list so that every share has about the same number of tiles
+ * (attentionengine_b200/attn_engine/attn_decode.py: `schedule`).  Skv is then the longest row.
+ * Paged K / V: give `block_table` [B, max_pages] (page = 128 keys = one tile); k / v are then pools
+ * [num_pages, 128, Hkv, D] and k_stride / v_stride their (page, key, head) strides. */
+typedef struct AeDecodeWorkItem {
+  int32_t row, split, tile_begin, n_tiles;
+} AeDecodeWorkItem;
 typedef struct AeDecodeParams {
   const void* q; /* [B, Sq, Hq, D]    */
   const void* k; /* [B, Skv, Hkv, D]  */
@@ -262,6 +275,13 @@ typedef struct AeDecodeParams {
   int64_t custom_stride[AE_MAX_CUSTOM_INPUTS][4];
   int32_t B, Hq, Hkv, Sq, Skv, n_split;
   uint32_t* status;
+  /* optional (all null / 0 = one length, dense K / V, n_split shares per row) */
+  const AeDecodeWorkItem* work; /* [n_items] */
+  int32_t n_items;
+  const int32_t* seqlens;     /* [B] */
+  const int32_t* part_off;    /* [B + 1]; o_partial / rowscale_partial then hold part_off[B] slots */
+  const int32_t* block_table; /* [B, max_pages] */
+  int32_t max_pages, num_pages;
 } AeDecodeParams;
 
 int ae_launch_attn_decode(void* module, const AeDecodeParams* p, void* stream);

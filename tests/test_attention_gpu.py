@@ -682,3 +682,77 @@ def test_backward_uses_the_block_mask_of_its_own_forward():
         ro, grads = orc.fwd_bwd(ref, (q, k, v), d_o)
         for name, got, r in zip(("o", "dq", "dk", "dv"), (o, *[t.grad for t in leaves]), (ro, *grads)):
             _check(name, got.detach().cpu(), r, dtype)
+
+
+# ---------------------------------------------------------------------------------------------------
+# split-KV decode: rows of different lengths, paged K / V, mask
+# ---------------------------------------------------------------------------------------------------
+def _ragged_ref(q, k, v, lens, keep=None):
+    outs = []
+    for b, L in enumerate(lens):
+        qb, kb, vb = q[b:b + 1].float(), k[b:b + 1, :L].float(), v[b:b + 1, :L].float()
+        g = qb.shape[2] // kb.shape[2]
+        s = torch.einsum("bqhd,bkhd->bhqk", qb, kb.repeat_interleave(g, 2)) / math.sqrt(qb.shape[-1])
+        if keep is not None:
+            s = s.masked_fill(~keep(L), float("-inf"))
+        outs.append(torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), vb.repeat_interleave(g, 2)))
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_gqa_decode_rows_of_different_lengths(paged, bwd_mode):
+    """Lengths from one key to 4000 in one batch: the schedule gives long rows several shares and short rows one;
+    dense K / V [B, S_max, ...] or a shuffled pool of 128-key pages with a block table."""
+    if bwd_mode == "fused":
+        pytest.skip("forward only")
+    B, Hq, Hkv, D, dtype = 5, 32, 8, 128, torch.float16
+    lens = [1, 4000, 129, 1000, 2048]
+    S_max = 4096
+    eng = helpers.decode_engine("B", Hq, Hkv, 1, "S_kv", D, dtype)
+    g = torch.Generator().manual_seed(90)
+    q = torch.randn(B, 1, Hq, D, generator=g).to(dtype)
+    k = torch.randn(B, S_max, Hkv, D, generator=g).to(dtype)
+    v = torch.randn(B, S_max, Hkv, D, generator=g).to(dtype)
+    meta = eng.decode_schedule(torch.tensor(lens), device="cuda")
+    assert meta["n_slots"] > B and int(meta["part_off"][2] - meta["part_off"][1]) > 1
+    if paged:
+        n_pages = B * (S_max // 128)
+        perm = torch.randperm(n_pages, generator=g)
+        table = perm.view(B, S_max // 128).to(torch.int32)
+        kp = torch.empty(n_pages, 128, Hkv, D, dtype=dtype)
+        vp = torch.empty(n_pages, 128, Hkv, D, dtype=dtype)
+        kp[perm] = k.view(n_pages, 128, Hkv, D)
+        vp[perm] = v.view(n_pages, 128, Hkv, D)
+        o = eng.decode_varlen(q.cuda(), kp.cuda(), vp.cuda(), None, block_table=table.cuda(), metadata=meta)
+    else:
+        o = eng.decode_varlen(q.cuda(), k.cuda(), v.cuda(), None, metadata=meta)
+    torch.cuda.synchronize()
+    eng.check_status()
+    _check("o", o.cpu(), _ragged_ref(q, k, v, lens), dtype)
+
+
+def test_mha_decode_with_a_mask_and_ragged_rows(bwd_mode):
+    """mha_inference.py shape class (Hq == Hkv, several query positions) with a mask_mod applied element by element:
+    a sliding window over the keys, rows of different lengths."""
+    if bwd_mode == "fused":
+        pytest.skip("forward only")
+    B, H, Sq, D, dtype, W = 3, 4, 3, 64, torch.bfloat16, 300
+    lens = [700, 77, 1500]
+    scale = 1 / math.sqrt(D)
+    metas = (helpers.meta_tensor(B, H, Sq, D, dtype=dtype), helpers.meta_tensor(B, H, 2048, D, dtype=dtype),
+             helpers.meta_tensor(B, H, 2048, D, dtype=dtype))
+    eng = AttentionEngine(metas, CustomIO({}), score_mod=lambda s, c, b, h, q, kv: s * scale,
+                          mask_mod=lambda b, h, q_idx, kv_idx: kv_idx % 512 < W, online_func=helpers.OnlineSoftmaxSplit())
+    g = torch.Generator().manual_seed(91)
+    q = torch.randn(B, Sq, H, D, generator=g).to(dtype)
+    k = torch.randn(B, 2048, H, D, generator=g).to(dtype)
+    v = torch.randn(B, 2048, H, D, generator=g).to(dtype)
+    o = eng.decode_varlen(q.cuda(), k.cuda(), v.cuda(), torch.tensor(lens))
+    torch.cuda.synchronize()
+    eng.check_status()
+    keep = lambda L: (torch.arange(L) % 512 < W).view(1, 1, 1, L)  # noqa: E731
+    _check("o", o.cpu(), _ragged_ref(q, k, v, lens, keep), dtype)
+    # the same engine, one length for all rows, through the plain call
+    o2 = eng(q.cuda(), k.cuda(), v.cuda())
+    torch.cuda.synchronize()
+    _check("o", o2.cpu(), _ragged_ref(q, k, v, [2048] * B, keep), dtype)

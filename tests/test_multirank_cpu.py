@@ -1,5 +1,5 @@
 """The N > 1 path of bench.py on CPU: two gloo ranks, no data-path collective, only the max-over-ranks timing
-reduction and the weak-scaling aggregate."""
+reduction, the aggregate over ranks and the split of the workload's batch rows."""
 import os
 import sys
 
@@ -38,3 +38,18 @@ def test_single_process_is_identity():
     import bench
     assert bench.max_over_ranks(3.5) == 3.5
     assert bench.aggregate_throughput(10.0, 2.0, 1) == (5000.0, 2.0)
+
+
+def test_workload_is_split_by_batch_rows_under_strong_scaling():
+    sys.path.insert(0, ROOT)
+    import pytest
+    import bench
+    assert [bench.shard_batch(8, n, "strong") for n in (1, 2, 4, 8)] == [8, 4, 2, 1]
+    assert [bench.shard_batch(8, n, "weak") for n in (1, 2, 4, 8)] == [8, 8, 8, 8]
+    with pytest.raises(SystemExit):
+        bench.shard_batch(8, 3, "strong")
+    # the job's figure: every rank's share of the FLOPs over the slowest rank's time = whole workload / that time
+    total = 3.5 * bench.flops_fwd(8, 32, 8192, 128)
+    share = 3.5 * bench.flops_fwd(bench.shard_batch(8, 4, "strong"), 32, 8192, 128)
+    per_s, ms = bench.aggregate_throughput(share, 5.0, 1)
+    assert abs(4 * share - total) < 1e-3 * total and ms == 5.0
