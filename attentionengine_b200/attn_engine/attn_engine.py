@@ -76,16 +76,16 @@ def _strides3(t: torch.Tensor):
 
 def _block_lists(cnt: torch.Tensor, q_blk: int, kv_blk: int, Sq: int, Skv: int, B: int, H: int, device):
     """Per (b, h, q tile): ascending list of kept kv tiles, entry = tile | partial << 30.
-    Returns (count [B,H,nq] int32, index [B,H,nq,nk] int32) and the transposed pair."""
-    cnt = cnt.to("cpu")
+    Returns (count [B,H,nq] int32, index [B,H,nq,nk] int32) and the transposed pair.  Runs where ``cnt`` lives: a
+    call-time block mask on the GPU is turned into lists there, without a copy to the host."""
     b_, h_, nq, nk = cnt.shape
-    rows = torch.clamp(Sq - torch.arange(nq) * q_blk, max=q_blk).view(1, 1, nq, 1)
-    cols = torch.clamp(Skv - torch.arange(nk) * kv_blk, max=kv_blk).view(1, 1, 1, nk)
+    dev = cnt.device
+    rows = torch.clamp(Sq - torch.arange(nq, device=dev) * q_blk, max=q_blk).view(1, 1, nq, 1)
+    cols = torch.clamp(Skv - torch.arange(nk, device=dev) * kv_blk, max=kv_blk).view(1, 1, 1, nk)
     full = cnt == rows * cols
     keep = cnt > 0
 
     def lists(keep_m, full_m):
-        n = keep_m.shape[-1]
         order = torch.argsort((~keep_m).to(torch.int8), dim=-1, stable=True)
         part = (~torch.gather(full_m, -1, order)).to(torch.int32)
         idx = (order.to(torch.int32) | (part << 30))
@@ -293,11 +293,11 @@ class AttentionEngine:
                     block_mask.shape[0] not in (1, B) or block_mask.shape[1] not in (1, Hq):
                 raise ValueError(f"block_mask has shape {tuple(block_mask.shape)}; expected [1 or {B}, 1 or {Hq}, {nq}, {nk}] "
                                  f"(one entry per 128 x 128 tile of the {Sq} x {Skv} score matrix)")
-            cnt = block_mask.to(torch.int32).cpu()
+            cnt = block_mask.to(torch.int32)  # stays on the mask's device: no host round trip per call
             if self.mask_mod is None:
                 # listed blocks are complete blocks
-                rows = torch.clamp(Sq - torch.arange(nq) * 128, max=128).view(1, 1, nq, 1)
-                cols = torch.clamp(Skv - torch.arange(nk) * 128, max=128).view(1, 1, 1, nk)
+                rows = torch.clamp(Sq - torch.arange(nq, device=cnt.device) * 128, max=128).view(1, 1, nq, 1)
+                cols = torch.clamp(Skv - torch.arange(nk, device=cnt.device) * 128, max=128).view(1, 1, 1, nk)
                 cnt = (cnt > 0).to(torch.int32) * rows * cols
             return _block_lists(cnt, 128, 128, Sq, Skv, B, Hq, device)
         if self._dynamic and self.mask_mod is not None:

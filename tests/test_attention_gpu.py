@@ -23,8 +23,10 @@ MAX_ABS, REL_L2 = parity.MAX_ABS, parity.REL_L2
 @pytest.fixture(params=["split", "fused"], autouse=True)
 def bwd_mode(request, monkeypatch):
     """Every test of this file runs with both forms of the attention backward (two-pass / one-pass)."""
+    from attentionengine_b200 import tune
     from attentionengine_b200.attn_engine import attn_bwd
     monkeypatch.setattr(attn_bwd, "DEFAULT_MODE", request.param)
+    monkeypatch.setattr(tune, "PACKAGE_FILE", tune.PACKAGE_FILE.with_name("no_table_in_these_tests.json"))
     return request.param
 
 
