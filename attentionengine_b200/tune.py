@@ -166,3 +166,41 @@ def resolve(engine_kwargs: dict, keys: dict, tune: bool, tune_file: str) -> dict
         cfg, _ = sweep(**engine_kwargs, keys=keys)
         return cfg
     return lookup(PACKAGE_FILE, keys, exact=False) or {}
+
+
+def main(argv=None):
+    """``python -m attentionengine_b200.tune [--out FILE]``: sweep the three problem classes of the benchmark
+    configurations (fp16 head dim 128 causal GQA; fp16 head dim 64 causal MHA; bf16 head dim 128 non-causal with an
+    identity online function) on the current CUDA device and write the table the package ships."""
+    import argparse
+    import math
+
+    import torch
+
+    from . import examples as ex
+    from .core import CustomIO
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default=str(PACKAGE_FILE))
+    args = ap.parse_args(argv)
+    if os.path.exists(args.out):
+        os.remove(args.out)
+    scale = 1 / math.sqrt(128)
+    problems = [
+        ("cfg2", dict(score_mod=lambda s, c, b, h, q, kv: s * scale, mask_mod=ex.causal_mask,
+                      online_func=ex.OnlineSoftmax(), custom_io=CustomIO({})),
+         problem_keys(8, 32, 8, 8192, 8192, 128, 128, torch.float16, 1)),
+        ("d64", dict(score_mod=lambda s, c, b, h, q, kv: s * 0.125, mask_mod=ex.causal_mask,
+                     online_func=ex.OnlineSoftmax(), custom_io=CustomIO({})),
+         problem_keys(4, 16, 16, 4096, 4096, 64, 64, torch.float16, 1)),
+        ("cfg3", dict(score_mod=lambda s, c, b, h, q, kv: (s * scale).max(0) * (1.0 / 4096), mask_mod=None,
+                      online_func=ex.OnlineIdentity(), custom_io=CustomIO({})),
+         problem_keys(4, 32, 32, 4096, 4096, 128, 128, torch.bfloat16, 0)),
+    ]
+    for name, kwargs, keys in problems:
+        cfg, table = sweep(**kwargs, keys=keys, log=lambda m, n=name: print(n, m, flush=True))
+        store(args.out, keys, cfg, table)
+        print(name, "->", cfg, flush=True)
+
+
+if __name__ == "__main__":
+    main()

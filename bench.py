@@ -192,7 +192,7 @@ def run_reference(args, rank, world):
 # kernel -> (batch of the capture, dram__bytes_read.sum + dram__bytes_write.sum of one launch) at Hq=32, Hkv=8,
 # S=8192, D=128, from ncu captures on one B200 (the summaries under profiles/ name the commands)
 NCU_DRAM_BYTES = {"ae_attn_fwd": (2, 301.5e6), "ae_attn_bwd_dq": (2, 450.9e6), "ae_attn_bwd_dkv": (2, 396.6e6),
-                  "ae_attn_bwd_prep": (2, 273.6e6), "ae_attn_bwd_fused": (1, 475.2e6)}
+                  "ae_attn_bwd_prep": (2, 273.6e6), "ae_attn_bwd_fused": (1, 436.7e6)}
 
 
 def time_events(torch, fn, steps, warmup):
