@@ -210,8 +210,17 @@ class AttentionEngine:
             self.tl_code = self._decode.src
             self.mask_mode = 0
             return
+        # Value head dims above 128 run as independent 128-wide value blocks: O[:, block] depends on V[:, block] only, and
+        # the backward is linear in dO, so the blocks' dQ / dK add up (torch autograd sums them) and dV is per block.
+        # Each block recomputes the scores.  (The reference's lowering has a DV > 256 path of its own, lower.py:648-654.)
+        self.DV_total = DV
+        if isinstance(DV, int) and DV > 128:
+            if DV % 128:
+                raise NotImplementedError(f"value head dim {DV}: above 128 it must be a multiple of 128")
+            DV = self.DV = 128
         if isinstance(D, str) or isinstance(DV, str) or D % 64 or DV % 64 or D > 128 or DV > 128:
-            raise NotImplementedError(f"head dims D={D}, DV={DV}: multiples of 64 up to 128 are supported")
+            raise NotImplementedError(f"head dims D={D}, DV={DV}: the query / key head dim is a multiple of 64 up to 128, "
+                                      "the value head dim a multiple of 64 up to 128 or a multiple of 128 above")
         if not isinstance(Hq, str) and not isinstance(Hkv, str):
             assert Hq % Hkv == 0, "query heads must be a multiple of kv heads"
 
@@ -424,6 +433,12 @@ class AttentionEngine:
         self._call_block_mask = block_mask if block_mask is not None else (
             self.block_mask if self.extern_block_mask else None)
         try:
+            if getattr(self, "DV_total", self.DV) != self.DV:
+                if v.shape[-1] != self.DV_total:
+                    raise ValueError(f"v has head dim {v.shape[-1]}, engine was built for {self.DV_total}")
+                outs = [_AttentionFn.apply(self, q, k, v[..., i:i + self.DV], *custom)
+                        for i in range(0, self.DV_total, self.DV)]
+                return torch.cat(outs, dim=-1)
             return _AttentionFn.apply(self, q, k, v, *custom)
         finally:
             self._call_block_mask = None

@@ -758,3 +758,15 @@ def test_mha_decode_with_a_mask_and_ragged_rows(bwd_mode):
     o2 = eng(q.cuda(), k.cuda(), v.cuda())
     torch.cuda.synchronize()
     _check("o", o2.cpu(), _ragged_ref(q, k, v, [2048] * B, keep), dtype)
+
+
+def test_value_head_dim_above_128_runs_as_value_blocks():
+    """DV = 256 with D = 128: two 128-wide value blocks through the same kernels, dQ / dK summed over the blocks."""
+    B, Hq, Hkv, S, D, DV, dtype = 1, 4, 2, 384, 128, 256, torch.float16
+    eng = helpers.softmax_engine(B, Hq, Hkv, S, D, DV, dtype, True)
+    q, k, v, d_o = helpers.seeded_qkv(B, Hq, Hkv, S, D, DV, dtype, seed=17)
+    got = _run(eng, q, k, v, d_o)
+    assert got[0].shape == (B, S, Hq, DV)
+    o, (dq, dk, dv) = orc.fwd_bwd(lambda a, b, c: orc.softmax_attention(a, b, c, True), (q, k, v), d_o)
+    for name, g, r in zip(("o", "dq", "dk", "dv"), got, (o, dq, dk, dv)):
+        _check(name, g, r, dtype)
