@@ -389,6 +389,26 @@ AE_DEVICE float ae_rcp(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two fp32 operations per instruction (packed f32x2, sm_100): the row passes are bound by instruction issue, and these
+// halve the count of their multiply-add and add instructions.
+AE_DEVICE void ae_fma2(float& d0, float& d1, float x0, float x1, u64 a2, u64 b2) {
+  u64 x, d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(x0), "f"(x1));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(x), "l"(a2), "l"(b2));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+}
+AE_DEVICE u64 ae_pack2f(float lo, float hi) {
+  u64 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+AE_DEVICE void ae_unpack2f(u64 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+AE_DEVICE u64 ae_add2(u64 acc, float x0, float x1) {
+  u64 x, d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(x0), "f"(x1));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(acc), "l"(x));
+  return d;
+}
 #define AE_LOG2E 1.4426950408889634f
 #define AE_LN2 0.6931471805599453f
 AE_DEVICE float ae_exp(float x) { return ae_exp2(x * AE_LOG2E); }

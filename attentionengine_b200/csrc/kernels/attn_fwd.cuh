@@ -37,6 +37,16 @@
 // runs two tiles ahead of P V, so the row threads find the next tile's scores ready when they finish a tile
 // (S MMA -> row pass -> P V MMA is no longer one chain per tile).
 #define AE_PINGPONG (AE_DECODE && AE_NQ == 1)
+// AE_TURNS = 1: the two row warpgroups take turns (named barriers 1 and 2 as a token), so that one group's row pass
+// runs while the tensor pipe works on the other tile.  Off by default: measured slower with all exponentials on the
+// special-function unit (a group's row pass is then longer than the other tile's two MMAs); a sweep candidate together
+// with AE_EXP_POLY_PERIOD.
+#ifndef AE_TURNS
+#define AE_TURNS 0
+#endif
+#if AE_TURNS && AE_DECODE
+#error "turn-taking is for the two-tile forward"
+#endif
 #if AE_PINGPONG && AE_STAGES < 3
 #error "the two-ahead S GEMM needs three K / V stages"
 #endif
@@ -505,8 +515,21 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     u32 n_done = 0;
     bool ok = true;
     AeKvStep step;
+#if AE_TURNS
+    // group 0 goes first: group 1 hands it the token once before the walk.  Every group passes the token at every
+    // step of the walk, also at steps its tile sits out, so the two sides stay in step whatever the masks are.
+    if (t == 1) named_bar_arrive(1, 256);
+#endif
     while (next_step(step)) {
+#if AE_TURNS
+      if (!(step.flags & (1u << t))) {
+        named_bar_sync(1 + t, 256);
+        named_bar_arrive(2 - t, 256);
+        continue;
+      }
+#else
       if (!(step.flags & (1u << t))) continue;
+#endif
 #if AE_PINGPONG
       // scores of this group's n-th tile: region n & 1, phase n >> 1 of that region's barriers
       const u32 rgn = n_done & 1u;
@@ -521,6 +544,9 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       const u32 s_par = n_done & 1u;
 #endif
       ok = ok && mbar_wait(s_bar, s_par, ctl, args.status, 9);
+#if AE_TURNS
+      named_bar_sync(1 + t, 256);  // this group's turn
+#endif
       tc_fence_after_sync();
 #if AE_MASK_MODE == 2
       if ((step.flags >> (4 + t)) & 1u) {
@@ -533,6 +559,9 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         tc_wait_st();
         tc_fence_before_sync();
         mbar_arrive_warp(p_bar);
+#if AE_TURNS
+        named_bar_arrive(2 - t, 256);
+#endif
         ++n_done;
         continue;
       }
@@ -559,6 +588,9 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         }
       }
       const float o_scale = ae_online_fwd<AE_BN>(s, st, b, h_row, q_idx, kv0, cu);
+#if AE_TURNS
+      named_bar_arrive(2 - t, 256);  // the exponentials are done: the other group's turn
+#endif
 
       // P -> TMEM (16-bit pairs, column c/2 holds kv columns c, c+1)
       {

@@ -15,6 +15,8 @@ does not depend on operand order the way the reference's in-place buffer reuse d
 """
 from __future__ import annotations
 
+import os
+
 import math
 import re
 from dataclasses import dataclass, field
@@ -85,6 +87,9 @@ class Emitter:
         self.aff: dict[int, tuple] = {}               # id(value) -> (base (expr, kind), a Scal|None, b Scal|None)
         self.used_leaves: set[str] = set()
         self.lazy_max: dict[int, int] = {}  # id(Max node) -> index of the operand that is the previous state
+        # packed f32x2 multiply-add / add in the tile loops: off unless AE_B200_PACKED=1 (measured 1 - 4 % slower in the
+        # forward kernel: the pack / unpack moves cost what the halved instruction count saves)
+        self.packed = tile_mode == "array" and os.environ.get("AE_B200_PACKED", "0") == "1"
         self.k = 0
 
     # -- helpers -------------------------------------------------------------------------------
@@ -220,10 +225,24 @@ class Emitter:
         return "tile" if id(v) in self.aff else self.names[id(v)][1]
 
     def _reduce(self, t: str, src_of_c) -> str:
-        """Row reduction over the N columns with four interleaved accumulators."""
+        """Row reduction over the N columns with four interleaved accumulators.  With ``packed`` (N a multiple of 8) the
+        sum takes two elements per instruction (packed f32x2 add): the row passes are issue-bound."""
         if self.tile_mode != "array":
             raise NotImplementedError("row reduction outside of online_fwd")
         name = self._tmp()
+        if self.packed and t == "ReduceSum":  # N is a multiple of 8 (asserted in the functor)
+            # (the three-input max of PTX assembles under nvcc 12.9 but not under NVRTC 12.9, so the maximum stays scalar)
+            if True:
+                self.lines.append("u64 " + ", ".join(f"{name}_{i} = 0ull" for i in range(4)) + ";")
+                body = " ".join(f"{name}_{i} = ae_add2({name}_{i}, {src_of_c(f'c + {2 * i}')}, {src_of_c(f'c + {2 * i + 1}')});"
+                                for i in range(4))
+                self.lines.append(f"#pragma unroll\nfor (int c = 0; c < {self.n}; c += 8) {{ {body} }}")
+                self.lines.append(f"float {name}_s[8];")
+                for i in range(4):
+                    self.lines.append(f"ae_unpack2f({name}_{i}, {name}_s[{2 * i}], {name}_s[{2 * i + 1}]);")
+                self.lines.append(f"const float {name} = (({name}_s[0] + {name}_s[1]) + ({name}_s[2] + {name}_s[3])) + "
+                                  f"(({name}_s[4] + {name}_s[5]) + ({name}_s[6] + {name}_s[7]));")
+            return name
         op = {"ReduceMax": "{a} = fmaxf({a}, {x});", "ReduceSum": "{a} += {x};", "ReduceAbsSum": "{a} += fabsf({x});"}[t]
         if t == "ReduceMax":
             inits = [src_of_c(str(i)) for i in range(4)]
@@ -312,6 +331,17 @@ class Emitter:
                     a = self._s_mul(a if a is not None else Scal("1.0f", 1.0), l2e)
                     b = self._s_mul(b, l2e) if b is not None else None
                 idx = "c" if self.tile_mode == "array" else "sel"
+                if self.packed and self.tile_mode == "array" and a is not None and b is not None:
+                    # exp2(x * a + b) over the tile: the multiply-add on two elements per instruction
+                    name = self._tmp()
+                    x0, x1 = self._tile_ref(base, "c"), self._tile_ref(base, "c + 1")
+                    self.lines.append(f"float {name}[{self.n}];")
+                    self.lines.append(f"{{ const u64 {name}_a = ae_pack2f({a.expr}, {a.expr}), {name}_b = ae_pack2f({b.expr}, {b.expr});")
+                    self.lines.append(f"#pragma unroll\nfor (int c = 0; c < {self.n}; c += 2) {{ float y0, y1; "
+                                      f"ae_fma2(y0, y1, {x0}, {x1}, {name}_a, {name}_b); "
+                                      f"{name}[c] = ae_exp2_mix(y0, c); {name}[c + 1] = ae_exp2_mix(y1, c + 1); }} }}")
+                    self.names[id(v)] = (name + "[{c}]", "tile")
+                    return
                 self.names[id(v)] = self._new_tile(f"ae_exp2_mix({self._affine_expr(base, a, b)}, {idx})")
                 return
             args = [self.ref(p, "c") for p in v.prev]
@@ -657,7 +687,8 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     body += "".join(f"  st.st_{k} = n_{k};\n" for k in new_exprs)
     src.append("// s[] holds the raw (masked) scores q.k on entry and P on exit: score_mod and online_fwd in one pass\n"
                "template <int N>\nAE_DEVICE float ae_online_fwd(float (&s)[N], AeRow& st, int b, int h, int q_idx, "
-               "int kv0, const AeCustom& cu) {\n" + body + "  return o_scale_;\n}\n")
+               "int kv0, const AeCustom& cu) {\n  static_assert(N % 8 == 0, \"tile loops take eight columns at a time\");\n"
+               + body + "  return o_scale_;\n}\n")
 
     # ---- epilogue --------------------------------------------------------------------------------------
     o_sym = SymbolicArray("o", Var("o"), shape_idx=["block_M", "dimv"])

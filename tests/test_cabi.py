@@ -30,15 +30,19 @@ def test_struct_sizes_match_header():
     """ctypes mirrors of the parameter blocks have the size the C compiler gives them."""
     import subprocess
     import tempfile
-    src = '#include <stdio.h>\n#include "ae_b200.h"\nint main(){printf("%zu %zu %zu %zu\\n", sizeof(AeKernelConfig), ' \
-          'sizeof(AeKernelInfo), sizeof(AeAttnParams), sizeof(AeAttnBwdParams));return 0;}\n'
+    names = ["AeKernelConfig", "AeKernelInfo", "AeAttnParams", "AeAttnBwdParams", "AeDecodeParams", "AeRowScaleParams",
+             "AeMlaParams", "AeMlaPagedParams", "AeLinearParams", "AeLinearBwdParams", "AeDecodeWorkItem"]
+    mirrors = [rt.KernelConfig, rt.KernelInfo, rt.AttnParams, rt.AttnBwdParams, rt.DecodeParams, rt.RowScaleParams,
+               rt.MlaParams, rt.MlaPagedParams, rt.LinearParams, rt.LinearBwdParams, C.c_int32 * 4]
+    src = '#include <stdio.h>\n#include "ae_b200.h"\nint main(){' + \
+          "".join(f'printf("%zu\\n", sizeof({n}));' for n in names) + "return 0;}\n"
     with tempfile.TemporaryDirectory() as d:
         c = os.path.join(d, "s.c")
         open(c, "w").write(src)
         subprocess.run(["gcc", f"-I{ROOT}/include", c, "-o", os.path.join(d, "s")], check=True)
         out = subprocess.run([os.path.join(d, "s")], capture_output=True, text=True, check=True).stdout.split()
-    assert [int(x) for x in out] == [C.sizeof(rt.KernelConfig), C.sizeof(rt.KernelInfo), C.sizeof(rt.AttnParams),
-                                     C.sizeof(rt.AttnBwdParams)]
+    for n, got, m in zip(names, out, mirrors):
+        assert int(got) == C.sizeof(m), f"{n}: header {got} bytes, ctypes mirror {C.sizeof(m)}"
 
 
 def test_strerror_and_invalid_arguments():
