@@ -9,6 +9,7 @@ them with NVRTC through the C ABI; the call launches those kernels on the curren
 """
 from __future__ import annotations
 
+import os
 import ctypes as C
 from typing import Optional
 
@@ -100,6 +101,9 @@ def _block_lists(cnt: torch.Tensor, q_blk: int, kv_blk: int, Sq: int, Skv: int, 
     return ex(c), ex(i), ex(ct), ex(it)
 
 
+FWD_FORM = (1, 0)  # (threads per score row, turn-taking) of the forward kernel when no tuned entry says otherwise
+
+
 class _AttnKernels:
     """Compiled kernels of one engine instance."""
 
@@ -108,12 +112,21 @@ class _AttnKernels:
         self.low = low
         self.D, self.DV, self.dtype_tag, self.mask_mode, self.stages = D, DV, dtype_tag, mask_mode, stages
         self.tuned = tuned or {}  # tile choices of the backward kernels (attentionengine_b200/tune.py)
+        # forward form: threads per score row (1 or 2) and whether the two q tiles take turns; from the tuned table,
+        # AE_B200_FWD_RSPLIT / AE_B200_FWD_TURNS override (experiments)
+        rsplit, turns = self.tuned.get("fwd_form", FWD_FORM)
+        rsplit = int(os.environ.get("AE_B200_FWD_RSPLIT", rsplit))
+        turns = int(os.environ.get("AE_B200_FWD_TURNS", turns))
+        self.fwd_form = (rsplit, turns)
         smem = 2 * 128 * D * 2 + stages * 128 * (D + DV) * 2 + 512 + 1024
+        if rsplit > 1:
+            smem += 2 * 2 * rsplit * 128 * 4  # partial row reductions exchanged between the threads of a row
         if mask_mode == 2:
             smem += 4 * MAX_LIST_KV_TILES  # the CTA's merged tile walk
-        cfg = rt.KernelConfig(kind=rt.KIND_ATTN_FWD, dtype=dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
-                              smem_bytes=smem, stages=stages, mask_mode=mask_mode)
-        self.fwd_src = rt.kernel_source("attn_fwd.cuh", prelude=low.prelude_fwd)
+        cfg = rt.KernelConfig(kind=rt.KIND_ATTN_FWD, dtype=dtype_tag, head_dim=D, head_dim_v=DV,
+                              threads=rsplit * 256 + 64, smem_bytes=smem, stages=stages, mask_mode=mask_mode)
+        self.fwd_src = rt.kernel_source("attn_fwd.cuh", prelude=low.prelude_fwd,
+                                        defines={"AE_RSPLIT": rsplit, "AE_TURNS": turns})
         self.fwd = rt.compile_module(self.fwd_src, "ae_attn_fwd", cfg)
         self._bwd = None
         self._bwd_fused = None

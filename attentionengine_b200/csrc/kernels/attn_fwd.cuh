@@ -8,7 +8,8 @@
 //                     row i: it reads its 128 scores from TMEM, applies mask,
 //                     score_mod and the online recurrence in registers (no shuffles),
 //                     writes P back to TMEM as 16-bit pairs, rescales O when needed
-//                     and runs the epilogue.
+//                     and runs the epilogue.  (AE_RSPLIT = 2: four row warpgroups, two
+//                     threads per row with 64 columns each; the roles below move up.)
 //   warp 8          : TMA producer (Q once, K/V ring of AE_STAGES stages).
 //   warp 9          : tcgen05.mma issuer; owns the TMEM allocation.
 // TMEM columns: S0 | S1 | O0 | O1 (P_t aliases the first half of S_t).
@@ -22,7 +23,6 @@
 
 #define AE_BM 128
 #define AE_BN 128
-#define AE_NTHREADS 320
 #ifndef AE_DECODE
 #define AE_DECODE 0  // 1: split-KV decode (reference: attn_decode_tl.py:34-141 / attn_gqa_decode_tl.py), see AeAttnFwdArgs
 #endif
@@ -47,6 +47,20 @@
 #if AE_TURNS && AE_DECODE
 #error "turn-taking is for the two-tile forward"
 #endif
+// AE_RSPLIT = 2: two threads per score row (warpgroups 2t and 2t + 1 work on q tile t, 64 kv columns each).  A row
+// pass is then half as long, which is what lets the two tiles alternate (AE_TURNS) with the tensor pipe busy on one
+// while the other's rows run.  Row reductions are completed between the two threads of a row by the generated
+// ae_row_xchg (shared memory slot + named barrier 3 + t).  The second half keeps its P in the second half of its own
+// score columns (16-bit pairs at column 96 ...), so that no thread writes TMEM columns another thread still reads.
+#ifndef AE_RSPLIT
+#define AE_RSPLIT 1
+#endif
+#if AE_RSPLIT != 1 && (AE_RSPLIT != 2 || AE_DECODE)
+#error "rows are split over two threads in the two-tile forward only"
+#endif
+#define AE_ROW_WARPS (8 * AE_RSPLIT)
+#define AE_NTHREADS (AE_ROW_WARPS * 32 + 64)
+#define AE_NC (AE_BN / AE_RSPLIT)  // score columns per row thread
 #if AE_PINGPONG && AE_STAGES < 3
 #error "the two-ahead S GEMM needs three K / V stages"
 #endif
@@ -59,7 +73,8 @@
 #define AE_SMEM_K (AE_NQ * AE_Q_BYTES)
 #define AE_SMEM_V (AE_SMEM_K + AE_STAGES * AE_K_BYTES)
 #define AE_SMEM_BAR (AE_SMEM_V + AE_STAGES * AE_V_BYTES)
-#define AE_SMEM_STEPS (AE_SMEM_BAR + 512)  // mask mode 2 only: one word per kv tile
+#define AE_SMEM_XCH (AE_SMEM_BAR + 512)  // AE_RSPLIT = 2 only: [q tile][phase][half][row] partial row reductions
+#define AE_SMEM_STEPS (AE_SMEM_XCH + (AE_RSPLIT > 1 ? 2 * 2 * AE_RSPLIT * 128 * 4 : 0))  // mask mode 2 only: one word per kv tile
 #define AE_MAX_KT 2048                    // kv tiles a block list may cover (4 * AE_MAX_KT bytes of shared memory)
 
 struct AeFwdBars {
@@ -196,7 +211,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->q_full[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->p_full[i], 4);
+      mbar_init(&bars->p_full[i], 4 * AE_RSPLIT);
       mbar_init(&bars->o_done[i], 1);
     }
     for (int i = 0; i < AE_STAGES; ++i) {
@@ -262,7 +277,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     }
   }
 #endif
-  if (warp == 9) {
+  if (warp == AE_ROW_WARPS + 1) {
     tmem_alloc(&ctl->tmem_base, 512);
     tmem_relinquish();
   }
@@ -275,7 +290,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #endif
   const u32 TM_S0 = 0, TM_S1 = 128, TM_O0 = 256, TM_O1 = 256 + AE_DV;
 
-  if (warp == 8) {
+  if (warp == AE_ROW_WARPS) {
     // =============================== TMA producer ===============================
     if (lane == 0) {
       tma_prefetch_desc(&args.tm_q);
@@ -319,7 +334,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         ++it;
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == AE_ROW_WARPS + 1) {
     // =============================== MMA issuer =================================
     if (lane == 0) {
       const u32 idesc_s = umma_idesc_f16(AE_BM, AE_BN, AE_BF16, 0, 0);
@@ -345,7 +360,8 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         const u32 d = tmem + (t ? TM_O1 : TM_O0);
         const u32 a = tmem + (t ? TM_S1 : TM_S0);
 #pragma unroll
-        for (int kk = 0; kk < AE_BN / 16; ++kk) umma_ts(d, a + kk * 8, umma_step_mn(db, kk), idesc_o, acc | (kk > 0));
+        for (int kk = 0; kk < AE_BN / 16; ++kk)
+          umma_ts(d, a + kk * 8 + ((AE_RSPLIT > 1 && kk >= AE_BN / 32) ? 64 : 0), umma_step_mn(db, kk), idesc_o, acc | (kk > 0));
       };
 
 #if AE_PINGPONG
@@ -483,7 +499,8 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     }
   } else {
     // =============================== row warpgroups =============================
-    const int t = warp >> 2;                 // q tile of this group
+    const int t = warp / (4 * AE_RSPLIT);    // q tile of this group
+    const u32 half = (warp >> 2) & (AE_RSPLIT - 1);  // which columns of the row this thread takes
     const u32 row = threadIdx.x & 127;       // row inside the tile == TMEM lane
     const u32 lane_base = ((warp & 3) * 32) << 16;
     const u32 tm_s = tmem + (t ? TM_S1 : TM_S0) + lane_base;
@@ -512,19 +529,27 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 
     AeRow st;
     st.init();
+#if AE_RSPLIT > 1
+    st.xch = (volatile float*)(smem + AE_SMEM_XCH) + t * (2 * AE_RSPLIT * 128);
+    st.xme = half * 128 + row;
+    st.xother = (half ^ 1u) * 128 + row;
+    st.xbar = 3 + t;
+    st.xn = AE_RSPLIT * 128;
+    st.xphase = 0;
+#endif
     u32 n_done = 0;
     bool ok = true;
     AeKvStep step;
 #if AE_TURNS
     // group 0 goes first: group 1 hands it the token once before the walk.  Every group passes the token at every
     // step of the walk, also at steps its tile sits out, so the two sides stay in step whatever the masks are.
-    if (t == 1) named_bar_arrive(1, 256);
+    if (t == 1) named_bar_arrive(1, AE_RSPLIT * 256);
 #endif
     while (next_step(step)) {
 #if AE_TURNS
       if (!(step.flags & (1u << t))) {
-        named_bar_sync(1 + t, 256);
-        named_bar_arrive(2 - t, 256);
+        named_bar_sync(1 + t, AE_RSPLIT * 256);
+        named_bar_arrive(2 - t, AE_RSPLIT * 256);
         continue;
       }
 #else
@@ -545,7 +570,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #endif
       ok = ok && mbar_wait(s_bar, s_par, ctl, args.status, 9);
 #if AE_TURNS
-      named_bar_sync(1 + t, 256);  // this group's turn
+      named_bar_sync(1 + t, AE_RSPLIT * 256);  // this group's turn
 #endif
       tc_fence_after_sync();
 #if AE_MASK_MODE == 2
@@ -555,25 +580,29 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) z[i] = 0u;
 #pragma unroll
-        for (int half = 0; half < AE_BN / 64; ++half) tmem_st32(tm_s_n + half * 32, z);
+        for (int hh = (int)half; hh < AE_BN / 64; hh += AE_RSPLIT) tmem_st32(tm_s_n + hh * 32 + (AE_RSPLIT > 1 ? hh * 64 : 0), z);
         tc_wait_st();
         tc_fence_before_sync();
         mbar_arrive_warp(p_bar);
 #if AE_TURNS
-        named_bar_arrive(2 - t, 256);
+        named_bar_arrive(2 - t, AE_RSPLIT * 256);
 #endif
         ++n_done;
         continue;
       }
 #endif
-      float s[AE_BN];
+      float s[AE_NC];
+#if AE_RSPLIT > 1
+      tmem_ld_f32x64(tm_s_n + half * AE_NC, s);
+#else
       tmem_ld_f32x128(tm_s_n, s);
-      const int kv0 = step.kt * AE_BN;
-      const bool tail = (kv0 + AE_BN > AE_SKV);
+#endif
+      const int kv0 = step.kt * AE_BN + (int)half * AE_NC;  // first kv column of this thread
+      const bool tail = (step.kt * AE_BN + AE_BN > AE_SKV);
       const bool partial = (step.flags >> (2 + t)) & 1u;
       if (partial || tail) {
 #pragma unroll
-        for (int c = 0; c < AE_BN; ++c) {
+        for (int c = 0; c < AE_NC; ++c) {
           const int kv_idx = kv0 + c;
           bool keep = kv_idx < AE_SKV;
 #if AE_MASK_MODE != 0
@@ -587,19 +616,19 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #endif
         }
       }
-      const float o_scale = ae_online_fwd<AE_BN>(s, st, b, h_row, q_idx, kv0, cu);
+      const float o_scale = ae_online_fwd<AE_NC>(s, st, b, h_row, q_idx, kv0, cu);
 #if AE_TURNS
-      named_bar_arrive(2 - t, 256);  // the exponentials are done: the other group's turn
+      named_bar_arrive(2 - t, AE_RSPLIT * 256);  // the exponentials are done: the other group's turn
 #endif
 
       // P -> TMEM (16-bit pairs, column c/2 holds kv columns c, c+1)
       {
         u32 pk[32];
 #pragma unroll
-        for (int half = 0; half < AE_BN / 64; ++half) {
+        for (int hh = 0; hh < AE_NC / 64; ++hh) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pk[i] = pack2<AE_BF16>(s[half * 64 + 2 * i], s[half * 64 + 2 * i + 1]);
-          tmem_st32(tm_s_n + half * 32, pk);
+          for (int i = 0; i < 32; ++i) pk[i] = pack2<AE_BF16>(s[hh * 64 + 2 * i], s[hh * 64 + 2 * i + 1]);
+          tmem_st32(tm_s_n + hh * 32 + (AE_RSPLIT > 1 ? half * 96 : 0), pk);
         }
       }
 #if !AE_O_SCALE_ONE
@@ -609,7 +638,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         ok = ok && mbar_wait(&bars->o_done[t], (n_done - 1) & 1, ctl, args.status, 10);
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < AE_DV / 32; ++c) {
+        for (int c = (int)half; c < AE_DV / 32; c += AE_RSPLIT) {  // the threads of a row share its O columns
           float f[32];
           u32 r[32];
           tmem_ld_f32x32(tm_o + c * 32, f);
@@ -640,7 +669,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       float* prow = args.o_part + part_row * AE_DV;
 #endif
 #pragma unroll
-      for (int c = 0; c < AE_DV / 32; ++c) {
+      for (int c = (int)half; c < AE_DV / 32; c += AE_RSPLIT) {
         float r[32];
         if (n_done > 0) {
           tmem_ld_f32x32(tm_o + c * 32, r);
@@ -671,7 +700,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         }
       }
 #if AE_NFINAL > 0
-      if (store) {
+      if (store && half == 0) {
         float fr[AE_NFINAL];
         ae_final_rowscales(st, fr);
 #pragma unroll
@@ -693,7 +722,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
   // ---- teardown --------------------------------------------------------------------
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == AE_ROW_WARPS + 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);
   }

@@ -242,7 +242,7 @@ class Emitter:
                     self.lines.append(f"ae_unpack2f({name}_{i}, {name}_s[{2 * i}], {name}_s[{2 * i + 1}]);")
                 self.lines.append(f"const float {name} = (({name}_s[0] + {name}_s[1]) + ({name}_s[2] + {name}_s[3])) + "
                                   f"(({name}_s[4] + {name}_s[5]) + ({name}_s[6] + {name}_s[7]));")
-            return name
+            return self._row_exchange(name, t)
         op = {"ReduceMax": "{a} = fmaxf({a}, {x});", "ReduceSum": "{a} += {x};", "ReduceAbsSum": "{a} += fabsf({x});"}[t]
         if t == "ReduceMax":
             inits = [src_of_c(str(i)) for i in range(4)]
@@ -257,7 +257,13 @@ class Emitter:
             self.lines.append(f"const float {name} = fmaxf(fmaxf({name}_0, {name}_1), fmaxf({name}_2, {name}_3));")
         else:
             self.lines.append(f"const float {name} = ({name}_0 + {name}_1) + ({name}_2 + {name}_3);")
-        return name
+        return self._row_exchange(name, t)
+
+    def _row_exchange(self, name: str, t: str) -> str:
+        """A kernel that gives one row's columns to several threads (AE_RSPLIT > 1) completes every row reduction across
+        them; in every other build AE_ROW_XCHG is the identity."""
+        self.lines.append(f"const float {name}x = AE_ROW_XCHG(st, {name}, {int(t == 'ReduceMax')});")
+        return name + "x"
 
     def _lower(self, v: SymbolScalar):
         if not v.prev:
@@ -655,8 +661,25 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
     row_struct = "struct AeRow {\n"
     if state_names:
         row_struct += "  float " + ", ".join(f"st_{k}" for k in state_names) + ";\n"
+    row_struct += ("#if AE_RSPLIT > 1\n  volatile float* xch; u32 xme, xother, xbar, xn, xphase;\n#endif\n")
     row_struct += "  AE_DEVICE void init() {" + " ".join(
         f"st_{k} = {_flit(state_init[k])};" for k in state_names) + " }\n};\n"
+    # the threads that share a row publish their partial reduction in shared memory (two alternating slot sets, so that
+    # the next exchange cannot overwrite a value a slower partner has yet to read), meet at a named barrier and combine
+    row_struct += (
+        "#if AE_RSPLIT > 1\n"
+        "AE_DEVICE float ae_row_xchg(AeRow& st, float x, int is_max) {\n"
+        "  volatile float* slot = st.xch + (st.xphase & 1u) * (AE_RSPLIT * 128);\n"
+        "  slot[st.xme] = x;\n"
+        "  named_bar_sync(st.xbar, st.xn);\n"
+        "  const float y = slot[st.xother];\n"
+        "  st.xphase++;\n"
+        "  return is_max ? fmaxf(x, y) : x + y;\n"
+        "}\n"
+        "#define AE_ROW_XCHG(st, x, is_max) ae_row_xchg(st, x, is_max)\n"
+        "#else\n"
+        "#define AE_ROW_XCHG(st, x, is_max) (x)\n"
+        "#endif\n")
     src.append(row_struct)
 
     raw, t_scores = trace_score_mod()
@@ -761,7 +784,9 @@ def lower_attention(score_mod, mask_mod, online_func, custom_fwd_inputs: CustomI
         "AE_DS_USES_S": int(ds_uses_s),
         "AE_MASK_NEG_INF": int(str(mask_value).strip() in ("-inf", "-float('inf')")),
     }
-    head = "".join(f"#define {k} {v}\n" for k, v in defines.items()) + "struct AeCustom;\n"
+    head = ("".join(f"#define {k} {v}\n" for k, v in defines.items())
+            + "#ifndef AE_RSPLIT\n#define AE_RSPLIT 1  // threads per score row in the kernel that includes this\n#endif\n"
+            + "struct AeCustom;\n")
     fwd = head + "".join(src)
     bwd = fwd + "".join(bsrc)
     return LoweredAttention(prelude_fwd=fwd, prelude_bwd=bwd, final_names=final_names, custom=specs,

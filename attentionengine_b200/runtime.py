@@ -174,13 +174,14 @@ def exp_poly_period() -> int:
     return int(os.environ.get("AE_B200_EXP_POLY", "0"))
 
 
-def kernel_source(*files: str, prelude: str = "", exp_poly: int | None = None) -> str:
+def kernel_source(*files: str, prelude: str = "", exp_poly: int | None = None, defines: dict | None = None) -> str:
     """Common header + argument blocks + generated prelude + kernel template(s), as one translation unit.
-    `exp_poly` is the kernel's own default for AE_EXP_POLY_PERIOD (the environment variable still wins)."""
+    `exp_poly` is the kernel's own default for AE_EXP_POLY_PERIOD (the environment variable still wins); `defines`
+    are build switches of the kernel file, placed before everything else."""
     poly = exp_poly_period() if (exp_poly is None or "AE_B200_EXP_POLY" in os.environ) else exp_poly
     parts = [f"#define AE_EXP_POLY_PERIOD {poly}\n#define AE_WAIT_MODE {int(os.environ.get('AE_B200_WAIT_MODE', '0'))}\n"
              + ("#define AE_TRACE 1\n" if os.environ.get("AE_B200_TRACE") else "")
-             + (f"#define AE_TURNS {int(os.environ['AE_B200_FWD_TURNS'])}\n" if os.environ.get("AE_B200_FWD_TURNS") else "")
+             + "".join(f"#define {k} {v}\n" for k, v in (defines or {}).items())
              + ("#define AE_SELFCHECK 1\n" if os.environ.get("AE_B200_SELFCHECK") else ""),
              (KERNEL_DIR / "ae_sm100.cuh").read_text().replace("#pragma once\n", ""),
              (KERNEL_DIR / "ae_args.h").read_text(), prelude]
