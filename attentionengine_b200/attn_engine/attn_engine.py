@@ -101,6 +101,7 @@ def _block_lists(cnt: torch.Tensor, q_blk: int, kv_blk: int, Sq: int, Skv: int, 
     return ex(c), ex(i), ex(ct), ex(it)
 
 
+FWD_PAIR = 0  # 1: the forward over CTA pairs where it applies
 FWD_FORM = (1, 0)  # (threads per score row, turn-taking) of the forward kernel when no tuned entry says otherwise
 
 
@@ -123,11 +124,25 @@ class _AttnKernels:
             smem += 2 * 2 * rsplit * 128 * 4  # partial row reductions exchanged between the threads of a row
         if mask_mode == 2:
             smem += 4 * MAX_LIST_KV_TILES  # the CTA's merged tile walk
-        cfg = rt.KernelConfig(kind=rt.KIND_ATTN_FWD, dtype=dtype_tag, head_dim=D, head_dim_v=DV,
-                              threads=rsplit * 256 + 64, smem_bytes=smem, stages=stages, mask_mode=mask_mode)
-        self.fwd_src = rt.kernel_source("attn_fwd.cuh", prelude=low.prelude_fwd,
-                                        defines={"AE_RSPLIT": rsplit, "AE_TURNS": turns})
-        self.fwd = rt.compile_module(self.fwd_src, "ae_attn_fwd", cfg)
+        # forward over CTA pairs (tcgen05 cta_group::2): for the shapes it is written for, when the tuned entry or
+        # AE_B200_FWD_PAIR asks for it
+        pair = int(os.environ.get("AE_B200_FWD_PAIR", self.tuned.get("fwd_pair", FWD_PAIR)))
+        self.fwd_pair = bool(pair) and mask_mode in (0, 1, 3) and DV == 128 and D in (64, 128)
+        if self.fwd_pair:
+            pstages = int(os.environ.get("AE_B200_FWD_PAIR_STAGES", self.tuned.get("fwd_pair_stages", 5)))
+            smem = 128 * D * 2 + pstages * (64 * D * 2 + 128 * 64 * 2) + 512 + 2048 + 1024
+            cfg = rt.KernelConfig(kind=rt.KIND_ATTN_FWD_PAIR, dtype=dtype_tag, head_dim=D, head_dim_v=DV, threads=320,
+                                  smem_bytes=smem, stages=pstages, mask_mode=mask_mode)
+            self.fwd_src = rt.kernel_source("attn_fwd_pair.cuh", prelude=low.prelude_fwd,
+                                            defines={"AE_PAIR_STAGES": pstages, "AE_RSPLIT": 2,
+                                                     "AE_PAIR_SCOPE": int(os.environ.get("AE_B200_PAIR_SCOPE", "0"))})
+            self.fwd = rt.compile_module(self.fwd_src, "ae_attn_fwd_pair", cfg)
+        else:
+            cfg = rt.KernelConfig(kind=rt.KIND_ATTN_FWD, dtype=dtype_tag, head_dim=D, head_dim_v=DV,
+                                  threads=rsplit * 256 + 64, smem_bytes=smem, stages=stages, mask_mode=mask_mode)
+            self.fwd_src = rt.kernel_source("attn_fwd.cuh", prelude=low.prelude_fwd,
+                                            defines={"AE_RSPLIT": rsplit, "AE_TURNS": turns})
+            self.fwd = rt.compile_module(self.fwd_src, "ae_attn_fwd", cfg)
         self._bwd = None
         self._bwd_fused = None
 

@@ -406,8 +406,14 @@ int ae_launch_probe(void* module, const void* a, const void* b, const void* p, f
 int ae_launch_attn_fwd(void* module, const AeAttnParams* p, void* stream) {
   if (!module || !p || !p->q || !p->k || !p->v || !p->o) return AE_ERR_INVALID;
   Module* m = (Module*)module;
-  int rc = check_attn_common(m, AE_KIND_ATTN_FWD, p->B, p->Hq, p->Hkv, p->Sq, p->Skv);
+  // the forward over CTA pairs takes the same parameter block; its K tiles are loaded as two 64-row halves
+  const bool pair = m->cfg.kind == AE_KIND_ATTN_FWD_PAIR;
+  int rc = check_attn_common(m, pair ? AE_KIND_ATTN_FWD_PAIR : AE_KIND_ATTN_FWD, p->B, p->Hq, p->Hkv, p->Sq, p->Skv);
   if (rc) return rc;
+  if (pair && (m->cfg.mask_mode == 2 || m->cfg.head_dim_v != 128 || (m->cfg.head_dim != 64 && m->cfg.head_dim != 128))) {
+    set_error("the pair forward takes mask modes 0, 1, 3, value head dim 128 and head dim 64 or 128");
+    return AE_ERR_INVALID;
+  }
   if (m->cfg.mask_mode == 2 && (!p->block_count || !p->block_index)) {
     set_error("block lists required for mask_mode 2");
     return AE_ERR_INVALID;
@@ -423,7 +429,7 @@ int ae_launch_attn_fwd(void* module, const AeAttnParams* p, void* stream) {
   const int D = m->cfg.head_dim, DV = m->cfg.head_dim_v;
   rc = make_bshd_map(&args.tm_q, p->q, m->cfg.dtype, p->B, p->Sq, p->Hq, D, p->q_stride, 128);
   if (rc) return rc;
-  rc = make_bshd_map(&args.tm_k, p->k, m->cfg.dtype, p->B, p->Skv, p->Hkv, D, p->k_stride, 128);
+  rc = make_bshd_map(&args.tm_k, p->k, m->cfg.dtype, p->B, p->Skv, p->Hkv, D, p->k_stride, pair ? 64 : 128);
   if (rc) return rc;
   rc = make_bshd_map(&args.tm_v, p->v, m->cfg.dtype, p->B, p->Skv, p->Hkv, DV, p->v_stride, 128);
   if (rc) return rc;
@@ -450,7 +456,8 @@ int ae_launch_attn_fwd(void* module, const AeAttnParams* p, void* stream) {
   args.n_qt = (p->Sq + 127) / 128;
   args.n_kt = (p->Skv + 127) / 128;
   args.status = p->status;
-  const unsigned gx = (unsigned)((args.n_qt + 1) / 2);
+  // single-CTA kernel: two q tiles per CTA; pair kernel: one per CTA, two per cluster (of two CTAs along x)
+  const unsigned gx = pair ? 2u * (unsigned)((args.n_qt + 1) / 2) : (unsigned)((args.n_qt + 1) / 2);
   return launch(m, gx, (unsigned)p->Hq, (unsigned)p->B, &args, stream);
 }
 

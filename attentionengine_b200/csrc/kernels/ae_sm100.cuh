@@ -297,6 +297,111 @@ AE_DEVICE void umma_commit_w(u64* bar) {
 }
 
 // ---------------------------------------------------------------------------
+// CTA pairs (cluster of two CTAs on one TPC, tcgen05 ... .cta_group::2)
+// One MMA of the pair covers 256 rows: each CTA holds its own 128 rows of A (shared memory or TMEM) and of D (TMEM),
+// and half of B (N / 2 columns) in its own shared memory; the even CTA of the pair issues.  All tcgen05 instructions
+// of a kernel that take a .cta_group use the same one, so a pair kernel uses only the wrappers below.
+// ---------------------------------------------------------------------------
+AE_DEVICE u32 cluster_ctarank() {
+  u32 r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// every thread of every CTA of the cluster (no time-out: placed where all threads arrive whatever happened before)
+AE_DEVICE void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of this CTA's shared-memory address `addr` in the CTA of rank `rank`
+AE_DEVICE u32 mapa_u32(u32 addr, u32 rank) {
+  u32 r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// AE_PAIR_SCOPE 1: arrivals and waits between the CTAs of a pair carry release / acquire at cluster scope; 0 (default):
+// the instructions' default scope.  What crosses between the CTAs of the pair kernels is TMEM and shared memory read
+// and written by the tensor cores and TMA, ordered by tcgen05.fence / tcgen05.commit and the mbarrier itself, not
+// generic-proxy memory; cluster-scope acquires on every wait cost the pair forward 20 % and changed no result.
+#ifndef AE_PAIR_SCOPE
+#define AE_PAIR_SCOPE 0
+#endif
+AE_DEVICE void mbar_arrive_cluster(u32 cluster_addr) {
+#if AE_PAIR_SCOPE
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+#else
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+#endif
+}
+// Bounded wait on a barrier that the other CTA of the pair (its threads or its tensor core) arrives on.
+AE_DEVICE bool mbar_try_wait_cl(u64* bar, u32 parity) {
+#if !AE_PAIR_SCOPE
+  return mbar_try_wait(bar, parity);
+#endif
+  u32 ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
+      : "memory");
+  return ok != 0;
+}
+AE_DEVICE bool mbar_wait_cl(u64* bar, u32 parity, AeCtaCtl* ctl, u32* g_status, u32 site) {
+  if (mbar_try_wait_cl(bar, parity)) return true;
+  const i64 t0 = clock64();
+  while (true) {
+    if (mbar_try_wait_cl(bar, parity)) return true;
+    if (ctl->abort) return false;
+    if (clock64() - t0 > AE_WAIT_CYCLES) {
+      ctl->abort = 1;
+      if (g_status) atomicCAS(g_status, 0u, AE_ST_TIMEOUT_BASE + site);
+      return false;
+    }
+  }
+}
+// TMEM allocation of a pair: one warp of EACH CTA runs it (a collective of the two); both get the same base.
+AE_DEVICE void tmem_alloc2(u32* smem_out, u32 ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)),
+               "r"(ncols)
+               : "memory");
+}
+AE_DEVICE void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+AE_DEVICE void tmem_dealloc2(u32 taddr, u32 ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+AE_DEVICE void umma_ss2(u32 tmem_d, u64 desc_a, u64 desc_b, u32 idesc, u32 accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+AE_DEVICE void umma_ts2(u32 tmem_d, u32 tmem_a, u64 desc_b, u32 idesc, u32 accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// All MMAs issued so far by this thread arrive, when complete, on the barrier at this offset in BOTH CTAs of the pair.
+AE_DEVICE void umma_commit2(u64* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"((u16)3)
+               : "memory");
+}
+
+// ---------------------------------------------------------------------------
 // TMEM <-> registers.  Shape 32x32b: lane i of the warp owns TMEM lane
 // (32 * (warp_id % 4) + i); register j holds column (col0 + j).
 // ---------------------------------------------------------------------------

@@ -655,6 +655,11 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
     }
 
     // ---- epilogue ------------------------------------------------------------------
+#if AE_PINGPONG
+    // The S GEMM of the last tile was issued before the P V of the tile before it, so o_done may still be two phases
+    // short here: a parity wait can only tell neighbouring phases apart, hence one wait per missing phase.
+    if (n_done > 1) ok = ok && mbar_wait(&bars->o_done[t], (n_done - 2) & 1, ctl, args.status, 14);
+#endif
     if (n_done > 0) {
       ok = ok && mbar_wait(&bars->o_done[t], (n_done - 1) & 1, ctl, args.status, 11);
       tc_fence_after_sync();

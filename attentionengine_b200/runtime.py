@@ -25,6 +25,7 @@ KIND_MLA_DECODE, KIND_MLA_COMBINE, KIND_LINEAR_FWD, KIND_LINEAR_BWD, KIND_LINEAR
 KIND_ATTN_DECODE = 10
 KIND_ROWSCALE = 11
 KIND_ATTN_BWD_FUSED, KIND_ATTN_BWD_CAST = 12, 13
+KIND_ATTN_FWD_PAIR = 14
 DTYPE_F16, DTYPE_BF16 = 0, 1
 
 

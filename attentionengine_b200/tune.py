@@ -4,8 +4,9 @@ Stands in for the reference's autotuner and its json cache (core/template/tl_tem
 a file holding a list of ``{problem keys..., "tuned_config": ...}`` entries, looked up by problem size, filled by
 profiling when the entry is missing; candidate enumeration autotuner/decider.py:40-128,
 autotuner/attnfwd_tunner.py:61-172).  The search space here is small because the kernels are hand-written
-templates: ring depths of the streamed tiles, the number of row warpgroups, and which form of the backward runs
-(one kv-stationary pass with fp32 dQ adds, or two passes without atomics).
+templates: ring depths of the streamed tiles, the number of row warpgroups, which form of the forward runs (one CTA
+with two q tiles, or a CTA pair on tcgen05 cta_group::2) and which form of the backward (one kv-stationary pass with
+fp32 dQ adds, or two passes without atomics).
 
 ``AttentionEngine(..., tune=True, tune_file=path)`` looks its problem up in ``path`` and, when it is not there, runs
 ``sweep`` on the current CUDA device (a few seconds: every candidate is compiled, timed with CUDA events on seeded
@@ -71,6 +72,8 @@ def candidates(D: int, DV: int, n_final: int) -> dict:
     from .attn_engine import attn_bwd as ab
     ncs = n_final + 1
     fwd = [{"stages": st} for st in (2, 3, 4) if 2 * 128 * D * 2 + st * 128 * (D + DV) * 2 + 1536 <= SMEM_MAX]
+    if DV == 128 and D in (64, 128):  # the forward over CTA pairs (falls back by itself under block lists)
+        fwd.append({"fwd_pair": 1, "fwd_pair_stages": 5})
     fused = [{"mode": "fused", "fused_tile": [q, d, g]} for q in (2, 3, 4) for d in (1, 2) for g in (4,)
              if ab.fused_smem_bytes(D, DV, ncs, q, d) <= SMEM_MAX]
     split = []

@@ -58,6 +58,7 @@ enum {
   AE_KIND_ROWSCALE = 11,
   AE_KIND_ATTN_BWD_FUSED = 12,
   AE_KIND_ATTN_BWD_CAST = 13,
+  AE_KIND_ATTN_FWD_PAIR = 14, /* kernel "ae_attn_fwd_pair": launched through ae_launch_attn_fwd */
 };
 
 #define AE_MAX_CUSTOM_INPUTS 4
@@ -127,6 +128,9 @@ typedef struct AeAttnParams {
   uint32_t* status;
 } AeAttnParams;
 
+/* Module kind AE_KIND_ATTN_FWD (kernel "ae_attn_fwd", one CTA per two q tiles) or AE_KIND_ATTN_FWD_PAIR (kernel
+ * "ae_attn_fwd_pair": a cluster of two CTAs per two q tiles on tcgen05 cta_group::2; mask_mode 0, 1 or 3, head_dim_v 128,
+ * head_dim 64 or 128, AE_ERR_INVALID otherwise).  Same parameter block and results for both. */
 int ae_launch_attn_fwd(void* module, const AeAttnParams* p, void* stream);
 
 /* ---- attention backward -----------------------------------------------------------

@@ -84,6 +84,30 @@ def test_softmax_shapes_against_oracle(B, Hq, Hkv, S, D, causal, dtype):
         _check(name, g, r, dtype)
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,S,D,causal,dtype", [
+    (2, 8, 2, 1024, 128, True, torch.float16),    # four pairs per head, the even tile of each idles on the last step
+    (1, 4, 4, 512, 128, False, torch.bfloat16),
+    (1, 2, 1, 200, 128, False, torch.float16),    # ragged: the second CTA's K half is partly out of range
+    (2, 4, 2, 129, 128, True, torch.bfloat16),    # the second tile has one row
+    (1, 2, 2, 640, 64, True, torch.float16),      # odd tile count: the last pair's second CTA has no tile
+])
+def test_forward_over_cta_pairs(B, Hq, Hkv, S, D, causal, dtype):
+    """The forward built on tcgen05 cta_group::2 (tuned entry ``fwd_pair``): output, saved LSE (through the gradients of
+    the backward that consumes it) against the oracle, and the output against the single-CTA forward's."""
+    q, k, v, d_o = helpers.seeded_qkv(B, Hq, Hkv, S, D, 128, dtype, seed=S + 1)
+    eng = helpers.softmax_engine(B, Hq, Hkv, S, D, 128, dtype, causal, tuned_config={"fwd_pair": 1})
+    assert eng.kernels.fwd_pair
+    got = _run(eng, q, k, v, d_o)
+    o, (dq, dk, dv) = orc.fwd_bwd(lambda a, b, c: orc.softmax_attention(a, b, c, causal), (q, k, v), d_o)
+    for name, g, r in zip(("o", "dq", "dk", "dv"), got, (o, dq, dk, dv)):
+        _check(name, g, r, dtype)
+    single = helpers.softmax_engine(B, Hq, Hkv, S, D, 128, dtype, causal)
+    assert not single.kernels.fwd_pair
+    o1, _ = single._launch_fwd(q.cuda(), k.cuda(), v.cuda(), ())
+    torch.cuda.synchronize()
+    torch.testing.assert_close(got[0].float(), o1.cpu().float(), rtol=0, atol=2e-3 if dtype == torch.float16 else 1.6e-2)
+
+
 def test_lse_is_saved_like_the_reference():
     """final_rowscales['lse'] is the natural-log LSE of the scaled scores, [B, H, S] fp32 (lower.py:385-392)."""
     B, Hq, Hkv, S, D = 1, 4, 2, 256, 64

@@ -28,11 +28,13 @@ def test_file_is_a_list_of_problem_entries_looked_up_by_keys(tmp_path):
 
 def test_candidates_fit_in_shared_memory():
     c = tune.candidates(128, 128, 1)
-    assert c["fwd"] == [{"stages": 2}]                               # three stages do not fit at head dim 128
+    # three stages do not fit at head dim 128; the forward over CTA pairs is a candidate at value head dim 128
+    assert c["fwd"] == [{"stages": 2}, {"fwd_pair": 1, "fwd_pair_stages": 5}]
     assert {"mode": "fused", "fused_tile": [2, 1, 4]} in c["bwd"]
     assert all(ab.fused_smem_bytes(128, 128, 2, *x["fused_tile"][:2]) <= tune.SMEM_MAX for x in c["bwd"] if x["mode"] == "fused")
     c64 = tune.candidates(64, 64, 1)
     assert {"stages": 4} in c64["fwd"] and len(c64["bwd"]) > len(c["bwd"])
+    assert not any("fwd_pair" in x for x in c64["fwd"])
 
 
 def test_engine_takes_its_tile_choice_from_the_tune_file(tmp_path, monkeypatch):
