@@ -65,6 +65,12 @@
 #error "the two-ahead S GEMM needs three K / V stages"
 #endif
 
+#ifdef AE_TRACE  // clock stamps of CTA (0, 0, 0)'s roles into the status buffer (experiments; needs a buffer that large)
+#define AE_TRW(cond, region, slot) \
+  if (tr_cta && (cond) && (slot) < 2048) args.status[64 + (region) * 4096 + (slot)] = (u32)clock64();
+#else
+#define AE_TRW(cond, region, slot)
+#endif
 // shared memory carve-up (dynamic, 1024-byte aligned by the launch)
 #define AE_Q_BYTES (AE_BM * AE_D * 2)
 #define AE_K_BYTES (AE_BN * AE_D * 2)
@@ -155,6 +161,9 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
   const int kt_off = 0;
 #endif
 
+#ifdef AE_TRACE
+  const bool tr_cta = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+#endif
   // ---- kv schedule (uniform over the CTA) ---------------------------------------
   int n_steps;
 #if AE_MASK_MODE == 1
@@ -450,9 +459,11 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
         auto tile_step = [&](auto T, u32& np) {
           constexpr int t = decltype(T)::value;
           if (!ok) return;
+          AE_TRW(true, 0, it * 8 + t * 4 + 0);
           if (cur.flags & (1u << t)) {
             ok = mbar_wait(&bars->p_full[t], np & 1, ctl, args.status, 5);
             if (!ok) return;
+            AE_TRW(true, 0, it * 8 + t * 4 + 1);
             if (!v_ready) {
               ok = mbar_wait(&bars->v_full[stage], par, ctl, args.status, 6);
               if (!ok) return;
@@ -462,6 +473,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
             issue_pv(T, stage, np > 0);
             umma_commit(&bars->o_done[t]);
             np++;
+            AE_TRW(true, 0, it * 8 + t * 4 + 2);
           }
           if (have_n && (nxt.flags & (1u << t))) {
             if (!k_ready) {
@@ -478,6 +490,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
             // other threads were fenced with the p_full wait of the step that made them)
             issue_s(T, nstage);
             umma_commit(&bars->s_full[t]);
+            AE_TRW(true, 0, it * 8 + t * 4 + 3);
           }
         };
         tile_step(AeInt<0>{}, np0);
@@ -568,7 +581,9 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       u64* const p_bar = &bars->p_full[t];
       const u32 s_par = n_done & 1u;
 #endif
+      AE_TRW((warp & 3) == 0 && half == 0 && lane == 0, 1 + t, n_done * 8 + 0);
       ok = ok && mbar_wait(s_bar, s_par, ctl, args.status, 9);
+      AE_TRW((warp & 3) == 0 && half == 0 && lane == 0, 1 + t, n_done * 8 + 1);
 #if AE_TURNS
       named_bar_sync(1 + t, AE_RSPLIT * 256);  // this group's turn
 #endif
@@ -597,6 +612,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
 #else
       tmem_ld_f32x128(tm_s_n, s);
 #endif
+      AE_TRW((warp & 3) == 0 && half == 0 && lane == 0, 1 + t, n_done * 8 + 2);
       const int kv0 = step.kt * AE_BN + (int)half * AE_NC;  // first kv column of this thread
       const bool tail = (step.kt * AE_BN + AE_BN > AE_SKV);
       const bool partial = (step.flags >> (2 + t)) & 1u;
@@ -621,6 +637,7 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       named_bar_arrive(2 - t, AE_RSPLIT * 256);  // the exponentials are done: the other group's turn
 #endif
 
+      AE_TRW((warp & 3) == 0 && half == 0 && lane == 0, 1 + t, n_done * 8 + 3);
       // P -> TMEM (16-bit pairs, column c/2 holds kv columns c, c+1)
       {
         u32 pk[32];
@@ -649,8 +666,10 @@ ae_attn_fwd(const __grid_constant__ AeAttnFwdArgs args) {
       }
 #endif
       tc_wait_st();
+      AE_TRW((warp & 3) == 0 && half == 0 && lane == 0, 1 + t, n_done * 8 + 4);
       tc_fence_before_sync();
       mbar_arrive_warp(p_bar);
+      AE_TRW((warp & 3) == 0 && half == 0 && lane == 0, 1 + t, n_done * 8 + 5);
       ++n_done;
     }
 
