@@ -30,6 +30,15 @@ def bwd_mode(request, monkeypatch):
     return request.param
 
 
+@pytest.fixture(params=["single", "pair"])
+def fwd_form(request, monkeypatch):
+    """A test that takes this fixture also runs with the forward over CTA pairs (tcgen05 cta_group::2) wherever the
+    engine's shape allows it (value head dim 128, no block lists)."""
+    from attentionengine_b200.attn_engine import attn_engine as ae
+    monkeypatch.setattr(ae, "FWD_PAIR", int(request.param == "pair"))
+    return request.param
+
+
 def _check(name, got, ref, dtype, unnormalised=False, stages=None):
     """bf16 rounding stages of the attention kernels: O and dV = (P rounded) x operand, stored -> 2; dQ and dK =
     (dS rounded) x operand, stored, with dS built from delta = rowsum(O dO) of the rounded O -> 3.  The linear-attention
@@ -121,7 +130,7 @@ def test_lse_is_saved_like_the_reference():
 
 
 @pytest.mark.parametrize("causal", [False, True])
-def test_sigmoid_attention(causal):
+def test_sigmoid_attention(causal, fwd_form):
     B, H, S, D, dtype = 1, 4, 512, 128, torch.bfloat16
     q, k, v, d_o = helpers.seeded_qkv(B, H, H, S, D, D, dtype, seed=11)
     bias = torch.tensor([-math.log(S)], dtype=torch.float32)
@@ -146,7 +155,7 @@ def test_relu_attention_against_reference_golden(golden_dir):
         assert rel <= REL_L2 and mx <= MAX_ABS * max(1.0, ref.abs().max().item()), f"{name}: {mx:.3e} {rel:.3e}"
 
 
-def test_relu_attention_benchmark_form():
+def test_relu_attention_benchmark_form(fwd_form):
     """P = relu(S / sqrt(D)) / S_len, non-causal, bf16 (config 3 of the benchmark, small)."""
     B, H, S, D, dtype = 1, 2, 512, 128, torch.bfloat16
     q, k, v, d_o = helpers.seeded_qkv(B, H, H, S, D, D, dtype, seed=12)
@@ -187,7 +196,7 @@ def test_sliding_window_block_sparse():
         _check(name, g, r, dtype)
 
 
-def test_dynamic_shape_engine_runs_several_lengths():
+def test_dynamic_shape_engine_runs_several_lengths(fwd_form):
     """One engine built from named dims serves different batch sizes and lengths: causal (analytic bounds) and a
     sliding window (tile lists rebuilt per shape)."""
     from attentionengine_b200 import AttentionEngine, CustomIO, meta_tensor
@@ -596,7 +605,7 @@ def test_extern_block_mask_given_at_call_time(D):
 
 
 @pytest.mark.gpu
-def test_element_mask_without_block_inference():
+def test_element_mask_without_block_inference(fwd_form):
     """infer_mask=False: every tile is visited and masked element by element (mask mode 3); a banded mask that the
     block inference would have turned into tile lists."""
     B, H, S, D, dtype, W = 1, 2, 384, 64, torch.float16, 100
@@ -622,7 +631,7 @@ def test_element_mask_without_block_inference():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("S,causal", [(384, True), (200, False)])
-def test_softcap_score_mod_keeps_the_raw_score_for_the_backward(S, causal):
+def test_softcap_score_mod_keeps_the_raw_score_for_the_backward(S, causal, fwd_form):
     """score_mod = cap * tanh(score * scale / cap): its derivative needs the raw score again, so the backward passes
     keep it next to P between their two row phases (the autodiff of Tanh is the reference's, core.py:129-195)."""
     B, Hq, Hkv, D, dtype, cap = 1, 4, 2, 128, torch.float16, 20.0
@@ -654,7 +663,7 @@ def test_softcap_score_mod_keeps_the_raw_score_for_the_backward(S, causal):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("S", [256, 384])
-def test_retention_parallel_with_tile_shaped_custom_input(S):
+def test_retention_parallel_with_tile_shaped_custom_input(S, fwd_form):
     """attn_script/retention.py: score * decay mask (custom input [1, H, S, S] in the input dtype), rows normalised by
     max(sum |.|, 1); forward and the three gradients against the oracle (bench_utils.py:1062-1067)."""
     B, H, D, DV, dtype = 1, 2, 128, 128, torch.float16
