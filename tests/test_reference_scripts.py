@@ -3,7 +3,8 @@
 ``import attn_engine`` / ``import core`` resolved to this package by ``install_reference_aliases()``, and an engine
 is built from the names the script defines, which traces, lowers and compiles its callables for sm_100a.
 
-Needs the reference's source tree (``AE_REFERENCE_ROOT``, default /root/reference); skipped where it is absent.
+Needs the reference's source tree (``AE_REFERENCE_ROOT``, default: a directory ``reference`` beside this repository);
+skipped where it is absent.
 No GPU: NVRTC compiles without one."""
 import os
 
@@ -12,7 +13,8 @@ import torch
 
 import attentionengine_b200 as ae
 
-REF = os.environ.get("AE_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("AE_REFERENCE_ROOT",
+                     os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "attn_script")),
                                 reason="reference source tree not present")
 
