@@ -77,7 +77,7 @@ def candidates(D: int, DV: int, n_final: int) -> dict:
     fused = [{"mode": "fused", "fused_tile": [q, d, g]} for q in (2, 3, 4) for d in (1, 2) for g in (4,)
              if ab.fused_smem_bytes(D, DV, ncs, q, d) <= SMEM_MAX]
     split = []
-    for bn, ks, vs in ((128, 3, 3), (128, 2, 2), (64, 4, 4)):
+    for bn, ks, vs in ((128, 3, 3), (128, 2, 2)):  # the dQ pass streams 128-row K / V tiles
         if bn * (ks * D + vs * DV) * 2 + 1536 <= SMEM_MAX:
             for dkv in ((128, 3, 2, 4, 0), (128, 2, 2, 4, 0), (128, 3, 3, 4, 0), (128, 2, 2, 2, 0)):
                 smem = 128 * (D + DV) * 2 + dkv[0] * (dkv[1] * D + dkv[2] * DV) * 2 + 2 * dkv[0] * ncs * 4 + 256
