@@ -104,6 +104,38 @@ class _Skip(torch.autograd.Function):
         return None, g, gx, gd
 
 
+class _ScaleScanSkip(torch.autograd.Function):
+    """y = scan(q, k, x * s[..., None], a) + x * d[head] as one node: row scale, scan and skip forward; in the backward
+    the two gradients that meet at x (through the scaled rows and through the skip) and the row sums for s and d come
+    out of one pass over x (ae_vskip_bwd) instead of two kernels and an add."""
+
+    @staticmethod
+    def forward(ctx, eng, q, k, x, a, s, d):
+        q, k, x, a, s = q.contiguous(), k.contiguous(), x.contiguous(), a.float().contiguous(), s.contiguous()
+        df = d.detach().float().reshape(-1).contiguous()
+        T, H = x.shape[2], x.shape[1]
+        v = torch.empty_like(x)
+        eng._rowscale("fwd", x, s, y=v)
+        o = eng._launch(q, k, v, a)
+        y = torch.empty_like(o)
+        eng._rowscale("skip_fwd", x, df, g=o, y=y, rows_per_head=T, n_heads=H)
+        ctx.eng, ctx.d_shape, ctx.d_dtype = eng, d.shape, d.dtype
+        ctx.save_for_backward(q, k, v, a, x, s, df)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        q, k, v, a, x, s, df = ctx.saved_tensors
+        g = g.contiguous()
+        dq, dk, dv, da = ctx.eng._launch_bwd(q, k, v, a, g)
+        gx, gs = torch.empty_like(x), torch.empty_like(s)
+        rows = torch.empty(x.shape[:3], dtype=torch.float32, device=x.device)
+        ctx.eng._rowscale("vskip_bwd", x, s, g=g, g2=dv, d=df, gx=gx, gs=gs, gs2=rows, rows_per_head=x.shape[2],
+                          n_heads=x.shape[1])
+        gd = rows.sum(dim=(0, 2)).reshape(ctx.d_shape).to(ctx.d_dtype)
+        return None, dq, dk, gx, da, gs, gd
+
+
 class LinearAttentionEngine:
     def __init__(self, qkv_meta, q_mod=None, k_mod=None, v_mod=None, decay_mod=None, custom_io=None, tune=False,
                  tune_filename="tune_result", tune_bwd=False, o_mod=None):
@@ -156,7 +188,7 @@ class LinearAttentionEngine:
             DV = 64  # the backward kernels are built for value blocks of 64
             tag = rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16
             pre = f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {DV}\n#define AE_LIN_STAGES 2\n"
-            smem_s = 2 * (128 * 128 * 2 + 128 * DV * 2) + 128 * DV * 2 + 1024 + 256 + 1024
+            smem_s = 2 * (128 * 128 * 2 + 128 * DV * 2) + 1024 + 256 + 1024  # two CTAs per SM
             cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_STATES, dtype=tag, head_dim=128, head_dim_v=DV, threads=192,
                                   smem_bytes=smem_s, stages=2, mask_mode=0)
             states = rt.compile_module(rt.kernel_source("linear_states.cuh", prelude=pre), "ae_linear_states", cfg)
@@ -200,7 +232,7 @@ class LinearAttentionEngine:
         """Launch one of the streaming kernels of rowscale.cuh: "fwd" / "bwd" (one scale per row) or "skip_fwd" /
         "skip_bwd" (one fp32 scale per head)."""
         D = x.shape[-1]
-        skip = which.startswith("skip")
+        skip = which.startswith("skip")  # s is the per-head fp32 weight vector
         s16 = s.dtype == self.dtype and not skip
         key = (which, D, s16)
         if key not in self._rowscale_mods:
@@ -208,7 +240,7 @@ class LinearAttentionEngine:
             cfg = rt.KernelConfig(kind=rt.KIND_ROWSCALE, dtype=rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16, head_dim=D,
                                   head_dim_v=D, threads=256, smem_bytes=0, stages=1, mask_mode=0)
             cfg.reserved[0] = int(s16)
-            name = f"ae_{which}" if skip else f"ae_rowscale_{which}"
+            name = f"ae_{which}" if (skip or which == "vskip_bwd") else f"ae_rowscale_{which}"
             self._rowscale_mods[key] = rt.compile_module(rt.kernel_source("rowscale.cuh", prelude=pre), name, cfg)
         p = rt.RowScaleParams()
         p.x, p.s, p.n_rows = x.data_ptr(), s.data_ptr(), x.numel() // D
@@ -335,6 +367,11 @@ class LinearAttentionEngine:
         a = self._apply_mod("decay", decay, custom)
         qm = self._apply_mod("q", q, custom)
         km = self._apply_mod("k", k, custom)
+        if self.o_mod is not None and "v" in self._traced and self.DK == 128 and self.DV == 64 and v.dtype == self.dtype:
+            # `v * s[b, h, t]` into the scan and `o + v * d[h]` after it (the Mamba2 block): one autograd node
+            s, d = self._rowscale_operand("v", v, custom), self._skip_operand(custom)
+            if s is not None and d is not None:
+                return _ScaleScanSkip.apply(self, qm, km, v, a, s, d)
         vm = self._apply_mod("v", v, custom)
         o = self._scan(qm, km, vm, a)
         return o if self.o_mod is None else self._apply_o_mod(o, v, custom)

@@ -891,14 +891,19 @@ int ae_launch_rowscale(void* module, const AeRowScaleParams* p, void* stream) {
     set_error("module kind does not match the entry point");
     return AE_ERR_UNSUPPORTED;
   }
-  const bool skip = m->kernel == "ae_skip_fwd" || m->kernel == "ae_skip_bwd";
-  const bool bwd = m->kernel == "ae_rowscale_bwd" || m->kernel == "ae_skip_bwd";
+  const bool both = m->kernel == "ae_vskip_bwd";
+  const bool skip = m->kernel == "ae_skip_fwd" || m->kernel == "ae_skip_bwd" || both;
+  const bool bwd = m->kernel == "ae_rowscale_bwd" || m->kernel == "ae_skip_bwd" || both;
   if (bwd ? (!p->g || !p->gx || !p->gs) : !p->y) return AE_ERR_INVALID;
   if (skip && (!p->g || p->rows_per_head <= 0 || p->n_heads <= 0)) {
     set_error("skip kernels need g, rows_per_head > 0 and n_heads > 0");
     return AE_ERR_INVALID;
   }
-  const void* ptrs[5] = {p->x, p->y, p->g, p->gx, nullptr};
+  if (both && (!p->g2 || !p->d || !p->gs2)) {
+    set_error("ae_vskip_bwd needs g2, d and gs2");
+    return AE_ERR_INVALID;
+  }
+  const void* ptrs[5] = {p->x, p->y, p->g, p->gx, both ? p->g2 : nullptr};
   for (const void* q : ptrs)
     if (q && (reinterpret_cast<uintptr_t>(q) & 15)) {
       set_error("row-scale tensors must be 16-byte aligned");
@@ -913,6 +918,11 @@ int ae_launch_rowscale(void* module, const AeRowScaleParams* p, void* stream) {
   a.n_rows = p->n_rows;
   a.rows_per_head = skip ? p->rows_per_head : 1;
   a.n_heads = skip ? p->n_heads : 1;
+  if (both) {
+    a.g2 = p->g2;
+    a.d = p->d;
+    a.gs2 = p->gs2;
+  }
   // 16 bytes per lane, 256 threads per CTA, up to 16 CTAs per SM's worth of blocks; the kernels stride over the rest
   const int64_t lanes = p->n_rows * (m->cfg.head_dim / 8);
   int64_t blocks = (lanes + 255) / 256;

@@ -170,6 +170,11 @@ struct AeRowScaleArgs {
   // per-head skip kernels (ae_skip_fwd / ae_skip_bwd): s is [n_heads] fp32, a row's head is (row / rows_per_head) % n_heads
   i64 rows_per_head;
   int n_heads;
+  // ae_vskip_bwd (row scale and skip of one block, both gradients in one pass): g2 = gradient of the scaled rows,
+  // d [n_heads] fp32 skip weights, gs2 [n_rows] fp32 = sum_d g * x
+  const void* g2;
+  const float* d;
+  float* gs2;
 };
 
 // ---- UMMA / TMA probe kernels (bring-up checks, kernel ae_probe) -------------------

@@ -4,6 +4,8 @@
 // Same walk as linear_fwd.cuh without the output path: per chunk the incoming state H [DK x DV] is
 // written to HBM in 16-bit, decayed by exp(g_last) and updated with k^T (v * exp(g_last - g)).
 // Roles: warps 0-3 row threads (thread r = step r = state row r), warp 4 TMA producer, warp 5 MMA issuer.
+// The kernel is a chain of short dependent steps per chunk, so two CTAs share an SM: 98 KB of shared memory (the
+// rescaled values overwrite the V tile they came from) and 128 TMEM columns each.
 // Expects AE_BF16, AE_LIN_DV, AE_LIN_STAGES.
 
 #define AE_LS_C 128
@@ -11,8 +13,7 @@
 #define AE_LS_K_BYTES (AE_LS_C * AE_LS_DK * 2)
 #define AE_LS_V_BYTES (AE_LS_C * AE_LIN_DV * 2)
 #define AE_LS_STAGE_BYTES (AE_LS_K_BYTES + AE_LS_V_BYTES)
-#define AE_LS_SMEM_V2 (AE_LIN_STAGES * AE_LS_STAGE_BYTES)
-#define AE_LS_SMEM_G (AE_LS_SMEM_V2 + AE_LS_V_BYTES)
+#define AE_LS_SMEM_G (AE_LIN_STAGES * AE_LS_STAGE_BYTES)
 #define AE_LS_SMEM_BAR (AE_LS_SMEM_G + 1024)
 
 struct AeLsBars {
@@ -23,7 +24,7 @@ struct AeLsBars {
   AeCtaCtl ctl;
 };
 
-extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_states(const __grid_constant__ AeLinearBwdArgs args) {
+extern "C" __global__ void __launch_bounds__(192, 2) ae_linear_states(const __grid_constant__ AeLinearBwdArgs args) {
   extern __shared__ u8 smem_raw[];
   u8* smem = smem_align1024(smem_raw);
   AeLsBars* bars = (AeLsBars*)(smem + AE_LS_SMEM_BAR);
@@ -72,8 +73,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_states(const __gr
   } else if (warp == 5) {
     if (lane == 0) {
       const u32 idesc_h = umma_idesc_f16(AE_LS_DK, AE_LIN_DV, AE_BF16, 1, 1);
-      const u32 v2_addr = smem_u32(smem + AE_LS_SMEM_V2);
-      const u64 bk_mn = umma_base_mn(smem_u32(smem), AE_LS_C), bv2_mn = umma_base_mn(v2_addr, AE_LS_C);
+      const u64 bk_mn = umma_base_mn(smem_u32(smem), AE_LS_C);
+      const u64 bv_mn = umma_base_mn(smem_u32(smem + AE_LS_K_BYTES), AE_LS_C);  // the stage's V tile, rescaled in place
       bool ok = true;
       for (int c = 0; c < n_chunks && ok; ++c) {
         const int stage = c % AE_LIN_STAGES;
@@ -83,7 +84,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_states(const __gr
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < AE_LS_C / 16; ++kk)
-          umma_ss(tmem, umma_step_mn(bk_mn + so, kk), umma_step_mn(bv2_mn, kk), idesc_h, (c > 0) | (kk > 0));
+          umma_ss(tmem, umma_step_mn(bk_mn + so, kk), umma_step_mn(bv_mn + so, kk), idesc_h, (c > 0) | (kk > 0));
         umma_commit(&bars->h_done);
         umma_commit(&bars->empty[stage]);
       }
@@ -147,8 +148,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_states(const __gr
       ok = ok && mbar_wait(&bars->full[stage], (c / AE_LIN_STAGES) & 1, ctl, args.status, 64);
       {
         const float wgt = ae_exp(g_last - g);
-        const u8* vt = smem + stage * AE_LS_STAGE_BYTES + AE_LS_K_BYTES;
-        u8* v2 = smem + AE_LS_SMEM_V2;
+        u8* vt = smem + stage * AE_LS_STAGE_BYTES + AE_LS_K_BYTES;  // row r of the tile is this thread's alone
 #pragma unroll
         for (int ch = 0; ch < AE_LIN_DV / 8; ++ch) {
           const u32 off = tile_off(r, ch * 8, AE_LS_C);
@@ -157,15 +157,14 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_states(const __gr
 #pragma unroll
           for (int i = 0; i < 4; ++i)
             xw[i] = pack2<AE_BF16>(unpack_lo<AE_BF16>(xw[i]) * wgt, unpack_hi<AE_BF16>(xw[i]) * wgt);
-          *(uint4*)(v2 + off) = x;
+          *(uint4*)(vt + off) = x;
         }
       }
       tc_wait_st();
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->prep_done);
-      // v2 may only be rewritten once this chunk's update has read it: next iteration waits on h_done(c)
-      // before touching TMEM, but v2 is written after that wait as well (program order), so it is safe.
+      // the stage (K and the rescaled V) goes back to the producer with the commit that follows this chunk's MMAs
     }
   }
   tc_fence_before_sync();

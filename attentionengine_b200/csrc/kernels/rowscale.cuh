@@ -17,6 +17,12 @@
 //             sums it over batch and steps to get the gradient of d)
 // with head(r) = (r / rows_per_head) % n_heads and d [n_heads] fp32 in `s`.
 
+//
+// And the two backward passes of a block that uses both (v' = x * s[row] into the scan, y = o + x * d[head] after it), as
+// one pass over x:   gx[r, :] = g2[r, :] * s[r] + g[r, :] * d[head(r)],   gs[r] = sum_d g2 * x,   gs2[r] = sum_d g * x
+// with g the gradient of y and g2 the gradient of v' (ae_vskip_bwd): x is read once, and the sum of the two
+// contributions to gx needs no pass of its own.
+
 #define AE_RS_TPR (AE_RS_D / 8)        // lanes per row
 #define AE_RS_RPW (32 / AE_RS_TPR)     // rows per warp and iteration
 #if AE_RS_D != 64 && AE_RS_D != 128 && AE_RS_D != 256
@@ -140,5 +146,51 @@ extern "C" __global__ void __launch_bounds__(256) ae_skip_bwd(const AeRowScaleAr
 #pragma unroll
     for (int o = AE_RS_TPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
     if (valid && (lane % AE_RS_TPR) == 0) ((float*)a.gs)[row] = dot;
+  }
+}
+
+extern "C" __global__ void __launch_bounds__(256) ae_vskip_bwd(const AeRowScaleArgs a) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp0 = ((i64)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const i64 n_warps = ((i64)gridDim.x * 256) >> 5;
+  for (i64 base = warp0 * AE_RS_RPW; base < a.n_rows; base += n_warps * AE_RS_RPW) {
+    const i64 row = base + lane / AE_RS_TPR;
+    const bool valid = row < a.n_rows;
+    float dot_v = 0.f, dot_o = 0.f;
+    if (valid) {
+      const i64 off = row * AE_RS_D + (lane % AE_RS_TPR) * 8;
+      const uint4 g = *(const uint4*)((const u16*)a.g + off);
+      const uint4 g2 = *(const uint4*)((const u16*)a.g2 + off);
+      const uint4 x = *(const uint4*)((const u16*)a.x + off);
+      const float sc = ae_rs_load_s(a.s, row);
+      const float dh = a.d[(row / a.rows_per_head) % a.n_heads];
+      const u32 gw[4] = {g.x, g.y, g.z, g.w}, vw[4] = {g2.x, g2.y, g2.z, g2.w}, xw[4] = {x.x, x.y, x.z, x.w};
+      u32 ow[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float g0 = unpack_lo<AE_BF16>(gw[i]), g1 = unpack_hi<AE_BF16>(gw[i]);
+        const float v0 = unpack_lo<AE_BF16>(vw[i]), v1 = unpack_hi<AE_BF16>(vw[i]);
+        const float x0 = unpack_lo<AE_BF16>(xw[i]), x1 = unpack_hi<AE_BF16>(xw[i]);
+        dot_v = fmaf(v0, x0, dot_v);
+        dot_v = fmaf(v1, x1, dot_v);
+        dot_o = fmaf(g0, x0, dot_o);
+        dot_o = fmaf(g1, x1, dot_o);
+        ow[i] = pack2<AE_BF16>(fmaf(v0, sc, g0 * dh), fmaf(v1, sc, g1 * dh));
+      }
+      *(uint4*)((u16*)a.gx + off) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+#pragma unroll
+    for (int o = AE_RS_TPR / 2; o > 0; o >>= 1) {
+      dot_v += __shfl_xor_sync(0xffffffffu, dot_v, o);
+      dot_o += __shfl_xor_sync(0xffffffffu, dot_o, o);
+    }
+    if (valid && (lane % AE_RS_TPR) == 0) {
+#if AE_RS_S16
+      ((u16*)a.gs)[row] = (u16)(pack2<AE_BF16>(dot_v, 0.f) & 0xffffu);
+#else
+      ((float*)a.gs)[row] = dot_v;
+#endif
+      a.gs2[row] = dot_o;
+    }
   }
 }

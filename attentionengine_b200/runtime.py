@@ -92,7 +92,8 @@ class DecodeParams(C.Structure):
 
 class RowScaleParams(C.Structure):
     _fields_ = [("x", C.c_void_p), ("s", C.c_void_p), ("y", C.c_void_p), ("g", C.c_void_p), ("gx", C.c_void_p),
-                ("gs", C.c_void_p), ("n_rows", C.c_int64), ("rows_per_head", C.c_int64), ("n_heads", C.c_int32)]
+                ("gs", C.c_void_p), ("n_rows", C.c_int64), ("rows_per_head", C.c_int64), ("n_heads", C.c_int32),
+                ("g2", C.c_void_p), ("d", C.c_void_p), ("gs2", C.c_void_p)]
 
 
 class MlaPagedParams(C.Structure):

@@ -321,7 +321,10 @@ int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream);
  * o += D_skip[h] * x; no counterpart in the reference, whose harness passes D=None, benchmark/bench_utils.py:304-308),
  * for rows ordered (batch, head, step): s is then [n_heads] fp32 and a row's head is (row / rows_per_head) % n_heads.
  * "ae_skip_fwd" writes y = g + x * s[head] (g carries the scan output); "ae_skip_bwd" writes gx = g * s[head] and
- * gs[row] = sum_d g * x in fp32 (summed over batch and steps by the caller for the gradient of s). */
+ * gs[row] = sum_d g * x in fp32 (summed over batch and steps by the caller for the gradient of s).
+ * "ae_vskip_bwd" is the backward of a block that uses both (v' = x * s[row] into the scan, y = o + x * d[head] after
+ * it) in one pass over x: gx = g2 * s[row] + g * d[head], gs[row] = sum_d g2 * x (type of s), gs2[row] = sum_d g * x
+ * (fp32), with g the gradient of y and g2 the gradient of v'. */
 typedef struct AeRowScaleParams {
   const void* x;
   const void* s;
@@ -332,6 +335,9 @@ typedef struct AeRowScaleParams {
   int64_t n_rows;
   int64_t rows_per_head; /* skip kernels only */
   int32_t n_heads;       /* skip kernels only */
+  const void* g2;        /* ae_vskip_bwd only: gradient of the scaled rows */
+  const float* d;        /* ae_vskip_bwd only: [n_heads] skip weights */
+  float* gs2;            /* ae_vskip_bwd only: [n_rows] */
 } AeRowScaleParams;
 
 int ae_launch_rowscale(void* module, const AeRowScaleParams* p, void* stream);
