@@ -49,13 +49,18 @@ class _Scan(torch.autograd.Function):
     def forward(ctx, eng, q, k, v, a):
         q, k, v, a = q.contiguous(), k.contiguous(), v.contiguous(), a.float().contiguous()
         ctx.eng = eng
-        ctx.save_for_backward(q, k, v, a)
-        return eng._launch(q, k, v, a)
+        # with a backward to come (value blocks of 64), the forward also writes the chunk start-states it has at hand
+        hs = eng._new_states(v) if (any(ctx.needs_input_grad) and v.shape[3] == 64) else None
+        o = eng._launch(q, k, v, a, h_out=hs)
+        ctx.has_states = hs is not None
+        ctx.save_for_backward(q, k, v, a, *([hs] if hs is not None else []))
+        return o
 
     @staticmethod
     def backward(ctx, d_o):
-        q, k, v, a = ctx.saved_tensors
-        dq, dk, dv, da = ctx.eng._launch_bwd(q, k, v, a, d_o.contiguous())
+        q, k, v, a = ctx.saved_tensors[:4]
+        hs = ctx.saved_tensors[4] if ctx.has_states else None
+        dq, dk, dv, da = ctx.eng._launch_bwd(q, k, v, a, d_o.contiguous(), hs=hs)
         return None, dq, dk, dv, da
 
 
@@ -105,29 +110,31 @@ class _Skip(torch.autograd.Function):
 
 
 class _ScaleScanSkip(torch.autograd.Function):
-    """y = scan(q, k, x * s[..., None], a) + x * d[head] as one node: row scale, scan and skip forward; in the backward
-    the two gradients that meet at x (through the scaled rows and through the skip) and the row sums for s and d come
-    out of one pass over x (ae_vskip_bwd) instead of two kernels and an add."""
+    """y = scan(q, k, x * s[..., None], a) + x * d[head] as one node.  Forward: one launch of the scan kernel built
+    with the two mods inside.  Backward: the two gradients that meet at x (through the scaled rows and through the
+    skip) and the row sums for s and d come out of one pass over x (ae_vskip_bwd) instead of two kernels and an add."""
 
     @staticmethod
     def forward(ctx, eng, q, k, x, a, s, d):
         q, k, x, a, s = q.contiguous(), k.contiguous(), x.contiguous(), a.float().contiguous(), s.contiguous()
         df = d.detach().float().reshape(-1).contiguous()
-        T, H = x.shape[2], x.shape[1]
-        v = torch.empty_like(x)
-        eng._rowscale("fwd", x, s, y=v)
-        o = eng._launch(q, k, v, a)
-        y = torch.empty_like(o)
-        eng._rowscale("skip_fwd", x, df, g=o, y=y, rows_per_head=T, n_heads=H)
+        # one kernel: the scan scales its V rows by s, adds x * d[head] to its output rows and writes the scaled v
+        # for the backward (only when a gradient is wanted)
+        need_v = any(ctx.needs_input_grad)
+        v = torch.empty_like(x) if need_v else None
+        hs = eng._new_states(x) if need_v else None  # the chunk start-states, for the reverse pass
+        y = eng._launch(q, k, x, a, vscale=s, dskip=df, v_out=v, h_out=hs)
         ctx.eng, ctx.d_shape, ctx.d_dtype = eng, d.shape, d.dtype
-        ctx.save_for_backward(q, k, v, a, x, s, df)
+        if not need_v:
+            return y
+        ctx.save_for_backward(q, k, v, a, x, s, df, hs)
         return y
 
     @staticmethod
     def backward(ctx, g):
-        q, k, v, a, x, s, df = ctx.saved_tensors
+        q, k, v, a, x, s, df, hs = ctx.saved_tensors
         g = g.contiguous()
-        dq, dk, dv, da = ctx.eng._launch_bwd(q, k, v, a, g)
+        dq, dk, dv, da = ctx.eng._launch_bwd(q, k, v, a, g, hs=hs)
         gx, gs = torch.empty_like(x), torch.empty_like(s)
         rows = torch.empty(x.shape[:3], dtype=torch.float32, device=x.device)
         ctx.eng._rowscale("vskip_bwd", x, s, g=g, g2=dv, d=df, gx=gx, gs=gs, gs2=rows, rows_per_head=x.shape[2],
@@ -172,16 +179,23 @@ class LinearAttentionEngine:
         self._dv_block = self.DV if self.DV in (64, 128) else (128 if self.DV % 128 == 0 else 64)
         self.fwd, self.tl_code = self._fwd_kernel(self._dv_block)
 
-    def _fwd_kernel(self, dv: int):
-        if dv not in self._fwd_by_dv:
+    def _fwd_kernel(self, dv: int, mods: bool = False):
+        """The forward kernel for value blocks of ``dv``; ``mods``: the build with the row scale of v and the skip
+        connection inside (one more 128 x dv tile of shared memory)."""
+        key = (dv, mods)
+        if key not in self._fwd_by_dv:
             stages = 2 if dv == 64 else 1
-            prelude = f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {dv}\n#define AE_LIN_STAGES {stages}\n"
+            prelude = (f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {dv}\n#define AE_LIN_STAGES {stages}\n"
+                       f"#define AE_LIN_MODS {int(mods)}\n")
             smem = stages * (2 * 128 * 128 * 2 + 128 * dv * 2) + 128 * dv * 2 + 128 * dv * 2 + 1024 + 256 + 1024
+            if mods:
+                smem += 128 * dv * 2
             cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_FWD, dtype=rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16,
                                   head_dim=128, head_dim_v=dv, threads=192, smem_bytes=smem, stages=stages, mask_mode=0)
+            cfg.reserved[0] = int(mods)
             src = rt.kernel_source("linear_fwd.cuh", prelude=prelude)
-            self._fwd_by_dv[dv] = (rt.compile_module(src, "ae_linear_fwd", cfg), src)
-        return self._fwd_by_dv[dv]
+            self._fwd_by_dv[key] = (rt.compile_module(src, "ae_linear_fwd", cfg), src)
+        return self._fwd_by_dv[key]
 
     def _bwd_kernels(self):
         if self._bwd is None:
@@ -200,7 +214,13 @@ class LinearAttentionEngine:
             self._bwd = (states, bwd)
         return self._bwd
 
-    def _launch_bwd(self, q, k, v, a, d_o):
+    def _new_states(self, v):
+        """Storage for the chunk start-states of a scan over v [B, H, T, DV]: [B, H, ceil(T / 128), 128, DV]."""
+        B, H, T, DV = v.shape
+        return torch.empty(B, H, -(-T // 128), 128, DV, dtype=self.dtype, device=v.device)
+
+    def _launch_bwd(self, q, k, v, a, d_o, hs=None):
+        """State recompute (unless the forward saved the states in ``hs``) and the reverse pass."""
         if v.shape[3] != 64:
             raise NotImplementedError("backward of the linear-attention scan runs on value blocks of 64")
         states, bwd = self._bwd_kernels()
@@ -208,8 +228,9 @@ class LinearAttentionEngine:
         HK = k.shape[1]
         H, DV = v.shape[1], v.shape[3]
         dev = q.device
-        nc = -(-T // 128)
-        hs = torch.empty(B, H, nc, DK, DV, dtype=self.dtype, device=dev)
+        recompute = hs is None
+        if recompute:
+            hs = self._new_states(v)
         dq_h = torch.empty(B, H, T, DK, dtype=self.dtype, device=dev)
         dk_h = torch.empty(B, H, T, DK, dtype=self.dtype, device=dev)
         dv = torch.empty(B, H, T, DV, dtype=self.dtype, device=dev)
@@ -222,11 +243,28 @@ class LinearAttentionEngine:
             self._status = torch.zeros(1, dtype=torch.int32, device=dev)
         p.status = self._status.data_ptr()
         stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-        rt.check(rt.lib().ae_launch_linear_states(states.handle, C.byref(p), stream), "ae_launch_linear_states")
+        if recompute:
+            rt.check(rt.lib().ae_launch_linear_states(states.handle, C.byref(p), stream), "ae_launch_linear_states")
         rt.check(rt.lib().ae_launch_linear_bwd(bwd.handle, C.byref(p), stream), "ae_launch_linear_bwd")
-        dq = dq_h if HQ == H else dq_h.view(B, HQ, H // HQ, T, DK).sum(2, dtype=torch.float32).to(self.dtype)
-        dk = dk_h if HK == H else dk_h.view(B, HK, H // HK, T, DK).sum(2, dtype=torch.float32).to(self.dtype)
+        dq = dq_h if HQ == H else self._head_sum(dq_h, HQ)
+        dk = dk_h if HK == H else self._head_sum(dk_h, HK)
         return dq, dk, dv, da
+
+    def _head_sum(self, x, n_out):
+        """[B, H, T, D] -> [B, n_out, T, D]: sum over the H / n_out heads of each group, fp32 accumulation, one pass."""
+        B, H, T, D = x.shape
+        y = torch.empty(B, n_out, T, D, dtype=x.dtype, device=x.device)
+        key = ("head_sum", D, False)
+        if key not in self._rowscale_mods:
+            pre = f"#define AE_BF16 {int(self._bf16)}\n#define AE_RS_D {D}\n#define AE_RS_S16 0\n"
+            cfg = rt.KernelConfig(kind=rt.KIND_ROWSCALE, dtype=rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16, head_dim=D,
+                                  head_dim_v=D, threads=256, smem_bytes=0, stages=1, mask_mode=0)
+            self._rowscale_mods[key] = rt.compile_module(rt.kernel_source("rowscale.cuh", prelude=pre), "ae_head_sum", cfg)
+        p = rt.RowScaleParams()
+        p.x, p.y, p.n_rows, p.rows_per_head, p.n_heads = x.data_ptr(), y.data_ptr(), B * n_out * T, T, H // n_out
+        stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+        rt.check(rt.lib().ae_launch_rowscale(self._rowscale_mods[key].handle, C.byref(p), stream), "ae_launch_rowscale")
+        return y
 
     def _rowscale(self, which, x, s, rows_per_head=0, n_heads=0, **out):
         """Launch one of the streaming kernels of rowscale.cuh: "fwd" / "bwd" (one scale per row) or "skip_fwd" /
@@ -307,7 +345,9 @@ class LinearAttentionEngine:
             env[id(sym)] = _align(t, tuple(sym.shape_idx), o.dim())
         return evaluate(self._o_traced, env).to(o.dtype)
 
-    def _launch(self, q, k, v, a):
+    def _launch(self, q, k, v, a, vscale=None, dskip=None, v_out=None, h_out=None):
+        """The scan kernel.  With ``vscale`` [B, H, T] / ``dskip`` [H] fp32 the build with the mods inside runs: scan of
+        v * vscale plus v * dskip[h]; ``v_out`` receives the scaled v."""
         B, HQ, T, DK = q.shape
         H, DV = v.shape[1], v.shape[3]
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
@@ -315,12 +355,23 @@ class LinearAttentionEngine:
         o = torch.empty(B, H, T, DV, dtype=self.dtype, device=q.device)
         p = rt.LinearParams()
         p.q, p.k, p.v, p.a, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), a.data_ptr(), o.data_ptr()
+        mods = vscale is not None or dskip is not None
+        if mods:
+            if vscale is not None:
+                p.vscale, p.vscale_16bit = vscale.data_ptr(), int(vscale.dtype != torch.float32)
+            if dskip is not None:
+                p.dskip = dskip.data_ptr()
+            if v_out is not None:
+                p.v_out = v_out.data_ptr()
+        if h_out is not None:
+            p.h_states_out = h_out.data_ptr()
         p.B, p.H, p.HQ, p.HK, p.T = B, H, HQ, k.shape[1], T
         if self._status is None or self._status.device != q.device:
             self._status = torch.zeros(1, dtype=torch.int32, device=q.device)
         p.status = self._status.data_ptr()
         stream = C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
-        rt.check(rt.lib().ae_launch_linear_fwd(self._fwd_kernel(DV)[0].handle, C.byref(p), stream), "ae_launch_linear_fwd")
+        rt.check(rt.lib().ae_launch_linear_fwd(self._fwd_kernel(DV, mods)[0].handle, C.byref(p), stream),
+                 "ae_launch_linear_fwd")
         return o
 
     def _scan(self, q, k, v, a):

@@ -187,8 +187,11 @@ int ensure_loaded(Module* m) {
   l.ctx = ctx;
   AE_CU(d.cuModuleLoadData(&l.mod, m->cubin.data()));
   AE_CU(d.cuModuleGetFunction(&l.fn, l.mod, m->kernel.c_str()));
-  if (m->cfg.smem_bytes > 48 * 1024)
+  if (m->cfg.smem_bytes > 48 * 1024) {
     AE_CU(d.cuFuncSetAttribute(l.fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, m->cfg.smem_bytes));
+    // the largest shared-memory carve-out, so that kernels sized for two CTAs per SM (about 100 KB each) get both
+    AE_CU(d.cuFuncSetAttribute(l.fn, CU_FUNC_ATTRIBUTE_PREFERRED_SHARED_MEMORY_CARVEOUT, CU_SHAREDMEM_CARVEOUT_MAX_SHARED));
+  }
   m->loaded.push_back(l);
   g_fn = l.fn;
   return AE_OK;
@@ -885,11 +888,33 @@ int ae_launch_decode_combine(void* module, const AeDecodeParams* p, void* stream
 }
 
 int ae_launch_rowscale(void* module, const AeRowScaleParams* p, void* stream) {
-  if (!module || !p || !p->x || !p->s || p->n_rows < 0) return AE_ERR_INVALID;
+  if (!module || !p || !p->x || p->n_rows < 0) return AE_ERR_INVALID;
   Module* m = (Module*)module;
+  if (!p->s && m->kernel != "ae_head_sum") return AE_ERR_INVALID;
   if (m->cfg.kind != AE_KIND_ROWSCALE) {
     set_error("module kind does not match the entry point");
     return AE_ERR_UNSUPPORTED;
+  }
+  if (m->kernel == "ae_head_sum") {
+    // x [groups, G, T, D] -> y [groups, T, D]: n_rows output rows, rows_per_head = T, n_heads = G; s is not used
+    if (!p->y || p->rows_per_head <= 0 || p->n_heads <= 0 || p->n_rows % p->rows_per_head) {
+      set_error("ae_head_sum needs y, rows_per_head = T > 0, n_heads = G > 0 and n_rows a multiple of T");
+      return AE_ERR_INVALID;
+    }
+    if ((reinterpret_cast<uintptr_t>(p->x) & 15) || (reinterpret_cast<uintptr_t>(p->y) & 15)) {
+      set_error("row-scale tensors must be 16-byte aligned");
+      return AE_ERR_INVALID;
+    }
+    if (p->n_rows == 0) return AE_OK;
+    int rc = ensure_loaded(m);
+    if (rc) return rc;
+    AeRowScaleArgs a;
+    memset(&a, 0, sizeof a);
+    a.x = p->x; a.y = p->y; a.n_rows = p->n_rows; a.rows_per_head = p->rows_per_head; a.n_heads = p->n_heads;
+    const int64_t lanes = p->n_rows * (m->cfg.head_dim / 8);
+    int64_t blocks = (lanes + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    return launch(m, (unsigned)blocks, 1, 1, &a, stream);
   }
   const bool both = m->kernel == "ae_vskip_bwd";
   const bool skip = m->kernel == "ae_skip_fwd" || m->kernel == "ae_skip_bwd" || both;
@@ -976,6 +1001,26 @@ int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream) {
   a.o = p->o;
   a.B = p->B; a.H = p->H; a.HQ = p->HQ; a.HK = p->HK; a.T = p->T;
   a.status = p->status;
+  if (p->h_states_out && (reinterpret_cast<uintptr_t>(p->h_states_out) & 15)) {
+    set_error("linear attention: h_states_out must be 16-byte aligned");
+    return AE_ERR_INVALID;
+  }
+  a.h_out = p->h_states_out;
+  // modules built with the block's mods inside (config reserved[0] = 1) take the three optional operands
+  if (m->cfg.reserved[0] == 1) {
+    if ((p->v_out && (reinterpret_cast<uintptr_t>(p->v_out) & 15)) ||
+        (p->vscale && (reinterpret_cast<uintptr_t>(p->vscale) & (p->vscale_16bit ? 1 : 3)))) {
+      set_error("linear attention: v_out must be 16-byte aligned, vscale aligned to its element size");
+      return AE_ERR_INVALID;
+    }
+    a.vscale = p->vscale;
+    a.vscale_16 = p->vscale_16bit;
+    a.dskip = p->dskip;
+    a.v_out = p->v_out;
+  } else if (p->vscale || p->dskip || p->v_out) {
+    set_error("linear attention: vscale / dskip / v_out need a module built with the mods inside (reserved[0] = 1)");
+    return AE_ERR_INVALID;
+  }
   return launch(m, (unsigned)p->H, (unsigned)p->B, 1, &a, stream);
 }
 

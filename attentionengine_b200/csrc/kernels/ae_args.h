@@ -139,6 +139,15 @@ struct AeLinearArgs {
   void* o;         // [B, H, T, DV] 16-bit
   int B, H, HQ, HK, T;
   u32* status;
+  // Build with AE_LIN_MODS (the Mamba2 block's mods inside the kernel): the scan runs on v = x * vscale[b, h, t] with x
+  // the tensor behind tm_v, the output is scan + x * dskip[h], and v is written out for the backward when v_out is set.
+  const void* vscale;  // [B, H, T] fp32, or the 16-bit type when vscale_16 != 0
+  const float* dskip;  // [H] fp32, or null
+  void* v_out;         // [B, H, T, DV] 16-bit, or null
+  int vscale_16;
+  // Any build: when set, the state each chunk starts from is written here in 16-bit, [B, H, n_chunks, DK, DV] (what
+  // ae_linear_states would recompute for the backward).
+  void* h_out;
 };
 
 // ---- chunked linear attention backward (kernels ae_linear_states, ae_linear_bwd) ---------

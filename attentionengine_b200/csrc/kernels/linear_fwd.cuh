@@ -1,7 +1,8 @@
 // Chunked linear-attention / SSD scan, forward, for sm_100a.  Replaces the reference's
 // `chunk_local_cumsum_scalar_kernel` + `chunk_fwd_h` + `chunk_o` kernels
 // (attention_engine/core/template/tl_template/linear/linear_tl.py:25-49, 114-233, 283-410) with one
-// kernel that never writes the per-chunk states to HBM.
+// kernel that does not need the per-chunk states in HBM (it writes them, 16-bit, only when the caller asks for them for
+// the backward: args.h_out; the reference always stores and re-reads them).
 //
 // Recurrence per (batch, head), with a_t <= 0 the log-decay of step t:
 //     S_t = exp(a_t) S_{t-1} + k_t^T v_t ,      o_t = q_t S_t
@@ -17,6 +18,15 @@
 // reference evaluates it everywhere and masks afterwards (linear_tl.py:372-378).
 // Roles: warps 0-3 row threads (thread r = step r of the chunk = state row r), warp 4 TMA producer,
 // warp 5 MMA issuer.  Expects AE_BF16, AE_LIN_DV (64 or 128), AE_LIN_STAGES; DK is 128.
+//
+// AE_LIN_MODS = 1 builds the Mamba2 block's two mods into the kernel (the reference runs them as eager PyTorch
+// statements around its kernels, linear_tl.py:1136-1144; mamba2_ngroup1.py:31-33 is `v * dt`): the tensor behind tm_v
+// is x, the scan runs on v = x * vscale[b, h, t] (the row thread that rescales its row of the V tile for the state
+// update anyway also scales it in place for P v and writes v out for the backward), and the output row gets
+// + x * dskip[h] from a copy of the raw row kept in shared memory.  Two streaming passes over x and one over o less.
+#ifndef AE_LIN_MODS
+#define AE_LIN_MODS 0
+#endif
 
 #define AE_LIN_C 128
 #define AE_LIN_DK 128
@@ -29,6 +39,7 @@
 #define AE_LIN_SMEM_H (AE_LIN_SMEM_V2 + AE_LIN_V_BYTES)
 #define AE_LIN_SMEM_G (AE_LIN_SMEM_H + AE_LIN_DK * AE_LIN_DV * 2)
 #define AE_LIN_SMEM_BAR (AE_LIN_SMEM_G + 1024)
+#define AE_LIN_SMEM_X (AE_LIN_SMEM_BAR + 256)  // AE_LIN_MODS: raw copy of the chunk's x rows, [128][DV] 16-bit, row r by thread r
 
 struct AeLinBars {
   u64 full[AE_LIN_STAGES];
@@ -162,12 +173,25 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
     const u32 lane_base = ((warp & 3) * 32) << 16;
     const float* a_row = args.a + ((i64)b * args.H + h) * args.T;
     u16* o_base = (u16*)args.o + ((i64)b * args.H + h) * (i64)args.T * AE_LIN_DV;
+#if AE_LIN_MODS
+    u16* vo_base = args.v_out ? (u16*)args.v_out + ((i64)b * args.H + h) * (i64)args.T * AE_LIN_DV : nullptr;
+    const float dsk = args.dskip ? args.dskip[h] : 0.f;
+    uint4* xs_row = (uint4*)(smem + AE_LIN_SMEM_X + r * (AE_LIN_DV * 2));
+#endif
     bool ok = true;
     for (int c = 0; c < n_chunks; ++c) {
       const int stage = c % AE_LIN_STAGES;
       const int t = c * AE_LIN_C + (int)r;
       // ---- A: inclusive cumulative sum of the log-decay over the chunk ----------------------
       float g = t < args.T ? a_row[t] : 0.f;
+#if AE_LIN_MODS
+      // requested here, used in phase C: the load's latency passes under the cumulative sum
+      float vsc = 1.f;
+      if (args.vscale && t < args.T) {
+        const i64 si = ((i64)b * args.H + h) * args.T + t;
+        vsc = args.vscale_16 ? unpack_lo<AE_BF16>((u32)((const u16*)args.vscale)[si]) : ((const float*)args.vscale)[si];
+      }
+#endif
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float n = __shfl_up_sync(0xffffffffu, g, o);
@@ -187,6 +211,12 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       named_bar_sync(1, 128);
       const float g_last = gs[AE_LIN_C - 1];
       // ---- B: incoming state -> bf16 copy for q h, and decay it in place --------------------
+      u16* hrow = args.h_out ? (u16*)args.h_out + ((((i64)b * args.H + h) * n_chunks + c) * AE_LIN_DK + r) * AE_LIN_DV
+                             : nullptr;  // row r of this chunk's incoming state, for the backward
+      if (c == 0 && hrow) {
+#pragma unroll
+        for (int i = 0; i < AE_LIN_DV / 8; ++i) *(uint4*)(hrow + i * 8) = make_uint4(0, 0, 0, 0);
+      }
       if (c > 0) {
         ok = ok && mbar_wait(&bars->h_done, (c - 1) & 1, ctl, args.status, 55);
         tc_fence_after_sync();
@@ -206,6 +236,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
             pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
             const u32 col = cc * 32 + i * 8;  // element column of this 16-byte chunk
             *(uint4*)(hb + (col >> 6) * (AE_LIN_DK * 128) + swz128(r, (col & 63) >> 3)) = pk;
+            if (hrow) *(uint4*)(hrow + col) = pk;
           }
 #pragma unroll
           for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(f[i] * dec);
@@ -216,13 +247,26 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       ok = ok && mbar_wait(&bars->full[stage], (c / AE_LIN_STAGES) & 1, ctl, args.status, 56);
       {
         const float wgt = ae_exp(g_last - g);
-        const u8* vt = smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES + 2 * AE_LIN_Q_BYTES;
+        u8* vt = smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES + 2 * AE_LIN_Q_BYTES;
         u8* v2 = smem + AE_LIN_SMEM_V2;
+#if AE_LIN_MODS
+        // v = x * vscale: in place for P v (row r of the tile is this thread's alone), out to HBM for the backward;
+        // the raw row is kept for the skip term of phase F (the stage may be refilled by then)
+        uint4* vo_row = (vo_base && t < args.T) ? (uint4*)(vo_base + (i64)t * AE_LIN_DV) : nullptr;
+#endif
 #pragma unroll
         for (int ch = 0; ch < AE_LIN_DV / 8; ++ch) {
           const u32 off = (ch >> 3) * (AE_LIN_C * 128) + swz128(r, ch & 7);
           uint4 x = *(const uint4*)(vt + off);
           u32* xw = (u32*)&x;
+#if AE_LIN_MODS
+          xs_row[ch ^ (r & 7)] = x;  // 16-byte chunks rotated by the row: conflict-free for a warp's 32 rows
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            xw[i] = pack2<AE_BF16>(unpack_lo<AE_BF16>(xw[i]) * vsc, unpack_hi<AE_BF16>(xw[i]) * vsc);
+          *(uint4*)(vt + off) = x;
+          if (vo_row) vo_row[ch] = x;
+#endif
 #pragma unroll
           for (int i = 0; i < 4; ++i)
             xw[i] = pack2<AE_BF16>(unpack_lo<AE_BF16>(xw[i]) * wgt, unpack_hi<AE_BF16>(xw[i]) * wgt);
@@ -286,6 +330,20 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
         for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
           float f[32];
           tmem_ld_f32x32(tmem + TM_O + lane_base + cc * 32, f);
+#if AE_LIN_MODS
+          if (args.dskip) {  // + x * dskip[h], x = the raw row saved in phase C
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 xr = xs_row[(cc * 4 + i) ^ (r & 7)];
+              const u32 xw[4] = {xr.x, xr.y, xr.z, xr.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                f[i * 8 + 2 * e] = fmaf(unpack_lo<AE_BF16>(xw[e]), dsk, f[i * 8 + 2 * e]);
+                f[i * 8 + 2 * e + 1] = fmaf(unpack_hi<AE_BF16>(xw[e]), dsk, f[i * 8 + 2 * e + 1]);
+              }
+            }
+          }
+#endif
           if (store) {
             uint4* dst = (uint4*)(orow + cc * 32);
 #pragma unroll

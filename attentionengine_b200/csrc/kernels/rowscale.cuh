@@ -194,3 +194,54 @@ extern "C" __global__ void __launch_bounds__(256) ae_vskip_bwd(const AeRowScaleA
     }
   }
 }
+
+// Sum over the heads of a group: x [n_groups, G, T, AE_RS_D] 16-bit -> y [n_groups, T, AE_RS_D] 16-bit, fp32 accumulation
+// (n_rows = n_groups * T output rows, rows_per_head = T, n_heads = G).  The reverse pass of the scan writes dq / dk per
+// value head; q and k may have fewer heads (the reference sums the same way, linear_tl.py:1198-1201).
+extern "C" __global__ void __launch_bounds__(256) ae_head_sum(const AeRowScaleArgs a) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp0 = ((i64)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const i64 n_warps = ((i64)gridDim.x * 256) >> 5;
+  const i64 T = a.rows_per_head;
+  const int G = a.n_heads;
+  for (i64 base = warp0 * AE_RS_RPW; base < a.n_rows; base += n_warps * AE_RS_RPW) {
+    const i64 row = base + lane / AE_RS_TPR;
+    if (row < a.n_rows) {
+      const i64 grp = row / T, t = row - grp * T;
+      const u16* src = (const u16*)a.x + ((grp * G) * T + t) * AE_RS_D + (lane % AE_RS_TPR) * 8;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      int g = 0;
+      for (; g + 4 <= G; g += 4) {  // four independent 16-byte loads in flight per lane
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = *(const uint4*)(src + (i64)(g + u) * T * AE_RS_D);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const u32 w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[2 * i] += unpack_lo<AE_BF16>(w[i]);
+            acc[2 * i + 1] += unpack_hi<AE_BF16>(w[i]);
+          }
+        }
+      }
+      for (; g < G; ++g) {
+        const uint4 v = *(const uint4*)(src + (i64)g * T * AE_RS_D);
+        const u32 w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] += unpack_lo<AE_BF16>(w[i]);
+          acc[2 * i + 1] += unpack_hi<AE_BF16>(w[i]);
+        }
+      }
+      uint4 o;
+      o.x = pack2<AE_BF16>(acc[0], acc[1]);
+      o.y = pack2<AE_BF16>(acc[2], acc[3]);
+      o.z = pack2<AE_BF16>(acc[4], acc[5]);
+      o.w = pack2<AE_BF16>(acc[6], acc[7]);
+      *(uint4*)((u16*)a.y + row * AE_RS_D + (lane % AE_RS_TPR) * 8) = o;
+    }
+  }
+}

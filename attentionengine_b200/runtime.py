@@ -107,7 +107,8 @@ class MlaPagedParams(C.Structure):
 class LinearParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("a", C.c_void_p), ("o", C.c_void_p),
                 ("B", C.c_int32), ("H", C.c_int32), ("HQ", C.c_int32), ("HK", C.c_int32), ("T", C.c_int32),
-                ("status", C.c_void_p)]
+                ("status", C.c_void_p), ("vscale", C.c_void_p), ("dskip", C.c_void_p), ("v_out", C.c_void_p),
+                ("vscale_16bit", C.c_int32), ("h_states_out", C.c_void_p)]
 
 
 class LinearBwdParams(C.Structure):

@@ -305,6 +305,18 @@ typedef struct AeLinearParams {
   void* o;        /* [B, H, T, DV]  */
   int32_t B, H, HQ, HK, T;
   uint32_t* status;
+  /* Modules compiled with AE_LIN_MODS (config reserved[0] = 1) only, each optional: the scan runs on
+   * v * vscale[b, h, t], the output is scan + v * dskip[h] (v as passed, unscaled), and the scaled v is written to v_out
+   * (what the backward entry points take as v).  The Mamba2 block's `v * dt` and `+ D x` (attn_script/
+   * mamba2_ngroup1.py:31-33; the reference runs such mods as eager PyTorch, linear_tl.py:1136-1144). */
+  const void* vscale;   /* [B, H, T] fp32, or the 16-bit type when vscale_16bit != 0 */
+  const float* dskip;   /* [H] */
+  void* v_out;          /* [B, H, T, DV] 16-bit */
+  int32_t vscale_16bit;
+  /* Any module, optional: the state every chunk starts from, [B, H, ceil(T/128), DK, DV] 16-bit - the h_states operand of
+   * ae_launch_linear_bwd, which then needs no ae_launch_linear_states (the reference's forward stores the same tensor,
+   * linear_tl.py:142, 185-186). */
+  void* h_states_out;
 } AeLinearParams;
 
 int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream);
@@ -324,7 +336,10 @@ int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream);
  * gs[row] = sum_d g * x in fp32 (summed over batch and steps by the caller for the gradient of s).
  * "ae_vskip_bwd" is the backward of a block that uses both (v' = x * s[row] into the scan, y = o + x * d[head] after
  * it) in one pass over x: gx = g2 * s[row] + g * d[head], gs[row] = sum_d g2 * x (type of s), gs2[row] = sum_d g * x
- * (fp32), with g the gradient of y and g2 the gradient of v'. */
+ * (fp32), with g the gradient of y and g2 the gradient of v'.
+ * "ae_head_sum" sums x [groups, G, T, D] over G into y [groups, T, D] with fp32 accumulation (n_rows = groups * T,
+ * rows_per_head = T, n_heads = G; s unused): the sum of the per-head dq / dk of the reverse pass when q / k have fewer
+ * heads than v (linear_tl.py:1198-1201). */
 typedef struct AeRowScaleParams {
   const void* x;
   const void* s;

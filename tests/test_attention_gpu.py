@@ -478,6 +478,27 @@ def test_mamba2_ssd_backward_against_oracle(B, H, T):
             parity.check(f"ssd T={T} {name}", got, ref, dt_, rel_limit=5e-2 if name == "dA" else 2e-2)
 
 
+def test_scan_states_from_the_forward_equal_the_recompute_pass():
+    """The chunk start-states the forward writes for the backward are the ones ae_linear_states recomputes, and the
+    reverse pass gives the same gradients from either (T not a multiple of the chunk, several heads per q / k head)."""
+    B, H, T, dt_ = 2, 4, 456, torch.bfloat16
+    x, dt, A, Bm, Cm = helpers.mamba2_inputs(B, H, T, 128, 64, dt_, seed=11)
+    g = torch.Generator().manual_seed(12)
+    d_o = (0.1 * torch.randn(B, H, T, 64, generator=g)).to(dt_).cuda()
+    eng = helpers.mamba2_engine(B, H, T, 128, 64, dt_)
+    q, k, v = Cm.cuda(), Bm.cuda(), (x.float() * dt[..., None]).to(dt_).cuda()
+    a = (dt * A.view(1, H, 1)).float().cuda()
+    hs = eng._new_states(v)
+    o = eng._launch(q, k, v, a, h_out=hs)
+    with_saved = eng._launch_bwd(q, k, v, a, d_o, hs=hs)
+    recomputed = eng._launch_bwd(q, k, v, a, d_o, hs=None)
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert torch.equal(o, eng._launch(q, k, v, a))  # writing the states does not change the output
+    for name, x1, x2 in zip(("dq", "dk", "dv", "da"), with_saved, recomputed):
+        assert torch.equal(x1, x2), name
+
+
 @pytest.mark.parametrize("n_split", [None, 1, 3])
 def test_mla_decode_paged_kv_with_ragged_lengths(n_split):
     """The call of the reference's CuTe kv-shared path (flash_mla_interface.py:73-113): a pool of 64-key pages in
