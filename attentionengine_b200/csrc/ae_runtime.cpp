@@ -1006,6 +1006,11 @@ int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream) {
     return AE_ERR_INVALID;
   }
   a.h_out = p->h_states_out;
+  if (p->h_states_out) {
+    const int64_t nc = (p->T + 127) / 128;
+    if ((rc = make_3d_map(&a.tm_hout, p->h_states_out, m->cfg.dtype, m->cfg.head_dim_v, 128, (int64_t)p->B * p->H * nc, 128)))
+      return rc;
+  }
   // modules built with the block's mods inside (config reserved[0] = 1) take the three optional operands
   if (m->cfg.reserved[0] == 1) {
     if ((p->v_out && (reinterpret_cast<uintptr_t>(p->v_out) & 15)) ||
@@ -1017,6 +1022,8 @@ int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream) {
     a.vscale_16 = p->vscale_16bit;
     a.dskip = p->dskip;
     a.v_out = p->v_out;
+    if (p->v_out && (rc = make_bhtd_map(&a.tm_vout, p->v_out, m->cfg.dtype, p->B, p->H, p->T, m->cfg.head_dim_v, 128)))
+      return rc;
   } else if (p->vscale || p->dskip || p->v_out) {
     set_error("linear attention: vscale / dskip / v_out need a module built with the mods inside (reserved[0] = 1)");
     return AE_ERR_INVALID;

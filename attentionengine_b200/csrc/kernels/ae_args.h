@@ -148,6 +148,8 @@ struct AeLinearArgs {
   // Any build: when set, the state each chunk starts from is written here in 16-bit, [B, H, n_chunks, DK, DV] (what
   // ae_linear_states would recompute for the backward).
   void* h_out;
+  AeTmaDesc tm_hout;  // h_out as [B * H * n_chunks, DK, DV], dims (dv, dk, n), box {64, 128, 1}   (when h_out is set)
+  AeTmaDesc tm_vout;  // v_out like tm_v                                                       (when v_out is set)
 };
 
 // ---- chunked linear attention backward (kernels ae_linear_states, ae_linear_bwd) ---------

@@ -50,6 +50,7 @@ struct AeLinBars {
   u64 p_full;
   u64 o_done;
   u64 h_done;
+  u64 hb_free;  // the bulk store of the previous chunk's state copy has read it (h_out builds)
   AeCtaCtl ctl;
 };
 
@@ -79,6 +80,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
     mbar_init(&bars->p_full, 4);
     mbar_init(&bars->o_done, 1);
     mbar_init(&bars->h_done, 1);
+    mbar_init(&bars->hb_free, 1);
     mbar_fence_init();
   }
   if (warp == 5) {
@@ -97,21 +99,55 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       tma_prefetch_desc(&args.tm_q);
       tma_prefetch_desc(&args.tm_k);
       tma_prefetch_desc(&args.tm_v);
-      for (int c = 0; c < n_chunks; ++c) {
-        const int stage = c % AE_LIN_STAGES;
-        const u32 par = ((c / AE_LIN_STAGES) & 1) ^ 1;
-        if (!mbar_wait(&bars->empty[stage], par, ctl, args.status, 51)) break;
-        u8* st = smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES;
-        mbar_arrive_expect_tx(&bars->full[stage], AE_LIN_STAGE_BYTES);
-        for (int dh = 0; dh < AE_LIN_DK / 64; ++dh) {
-          tma_load_4d(st + dh * (AE_LIN_C * 128), &args.tm_q, &bars->full[stage], dh * 64, c * AE_LIN_C, hq, b);
-          tma_load_4d(st + AE_LIN_Q_BYTES + dh * (AE_LIN_C * 128), &args.tm_k, &bars->full[stage], dh * 64,
-                      c * AE_LIN_C, hk, b);
+      // Outputs that are whole shared-memory tiles leave through bulk stores issued here, one chunk behind the loads,
+      // instead of through per-row stores of the row threads (who are this kernel's critical path): the 16-bit copy of
+      // each chunk's incoming state (h_out) and, in the build with the mods inside, the scaled V tile (v_out).
+      const bool st_h = args.h_out != nullptr;
+      const bool st_v = AE_LIN_MODS && args.v_out != nullptr;
+      if (st_h) tma_prefetch_desc(&args.tm_hout);
+      if (st_v) tma_prefetch_desc(&args.tm_vout);
+      bool ok = true;
+      for (int c = 0; c <= n_chunks && ok; ++c) {
+        // first the stores of chunk c - 1, then the loads of chunk c: the row threads cannot reach prep_done of chunk c
+        // without those loads, so the parity wait below can never be two phases behind
+        if ((st_h || st_v) && c >= 1) {
+          const int cs = c - 1;  // its row threads have written and fenced the state copy and the scaled V tile
+          ok = mbar_wait(&bars->prep_done, cs & 1, ctl, args.status, 60);
+          if (!ok) break;
+          if (st_h && cs >= 1) {
+            for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
+              tma_store_3d(&args.tm_hout, smem + AE_LIN_SMEM_H + dh * (AE_LIN_DK * 128), dh * 64, 0,
+                           (b * args.H + h) * n_chunks + cs);
+          }
+          if (st_v) {
+            const u8* vt = smem + AE_LIN_SMEM_STAGE + (cs % AE_LIN_STAGES) * AE_LIN_STAGE_BYTES + 2 * AE_LIN_Q_BYTES;
+            for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
+              tma_store_4d(&args.tm_vout, vt + dh * (AE_LIN_C * 128), dh * 64, cs * AE_LIN_C, h, b);
+          }
+          tma_store_commit();
+          if (st_h && cs >= 1) {
+            tma_store_wait_read();  // the state copy is rewritten by the row threads of the next chunk
+            mbar_arrive(&bars->hb_free);
+          }
         }
-        for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
-          tma_load_4d(st + 2 * AE_LIN_Q_BYTES + dh * (AE_LIN_C * 128), &args.tm_v, &bars->full[stage], dh * 64,
-                      c * AE_LIN_C, h, b);
+        if (c < n_chunks) {
+          const int stage = c % AE_LIN_STAGES;
+          const u32 par = ((c / AE_LIN_STAGES) & 1) ^ 1;
+          if (!mbar_wait(&bars->empty[stage], par, ctl, args.status, 51)) break;
+          if (st_v) tma_store_wait_read();  // no bulk store still reads the V tile about to be refilled
+          u8* st = smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES;
+          mbar_arrive_expect_tx(&bars->full[stage], AE_LIN_STAGE_BYTES);
+          for (int dh = 0; dh < AE_LIN_DK / 64; ++dh) {
+            tma_load_4d(st + dh * (AE_LIN_C * 128), &args.tm_q, &bars->full[stage], dh * 64, c * AE_LIN_C, hq, b);
+            tma_load_4d(st + AE_LIN_Q_BYTES + dh * (AE_LIN_C * 128), &args.tm_k, &bars->full[stage], dh * 64,
+                        c * AE_LIN_C, hk, b);
+          }
+          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
+            tma_load_4d(st + 2 * AE_LIN_Q_BYTES + dh * (AE_LIN_C * 128), &args.tm_v, &bars->full[stage], dh * 64,
+                        c * AE_LIN_C, h, b);
+        }
       }
+      if (st_h || st_v) tma_store_wait_read();  // the tiles belong to this CTA until the bulk engine has read them
     }
   } else if (warp == 5) {
     // =============================== MMA issuer =================================
@@ -174,7 +210,6 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
     const float* a_row = args.a + ((i64)b * args.H + h) * args.T;
     u16* o_base = (u16*)args.o + ((i64)b * args.H + h) * (i64)args.T * AE_LIN_DV;
 #if AE_LIN_MODS
-    u16* vo_base = args.v_out ? (u16*)args.v_out + ((i64)b * args.H + h) * (i64)args.T * AE_LIN_DV : nullptr;
     const float dsk = args.dskip ? args.dskip[h] : 0.f;
     uint4* xs_row = (uint4*)(smem + AE_LIN_SMEM_X + r * (AE_LIN_DV * 2));
 #endif
@@ -211,13 +246,14 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       named_bar_sync(1, 128);
       const float g_last = gs[AE_LIN_C - 1];
       // ---- B: incoming state -> bf16 copy for q h, and decay it in place --------------------
-      u16* hrow = args.h_out ? (u16*)args.h_out + ((((i64)b * args.H + h) * n_chunks + c) * AE_LIN_DK + r) * AE_LIN_DV
-                             : nullptr;  // row r of this chunk's incoming state, for the backward
-      if (c == 0 && hrow) {
+      if (c == 0 && args.h_out) {  // the first chunk starts from zero; the later ones leave through the producer's bulk stores
+        u16* hrow = (u16*)args.h_out + (((i64)b * args.H + h) * n_chunks * AE_LIN_DK + r) * AE_LIN_DV;
 #pragma unroll
         for (int i = 0; i < AE_LIN_DV / 8; ++i) *(uint4*)(hrow + i * 8) = make_uint4(0, 0, 0, 0);
       }
       if (c > 0) {
+        // the bulk store of the previous chunk's copy has read it (long ago: it was issued a chunk earlier)
+        if (args.h_out && c >= 2) ok = ok && mbar_wait(&bars->hb_free, (c - 2) & 1, ctl, args.status, 61);
         ok = ok && mbar_wait(&bars->h_done, (c - 1) & 1, ctl, args.status, 55);
         tc_fence_after_sync();
         const float dec = ae_exp(g_last);
@@ -236,7 +272,6 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
             pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
             const u32 col = cc * 32 + i * 8;  // element column of this 16-byte chunk
             *(uint4*)(hb + (col >> 6) * (AE_LIN_DK * 128) + swz128(r, (col & 63) >> 3)) = pk;
-            if (hrow) *(uint4*)(hrow + col) = pk;
           }
 #pragma unroll
           for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(f[i] * dec);
@@ -250,9 +285,9 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
         u8* vt = smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES + 2 * AE_LIN_Q_BYTES;
         u8* v2 = smem + AE_LIN_SMEM_V2;
 #if AE_LIN_MODS
-        // v = x * vscale: in place for P v (row r of the tile is this thread's alone), out to HBM for the backward;
-        // the raw row is kept for the skip term of phase F (the stage may be refilled by then)
-        uint4* vo_row = (vo_base && t < args.T) ? (uint4*)(vo_base + (i64)t * AE_LIN_DV) : nullptr;
+        // v = x * vscale: in place for P v (row r of the tile is this thread's alone; the producer's bulk store sends
+        // the tile to v_out for the backward); the raw row is kept for the skip term of phase F (the stage may be
+        // refilled by then)
 #endif
 #pragma unroll
         for (int ch = 0; ch < AE_LIN_DV / 8; ++ch) {
@@ -265,7 +300,6 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
           for (int i = 0; i < 4; ++i)
             xw[i] = pack2<AE_BF16>(unpack_lo<AE_BF16>(xw[i]) * vsc, unpack_hi<AE_BF16>(xw[i]) * vsc);
           *(uint4*)(vt + off) = x;
-          if (vo_row) vo_row[ch] = x;
 #endif
 #pragma unroll
           for (int i = 0; i < 4; ++i)
