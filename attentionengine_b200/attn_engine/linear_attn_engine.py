@@ -181,15 +181,14 @@ class LinearAttentionEngine:
 
     def _fwd_kernel(self, dv: int, mods: bool = False):
         """The forward kernel for value blocks of ``dv``; ``mods``: the build with the row scale of v and the skip
-        connection inside (one more 128 x dv tile of shared memory)."""
+        connection inside."""
         key = (dv, mods)
         if key not in self._fwd_by_dv:
             stages = 2 if dv == 64 else 1
             prelude = (f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {dv}\n#define AE_LIN_STAGES {stages}\n"
                        f"#define AE_LIN_MODS {int(mods)}\n")
-            smem = stages * (2 * 128 * 128 * 2 + 128 * dv * 2) + 128 * dv * 2 + 128 * dv * 2 + 1024 + 256 + 1024
-            if mods:
-                smem += 128 * dv * 2
+            # K/V ring, rescaled V, state copy, cumulative decays, barriers, output staging tile, alignment slack
+            smem = stages * (2 * 128 * 128 * 2 + 128 * dv * 2) + 3 * 128 * dv * 2 + 1024 + 1024 + 1024
             cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_FWD, dtype=rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16,
                                   head_dim=128, head_dim_v=dv, threads=192, smem_bytes=smem, stages=stages, mask_mode=0)
             cfg.reserved[0] = int(mods)

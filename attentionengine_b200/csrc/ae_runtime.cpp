@@ -999,6 +999,7 @@ int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream) {
   if ((rc = make_bhtd_map(&a.tm_v, p->v, m->cfg.dtype, p->B, p->H, p->T, m->cfg.head_dim_v, 128))) return rc;
   a.a = p->a;
   a.o = p->o;
+  if ((rc = make_bhtd_map(&a.tm_o, p->o, m->cfg.dtype, p->B, p->H, p->T, m->cfg.head_dim_v, 128))) return rc;
   a.B = p->B; a.H = p->H; a.HQ = p->HQ; a.HK = p->HK; a.T = p->T;
   a.status = p->status;
   if (p->h_states_out && (reinterpret_cast<uintptr_t>(p->h_states_out) & 15)) {

@@ -150,6 +150,7 @@ struct AeLinearArgs {
   void* h_out;
   AeTmaDesc tm_hout;  // h_out as [B * H * n_chunks, DK, DV], dims (dv, dk, n), box {64, 128, 1}   (when h_out is set)
   AeTmaDesc tm_vout;  // v_out like tm_v                                                       (when v_out is set)
+  AeTmaDesc tm_o;     // o like tm_v: the output tile leaves through a bulk store
 };
 
 // ---- chunked linear attention backward (kernels ae_linear_states, ae_linear_bwd) ---------

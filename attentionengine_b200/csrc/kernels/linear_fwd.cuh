@@ -39,7 +39,10 @@
 #define AE_LIN_SMEM_H (AE_LIN_SMEM_V2 + AE_LIN_V_BYTES)
 #define AE_LIN_SMEM_G (AE_LIN_SMEM_H + AE_LIN_DK * AE_LIN_DV * 2)
 #define AE_LIN_SMEM_BAR (AE_LIN_SMEM_G + 1024)
-#define AE_LIN_SMEM_X (AE_LIN_SMEM_BAR + 256)  // AE_LIN_MODS: raw copy of the chunk's x rows, [128][DV] 16-bit, row r by thread r
+// Output staging tile [128 rows][DV] 16-bit in the layout of a 128-byte-swizzled TMA box (64-column blocks): row r is
+// written by thread r alone and the tile leaves through one bulk store per chunk.  In the AE_LIN_MODS build the same
+// rows first hold the raw x of the chunk (phase C) for the skip term of phase F.
+#define AE_LIN_SMEM_Y (AE_LIN_SMEM_BAR + 1024)
 
 struct AeLinBars {
   u64 full[AE_LIN_STAGES];
@@ -51,6 +54,8 @@ struct AeLinBars {
   u64 o_done;
   u64 h_done;
   u64 hb_free;  // the bulk store of the previous chunk's state copy has read it (h_out builds)
+  u64 y_full;   // the chunk's output tile is in shared memory
+  u64 y_free;   // ... and its bulk store has read it
   AeCtaCtl ctl;
 };
 
@@ -81,6 +86,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
     mbar_init(&bars->o_done, 1);
     mbar_init(&bars->h_done, 1);
     mbar_init(&bars->hb_free, 1);
+    mbar_init(&bars->y_full, 4);
+    mbar_init(&bars->y_free, 1);
     mbar_fence_init();
   }
   if (warp == 5) {
@@ -106,6 +113,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       const bool st_v = AE_LIN_MODS && args.v_out != nullptr;
       if (st_h) tma_prefetch_desc(&args.tm_hout);
       if (st_v) tma_prefetch_desc(&args.tm_vout);
+      tma_prefetch_desc(&args.tm_o);
       bool ok = true;
       for (int c = 0; c <= n_chunks && ok; ++c) {
         // first the stores of chunk c - 1, then the loads of chunk c: the row threads cannot reach prep_done of chunk c
@@ -146,8 +154,19 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
             tma_load_4d(st + 2 * AE_LIN_Q_BYTES + dh * (AE_LIN_C * 128), &args.tm_v, &bars->full[stage], dh * 64,
                         c * AE_LIN_C, h, b);
         }
+        if (c >= 1) {
+          // the output tile of chunk c - 1 (complete at the end of that chunk; the loads of chunk c are already out)
+          const int cy = c - 1;
+          ok = mbar_wait(&bars->y_full, cy & 1, ctl, args.status, 62);
+          if (!ok) break;
+          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
+            tma_store_4d(&args.tm_o, smem + AE_LIN_SMEM_Y + dh * (AE_LIN_C * 128), dh * 64, cy * AE_LIN_C, h, b);
+          tma_store_commit();
+          tma_store_wait_read();  // the rows of the next chunk write the tile again
+          mbar_arrive(&bars->y_free);
+        }
       }
-      if (st_h || st_v) tma_store_wait_read();  // the tiles belong to this CTA until the bulk engine has read them
+      tma_store_wait_read();  // the tiles belong to this CTA until the bulk engine has read them
     }
   } else if (warp == 5) {
     // =============================== MMA issuer =================================
@@ -208,10 +227,9 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
     const u32 r = threadIdx.x & 127;
     const u32 lane_base = ((warp & 3) * 32) << 16;
     const float* a_row = args.a + ((i64)b * args.H + h) * args.T;
-    u16* o_base = (u16*)args.o + ((i64)b * args.H + h) * (i64)args.T * AE_LIN_DV;
+    u8* y_tile = smem + AE_LIN_SMEM_Y;
 #if AE_LIN_MODS
     const float dsk = args.dskip ? args.dskip[h] : 0.f;
-    uint4* xs_row = (uint4*)(smem + AE_LIN_SMEM_X + r * (AE_LIN_DV * 2));
 #endif
     bool ok = true;
     for (int c = 0; c < n_chunks; ++c) {
@@ -280,6 +298,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       }
       // ---- C: v' = v * exp(g_last - g), second copy of the v tile ---------------------------
       ok = ok && mbar_wait(&bars->full[stage], (c / AE_LIN_STAGES) & 1, ctl, args.status, 56);
+      // the bulk store of the previous chunk's output tile has read it (this chunk writes its rows again)
+      if (c > 0) ok = ok && mbar_wait(&bars->y_free, (c - 1) & 1, ctl, args.status, 63);
       {
         const float wgt = ae_exp(g_last - g);
         u8* vt = smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES + 2 * AE_LIN_Q_BYTES;
@@ -295,7 +315,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
           uint4 x = *(const uint4*)(vt + off);
           u32* xw = (u32*)&x;
 #if AE_LIN_MODS
-          xs_row[ch ^ (r & 7)] = x;  // 16-byte chunks rotated by the row: conflict-free for a warp's 32 rows
+          *(uint4*)(y_tile + off) = x;  // the raw row, for the skip term (same swizzled layout as the V tile)
 #pragma unroll
           for (int i = 0; i < 4; ++i)
             xw[i] = pack2<AE_BF16>(unpack_lo<AE_BF16>(xw[i]) * vsc, unpack_hi<AE_BF16>(xw[i]) * vsc);
@@ -358,8 +378,6 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       ok = ok && mbar_wait(&bars->o_done, c & 1, ctl, args.status, 59);
       tc_fence_after_sync();
       {
-        const bool store = ok && t < args.T;
-        u16* orow = o_base + (i64)(store ? t : 0) * AE_LIN_DV;
 #pragma unroll
         for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
           float f[32];
@@ -368,7 +386,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
           if (args.dskip) {  // + x * dskip[h], x = the raw row saved in phase C
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const uint4 xr = xs_row[(cc * 4 + i) ^ (r & 7)];
+              const uint4 xr = *(const uint4*)(y_tile + tile_off(r, cc * 32 + i * 8, AE_LIN_C));
               const u32 xw[4] = {xr.x, xr.y, xr.z, xr.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
@@ -378,21 +396,20 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
             }
           }
 #endif
-          if (store) {
-            uint4* dst = (uint4*)(orow + cc * 32);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 pk;
-              pk.x = pack2<AE_BF16>(f[i * 8 + 0], f[i * 8 + 1]);
-              pk.y = pack2<AE_BF16>(f[i * 8 + 2], f[i * 8 + 3]);
-              pk.z = pack2<AE_BF16>(f[i * 8 + 4], f[i * 8 + 5]);
-              pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
-              dst[i] = pk;
-            }
+          for (int i = 0; i < 4; ++i) {  // rows past T hold zeros or leftovers: the bulk store clips them
+            uint4 pk;
+            pk.x = pack2<AE_BF16>(f[i * 8 + 0], f[i * 8 + 1]);
+            pk.y = pack2<AE_BF16>(f[i * 8 + 2], f[i * 8 + 3]);
+            pk.z = pack2<AE_BF16>(f[i * 8 + 4], f[i * 8 + 5]);
+            pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
+            *(uint4*)(y_tile + tile_off(r, cc * 32 + i * 8, AE_LIN_C)) = pk;
           }
         }
       }
+      fence_proxy_async_smem();
       tc_fence_before_sync();
+      mbar_arrive_warp(&bars->y_full);
       named_bar_sync(1, 128);  // every row has read O before the next chunk's q h overwrites it
     }
   }
