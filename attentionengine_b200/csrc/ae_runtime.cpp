@@ -1053,6 +1053,9 @@ static int fill_linear_bwd(Module* m, const AeLinearBwdParams* p, AeLinearBwdArg
     if ((rc = make_bhtd_map(&a->tm_q, p->q, m->cfg.dtype, p->B, p->HQ, p->T, 128, 128))) return rc;
     if ((rc = make_bhtd_map(&a->tm_do, p->d_o, m->cfg.dtype, p->B, p->H, p->T, DV, 128))) return rc;
     if ((rc = make_3d_map(&a->tm_h, p->h_states, m->cfg.dtype, DV, 128, (int64_t)p->B * p->H * nc, 128))) return rc;
+    if ((rc = make_bhtd_map(&a->tm_dq, p->dq, m->cfg.dtype, p->B, p->H, p->T, 128, 128))) return rc;
+    if ((rc = make_bhtd_map(&a->tm_dk, p->dk, m->cfg.dtype, p->B, p->H, p->T, 128, 128))) return rc;
+    if ((rc = make_bhtd_map(&a->tm_dv, p->dv, m->cfg.dtype, p->B, p->H, p->T, DV, 128))) return rc;
   }
   a->a = p->a;
   a->h_states = p->h_states;

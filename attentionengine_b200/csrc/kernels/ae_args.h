@@ -168,6 +168,9 @@ struct AeLinearBwdArgs {
   float* da;        // [B, H, T] fp32
   int B, H, HQ, HK, T;
   u32* status;
+  AeTmaDesc tm_dq;  // dq, dk, dv as store targets: like tm_q / tm_v with H heads (ae_linear_bwd stages each chunk's tiles in
+  AeTmaDesc tm_dk;  // shared memory and sends them out as bulk stores)
+  AeTmaDesc tm_dv;
 };
 
 // ---- row-scale mod and its backward (kernels ae_rowscale_fwd, ae_rowscale_bwd) ---------------

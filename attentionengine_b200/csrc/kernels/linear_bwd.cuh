@@ -19,6 +19,10 @@
 // dq / dk are written per head; the caller sums them over a head group when q / k have fewer heads.
 // All transposed products read the same 16-bit tiles through MN-major descriptors: nothing is transposed in
 // registers.  Roles: warps 0-3 row threads (thread r = step r = state row r), warp 4 TMA, warp 5 MMA.
+// The row threads are the critical path (one warp per sub-partition, every phase of a chunk waits for them), so the
+// chunk's dq / dk / dv rows do not leave through their per-row global stores: they are written as 16-bit tiles over the
+// P, dS and dO-copy tiles (dead once the chunk's last MMAs have completed) and the TMA warp sends them out as bulk
+// stores while the next chunk is under way.
 // Expects AE_BF16, AE_LIN_DV (64).
 
 #define AE_LB_C 128
@@ -49,6 +53,8 @@ struct AeLbBars {
   u64 inter_full;
   u64 scaled_done;
   u64 out_full;
+  u64 o_ready;  // the chunk's dq / dk / dv tiles are in shared memory
+  u64 o_free;   // ... and their bulk stores have read them
   AeCtaCtl ctl;
 };
 
@@ -75,6 +81,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
     mbar_init(&bars->inter_full, 1);
     mbar_init(&bars->scaled_done, 4);
     mbar_init(&bars->out_full, 1);
+    mbar_init(&bars->o_ready, 4);
+    mbar_init(&bars->o_free, 1);
     mbar_fence_init();
   }
   if (warp == 5) {
@@ -95,21 +103,43 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       tma_prefetch_desc(&args.tm_v);
       tma_prefetch_desc(&args.tm_do);
       tma_prefetch_desc(&args.tm_h);
-      for (int it = 0; it < n_chunks; ++it) {
-        const int c = n_chunks - 1 - it;
-        if (!mbar_wait(&bars->empty, (it & 1) ^ 1, ctl, args.status, 71)) break;
-        mbar_arrive_expect_tx(&bars->full, AE_LB_LOAD_BYTES);
-        for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
-          tma_load_4d(smem + AE_LB_SMEM_Q + dh * (AE_LB_C * 128), &args.tm_q, &bars->full, dh * 64, c * AE_LB_C, hq, b);
-          tma_load_4d(smem + AE_LB_SMEM_K + dh * (AE_LB_C * 128), &args.tm_k, &bars->full, dh * 64, c * AE_LB_C, hk, b);
+      tma_prefetch_desc(&args.tm_dq);
+      tma_prefetch_desc(&args.tm_dk);
+      tma_prefetch_desc(&args.tm_dv);
+      bool ok = true;
+      for (int it = 0; it <= n_chunks && ok; ++it) {
+        if (it < n_chunks) {
+          const int c = n_chunks - 1 - it;
+          if (!mbar_wait(&bars->empty, (it & 1) ^ 1, ctl, args.status, 71)) break;
+          mbar_arrive_expect_tx(&bars->full, AE_LB_LOAD_BYTES);
+          for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
+            tma_load_4d(smem + AE_LB_SMEM_Q + dh * (AE_LB_C * 128), &args.tm_q, &bars->full, dh * 64, c * AE_LB_C, hq, b);
+            tma_load_4d(smem + AE_LB_SMEM_K + dh * (AE_LB_C * 128), &args.tm_k, &bars->full, dh * 64, c * AE_LB_C, hk, b);
+          }
+          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh) {
+            tma_load_4d(smem + AE_LB_SMEM_V + dh * (AE_LB_C * 128), &args.tm_v, &bars->full, dh * 64, c * AE_LB_C, h, b);
+            tma_load_4d(smem + AE_LB_SMEM_DO + dh * (AE_LB_C * 128), &args.tm_do, &bars->full, dh * 64, c * AE_LB_C, h, b);
+            tma_load_3d(smem + AE_LB_SMEM_HC + dh * (AE_LB_DK * 128), &args.tm_h, &bars->full, dh * 64, 0,
+                        (b * args.H + h) * n_chunks + c);
+          }
         }
-        for (int dh = 0; dh < AE_LIN_DV / 64; ++dh) {
-          tma_load_4d(smem + AE_LB_SMEM_V + dh * (AE_LB_C * 128), &args.tm_v, &bars->full, dh * 64, c * AE_LB_C, h, b);
-          tma_load_4d(smem + AE_LB_SMEM_DO + dh * (AE_LB_C * 128), &args.tm_do, &bars->full, dh * 64, c * AE_LB_C, h, b);
-          tma_load_3d(smem + AE_LB_SMEM_HC + dh * (AE_LB_DK * 128), &args.tm_h, &bars->full, dh * 64, 0,
-                      (b * args.H + h) * n_chunks + c);
+        if (it >= 1) {
+          // the output tiles of the chunk before (ready just before its `empty` arrival; the next loads are already out)
+          const int co = n_chunks - it;
+          ok = mbar_wait(&bars->o_ready, (it - 1) & 1, ctl, args.status, 80);
+          if (!ok) break;
+          for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
+            tma_store_4d(&args.tm_dq, smem + AE_LB_SMEM_P + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
+            tma_store_4d(&args.tm_dk, smem + AE_LB_SMEM_DS + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
+          }
+          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
+            tma_store_4d(&args.tm_dv, smem + AE_LB_SMEM_DO2 + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
+          tma_store_commit();
+          tma_store_wait_read();  // the row threads of the next chunk write these tiles again
+          mbar_arrive(&bars->o_free);
         }
       }
+      tma_store_wait_read();
     }
   } else if (warp == 5) {
     // =============================== MMA issuer =================================
@@ -240,6 +270,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       }
       // ---- C: dO2 = dO * exp(g) -----------------------------------------------------------------------
       ok = ok && mbar_wait(&bars->full, par, ctl, args.status, 76);
+      // the bulk stores of the chunk before have read the tiles this chunk writes again (dO copy here, P and dS in D)
+      if (it > 0) ok = ok && mbar_wait(&bars->o_free, (it - 1) & 1, ctl, args.status, 81);
       {
         const u8* dsrc = smem + AE_LB_SMEM_DO;
         u8* d2 = smem + AE_LB_SMEM_DO2;
@@ -316,14 +348,12 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       float dg = 0.f;
       {
         const bool store = ok && row_ok;
-        const i64 trow = bh * args.T + (store ? t : 0);
-        u16* dq_row = (u16*)args.dq + trow * AE_LB_DK;
-        u16* dk_row = (u16*)args.dk + trow * AE_LB_DK;
-        u16* dv_row = (u16*)args.dv + trow * AE_LIN_DV;
+        // rows past T are clipped by the bulk stores
+        u8* dv_tile = smem + AE_LB_SMEM_DO2;
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
           const u8* src = smem + (which == 0 ? AE_LB_SMEM_Q : AE_LB_SMEM_K);
-          u16* orow = which == 0 ? dq_row : dk_row;
+          u8* otile = smem + (which == 0 ? AE_LB_SMEM_P : AE_LB_SMEM_DS);
           float dot = 0.f;
 #pragma unroll
           for (int cc = 0; cc < AE_LB_DK / 32; ++cc) {
@@ -340,7 +370,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
                 dot += unpack_lo<AE_BF16>(xw[e2]) * f[i * 8 + e2 * 2] + unpack_hi<AE_BF16>(xw[e2]) * f[i * 8 + e2 * 2 + 1];
                 pw[e2] = pack2<AE_BF16>(f[i * 8 + e2 * 2], f[i * 8 + e2 * 2 + 1]);
               }
-              if (store) *(uint4*)(orow + cc * 32 + i * 8) = pk;
+              *(uint4*)(otile + tile_off(r, cc * 32 + i * 8, AE_LB_C)) = pk;
             }
           }
           dg += which == 0 ? dot : -dot;
@@ -349,18 +379,18 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
           float f[32];
           tmem_ld_f32x32(tmem + TM_DV + lane_base + cc * 32, f);
-          if (store) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 pk;
-              pk.x = pack2<AE_BF16>(f[i * 8 + 0], f[i * 8 + 1]);
-              pk.y = pack2<AE_BF16>(f[i * 8 + 2], f[i * 8 + 3]);
-              pk.z = pack2<AE_BF16>(f[i * 8 + 4], f[i * 8 + 5]);
-              pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
-              *(uint4*)(dv_row + cc * 32 + i * 8) = pk;
-            }
+          for (int i = 0; i < 4; ++i) {
+            uint4 pk;
+            pk.x = pack2<AE_BF16>(f[i * 8 + 0], f[i * 8 + 1]);
+            pk.y = pack2<AE_BF16>(f[i * 8 + 2], f[i * 8 + 3]);
+            pk.z = pack2<AE_BF16>(f[i * 8 + 4], f[i * 8 + 5]);
+            pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
+            *(uint4*)(dv_tile + tile_off(r, cc * 32 + i * 8, AE_LB_C)) = pk;
           }
         }
+        fence_proxy_async_smem();
+        mbar_arrive_warp(&bars->o_ready);
         if (!row_ok) dg = 0.f;
         // <dH, h> of this chunk (row r of both), the carry for the chunk before it
         float hd = 0.f;
