@@ -149,7 +149,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       const u32 P = smem_u32(smem + AE_LB_SMEM_P), DS = smem_u32(smem + AE_LB_SMEM_DS);
       const u32 DHB = smem_u32(smem + AE_LB_SMEM_DHB), DO2 = smem_u32(smem + AE_LB_SMEM_DO2);
       const u64 kQ = umma_base_k(Q), kK = umma_base_k(K), kV = umma_base_k(V), kDO = umma_base_k(DO), kHC = umma_base_k(HC);
-      const u64 kDHB = umma_base_k(DHB), kDS = umma_base_k(DS);
+      const u64 kDHB = umma_base_k(DHB), kDS = umma_base_k(DS), kDO2 = umma_base_k(DO2);
       const u64 mQ = umma_base_mn(Q, 128), mK = umma_base_mn(K, 128), mDO = umma_base_mn(DO, 128), mDO2 = umma_base_mn(DO2, 128);
       const u64 mDHB = umma_base_mn(DHB, 128), mDS = umma_base_mn(DS, 128), mP = umma_base_mn(P, 128);
       const u32 id_kk_128 = umma_idesc_f16(128, 128, AE_BF16, 0, 0);
@@ -176,10 +176,11 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         ok = mbar_wait_w(&bars->pds_full, par, ctl, args.status, 74);
         if (!ok) break;
         tc_fence_after_sync();
-        // inter-chunk parts (overwrite R0, R1, DV)
+        // inter-chunk parts (overwrite R0, R1, DV).  dq's takes the copy of dO whose rows already carry exp(g_i), so
+        // R0 needs no row scaling afterwards.
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
-          umma_ss_w(tmem + TM_R0, umma_step_k(kDO, kk, 128), umma_step_k(kHC, kk, 128), id_kk_128, kk > 0);
+          umma_ss_w(tmem + TM_R0, umma_step_k(kDO2, kk, 128), umma_step_k(kHC, kk, 128), id_kk_128, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
           umma_ss_w(tmem + TM_R1, umma_step_k(kV, kk, 128), umma_step_k(kDHB, kk, 128), id_kk_128, kk > 0);
@@ -325,10 +326,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       ok = ok && mbar_wait(&bars->inter_full, par, ctl, args.status, 78);
       tc_fence_after_sync();
 #pragma unroll
-      for (int which = 0; which < 3; ++which) {
-        const u32 base = tmem + lane_base + (which == 0 ? TM_R0 : (which == 1 ? TM_R1 : TM_DV));
+      for (int which = 1; which < 3; ++which) {  // R1 (dk) and DV by w_j; R0 (dq) came out scaled
+        const u32 base = tmem + lane_base + (which == 1 ? TM_R1 : TM_DV);
         const int ncol = which == 2 ? AE_LIN_DV : 128;
-        const float sc = which == 0 ? eg : wj;
+        const float sc = wj;
 #pragma unroll
         for (int cc = 0; cc < ncol / 32; ++cc) {
           float f[32];
@@ -413,6 +414,9 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
           for (int o = 16; o > 0; o >>= 1) hd += __shfl_xor_sync(0xffffffffu, hd, o);
           if (lane == 0) gs[136 + (warp & 3)] = hd;
         }
+        // last read of this chunk's tiles and accumulators: the next chunk's loads start under the sums below
+        tc_fence_before_sync();
+        mbar_arrive_warp(&bars->empty);
         // inclusive suffix sum of dG over the chunk, plus everything from later chunks
         float sfx = dg;
 #pragma unroll
@@ -431,8 +435,6 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         if (store) args.da[bh * args.T + t] = sfx + after + carry;
         carry = next_carry;
       }
-      tc_fence_before_sync();
-      mbar_arrive_warp(&bars->empty);  // this chunk's tiles and accumulators are free
     }
   }
   tc_fence_before_sync();
