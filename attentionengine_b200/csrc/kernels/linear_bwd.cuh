@@ -8,8 +8,9 @@
 // h the chunk's incoming state (recomputed by linear_states.cuh) and dH' the gradient of its outgoing state:
 //     A  = q k^T          dPr = dO v^T                          (SS MMAs into R0, R1)
 //     row threads: P = E o A, dS = E o dPr  -> 16-bit tiles in shared memory
-//     dq_i = exp(g_i) (dO h^T)_i + (dS k)_i                      (R0: inter MMA, row scaling, intra MMA on top)
-//     dk_j = w_j (v dH'^T)_j + (dS^T q)_j                        (R1, same scheme)
+//     dq_i = exp(g_i) (dO h^T)_i + (dS k)_i                      (R0: inter MMA on the copy of dO that carries exp(g_i),
+//                                                                 intra MMA on top; no row scaling)
+//     dk_j = w_j (v dH'^T)_j + (dS^T q)_j                        (R2: inter MMA early, rows scale by w_j, intra on top)
 //     dv_j = w_j (k dH')_j + (P^T dO)_j
 //     dH   = exp(g_last) dH' + q^T (dO o exp(g))
 //     d a_t = sum over s >= t of (q_s . dq_s - k_s . dk_s): a suffix sum inside the chunk; what the later chunks add
@@ -25,6 +26,13 @@
 // stores while the next chunk is under way.
 // Expects AE_BF16, AE_LIN_DV (64).
 
+#ifdef AE_TRACE  // clock stamps of CTA (0, 0)'s row warp 0 and MMA warp into the status buffer (experiments)
+#define AE_TRL(cond, region, slot) \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (cond) && (slot) < 4096) \
+    args.status[64 + (region) * 4096 + (slot)] = (u32)clock64();
+#else
+#define AE_TRL(cond, region, slot)
+#endif
 #define AE_LB_C 128
 #define AE_LB_DK 128
 #define AE_LB_QK_BYTES (AE_LB_C * AE_LB_DK * 2)
@@ -93,7 +101,9 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
   __syncthreads();
   tc_fence_after_sync();
   const u32 tmem = ctl->tmem_base;
-  const u32 TM_R0 = 0, TM_R1 = 128, TM_DV = 256, TM_DH = 256 + AE_LIN_DV;
+  // R0: A = q k^T, then dq.  R1: dPr = dO v^T.  R2: dk.  The inter-chunk parts of dk and dv do not wait for the row
+  // threads' P / dS pass: they go to regions that pass does not read.
+  const u32 TM_R0 = 0, TM_R1 = 128, TM_DV = 256, TM_DH = 256 + AE_LIN_DV, TM_R2 = 384;
 
   if (warp == 4) {
     // =============================== TMA producer ===============================
@@ -108,6 +118,20 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       tma_prefetch_desc(&args.tm_dv);
       bool ok = true;
       for (int it = 0; it <= n_chunks && ok; ++it) {
+        if (it >= 1) {
+          // the output tiles of the chunk before: ready a little before its tiles are handed back, so the stores go out
+          // first and are read while the next loads are issued
+          const int co = n_chunks - it;
+          ok = mbar_wait(&bars->o_ready, (it - 1) & 1, ctl, args.status, 80);
+          if (!ok) break;
+          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)  // dv first: its tile is the first one the next chunk rewrites
+            tma_store_4d(&args.tm_dv, smem + AE_LB_SMEM_DO2 + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
+          for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
+            tma_store_4d(&args.tm_dq, smem + AE_LB_SMEM_P + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
+            tma_store_4d(&args.tm_dk, smem + AE_LB_SMEM_DS + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
+          }
+          tma_store_commit();
+        }
         if (it < n_chunks) {
           const int c = n_chunks - 1 - it;
           if (!mbar_wait(&bars->empty, (it & 1) ^ 1, ctl, args.status, 71)) break;
@@ -124,17 +148,6 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
           }
         }
         if (it >= 1) {
-          // the output tiles of the chunk before (ready just before its `empty` arrival; the next loads are already out)
-          const int co = n_chunks - it;
-          ok = mbar_wait(&bars->o_ready, (it - 1) & 1, ctl, args.status, 80);
-          if (!ok) break;
-          for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
-            tma_store_4d(&args.tm_dq, smem + AE_LB_SMEM_P + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
-            tma_store_4d(&args.tm_dk, smem + AE_LB_SMEM_DS + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
-          }
-          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
-            tma_store_4d(&args.tm_dv, smem + AE_LB_SMEM_DO2 + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
-          tma_store_commit();
           tma_store_wait_read();  // the row threads of the next chunk write these tiles again
           mbar_arrive(&bars->o_free);
         }
@@ -173,17 +186,12 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         umma_commit_w(&bars->s_full);
         ok = mbar_wait_w(&bars->prep_done, par, ctl, args.status, 73);
         if (!ok) break;
-        ok = mbar_wait_w(&bars->pds_full, par, ctl, args.status, 74);
-        if (!ok) break;
         tc_fence_after_sync();
-        // inter-chunk parts (overwrite R0, R1, DV).  dq's takes the copy of dO whose rows already carry exp(g_i), so
-        // R0 needs no row scaling afterwards.
+        // inter-chunk parts of dk and dv (their regions are not read by the P / dS pass under way), then the state
+        // gradient; the row threads scale the two by w_j once they are done with P / dS
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
-          umma_ss_w(tmem + TM_R0, umma_step_k(kDO2, kk, 128), umma_step_k(kHC, kk, 128), id_kk_128, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
-          umma_ss_w(tmem + TM_R1, umma_step_k(kV, kk, 128), umma_step_k(kDHB, kk, 128), id_kk_128, kk > 0);
+          umma_ss_w(tmem + TM_R2, umma_step_k(kV, kk, 128), umma_step_k(kDHB, kk, 128), id_kk_128, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < AE_LB_DK / 16; ++kk)
           umma_ss_w(tmem + TM_DV, umma_step_k(kK, kk, 128), umma_step_mn(mDHB, kk), id_kmn_dv, kk > 0);
@@ -192,16 +200,24 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
           umma_ss_w(tmem + TM_DH, umma_step_mn(mQ, kk), umma_step_mn(mDO2, kk), id_mnmn_dv, (it > 0) | (kk > 0));
-        ok = mbar_wait_w(&bars->scaled_done, par, ctl, args.status, 75);
+        ok = mbar_wait_w(&bars->pds_full, par, ctl, args.status, 74);
         if (!ok) break;
         tc_fence_after_sync();
-        // intra-chunk parts on top
+        // dq: the inter-chunk part over A (the copy of dO whose rows already carry exp(g_i): no row scaling), the
+        // intra-chunk part on top, back to back
+#pragma unroll
+        for (int kk = 0; kk < AE_LIN_DV / 16; ++kk)
+          umma_ss_w(tmem + TM_R0, umma_step_k(kDO2, kk, 128), umma_step_k(kHC, kk, 128), id_kk_128, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
           umma_ss_w(tmem + TM_R0, umma_step_k(kDS, kk, 128), umma_step_mn(mK, kk), id_kmn_128, 1);
+        ok = mbar_wait_w(&bars->scaled_done, par, ctl, args.status, 75);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // intra-chunk parts of dk and dv on top of the scaled inter-chunk parts
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
-          umma_ss_w(tmem + TM_R1, umma_step_mn(mDS, kk), umma_step_mn(mQ, kk), id_mnmn_128, 1);
+          umma_ss_w(tmem + TM_R2, umma_step_mn(mDS, kk), umma_step_mn(mQ, kk), id_mnmn_128, 1);
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
           umma_ss_w(tmem + TM_DV, umma_step_mn(mP, kk), umma_step_mn(mDO, kk), id_mnmn_dv, 1);
@@ -216,13 +232,18 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
     const float* a_row = args.a + bh * args.T;
     float carry = 0.f;  // sum of dG over all later chunks = <dH, h> at the boundary to the next chunk
     bool ok = true;
+    // this thread's log-decay of the chunk at hand, requested one chunk ahead (the load would otherwise sit at the top
+    // of every chunk's chain)
+    float a_next = ((n_chunks - 1) * AE_LB_C + (int)r) < args.T ? a_row[(n_chunks - 1) * AE_LB_C + (int)r] : 0.f;
     for (int it = 0; it < n_chunks; ++it) {
       const int c = n_chunks - 1 - it;
       const u32 par = it & 1;
       const int t = c * AE_LB_C + (int)r;
       const bool row_ok = t < args.T;
+      AE_TRL(warp == 0, 1, it * 16 + 0)
       // ---- A: cumulative log-decay of the chunk -------------------------------------------------
-      float g = row_ok ? a_row[t] : 0.f;
+      float g = a_next;
+      if (c > 0) a_next = a_row[t - AE_LB_C];  // chunks before the last one are full
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float n = __shfl_up_sync(0xffffffffu, g, o);
@@ -241,6 +262,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       named_bar_sync(1, 128);
       const float g_last = gs[AE_LB_C - 1];
       const float eg = ae_exp(g), wj = ae_exp(g_last - g);
+      AE_TRL(warp == 0, 1, it * 16 + 1)
       // ---- B: dH' -> 16-bit copy, then decay dH in place ------------------------------------------
       {
         u8* dhb = smem + AE_LB_SMEM_DHB;
@@ -269,8 +291,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
           for (int ch = 0; ch < AE_LIN_DV / 8; ++ch) *(uint4*)(dhb + tile_off(r, ch * 8, AE_LB_DK)) = make_uint4(0, 0, 0, 0);
         }
       }
+      AE_TRL(warp == 0, 1, it * 16 + 2)
       // ---- C: dO2 = dO * exp(g) -----------------------------------------------------------------------
       ok = ok && mbar_wait(&bars->full, par, ctl, args.status, 76);
+      AE_TRL(warp == 0, 1, it * 16 + 3)
       // the bulk stores of the chunk before have read the tiles this chunk writes again (dO copy here, P and dS in D)
       if (it > 0) ok = ok && mbar_wait(&bars->o_free, (it - 1) & 1, ctl, args.status, 81);
       {
@@ -291,8 +315,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->prep_done);
+      AE_TRL(warp == 0, 1, it * 16 + 4)
       // ---- D: P = E o A, dS = E o dPr -> shared memory ------------------------------------------------
       ok = ok && mbar_wait(&bars->s_full, par, ctl, args.status, 77);
+      AE_TRL(warp == 0, 1, it * 16 + 5)
       tc_fence_after_sync();
       {
         u8* pt = smem + AE_LB_SMEM_P;
@@ -322,12 +348,14 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->pds_full);
+      AE_TRL(warp == 0, 1, it * 16 + 6)
       // ---- E: row scaling of the inter-chunk parts ------------------------------------------------------
       ok = ok && mbar_wait(&bars->inter_full, par, ctl, args.status, 78);
+      AE_TRL(warp == 0, 1, it * 16 + 7)
       tc_fence_after_sync();
 #pragma unroll
-      for (int which = 1; which < 3; ++which) {  // R1 (dk) and DV by w_j; R0 (dq) came out scaled
-        const u32 base = tmem + lane_base + (which == 1 ? TM_R1 : TM_DV);
+      for (int which = 1; which < 3; ++which) {  // R2 (dk) and DV by w_j; dq needs no scaling
+        const u32 base = tmem + lane_base + (which == 1 ? TM_R2 : TM_DV);
         const int ncol = which == 2 ? AE_LIN_DV : 128;
         const float sc = wj;
 #pragma unroll
@@ -343,8 +371,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       tc_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->scaled_done);
+      AE_TRL(warp == 0, 1, it * 16 + 8)
       // ---- F: outputs -------------------------------------------------------------------------------------
       ok = ok && mbar_wait(&bars->out_full, par, ctl, args.status, 79);
+      AE_TRL(warp == 0, 1, it * 16 + 9)
       tc_fence_after_sync();
       float dg = 0.f;
       {
@@ -359,7 +389,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
 #pragma unroll
           for (int cc = 0; cc < AE_LB_DK / 32; ++cc) {
             float f[32];
-            tmem_ld_f32x32(tmem + (which == 0 ? TM_R0 : TM_R1) + lane_base + cc * 32, f);
+            tmem_ld_f32x32(tmem + (which == 0 ? TM_R0 : TM_R2) + lane_base + cc * 32, f);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const uint4 x = *(const uint4*)(src + tile_off(r, cc * 32 + i * 8, AE_LB_C));
@@ -392,6 +422,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         }
         fence_proxy_async_smem();
         mbar_arrive_warp(&bars->o_ready);
+        AE_TRL(warp == 0, 1, it * 16 + 10)
         if (!row_ok) dg = 0.f;
         // <dH, h> of this chunk (row r of both), the carry for the chunk before it
         float hd = 0.f;
@@ -417,6 +448,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         // last read of this chunk's tiles and accumulators: the next chunk's loads start under the sums below
         tc_fence_before_sync();
         mbar_arrive_warp(&bars->empty);
+        AE_TRL(warp == 0, 1, it * 16 + 11)
         // inclusive suffix sum of dG over the chunk, plus everything from later chunks
         float sfx = dg;
 #pragma unroll
@@ -435,6 +467,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         if (store) args.da[bh * args.T + t] = sfx + after + carry;
         carry = next_carry;
       }
+      AE_TRL(warp == 0, 1, it * 16 + 12)
     }
   }
   tc_fence_before_sync();
