@@ -53,7 +53,9 @@
 #define AE_LB_LOAD_BYTES (2 * AE_LB_QK_BYTES + 2 * AE_LB_V_BYTES + AE_LB_H_BYTES)
 
 struct AeLbBars {
-  u64 full;
+  u64 full;     // q, k of the chunk (requested when the chunk before hands its tiles back)
+  u64 full_vd;  // v, dO (requested earlier: at the chunk before's last MMA, nothing reads those two tiles after it)
+  u64 full_h;   // the chunk's start state (same request as q, k; first needed by the dq MMA, late in the chunk)
   u64 empty;
   u64 s_full;
   u64 prep_done;
@@ -62,7 +64,8 @@ struct AeLbBars {
   u64 scaled_done;
   u64 out_full;
   u64 o_ready;  // the chunk's dq / dk / dv tiles are in shared memory
-  u64 o_free;   // ... and their bulk stores have read them
+  u64 o_free;   // ... and the bulk store of dv has read its tile (the dO copy, rewritten early in the next chunk)
+  u64 o_free2;  // ... and those of dq, dk theirs (the P and dS tiles, rewritten by the next chunk's P / dS pass)
   AeCtaCtl ctl;
 };
 
@@ -82,6 +85,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
   if (threadIdx.x == 0) {
     ctl->abort = 0;
     mbar_init(&bars->full, 1);
+    mbar_init(&bars->full_vd, 1);
+    mbar_init(&bars->full_h, 1);
     mbar_init(&bars->empty, 4);
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->prep_done, 4);
@@ -91,6 +96,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
     mbar_init(&bars->out_full, 1);
     mbar_init(&bars->o_ready, 4);
     mbar_init(&bars->o_free, 1);
+    mbar_init(&bars->o_free2, 1);
     mbar_fence_init();
   }
   if (warp == 5) {
@@ -117,39 +123,56 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       tma_prefetch_desc(&args.tm_dk);
       tma_prefetch_desc(&args.tm_dv);
       bool ok = true;
+      // Shared memory holds one chunk, so the loads of the next one can only be requested as its tiles fall free: v and
+      // dO (the two that come from HBM and are not read by the row threads' output phase) at the chunk's last MMA, the
+      // rest when the row threads hand the tiles back.  The output tiles of the chunk before go out in between.
       for (int it = 0; it <= n_chunks && ok; ++it) {
+        const int c = n_chunks - 1 - it;
         if (it >= 1) {
-          // the output tiles of the chunk before: ready a little before its tiles are handed back, so the stores go out
-          // first and are read while the next loads are issued
+          ok = mbar_wait(&bars->out_full, (it - 1) & 1, ctl, args.status, 82);
+          if (!ok) break;
+        }
+        if (it < n_chunks) {
+          mbar_arrive_expect_tx(&bars->full_vd, 2 * AE_LB_V_BYTES);
+          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh) {
+            tma_load_4d(smem + AE_LB_SMEM_V + dh * (AE_LB_C * 128), &args.tm_v, &bars->full_vd, dh * 64, c * AE_LB_C, h, b);
+            tma_load_4d(smem + AE_LB_SMEM_DO + dh * (AE_LB_C * 128), &args.tm_do, &bars->full_vd, dh * 64, c * AE_LB_C, h, b);
+          }
+        }
+        if (it >= 1) {
+          // the output tiles of the chunk before: ready a little before its tiles are handed back
           const int co = n_chunks - it;
           ok = mbar_wait(&bars->o_ready, (it - 1) & 1, ctl, args.status, 80);
           if (!ok) break;
-          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)  // dv first: its tile is the first one the next chunk rewrites
+          // dv now (a small group of its own: its tile is rewritten early in the next chunk); dq and dk go out after
+          // the loads of q and k below, which the next chunk needs first
+          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
             tma_store_4d(&args.tm_dv, smem + AE_LB_SMEM_DO2 + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
+          tma_store_commit();
+        }
+        if (it < n_chunks) {
+          if (!mbar_wait(&bars->empty, (it & 1) ^ 1, ctl, args.status, 71)) break;
+          mbar_arrive_expect_tx(&bars->full, 2 * AE_LB_QK_BYTES);
+          for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
+            tma_load_4d(smem + AE_LB_SMEM_Q + dh * (AE_LB_C * 128), &args.tm_q, &bars->full, dh * 64, c * AE_LB_C, hq, b);
+            tma_load_4d(smem + AE_LB_SMEM_K + dh * (AE_LB_C * 128), &args.tm_k, &bars->full, dh * 64, c * AE_LB_C, hk, b);
+          }
+          mbar_arrive_expect_tx(&bars->full_h, AE_LB_H_BYTES);
+          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
+            tma_load_3d(smem + AE_LB_SMEM_HC + dh * (AE_LB_DK * 128), &args.tm_h, &bars->full_h, dh * 64, 0,
+                        (b * args.H + h) * n_chunks + c);
+        }
+        if (it >= 1) {
+          const int co = n_chunks - it;
           for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
             tma_store_4d(&args.tm_dq, smem + AE_LB_SMEM_P + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
             tma_store_4d(&args.tm_dk, smem + AE_LB_SMEM_DS + dh * (AE_LB_C * 128), dh * 64, co * AE_LB_C, h, b);
           }
           tma_store_commit();
-        }
-        if (it < n_chunks) {
-          const int c = n_chunks - 1 - it;
-          if (!mbar_wait(&bars->empty, (it & 1) ^ 1, ctl, args.status, 71)) break;
-          mbar_arrive_expect_tx(&bars->full, AE_LB_LOAD_BYTES);
-          for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
-            tma_load_4d(smem + AE_LB_SMEM_Q + dh * (AE_LB_C * 128), &args.tm_q, &bars->full, dh * 64, c * AE_LB_C, hq, b);
-            tma_load_4d(smem + AE_LB_SMEM_K + dh * (AE_LB_C * 128), &args.tm_k, &bars->full, dh * 64, c * AE_LB_C, hk, b);
-          }
-          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh) {
-            tma_load_4d(smem + AE_LB_SMEM_V + dh * (AE_LB_C * 128), &args.tm_v, &bars->full, dh * 64, c * AE_LB_C, h, b);
-            tma_load_4d(smem + AE_LB_SMEM_DO + dh * (AE_LB_C * 128), &args.tm_do, &bars->full, dh * 64, c * AE_LB_C, h, b);
-            tma_load_3d(smem + AE_LB_SMEM_HC + dh * (AE_LB_DK * 128), &args.tm_h, &bars->full, dh * 64, 0,
-                        (b * args.H + h) * n_chunks + c);
-          }
-        }
-        if (it >= 1) {
-          tma_store_wait_read();  // the row threads of the next chunk write these tiles again
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the dv group has read its tile
           mbar_arrive(&bars->o_free);
+          tma_store_wait_read();  // the row threads of the next chunk write these tiles again
+          mbar_arrive(&bars->o_free2);
         }
       }
       tma_store_wait_read();
@@ -173,7 +196,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       bool ok = true;
       for (int it = 0; it < n_chunks && ok; ++it) {
         const u32 par = it & 1;
-        ok = mbar_wait_w(&bars->full, par, ctl, args.status, 72);
+        ok = mbar_wait_w(&bars->full, par, ctl, args.status, 72) && mbar_wait_w(&bars->full_vd, par, ctl, args.status, 83);
         if (!ok) break;
         tc_fence_after_sync();
         // A = q k^T -> R0 ; dPr = dO v^T -> R1
@@ -200,7 +223,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
 #pragma unroll
         for (int kk = 0; kk < AE_LB_C / 16; ++kk)
           umma_ss_w(tmem + TM_DH, umma_step_mn(mQ, kk), umma_step_mn(mDO2, kk), id_mnmn_dv, (it > 0) | (kk > 0));
-        ok = mbar_wait_w(&bars->pds_full, par, ctl, args.status, 74);
+        ok = mbar_wait_w(&bars->pds_full, par, ctl, args.status, 74) && mbar_wait_w(&bars->full_h, par, ctl, args.status, 84);
         if (!ok) break;
         tc_fence_after_sync();
         // dq: the inter-chunk part over A (the copy of dO whose rows already carry exp(g_i): no row scaling), the
@@ -293,9 +316,9 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       }
       AE_TRL(warp == 0, 1, it * 16 + 2)
       // ---- C: dO2 = dO * exp(g) -----------------------------------------------------------------------
-      ok = ok && mbar_wait(&bars->full, par, ctl, args.status, 76);
+      ok = ok && mbar_wait(&bars->full_vd, par, ctl, args.status, 76);
       AE_TRL(warp == 0, 1, it * 16 + 3)
-      // the bulk stores of the chunk before have read the tiles this chunk writes again (dO copy here, P and dS in D)
+      // the bulk store of the chunk before's dv has read the dO-copy tile this phase writes again
       if (it > 0) ok = ok && mbar_wait(&bars->o_free, (it - 1) & 1, ctl, args.status, 81);
       {
         const u8* dsrc = smem + AE_LB_SMEM_DO;
@@ -318,6 +341,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       AE_TRL(warp == 0, 1, it * 16 + 4)
       // ---- D: P = E o A, dS = E o dPr -> shared memory ------------------------------------------------
       ok = ok && mbar_wait(&bars->s_full, par, ctl, args.status, 77);
+      if (it > 0) ok = ok && mbar_wait(&bars->o_free2, (it - 1) & 1, ctl, args.status, 87);  // P and dS tiles are free
       AE_TRL(warp == 0, 1, it * 16 + 5)
       tc_fence_after_sync();
       {
@@ -374,6 +398,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       AE_TRL(warp == 0, 1, it * 16 + 8)
       // ---- F: outputs -------------------------------------------------------------------------------------
       ok = ok && mbar_wait(&bars->out_full, par, ctl, args.status, 79);
+      // q, k and the start state are read below with ordinary loads: this thread has to have seen their barriers too
+      ok = ok && mbar_wait(&bars->full, par, ctl, args.status, 85) && mbar_wait(&bars->full_h, par, ctl, args.status, 86);
       AE_TRL(warp == 0, 1, it * 16 + 9)
       tc_fence_after_sync();
       float dg = 0.f;
