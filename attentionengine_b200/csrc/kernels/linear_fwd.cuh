@@ -28,6 +28,13 @@
 #define AE_LIN_MODS 0
 #endif
 
+#ifdef AE_TRACE  // clock stamps of CTA (0, 0)'s row warp 0 into the status buffer (experiments)
+#define AE_TRL(cond, region, slot) \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (cond) && (slot) < 4096) \
+    args.status[64 + (region) * 4096 + (slot)] = (u32)clock64();
+#else
+#define AE_TRL(cond, region, slot)
+#endif
 #define AE_LIN_C 128
 #define AE_LIN_DK 128
 
@@ -232,26 +239,38 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
     const float dsk = args.dskip ? args.dskip[h] : 0.f;
 #endif
     bool ok = true;
+    // The per-step scalars of a chunk (log-decay; the row scale of v in the AE_LIN_MODS build) are requested one chunk
+    // ahead: a global load at the top of every chunk would sit on the chain of dependent phases.
+    auto load_a = [&](int tt) { return tt < args.T ? a_row[tt] : 0.f; };
+    float a_next = load_a((int)r);
+#if AE_LIN_MODS
+    // the raw bits are kept until the value is used a chunk later: converting at once would wait for the load right here
+    const bool vs16 = args.vscale_16 != 0;
+    auto load_vs = [&](int tt) -> u32 {
+      if (!args.vscale || tt >= args.T) return vs16 ? (AE_BF16 ? 0x3f80u : 0x3c00u) : 0x3f800000u;  // 1.0
+      const i64 si = ((i64)b * args.H + h) * args.T + tt;
+      return vs16 ? (u32)((const u16*)args.vscale)[si] : ((const u32*)args.vscale)[si];
+    };
+    u32 vs_next = load_vs((int)r);
+#endif
     for (int c = 0; c < n_chunks; ++c) {
       const int stage = c % AE_LIN_STAGES;
       const int t = c * AE_LIN_C + (int)r;
+      AE_TRL(warp == 0, 1, c * 16 + 0)
       // ---- A: inclusive cumulative sum of the log-decay over the chunk ----------------------
-      float g = t < args.T ? a_row[t] : 0.f;
+      float g = a_next;
 #if AE_LIN_MODS
-      // requested here, used in phase C: the load's latency passes under the cumulative sum
-      float vsc = 1.f;
-      if (args.vscale && t < args.T) {
-        const i64 si = ((i64)b * args.H + h) * args.T + t;
-        vsc = args.vscale_16 ? unpack_lo<AE_BF16>((u32)((const u16*)args.vscale)[si]) : ((const float*)args.vscale)[si];
-      }
+      const float vsc = vs16 ? unpack_lo<AE_BF16>(vs_next) : __uint_as_float(vs_next);
 #endif
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float n = __shfl_up_sync(0xffffffffu, g, o);
         if (lane >= (u32)o) g += n;
       }
+      AE_TRL(warp == 0, 1, c * 16 + 11)
       if (lane == 31) gs[128 + (warp & 3)] = g;
       named_bar_sync(1, 128);
+      AE_TRL(warp == 0, 1, c * 16 + 12)
       {
         float pre = 0.f;
 #pragma unroll
@@ -260,9 +279,15 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
         g += pre;
       }
       named_bar_sync(1, 128);  // warp totals consumed; also: last chunk's readers of gs[] are done
+      AE_TRL(warp == 0, 1, c * 16 + 13)
       gs[r] = g;
       named_bar_sync(1, 128);
       const float g_last = gs[AE_LIN_C - 1];
+      a_next = load_a(t + AE_LIN_C);  // for the next chunk
+#if AE_LIN_MODS
+      vs_next = load_vs(t + AE_LIN_C);
+#endif
+      AE_TRL(warp == 0, 1, c * 16 + 1)
       // ---- B: incoming state -> bf16 copy for q h, and decay it in place --------------------
       if (c == 0 && args.h_out) {  // the first chunk starts from zero; the later ones leave through the producer's bulk stores
         u16* hrow = (u16*)args.h_out + (((i64)b * args.H + h) * n_chunks * AE_LIN_DK + r) * AE_LIN_DV;
@@ -296,10 +321,12 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
           tmem_st32(tmem + TM_H + lane_base + cc * 32, w);
         }
       }
+      AE_TRL(warp == 0, 1, c * 16 + 2)
       // ---- C: v' = v * exp(g_last - g), second copy of the v tile ---------------------------
       ok = ok && mbar_wait(&bars->full[stage], (c / AE_LIN_STAGES) & 1, ctl, args.status, 56);
       // the bulk store of the previous chunk's output tile has read it (this chunk writes its rows again)
       if (c > 0) ok = ok && mbar_wait(&bars->y_free, (c - 1) & 1, ctl, args.status, 63);
+      AE_TRL(warp == 0, 1, c * 16 + 3)
       {
         const float wgt = ae_exp(g_last - g);
         u8* vt = smem + AE_LIN_SMEM_STAGE + stage * AE_LIN_STAGE_BYTES + 2 * AE_LIN_Q_BYTES;
@@ -331,8 +358,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->prep_done);
+      AE_TRL(warp == 0, 1, c * 16 + 4)
       // ---- D: P = A * exp(g_i - g_j) for j <= i -------------------------------------------------
       ok = ok && mbar_wait(&bars->s_full, c & 1, ctl, args.status, 57);
+      AE_TRL(warp == 0, 1, c * 16 + 5)
       tc_fence_after_sync();
       {
         float s[AE_LIN_C];
@@ -356,8 +385,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
           tmem_st32(tmem + TM_S + lane_base + half * 32, pk);
         }
       }
+      AE_TRL(warp == 0, 1, c * 16 + 6)
       // ---- E: scale the inter-chunk part of O by exp(g_i) ---------------------------------------
       ok = ok && mbar_wait(&bars->oi_full, c & 1, ctl, args.status, 58);
+      AE_TRL(warp == 0, 1, c * 16 + 7)
       tc_fence_after_sync();
       if (c > 0) {
         const float eg = ae_exp(g);
@@ -374,8 +405,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       tc_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->p_full);
+      AE_TRL(warp == 0, 1, c * 16 + 8)
       // ---- F: O rows out ---------------------------------------------------------------------------
       ok = ok && mbar_wait(&bars->o_done, c & 1, ctl, args.status, 59);
+      AE_TRL(warp == 0, 1, c * 16 + 9)
       tc_fence_after_sync();
       {
 #pragma unroll
@@ -411,6 +444,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->y_full);
       named_bar_sync(1, 128);  // every row has read O before the next chunk's q h overwrites it
+      AE_TRL(warp == 0, 1, c * 16 + 10)
     }
   }
 
