@@ -235,6 +235,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
     const u32 lane_base = ((warp & 3) * 32) << 16;
     const float* a_row = args.a + ((i64)b * args.H + h) * args.T;
     u8* y_tile = smem + AE_LIN_SMEM_Y;
+    float* cf = (float*)(smem + AE_LIN_SMEM_BAR + 512);  // [128] column factors of the chunk's decay matrix
 #if AE_LIN_MODS
     const float dsk = args.dskip ? args.dskip[h] : 0.f;
 #endif
@@ -281,6 +282,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       named_bar_sync(1, 128);  // warp totals consumed; also: last chunk's readers of gs[] are done
       AE_TRL(warp == 0, 1, c * 16 + 13)
       gs[r] = g;
+      // column factor of the decay matrix: exp(g at the end of this step's 32-step block - g) <= 1, see phase D
+      cf[r] = ae_exp(__shfl_sync(0xffffffffu, g, 31) - g);
       named_bar_sync(1, 128);
       const float g_last = gs[AE_LIN_C - 1];
       a_next = load_a(t + AE_LIN_C);  // for the next chunk
@@ -366,21 +369,44 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       {
         float s[AE_LIN_C];
         tmem_ld_f32x128(tmem + TM_S + lane_base, s);
+        // exp(g_i - g_j) per 32-column block (the rows of a warp share the block that holds their diagonal): blocks
+        // left of it take exp(g_i - g_end) * exp(g_end - g_j) with g_end the block's last step - one exponential per
+        // row and block, the column factors computed once per chunk in phase A, both <= 1 - the diagonal block is
+        // evaluated element by element, the blocks right of it are zero.  128 exponentials per row become 35.
+        const u32 wq = warp & 3;
         u32 pk[32];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float4 gj = *(const float4*)(gs + half * 64 + 2 * i);
-            const float gv[4] = {gj.x, gj.y, gj.z, gj.w};
+          for (int q2 = 0; q2 < 2; ++q2) {
+            const int cc = half * 2 + q2;  // 32-column block
+            if ((u32)cc < wq) {
+              const float rf = ae_exp(g - gs[cc * 32 + 31]);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = half * 64 + 2 * i + e;
-              const float p = ((u32)j <= r) ? s[j] * ae_exp(g - gv[e]) : 0.f;
-              s[j] = p;
+              for (int i = 0; i < 32; i += 4) {
+                const float4 c4 = *(const float4*)(cf + cc * 32 + i);
+                s[cc * 32 + i + 0] *= rf * c4.x;
+                s[cc * 32 + i + 1] *= rf * c4.y;
+                s[cc * 32 + i + 2] *= rf * c4.z;
+                s[cc * 32 + i + 3] *= rf * c4.w;
+              }
+            } else if ((u32)cc == wq) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                const float4 gj = *(const float4*)(gs + cc * 32 + i);
+                const float gv[4] = {gj.x, gj.y, gj.z, gj.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int j = cc * 32 + i + e;
+                  s[j] = ((u32)j <= r) ? s[j] * ae_exp(g - gv[e]) : 0.f;
+                }
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) s[cc * 32 + i] = 0.f;
             }
-            pk[i] = pack2<AE_BF16>(s[half * 64 + 2 * i], s[half * 64 + 2 * i + 1]);
-            pk[i + 1] = pack2<AE_BF16>(s[half * 64 + 2 * i + 2], s[half * 64 + 2 * i + 3]);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[q2 * 16 + i] = pack2<AE_BF16>(s[cc * 32 + 2 * i], s[cc * 32 + 2 * i + 1]);
           }
           tmem_st32(tmem + TM_S + lane_base + half * 32, pk);
         }
