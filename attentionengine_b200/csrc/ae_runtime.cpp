@@ -511,8 +511,8 @@ int ae_launch_attn_bwd_prep(void* module, const AeAttnBwdParams* p, void* stream
   if (rc) return rc;
   rc = ensure_loaded(m);
   if (rc) return rc;
-  if ((reinterpret_cast<uintptr_t>(p->o) & 3) || (reinterpret_cast<uintptr_t>(p->d_o) & 3)) {
-    set_error("o / dO must be 4-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(p->o) & 15) || (reinterpret_cast<uintptr_t>(p->d_o) & 15)) {
+    set_error("o / dO must be 16-byte aligned");
     return AE_ERR_INVALID;
   }
   AeAttnBwdPrepArgs a;
@@ -522,12 +522,17 @@ int ae_launch_attn_bwd_prep(void* module, const AeAttnBwdParams* p, void* stream
   a.delta = p->delta;
   a.o_sb = p->o_stride[0]; a.o_ss = p->o_stride[1]; a.o_sh = p->o_stride[2];
   a.do_sb = p->do_stride[0]; a.do_ss = p->do_stride[1]; a.do_sh = p->do_stride[2];
-  if (a.o_sb % 2 || a.o_ss % 2 || a.o_sh % 2 || a.do_sb % 2 || a.do_ss % 2 || a.do_sh % 2) {
-    set_error("o / dO strides must be even");
+  if (a.o_sb % 8 || a.o_ss % 8 || a.o_sh % 8 || a.do_sb % 8 || a.do_ss % 8 || a.do_sh % 8) {
+    set_error("o / dO strides must be multiples of 8 elements");
     return AE_ERR_INVALID;
   }
   a.B = p->B; a.Hq = p->Hq; a.Sq = p->Sq; a.DV = m->cfg.head_dim_v;
-  return launch(m, (unsigned)((p->Sq + 7) / 8), (unsigned)p->Hq, (unsigned)p->B, &a, stream);
+  // 16 bytes per lane, four rows per lane group and iteration; the CTAs stride over the rest
+  const int64_t rows = (int64_t)p->B * p->Sq * p->Hq;
+  const int64_t rows_per_cta = 8 * (32 / (m->cfg.head_dim_v / 8)) * 4;
+  int64_t blocks = (rows + rows_per_cta - 1) / rows_per_cta;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch(m, (unsigned)blocks, 1, 1, &a, stream);
 }
 
 int ae_launch_attn_bwd_dq(void* module, const AeAttnBwdParams* p, void* stream) {
