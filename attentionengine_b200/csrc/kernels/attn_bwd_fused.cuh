@@ -64,6 +64,7 @@ struct AeFuBars {
   u64 q_full[AE_FU_QSTAGES], q_empty[AE_FU_QSTAGES];
   u64 do_full[AE_FU_DOSTAGES], do_empty[AE_FU_DOSTAGES];
   u64 cs_full[2], cs_empty[2];  // per-column row scales of a q tile (two slots)
+  u64 q_req;  // step s: dK_s has completed and the producer has requested the Q tile that takes its place (if any)
   u64 s_full, dp_full, dq_full;  // S^T / dP^T / dQ of a step are in TMEM
   u64 acc_done;
   AeCtaCtl ctl;
@@ -180,6 +181,7 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->cs_full[i], 32);
       mbar_init(&bars->cs_empty[i], AE_FU_NWG * 4);
+      if (i == 0) mbar_init(&bars->q_req, 1);
     }
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->dp_full, 1);
@@ -215,14 +217,27 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
       for (int dh = 0; dh < AE_DV / 64; ++dh)
         tma_load_bshd(smem + AE_FU_SMEM_V + dh * (AE_FU_BM * 128), &args.tm_v, &bars->kv_full, dh * 64, hk, kv0, b);
     }
-    for (; have; have = next_step(st)) {
+    // The walk plus AE_FU_QSTAGES closing iterations: iteration s waits for the Q slot of step s - AE_FU_QSTAGES to
+    // fall free (its dK has completed), requests the Q tile of step s if there is one, and tells the drain warps of
+    // step s - AE_FU_QSTAGES that the request is out (q_req), so that their reduce-adds queue up behind it.
+    int tail = 0;
+    bool pok = true;
+    for (; pok && (have || tail < AE_FU_QSTAGES); ) {
       const int sq = s % AE_FU_QSTAGES, sd = s % AE_FU_DOSTAGES;
       if (!mbar_wait_w(&bars->q_empty[sq], ((s / AE_FU_QSTAGES) & 1) ^ 1, ctl, args.status, 31)) break;
       if (lane == 0) {
-        mbar_arrive_expect_tx(&bars->q_full[sq], AE_FU_Q_BYTES);
-        for (int dh = 0; dh < AE_D / 64; ++dh)
-          tma_load_bshd(smem + AE_FU_SMEM_Q + sq * AE_FU_Q_BYTES + dh * (AE_FU_BN * 128), &args.tm_q, &bars->q_full[sq],
-                        dh * 64, st.hq, st.q0, b);
+        if (have) {
+          mbar_arrive_expect_tx(&bars->q_full[sq], AE_FU_Q_BYTES);
+          for (int dh = 0; dh < AE_D / 64; ++dh)
+            tma_load_bshd(smem + AE_FU_SMEM_Q + sq * AE_FU_Q_BYTES + dh * (AE_FU_BN * 128), &args.tm_q, &bars->q_full[sq],
+                          dh * 64, st.hq, st.q0, b);
+        }
+        if (s >= AE_FU_QSTAGES) mbar_arrive(&bars->q_req);
+      }
+      if (!have) {
+        ++tail;
+        ++s;
+        continue;
       }
       {
         if (!mbar_wait_w(&bars->cs_empty[s & 1], ((s >> 1) & 1) ^ 1, ctl, args.status, 42)) break;
@@ -251,6 +266,7 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
                         &bars->do_full[sd], dh * 64, st.hq, st.q0, b);
       }
       ++s;
+      have = next_step(st);
     }
   } else if (warp == AE_FU_NWG * 4 + 1) {
     // =============================== MMA issuer =================================
@@ -311,6 +327,7 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
         umma_ts_w(tmem + TM_DV, tmem + TM_S + (kk >> 1) * 32 + (kk & 1) * 8, umma_step_mn(ddm, kk), idesc_dv,
                   (s > 0) | (kk > 0));
       umma_commit_w(&bars->do_empty[sd]);  // dO_s was also read by dP^T_s, issued earlier
+      AE_TRF(true, 0, s * 8 + 7)
       if (s + 1 < n_steps) ok = issue_s(s + 1);
       if (!ok) break;
       AE_TRF(true, 0, s * 8 + 2)
@@ -361,14 +378,14 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
     AeFuStep st, st_next;
     bool have = next_step(st);
     if (lane == 0) tma_prefetch_desc(&args.tm_dqacc);
-    auto push_box = [&](const float (&v)[32], int c, const AeFuStep& stp) {
-      // slot c & 1: wait until the bulk group issued two boxes ago has read it, fill it, hand it to the TMA
-      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-      __syncwarp();
+    // A box goes out in two steps: into its staging slot (c & 1), then as a TMA reduce-add of its own bulk group.
+    auto stage_box = [&](const float (&v)[32], int c) {
       u8* box = box0 + (c & 1) * AE_FU_DQS_BOX;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch)
         *(float4*)(box + swz128(lane, ch)) = make_float4(v[ch * 4 + 0], v[ch * 4 + 1], v[ch * 4 + 2], v[ch * 4 + 3]);
+    };
+    auto issue_box = [&](int c, const AeFuStep& stp) {
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
@@ -376,10 +393,19 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
           asm volatile(
               "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
                   (u64)&args.tm_dqacc),
-              "r"(smem_u32(box)), "r"(c * 32), "r"(stp.q0 + (int)wq * 32), "r"(stp.hq), "r"(b)
+              "r"(smem_u32(box0 + (c & 1) * AE_FU_DQS_BOX)), "r"(c * 32), "r"(stp.q0 + (int)wq * 32), "r"(stp.hq), "r"(b)
               : "memory");
         tma_store_commit();  // an empty group when the CTA is aborting: the slot accounting stays the same
       }
+    };
+    auto slot_free = [&](int pending) {  // the bulk group issued `pending + 1` boxes ago has read its slot
+      if (lane == 0) {
+        if (pending)
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        else
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      }
+      __syncwarp();
     };
     for (int s = 0; have; ++s) {
       const bool more = next_step(st_next);
@@ -387,18 +413,29 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
       tc_fence_after_sync();
       AE_TRF(lane == 0, 5, s * 8 + wq * 2)
       float keep[NKEEP > 0 ? NKEEP : 1][32];
+      slot_free(0);  // the last two boxes of the tile before have left both slots
 #pragma unroll
       for (int c = 0; c < NBOX && c < 2; ++c) {
         float v[32];
         tmem_ld_f32x32(tm_dp + c * 32, v);
-        push_box(v, c, st);
+        stage_box(v, c);
       }
 #pragma unroll
       for (int c = 2; c < NBOX; ++c) tmem_ld_f32x32(tm_dp + c * 32, keep[c - 2]);
       tc_fence_before_sync();
       if (more) named_bar_arrive(3, AE_FU_NDRAIN + 32);  // the columns may be overwritten by the next dP^T
+      // The reduce-adds are slow (the L2 reduce units) and share the SM's bulk-copy queue with the loads: a Q tile
+      // requested behind a tile's worth of them arrives late for the next S GEMM.  The producer requests the next Q tile
+      // the moment dK_s has completed and then arrives on q_req: the adds of this tile are held back until then.
+      ok = ok && mbar_wait(&bars->q_req, s & 1, ctl, args.status, 47);
 #pragma unroll
-      for (int c = 2; c < NBOX; ++c) push_box(keep[c - 2], c, st);
+      for (int c = 0; c < NBOX && c < 2; ++c) issue_box(c, st);
+#pragma unroll
+      for (int c = 2; c < NBOX; ++c) {
+        slot_free(1);
+        stage_box(keep[c - 2], c);
+        issue_box(c, st);
+      }
       AE_TRF(lane == 0, 5, s * 8 + wq * 2 + 1)
       st = st_next;
       have = more;
