@@ -81,7 +81,8 @@ def compile_fused(k) -> FusedBwdKernels:
     src_prep = rt.kernel_source("attn_bwd_prep.cuh", prelude=low.prelude_bwd)
     prep = rt.compile_module(src_prep, "ae_attn_bwd_prep", cfg)
     prelude = low.prelude_bwd + (f"#define AE_FU_QSTAGES {qst}\n#define AE_FU_DOSTAGES {dost}\n#define AE_FU_NWG {nwg}\n"
-                                 f"#define AE_FU_SMEM {smem}\n")
+                                 f"#define AE_FU_SMEM {smem}\n"
+                                 f"#define AE_FU_L2_AHEAD {int(os.environ.get('AE_B200_BWD_L2_AHEAD', k.tuned.get('fused_l2_ahead', 0)))}\n")
     src = rt.kernel_source("attn_bwd_fused.cuh", prelude=prelude)
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_FUSED, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV,
                           threads=nwg * 128 + 64 + 128, smem_bytes=smem, stages=qst, mask_mode=k.mask_mode)

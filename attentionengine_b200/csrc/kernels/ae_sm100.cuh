@@ -179,6 +179,12 @@ AE_DEVICE void named_bar_sync(u32 id, u32 nthreads) {
 AE_DEVICE void tma_prefetch_desc(const AeTmaDesc* d) {
   asm volatile("prefetch.tensormap [%0];" ::"l"((u64)d) : "memory");
 }
+// Bring a box into L2 only (no shared-memory destination, no barrier): for tiles that will be loaded a few steps later.
+AE_DEVICE void tma_prefetch_l2_4d(const AeTmaDesc* d, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"((u64)d), "r"(c0), "r"(c1),
+               "r"(c2), "r"(c3)
+               : "memory");
+}
 AE_DEVICE void tma_load_4d(void* smem_dst, const AeTmaDesc* d, u64* bar, int c0, int c1, int c2, int c3) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"

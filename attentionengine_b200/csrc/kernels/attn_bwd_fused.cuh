@@ -29,6 +29,9 @@
 // producer warp, one MMA-issuing warp, four drain warps (one per 32 TMEM lanes).
 // Expects AE_FU_QSTAGES / AE_FU_DOSTAGES (ring depths), AE_FU_NWG (2 or 4), AE_FU_SMEM (the launch's dynamic bytes).
 
+#ifndef AE_FU_L2_AHEAD
+#define AE_FU_L2_AHEAD 0  // > 0: the producer prefetches the Q / dO tiles of that many steps ahead into L2
+#endif
 #define AE_FU_BM 128  // kv rows per CTA
 #define AE_FU_BN 128  // q rows per streamed tile
 #ifdef AE_TRACE
@@ -225,6 +228,18 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
     for (; pok && (have || tail < AE_FU_QSTAGES); ) {
       const int sq = s % AE_FU_QSTAGES, sd = s % AE_FU_DOSTAGES;
       if (!mbar_wait_w(&bars->q_empty[sq], ((s / AE_FU_QSTAGES) & 1) ^ 1, ctl, args.status, 31)) break;
+      AE_TRF(true, 6, s * 8 + 2)
+#if AE_MASK_MODE != 2 && AE_FU_L2_AHEAD > 0
+      if (lane == 0 && have) {
+        // the Q and dO tiles of the step AE_FU_L2_AHEAD ahead, into L2: their loads then pay the L2 latency, not HBM's
+        const int n_i = n_q_bn - i_start, sa = s + AE_FU_L2_AHEAD;
+        if (n_i > 0 && sa < n_i * G) {
+          const int hqa = hk * G + sa / n_i, q0a = (i_start + sa % n_i) * AE_FU_BN;
+          for (int dh = 0; dh < AE_D / 64; ++dh) tma_prefetch_l2_4d(&args.tm_q, dh * 64, q0a, hqa, b);
+          for (int dh = 0; dh < AE_DV / 64; ++dh) tma_prefetch_l2_4d(&args.tm_do, dh * 64, q0a, hqa, b);
+        }
+      }
+#endif
       if (lane == 0) {
         if (have) {
           mbar_arrive_expect_tx(&bars->q_full[sq], AE_FU_Q_BYTES);
@@ -287,7 +302,9 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
     const u64 dds_k = umma_base_k(ds_addr), dds_mn = umma_base_mn(ds_addr, AE_FU_BM);
     auto issue_s = [&](int s) -> bool {  // S^T_s = K Q_s^T
       const int stage = s % AE_FU_QSTAGES;
+      AE_TRF(true, 6, s * 8 + 0)
       if (!mbar_wait_w(&bars->q_full[stage], (s / AE_FU_QSTAGES) & 1, ctl, args.status, 32)) return false;
+      AE_TRF(true, 6, s * 8 + 1)
       const u64 dqq = dq0 + (u64)((stage * AE_FU_Q_BYTES) >> 4);
 #pragma unroll
       for (int kk = 0; kk < AE_D / 16; ++kk)
