@@ -82,6 +82,7 @@ def compile_fused(k) -> FusedBwdKernels:
     prep = rt.compile_module(src_prep, "ae_attn_bwd_prep", cfg)
     prelude = low.prelude_bwd + (f"#define AE_FU_QSTAGES {qst}\n#define AE_FU_DOSTAGES {dost}\n#define AE_FU_NWG {nwg}\n"
                                  f"#define AE_FU_SMEM {smem}\n"
+                                 f"#define AE_FU_DEFER_ADDS {int(os.environ.get('AE_B200_BWD_DEFER', '1'))}\n"
                                  f"#define AE_FU_L2_AHEAD {int(os.environ.get('AE_B200_BWD_L2_AHEAD', k.tuned.get('fused_l2_ahead', 0)))}\n")
     src = rt.kernel_source("attn_bwd_fused.cuh", prelude=prelude)
     cfg = rt.KernelConfig(kind=rt.KIND_ATTN_BWD_FUSED, dtype=k.dtype_tag, head_dim=D, head_dim_v=DV,

@@ -29,6 +29,9 @@
 // producer warp, one MMA-issuing warp, four drain warps (one per 32 TMEM lanes).
 // Expects AE_FU_QSTAGES / AE_FU_DOSTAGES (ring depths), AE_FU_NWG (2 or 4), AE_FU_SMEM (the launch's dynamic bytes).
 
+#ifndef AE_FU_DEFER_ADDS
+#define AE_FU_DEFER_ADDS 1  // 0: the drain warps issue their reduce-adds as soon as the boxes are staged
+#endif
 #ifndef AE_FU_L2_AHEAD
 #define AE_FU_L2_AHEAD 0  // > 0: the producer prefetches the Q / dO tiles of that many steps ahead into L2
 #endif
@@ -444,7 +447,9 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
       // The reduce-adds are slow (the L2 reduce units) and share the SM's bulk-copy queue with the loads: a Q tile
       // requested behind a tile's worth of them arrives late for the next S GEMM.  The producer requests the next Q tile
       // the moment dK_s has completed and then arrives on q_req: the adds of this tile are held back until then.
+#if AE_FU_DEFER_ADDS
       ok = ok && mbar_wait(&bars->q_req, s & 1, ctl, args.status, 47);
+#endif
 #pragma unroll
       for (int c = 0; c < NBOX && c < 2; ++c) issue_box(c, st);
 #pragma unroll
