@@ -227,8 +227,7 @@ ae_attn_bwd_fused(const __grid_constant__ AeAttnBwdArgs args) {
     // fall free (its dK has completed), requests the Q tile of step s if there is one, and tells the drain warps of
     // step s - AE_FU_QSTAGES that the request is out (q_req), so that their reduce-adds queue up behind it.
     int tail = 0;
-    bool pok = true;
-    for (; pok && (have || tail < AE_FU_QSTAGES); ) {
+    while (have || tail < AE_FU_QSTAGES) {
       const int sq = s % AE_FU_QSTAGES, sd = s % AE_FU_DOSTAGES;
       if (!mbar_wait_w(&bars->q_empty[sq], ((s / AE_FU_QSTAGES) & 1) ^ 1, ctl, args.status, 31)) break;
       AE_TRF(true, 6, s * 8 + 2)
