@@ -478,6 +478,72 @@ def test_mamba2_ssd_backward_against_oracle(B, H, T):
             parity.check(f"ssd T={T} {name}", got, ref, dt_, rel_limit=5e-2 if name == "dA" else 2e-2)
 
 
+@pytest.mark.parametrize("dt_", [torch.bfloat16, torch.float16])
+def test_streaming_kernels_of_the_scan_against_torch(dt_):
+    """The row-scale / skip / head-sum kernels of rowscale.cuh one by one (bit-exact where the arithmetic is a single
+    rounding of an fp32 result, otherwise within one 16-bit rounding of the fp32 reference)."""
+    B, H, T, D = 2, 6, 300, 64
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(B, H, T, D, generator=g).to(dt_).cuda()
+    go = torch.randn(B, H, T, D, generator=g).to(dt_).cuda()
+    gv = torch.randn(B, H, T, D, generator=g).to(dt_).cuda()
+    s = torch.rand(B, H, T, generator=g).to(dt_).cuda()
+    d = torch.randn(H, generator=g).cuda()
+    eng = helpers.mamba2_engine(B, H, T, 128, D, dt_, d_skip=True)
+    # y = x * s
+    y = torch.empty_like(x)
+    eng._rowscale("fwd", x, s, y=y)
+    assert torch.equal(y, (x.float() * s.float()[..., None]).to(dt_))
+    # both backward passes in one: gx = gv * s + go * d[h], gs = sum gv * x, rows = sum go * x
+    gx, gs = torch.empty_like(x), torch.empty_like(s)
+    rows = torch.empty(B, H, T, dtype=torch.float32, device="cuda")
+    eng._rowscale("vskip_bwd", x, s, g=go, g2=gv, d=d, gx=gx, gs=gs, gs2=rows, rows_per_head=T, n_heads=H)
+    ref_gx = gv.float() * s.float()[..., None] + go.float() * d.view(1, H, 1, 1)
+    torch.testing.assert_close(gx.float(), ref_gx, rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(gs.float(), (gv.float() * x.float()).sum(-1), rtol=1e-2, atol=6e-2)
+    torch.testing.assert_close(rows, (go.float() * x.float()).sum(-1), rtol=1e-5, atol=1e-4)
+    # the separate kernels give the same numbers
+    gx1, gs1 = torch.empty_like(x), torch.empty_like(s)
+    eng._rowscale("bwd", x, s, g=gv, gx=gx1, gs=gs1)
+    gx2, rows2 = torch.empty_like(x), torch.empty_like(rows)
+    eng._rowscale("skip_bwd", x, d, g=go, gx=gx2, gs=rows2, rows_per_head=T, n_heads=H)
+    assert torch.equal(gs1, gs) and torch.equal(rows2, rows)
+    torch.testing.assert_close(gx.float(), gx1.float() + gx2.float(), rtol=1e-2, atol=2e-2)
+    # head sums: [B, H, T, D] -> [B, n_out, T, D]
+    for n_out in (1, 2, 3):
+        got = eng._head_sum(x, n_out)
+        ref = x.view(B, n_out, H // n_out, T, D).float().sum(2).to(dt_)
+        assert torch.equal(got, ref), n_out
+
+
+def test_scan_forward_with_the_block_mods_inside_against_the_separate_kernels():
+    """y = scan(q, k, x * s, a) + x * d[h] from the kernel built with the mods inside, its v_out and its chunk states
+    against the same engine's plain scan on the row-scaled input and the separate skip kernel."""
+    B, H, T, dt_ = 2, 4, 456, torch.bfloat16
+    x, dt, A, Bm, Cm = helpers.mamba2_inputs(B, H, T, 128, 64, dt_, seed=13)
+    eng = helpers.mamba2_engine(B, H, T, 128, 64, dt_, d_skip=True)
+    q, k, xc = Cm.cuda(), Bm.cuda(), x.cuda()
+    s = dt.to(dt_).cuda()
+    a = (dt * A.view(1, H, 1)).float().cuda()
+    d = torch.randn(H, generator=torch.Generator().manual_seed(14)).cuda()
+    v = torch.empty_like(xc)
+    eng._rowscale("fwd", xc, s, y=v)
+    hs_ref = eng._new_states(v)
+    o = eng._launch(q, k, v, a, h_out=hs_ref)
+    y_ref = torch.empty_like(o)
+    eng._rowscale("skip_fwd", xc, d, g=o, y=y_ref, rows_per_head=T, n_heads=H)
+    v_out, hs = torch.empty_like(xc), eng._new_states(xc)
+    y = eng._launch(q, k, xc, a, vscale=s, dskip=d, v_out=v_out, h_out=hs)
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert torch.equal(v_out, v) and torch.equal(hs, hs_ref)
+    # the fused kernel adds the skip term to the fp32 accumulator, the separate kernel to the stored 16-bit output
+    torch.testing.assert_close(y.float(), y_ref.float(), rtol=2e-2, atol=2e-2 * y_ref.float().abs().max().item())
+    # fp32 row scales take the other load path
+    y32 = eng._launch(q, k, xc, a, vscale=s.float(), dskip=d)
+    assert torch.equal(y32, y)
+
+
 def test_scan_states_from_the_forward_equal_the_recompute_pass():
     """The chunk start-states the forward writes for the backward are the ones ae_linear_states recomputes, and the
     reverse pass gives the same gradients from either (T not a multiple of the chunk, several heads per q / k head)."""
