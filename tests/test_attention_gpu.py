@@ -449,7 +449,7 @@ def test_mamba2_ssd_forward_against_oracle(B, H, T, DV):
     _check("ssd.o", o.cpu(), ref.float(), dt_, unnormalised=True)
 
 
-@pytest.mark.parametrize("B,H,T", [(1, 2, 256), (2, 4, 512), (1, 3, 200)])
+@pytest.mark.parametrize("B,H,T", [(1, 2, 256), (2, 4, 512), (1, 3, 200), (1, 2, 64), (2, 1, 128), (1, 2, 129)])
 def test_mamba2_ssd_backward_against_oracle(B, H, T):
     """Gradients of the Mamba2 mapping (q = C, k = B, v = x * dt, a = dt * A, one q/k head shared by all heads)
     against fp64 autograd through the step-by-step recurrence.  The tensor gradients follow the bf16 rule of
