@@ -33,6 +33,14 @@
 #else
 #define AE_TRL(cond, region, slot)
 #endif
+// AE_LB_NWG = 2: a second row warpgroup takes half of the columns of the two heaviest row phases (the P / dS pass and
+// the output phase); the cumulative sum, the copies and the row scalings stay with the first group.  The groups meet at
+// named barrier 2 (the chunk's cumulative decays are ready) and 3 (the second group's share of q.dq - k.dk is in
+// shared memory).
+#ifndef AE_LB_NWG
+#define AE_LB_NWG 1
+#endif
+#define AE_LB_ROWW (4 * AE_LB_NWG)  // row warps; then the TMA warp and the MMA warp
 #define AE_LB_C 128
 #define AE_LB_DK 128
 #define AE_LB_QK_BYTES (AE_LB_C * AE_LB_DK * 2)
@@ -50,6 +58,7 @@
 #define AE_LB_SMEM_DO2 (AE_LB_SMEM_DHB + AE_LB_H_BYTES)
 #define AE_LB_SMEM_G (AE_LB_SMEM_DO2 + AE_LB_V_BYTES)
 #define AE_LB_SMEM_BAR (AE_LB_SMEM_G + 1024)
+#define AE_LB_SMEM_XG (AE_LB_SMEM_BAR + 256)  // AE_LB_NWG = 2: [128] fp32, the second group's partial dG per row
 #define AE_LB_LOAD_BYTES (2 * AE_LB_QK_BYTES + 2 * AE_LB_V_BYTES + AE_LB_H_BYTES)
 
 struct AeLbBars {
@@ -69,7 +78,7 @@ struct AeLbBars {
   AeCtaCtl ctl;
 };
 
-extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_constant__ AeLinearBwdArgs args) {
+extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_bwd(const __grid_constant__ AeLinearBwdArgs args) {
   extern __shared__ u8 smem_raw[];
   u8* smem = smem_align1024(smem_raw);
   AeLbBars* bars = (AeLbBars*)(smem + AE_LB_SMEM_BAR);
@@ -87,19 +96,19 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
     mbar_init(&bars->full, 1);
     mbar_init(&bars->full_vd, 1);
     mbar_init(&bars->full_h, 1);
-    mbar_init(&bars->empty, 4);
+    mbar_init(&bars->empty, AE_LB_ROWW);
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->prep_done, 4);
-    mbar_init(&bars->pds_full, 4);
+    mbar_init(&bars->pds_full, AE_LB_ROWW);
     mbar_init(&bars->inter_full, 1);
     mbar_init(&bars->scaled_done, 4);
     mbar_init(&bars->out_full, 1);
-    mbar_init(&bars->o_ready, 4);
+    mbar_init(&bars->o_ready, AE_LB_ROWW);
     mbar_init(&bars->o_free, 1);
     mbar_init(&bars->o_free2, 1);
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == AE_LB_ROWW + 1) {
     tmem_alloc(&ctl->tmem_base, 512);
     tmem_relinquish();
   }
@@ -111,7 +120,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
   // threads' P / dS pass: they go to regions that pass does not read.
   const u32 TM_R0 = 0, TM_R1 = 128, TM_DV = 256, TM_DH = 256 + AE_LIN_DV, TM_R2 = 384;
 
-  if (warp == 4) {
+  if (warp == AE_LB_ROWW) {
     // =============================== TMA producer ===============================
     if (lane == 0) {
       tma_prefetch_desc(&args.tm_q);
@@ -177,7 +186,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       }
       tma_store_wait_read();
     }
-  } else if (warp == 5) {
+  } else if (warp == AE_LB_ROWW + 1) {
     // =============================== MMA issuer =================================
     {  // all 32 lanes run the control flow; MMAs and commits are issued by an elected lane
       const u32 Q = smem_u32(smem + AE_LB_SMEM_Q), K = smem_u32(smem + AE_LB_SMEM_K), V = smem_u32(smem + AE_LB_SMEM_V);
@@ -251,6 +260,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
     // =============================== row threads ================================
     const u32 r = threadIdx.x & 127;
     const u32 lane_base = ((warp & 3) * 32) << 16;
+    const u32 wg = warp >> 2;  // 0: the group that also runs phases A, B, C, E and the suffix sums
+    float* xg = (float*)(smem + AE_LB_SMEM_XG);
     const i64 bh = (i64)b * args.H + h;
     const float* a_row = args.a + bh * args.T;
     float carry = 0.f;  // sum of dG over all later chunks = <dH, h> at the boundary to the next chunk
@@ -264,8 +275,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       const int t = c * AE_LB_C + (int)r;
       const bool row_ok = t < args.T;
       AE_TRL(warp == 0, 1, it * 16 + 0)
+      float g = 0.f, eg = 0.f, wj = 0.f;
+      if (wg == 0) {
       // ---- A: cumulative log-decay of the chunk -------------------------------------------------
-      float g = a_next;
+      g = a_next;
       if (c > 0) a_next = a_row[t - AE_LB_C];  // chunks before the last one are full
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -283,8 +296,12 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       }
       gs[r] = g;
       named_bar_sync(1, 128);
+#if AE_LB_NWG > 1
+      named_bar_sync(2, 128 * AE_LB_NWG);  // the second group may read the chunk's cumulative decays
+#endif
       const float g_last = gs[AE_LB_C - 1];
-      const float eg = ae_exp(g), wj = ae_exp(g_last - g);
+      eg = ae_exp(g);
+      wj = ae_exp(g_last - g);
       AE_TRL(warp == 0, 1, it * 16 + 1)
       // ---- B: dH' -> 16-bit copy, then decay dH in place ------------------------------------------
       {
@@ -338,6 +355,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->prep_done);
+      } else {
+        named_bar_sync(2, 128 * AE_LB_NWG);
+        g = gs[r];
+      }
       AE_TRL(warp == 0, 1, it * 16 + 4)
       // ---- D: P = E o A, dS = E o dPr -> shared memory ------------------------------------------------
       ok = ok && mbar_wait(&bars->s_full, par, ctl, args.status, 77);
@@ -348,7 +369,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         u8* pt = smem + AE_LB_SMEM_P;
         u8* dst = smem + AE_LB_SMEM_DS;
 #pragma unroll
-        for (int cc = 0; cc < AE_LB_C / 32; ++cc) {
+        for (int c2 = 0; c2 < AE_LB_C / 32 / AE_LB_NWG; ++c2) {
+          const int cc = (int)wg * (AE_LB_C / 32 / AE_LB_NWG) + c2;  // this group's 32-column blocks
           float av[32], dv[32];
           tmem_ld_2xf32x32(tmem + TM_R0 + lane_base + cc * 32, tmem + TM_R1 + lane_base + cc * 32, av, dv);
 #pragma unroll
@@ -374,6 +396,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       mbar_arrive_warp(&bars->pds_full);
       AE_TRL(warp == 0, 1, it * 16 + 6)
       // ---- E: row scaling of the inter-chunk parts ------------------------------------------------------
+      if (wg == 0) {
       ok = ok && mbar_wait(&bars->inter_full, par, ctl, args.status, 78);
       AE_TRL(warp == 0, 1, it * 16 + 7)
       tc_fence_after_sync();
@@ -395,6 +418,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
       tc_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->scaled_done);
+      }
       AE_TRL(warp == 0, 1, it * 16 + 8)
       // ---- F: outputs -------------------------------------------------------------------------------------
       ok = ok && mbar_wait(&bars->out_full, par, ctl, args.status, 79);
@@ -413,7 +437,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
           u8* otile = smem + (which == 0 ? AE_LB_SMEM_P : AE_LB_SMEM_DS);
           float dot = 0.f;
 #pragma unroll
-          for (int cc = 0; cc < AE_LB_DK / 32; ++cc) {
+          for (int c2 = 0; c2 < AE_LB_DK / 32 / AE_LB_NWG; ++c2) {
+            const int cc = (int)wg * (AE_LB_DK / 32 / AE_LB_NWG) + c2;
             float f[32];
             tmem_ld_f32x32(tmem + (which == 0 ? TM_R0 : TM_R2) + lane_base + cc * 32, f);
 #pragma unroll
@@ -433,7 +458,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
           dg += which == 0 ? dot : -dot;
         }
 #pragma unroll
-        for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+        for (int c2 = 0; c2 < AE_LIN_DV / 32 / AE_LB_NWG; ++c2) {
+          const int cc = (int)wg * (AE_LIN_DV / 32 / AE_LB_NWG) + c2;
           float f[32];
           tmem_ld_f32x32(tmem + TM_DV + lane_base + cc * 32, f);
 #pragma unroll
@@ -455,7 +481,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         {
           const u8* hc = smem + AE_LB_SMEM_HC;
 #pragma unroll
-          for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+          for (int c2 = 0; c2 < AE_LIN_DV / 32 / AE_LB_NWG; ++c2) {
+            const int cc = (int)wg * (AE_LIN_DV / 32 / AE_LB_NWG) + c2;
             float f[32];
             tmem_ld_f32x32(tmem + TM_DH + lane_base + cc * 32, f);
 #pragma unroll
@@ -469,12 +496,19 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
           }
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) hd += __shfl_xor_sync(0xffffffffu, hd, o);
-          if (lane == 0) gs[136 + (warp & 3)] = hd;
+          if (lane == 0) gs[136 + warp] = hd;  // one slot per row warp of either group
         }
         // last read of this chunk's tiles and accumulators: the next chunk's loads start under the sums below
         tc_fence_before_sync();
         mbar_arrive_warp(&bars->empty);
         AE_TRL(warp == 0, 1, it * 16 + 11)
+#if AE_LB_NWG > 1
+        // the second group's share of q.dq - k.dk (and its <dH, h> slot, written above) reaches the first group
+        if (wg != 0) xg[r] = dg;
+        named_bar_sync(3, 128 * AE_LB_NWG);
+        if (wg != 0) continue;
+        dg += xg[r];
+#endif
         // inclusive suffix sum of dG over the chunk, plus everything from later chunks
         float sfx = dg;
 #pragma unroll
@@ -486,10 +520,10 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
         named_bar_sync(1, 128);
         float after = 0.f, next_carry = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < 4; ++w)
           if ((u32)w > (warp & 3)) after += gs[132 + w];
-          next_carry += gs[136 + w];
-        }
+#pragma unroll
+        for (int w = 0; w < AE_LB_ROWW; ++w) next_carry += gs[136 + w];
         if (store) args.da[bh * args.T + t] = sfx + after + carry;
         carry = next_carry;
       }
@@ -498,7 +532,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_bwd(const __grid_
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == AE_LB_ROWW + 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);
   }
