@@ -33,9 +33,9 @@
 #else
 #define AE_TRL(cond, region, slot)
 #endif
-// AE_LB_NWG = 2: a second row warpgroup takes half of the columns of the two heaviest row phases (the P / dS pass and
-// the output phase); the cumulative sum, the copies and the row scalings stay with the first group.  The groups meet at
-// named barrier 2 (the chunk's cumulative decays are ready) and 3 (the second group's share of q.dq - k.dk is in
+// AE_LB_NWG = 2: a second row warpgroup takes half of the columns of every row phase (same rows, other 32-column
+// blocks); the cumulative sum and the suffix sums of the decay gradient stay with the first group.  The groups meet
+// at named barrier 2 (the chunk's cumulative decays are ready) and 3 (the second group's share of q.dq - k.dk is in
 // shared memory).
 #ifndef AE_LB_NWG
 #define AE_LB_NWG 1
@@ -98,10 +98,10 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
     mbar_init(&bars->full_h, 1);
     mbar_init(&bars->empty, AE_LB_ROWW);
     mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->prep_done, 4);
+    mbar_init(&bars->prep_done, AE_LB_ROWW);
     mbar_init(&bars->pds_full, AE_LB_ROWW);
     mbar_init(&bars->inter_full, 1);
-    mbar_init(&bars->scaled_done, 4);
+    mbar_init(&bars->scaled_done, AE_LB_ROWW);
     mbar_init(&bars->out_full, 1);
     mbar_init(&bars->o_ready, AE_LB_ROWW);
     mbar_init(&bars->o_free, 1);
@@ -299,6 +299,10 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
 #if AE_LB_NWG > 1
       named_bar_sync(2, 128 * AE_LB_NWG);  // the second group may read the chunk's cumulative decays
 #endif
+      } else {
+        named_bar_sync(2, 128 * AE_LB_NWG);
+        g = gs[r];
+      }
       const float g_last = gs[AE_LB_C - 1];
       eg = ae_exp(g);
       wj = ae_exp(g_last - g);
@@ -309,7 +313,8 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
         if (it > 0) {
           const float dec = ae_exp(g_last);
 #pragma unroll
-          for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+          for (int c2 = 0; c2 < AE_LIN_DV / 32 / AE_LB_NWG; ++c2) {
+            const int cc = (int)wg * (AE_LIN_DV / 32 / AE_LB_NWG) + c2;
             float f[32];
             u32 w[32];
             tmem_ld_f32x32(tmem + TM_DH + lane_base + cc * 32, f);
@@ -328,7 +333,10 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
           }
         } else {
 #pragma unroll
-          for (int ch = 0; ch < AE_LIN_DV / 8; ++ch) *(uint4*)(dhb + tile_off(r, ch * 8, AE_LB_DK)) = make_uint4(0, 0, 0, 0);
+          for (int c2 = 0; c2 < AE_LIN_DV / 8 / AE_LB_NWG; ++c2) {
+            const int ch = (int)wg * (AE_LIN_DV / 8 / AE_LB_NWG) + c2;
+            *(uint4*)(dhb + tile_off(r, ch * 8, AE_LB_DK)) = make_uint4(0, 0, 0, 0);
+          }
         }
       }
       AE_TRL(warp == 0, 1, it * 16 + 2)
@@ -341,7 +349,8 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
         const u8* dsrc = smem + AE_LB_SMEM_DO;
         u8* d2 = smem + AE_LB_SMEM_DO2;
 #pragma unroll
-        for (int ch = 0; ch < AE_LIN_DV / 8; ++ch) {
+        for (int c2 = 0; c2 < AE_LIN_DV / 8 / AE_LB_NWG; ++c2) {
+          const int ch = (int)wg * (AE_LIN_DV / 8 / AE_LB_NWG) + c2;
           const u32 off = tile_off(r, ch * 8, AE_LB_C);
           uint4 x = *(const uint4*)(dsrc + off);
           u32* xw = (u32*)&x;
@@ -355,10 +364,6 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->prep_done);
-      } else {
-        named_bar_sync(2, 128 * AE_LB_NWG);
-        g = gs[r];
-      }
       AE_TRL(warp == 0, 1, it * 16 + 4)
       // ---- D: P = E o A, dS = E o dPr -> shared memory ------------------------------------------------
       ok = ok && mbar_wait(&bars->s_full, par, ctl, args.status, 77);
@@ -396,7 +401,7 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
       mbar_arrive_warp(&bars->pds_full);
       AE_TRL(warp == 0, 1, it * 16 + 6)
       // ---- E: row scaling of the inter-chunk parts ------------------------------------------------------
-      if (wg == 0) {
+      {
       ok = ok && mbar_wait(&bars->inter_full, par, ctl, args.status, 78);
       AE_TRL(warp == 0, 1, it * 16 + 7)
       tc_fence_after_sync();
@@ -406,7 +411,8 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
         const int ncol = which == 2 ? AE_LIN_DV : 128;
         const float sc = wj;
 #pragma unroll
-        for (int cc = 0; cc < ncol / 32; ++cc) {
+        for (int c2 = 0; c2 < ncol / 32 / AE_LB_NWG; ++c2) {
+          const int cc = (int)wg * (ncol / 32 / AE_LB_NWG) + c2;
           float f[32];
           u32 w[32];
           tmem_ld_f32x32(base + cc * 32, f);
