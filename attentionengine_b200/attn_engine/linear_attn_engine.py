@@ -27,6 +27,8 @@ from ..core.transform.core import CustomIO, SymbolScalar
 from ..core.transform.graph import Var
 from ..lower.torch_eval import evaluate
 
+LIN_FWD_NWG = 2  # row warpgroups of the scan's forward kernel (measured: cfg4 3.72 against 4.14 ms)
+LIN_BWD_MODS = 1  # the row scale of v and the skip term inside the reverse pass (0: a streaming kernel after it)
 LIN_BWD_NWG = 2  # row warpgroups of the reverse pass of the scan (measured: 4.05 against 4.33 ms at cfg4)
 
 _DIM_POS = {"batch": 0, "heads": 1, "seq_len": 2}
@@ -137,6 +139,10 @@ class _ScaleScanSkip(torch.autograd.Function):
     def backward(ctx, g):
         q, k, v, a, x, s, df, hs = ctx.saved_tensors
         g = g.contiguous()
+        if int(os.environ.get("AE_B200_LIN_BWD_MODS", LIN_BWD_MODS)):
+            # the reverse pass built with the two mods inside: no pass over x of its own
+            dq, dk, gx, da, gs, rows = ctx.eng._launch_bwd(q, k, v, a, g, hs=hs, mods=(x, s, df))
+            return None, dq, dk, gx, da, gs, rows.sum(dim=0).reshape(ctx.d_shape).to(ctx.d_dtype)
         dq, dk, dv, da = ctx.eng._launch_bwd(q, k, v, a, g, hs=hs)
         gx, gs = torch.empty_like(x), torch.empty_like(s)
         rows = torch.empty(x.shape[:3], dtype=torch.float32, device=x.device)
@@ -175,6 +181,7 @@ class LinearAttentionEngine:
         self._bf16 = self.dtype == torch.bfloat16
         self._status = None
         self._bwd = None
+        self._bwd_mods = None
         self._fwd_by_dv = {}
         self._rowscale_mods = {}
         # The kernels work on blocks of 128 key dims x 64 or 128 value dims.  Larger heads (simple_gla / retention_linear
@@ -188,18 +195,27 @@ class LinearAttentionEngine:
         key = (dv, mods)
         if key not in self._fwd_by_dv:
             stages = 2 if dv == 64 else 1
+            nwg = int(os.environ.get("AE_B200_LIN_FWD_NWG", LIN_FWD_NWG))
             prelude = (f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {dv}\n#define AE_LIN_STAGES {stages}\n"
-                       f"#define AE_LIN_MODS {int(mods)}\n")
+                       f"#define AE_LIN_MODS {int(mods)}\n#define AE_LIN_NWG {nwg}\n")
             # K/V ring, rescaled V, state copy, cumulative decays, barriers, output staging tile, alignment slack
             smem = stages * (2 * 128 * 128 * 2 + 128 * dv * 2) + 3 * 128 * dv * 2 + 1024 + 1024 + 1024
             cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_FWD, dtype=rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16,
-                                  head_dim=128, head_dim_v=dv, threads=192, smem_bytes=smem, stages=stages, mask_mode=0)
+                                  head_dim=128, head_dim_v=dv, threads=nwg * 128 + 64, smem_bytes=smem, stages=stages,
+                                  mask_mode=0)
             cfg.reserved[0] = int(mods)
             src = rt.kernel_source("linear_fwd.cuh", prelude=prelude)
             self._fwd_by_dv[key] = (rt.compile_module(src, "ae_linear_fwd", cfg), src)
         return self._fwd_by_dv[key]
 
-    def _bwd_kernels(self):
+    def _bwd_kernels(self, mods: bool = False):
+        """(state recompute, reverse pass).  ``mods``: the reverse pass built with the block's row scale of v and skip
+        term inside (it then writes the gradient of x where dv went, the row sums for the scale and the per-head sum
+        for the skip weight)."""
+        if mods:
+            if self._bwd_mods is None:
+                self._bwd_mods = (self._bwd_kernels()[0], self._build_bwd(True))
+            return self._bwd_mods
         if self._bwd is None:
             DV = 64  # the backward kernels are built for value blocks of 64
             tag = rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16
@@ -208,27 +224,35 @@ class LinearAttentionEngine:
             cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_STATES, dtype=tag, head_dim=128, head_dim_v=DV, threads=192,
                                   smem_bytes=smem_s, stages=2, mask_mode=0)
             states = rt.compile_module(rt.kernel_source("linear_states.cuh", prelude=pre), "ae_linear_states", cfg)
-            # row warpgroups of the reverse pass (2: the second one takes half of the P / dS pass and of the output phase)
-            nwg = int(os.environ.get("AE_B200_LIN_BWD_NWG", LIN_BWD_NWG))
-            smem_b = (2 * 128 * 128 * 2 + 2 * 128 * DV * 2 + 128 * DV * 2 + 2 * 128 * 128 * 2
-                      + 128 * DV * 2 + 128 * DV * 2 + 1024 + 256 + 512 + 1024)
-            cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_BWD, dtype=tag, head_dim=128, head_dim_v=DV,
-                                  threads=nwg * 128 + 64, smem_bytes=smem_b, stages=1, mask_mode=0)
-            bwd = rt.compile_module(rt.kernel_source("linear_bwd.cuh", prelude=pre + f"#define AE_LB_NWG {nwg}\n"),
-                                    "ae_linear_bwd", cfg)
-            self._bwd = (states, bwd)
+            self._bwd = (states, self._build_bwd(False))
         return self._bwd
+
+    def _build_bwd(self, mods: bool):
+        DV = 64
+        tag = rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16
+        # row warpgroups of the reverse pass (2: the second one takes half of the P / dS pass and of the output phase)
+        nwg = int(os.environ.get("AE_B200_LIN_BWD_NWG", LIN_BWD_NWG))
+        pre = (f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {DV}\n#define AE_LIN_STAGES 2\n"
+               f"#define AE_LB_NWG {nwg}\n#define AE_LB_MODS {int(mods)}\n")
+        smem_b = (2 * 128 * 128 * 2 + 2 * 128 * DV * 2 + 128 * DV * 2 + 2 * 128 * 128 * 2
+                  + 128 * DV * 2 + 128 * DV * 2 + int(mods) * 128 * DV * 2 + 1024 + 256 + 512 + 1024)
+        cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_BWD, dtype=tag, head_dim=128, head_dim_v=DV,
+                              threads=nwg * 128 + 64, smem_bytes=smem_b, stages=1, mask_mode=0)
+        cfg.reserved[0] = int(mods)
+        return rt.compile_module(rt.kernel_source("linear_bwd.cuh", prelude=pre), "ae_linear_bwd", cfg)
 
     def _new_states(self, v):
         """Storage for the chunk start-states of a scan over v [B, H, T, DV]: [B, H, ceil(T / 128), 128, DV]."""
         B, H, T, DV = v.shape
         return torch.empty(B, H, -(-T // 128), 128, DV, dtype=self.dtype, device=v.device)
 
-    def _launch_bwd(self, q, k, v, a, d_o, hs=None):
-        """State recompute (unless the forward saved the states in ``hs``) and the reverse pass."""
+    def _launch_bwd(self, q, k, v, a, d_o, hs=None, mods=None):
+        """State recompute (unless the forward saved the states in ``hs``) and the reverse pass -> dq, dk, dv, da.
+        ``mods`` = (x, s, d) with v = x * s[..., None] and the output's skip term x * d[head]: the reverse pass built
+        with the two inside returns dq, dk, gx, da, gs, gd (gd per (batch, head), fp32)."""
         if v.shape[3] != 64:
             raise NotImplementedError("backward of the linear-attention scan runs on value blocks of 64")
-        states, bwd = self._bwd_kernels()
+        states, bwd = self._bwd_kernels(mods is not None)
         B, HQ, T, DK = q.shape
         HK = k.shape[1]
         H, DV = v.shape[1], v.shape[3]
@@ -247,12 +271,20 @@ class LinearAttentionEngine:
         if self._status is None or self._status.device != dev:
             self._status = torch.zeros(1, dtype=torch.int32, device=dev)
         p.status = self._status.data_ptr()
+        if mods is not None:
+            x, s, d = mods
+            gs = torch.empty_like(s)
+            gd = torch.empty(B, H, dtype=torch.float32, device=dev)
+            p.x, p.vscale, p.dskip, p.gs, p.gd = x.data_ptr(), s.data_ptr(), d.data_ptr(), gs.data_ptr(), gd.data_ptr()
+            p.vscale_16bit = int(s.dtype != torch.float32)
         stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         if recompute:
             rt.check(rt.lib().ae_launch_linear_states(states.handle, C.byref(p), stream), "ae_launch_linear_states")
         rt.check(rt.lib().ae_launch_linear_bwd(bwd.handle, C.byref(p), stream), "ae_launch_linear_bwd")
         dq = dq_h if HQ == H else self._head_sum(dq_h, HQ)
         dk = dk_h if HK == H else self._head_sum(dk_h, HK)
+        if mods is not None:
+            return dq, dk, dv, da, gs, gd
         return dq, dk, dv, da
 
     def _head_sum(self, x, n_out):

@@ -1061,6 +1061,15 @@ static int fill_linear_bwd(Module* m, const AeLinearBwdParams* p, AeLinearBwdArg
     if ((rc = make_bhtd_map(&a->tm_dq, p->dq, m->cfg.dtype, p->B, p->H, p->T, 128, 128))) return rc;
     if ((rc = make_bhtd_map(&a->tm_dk, p->dk, m->cfg.dtype, p->B, p->H, p->T, 128, 128))) return rc;
     if ((rc = make_bhtd_map(&a->tm_dv, p->dv, m->cfg.dtype, p->B, p->H, p->T, DV, 128))) return rc;
+    if (m->cfg.reserved[0] == 1) {  // built with the block's mods inside: dv receives the gradient of x
+      if (!p->x || !p->vscale || !p->dskip || !p->gs || !p->gd || (reinterpret_cast<uintptr_t>(p->x) & 15)) {
+        set_error("linear attention backward with mods: x (16-byte aligned), vscale, dskip, gs and gd are required");
+        return AE_ERR_INVALID;
+      }
+      if ((rc = make_bhtd_map(&a->tm_x, p->x, m->cfg.dtype, p->B, p->H, p->T, DV, 128))) return rc;
+      a->vscale = p->vscale; a->dskip = p->dskip; a->gs = p->gs; a->gd = p->gd;
+      a->vscale_16 = p->vscale_16bit;
+    }
   }
   a->a = p->a;
   a->h_states = p->h_states;

@@ -171,6 +171,13 @@ struct AeLinearBwdArgs {
   AeTmaDesc tm_dq;  // dq, dk, dv as store targets: like tm_q / tm_v with H heads (ae_linear_bwd stages each chunk's tiles in
   AeTmaDesc tm_dk;  // shared memory and sends them out as bulk stores)
   AeTmaDesc tm_dv;
+  // AE_LB_MODS build (v = x * vscale before the scan, y += x * dskip[h] after it): dv receives gx
+  AeTmaDesc tm_x;       // [B, H, T, DV]
+  const void* vscale;   // [B, H, T] fp32 or 16-bit
+  const float* dskip;   // [H]
+  void* gs;             // [B, H, T] in the type of vscale: sum_d dv * x
+  float* gd;            // [B, H]: sum over t, d of dO * x
+  int vscale_16;
 };
 
 // ---- row-scale mod and its backward (kernels ae_rowscale_fwd, ae_rowscale_bwd) ---------------

@@ -24,6 +24,11 @@
 // chunk's dq / dk / dv rows do not leave through their per-row global stores: they are written as 16-bit tiles over the
 // P, dS and dO-copy tiles (dead once the chunk's last MMAs have completed) and the TMA warp sends them out as bulk
 // stores while the next chunk is under way.
+// AE_LB_MODS = 1 (the Mamba2 block: v = x * s[b, h, t] before the scan, y += x * d[h] after it): the gradients that
+// meet at x leave this kernel instead of a streaming pass of their own.  The chunk's x tile is loaded next to q and k;
+// the row threads keep their piece of the dO row from phase C in registers (the dO tile is refilled before the output
+// phase) and write gx = dv * s + dO * d[h] where dv went, the row sums gs = <dv, x> (dv rounded to 16 bits first, as
+// the separate kernel saw it) per step, and one sum of <dO, x> per (batch, head) for the gradient of d.
 // Expects AE_BF16, AE_LIN_DV (64).
 
 #ifdef AE_TRACE  // clock stamps of CTA (0, 0)'s row warp 0 and MMA warp into the status buffer (experiments)
@@ -39,6 +44,9 @@
 // shared memory).
 #ifndef AE_LB_NWG
 #define AE_LB_NWG 1
+#endif
+#ifndef AE_LB_MODS
+#define AE_LB_MODS 0
 #endif
 #define AE_LB_ROWW (4 * AE_LB_NWG)  // row warps; then the TMA warp and the MMA warp
 #define AE_LB_C 128
@@ -56,7 +64,8 @@
 #define AE_LB_SMEM_DS (AE_LB_SMEM_P + AE_LB_PP_BYTES)
 #define AE_LB_SMEM_DHB (AE_LB_SMEM_DS + AE_LB_PP_BYTES)
 #define AE_LB_SMEM_DO2 (AE_LB_SMEM_DHB + AE_LB_H_BYTES)
-#define AE_LB_SMEM_G (AE_LB_SMEM_DO2 + AE_LB_V_BYTES)
+#define AE_LB_SMEM_X (AE_LB_SMEM_DO2 + AE_LB_V_BYTES)  // AE_LB_MODS: the chunk's rows of x
+#define AE_LB_SMEM_G (AE_LB_SMEM_X + AE_LB_MODS * AE_LB_V_BYTES)
 #define AE_LB_SMEM_BAR (AE_LB_SMEM_G + 1024)
 #define AE_LB_SMEM_XG (AE_LB_SMEM_BAR + 256)  // AE_LB_NWG = 2: [128] fp32, the second group's partial dG per row
 #define AE_LB_LOAD_BYTES (2 * AE_LB_QK_BYTES + 2 * AE_LB_V_BYTES + AE_LB_H_BYTES)
@@ -82,8 +91,9 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
   extern __shared__ u8 smem_raw[];
   u8* smem = smem_align1024(smem_raw);
   AeLbBars* bars = (AeLbBars*)(smem + AE_LB_SMEM_BAR);
-  float* gs = (float*)(smem + AE_LB_SMEM_G);  // [0..127] g of the chunk, [128..131] warp totals, [132..135] warp sums of dG,
-                                              // [136..139] warp sums of <dH, h>
+  float* gs = (float*)(smem + AE_LB_SMEM_G);  // [0..127] g of the chunk (after the P / dS pass: the second group's <dv, x>),
+                                              // [128..131] warp totals, [132..135] warp sums of dG, [136..143] warp sums
+                                              // of <dH, h>, [144..151] warp sums of <dO, x> at the end
   AeCtaCtl* ctl = &bars->ctl;
   const u32 warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x, b = blockIdx.y;
@@ -131,6 +141,9 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
       tma_prefetch_desc(&args.tm_dq);
       tma_prefetch_desc(&args.tm_dk);
       tma_prefetch_desc(&args.tm_dv);
+#if AE_LB_MODS
+      tma_prefetch_desc(&args.tm_x);
+#endif
       bool ok = true;
       // Shared memory holds one chunk, so the loads of the next one can only be requested as its tiles fall free: v and
       // dO (the two that come from HBM and are not read by the row threads' output phase) at the chunk's last MMA, the
@@ -161,11 +174,16 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
         }
         if (it < n_chunks) {
           if (!mbar_wait(&bars->empty, (it & 1) ^ 1, ctl, args.status, 71)) break;
-          mbar_arrive_expect_tx(&bars->full, 2 * AE_LB_QK_BYTES);
+          mbar_arrive_expect_tx(&bars->full, 2 * AE_LB_QK_BYTES + AE_LB_MODS * AE_LB_V_BYTES);
           for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
             tma_load_4d(smem + AE_LB_SMEM_Q + dh * (AE_LB_C * 128), &args.tm_q, &bars->full, dh * 64, c * AE_LB_C, hq, b);
             tma_load_4d(smem + AE_LB_SMEM_K + dh * (AE_LB_C * 128), &args.tm_k, &bars->full, dh * 64, c * AE_LB_C, hk, b);
           }
+#if AE_LB_MODS
+          // x is first read by the output phase, at the far end of the chunk: its trip from HBM is off the chain
+          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
+            tma_load_4d(smem + AE_LB_SMEM_X + dh * (AE_LB_C * 128), &args.tm_x, &bars->full, dh * 64, c * AE_LB_C, h, b);
+#endif
           mbar_arrive_expect_tx(&bars->full_h, AE_LB_H_BYTES);
           for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
             tma_load_3d(smem + AE_LB_SMEM_HC + dh * (AE_LB_DK * 128), &args.tm_h, &bars->full_h, dh * 64, 0,
@@ -269,6 +287,18 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
     // this thread's log-decay of the chunk at hand, requested one chunk ahead (the load would otherwise sit at the top
     // of every chunk's chain)
     float a_next = ((n_chunks - 1) * AE_LB_C + (int)r) < args.T ? a_row[(n_chunks - 1) * AE_LB_C + (int)r] : 0.f;
+#if AE_LB_MODS
+    // the row scale of v, requested a chunk ahead like the log-decay; the raw bits are kept until they are used
+    // (converting at once would wait for the load right here)
+    const bool vs16 = args.vscale_16 != 0;
+    auto load_vs = [&](int tt) -> u32 {
+      if (tt < 0 || tt >= args.T) return 0u;
+      return vs16 ? (u32)((const u16*)args.vscale)[bh * args.T + tt] : ((const u32*)args.vscale)[bh * args.T + tt];
+    };
+    u32 vs_next = load_vs((n_chunks - 1) * AE_LB_C + (int)r);
+    const float dsk = args.dskip[h];
+    float acc_o = 0.f;  // this thread's share of <dO, x> over all chunks
+#endif
     for (int it = 0; it < n_chunks; ++it) {
       const int c = n_chunks - 1 - it;
       const u32 par = it & 1;
@@ -276,6 +306,11 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
       const bool row_ok = t < args.T;
       AE_TRL(warp == 0, 1, it * 16 + 0)
       float g = 0.f, eg = 0.f, wj = 0.f;
+#if AE_LB_MODS
+      const float vsc = vs16 ? unpack_lo<AE_BF16>(vs_next) : __uint_as_float(vs_next);
+      vs_next = load_vs(t - AE_LB_C);
+      uint4 dos[AE_LIN_DV / 8 / AE_LB_NWG];  // this thread's piece of the dO row, for the output phase
+#endif
       if (wg == 0) {
       // ---- A: cumulative log-decay of the chunk -------------------------------------------------
       g = a_next;
@@ -353,6 +388,9 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
           const int ch = (int)wg * (AE_LIN_DV / 8 / AE_LB_NWG) + c2;
           const u32 off = tile_off(r, ch * 8, AE_LB_C);
           uint4 x = *(const uint4*)(dsrc + off);
+#if AE_LB_MODS
+          dos[c2] = x;
+#endif
           u32* xw = (u32*)&x;
 #pragma unroll
           for (int i = 0; i < 4; ++i)
@@ -437,6 +475,9 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
         const bool store = ok && row_ok;
         // rows past T are clipped by the bulk stores
         u8* dv_tile = smem + AE_LB_SMEM_DO2;
+#if AE_LB_MODS
+        float dot_v = 0.f, dot_o = 0.f;
+#endif
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
           const u8* src = smem + (which == 0 ? AE_LB_SMEM_Q : AE_LB_SMEM_K);
@@ -475,9 +516,30 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
             pk.y = pack2<AE_BF16>(f[i * 8 + 2], f[i * 8 + 3]);
             pk.z = pack2<AE_BF16>(f[i * 8 + 4], f[i * 8 + 5]);
             pk.w = pack2<AE_BF16>(f[i * 8 + 6], f[i * 8 + 7]);
+#if AE_LB_MODS
+            // gx = dv * s + dO * d[h] over the 16-bit dv; <dv, x> and <dO, x> on the way
+            const uint4 xr = *(const uint4*)(smem + AE_LB_SMEM_X + tile_off(r, cc * 32 + i * 8, AE_LB_C));
+            const uint4 gr = dos[c2 * 4 + i];
+            const u32 xw[4] = {xr.x, xr.y, xr.z, xr.w}, gw[4] = {gr.x, gr.y, gr.z, gr.w};
+            u32* pw = (u32*)&pk;
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+              const float v0 = unpack_lo<AE_BF16>(pw[e2]), v1 = unpack_hi<AE_BF16>(pw[e2]);
+              const float g0 = unpack_lo<AE_BF16>(gw[e2]), g1 = unpack_hi<AE_BF16>(gw[e2]);
+              const float x0 = unpack_lo<AE_BF16>(xw[e2]), x1 = unpack_hi<AE_BF16>(xw[e2]);
+              dot_v = fmaf(v0, x0, dot_v);
+              dot_v = fmaf(v1, x1, dot_v);
+              dot_o = fmaf(g0, x0, dot_o);
+              dot_o = fmaf(g1, x1, dot_o);
+              pw[e2] = pack2<AE_BF16>(fmaf(v0, vsc, g0 * dsk), fmaf(v1, vsc, g1 * dsk));
+            }
+#endif
             *(uint4*)(dv_tile + tile_off(r, cc * 32 + i * 8, AE_LB_C)) = pk;
           }
         }
+#if AE_LB_MODS
+        if (row_ok) acc_o += dot_o;
+#endif
         fence_proxy_async_smem();
         mbar_arrive_warp(&bars->o_ready);
         AE_TRL(warp == 0, 1, it * 16 + 10)
@@ -511,9 +573,21 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
 #if AE_LB_NWG > 1
         // the second group's share of q.dq - k.dk (and its <dH, h> slot, written above) reaches the first group
         if (wg != 0) xg[r] = dg;
+#if AE_LB_MODS
+        if (wg != 0) gs[r] = dot_v;  // the chunk's cumulative decays are dead since the P / dS pass
+#endif
         named_bar_sync(3, 128 * AE_LB_NWG);
         if (wg != 0) continue;
         dg += xg[r];
+#if AE_LB_MODS
+        dot_v += gs[r];
+#endif
+#endif
+#if AE_LB_MODS
+        if (store) {
+          if (vs16) ((u16*)args.gs)[bh * args.T + t] = (u16)(pack2<AE_BF16>(dot_v, 0.f) & 0xffffu);
+          else ((float*)args.gs)[bh * args.T + t] = dot_v;
+        }
 #endif
         // inclusive suffix sum of dG over the chunk, plus everything from later chunks
         float sfx = dg;
@@ -535,6 +609,19 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
       }
       AE_TRL(warp == 0, 1, it * 16 + 12)
     }
+#if AE_LB_MODS
+    // <dO, x> of this (batch, head): the row threads' sums meet in shared memory
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc_o += __shfl_xor_sync(0xffffffffu, acc_o, o);
+    if (lane == 0) gs[144 + warp] = acc_o;
+    named_bar_sync(4, 128 * AE_LB_NWG);
+    if (threadIdx.x == 0) {
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < AE_LB_ROWW; ++w) tot += gs[144 + w];
+      args.gd[bh] = tot;
+    }
+#endif
   }
   tc_fence_before_sync();
   __syncthreads();

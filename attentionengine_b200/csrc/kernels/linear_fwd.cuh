@@ -35,6 +35,14 @@
 #else
 #define AE_TRL(cond, region, slot)
 #endif
+// AE_LIN_NWG = 2: a second row warpgroup takes half of the columns of every row phase (same rows, other 32-column
+// blocks); the cumulative sum stays with the first group.  The groups meet at named barrier 2 (the chunk's cumulative
+// decays and column factors are ready) and 3 (end of the chunk).  The second group keeps its P in the second half of
+// its own score columns (16-bit pairs at column 96 ...), so neither group writes TMEM columns the other still reads.
+#ifndef AE_LIN_NWG
+#define AE_LIN_NWG 1
+#endif
+#define AE_LIN_ROWW (4 * AE_LIN_NWG)  // row warps; then the TMA warp and the MMA warp
 #define AE_LIN_C 128
 #define AE_LIN_DK 128
 
@@ -66,7 +74,7 @@ struct AeLinBars {
   AeCtaCtl ctl;
 };
 
-extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_constant__ AeLinearArgs args) {
+extern "C" __global__ void __launch_bounds__(AE_LIN_ROWW * 32 + 64, 1) ae_linear_fwd(const __grid_constant__ AeLinearArgs args) {
   extern __shared__ u8 smem_raw[];
   u8* smem = smem_align1024(smem_raw);
   AeLinBars* bars = (AeLinBars*)(smem + AE_LIN_SMEM_BAR);
@@ -87,17 +95,17 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       mbar_init(&bars->empty[i], 1);
     }
     mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->prep_done, 4);
+    mbar_init(&bars->prep_done, AE_LIN_ROWW);
     mbar_init(&bars->oi_full, 1);
-    mbar_init(&bars->p_full, 4);
+    mbar_init(&bars->p_full, AE_LIN_ROWW);
     mbar_init(&bars->o_done, 1);
     mbar_init(&bars->h_done, 1);
     mbar_init(&bars->hb_free, 1);
-    mbar_init(&bars->y_full, 4);
+    mbar_init(&bars->y_full, AE_LIN_ROWW);
     mbar_init(&bars->y_free, 1);
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == AE_LIN_ROWW + 1) {
     tmem_alloc(&ctl->tmem_base, 512);
     tmem_relinquish();
   }
@@ -107,7 +115,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
   const u32 tmem = ctl->tmem_base;
   const u32 TM_S = 0, TM_O = 128, TM_H = 128 + AE_LIN_DV;
 
-  if (warp == 4) {
+  if (warp == AE_LIN_ROWW) {
     // =============================== TMA producer ===============================
     if (lane == 0) {
       tma_prefetch_desc(&args.tm_q);
@@ -175,7 +183,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       }
       tma_store_wait_read();  // the tiles belong to this CTA until the bulk engine has read them
     }
-  } else if (warp == 5) {
+  } else if (warp == AE_LIN_ROWW + 1) {
     // =============================== MMA issuer =================================
     if (n_chunks > 0) {  // all 32 lanes run the control flow; MMAs and commits are issued by an elected lane
       const u32 idesc_s = umma_idesc_f16(128, AE_LIN_C, AE_BF16, 0, 0);          // q k^T
@@ -223,7 +231,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < AE_LIN_C / 16; ++kk)
-          umma_ts_w(tmem + TM_O, tmem + TM_S + kk * 8, umma_step_mn(bv_mn + so, kk), idesc_oi, (c > 0) | (kk > 0));
+          umma_ts_w(tmem + TM_O, tmem + TM_S + kk * 8 + ((AE_LIN_NWG > 1 && kk >= AE_LIN_C / 32) ? 64 : 0),
+                    umma_step_mn(bv_mn + so, kk), idesc_oi, (c > 0) | (kk > 0));
         umma_commit_w(&bars->o_done);
         umma_commit_w(&bars->empty[stage]);
         if (c + 1 < n_chunks) ok = issue_s(c + 1);
@@ -243,6 +252,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
     // The per-step scalars of a chunk (log-decay; the row scale of v in the AE_LIN_MODS build) are requested one chunk
     // ahead: a global load at the top of every chunk would sit on the chain of dependent phases.
     auto load_a = [&](int tt) { return tt < args.T ? a_row[tt] : 0.f; };
+    const u32 wg = warp >> 2;  // 0: the group that also runs the cumulative sum
     float a_next = load_a((int)r);
 #if AE_LIN_MODS
     // the raw bits are kept until the value is used a chunk later: converting at once would wait for the load right here
@@ -263,6 +273,7 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
 #if AE_LIN_MODS
       const float vsc = vs16 ? unpack_lo<AE_BF16>(vs_next) : __uint_as_float(vs_next);
 #endif
+      if (wg == 0) {
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float n = __shfl_up_sync(0xffffffffu, g, o);
@@ -285,14 +296,19 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       // column factor of the decay matrix: exp(g at the end of this step's 32-step block - g) <= 1, see phase D
       cf[r] = ae_exp(__shfl_sync(0xffffffffu, g, 31) - g);
       named_bar_sync(1, 128);
-      const float g_last = gs[AE_LIN_C - 1];
       a_next = load_a(t + AE_LIN_C);  // for the next chunk
+      }
+#if AE_LIN_NWG > 1
+      named_bar_sync(2, 128 * AE_LIN_NWG);  // the chunk's cumulative decays and column factors are there for both groups
+      if (wg != 0) g = gs[r];
+#endif
+      const float g_last = gs[AE_LIN_C - 1];
 #if AE_LIN_MODS
       vs_next = load_vs(t + AE_LIN_C);
 #endif
       AE_TRL(warp == 0, 1, c * 16 + 1)
       // ---- B: incoming state -> bf16 copy for q h, and decay it in place --------------------
-      if (c == 0 && args.h_out) {  // the first chunk starts from zero; the later ones leave through the producer's bulk stores
+      if (c == 0 && args.h_out && wg == 0) {  // the first chunk starts from zero; the later ones leave through the producer's bulk stores
         u16* hrow = (u16*)args.h_out + (((i64)b * args.H + h) * n_chunks * AE_LIN_DK + r) * AE_LIN_DV;
 #pragma unroll
         for (int i = 0; i < AE_LIN_DV / 8; ++i) *(uint4*)(hrow + i * 8) = make_uint4(0, 0, 0, 0);
@@ -305,7 +321,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
         const float dec = ae_exp(g_last);
         u8* hb = smem + AE_LIN_SMEM_H;
 #pragma unroll
-        for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+        for (int c2 = 0; c2 < AE_LIN_DV / 32 / AE_LIN_NWG; ++c2) {
+          const int cc = (int)wg * (AE_LIN_DV / 32 / AE_LIN_NWG) + c2;  // this group's 32-column chunks
           float f[32];
           u32 w[32];
           tmem_ld_f32x32(tmem + TM_H + lane_base + cc * 32, f);
@@ -340,7 +357,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
         // refilled by then)
 #endif
 #pragma unroll
-        for (int ch = 0; ch < AE_LIN_DV / 8; ++ch) {
+        for (int c2 = 0; c2 < AE_LIN_DV / 8 / AE_LIN_NWG; ++c2) {
+          const int ch = (int)wg * (AE_LIN_DV / 8 / AE_LIN_NWG) + c2;
           const u32 off = (ch >> 3) * (AE_LIN_C * 128) + swz128(r, ch & 7);
           uint4 x = *(const uint4*)(vt + off);
           u32* xw = (u32*)&x;
@@ -367,8 +385,15 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       AE_TRL(warp == 0, 1, c * 16 + 5)
       tc_fence_after_sync();
       {
-        float s[AE_LIN_C];
+        // this group's columns: all 128, or its 64 (two 32-column blocks); s[] is indexed from the first of them
+        constexpr int NCOL = AE_LIN_C / AE_LIN_NWG;
+        const int col0 = (int)wg * NCOL;
+        float s[NCOL];
+#if AE_LIN_NWG > 1
+        tmem_ld_f32x64(tmem + TM_S + lane_base + col0, s);
+#else
         tmem_ld_f32x128(tmem + TM_S + lane_base, s);
+#endif
         // exp(g_i - g_j) per 32-column block (the rows of a warp share the block that holds their diagonal): blocks
         // left of it take exp(g_i - g_end) * exp(g_end - g_j) with g_end the block's last step - one exponential per
         // row and block, the column factors computed once per chunk in phase A, both <= 1 - the diagonal block is
@@ -376,19 +401,20 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
         const u32 wq = warp & 3;
         u32 pk[32];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < NCOL / 64; ++half) {
 #pragma unroll
           for (int q2 = 0; q2 < 2; ++q2) {
-            const int cc = half * 2 + q2;  // 32-column block
+            const int lc = half * 64 + q2 * 32;  // first of the block's columns in s[]
+            const int cc = (col0 + lc) / 32;     // 32-column block of the chunk
             if ((u32)cc < wq) {
               const float rf = ae_exp(g - gs[cc * 32 + 31]);
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
                 const float4 c4 = *(const float4*)(cf + cc * 32 + i);
-                s[cc * 32 + i + 0] *= rf * c4.x;
-                s[cc * 32 + i + 1] *= rf * c4.y;
-                s[cc * 32 + i + 2] *= rf * c4.z;
-                s[cc * 32 + i + 3] *= rf * c4.w;
+                s[lc + i + 0] *= rf * c4.x;
+                s[lc + i + 1] *= rf * c4.y;
+                s[lc + i + 2] *= rf * c4.z;
+                s[lc + i + 3] *= rf * c4.w;
               }
             } else if ((u32)cc == wq) {
 #pragma unroll
@@ -398,17 +424,18 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const int j = cc * 32 + i + e;
-                  s[j] = ((u32)j <= r) ? s[j] * ae_exp(g - gv[e]) : 0.f;
+                  s[lc + i + e] = ((u32)j <= r) ? s[lc + i + e] * ae_exp(g - gv[e]) : 0.f;
                 }
               }
             } else {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) s[cc * 32 + i] = 0.f;
+              for (int i = 0; i < 32; ++i) s[lc + i] = 0.f;
             }
 #pragma unroll
-            for (int i = 0; i < 16; ++i) pk[q2 * 16 + i] = pack2<AE_BF16>(s[cc * 32 + 2 * i], s[cc * 32 + 2 * i + 1]);
+            for (int i = 0; i < 16; ++i) pk[q2 * 16 + i] = pack2<AE_BF16>(s[lc + 2 * i], s[lc + 2 * i + 1]);
           }
-          tmem_st32(tmem + TM_S + lane_base + half * 32, pk);
+          // 16-bit pairs: columns half * 32 ... of the region; the second group's at column 96 (inside its own scores)
+          tmem_st32(tmem + TM_S + lane_base + (AE_LIN_NWG > 1 ? (int)wg * 96 : half * 32), pk);
         }
       }
       AE_TRL(warp == 0, 1, c * 16 + 6)
@@ -419,7 +446,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       if (c > 0) {
         const float eg = ae_exp(g);
 #pragma unroll
-        for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+        for (int c2 = 0; c2 < AE_LIN_DV / 32 / AE_LIN_NWG; ++c2) {
+          const int cc = (int)wg * (AE_LIN_DV / 32 / AE_LIN_NWG) + c2;
           float f[32];
           u32 w[32];
           tmem_ld_f32x32(tmem + TM_O + lane_base + cc * 32, f);
@@ -438,7 +466,8 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       tc_fence_after_sync();
       {
 #pragma unroll
-        for (int cc = 0; cc < AE_LIN_DV / 32; ++cc) {
+        for (int c2 = 0; c2 < AE_LIN_DV / 32 / AE_LIN_NWG; ++c2) {
+          const int cc = (int)wg * (AE_LIN_DV / 32 / AE_LIN_NWG) + c2;
           float f[32];
           tmem_ld_f32x32(tmem + TM_O + lane_base + cc * 32, f);
 #if AE_LIN_MODS
@@ -469,14 +498,16 @@ extern "C" __global__ void __launch_bounds__(192, 1) ae_linear_fwd(const __grid_
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->y_full);
-      named_bar_sync(1, 128);  // every row has read O before the next chunk's q h overwrites it
+      // every row has read O before the next chunk's q h overwrites it (and, with two groups, the second one is done with
+      // the chunk's decays before the first rewrites them)
+      named_bar_sync(AE_LIN_NWG > 1 ? 3 : 1, 128 * AE_LIN_NWG);
       AE_TRL(warp == 0, 1, c * 16 + 10)
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == AE_LIN_ROWW + 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);
   }

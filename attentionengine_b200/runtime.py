@@ -115,7 +115,8 @@ class LinearBwdParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("a", C.c_void_p), ("d_o", C.c_void_p),
                 ("h_states", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("da", C.c_void_p),
                 ("B", C.c_int32), ("H", C.c_int32), ("HQ", C.c_int32), ("HK", C.c_int32), ("T", C.c_int32),
-                ("status", C.c_void_p)]
+                ("status", C.c_void_p), ("x", C.c_void_p), ("vscale", C.c_void_p), ("dskip", C.c_void_p),
+                ("gs", C.c_void_p), ("gd", C.c_void_p), ("vscale_16bit", C.c_int32)]
 
 
 _lib = None

@@ -271,10 +271,10 @@ def run_other(args):
         fwd = (2 * Q * Q * DK + 2 * Q * Q * DV + 4 * Q * DK * DV) * (T // Q) * H * B
         work = 3.5 * fwd
         value, unit, bound, peak = work / ms / 1e9, "TFLOPS", "tensor", float(peaks.get("bf16_tflops", 1590.0))
-        desc = ("Mamba2 SSD fwd+bwd with D_skip (v_mod and the skip inside the scan kernel, their backward one streaming kernel, decay mod eager torch), B=8 L=8192 H=80 P=64 N=128 ngroups=1 bf16; FLOPs by "
+        desc = ("Mamba2 SSD fwd+bwd with D_skip (v_mod and the skip inside the scan kernel, their backward inside the reverse pass, decay mod eager torch), B=8 L=8192 H=80 P=64 N=128 ngroups=1 bf16; FLOPs by "
                 "the chunk-256 convention, fwd (2Q^2N+2Q^2P+4QNP) per chunk and head, bwd counted as 2.5x fwd")
         desc = desc.replace("B=8 ", f"B={B} ")
-        launches = 5 * args.steps  # scan (row scale, skip and the chunk states inside), reverse pass, two head sums, row-scale + skip backward
+        launches = 4 * args.steps  # scan (row scale, skip and the chunk states inside), reverse pass (their gradients inside), two head sums
         from oracle.linear_oracle import linear_scan
         xs, dt_s, As, Bs, Cs = helpers.mamba2_inputs(1, 2, 1024, DK, DV, dt, seed=0)
         t0 = time.perf_counter()

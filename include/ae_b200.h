@@ -377,6 +377,15 @@ typedef struct AeLinearBwdParams {
   float* da;       /* [B, H, T] fp32 */
   int32_t B, H, HQ, HK, T;
   uint32_t* status;
+  /* Only read by a reverse-pass module compiled with the block's mods inside (AeKernelConfig.reserved[0] = 1; the
+   * forward's counterpart is AeLinearParams.vscale / dskip): v was x * vscale[b, h, t] and the output had
+   * x * dskip[h] added.  `dv` then receives the gradient of x, dv * vscale + d_o * dskip[h], instead of dv. */
+  const void* x;      /* [B, H, T, DV] 16-bit, 16-byte aligned */
+  const void* vscale; /* [B, H, T] fp32, or 16-bit when vscale_16bit != 0 */
+  const float* dskip; /* [H] */
+  void* gs;           /* out [B, H, T] in the type of vscale: sum over DV of dv * x */
+  float* gd;          /* out [B, H]: sum over t and DV of d_o * x (sum it over B for the gradient of dskip) */
+  int32_t vscale_16bit;
 } AeLinearBwdParams;
 
 int ae_launch_linear_states(void* module, const AeLinearBwdParams* p, void* stream);

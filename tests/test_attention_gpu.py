@@ -39,6 +39,16 @@ def fwd_form(request, monkeypatch):
     return request.param
 
 
+@pytest.fixture(params=[2, 1])
+def scan_groups(request, monkeypatch):
+    """A test that takes this fixture runs the scan's forward and reverse kernels with two row warpgroups (the default)
+    and with one."""
+    from attentionengine_b200.attn_engine import linear_attn_engine as le
+    monkeypatch.setattr(le, "LIN_FWD_NWG", request.param)
+    monkeypatch.setattr(le, "LIN_BWD_NWG", request.param)
+    return request.param
+
+
 def _check(name, got, ref, dtype, unnormalised=False, stages=None):
     """bf16 rounding stages of the attention kernels: O and dV = (P rounded) x operand, stored -> 2; dQ and dK =
     (dS rounded) x operand, stored, with dS built from delta = rowsum(O dO) of the rounded O -> 3.  The linear-attention
@@ -434,7 +444,7 @@ def test_linear_scan_against_fla_golden(golden_dir):
 
 
 @pytest.mark.parametrize("B,H,T,DV", [(2, 4, 512, 64), (1, 3, 200, 64), (1, 2, 1024, 128)])
-def test_mamba2_ssd_forward_against_oracle(B, H, T, DV):
+def test_mamba2_ssd_forward_against_oracle(B, H, T, DV, scan_groups):
     dt_ = torch.bfloat16
     x, dt, A, Bm, Cm = helpers.mamba2_inputs(B, H, T, 128, DV, dt_, seed=T)
     eng = helpers.mamba2_engine(B, H, T, 128, DV, dt_)
@@ -450,7 +460,7 @@ def test_mamba2_ssd_forward_against_oracle(B, H, T, DV):
 
 
 @pytest.mark.parametrize("B,H,T", [(1, 2, 256), (2, 4, 512), (1, 3, 200), (1, 2, 64), (2, 1, 128), (1, 2, 129)])
-def test_mamba2_ssd_backward_against_oracle(B, H, T):
+def test_mamba2_ssd_backward_against_oracle(B, H, T, scan_groups):
     """Gradients of the Mamba2 mapping (q = C, k = B, v = x * dt, a = dt * A, one q/k head shared by all heads)
     against fp64 autograd through the step-by-step recurrence.  The tensor gradients follow the bf16 rule of
     tests/parity.py with four rounding stages (P / dS, v', the carried states, the stored result); the gradients of dt
@@ -516,7 +526,7 @@ def test_streaming_kernels_of_the_scan_against_torch(dt_):
         assert torch.equal(got, ref), n_out
 
 
-def test_scan_forward_with_the_block_mods_inside_against_the_separate_kernels():
+def test_scan_forward_with_the_block_mods_inside_against_the_separate_kernels(scan_groups):
     """y = scan(q, k, x * s, a) + x * d[h] from the kernel built with the mods inside, its v_out and its chunk states
     against the same engine's plain scan on the row-scaled input and the separate skip kernel."""
     B, H, T, dt_ = 2, 4, 456, torch.bfloat16
@@ -563,6 +573,39 @@ def test_scan_states_from_the_forward_equal_the_recompute_pass():
     assert torch.equal(o, eng._launch(q, k, v, a))  # writing the states does not change the output
     for name, x1, x2 in zip(("dq", "dk", "dv", "da"), with_saved, recomputed):
         assert torch.equal(x1, x2), name
+
+
+@pytest.mark.parametrize("T,s_dtype", [(456, torch.bfloat16), (128, torch.float32), (1000, torch.bfloat16)])
+def test_scan_reverse_pass_with_the_block_mods_inside_against_the_separate_kernels(T, s_dtype, scan_groups):
+    """The reverse pass built with v = x * s and the skip term inside (it writes the gradient of x where dv went, the
+    row sums <dv, x> for s and <dO, x> per (batch, head) for the skip weight) against the plain reverse pass followed
+    by the streaming kernel: the gradient of x bit for bit (same inputs, same arithmetic per element), the sums within
+    fp32 summation-order noise (and one 16-bit rounding where s is 16-bit)."""
+    B, H, dt_ = 2, 3, torch.bfloat16
+    x, dt, A, Bm, Cm = helpers.mamba2_inputs(B, H, T, 128, 64, dt_, seed=T)
+    eng = helpers.mamba2_engine(B, H, T, 128, 64, dt_, d_skip=True)
+    q, k, xc = Cm.cuda(), Bm.cuda(), x.cuda()
+    s = dt.to(s_dtype).cuda()
+    a = (dt * A.view(1, H, 1)).float().cuda()
+    d = torch.randn(H, generator=torch.Generator().manual_seed(15)).cuda()
+    d_o = (0.1 * torch.randn(B, H, T, 64, generator=torch.Generator().manual_seed(16))).to(dt_).cuda()
+    v, hs = torch.empty_like(xc), eng._new_states(xc)
+    eng._launch(q, k, xc, a, vscale=s, dskip=d, v_out=v, h_out=hs)
+    dq, dk, dv, da = eng._launch_bwd(q, k, v, a, d_o, hs=hs)
+    gx, gs = torch.empty_like(xc), torch.empty_like(s)
+    rows = torch.empty(B, H, T, dtype=torch.float32, device="cuda")
+    eng._rowscale("vskip_bwd", xc, s, g=d_o, g2=dv, d=d, gx=gx, gs=gs, gs2=rows, rows_per_head=T, n_heads=H)
+    fdq, fdk, fgx, fda, fgs, fgd = eng._launch_bwd(q, k, v, a, d_o, hs=hs, mods=(xc, s, d))
+    torch.cuda.synchronize()
+    eng.check_status()
+    for name, x1, x2 in (("dq", fdq, dq), ("dk", fdk, dk), ("gx", fgx, gx), ("da", fda, da)):
+        assert torch.equal(x1, x2), name
+    assert fgs.dtype == s.dtype and fgd.shape == (B, H)
+    scale = gs.float().abs().max().item()
+    tol = 2e-5 * scale if s_dtype == torch.float32 else 1e-2 * scale  # 16-bit: a sum on a rounding edge moves one ulp
+    assert (fgs.float() - gs.float()).abs().max().item() <= tol
+    ref_gd = rows.double().sum(dim=2)
+    assert (fgd.double() - ref_gd).abs().max().item() <= 1e-4 * ref_gd.abs().max().item() + 1e-4
 
 
 @pytest.mark.parametrize("n_split", [None, 1, 3])
