@@ -199,7 +199,7 @@ class LinearAttentionEngine:
             prelude = (f"#define AE_BF16 {int(self._bf16)}\n#define AE_LIN_DV {dv}\n#define AE_LIN_STAGES {stages}\n"
                        f"#define AE_LIN_MODS {int(mods)}\n#define AE_LIN_NWG {nwg}\n")
             # K/V ring, rescaled V, state copy, cumulative decays, barriers, output staging tile, alignment slack
-            smem = stages * (2 * 128 * 128 * 2 + 128 * dv * 2) + 3 * 128 * dv * 2 + 1024 + 1024 + 1024
+            smem = stages * (2 * 128 * 128 * 2 + 128 * dv * 2) + 3 * 128 * dv * 2 + 1024 + 2048 + 1024
             cfg = rt.KernelConfig(kind=rt.KIND_LINEAR_FWD, dtype=rt.DTYPE_BF16 if self._bf16 else rt.DTYPE_F16,
                                   head_dim=128, head_dim_v=dv, threads=nwg * 128 + 64, smem_bytes=smem, stages=stages,
                                   mask_mode=0)

@@ -74,7 +74,8 @@ struct AeLbBars {
   u64 full;     // q, k of the chunk (requested when the chunk before hands its tiles back)
   u64 full_vd;  // v, dO (requested earlier: at the chunk before's last MMA, nothing reads those two tiles after it)
   u64 full_h;   // the chunk's start state (same request as q, k; first needed by the dq MMA, late in the chunk)
-  u64 empty;
+  u64 empty;    // the row threads are done with the chunk's start state (and x)
+  u64 qk_free;  // ... and, earlier, with its q and k tiles
   u64 s_full;
   u64 prep_done;
   u64 pds_full;
@@ -91,9 +92,12 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
   extern __shared__ u8 smem_raw[];
   u8* smem = smem_align1024(smem_raw);
   AeLbBars* bars = (AeLbBars*)(smem + AE_LB_SMEM_BAR);
-  float* gs = (float*)(smem + AE_LB_SMEM_G);  // [0..127] g of the chunk (after the P / dS pass: the second group's <dv, x>),
-                                              // [128..131] warp totals, [132..135] warp sums of dG, [136..143] warp sums
-                                              // of <dH, h>, [144..151] warp sums of <dO, x> at the end
+  // Two buffers of 128 cumulative log-decays: the chunk at hand reads one (after its P / dS pass it carries the second
+  // group's <dv, x>) while the first group already fills the other for the next chunk.
+  float* gs = (float*)(smem + AE_LB_SMEM_G);
+  // [0..3] warp totals of the cumulative sum, [4..7] warp sums of dG, [8..23] warp sums of <dH, h> (two chunks' worth,
+  // by chunk parity), [24..31] warp sums of <dO, x> at the end
+  float* misc = (float*)(smem + AE_LB_SMEM_BAR + 128);
   AeCtaCtl* ctl = &bars->ctl;
   const u32 warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x, b = blockIdx.y;
@@ -107,6 +111,7 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
     mbar_init(&bars->full_vd, 1);
     mbar_init(&bars->full_h, 1);
     mbar_init(&bars->empty, AE_LB_ROWW);
+    mbar_init(&bars->qk_free, AE_LB_ROWW);
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->prep_done, AE_LB_ROWW);
     mbar_init(&bars->pds_full, AE_LB_ROWW);
@@ -161,8 +166,18 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
             tma_load_4d(smem + AE_LB_SMEM_DO + dh * (AE_LB_C * 128), &args.tm_do, &bars->full_vd, dh * 64, c * AE_LB_C, h, b);
           }
         }
+        if (it < n_chunks) {
+          // q and k: handed back by the row threads as soon as their dq / dk rows are done, ahead of the rest of the
+          // output phase - the next chunk's first MMA waits for these two
+          if (it >= 1 && !mbar_wait(&bars->qk_free, (it - 1) & 1, ctl, args.status, 88)) break;
+          mbar_arrive_expect_tx(&bars->full, 2 * AE_LB_QK_BYTES);
+          for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
+            tma_load_4d(smem + AE_LB_SMEM_Q + dh * (AE_LB_C * 128), &args.tm_q, &bars->full, dh * 64, c * AE_LB_C, hq, b);
+            tma_load_4d(smem + AE_LB_SMEM_K + dh * (AE_LB_C * 128), &args.tm_k, &bars->full, dh * 64, c * AE_LB_C, hk, b);
+          }
+        }
         if (it >= 1) {
-          // the output tiles of the chunk before: ready a little before its tiles are handed back
+          // the output tiles of the chunk before: ready a little before its last tiles are handed back
           const int co = n_chunks - it;
           ok = mbar_wait(&bars->o_ready, (it - 1) & 1, ctl, args.status, 80);
           if (!ok) break;
@@ -174,20 +189,16 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
         }
         if (it < n_chunks) {
           if (!mbar_wait(&bars->empty, (it & 1) ^ 1, ctl, args.status, 71)) break;
-          mbar_arrive_expect_tx(&bars->full, 2 * AE_LB_QK_BYTES + AE_LB_MODS * AE_LB_V_BYTES);
-          for (int dh = 0; dh < AE_LB_DK / 64; ++dh) {
-            tma_load_4d(smem + AE_LB_SMEM_Q + dh * (AE_LB_C * 128), &args.tm_q, &bars->full, dh * 64, c * AE_LB_C, hq, b);
-            tma_load_4d(smem + AE_LB_SMEM_K + dh * (AE_LB_C * 128), &args.tm_k, &bars->full, dh * 64, c * AE_LB_C, hk, b);
-          }
-#if AE_LB_MODS
-          // x is first read by the output phase, at the far end of the chunk: its trip from HBM is off the chain
-          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
-            tma_load_4d(smem + AE_LB_SMEM_X + dh * (AE_LB_C * 128), &args.tm_x, &bars->full, dh * 64, c * AE_LB_C, h, b);
-#endif
-          mbar_arrive_expect_tx(&bars->full_h, AE_LB_H_BYTES);
+          mbar_arrive_expect_tx(&bars->full_h, AE_LB_H_BYTES + AE_LB_MODS * AE_LB_V_BYTES);
           for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
             tma_load_3d(smem + AE_LB_SMEM_HC + dh * (AE_LB_DK * 128), &args.tm_h, &bars->full_h, dh * 64, 0,
                         (b * args.H + h) * n_chunks + c);
+#if AE_LB_MODS
+          // x is first read by the output phase, at the far end of the chunk: it travels with the start state, behind
+          // q and k, which the chunk's first MMA waits for
+          for (int dh = 0; dh < AE_LIN_DV / 64; ++dh)
+            tma_load_4d(smem + AE_LB_SMEM_X + dh * (AE_LB_C * 128), &args.tm_x, &bars->full_h, dh * 64, c * AE_LB_C, h, b);
+#endif
         }
         if (it >= 1) {
           const int co = n_chunks - it;
@@ -299,46 +310,74 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
     const float dsk = args.dskip[h];
     float acc_o = 0.f;  // this thread's share of <dO, x> over all chunks
 #endif
-    for (int it = 0; it < n_chunks; ++it) {
-      const int c = n_chunks - 1 - it;
-      const u32 par = it & 1;
-      const int t = c * AE_LB_C + (int)r;
-      const bool row_ok = t < args.T;
-      AE_TRL(warp == 0, 1, it * 16 + 0)
-      float g = 0.f, eg = 0.f, wj = 0.f;
-#if AE_LB_MODS
-      const float vsc = vs16 ? unpack_lo<AE_BF16>(vs_next) : __uint_as_float(vs_next);
-      vs_next = load_vs(t - AE_LB_C);
-      uint4 dos[AE_LIN_DV / 8 / AE_LB_NWG];  // this thread's piece of the dO row, for the output phase
-#endif
-      if (wg == 0) {
-      // ---- A: cumulative log-decay of the chunk -------------------------------------------------
-      g = a_next;
-      if (c > 0) a_next = a_row[t - AE_LB_C];  // chunks before the last one are full
+    // The two scans over the chunk's steps (cumulative log-decay; suffix sums of dG) are shuffles, shared-memory round
+    // trips and a barrier of the first group.  At the chunk boundary they sat in the burst of bulk copies (the chunk's
+    // output tiles leave, the next chunk's tiles arrive) and took 2700 clk of the chain for a few dozen instructions.
+    // Both now run in the idle time before the output phase: the cumulative sum of the NEXT chunk into the other
+    // buffer, the suffix sums of the chunk BEFORE from values kept in registers.
+    auto cum_sum = [&](float g, float* gb) -> float {  // first group only
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float n = __shfl_up_sync(0xffffffffu, g, o);
         if (lane >= (u32)o) g += n;
       }
-      if (lane == 31) gs[128 + (warp & 3)] = g;
+      if (lane == 31) misc[warp & 3] = g;
       named_bar_sync(1, 128);
-      {
-        float pre = 0.f;
+      float pre = 0.f;
 #pragma unroll
-        for (int w = 0; w < 3; ++w)
-          if ((u32)w < (warp & 3)) pre += gs[128 + w];
-        g += pre;
+      for (int w = 0; w < 3; ++w)
+        if ((u32)w < (warp & 3)) pre += misc[w];
+      g += pre;
+      gb[r] = g;
+      return g;  // the others read gb[] after the barrier at the top of the chunk
+    };
+    float dg_pend = 0.f;
+    int t_pend = 0;
+    bool store_pend = false;
+    auto finish_da = [&](u32 hp) {  // first group only: da of the chunk whose dG is in dg_pend, <dH, h> sums in misc[8 + hp * 8 ..]
+      float sfx = dg_pend;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float n = __shfl_down_sync(0xffffffffu, sfx, o);
+        if (lane + (u32)o < 32) sfx += n;
       }
-      gs[r] = g;
+      if (lane == 0) misc[4 + (warp & 3)] = sfx;
       named_bar_sync(1, 128);
-#if AE_LB_NWG > 1
-      named_bar_sync(2, 128 * AE_LB_NWG);  // the second group may read the chunk's cumulative decays
+      float after = 0.f, next_carry = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w)
+        if ((u32)w > (warp & 3)) after += misc[4 + w];
+#pragma unroll
+      for (int w = 0; w < AE_LB_ROWW; ++w) next_carry += misc[8 + hp * 8 + w];
+      if (store_pend) args.da[bh * args.T + t_pend] = sfx + after + carry;
+      carry = next_carry;
+    };
+    float g_nxt = 0.f;
+    if (wg == 0) {
+      g_nxt = cum_sum(a_next, gs);
+      a_next = n_chunks >= 2 ? a_row[(n_chunks - 2) * AE_LB_C + (int)r] : 0.f;  // chunks before the last one are full
+    }
+    for (int it = 0; it < n_chunks; ++it) {
+      const int c = n_chunks - 1 - it;
+      const u32 par = it & 1;
+      const int t = c * AE_LB_C + (int)r;
+      const bool row_ok = t < args.T;
+      float* gc = gs + par * 128;  // this chunk's cumulative log-decays
+      AE_TRL(warp == 0, 1, it * 16 + 0)
+      float g = g_nxt, eg = 0.f, wj = 0.f;
+#if AE_LB_MODS
+      const float vsc = vs16 ? unpack_lo<AE_BF16>(vs_next) : __uint_as_float(vs_next);
+      vs_next = load_vs(t - AE_LB_C);
+      uint4 dos[AE_LIN_DV / 8 / AE_LB_NWG];  // this thread's piece of the dO row, for the output phase
 #endif
-      } else {
-        named_bar_sync(2, 128 * AE_LB_NWG);
-        g = gs[r];
-      }
-      const float g_last = gs[AE_LB_C - 1];
+      // ---- A: the chunk's cumulative log-decays were summed during the chunk before ------------------
+#if AE_LB_NWG > 1
+      named_bar_sync(2, 128 * AE_LB_NWG);
+      if (wg != 0) g = gc[r];
+#else
+      named_bar_sync(1, 128);
+#endif
+      const float g_last = gc[AE_LB_C - 1];
       eg = ae_exp(g);
       wj = ae_exp(g_last - g);
       AE_TRL(warp == 0, 1, it * 16 + 1)
@@ -422,7 +461,7 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
 #pragma unroll
             for (int e2 = 0; e2 < 4; ++e2) {
               const int j0 = cc * 32 + i * 8 + e2 * 2;
-              const float2 gj = *(const float2*)(gs + j0);
+              const float2 gj = *(const float2*)(gc + j0);
               const float e0 = ((u32)j0 <= r) ? ae_exp(g - gj.x) : 0.f;
               const float e1 = ((u32)(j0 + 1) <= r) ? ae_exp(g - gj.y) : 0.f;
               pw[e2] = pack2<AE_BF16>(av[i * 8 + e2 * 2] * e0, av[i * 8 + e2 * 2 + 1] * e1);
@@ -464,6 +503,14 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
       mbar_arrive_warp(&bars->scaled_done);
       }
       AE_TRL(warp == 0, 1, it * 16 + 8)
+      if (wg == 0) {  // under the chunk's last MMAs
+        if (it > 0) finish_da((it - 1) & 1);
+        if (c > 0) {
+          g_nxt = cum_sum(a_next, gs + (par ^ 1) * 128);
+          a_next = c >= 2 ? a_row[t - 2 * AE_LB_C] : 0.f;
+        }
+      }
+      AE_TRL(warp == 0, 1, it * 16 + 13)
       // ---- F: outputs -------------------------------------------------------------------------------------
       ok = ok && mbar_wait(&bars->out_full, par, ctl, args.status, 79);
       // q, k and the start state are read below with ordinary loads: this thread has to have seen their barriers too
@@ -504,6 +551,8 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
           }
           dg += which == 0 ? dot : -dot;
         }
+        tc_fence_before_sync();
+        mbar_arrive_warp(&bars->qk_free);  // last read of the q and k tiles (their MMAs completed before this phase)
 #pragma unroll
         for (int c2 = 0; c2 < AE_LIN_DV / 32 / AE_LB_NWG; ++c2) {
           const int cc = (int)wg * (AE_LIN_DV / 32 / AE_LB_NWG) + c2;
@@ -564,7 +613,7 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
           }
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) hd += __shfl_xor_sync(0xffffffffu, hd, o);
-          if (lane == 0) gs[136 + warp] = hd;  // one slot per row warp of either group
+          if (lane == 0) misc[8 + par * 8 + warp] = hd;  // one slot per row warp of either group
         }
         // last read of this chunk's tiles and accumulators: the next chunk's loads start under the sums below
         tc_fence_before_sync();
@@ -574,13 +623,14 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
         // the second group's share of q.dq - k.dk (and its <dH, h> slot, written above) reaches the first group
         if (wg != 0) xg[r] = dg;
 #if AE_LB_MODS
-        if (wg != 0) gs[r] = dot_v;  // the chunk's cumulative decays are dead since the P / dS pass
+        if (wg != 0) gc[r] = dot_v;  // the chunk's cumulative decays are dead since the P / dS pass
 #endif
         named_bar_sync(3, 128 * AE_LB_NWG);
+        AE_TRL(warp == 0, 1, it * 16 + 12)
         if (wg != 0) continue;
         dg += xg[r];
 #if AE_LB_MODS
-        dot_v += gs[r];
+        dot_v += gc[r];
 #endif
 #endif
 #if AE_LB_MODS
@@ -589,36 +639,23 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
           else ((float*)args.gs)[bh * args.T + t] = dot_v;
         }
 #endif
-        // inclusive suffix sum of dG over the chunk, plus everything from later chunks
-        float sfx = dg;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const float n = __shfl_down_sync(0xffffffffu, sfx, o);
-          if (lane + (u32)o < 32) sfx += n;
-        }
-        if (lane == 0) gs[132 + (warp & 3)] = sfx;
-        named_bar_sync(1, 128);
-        float after = 0.f, next_carry = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w)
-          if ((u32)w > (warp & 3)) after += gs[132 + w];
-#pragma unroll
-        for (int w = 0; w < AE_LB_ROWW; ++w) next_carry += gs[136 + w];
-        if (store) args.da[bh * args.T + t] = sfx + after + carry;
-        carry = next_carry;
+        // the suffix sums of dG (-> da) follow under the next chunk's last MMAs
+        dg_pend = dg;
+        t_pend = t;
+        store_pend = store;
       }
-      AE_TRL(warp == 0, 1, it * 16 + 12)
     }
+    if (wg == 0) finish_da((n_chunks - 1) & 1);
 #if AE_LB_MODS
     // <dO, x> of this (batch, head): the row threads' sums meet in shared memory
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc_o += __shfl_xor_sync(0xffffffffu, acc_o, o);
-    if (lane == 0) gs[144 + warp] = acc_o;
+    if (lane == 0) misc[24 + warp] = acc_o;
     named_bar_sync(4, 128 * AE_LB_NWG);
     if (threadIdx.x == 0) {
       float tot = 0.f;
 #pragma unroll
-      for (int w = 0; w < AE_LB_ROWW; ++w) tot += gs[144 + w];
+      for (int w = 0; w < AE_LB_ROWW; ++w) tot += misc[24 + w];
       args.gd[bh] = tot;
     }
 #endif

@@ -36,8 +36,8 @@
 #define AE_TRL(cond, region, slot)
 #endif
 // AE_LIN_NWG = 2: a second row warpgroup takes half of the columns of every row phase (same rows, other 32-column
-// blocks); the cumulative sum stays with the first group.  The groups meet at named barrier 2 (the chunk's cumulative
-// decays and column factors are ready) and 3 (end of the chunk).  The second group keeps its P in the second half of
+// blocks); the cumulative sum stays with the first group, which runs it one chunk ahead into the other of two buffers.
+// The groups meet at named barrier 2 at the top of every chunk.  The second group keeps its P in the second half of
 // its own score columns (16-bit pairs at column 96 ...), so neither group writes TMEM columns the other still reads.
 #ifndef AE_LIN_NWG
 #define AE_LIN_NWG 1
@@ -57,7 +57,7 @@
 // Output staging tile [128 rows][DV] 16-bit in the layout of a 128-byte-swizzled TMA box (64-column blocks): row r is
 // written by thread r alone and the tile leaves through one bulk store per chunk.  In the AE_LIN_MODS build the same
 // rows first hold the raw x of the chunk (phase C) for the skip term of phase F.
-#define AE_LIN_SMEM_Y (AE_LIN_SMEM_BAR + 1024)
+#define AE_LIN_SMEM_Y (AE_LIN_SMEM_BAR + 2048)
 
 struct AeLinBars {
   u64 full[AE_LIN_STAGES];
@@ -244,7 +244,10 @@ extern "C" __global__ void __launch_bounds__(AE_LIN_ROWW * 32 + 64, 1) ae_linear
     const u32 lane_base = ((warp & 3) * 32) << 16;
     const float* a_row = args.a + ((i64)b * args.H + h) * args.T;
     u8* y_tile = smem + AE_LIN_SMEM_Y;
-    float* cf = (float*)(smem + AE_LIN_SMEM_BAR + 512);  // [128] column factors of the chunk's decay matrix
+    // [2][128] column factors of the chunk's decay matrix; like the cumulative log-decays (gs, [2][128]) by chunk parity:
+    // the first group fills the next chunk's while the chunk at hand still reads its own
+    float* cf_all = (float*)(smem + AE_LIN_SMEM_BAR + 1024);
+    float* misc = (float*)(smem + AE_LIN_SMEM_BAR + 512);  // [0..3] warp totals of the cumulative sum
 #if AE_LIN_MODS
     const float dsk = args.dskip ? args.dskip[h] : 0.f;
 #endif
@@ -264,45 +267,51 @@ extern "C" __global__ void __launch_bounds__(AE_LIN_ROWW * 32 + 64, 1) ae_linear
     };
     u32 vs_next = load_vs((int)r);
 #endif
-    for (int c = 0; c < n_chunks; ++c) {
-      const int stage = c % AE_LIN_STAGES;
-      const int t = c * AE_LIN_C + (int)r;
-      AE_TRL(warp == 0, 1, c * 16 + 0)
-      // ---- A: inclusive cumulative sum of the log-decay over the chunk ----------------------
-      float g = a_next;
-#if AE_LIN_MODS
-      const float vsc = vs16 ? unpack_lo<AE_BF16>(vs_next) : __uint_as_float(vs_next);
-#endif
-      if (wg == 0) {
+    // Inclusive cumulative sum of the log-decay over a chunk and the column factors of its decay matrix (first group
+    // only).  It runs one chunk ahead, while the P v MMAs of the chunk at hand are under way: at the top of the chunk
+    // its shuffles, shared-memory round trips and barrier were 500 to 800 clk of the chain.
+    auto cum_sum = [&](float g, float* gb, float* cb) -> float {
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float n = __shfl_up_sync(0xffffffffu, g, o);
         if (lane >= (u32)o) g += n;
       }
-      AE_TRL(warp == 0, 1, c * 16 + 11)
-      if (lane == 31) gs[128 + (warp & 3)] = g;
+      if (lane == 31) misc[warp & 3] = g;
       named_bar_sync(1, 128);
-      AE_TRL(warp == 0, 1, c * 16 + 12)
-      {
-        float pre = 0.f;
+      float pre = 0.f;
 #pragma unroll
-        for (int w = 0; w < 3; ++w)
-          if ((u32)w < (warp & 3)) pre += gs[128 + w];
-        g += pre;
-      }
-      named_bar_sync(1, 128);  // warp totals consumed; also: last chunk's readers of gs[] are done
-      AE_TRL(warp == 0, 1, c * 16 + 13)
-      gs[r] = g;
+      for (int w = 0; w < 3; ++w)
+        if ((u32)w < (warp & 3)) pre += misc[w];
+      g += pre;
+      gb[r] = g;
       // column factor of the decay matrix: exp(g at the end of this step's 32-step block - g) <= 1, see phase D
-      cf[r] = ae_exp(__shfl_sync(0xffffffffu, g, 31) - g);
-      named_bar_sync(1, 128);
-      a_next = load_a(t + AE_LIN_C);  // for the next chunk
-      }
-#if AE_LIN_NWG > 1
-      named_bar_sync(2, 128 * AE_LIN_NWG);  // the chunk's cumulative decays and column factors are there for both groups
-      if (wg != 0) g = gs[r];
+      cb[r] = ae_exp(__shfl_sync(0xffffffffu, g, 31) - g);
+      return g;
+    };
+    float g_nxt = 0.f;
+    if (wg == 0) {
+      g_nxt = cum_sum(a_next, gs, cf_all);
+      a_next = load_a(AE_LIN_C + (int)r);
+    }
+    for (int c = 0; c < n_chunks; ++c) {
+      const int stage = c % AE_LIN_STAGES;
+      const int t = c * AE_LIN_C + (int)r;
+      AE_TRL(warp == 0, 1, c * 16 + 0)
+      // ---- A: the chunk's cumulative log-decays were summed during the chunk before (cum_sum) -----
+      float* gc = gs + (c & 1) * 128;
+      const float* cf = cf_all + (c & 1) * 128;
+      float g = g_nxt;
+#if AE_LIN_MODS
+      const float vsc = vs16 ? unpack_lo<AE_BF16>(vs_next) : __uint_as_float(vs_next);
 #endif
-      const float g_last = gs[AE_LIN_C - 1];
+      // all row threads are done with the chunk before; its sums (written by the first group) are visible
+#if AE_LIN_NWG > 1
+      named_bar_sync(2, 128 * AE_LIN_NWG);
+      if (wg != 0) g = gc[r];
+#else
+      named_bar_sync(1, 128);
+#endif
+      const float g_last = gc[AE_LIN_C - 1];
 #if AE_LIN_MODS
       vs_next = load_vs(t + AE_LIN_C);
 #endif
@@ -407,7 +416,7 @@ extern "C" __global__ void __launch_bounds__(AE_LIN_ROWW * 32 + 64, 1) ae_linear
             const int lc = half * 64 + q2 * 32;  // first of the block's columns in s[]
             const int cc = (col0 + lc) / 32;     // 32-column block of the chunk
             if ((u32)cc < wq) {
-              const float rf = ae_exp(g - gs[cc * 32 + 31]);
+              const float rf = ae_exp(g - gc[cc * 32 + 31]);
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
                 const float4 c4 = *(const float4*)(cf + cc * 32 + i);
@@ -419,7 +428,7 @@ extern "C" __global__ void __launch_bounds__(AE_LIN_ROWW * 32 + 64, 1) ae_linear
             } else if ((u32)cc == wq) {
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
-                const float4 gj = *(const float4*)(gs + cc * 32 + i);
+                const float4 gj = *(const float4*)(gc + cc * 32 + i);
                 const float gv[4] = {gj.x, gj.y, gj.z, gj.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -460,6 +469,11 @@ extern "C" __global__ void __launch_bounds__(AE_LIN_ROWW * 32 + 64, 1) ae_linear
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->p_full);
       AE_TRL(warp == 0, 1, c * 16 + 8)
+      if (wg == 0 && c + 1 < n_chunks) {  // under the P v MMAs
+        g_nxt = cum_sum(a_next, gs + ((c + 1) & 1) * 128, cf_all + ((c + 1) & 1) * 128);
+        a_next = load_a(t + 2 * AE_LIN_C);
+      }
+      AE_TRL(warp == 0, 1, c * 16 + 11)
       // ---- F: O rows out ---------------------------------------------------------------------------
       ok = ok && mbar_wait(&bars->o_done, c & 1, ctl, args.status, 59);
       AE_TRL(warp == 0, 1, c * 16 + 9)
@@ -498,9 +512,8 @@ extern "C" __global__ void __launch_bounds__(AE_LIN_ROWW * 32 + 64, 1) ae_linear
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive_warp(&bars->y_full);
-      // every row has read O before the next chunk's q h overwrites it (and, with two groups, the second one is done with
-      // the chunk's decays before the first rewrites them)
-      named_bar_sync(AE_LIN_NWG > 1 ? 3 : 1, 128 * AE_LIN_NWG);
+      // no barrier here: the next chunk's q h MMA (which overwrites O) waits for every row warp's prep_done arrival,
+      // and each warp arrives there only after this point
       AE_TRL(warp == 0, 1, c * 16 + 10)
     }
   }
