@@ -28,6 +28,7 @@ from ..core.transform.graph import Var
 from ..lower.torch_eval import evaluate
 
 LIN_FWD_NWG = 2  # row warpgroups of the scan's forward kernel (measured: cfg4 3.72 against 4.14 ms)
+LIN_DECAY_SCALE = 1  # a decay mod `decay * c[heads]` inside the scan kernels of the Mamba2 block (0: eager PyTorch)
 LIN_BWD_MODS = 1  # the row scale of v and the skip term inside the reverse pass (0: a streaming kernel after it)
 LIN_BWD_NWG = 2  # row warpgroups of the reverse pass of the scan (measured: 4.05 against 4.33 ms at cfg4)
 
@@ -120,36 +121,46 @@ class _ScaleScanSkip(torch.autograd.Function):
     skip) and the row sums for s and d come out of one pass over x (ae_vskip_bwd) instead of two kernels and an add."""
 
     @staticmethod
-    def forward(ctx, eng, q, k, x, a, s, d):
+    def forward(ctx, eng, q, k, x, a, s, d, asc=None):
         q, k, x, a, s = q.contiguous(), k.contiguous(), x.contiguous(), a.float().contiguous(), s.contiguous()
         df = d.detach().float().reshape(-1).contiguous()
+        # a decay mod of the form decay * custom[heads]: a is the decay as passed, the kernels scale it
+        af = None if asc is None else asc.detach().float().reshape(-1).contiguous()
+        ctx.asc_meta = None if asc is None else (asc.shape, asc.dtype)
         # one kernel: the scan scales its V rows by s, adds x * d[head] to its output rows and writes the scaled v
         # for the backward (only when a gradient is wanted)
         need_v = any(ctx.needs_input_grad)
         v = torch.empty_like(x) if need_v else None
         hs = eng._new_states(x) if need_v else None  # the chunk start-states, for the reverse pass
-        y = eng._launch(q, k, x, a, vscale=s, dskip=df, v_out=v, h_out=hs)
+        y = eng._launch(q, k, x, a, vscale=s, dskip=df, v_out=v, h_out=hs, ascale=af)
         ctx.eng, ctx.d_shape, ctx.d_dtype = eng, d.shape, d.dtype
         if not need_v:
             return y
-        ctx.save_for_backward(q, k, v, a, x, s, df, hs)
+        ctx.save_for_backward(q, k, v, a, x, s, df, hs, af)
         return y
 
     @staticmethod
     def backward(ctx, g):
-        q, k, v, a, x, s, df, hs = ctx.saved_tensors
+        q, k, v, a, x, s, df, hs, af = ctx.saved_tensors
         g = g.contiguous()
+        gasc = None
         if int(os.environ.get("AE_B200_LIN_BWD_MODS", LIN_BWD_MODS)):
             # the reverse pass built with the two mods inside: no pass over x of its own
-            dq, dk, gx, da, gs, rows = ctx.eng._launch_bwd(q, k, v, a, g, hs=hs, mods=(x, s, df))
-            return None, dq, dk, gx, da, gs, rows.sum(dim=0).reshape(ctx.d_shape).to(ctx.d_dtype)
-        dq, dk, dv, da = ctx.eng._launch_bwd(q, k, v, a, g, hs=hs)
+            res = ctx.eng._launch_bwd(q, k, v, a, g, hs=hs, mods=(x, s, df), ascale=af)
+            dq, dk, gx, da, gs, rows = res[:6]
+            if af is not None:
+                gasc = res[6].sum(dim=0).reshape(ctx.asc_meta[0]).to(ctx.asc_meta[1])
+            return None, dq, dk, gx, da, gs, rows.sum(dim=0).reshape(ctx.d_shape).to(ctx.d_dtype), gasc
+        res = ctx.eng._launch_bwd(q, k, v, a, g, hs=hs, ascale=af)
+        dq, dk, dv, da = res[:4]
+        if af is not None:
+            gasc = res[4].sum(dim=0).reshape(ctx.asc_meta[0]).to(ctx.asc_meta[1])
         gx, gs = torch.empty_like(x), torch.empty_like(s)
         rows = torch.empty(x.shape[:3], dtype=torch.float32, device=x.device)
         ctx.eng._rowscale("vskip_bwd", x, s, g=g, g2=dv, d=df, gx=gx, gs=gs, gs2=rows, rows_per_head=x.shape[2],
                           n_heads=x.shape[1])
         gd = rows.sum(dim=(0, 2)).reshape(ctx.d_shape).to(ctx.d_dtype)
-        return None, dq, dk, gx, da, gs, gd
+        return None, dq, dk, gx, da, gs, gd, gasc
 
 
 class LinearAttentionEngine:
@@ -246,10 +257,12 @@ class LinearAttentionEngine:
         B, H, T, DV = v.shape
         return torch.empty(B, H, -(-T // 128), 128, DV, dtype=self.dtype, device=v.device)
 
-    def _launch_bwd(self, q, k, v, a, d_o, hs=None, mods=None):
+    def _launch_bwd(self, q, k, v, a, d_o, hs=None, mods=None, ascale=None):
         """State recompute (unless the forward saved the states in ``hs``) and the reverse pass -> dq, dk, dv, da.
         ``mods`` = (x, s, d) with v = x * s[..., None] and the output's skip term x * d[head]: the reverse pass built
-        with the two inside returns dq, dk, gx, da, gs, gd (gd per (batch, head), fp32)."""
+        with the two inside returns dq, dk, gx, da, gs, gd (gd per (batch, head), fp32).  ``ascale`` [H] fp32: the
+        forward ran on a * ascale[h]; da is then the gradient of ``a`` as passed and one more result, [B, H] fp32, holds
+        the per-(batch, head) sums for the gradient of ascale."""
         if v.shape[3] != 64:
             raise NotImplementedError("backward of the linear-attention scan runs on value blocks of 64")
         states, bwd = self._bwd_kernels(mods is not None)
@@ -277,15 +290,18 @@ class LinearAttentionEngine:
             gd = torch.empty(B, H, dtype=torch.float32, device=dev)
             p.x, p.vscale, p.dskip, p.gs, p.gd = x.data_ptr(), s.data_ptr(), d.data_ptr(), gs.data_ptr(), gd.data_ptr()
             p.vscale_16bit = int(s.dtype != torch.float32)
+        gasc = None
+        if ascale is not None:
+            gasc = torch.empty(B, H, dtype=torch.float32, device=dev)
+            p.ascale, p.gasc = ascale.data_ptr(), gasc.data_ptr()
         stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         if recompute:
             rt.check(rt.lib().ae_launch_linear_states(states.handle, C.byref(p), stream), "ae_launch_linear_states")
         rt.check(rt.lib().ae_launch_linear_bwd(bwd.handle, C.byref(p), stream), "ae_launch_linear_bwd")
         dq = dq_h if HQ == H else self._head_sum(dq_h, HQ)
         dk = dk_h if HK == H else self._head_sum(dk_h, HK)
-        if mods is not None:
-            return dq, dk, dv, da, gs, gd
-        return dq, dk, dv, da
+        out = (dq, dk, dv, da) + ((gs, gd) if mods is not None else ())
+        return out + ((gasc,) if ascale is not None else ())
 
     def _head_sum(self, x, n_out):
         """[B, H, T, D] -> [B, n_out, T, D]: sum over the H / n_out heads of each group, fp32 accumulation, one pass."""
@@ -355,6 +371,24 @@ class LinearAttentionEngine:
         y = evaluate(out, env)
         return y if name == "decay" else y.to(x.dtype)
 
+    def _decay_scale_operand(self, decay, custom):
+        """The custom tensor c when the traced decay_mod is exactly ``decay * c`` with c indexed by heads only (fp32,
+        [1, H] or [H]); None otherwise (the mod then runs as eager PyTorch)."""
+        if "decay" not in self._traced or decay.dtype != torch.float32:
+            return None
+        leaf, out = self._traced["decay"]
+        if out.code.type != "Mul" or len(out.prev) != 2:
+            return None
+        other = out.prev[1] if out.prev[0] is leaf else out.prev[0] if out.prev[1] is leaf else None
+        if other is None:
+            return None
+        for (cname, sym), t in zip(self.custom_io.input_tensors.items(), custom):
+            if sym is other:
+                names = tuple(str(n) for n in sym.shape_idx if str(n) != "1")
+                if names == ("heads",) and t.numel() == self.H and t.dtype == torch.float32:
+                    return t
+        return None
+
     def _skip_operand(self, custom):
         """The custom tensor d when the traced o_mod is exactly ``o + v * d`` with d indexed by heads only (fp32,
         [1, H] or [H]); None otherwise (the mod then runs as eager PyTorch)."""
@@ -382,7 +416,7 @@ class LinearAttentionEngine:
             env[id(sym)] = _align(t, tuple(sym.shape_idx), o.dim())
         return evaluate(self._o_traced, env).to(o.dtype)
 
-    def _launch(self, q, k, v, a, vscale=None, dskip=None, v_out=None, h_out=None):
+    def _launch(self, q, k, v, a, vscale=None, dskip=None, v_out=None, h_out=None, ascale=None):
         """The scan kernel.  With ``vscale`` [B, H, T] / ``dskip`` [H] fp32 the build with the mods inside runs: scan of
         v * vscale plus v * dskip[h]; ``v_out`` receives the scaled v."""
         B, HQ, T, DK = q.shape
@@ -402,6 +436,8 @@ class LinearAttentionEngine:
                 p.v_out = v_out.data_ptr()
         if h_out is not None:
             p.h_states_out = h_out.data_ptr()
+        if ascale is not None:  # [H] fp32: the scan runs on a * ascale[h]
+            p.ascale = ascale.data_ptr()
         p.B, p.H, p.HQ, p.HK, p.T = B, H, HQ, k.shape[1], T
         if self._status is None or self._status.device != q.device:
             self._status = torch.zeros(1, dtype=torch.int32, device=q.device)
@@ -452,14 +488,18 @@ class LinearAttentionEngine:
             raise TypeError(f"expected {len(self.custom_io.input_tensors)} custom input(s), got {len(custom)}")
         if q.shape[3] != self.DK or v.shape[3] != self.DV or v.shape[1] % q.shape[1] or v.shape[1] % k.shape[1]:
             raise ValueError("inconsistent q/k/v shapes")
-        a = self._apply_mod("decay", decay, custom)
         qm = self._apply_mod("q", q, custom)
         km = self._apply_mod("k", k, custom)
         if self.o_mod is not None and "v" in self._traced and self.DK == 128 and self.DV == 64 and v.dtype == self.dtype:
-            # `v * s[b, h, t]` into the scan and `o + v * d[h]` after it (the Mamba2 block): one autograd node
+            # `v * s[b, h, t]` into the scan and `o + v * d[h]` after it (the Mamba2 block): one autograd node, which
+            # also takes a decay mod of the form `decay * c[h]` into the kernels
             s, d = self._rowscale_operand("v", v, custom), self._skip_operand(custom)
             if s is not None and d is not None:
-                return _ScaleScanSkip.apply(self, qm, km, v, a, s, d)
+                c = self._decay_scale_operand(decay, custom) if LIN_DECAY_SCALE else None
+                if c is not None:
+                    return _ScaleScanSkip.apply(self, qm, km, v, decay, s, d, c)
+                return _ScaleScanSkip.apply(self, qm, km, v, self._apply_mod("decay", decay, custom), s, d, None)
+        a = self._apply_mod("decay", decay, custom)
         vm = self._apply_mod("v", v, custom)
         o = self._scan(qm, km, vm, a)
         return o if self.o_mod is None else self._apply_o_mod(o, v, custom)

@@ -1012,6 +1012,7 @@ int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream) {
     return AE_ERR_INVALID;
   }
   a.h_out = p->h_states_out;
+  a.ascale = p->ascale;
   if (p->h_states_out) {
     const int64_t nc = (p->T + 127) / 128;
     if ((rc = make_3d_map(&a.tm_hout, p->h_states_out, m->cfg.dtype, m->cfg.head_dim_v, 128, (int64_t)p->B * p->H * nc, 128)))
@@ -1071,6 +1072,12 @@ static int fill_linear_bwd(Module* m, const AeLinearBwdParams* p, AeLinearBwdArg
       a->vscale_16 = p->vscale_16bit;
     }
   }
+  if (p->ascale && kind == AE_KIND_LINEAR_BWD && !p->gasc) {
+    set_error("linear attention backward: ascale needs gasc");
+    return AE_ERR_INVALID;
+  }
+  a->ascale = p->ascale;
+  a->gasc = p->gasc;
   a->a = p->a;
   a->h_states = p->h_states;
   a->dq = p->dq; a->dk = p->dk; a->dv = p->dv; a->da = p->da;

@@ -151,6 +151,7 @@ struct AeLinearArgs {
   AeTmaDesc tm_hout;  // h_out as [B * H * n_chunks, DK, DV], dims (dv, dk, n), box {64, 128, 1}   (when h_out is set)
   AeTmaDesc tm_vout;  // v_out like tm_v                                                       (when v_out is set)
   AeTmaDesc tm_o;     // o like tm_v: the output tile leaves through a bulk store
+  const float* ascale;  // [H] or null: the scan runs on a * ascale[h] (a decay mod of the form decay * custom[heads])
 };
 
 // ---- chunked linear attention backward (kernels ae_linear_states, ae_linear_bwd) ---------
@@ -178,6 +179,10 @@ struct AeLinearBwdArgs {
   void* gs;             // [B, H, T] in the type of vscale: sum_d dv * x
   float* gd;            // [B, H]: sum over t, d of dO * x
   int vscale_16;
+  // Any build: a decay mod of the form decay * custom[heads] inside the kernels.  The scan runs on a * ascale[h]; da is
+  // then the gradient of a as passed (times ascale[h]) and gasc [B, H] receives sum_t (gradient of the scaled decay) * a.
+  const float* ascale;  // [H] or null
+  float* gasc;          // [B, H] (required with ascale)
 };
 
 // ---- row-scale mod and its backward (kernels ae_rowscale_fwd, ae_rowscale_bwd) ---------------

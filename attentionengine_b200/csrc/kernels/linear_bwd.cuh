@@ -298,6 +298,10 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
     // this thread's log-decay of the chunk at hand, requested one chunk ahead (the load would otherwise sit at the top
     // of every chunk's chain)
     float a_next = ((n_chunks - 1) * AE_LB_C + (int)r) < args.T ? a_row[(n_chunks - 1) * AE_LB_C + (int)r] : 0.f;
+    // a decay mod of the form decay * custom[heads] (applied where the prefetched value is used): da leaves as the
+    // gradient of the decay as passed, and sum_t (gradient of the scaled decay) * decay is the gradient of the scale
+    const float asc = args.ascale ? args.ascale[h] : 1.f;
+    float acc_a = 0.f, araw_nxt = 0.f, araw_pend = 0.f;
 #if AE_LB_MODS
     // the row scale of v, requested a chunk ahead like the log-decay; the raw bits are kept until they are used
     // (converting at once would wait for the load right here)
@@ -349,12 +353,17 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
         if ((u32)w > (warp & 3)) after += misc[4 + w];
 #pragma unroll
       for (int w = 0; w < AE_LB_ROWW; ++w) next_carry += misc[8 + hp * 8 + w];
-      if (store_pend) args.da[bh * args.T + t_pend] = sfx + after + carry;
+      if (store_pend) {
+        const float da = sfx + after + carry;
+        args.da[bh * args.T + t_pend] = da * asc;
+        acc_a = fmaf(da, araw_pend, acc_a);
+      }
       carry = next_carry;
     };
     float g_nxt = 0.f;
     if (wg == 0) {
-      g_nxt = cum_sum(a_next, gs);
+      g_nxt = cum_sum(a_next * asc, gs);
+      araw_nxt = a_next;
       a_next = n_chunks >= 2 ? a_row[(n_chunks - 2) * AE_LB_C + (int)r] : 0.f;  // chunks before the last one are full
     }
     for (int it = 0; it < n_chunks; ++it) {
@@ -365,6 +374,7 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
       float* gc = gs + par * 128;  // this chunk's cumulative log-decays
       AE_TRL(warp == 0, 1, it * 16 + 0)
       float g = g_nxt, eg = 0.f, wj = 0.f;
+      const float araw_cur = araw_nxt;  // this row's decay as passed (first group)
 #if AE_LB_MODS
       const float vsc = vs16 ? unpack_lo<AE_BF16>(vs_next) : __uint_as_float(vs_next);
       vs_next = load_vs(t - AE_LB_C);
@@ -506,7 +516,8 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
       if (wg == 0) {  // under the chunk's last MMAs
         if (it > 0) finish_da((it - 1) & 1);
         if (c > 0) {
-          g_nxt = cum_sum(a_next, gs + (par ^ 1) * 128);
+          g_nxt = cum_sum(a_next * asc, gs + (par ^ 1) * 128);
+          araw_nxt = a_next;
           a_next = c >= 2 ? a_row[t - 2 * AE_LB_C] : 0.f;
         }
       }
@@ -641,11 +652,21 @@ extern "C" __global__ void __launch_bounds__(AE_LB_ROWW * 32 + 64, 1) ae_linear_
 #endif
         // the suffix sums of dG (-> da) follow under the next chunk's last MMAs
         dg_pend = dg;
+        araw_pend = araw_cur;
         t_pend = t;
         store_pend = store;
       }
     }
-    if (wg == 0) finish_da((n_chunks - 1) & 1);
+    if (wg == 0) {
+      finish_da((n_chunks - 1) & 1);
+      if (args.ascale) {  // gradient of the decay scale of this (batch, head)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o);
+        if (lane == 0) misc[warp & 3] = acc_a;
+        named_bar_sync(1, 128);
+        if (threadIdx.x == 0) args.gasc[bh] = misc[0] + misc[1] + misc[2] + misc[3];
+      }
+    }
 #if AE_LB_MODS
     // <dO, x> of this (batch, head): the row threads' sums meet in shared memory
 #pragma unroll

@@ -257,6 +257,8 @@ extern "C" __global__ void __launch_bounds__(AE_LIN_ROWW * 32 + 64, 1) ae_linear
     auto load_a = [&](int tt) { return tt < args.T ? a_row[tt] : 0.f; };
     const u32 wg = warp >> 2;  // 0: the group that also runs the cumulative sum
     float a_next = load_a((int)r);
+    // a decay mod of the form decay * custom[heads]; applied where the prefetched value is used, not where it is loaded
+    const float asc = args.ascale ? args.ascale[h] : 1.f;
 #if AE_LIN_MODS
     // the raw bits are kept until the value is used a chunk later: converting at once would wait for the load right here
     const bool vs16 = args.vscale_16 != 0;
@@ -290,7 +292,7 @@ extern "C" __global__ void __launch_bounds__(AE_LIN_ROWW * 32 + 64, 1) ae_linear
     };
     float g_nxt = 0.f;
     if (wg == 0) {
-      g_nxt = cum_sum(a_next, gs, cf_all);
+      g_nxt = cum_sum(a_next * asc, gs, cf_all);
       a_next = load_a(AE_LIN_C + (int)r);
     }
     for (int c = 0; c < n_chunks; ++c) {
@@ -470,7 +472,7 @@ extern "C" __global__ void __launch_bounds__(AE_LIN_ROWW * 32 + 64, 1) ae_linear
       mbar_arrive_warp(&bars->p_full);
       AE_TRL(warp == 0, 1, c * 16 + 8)
       if (wg == 0 && c + 1 < n_chunks) {  // under the P v MMAs
-        g_nxt = cum_sum(a_next, gs + ((c + 1) & 1) * 128, cf_all + ((c + 1) & 1) * 128);
+        g_nxt = cum_sum(a_next * asc, gs + ((c + 1) & 1) * 128, cf_all + ((c + 1) & 1) * 128);
         a_next = load_a(t + 2 * AE_LIN_C);
       }
       AE_TRL(warp == 0, 1, c * 16 + 11)

@@ -98,7 +98,7 @@ extern "C" __global__ void __launch_bounds__(192, 2) ae_linear_states(const __gr
     for (int c = 0; c < n_chunks; ++c) {
       const int stage = c % AE_LIN_STAGES;
       const int t = c * AE_LS_C + (int)r;
-      float g = t < args.T ? a_row[t] : 0.f;
+      float g = t < args.T ? a_row[t] * (args.ascale ? args.ascale[h] : 1.f) : 0.f;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float n = __shfl_up_sync(0xffffffffu, g, o);

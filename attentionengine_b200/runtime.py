@@ -108,7 +108,7 @@ class LinearParams(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("a", C.c_void_p), ("o", C.c_void_p),
                 ("B", C.c_int32), ("H", C.c_int32), ("HQ", C.c_int32), ("HK", C.c_int32), ("T", C.c_int32),
                 ("status", C.c_void_p), ("vscale", C.c_void_p), ("dskip", C.c_void_p), ("v_out", C.c_void_p),
-                ("vscale_16bit", C.c_int32), ("h_states_out", C.c_void_p)]
+                ("vscale_16bit", C.c_int32), ("h_states_out", C.c_void_p), ("ascale", C.c_void_p)]
 
 
 class LinearBwdParams(C.Structure):
@@ -116,7 +116,8 @@ class LinearBwdParams(C.Structure):
                 ("h_states", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("da", C.c_void_p),
                 ("B", C.c_int32), ("H", C.c_int32), ("HQ", C.c_int32), ("HK", C.c_int32), ("T", C.c_int32),
                 ("status", C.c_void_p), ("x", C.c_void_p), ("vscale", C.c_void_p), ("dskip", C.c_void_p),
-                ("gs", C.c_void_p), ("gd", C.c_void_p), ("vscale_16bit", C.c_int32)]
+                ("gs", C.c_void_p), ("gd", C.c_void_p), ("vscale_16bit", C.c_int32), ("ascale", C.c_void_p),
+                ("gasc", C.c_void_p)]
 
 
 _lib = None

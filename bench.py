@@ -274,6 +274,11 @@ def run_other(args):
         desc = ("Mamba2 SSD fwd+bwd with D_skip (v_mod and the skip inside the scan kernel, their backward inside the reverse pass, decay mod eager torch), B=8 L=8192 H=80 P=64 N=128 ngroups=1 bf16; FLOPs by "
                 "the chunk-256 convention, fwd (2Q^2N+2Q^2P+4QNP) per chunk and head, bwd counted as 2.5x fwd")
         desc = desc.replace("B=8 ", f"B={B} ")
+        # the MMAs the two scan kernels issue, at the chunk size they run (128): forward q k^T, q h, k^T v', P v; reverse
+        # pass three 128^3 products and six 128 x 128 x 64 ones per chunk and head
+        executed = 2.0 * 128 * 128 * ((128 + 3 * DV) + (3 * 128 + 6 * DV)) * (-(-T // 128)) * H * B
+        extra = {"executed_tflops_chunk128": executed / ms / 1e9,
+                 "note": "value counts FLOPs by the chunk-256 convention; executed_tflops_chunk128 counts the tensor-core products issued"}
         launches = 4 * args.steps  # scan (row scale, skip and the chunk states inside), reverse pass (their gradients inside), two head sums
         from oracle.linear_oracle import linear_scan
         xs, dt_s, As, Bs, Cs = helpers.mamba2_inputs(1, 2, 1024, DK, DV, dt, seed=0)
@@ -333,10 +338,11 @@ def run_other(args):
         raise SystemExit(f"unknown workload {wl}")
     clocks = sampler.stop()
     ach = value
+    cfg_extra = locals().get("extra", {})
     line = {"metric": desc, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16" if "fp16" not in desc else "f16", "data": "synthetic",
-            "config": {"workload": wl, "l2": "inputs larger than L2"}, "clocks": clocks, "e2e": None,
+            "config": {"workload": wl, "l2": "inputs larger than L2", **cfg_extra}, "clocks": clocks, "e2e": None,
             "gpu_launches": launches,
             "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": "TFLOP/s" if unit == "TFLOPS" else "GB/s",
                          "frac": ach / peak, "peak_source": f"{which}", "traffic": None, "kernel": "whole step"},

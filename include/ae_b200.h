@@ -317,6 +317,9 @@ typedef struct AeLinearParams {
    * ae_launch_linear_bwd, which then needs no ae_launch_linear_states (the reference's forward stores the same tensor,
    * linear_tl.py:142, 185-186). */
   void* h_states_out;
+  /* Any module, optional: a decay mod of the form `decay * custom[heads]` (Mamba2's `decay_mod = dt * A`,
+   * attn_script/mamba2_ngroup1.py:26-29) inside the kernel - the scan runs on a * ascale[h]. */
+  const float* ascale; /* [H] */
 } AeLinearParams;
 
 int ae_launch_linear_fwd(void* module, const AeLinearParams* p, void* stream);
@@ -386,6 +389,11 @@ typedef struct AeLinearBwdParams {
   void* gs;           /* out [B, H, T] in the type of vscale: sum over DV of dv * x */
   float* gd;          /* out [B, H]: sum over t and DV of d_o * x (sum it over B for the gradient of dskip) */
   int32_t vscale_16bit;
+  /* Any module, optional (both or neither): the forward ran with AeLinearParams.ascale.  `a` is the decay as passed
+   * there; `da` then receives the gradient of that tensor and gasc [B, H] the per-(batch, head) sums of
+   * (gradient of a * ascale[h]) * a - sum them over B for the gradient of ascale. */
+  const float* ascale; /* [H] */
+  float* gasc;         /* out [B, H] */
 } AeLinearBwdParams;
 
 int ae_launch_linear_states(void* module, const AeLinearBwdParams* p, void* stream);

@@ -608,6 +608,38 @@ def test_scan_reverse_pass_with_the_block_mods_inside_against_the_separate_kerne
     assert (fgd.double() - ref_gd).abs().max().item() <= 1e-4 * ref_gd.abs().max().item() + 1e-4
 
 
+@pytest.mark.parametrize("T", [456, 128, 1000])
+def test_decay_scale_inside_the_scan_kernels_against_the_eager_mod(T, monkeypatch):
+    """Mamba2's ``decay_mod = decay * A[heads]`` taken into the scan kernels (the forward scales the log-decay where it
+    uses it, the reverse pass returns the gradient of the decay as passed and the per-head sums for A) against the same
+    engine with the mod run as eager PyTorch: output and every tensor gradient bit for bit (the same fp32 products feed
+    the same kernels), the gradient of A within fp32 summation-order noise."""
+    from attentionengine_b200.attn_engine import linear_attn_engine as le
+    B, H, dt_ = 2, 3, torch.bfloat16
+    x, dt, A, Bm, Cm = helpers.mamba2_inputs(B, H, T, 128, 64, dt_, seed=T + 1)
+    Dk = torch.randn(1, H, generator=torch.Generator().manual_seed(17))
+    d_o = (0.1 * torch.randn(B, H, T, 64, generator=torch.Generator().manual_seed(18))).to(dt_).cuda()
+
+    def run(inside):
+        monkeypatch.setattr(le, "LIN_DECAY_SCALE", inside)
+        eng = helpers.mamba2_engine(B, H, T, 128, 64, dt_, d_skip=True)
+        leaves = [t.cuda().requires_grad_() for t in (Cm, Bm, x, dt, A.view(1, H), dt.to(dt_), Dk)]
+        y = eng(*leaves)
+        y.backward(d_o)
+        torch.cuda.synchronize()
+        eng.check_status()
+        return y.detach(), [t.grad for t in leaves]
+
+    y1, g1 = run(1)
+    y0, g0 = run(0)
+    assert torch.equal(y1, y0)
+    for name, a1, a0 in zip(("dC", "dB", "dx", "d(dt) through the decay", "dA", "d(dt) through v", "dD"), g1, g0):
+        if name == "dA":
+            assert (a1 - a0).abs().max().item() <= 1e-4 * a0.abs().max().item() + 1e-6, name
+        else:
+            assert torch.equal(a1, a0), name
+
+
 @pytest.mark.parametrize("n_split", [None, 1, 3])
 def test_mla_decode_paged_kv_with_ragged_lengths(n_split):
     """The call of the reference's CuTe kv-shared path (flash_mla_interface.py:73-113): a pool of 64-key pages in
