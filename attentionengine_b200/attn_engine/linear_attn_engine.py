@@ -28,6 +28,8 @@ from ..core.transform.graph import Var
 from ..lower.torch_eval import evaluate
 
 LIN_FWD_NWG = 2  # row warpgroups of the scan's forward kernel (measured: cfg4 3.72 against 4.14 ms)
+LIN_BWD_PARTS = 2  # batch ranges of the reverse pass on streams of their own when a head sum follows (1: one launch;
+                   # measured at cfg4: 3.31 ms with 1, 3.10 with 2, 3.11 with 4)
 LIN_DECAY_SCALE = 1  # a decay mod `decay * c[heads]` inside the scan kernels of the Mamba2 block (0: eager PyTorch)
 LIN_BWD_MODS = 1  # the row scale of v and the skip term inside the reverse pass (0: a streaming kernel after it)
 LIN_BWD_NWG = 2  # row warpgroups of the reverse pass of the scan (measured: 4.05 against 4.33 ms at cfg4)
@@ -193,6 +195,7 @@ class LinearAttentionEngine:
         self._status = None
         self._bwd = None
         self._bwd_mods = None
+        self._streams = {}
         self._fwd_by_dv = {}
         self._rowscale_mods = {}
         # The kernels work on blocks of 128 key dims x 64 or 128 value dims.  Larger heads (simple_gla / retention_linear
@@ -294,19 +297,66 @@ class LinearAttentionEngine:
         if ascale is not None:
             gasc = torch.empty(B, H, dtype=torch.float32, device=dev)
             p.ascale, p.gasc = ascale.data_ptr(), gasc.data_ptr()
-        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-        if recompute:
-            rt.check(rt.lib().ae_launch_linear_states(states.handle, C.byref(p), stream), "ae_launch_linear_states")
-        rt.check(rt.lib().ae_launch_linear_bwd(bwd.handle, C.byref(p), stream), "ae_launch_linear_bwd")
-        dq = dq_h if HQ == H else self._head_sum(dq_h, HQ)
-        dk = dk_h if HK == H else self._head_sum(dk_h, HK)
+        dq = dq_h if HQ == H else torch.empty(B, HQ, T, DK, dtype=self.dtype, device=dev)
+        dk = dk_h if HK == H else torch.empty(B, HK, T, DK, dtype=self.dtype, device=dev)
+        # Batch ranges on streams of their own when a head sum follows: the (batch, head) CTAs of all ranges fill the
+        # SMs in launch order as before, and the head sums of a range that is complete run under the later ranges'
+        # chunk walks (a latency-bound kernel next to an HBM-bound one) instead of after the whole pass.
+        n_parts = self._bwd_batch_parts(B, H, dev) if (HQ != H or HK != H) else 1
+        main = torch.cuda.current_stream(dev)
+        if n_parts > 1:
+            side, start, done = self._side_streams(dev, n_parts - 1)
+            start.record(main)
+        nb = B // n_parts
+        for i in range(n_parts):
+            st = main if i == 0 else side[i - 1]
+            if i:
+                st.wait_event(start)
+            sl = slice(i * nb, (i + 1) * nb)
+            p.q, p.k, p.v, p.a, p.d_o = (t[sl].data_ptr() for t in (q, k, v, a, d_o))
+            p.h_states, p.dq, p.dk, p.dv, p.da = (t[sl].data_ptr() for t in (hs, dq_h, dk_h, dv, da))
+            if mods is not None:
+                p.x, p.vscale, p.gs, p.gd = x[sl].data_ptr(), s[sl].data_ptr(), gs[sl].data_ptr(), gd[sl].data_ptr()
+            if ascale is not None:
+                p.gasc = gasc[sl].data_ptr()
+            p.B = nb
+            stream = C.c_void_p(st.cuda_stream)
+            if recompute:
+                rt.check(rt.lib().ae_launch_linear_states(states.handle, C.byref(p), stream), "ae_launch_linear_states")
+            rt.check(rt.lib().ae_launch_linear_bwd(bwd.handle, C.byref(p), stream), "ae_launch_linear_bwd")
+            if HQ != H:
+                self._head_sum(dq_h[sl], HQ, out=dq[sl], stream=st)
+            if HK != H:
+                self._head_sum(dk_h[sl], HK, out=dk[sl], stream=st)
+            if i:
+                done[i - 1].record(st)
+                main.wait_event(done[i - 1])
         out = (dq, dk, dv, da) + ((gs, gd) if mods is not None else ())
         return out + ((gasc,) if ascale is not None else ())
 
-    def _head_sum(self, x, n_out):
+    def _bwd_batch_parts(self, B, H, dev):
+        """Into how many batch ranges the reverse pass is split (see _launch_bwd): 4 or 2 when the batch divides and a
+        range still has one CTA per SM, else 1."""
+        want = int(os.environ.get("AE_B200_LIN_BWD_PARTS", LIN_BWD_PARTS))
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        for n in (4, 2):
+            if n <= want and B % n == 0 and (B // n) * H >= sms:
+                return n
+        return 1
+
+    def _side_streams(self, dev, n):
+        """n side streams of this engine on ``dev`` with an event to start them after the caller's stream and one each
+        to join them back."""
+        key = (dev.index if dev.index is not None else torch.cuda.current_device(), n)
+        if key not in self._streams:
+            self._streams[key] = ([torch.cuda.Stream(device=dev) for _ in range(n)], torch.cuda.Event(),
+                                  [torch.cuda.Event() for _ in range(n)])
+        return self._streams[key]
+
+    def _head_sum(self, x, n_out, out=None, stream=None):
         """[B, H, T, D] -> [B, n_out, T, D]: sum over the H / n_out heads of each group, fp32 accumulation, one pass."""
         B, H, T, D = x.shape
-        y = torch.empty(B, n_out, T, D, dtype=x.dtype, device=x.device)
+        y = out if out is not None else torch.empty(B, n_out, T, D, dtype=x.dtype, device=x.device)
         key = ("head_sum", D, False)
         if key not in self._rowscale_mods:
             pre = f"#define AE_BF16 {int(self._bf16)}\n#define AE_RS_D {D}\n#define AE_RS_S16 0\n"
@@ -315,7 +365,7 @@ class LinearAttentionEngine:
             self._rowscale_mods[key] = rt.compile_module(rt.kernel_source("rowscale.cuh", prelude=pre), "ae_head_sum", cfg)
         p = rt.RowScaleParams()
         p.x, p.y, p.n_rows, p.rows_per_head, p.n_heads = x.data_ptr(), y.data_ptr(), B * n_out * T, T, H // n_out
-        stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+        stream = C.c_void_p((stream if stream is not None else torch.cuda.current_stream(x.device)).cuda_stream)
         rt.check(rt.lib().ae_launch_rowscale(self._rowscale_mods[key].handle, C.byref(p), stream), "ae_launch_rowscale")
         return y
 

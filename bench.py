@@ -279,7 +279,7 @@ def run_other(args):
         executed = 2.0 * 128 * 128 * ((128 + 3 * DV) + (3 * 128 + 6 * DV)) * (-(-T // 128)) * H * B
         extra = {"executed_tflops_chunk128": executed / ms / 1e9,
                  "note": "value counts FLOPs by the chunk-256 convention; executed_tflops_chunk128 counts the tensor-core products issued"}
-        launches = 4 * args.steps  # scan (row scale, skip and the chunk states inside), reverse pass (their gradients inside), two head sums
+        launches = 7 * args.steps  # scan (row scale, skip, decay scale and the chunk states inside); per batch half: reverse pass (their gradients inside) and two head sums
         from oracle.linear_oracle import linear_scan
         xs, dt_s, As, Bs, Cs = helpers.mamba2_inputs(1, 2, 1024, DK, DV, dt, seed=0)
         t0 = time.perf_counter()

@@ -640,6 +640,37 @@ def test_decay_scale_inside_the_scan_kernels_against_the_eager_mod(T, monkeypatc
             assert torch.equal(a1, a0), name
 
 
+@pytest.mark.parametrize("parts", [2, 4])
+def test_reverse_pass_in_batch_ranges_on_side_streams_equals_one_launch(parts, monkeypatch):
+    """The reverse pass split into batch ranges, each on a stream of its own with its head sums behind it (what the
+    engine does at sizes where a range still fills the SMs), against one launch: every gradient bit for bit - a
+    (batch, head) CTA does the same work either way - also when the caller's stream is not the default one."""
+    from attentionengine_b200.attn_engine import linear_attn_engine as le
+    B, H, T, dt_ = 4, 2, 300, torch.bfloat16
+    x, dt, A, Bm, Cm = helpers.mamba2_inputs(B, H, T, 128, 64, dt_, seed=parts)
+    Dk = torch.randn(1, H, generator=torch.Generator().manual_seed(19))
+    d_o = (0.1 * torch.randn(B, H, T, 64, generator=torch.Generator().manual_seed(20))).to(dt_).cuda()
+
+    def run(n, stream):
+        monkeypatch.setattr(le.LinearAttentionEngine, "_bwd_batch_parts", lambda self, B_, H_, dev: n)
+        eng = helpers.mamba2_engine(B, H, T, 128, 64, dt_, d_skip=True)
+        leaves = [t.cuda().requires_grad_() for t in (Cm, Bm, x, dt, A.view(1, H), dt.to(dt_), Dk)]
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            for _ in range(2):  # the second call reuses the engine's side streams and events
+                for t in leaves:
+                    t.grad = None
+                eng(*leaves).backward(d_o)
+        torch.cuda.synchronize()
+        eng.check_status()
+        return [t.grad for t in leaves]
+
+    one = run(1, torch.cuda.current_stream())
+    split = run(parts, torch.cuda.Stream())
+    for name, a1, a0 in zip(("dC", "dB", "dx", "d(dt) through the decay", "dA", "d(dt) through v", "dD"), split, one):
+        assert torch.equal(a1, a0), name
+
+
 @pytest.mark.parametrize("n_split", [None, 1, 3])
 def test_mla_decode_paged_kv_with_ragged_lengths(n_split):
     """The call of the reference's CuTe kv-shared path (flash_mla_interface.py:73-113): a pool of 64-key pages in
