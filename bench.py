@@ -575,7 +575,9 @@ def main():
             tf, t = cpu_sample(16, threads)
             cpu = {"value": tf, "unit": "TFLOPS", "cores": threads, "kind": "port", "seconds": round(t, 2),
                    "sample": "16 of 64 (batch, kv-group) slices: 4 q-heads x S=8192 x D=128 vs one kv-head, fwd+bwd, fp32 torch"}
-        n_launch = (4 if mode == "fused" else 4) * args.steps  # fwd, prep, fused + cast | fwd, prep, dQ pass, dK/dV pass
+        # fwd, then per batch range of the one-pass backward: prep, fused, cast | fwd, prep, dQ pass, dK/dV pass
+        from attentionengine_b200.attn_engine import attn_bwd as _ab
+        n_launch = ((1 + 3 * _ab._batch_parts(B, 32, 8192, dev)) if mode == "fused" else 4) * args.steps
         line = {"metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": args.scaling,
                 "vs_baseline": None, "dtype": "f16", "data": "synthetic",

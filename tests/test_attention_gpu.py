@@ -641,6 +641,33 @@ def test_decay_scale_inside_the_scan_kernels_against_the_eager_mod(T, monkeypatc
 
 
 @pytest.mark.parametrize("parts", [2, 4])
+def test_attention_backward_in_batch_ranges_on_side_streams(parts, monkeypatch):
+    """The one-pass attention backward launched as batch ranges on streams of their own (an opt-in, AE_B200_BWD_PARTS)
+    against one launch: dK and dV bit for bit, dQ within the order noise of its fp32 accumulation."""
+    from attentionengine_b200.attn_engine import attn_bwd as ab
+    B, Hq, Hkv, S, D, dtype = 4, 4, 2, 384, 64, torch.float16
+    g = torch.Generator().manual_seed(40 + parts)
+    q, k, v, d_o = (torch.randn(B, S, h, D, generator=g).to(dtype).cuda() for h in (Hq, Hkv, Hkv, Hq))
+    eng = helpers.softmax_engine(B, Hq, Hkv, S, D, D, dtype, True)
+    eng.bwd_mode = "fused"
+
+    def run(n):
+        monkeypatch.setattr(ab, "_batch_parts", lambda B_, Hq_, Sq_, dev: n)
+        leaves = [t.clone().requires_grad_() for t in (q, k, v)]
+        for _ in range(2):
+            for t in leaves:
+                t.grad = None
+            eng(*leaves).backward(d_o)
+        torch.cuda.synchronize()
+        eng.check_status()
+        return [t.grad for t in leaves]
+
+    one, split = run(1), run(parts)
+    assert torch.equal(split[1], one[1]) and torch.equal(split[2], one[2])
+    assert (split[0].float() - one[0].float()).abs().max().item() <= 2e-3 * one[0].float().abs().max().item()
+
+
+@pytest.mark.parametrize("parts", [2, 4])
 def test_reverse_pass_in_batch_ranges_on_side_streams_equals_one_launch(parts, monkeypatch):
     """The reverse pass split into batch ranges, each on a stream of its own with its head sums behind it (what the
     engine does at sizes where a range still fills the SMs), against one launch: every gradient bit for bit - a
