@@ -532,6 +532,10 @@ class LinearAttentionEngine:
         for name, t in (("q", q), ("k", k), ("v", v), ("decay", decay)):
             if not t.is_cuda:
                 raise rt.AeError(f"{name} must be a CUDA tensor: this back end has no CPU path")
+        with torch.cuda.device(q.device):  # the C ABI launches on the current device's context
+            return self._call(q, k, v, decay, *custom)
+
+    def _call(self, q, k, v, decay, *custom):
         if q.dtype != self.dtype or k.dtype != self.dtype or v.dtype != self.dtype:
             raise TypeError(f"q/k/v must be {self.dtype}")
         if len(custom) != len(self.custom_io.input_tensors):
