@@ -167,13 +167,19 @@ def _s3(t):
 BWD_PARTS = 4
 
 
+def batch_ranges(B: int, ctas_per_batch_row: int, sms: int, want: int, min_rounds: int = 1) -> int:
+    """Into how many equal batch ranges (4, 2 or 1) a pass over B batch rows is launched: at most ``want``, the batch
+    has to divide, and a range must still bring ``min_rounds`` CTAs per SM."""
+    for n in (4, 2):
+        if n <= want and B % n == 0 and (B // n) * ctas_per_batch_row >= min_rounds * sms:
+            return n
+    return 1
+
+
 def _batch_parts(B, Hq, Sq, dev):
     want = int(os.environ.get("AE_B200_BWD_PARTS", BWD_PARTS))
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    for n in (4, 2):
-        if n <= want and B % n == 0 and (B // n) * Hq * ((Sq + 127) // 128) >= 8 * sms:
-            return n
-    return 1
+    return batch_ranges(B, Hq * ((Sq + 127) // 128), sms, want, min_rounds=8)
 
 
 def _side_streams(eng, dev, n):

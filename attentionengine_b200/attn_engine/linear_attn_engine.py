@@ -337,12 +337,9 @@ class LinearAttentionEngine:
     def _bwd_batch_parts(self, B, H, dev):
         """Into how many batch ranges the reverse pass is split (see _launch_bwd): 4 or 2 when the batch divides and a
         range still has one CTA per SM, else 1."""
+        from .attn_bwd import batch_ranges
         want = int(os.environ.get("AE_B200_LIN_BWD_PARTS", LIN_BWD_PARTS))
-        sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        for n in (4, 2):
-            if n <= want and B % n == 0 and (B // n) * H >= sms:
-                return n
-        return 1
+        return batch_ranges(B, H, torch.cuda.get_device_properties(dev).multi_processor_count, want)
 
     def _side_streams(self, dev, n):
         """n side streams of this engine on ``dev`` with an event to start them after the caller's stream and one each

@@ -49,3 +49,18 @@ def test_engine_takes_its_tile_choice_from_the_tune_file(tmp_path, monkeypatch):
     monkeypatch.setattr(tune, "PACKAGE_FILE", tmp_path / "absent.json")
     plain = helpers.softmax_engine(1, 4, 2, 512, 64, 64, torch.float16, True)
     assert plain.tuned_config == {} and plain.kernels.stages == 2 and plain.bwd_mode is None
+
+
+def test_batch_ranges_of_the_backward_launches():
+    """The backward passes are launched as 4, 2 or 1 batch ranges: never more than asked for, only when the batch
+    divides, and only while a range still brings the required number of CTAs per SM."""
+    # the 8K GQA problem: 32 heads x 64 kv tiles per batch row, eight rounds of 148 SMs asked per range
+    assert ab.batch_ranges(8, 32 * 64, 148, 4, min_rounds=8) == 4
+    assert ab.batch_ranges(8, 32 * 64, 148, 2, min_rounds=8) == 2
+    assert ab.batch_ranges(8, 32 * 64, 148, 1, min_rounds=8) == 1
+    assert ab.batch_ranges(1, 32 * 64, 148, 4, min_rounds=8) == 1      # one batch row per rank at eight ranks
+    assert ab.batch_ranges(6, 32 * 64, 148, 4, min_rounds=8) == 2      # 6 rows do not divide by 4
+    assert ab.batch_ranges(4, 4 * 3, 148, 4, min_rounds=8) == 1        # small problems stay one launch
+    # the scan's reverse pass: one CTA per (batch row, head), 80 heads
+    assert ab.batch_ranges(8, 80, 148, 2) == 2 and ab.batch_ranges(8, 80, 148, 4) == 4
+    assert ab.batch_ranges(2, 80, 148, 4) == 1                         # a single row would leave SMs empty
