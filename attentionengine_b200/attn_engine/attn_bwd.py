@@ -224,7 +224,10 @@ def launch_bwd(eng, q, k, v, o, d_o, finals, custom, lists=None):
     p.status = eng._get_status(dev).data_ptr()
     stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
     L = rt.lib()
-    n_parts = _batch_parts(B, Hq, Sq, dev) if (mode == "fused" and lists is None and not custom) else 1
+    # custom tensors may come along when none of them is indexed by the batch (stride slot 0): the kernels of a range
+    # then see the same pointers and strides
+    batch_free = all(p.custom_stride[i][0] == 0 for i in range(rt.AE_MAX_CUSTOM))
+    n_parts = _batch_parts(B, Hq, Sq, dev) if (mode == "fused" and lists is None and batch_free) else 1
     if n_parts > 1:
         # Batch ranges on streams of their own: the HBM-bound kernels around the main one (clearing the fp32 dQ buffer,
         # delta = rowsum(O dO), the cast of dQ) of one range run next to the tensor-bound main kernel of another

@@ -237,7 +237,11 @@ def run_other(args):
         work = 3.5 * 4.0 * B * H * S * S * D
         value, unit, bound, peak = work / ms / 1e9, "TFLOPS", "tensor", float(peaks.get("bf16_tflops", 1590.0))
         desc = f"{wl[5:]} attention fwd+bwd, B=4 H=32 S=4096 D=128 bf16 non-causal"
-        launches = 3 * args.steps
+        # forward; per batch range of the one-pass backward the main kernel and the dQ cast, and the delta pre-pass where
+        # the functor needs it (the ranges apply when no custom tensor is indexed by the batch)
+        from attentionengine_b200.attn_engine import attn_bwd as _ab
+        n_rng = _ab._batch_parts(B, H, S, dev)  # the sigmoid bias is one scalar: no batch index
+        launches = (1 + n_rng * (2 + int(eng.lowered.uses_doosum))) * args.steps
         g = torch.Generator().manual_seed(0)
         qs, ks, vs, ds = (torch.randn(1, S, 2, D, generator=g).to(dt) for _ in range(4))
         fn = ((lambda a, b, c: orc.sigmoid_attention(a, b, c, bias=-math.log(S))) if wl == "cfg3_sigmoid"

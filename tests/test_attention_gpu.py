@@ -640,15 +640,23 @@ def test_decay_scale_inside_the_scan_kernels_against_the_eager_mod(T, monkeypatc
             assert torch.equal(a1, a0), name
 
 
+@pytest.mark.parametrize("kind", ["softmax", "sigmoid"])
 @pytest.mark.parametrize("parts", [2, 4])
-def test_attention_backward_in_batch_ranges_on_side_streams(parts, monkeypatch):
-    """The one-pass attention backward launched as batch ranges on streams of their own (an opt-in, AE_B200_BWD_PARTS)
-    against one launch: dK and dV bit for bit, dQ within the order noise of its fp32 accumulation."""
+def test_attention_backward_in_batch_ranges_on_side_streams(parts, kind, monkeypatch):
+    """The one-pass attention backward launched as batch ranges on streams of their own (what the engine does at sizes
+    where a range still fills the SMs several times over) against one launch: dK and dV bit for bit, dQ within the
+    order noise of its fp32 accumulation.  The sigmoid case carries a custom tensor that has no batch index (the
+    scalar bias), which travels with every range."""
     from attentionengine_b200.attn_engine import attn_bwd as ab
-    B, Hq, Hkv, S, D, dtype = 4, 4, 2, 384, 64, torch.float16
+    B, Hq, Hkv, S, D = 4, 4, 2, 384, 64
     g = torch.Generator().manual_seed(40 + parts)
+    if kind == "softmax":
+        dtype = torch.float16
+        eng, custom = helpers.softmax_engine(B, Hq, Hkv, S, D, D, dtype, True), ()
+    else:
+        dtype, Hkv = torch.bfloat16, Hq
+        eng, custom = helpers.sigmoid_engine(B, Hq, S, D, dtype, False), (torch.tensor([-math.log(S)], device="cuda"),)
     q, k, v, d_o = (torch.randn(B, S, h, D, generator=g).to(dtype).cuda() for h in (Hq, Hkv, Hkv, Hq))
-    eng = helpers.softmax_engine(B, Hq, Hkv, S, D, D, dtype, True)
     eng.bwd_mode = "fused"
 
     def run(n):
@@ -657,7 +665,7 @@ def test_attention_backward_in_batch_ranges_on_side_streams(parts, monkeypatch):
         for _ in range(2):
             for t in leaves:
                 t.grad = None
-            eng(*leaves).backward(d_o)
+            eng(*leaves, *custom).backward(d_o)
         torch.cuda.synchronize()
         eng.check_status()
         return [t.grad for t in leaves]
