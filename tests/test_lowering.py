@@ -111,6 +111,27 @@ def test_row_scale_mod_is_recognised_in_the_trace():
     assert e._rowscale_operand("v", x, (A, dt[:1])) is None  # a broadcast batch dim is left to PyTorch
 
 
+def test_decay_scale_and_skip_are_recognised_in_the_trace():
+    """`decay * custom[1, heads]` (Mamba2's decay_mod) and `o + v * custom[1, heads]` (the skip) are taken into the
+    scan kernels when their operands are fp32 with one value per head; anything else stays eager PyTorch."""
+    from attentionengine_b200.attn_engine import LinearAttentionEngine
+    from attentionengine_b200.core import CustomIO, meta_tensor
+    e = helpers.mamba2_engine(2, 4, 256, 128, 64, torch.bfloat16, d_skip=True)
+    decay = torch.zeros(2, 4, 256)
+    A, dt, D = torch.zeros(1, 4), torch.zeros(2, 4, 256, dtype=torch.bfloat16), torch.zeros(1, 4)
+    assert e._decay_scale_operand(decay, (A, dt, D)) is A
+    assert e._skip_operand((A, dt, D)) is D
+    assert e._decay_scale_operand(decay.double(), (A, dt, D)) is None          # the kernels read an fp32 decay
+    assert e._decay_scale_operand(decay, (A.to(torch.bfloat16), dt, D)) is None  # ... and an fp32 scale
+    metas = (meta_tensor(2, 1, 256, 128, dtype=torch.bfloat16),) * 2 + (meta_tensor(2, 4, 256, 64, dtype=torch.bfloat16),)
+    other = LinearAttentionEngine(metas, decay_mod=lambda decay, io: decay + io.input_tensors["A"],
+                                  custom_io=CustomIO({"A": (1, "heads")}))
+    assert other._decay_scale_operand(decay, (A,)) is None                     # not a product
+    per_step = LinearAttentionEngine(metas, decay_mod=lambda decay, io: decay * io.input_tensors["w"],
+                                     custom_io=CustomIO({"w": ("batch", "heads", "seq_len")}))
+    assert per_step._decay_scale_operand(decay, (torch.zeros(2, 4, 256),)) is None  # one value per step: eager
+
+
 def test_block_lists_layout():
     from attentionengine_b200.attn_engine.attn_engine import _block_lists
     cnt = torch.tensor([[[[128 * 128, 0, 5], [0, 0, 0], [1, 128 * 128, 128 * 128]]]], dtype=torch.int32)
